@@ -1,0 +1,301 @@
+"""CPU restatement of the MSA routing / sparse-attention hot path.  TEST INFRASTRUCTURE ONLY.
+
+This module is the checker for the CUDA kernels of ``msa_b200``.  It restates, in plain
+fp32 torch ops on the CPU, the algorithm of the EverMind-AI/MSA reference for:
+
+  * stage-1 chunk bookkeeping + chunk-mean pooling
+        src/msa/memory_sparse_attention.py:138-194, 467-486
+  * routing scores, reductions, per-shard top-k
+        src/msa_service.py:703-828
+  * query gather, cross-rank merge, fetch and regroup
+        src/msa_service.py:1088-1314
+  * decode attention over the compact cache
+        src/msa/memory_sparse_attention.py:361-405
+
+Only ``tests/``, ``__graft_entry__.smoke()`` and the CPU-baseline / reference legs of
+``bench.py`` may import it.  The product package never does.
+
+Pinning: the reference ships no tests, golden vectors or fixtures for this path.  The pin
+is the reference's own code executed on CPU in the authoring container:
+``tests/golden/make_golden.py`` imports the reference, runs it on seeded inputs and stores
+inputs and outputs under ``tests/golden/*.npz``; ``tests/test_oracle_golden.py`` checks every
+function below against those files.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn.functional as F
+
+
+# --------------------------------------------------------------------------------------
+# Stage 1: chunk bookkeeping and chunk-mean pooling
+# --------------------------------------------------------------------------------------
+
+def chunk_bookkeeping(doc_ids: torch.Tensor, attention_mask: torch.Tensor, pooling_kernel_size: int):
+    """Per document token: which chunk it falls in; per chunk: owning (1-based) doc id.
+
+    Follows src/msa/memory_sparse_attention.py:138-163.  ``doc_ids`` is ``[B, T]`` int64 with
+    >0 = memory document (1-based within the block), 0 = query, -1 = response, -2 = template.
+
+    Returns ``(doc_indices[Td,2], global_chunk_ids[Td], pooled_doc_ids[C], chunk_lengths[C])``.
+    """
+    q_len = doc_ids.shape[1]
+    max_doc_id = int(doc_ids.max().item())
+    doc_token_mask = (doc_ids > 0) & (attention_mask == 1)
+    doc_indices = torch.nonzero(doc_token_mask, as_tuple=False)
+    original_doc_ids = doc_ids[doc_token_mask]
+    global_doc_ids = doc_indices[:, 0] * (max_doc_id + 1) + original_doc_ids
+    _, counts = torch.unique_consecutive(global_doc_ids, return_counts=True)
+    total = global_doc_ids.shape[0]
+    offsets = torch.zeros(counts.shape[0] + 1, dtype=counts.dtype)
+    offsets[1:] = counts.cumsum(0)
+    offsets = offsets[:-1]
+    ranks = torch.arange(total) - torch.repeat_interleave(offsets, counts)
+    chunk_indices = ranks // pooling_kernel_size
+    max_chunks_per_doc = (q_len // pooling_kernel_size) + 1
+    global_chunk_ids = global_doc_ids * max_chunks_per_doc + chunk_indices
+    uniq, chunk_lengths = torch.unique_consecutive(global_chunk_ids, return_counts=True)
+    pooled_doc_ids = uniq // max_chunks_per_doc % (max_doc_id + 1)
+    return doc_indices, global_chunk_ids, pooled_doc_ids, chunk_lengths
+
+
+def pool_chunks_cumsum(states: torch.Tensor, chunk_lengths: torch.Tensor) -> torch.Tensor:
+    """Chunk mean exactly as the reference computes it: fp32 cumulative sum over the token
+    axis, difference at chunk boundaries, divide by the chunk's token count, cast back.
+
+    ``states`` is ``[T, H, D]`` (doc tokens only, in order); returns ``[C, H, D]``.
+    src/msa/memory_sparse_attention.py:475-482 (and the inline K_r copy at :181-188).
+    """
+    t, h, d = states.shape
+    flat = states.reshape(t, -1).to(torch.float32)
+    cs = F.pad(torch.cumsum(flat, dim=0), (0, 0, 1, 0))
+    cu = F.pad(torch.cumsum(chunk_lengths, 0), (1, 0))
+    sums = cs[cu[1:]] - cs[cu[:-1]]
+    out = sums.view(chunk_lengths.shape[0], h, d) / chunk_lengths.view(-1, 1, 1).to(torch.float32)
+    return out.to(states.dtype)
+
+
+def pool_chunks_exact(states: torch.Tensor, chunk_lengths: torch.Tensor) -> torch.Tensor:
+    """fp64 direct per-chunk mean: the ground truth both the reference's cumsum-difference and
+    the CUDA kernel's direct fp32 sum are judged against (norm-wise)."""
+    t, h, d = states.shape
+    x = states.reshape(t, -1).to(torch.float64)
+    cu = F.pad(torch.cumsum(chunk_lengths, 0), (1, 0)).tolist()
+    out = torch.stack([x[cu[i]:cu[i + 1]].mean(0) for i in range(len(cu) - 1)])
+    return out.view(-1, h, d)
+
+
+def sequence_pooling_kv(key_states, value_states, doc_indices, global_chunk_ids):
+    """src/msa/memory_sparse_attention.py:467-486.  ``key_states`` ``[B, H, T, D]``."""
+    k_docs = key_states[doc_indices[:, 0], :, doc_indices[:, 1]]
+    v_docs = value_states[doc_indices[:, 0], :, doc_indices[:, 1]]
+    _, lengths = torch.unique_consecutive(global_chunk_ids, return_counts=True)
+    return pool_chunks_cumsum(k_docs, lengths), pool_chunks_cumsum(v_docs, lengths)
+
+
+def l2_normalize(x: torch.Tensor) -> torch.Tensor:
+    """``F.normalize(x, p=2, dim=-1)``: x / max(||x||, 1e-12), computed in x's dtype
+    (src/msa/memory_sparse_attention.py:192-194, 264-265)."""
+    return F.normalize(x, p=2, dim=-1)
+
+
+# --------------------------------------------------------------------------------------
+# Routing: score, reduce, select (one shard)
+# --------------------------------------------------------------------------------------
+
+def route_chunk_scores(q: torch.Tensor, mask: torch.Tensor, rk: torch.Tensor,
+                       head_reduce: str = "mean", query_reduce: str = "max") -> torch.Tensor:
+    """Per (sample, chunk) score before the chunk->doc reduction.
+
+    q ``[B, Hkv, G, S, D]``, mask ``[B, S]`` bool (True = routing-query token),
+    rk ``[Hkv, C, D]``.  src/msa_service.py:730-780.  Computation in q's dtype
+    (fp32 for the oracle proper)."""
+    b, hkv, g, s, d = q.shape
+    min_val = torch.finfo(q.dtype).min
+    scores = torch.matmul(q, rk.transpose(-1, -2).unsqueeze(0).unsqueeze(2))  # [B,Hkv,G,S,C]
+    scores = scores.masked_fill(~mask.view(b, 1, 1, s, 1), min_val).flatten(1, 2)  # [B,32,S,C]
+    if head_reduce == "max":
+        scores = scores.max(dim=1).values
+    elif head_reduce == "mean":
+        scores = scores.mean(dim=1)
+    else:
+        raise NotImplementedError(head_reduce)
+    if query_reduce == "max":
+        return scores.max(dim=1).values
+    if query_reduce == "mean":
+        m = mask.view(b, s, 1)
+        summed = torch.where(m, scores, torch.zeros_like(scores)).sum(dim=1)
+        return summed / m.sum(dim=1).clamp(min=1.0)
+    if query_reduce == "last":
+        last = (mask.sum(dim=1).long() - 1).clamp(min=0)
+        return scores.gather(1, last.view(b, 1, 1).expand(-1, 1, scores.shape[-1])).squeeze(1)
+    raise NotImplementedError(query_reduce)
+
+
+def route_doc_scores(q, mask, rk, pool_ids: torch.Tensor, nr_docs: int,
+                     head_reduce="mean", query_reduce="max", chunk_reduce="max",
+                     slice_chunks: int = 16384) -> torch.Tensor:
+    """Score table ``[B, nr_docs + 1]``; column 0 is the dummy document and every column
+    starts at ``finfo(dtype).min`` (src/msa_service.py:716-717, 785-820).  ``pool_ids`` is the
+    1-based local doc id of each chunk.  Chunks are processed in slices only to bound the
+    temporary; results do not depend on the slicing."""
+    b = q.shape[0]
+    c = rk.shape[1]
+    min_val = torch.finfo(q.dtype).min
+    table = torch.full((b, nr_docs + 1), min_val, dtype=q.dtype)
+    if chunk_reduce == "mean":
+        sums = torch.zeros((b, nr_docs + 1), dtype=q.dtype)
+        cnts = torch.zeros((nr_docs + 1,), dtype=q.dtype)
+    for c0 in range(0, c, slice_chunks):
+        c1 = min(c, c0 + slice_chunks)
+        cs = route_chunk_scores(q, mask, rk[:, c0:c1], head_reduce, query_reduce)  # [B, c]
+        idx = pool_ids[c0:c1].view(1, -1).expand(b, -1)
+        if chunk_reduce == "max":
+            table.scatter_reduce_(1, idx, cs, reduce="amax", include_self=True)
+        elif chunk_reduce == "mean":
+            sums.scatter_add_(1, idx, cs)
+            cnts.scatter_add_(0, pool_ids[c0:c1], torch.ones(c1 - c0, dtype=q.dtype))
+        else:
+            raise ValueError(chunk_reduce)
+    if chunk_reduce == "mean":
+        mean = sums / cnts.clamp(min=1.0)
+        table = torch.where(cnts.view(1, -1) > 0, torch.maximum(mean, table), table)
+    return table
+
+
+def prefill_stage2(q, mask, rk, pool_ids, doc_ids_table: torch.Tensor, top_k: int, **kw):
+    """Per-shard selection.  Returns ``(scores[B,k'], local_ids[B,k'], global_ids[B,k'])`` with
+    ``k' = min(top_k, nr_docs + 1)`` sorted by descending score; ``doc_ids_table`` is the
+    local->global table whose slot 0 is the dummy (src/msa_service.py:207-219, 826-828)."""
+    nr_docs = doc_ids_table.shape[0] - 1
+    table = route_doc_scores(q, mask, rk, pool_ids, nr_docs, **kw)
+    scores, local_ids = torch.topk(table, k=min(top_k, table.shape[1]), dim=1)
+    return scores, local_ids, doc_ids_table[local_ids]
+
+
+# --------------------------------------------------------------------------------------
+# Memory Parallel: all ranks of one node emulated in one process
+# --------------------------------------------------------------------------------------
+
+class Shard:
+    """One rank's bank for one layer: pooled K, V, K_r ``[Hkv, C, D]`` plus the tables of
+    src/msa_service.py:191-231 (``doc_ids`` local->global with dummy slot 0, per-doc chunk
+    offsets and lengths, ``pool_ids`` 1-based doc per chunk)."""
+
+    def __init__(self, k, v, rk, chunks_per_doc: Sequence[int], global_ids: Sequence[int]):
+        self.k, self.v, self.rk = k, v, rk
+        lens = [0] + list(chunks_per_doc)
+        self.doc_lens = torch.tensor(lens, dtype=torch.long)
+        self.doc_offsets = torch.cumsum(torch.tensor([0] + lens[:-1], dtype=torch.long), 0)
+        self.doc_ids = torch.tensor([0] + list(global_ids), dtype=torch.long)
+        self.pool_ids = torch.repeat_interleave(torch.arange(len(lens)), self.doc_lens)
+        assert self.pool_ids.shape[0] == rk.shape[1]
+
+
+def doc_query_world(queries: List[torch.Tensor], masks: List[torch.Tensor], shards: List[Shard],
+                    top_k: int, num_kv_groups: int, scaling: float = -1.0,
+                    shard_top_k: Optional[int] = None, **reduce_kw):
+    """What ``MSAService.doc_query`` returns on every rank of a W-rank job
+    (src/msa_service.py:1133-1314), computed in one process.
+
+    queries[r] ``[B, Hq, S_r, D]``, masks[r] ``[B, S_r]``.  Returns a list, one entry per
+    rank: ``(final_k[Hkv,sumN,D], final_v, final_scores[B,k], n_sel[B], winner_global_ids[B,k])``.
+
+    Entry order inside a sample is (owner rank, local doc id, chunk), as the reference's
+    unique()/all-to-all produce (:1214, :1236-1244, :1289-1306).  One deliberate difference:
+    winners whose score is <= -1e9 select nothing here, whereas the reference still matches
+    their (dummy) global id against received chunks (:1289).
+    """
+    w = len(shards)
+    k_shard = shard_top_k or top_k
+    out = []
+    # every rank scores every rank's queries against its own shard (:1153-1161)
+    cand = [[None] * w for _ in range(w)]  # cand[owner][target]
+    for owner, sh in enumerate(shards):
+        for target in range(w):
+            q = queries[target]
+            if scaling > 0:
+                q = q * scaling
+            b, hq, s, d = q.shape
+            q5 = q.view(b, hq // num_kv_groups, num_kv_groups, s, d)
+            cand[owner][target] = prefill_stage2(q5, masks[target], sh.rk, sh.pool_ids, sh.doc_ids,
+                                                 k_shard, **reduce_kw)
+    for target in range(w):
+        b = queries[target].shape[0]
+        sc = torch.cat([cand[o][target][0] for o in range(w)], dim=1)
+        li = torch.cat([cand[o][target][1] for o in range(w)], dim=1)
+        gi = torch.cat([cand[o][target][2] for o in range(w)], dim=1)
+        rk_ = torch.cat([torch.full_like(cand[o][target][1], o) for o in range(w)], dim=1)
+        k_eff = min(top_k, sc.shape[1])
+        fs, fi = torch.topk(sc, k=k_eff, dim=1)
+        wl, wg, wr = li.gather(1, fi), gi.gather(1, fi), rk_.gather(1, fi)
+        valid = fs > -1e9
+        ks, vs, nsel = [], [], []
+        for i in range(b):
+            n = 0
+            for o in range(w):
+                ids = wl[i][(wr[i] == o) & valid[i]]
+                for lid in sorted(set(ids.tolist())):
+                    if lid <= 0:
+                        continue
+                    off, ln = int(shards[o].doc_offsets[lid]), int(shards[o].doc_lens[lid])
+                    ks.append(shards[o].k[:, off:off + ln])
+                    vs.append(shards[o].v[:, off:off + ln])
+                    n += ln
+            nsel.append(n)
+        hkv, _, d = shards[0].k.shape
+        fk = torch.cat(ks, dim=1) if ks else torch.empty(hkv, 0, d, dtype=shards[0].k.dtype)
+        fv = torch.cat(vs, dim=1) if vs else torch.empty(hkv, 0, d, dtype=shards[0].v.dtype)
+        out.append((fk, fv, fs, torch.tensor(nsel, dtype=torch.long), wg))
+    return out
+
+
+# --------------------------------------------------------------------------------------
+# Decode attention over the compact cache
+# --------------------------------------------------------------------------------------
+
+def decode_attention(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor,
+                     kv_lengths: torch.Tensor, new_k: torch.Tensor, new_v: torch.Tensor,
+                     scale: Optional[float] = None) -> torch.Tensor:
+    """One decode step.  q ``[B, Hq, 1, D]``; cache ``[B, Hkv, maxL, D]`` LEFT-padded, valid
+    length ``kv_lengths[b]``; new_k/new_v ``[B, Hkv, 1, D]`` appended on the right.  Returns
+    ``[B, 1, Hq*D]`` (src/msa/memory_sparse_attention.py:371-399; GQA by head repetition,
+    softmax scale ``D**-0.5`` = SDPA default)."""
+    b, hq, ql, d = q.shape
+    hkv = cache_k.shape[1]
+    g = hq // hkv
+    full_k = torch.cat([cache_k, new_k], dim=2)
+    full_v = torch.cat([cache_v, new_v], dim=2)
+    max_new = full_k.shape[2]
+    new_len = kv_lengths + 1
+    mask = torch.arange(max_new).unsqueeze(0) >= (max_new - new_len.unsqueeze(1))  # [B, L]
+    kk = full_k.repeat_interleave(g, dim=1).to(torch.float32)
+    vv = full_v.repeat_interleave(g, dim=1).to(torch.float32)
+    s = scale if scale is not None else 1.0 / math.sqrt(d)
+    att = torch.matmul(q.to(torch.float32), kk.transpose(-1, -2)) * s
+    att = att.masked_fill(~mask[:, None, None, :], float("-inf"))
+    p = torch.softmax(att, dim=-1)
+    o = torch.matmul(p, vv)
+    return o.transpose(1, 2).reshape(b, ql, hq * d).to(q.dtype)
+
+
+def rope_rotate_half(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Half-split RoPE of transformers' Qwen3 (``apply_rotary_pos_emb``; third-party, pinned
+    by requirements.txt to transformers 4.51.3; call site
+    src/msa/memory_sparse_attention.py:133): ``x*cos + rotate_half(x)*sin`` with
+    ``rotate_half(x) = cat(-x[..., D/2:], x[..., :D/2])``."""
+    d = x.shape[-1]
+    rot = torch.cat([-x[..., d // 2:], x[..., : d // 2]], dim=-1)
+    return x * cos + rot * sin
+
+
+def rope_cos_sin(positions: torch.Tensor, head_dim: int, theta: float = 1_000_000.0):
+    """cos/sin tables as Qwen3RotaryEmbedding builds them: inv_freq = theta^(-2i/D), angles
+    in fp32, duplicated over both halves.  positions ``[..., T]`` -> ``[..., T, D]``."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
+    ang = positions.to(torch.float32).unsqueeze(-1) * inv
+    emb = torch.cat([ang, ang], dim=-1)
+    return emb.cos(), emb.sin()

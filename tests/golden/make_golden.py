@@ -1,0 +1,303 @@
+"""Generate the golden fixtures of this folder from the EverMind-AI/MSA reference itself.
+
+Run in a container that has the reference checked out (read-only is fine):
+
+    python tests/golden/make_golden.py --reference /path/to/MSA
+
+The reference is imported unmodified.  Two names removed from transformers 5.x are
+injected into ``transformers.cache_utils`` so that ``src/utils/cache.py:11`` imports (only
+its unused quantized cache needs them), ``flash_attn_varlen_func`` (third party, CUDA only)
+is replaced by an SDPA loop with bottom-right-aligned causal masking, and on a GPU-less box
+``torch.cuda.current_stream`` is stubbed (``src/msa_service.py:1272`` synchronises it).
+Everything is fp32 on the CPU.  Inputs AND outputs are stored, so the tests that consume
+the ``.npz`` files need neither the reference nor this script.
+"""
+import argparse
+import os
+import sys
+from types import SimpleNamespace
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def import_reference(path):
+    sys.path.insert(0, path)
+    import transformers.cache_utils as cu
+    for n in ("QuantoQuantizedCache", "QuantizedCacheConfig"):
+        if not hasattr(cu, n):
+            setattr(cu, n, type(n, (), {}))
+    import src.msa_service as svc
+    import src.msa.memory_sparse_attention as msa_layer
+    from src.msa.configuration_msa import MSAConfig
+    return svc, msa_layer, MSAConfig
+
+
+def save(name, **arrays):
+    out = {}
+    for k, v in arrays.items():
+        if torch.is_tensor(v):
+            v = v.detach().cpu().numpy()
+        out[k] = np.asarray(v)
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **out)
+    print("wrote", name, {k: v.shape for k, v in out.items()})
+
+
+def make_memory(svc, chunks_per_doc, global_ids, rk, k, v, top_k, reduce=("mean", "max", "max"),
+                cls=None, slice_chunks=16):
+    cls = cls or svc.Memory
+    docs = [svc.Document(doc="", doc_id=g, num_chunks=n) for g, n in zip(global_ids, chunks_per_doc)]
+    m = object.__new__(cls)
+    m.device = "cpu"
+    m.gpu_id = 0
+    m.router_layer_ids = [0]
+    m.head_reduce_method, m.query_reduce_method, m.chunk_reduce_method = reduce
+    m.model_config = SimpleNamespace(doc_top_k=top_k)
+    m.block_desc = svc.BlockDesc()
+    m.block_desc.init_docs(docs, "cpu")
+    m.block_desc.pool_ids = torch.repeat_interleave(torch.arange(1, len(docs) + 1), torch.tensor(chunks_per_doc))
+    m.blocks = {0: svc.BlockData(k=k, v=v, rk=rk)}
+    m._generate_slice(slice_chunks)
+    return m
+
+
+def gen_pooling(svc, msa_layer):
+    g = torch.Generator().manual_seed(101)
+    p = 16
+    doc_lens = [50, 16, 33, 1, 64]
+    t_template = 3
+    ids = [-2] * t_template
+    for i, n in enumerate(doc_lens):
+        ids += [i + 1] * n
+    doc_ids = torch.tensor([ids])
+    t = doc_ids.shape[1]
+    attention_mask = torch.ones_like(doc_ids)
+    h, d = 2, 128
+    k = torch.randn(1, h, t, d, generator=g)
+    v = torch.randn(1, h, t, d, generator=g)
+    # the reference's inline bookkeeping (memory_sparse_attention.py:138-163), executed verbatim
+    max_doc_id = int(doc_ids.max().item())
+    mask = (doc_ids > 0) & (attention_mask == 1)
+    doc_indices = torch.nonzero(mask, as_tuple=False)
+    gdi = doc_indices[:, 0] * (max_doc_id + 1) + doc_ids[mask]
+    _, counts = torch.unique_consecutive(gdi, return_counts=True)
+    offsets = torch.zeros(counts.shape[0] + 1, dtype=counts.dtype)
+    offsets[1:] = counts.cumsum(0)
+    ranks = torch.arange(gdi.shape[0]) - torch.repeat_interleave(offsets[:-1], counts)
+    gci = gdi * ((t // p) + 1) + ranks // p
+    pk, pv = msa_layer.MemorySparseAttention.sequence_pooling_kv(None, k, v, doc_indices, gci)
+    save("pooling_ragged", doc_ids=doc_ids, attention_mask=attention_mask, pooling_kernel_size=p,
+         key_states=k, value_states=v, pooled_k=pk, pooled_v=pv)
+
+
+def sdpa_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, dropout_p=0.0, causal=True):
+    outs = []
+    for i in range(cu_seqlens_q.shape[0] - 1):
+        qs, qe = int(cu_seqlens_q[i]), int(cu_seqlens_q[i + 1])
+        ks, ke = int(cu_seqlens_k[i]), int(cu_seqlens_k[i + 1])
+        qi, ki, vi = q[qs:qe].transpose(0, 1), k[ks:ke].transpose(0, 1), v[ks:ke].transpose(0, 1)
+        if ki.shape[0] != qi.shape[0]:
+            rep = qi.shape[0] // ki.shape[0]
+            ki, vi = ki.repeat_interleave(rep, 0), vi.repeat_interleave(rep, 0)
+        lq, lk = qe - qs, ke - ks
+        m = torch.ones(lq, lk, dtype=torch.bool).tril(diagonal=lk - lq)
+        att = (qi @ ki.transpose(-1, -2)) / qi.shape[-1] ** 0.5
+        att = att.masked_fill(~m, float("-inf")).softmax(-1)
+        outs.append((att @ vi).transpose(0, 1))
+    return torch.cat(outs, 0)
+
+
+class StubCache:
+    def __init__(self):
+        self.cache_kwargs, self.meta, self.kv, self.rk = {}, {}, {}, {}
+
+    def record_kwargs(self, layer, kw):
+        self.cache_kwargs.setdefault(layer, {}).update(kw)
+
+    def update(self, k, v, layer, cache_kwargs=None):
+        self.kv[layer] = (k, v)
+        return k, v
+
+    def update_router_kcache(self, k, layer):
+        self.rk[layer] = k
+        return k
+
+
+def gen_layer(svc, msa_layer, MSAConfig):
+    """Stage-1 and decode branches of the reference layer at small model sizes."""
+    from transformers.models.qwen3.modeling_qwen3 import Qwen3RotaryEmbedding, apply_rotary_pos_emb
+    msa_layer.flash_attn_varlen_func = sdpa_varlen
+    torch.manual_seed(202)
+    hq, hkv, d = 4, 2, 16
+    cfg = MSAConfig(
+        msa_config=dict(router_layer_idx="0", aux_loss=False, aux_loss_method="INFONCE", decouple_router=True,
+                        top_k_docs=2, pooling_kernel_size=8, head_reduce_method="mean",
+                        query_reduce_method="max", chunk_reduce_method="max", decouple_pooling_mode="mean"),
+        hidden_size=hq * d, num_attention_heads=hq, num_key_value_heads=hkv, head_dim=d,
+        num_hidden_layers=1, intermediate_size=64, vocab_size=32, max_position_embeddings=512)
+    cfg._attn_implementation = "eager"
+    layer = msa_layer.MemorySparseAttention(cfg, 0).eval()
+    with torch.no_grad():
+        layer.o_proj.weight.copy_(torch.eye(hq * d))
+    rope = Qwen3RotaryEmbedding(cfg)
+
+    # ---- stage 1
+    doc_lens = [20, 8, 13]
+    ids, pos = [-2, -2, -2], [0, 1, 2]
+    for i, n in enumerate(doc_lens):
+        ids += [i + 1] * n
+        pos += list(range(n))
+    doc_ids = torch.tensor([ids])
+    position_ids = torch.tensor([pos])
+    t = doc_ids.shape[1]
+    hidden = torch.randn(1, t, hq * d)
+    attention_mask = torch.ones(1, t, dtype=torch.long)
+    cos, sin = rope(hidden, position_ids)
+    cache = StubCache()
+    cache.record_kwargs(0, {"stage": "prefill_stage1"})
+    with torch.no_grad():
+        layer(hidden, doc_ids, attention_mask, (cos, sin), cache)
+        shape = (1, t, -1, d)
+        qs = layer.q_norm(layer.q_proj(hidden).view(shape)).transpose(1, 2)
+        ks = layer.k_norm(layer.k_proj(hidden).view(shape)).transpose(1, 2)
+        vs = layer.v_proj(hidden).view(shape).transpose(1, 2)
+        pre_rope_k = ks.clone()
+        qs, ks = apply_rotary_pos_emb(qs, ks, cos, sin)
+        rks = layer.router_k_proj(hidden).view(shape).transpose(1, 2)
+    kw = cache.cache_kwargs[0]
+    save("layer_stage1", doc_ids=doc_ids, attention_mask=attention_mask, position_ids=position_ids,
+         pooling_kernel_size=8, rope_theta=float(getattr(cfg, "rope_theta", 0.0) or cfg.rope_parameters["rope_theta"]),
+         cos=cos, sin=sin, pre_rope_k=pre_rope_k, key_states=ks, value_states=vs, router_k_states=rks,
+         pooled_k=cache.kv[0][0], pooled_v=cache.kv[0][1], pooled_rk=cache.rk[0],
+         pooled_doc_ids=kw["pooled_doc_ids"], template_k=kw["template_prefix_kcache"],
+         template_v=kw["template_prefix_vcache"])
+
+    # ---- decode: two steps over a left-padded compact cache
+    b, max_l = 3, 11
+    kv_lengths = torch.tensor([11, 7, 4])
+    ck = torch.randn(b, hkv, max_l, d)
+    cv = torch.randn(b, hkv, max_l, d)
+    cache = StubCache()
+    cache.record_kwargs(0, {"stage": "generate", "compacked_key_cache": ck.clone(), "compacked_value_cache": cv.clone(),
+                            "kv_lengths": kv_lengths.clone(),
+                            "attention_mask": torch.arange(max_l).unsqueeze(0) >= (max_l - kv_lengths.unsqueeze(1))})
+    steps = {}
+    for step in range(2):
+        hidden = torch.randn(b, 1, hq * d)
+        position_ids = (kv_lengths + step).view(b, 1)
+        cos, sin = rope(hidden, position_ids)
+        with torch.no_grad():
+            out, _ = layer(hidden, torch.full((b, 1), -1), torch.ones(b, 1, dtype=torch.long), (cos, sin), cache)
+            shape = (b, 1, -1, d)
+            qs = layer.q_norm(layer.q_proj(hidden).view(shape)).transpose(1, 2)
+            ks = layer.k_norm(layer.k_proj(hidden).view(shape)).transpose(1, 2)
+            vs = layer.v_proj(hidden).view(shape).transpose(1, 2)
+            qs, ks = apply_rotary_pos_emb(qs, ks, cos, sin)
+        steps[f"q{step}"], steps[f"k{step}"], steps[f"v{step}"], steps[f"out{step}"] = qs, ks, vs, out
+    save("layer_decode", cache_k=ck, cache_v=cv, kv_lengths=kv_lengths, **steps)
+
+
+def gen_routing(svc):
+    g = torch.Generator().manual_seed(303)
+    chunks = [4, 1, 3, 8, 2, 8, 8, 5, 1, 7]          # ragged documents, 47 chunks, cut into 2 slices
+    gids = [900 + 7 * i for i in range(len(chunks))]
+    c = sum(chunks)
+    hkv, grp, d = 8, 4, 128
+    rk = torch.randn(1, hkv, c, d, generator=g)
+    q = torch.randn(3, hkv, grp, 6, d, generator=g)
+    mask = torch.ones(3, 1, 1, 6, 1, dtype=torch.bool)
+    mask[1, 0, 0, 4:, 0] = False        # right padding
+    mask[2] = False                     # a sample with no routing token at all
+    arrays = dict(rk=rk[0], q=q, mask=mask.view(3, 6), chunks_per_doc=chunks, global_ids=gids, top_k=4)
+    for name, reduce, cosine in [
+        ("mean_max_max", ("mean", "max", "max"), False),
+        ("cosine", ("mean", "max", "max"), True),
+        ("max_max_max", ("max", "max", "max"), False),
+        ("mean_mean_max", ("mean", "mean", "max"), False),
+        ("mean_last_max", ("mean", "last", "max"), False),
+        ("mean_max_mean", ("mean", "max", "mean"), False),
+    ]:
+        # the cosine case L2-normalises both sides first, as the layer does when
+        # aux_loss_method == "INFONCE" (memory_sparse_attention.py:192-194, 264-265)
+        qq = torch.nn.functional.normalize(q, dim=-1) if cosine else q
+        rr = torch.nn.functional.normalize(rk, dim=-1) if cosine else rk
+        m = make_memory(svc, chunks, gids, rr, rr, rr, top_k=4, reduce=reduce)
+        s, li, gi = m.prefill_stage2(0, qq, mask)
+        assert len(m.slice_desc) == 2      # tail under 1024 chunks is merged (msa_service.py:665-670)
+        arrays.update({name + "__scores": s, name + "__local_ids": li, name + "__global_ids": gi})
+    # fewer documents than k: k' = min(k, N + 1), the dummy document shows up among the winners
+    m = make_memory(svc, chunks[:2], gids[:2], rk[:, :, :5], rk[:, :, :5], rk[:, :, :5], top_k=4)
+    s, li, gi = m.prefill_stage2(0, q, mask)
+    arrays.update({"k_gt_docs__scores": s, "k_gt_docs__local_ids": li, "k_gt_docs__global_ids": gi})
+    save("route_cases", **arrays)
+
+
+def _rank_main(rank, world, ref_path, payload, ret):
+    import torch.distributed as dist
+    svc, _, _ = import_reference(ref_path)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29611")
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    if not torch.cuda.is_available():
+        torch.cuda.current_stream = lambda *a, **k: SimpleNamespace(synchronize=lambda: None)
+    p = payload[rank]
+    s = make_memory(svc, p["chunks"], p["gids"], p["rk"], p["k"], p["v"], top_k=payload["top_k"], cls=svc.MSAService,
+                    slice_chunks=16)
+    s.gpu_id = rank
+    s.world_size = world
+    s.num_key_value_groups = payload["groups"]
+    s.scaling = -1.0
+    out = s.doc_query(p["q"], p["mask"], 0)
+    ret[rank] = [o.clone() for o in out]
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def gen_doc_query(ref_path):
+    import torch.multiprocessing as mp
+    g = torch.Generator().manual_seed(404)
+    world, hkv, grp, d, top_k = 2, 8, 4, 128, 3
+    chunk_lists = [[3, 1, 4, 2, 5, 2], [2, 6, 1, 3, 3]]
+    payload = {"top_k": top_k, "groups": grp}
+    gid = 10
+    for r in range(world):
+        c = sum(chunk_lists[r])
+        gids = list(range(gid, gid + len(chunk_lists[r])))
+        gid += len(chunk_lists[r])
+        # ranks with different query lengths.  Both are >= the group count (4): doc_query trims
+        # the gathered queries with [:, :, :seqlen, :] (msa_service.py:1155), which indexes the
+        # GROUP axis of [B, Hkv, G, S, D], so a query shorter than G silently loses groups there.
+        s_len = 5 if r == 0 else 4
+        q = torch.nn.functional.normalize(torch.randn(2, hkv * grp, s_len, d, generator=g), dim=-1)
+        mask = torch.ones(2, s_len, dtype=torch.bool)
+        if r == 0:
+            mask[1, 3:] = False
+        payload[r] = dict(chunks=chunk_lists[r], gids=gids,
+                          rk=torch.nn.functional.normalize(torch.randn(1, hkv, c, d, generator=g), dim=-1),
+                          k=torch.randn(1, hkv, c, d, generator=g), v=torch.randn(1, hkv, c, d, generator=g),
+                          q=q, mask=mask)
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_rank_main, args=(world, ref_path, payload, ret), nprocs=world, join=True)
+    arrays = dict(world=world, top_k=top_k, groups=grp)
+    for r in range(world):
+        p = payload[r]
+        fk, fv, fs, nsel, wg = ret[r]
+        arrays.update({f"r{r}_chunks": p["chunks"], f"r{r}_gids": p["gids"], f"r{r}_rk": p["rk"][0],
+                       f"r{r}_k": p["k"][0], f"r{r}_v": p["v"][0], f"r{r}_q": p["q"], f"r{r}_mask": p["mask"],
+                       f"r{r}_final_k": fk, f"r{r}_final_v": fv, f"r{r}_final_scores": fs,
+                       f"r{r}_num_selected": nsel, f"r{r}_winner_global_ids": wg})
+    save("doc_query_w2", **arrays)
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", required=True)
+    a = ap.parse_args()
+    svc, msa_layer, MSAConfig = import_reference(a.reference)
+    gen_pooling(svc, msa_layer)
+    gen_layer(svc, msa_layer, MSAConfig)
+    gen_routing(svc)
+    gen_doc_query(a.reference)

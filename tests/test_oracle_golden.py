@@ -1,0 +1,118 @@
+"""The oracle restatement against outputs of the reference's own code (tests/golden/*.npz,
+produced by tests/golden/make_golden.py).  CPU only."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import msa_oracle as O
+
+
+def T(x):
+    return torch.from_numpy(np.asarray(x))
+
+
+def test_bookkeeping_and_pooling_match_reference(golden):
+    g = golden("pooling_ragged")
+    p = int(g["pooling_kernel_size"])
+    doc_indices, gci, pooled_doc_ids, lengths = O.chunk_bookkeeping(T(g["doc_ids"]), T(g["attention_mask"]), p)
+    assert lengths.tolist() == [16, 16, 16, 2, 16, 16, 16, 1, 1, 16, 16, 16, 16]
+    assert pooled_doc_ids.tolist() == [1, 1, 1, 1, 2, 3, 3, 3, 4, 5, 5, 5, 5]
+    pk, pv = O.sequence_pooling_kv(T(g["key_states"]), T(g["value_states"]), doc_indices, gci)
+    # same formula, same fp32 op order: bit-exact
+    assert torch.equal(pk, T(g["pooled_k"])) and torch.equal(pv, T(g["pooled_v"]))
+    # and the cumsum-difference agrees with the exact mean norm-wise to fp32 accuracy
+    k_docs = T(g["key_states"])[doc_indices[:, 0], :, doc_indices[:, 1]]
+    exact = O.pool_chunks_exact(k_docs, lengths)
+    rel = (pk.double() - exact).norm() / exact.norm()
+    assert rel < 1e-6
+
+
+def test_stage1_layer_outputs(golden):
+    g = golden("layer_stage1")
+    p = int(g["pooling_kernel_size"])
+    doc_ids, am = T(g["doc_ids"]), T(g["attention_mask"])
+    doc_indices, gci, pooled_doc_ids, lengths = O.chunk_bookkeeping(doc_ids, am, p)
+    assert torch.equal(pooled_doc_ids, T(g["pooled_doc_ids"]))
+    assert lengths.tolist() == [8, 8, 4, 8, 8, 5]
+    # RoPE restatement against the keys the reference produced (positions restart per doc)
+    cos, sin = O.rope_cos_sin(T(g["position_ids"]), 16, float(g["rope_theta"]))
+    assert torch.allclose(cos, T(g["cos"]), atol=1e-6) and torch.allclose(sin, T(g["sin"]), atol=1e-6)
+    k_rot = O.rope_rotate_half(T(g["pre_rope_k"]), cos.unsqueeze(1), sin.unsqueeze(1))
+    assert torch.allclose(k_rot, T(g["key_states"]), atol=1e-6)
+    pk, pv = O.sequence_pooling_kv(T(g["key_states"]), T(g["value_states"]), doc_indices, gci)
+    assert torch.equal(pk.transpose(0, 1).unsqueeze(0), T(g["pooled_k"]))
+    assert torch.equal(pv.transpose(0, 1).unsqueeze(0), T(g["pooled_v"]))
+    rk_docs = T(g["router_k_states"])[doc_indices[:, 0], :, doc_indices[:, 1]]
+    prk = O.l2_normalize(O.pool_chunks_cumsum(rk_docs, lengths).transpose(0, 1).unsqueeze(0))
+    assert torch.equal(prk, T(g["pooled_rk"]))
+    n_t = int((doc_ids == -2).sum())
+    assert torch.equal(T(g["key_states"])[:, :, :n_t], T(g["template_k"]))
+
+
+CASES = {
+    "mean_max_max": ("mean", "max", "max"),
+    "cosine": ("mean", "max", "max"),
+    "max_max_max": ("max", "max", "max"),
+    "mean_mean_max": ("mean", "mean", "max"),
+    "mean_last_max": ("mean", "last", "max"),
+    "mean_max_mean": ("mean", "max", "mean"),
+}
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_routing_matches_reference(golden, name):
+    g = golden("route_cases")
+    q, rk = T(g["q"]), T(g["rk"])
+    if name == "cosine":
+        q, rk = O.l2_normalize(q), O.l2_normalize(rk)
+    chunks = g["chunks_per_doc"].tolist()
+    pool_ids = torch.repeat_interleave(torch.arange(1, len(chunks) + 1), torch.tensor(chunks))
+    table = torch.tensor([0] + g["global_ids"].tolist())
+    h, qr, cr = CASES[name]
+    s, li, gi = O.prefill_stage2(q, T(g["mask"]), rk, pool_ids, table, int(g["top_k"]),
+                                 head_reduce=h, query_reduce=qr, chunk_reduce=cr, slice_chunks=7)
+    ref_s = T(g[name + "__scores"])
+    valid = ref_s > -1e9
+    assert torch.allclose(s[valid], ref_s[valid], atol=1e-5, rtol=1e-5)
+    assert torch.equal(li[valid], T(g[name + "__local_ids"])[valid])
+    assert torch.equal(gi[valid], T(g[name + "__global_ids"])[valid])
+    # the sample without any routing token scores finfo.min everywhere
+    assert (s[2] == torch.finfo(torch.float32).min).all() or name == "mean_mean_max"
+
+
+def test_routing_k_larger_than_docs(golden):
+    g = golden("route_cases")
+    pool_ids = torch.tensor([1, 1, 1, 1, 2])
+    table = torch.tensor([0] + g["global_ids"].tolist()[:2])
+    s, li, gi = O.prefill_stage2(T(g["q"]), T(g["mask"]), T(g["rk"])[:, :5], pool_ids, table, 4)
+    assert s.shape == (3, 3)                      # k' = min(k, N + 1)
+    ref_s = T(g["k_gt_docs__scores"])
+    assert torch.allclose(s[:2], ref_s[:2], atol=1e-5)
+    assert torch.equal(li[:2], T(g["k_gt_docs__local_ids"])[:2])
+    assert (li[:2, -1] == 0).all()                # the dummy document comes last
+
+
+def test_doc_query_two_ranks(golden):
+    g = golden("doc_query_w2")
+    w, top_k, grp = int(g["world"]), int(g["top_k"]), int(g["groups"])
+    shards = [O.Shard(T(g[f"r{r}_k"]), T(g[f"r{r}_v"]), T(g[f"r{r}_rk"]),
+                      g[f"r{r}_chunks"].tolist(), g[f"r{r}_gids"].tolist()) for r in range(w)]
+    qs = [T(g[f"r{r}_q"]) for r in range(w)]
+    ms = [T(g[f"r{r}_mask"]) for r in range(w)]
+    outs = O.doc_query_world(qs, ms, shards, top_k, grp)
+    for r, (fk, fv, fs, nsel, wg) in enumerate(outs):
+        assert torch.allclose(fs, T(g[f"r{r}_final_scores"]), atol=1e-5)
+        assert torch.equal(wg, T(g[f"r{r}_winner_global_ids"]))
+        assert torch.equal(nsel, T(g[f"r{r}_num_selected"]))
+        assert torch.equal(fk, T(g[f"r{r}_final_k"]))
+        assert torch.equal(fv, T(g[f"r{r}_final_v"]))
+
+
+def test_decode_matches_reference_layer(golden):
+    g = golden("layer_decode")
+    ck, cv, lens = T(g["cache_k"]), T(g["cache_v"]), T(g["kv_lengths"])
+    for step in range(2):
+        q, k, v = T(g[f"q{step}"]), T(g[f"k{step}"]), T(g[f"v{step}"])
+        out = O.decode_attention(q, ck, cv, lens, k, v)
+        assert torch.allclose(out, T(g[f"out{step}"]), atol=2e-6, rtol=1e-5)
+        ck, cv, lens = torch.cat([ck, k], 2), torch.cat([cv, v], 2), lens + 1
