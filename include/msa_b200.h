@@ -1,0 +1,217 @@
+/*
+ * msa_b200 -- C ABI of the B200 (sm_100a) kernels for MSA's Memory-Parallel routing and
+ * sparse-attention hot path.
+ *
+ * Conventions
+ *   - Every pointer is a raw address.  "device" pointers are CUDA device addresses
+ *     (tensor.data_ptr() of a CUDA tensor); "host-mapped" pointers are device-visible
+ *     addresses of pinned host memory.  The caller owns every buffer; the library borrows
+ *     it for the lifetime of the enqueued work and never allocates on the hot path.
+ *   - `stream` is a cudaStream_t passed as void*.  All work is enqueued asynchronously.
+ *   - Strides are in ELEMENTS of the tensor's dtype unless the name says bytes.
+ *   - Return value: MSA_OK, or a negative MSA_ERR_* after which msa_last_error() holds a
+ *     message for the calling thread.  Argument errors are detected before any launch.
+ *   - Kernels that wait on hardware barriers bound every wait; a wait that runs out sets
+ *     a non-zero word in the caller's `status` buffer instead of hanging.
+ *
+ * Reference interfaces are cited by path inside the EverMind-AI/MSA repository.
+ */
+#ifndef MSA_B200_H
+#define MSA_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MSA_ABI_VERSION 1
+
+enum msa_status {
+  MSA_OK = 0,
+  MSA_ERR_ARG = -1,         /* bad pointer / size / stride / alignment */
+  MSA_ERR_UNSUPPORTED = -2, /* a mode the reference has but this build rejects */
+  MSA_ERR_CUDA = -3,        /* a CUDA runtime or driver call failed */
+  MSA_ERR_NO_DEVICE = -4    /* no sm_100 device is current */
+};
+
+enum msa_dtype { MSA_F32 = 0, MSA_BF16 = 1 };
+
+/* query_reduce_method of the reference (src/msa_service.py:749-780) */
+enum msa_query_reduce { MSA_QREDUCE_MAX = 0, MSA_QREDUCE_MEAN = 1, MSA_QREDUCE_LAST = 2 };
+
+/* flags of msa_route_scores */
+#define MSA_ROUTE_FORCE_SIMT 1u /* use the CUDA-core kernel even for bf16 (cross-checks) */
+#define MSA_ROUTE_NO_INIT 2u    /* do not reset the score table first (accumulate slices) */
+
+int msa_abi_version(void);
+const char* msa_last_error(void);
+
+/* ---------------------------------------------------------------------------------------
+ * Stage 1: chunk bookkeeping.
+ * Replaces the inline tensor code of src/msa/memory_sparse_attention.py:138-163
+ * (doc-token mask, rank inside the document, chunk id, owning doc per chunk).
+ *
+ * doc_ids, attention_mask: device int64 [n_rows * row_len]; attention_mask may be NULL
+ * (all ones).  A document is a run of equal doc_ids > 0 inside one row.
+ * Outputs (device): token_index[i] = flat position of the i-th document token;
+ * chunk_offsets[c] .. chunk_offsets[c+1] = range of chunk c in that token stream;
+ * pooled_doc_ids[c] = doc id owning chunk c; counts[0] = #document tokens,
+ * counts[1] = #chunks, counts[2] = 1 if max_chunks was too small (outputs truncated).
+ * token_index needs n_rows*row_len entries, chunk_offsets max_chunks+1, pooled_doc_ids
+ * max_chunks.
+ */
+int msa_chunk_bookkeeping(const int64_t* doc_ids, const int64_t* attention_mask, int32_t n_rows,
+                          int32_t row_len, int32_t pooling_kernel_size, int32_t* token_index,
+                          int32_t* chunk_offsets, int64_t* pooled_doc_ids, int32_t max_chunks,
+                          int32_t* counts, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Stage 1: chunk-mean pooling (+ optional L2 normalisation of the pooled rows).
+ * Replaces MemorySparseAttention.sequence_pooling_kv
+ * (src/msa/memory_sparse_attention.py:467-486), the inline K_r pooling (:177-190) and
+ * F.normalize of the pooled router keys (:192-194).
+ *
+ * states: device, element (row r, head h, d) at states[r*token_stride + h*head_stride + d].
+ * Row of the i-th document token is token_index[i] (or i when token_index is NULL).
+ * out: element (chunk c, head h, d) at out[c*out_chunk_stride + h*out_head_stride + d].
+ * Mean over the tokens actually in the chunk, fp32 accumulation, result in `dtype`.
+ * n_chunks_dev (nullable): device int32 holding the live chunk count (<= n_chunks).
+ * Requires n_heads*head_dim*sizeof(dtype)/16 to divide 256 and head_dim*sizeof/16 <= 32.
+ */
+int msa_pool_chunks(const void* states, int32_t dtype, int64_t token_stride, int64_t head_stride,
+                    const int32_t* token_index, const int32_t* chunk_offsets,
+                    const int32_t* n_chunks_dev, int32_t n_chunks, int32_t n_heads,
+                    int32_t head_dim, void* out, int64_t out_chunk_stride, int64_t out_head_stride,
+                    int32_t l2_normalize, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Routing, step 1: fold the query heads.
+ * Replaces the view/scale/pad part of MSAService._gather_querys
+ * (src/msa_service.py:1095-1100), F.normalize of the routing query
+ * (src/msa/memory_sparse_attention.py:264-265) and, because the head reduction is a mean,
+ * the 4x redundant per-group matmul of Memory.prefill_stage2 (src/msa_service.py:730-745):
+ * folded[b, s, h, :] = sum_g q[b, h*G + g, s, :], so one 1024-wide dot product per
+ * (token, chunk) gives the head-mean score after scaling by alpha = scale/(Hkv*G).
+ *
+ * q: device [B, Hq, S, D] addressed by strides (D contiguous).  query_mask: device uint8
+ * [B, S] (row stride mask_stride_b), non-zero = routing-query token.
+ * query_reduce MAX keeps S rows per sequence (padded to s_pad rows; pad and masked rows get
+ * row_bias = -inf).  MEAN / LAST reduce the tokens here (mean of valid tokens / last valid
+ * token) and need s_pad == 1.
+ * q_folded: device [B*s_pad, Hkv*D] in `dtype`; row_bias: device float [B*s_pad].
+ */
+int msa_fold_queries(const void* q, int32_t dtype, int64_t stride_b, int64_t stride_h,
+                     int64_t stride_s, const uint8_t* query_mask, int64_t mask_stride_b,
+                     int32_t n_seq, int32_t n_q_heads, int32_t n_groups, int32_t seq_len,
+                     int32_t head_dim, int32_t l2_normalize, int32_t query_reduce, int32_t s_pad,
+                     void* q_folded, float* row_bias, void* stream);
+
+/* Rows per sequence msa_route_scores wants for a query of seq_len tokens (>= seq_len). */
+int32_t msa_route_s_pad(int32_t seq_len, int32_t query_reduce);
+
+/* ---------------------------------------------------------------------------------------
+ * Routing, step 2: score + reduce.
+ * Replaces the slice loop of Memory.prefill_stage2 (src/msa_service.py:716-821): matmul,
+ * masked_fill, head mean, token max, chunk->doc amax, for head_reduce "mean",
+ * chunk_reduce "max".  Per-(token, chunk) scores stay on chip.
+ *
+ * q_folded / row_bias: output of msa_fold_queries (n_seq sequences of s_pad rows).
+ * rk: device pooled router keys, chunk c at rk + c*rk_chunk_stride, kdim contiguous elements.
+ * chunk_doc: device int32 [n_chunks], 1-based local doc id of each chunk (the reference's
+ * BlockDesc.pool_ids, src/msa_service.py:196-198), non-decreasing.
+ * score_keys: device uint32 [n_seq, table_stride]; column d (0..n_docs) receives the
+ * order-preserving key of max(min_val, alpha * max_tokens max_chunks dot).  Column 0 is the
+ * reference's dummy document (src/msa_service.py:716-717).  Decode with msa_topk_select.
+ * bf16 runs on the tcgen05 tensor-core kernel (needs kdim % 64 == 0, 16-byte aligned rows,
+ * s_pad == 1 or s_pad % 16 == 0); fp32 runs on the CUDA-core kernel.
+ * status: device int32 [4], zero on success; word 0 != 0 reports a barrier wait that ran out.
+ */
+int msa_route_scores(const void* q_folded, const float* row_bias, int32_t dtype, int32_t n_seq,
+                     int32_t s_pad, const void* rk, int64_t rk_chunk_stride, int32_t n_chunks,
+                     int32_t kdim, const int32_t* chunk_doc, float alpha, uint32_t* score_keys,
+                     int64_t table_stride, int32_t n_docs, float min_val, uint32_t flags,
+                     int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Routing, step 3: exact per-shard top-k (block radix select + sort of the winners).
+ * Replaces torch.topk + create_global_doc_ids (src/msa_service.py:826-828).
+ * Selects k_eff = min(k, n_cols) columns per row, sorted by descending score; equal scores
+ * are ordered by ascending column.  out_* are [n_seq, k_eff].  doc_ids_table (nullable) is the
+ * local->global table (BlockDesc.doc_ids, src/msa_service.py:199-201, 218-219).
+ */
+int msa_topk_select(const uint32_t* score_keys, int64_t table_stride, int32_t n_seq,
+                    int32_t n_cols, int32_t k, const int64_t* doc_ids_table, float* out_scores,
+                    int64_t* out_local_ids, int64_t* out_global_ids, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Cross-rank merge of the per-shard candidates.
+ * Replaces steps 4-5 of MSAService.doc_query (src/msa_service.py:1174-1196): top-k over
+ * the W*kc candidates of each query, owner rank of each winner, invalidation of winners
+ * whose score is <= invalid_below (-1e9 in the reference, :1190).
+ * cand_*: device, candidate (w, b, j) at index w*stride_w + b*kc + j.
+ * Outputs [n_seq, k]: scores, local ids (-1 where invalid), global ids, owner ranks.
+ * Ties: lower rank, then lower position first.  Requires W*kc <= 4096.
+ */
+int msa_topk_merge(const float* cand_scores, const int64_t* cand_local, const int64_t* cand_global,
+                   int64_t stride_w, int32_t world, int32_t n_seq, int32_t kc, int32_t k,
+                   float invalid_below, float* out_scores, int64_t* out_local, int64_t* out_global,
+                   int32_t* out_rank, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Fetch of the selected documents' pooled K/V from pinned host memory.
+ * Replaces steps 5-8 of MSAService.doc_query (src/msa_service.py:1193-1312): request
+ * exchange, CPU index build, index_select on the pinned bank, H2D, all-to-all-v, regroup.
+ *
+ * Bank layout (this library's): per shard one host-mapped array [chunks, 2, Hkv, D]
+ * (K then V per chunk), so a document is one contiguous run.  The directory lives on the
+ * device: shard_doc_base[w] = first row of shard w in doc_chunk_offset / doc_chunk_len
+ * (indexed by shard_doc_base[w] + local id, slot 0 = dummy of length 0);
+ * shard_kv_base[w] = host-mapped address of shard w's array.
+ *
+ * msa_gather_plan: orders each sample's valid winners by (owner rank, local id), as the
+ * reference's exchange does, and computes where their chunks go.  plan is device int64
+ * [n_seq*k, 4] = (source address, chunks, destination entry, unused); n_sel device int64
+ * [n_seq]; total device int64 [1] (also written to *total_host_mapped when non-NULL).
+ * msa_gather_run: copies every planned document into out_k / out_v, device
+ * [Hkv, out_entries, D] (entry stride = D, head stride = out_head_stride elements).
+ */
+int msa_gather_plan(const int64_t* sel_local, const int32_t* sel_rank, int32_t n_seq, int32_t k,
+                    int32_t world, const int64_t* shard_doc_base, const int64_t* doc_chunk_offset,
+                    const int32_t* doc_chunk_len, const uint64_t* shard_kv_base,
+                    int64_t chunk_bytes, int64_t* plan, int64_t* n_sel, int64_t* total,
+                    int64_t* total_host_mapped, void* stream);
+
+int msa_gather_run(const int64_t* plan, int32_t n_items, int32_t dtype, int32_t n_kv_heads,
+                   int32_t head_dim, void* out_k, void* out_v, int64_t out_head_stride,
+                   int64_t out_entries, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Decode attention over the sparse context (split-KV flash-decode, GQA).
+ * Replaces the decode branch of MemorySparseAttention
+ * (src/msa/memory_sparse_attention.py:371-399): torch.cat of the cache, repeat_kv,
+ * boolean-mask SDPA with q_len == 1.
+ *
+ * q: device [B, Hq, D].  k_cache / v_cache: device, element (b, h, pos, d) at
+ * b*stride_b + h*stride_h + pos*D + d with capacity >= kv_start[b] + kv_len[b] + 1.
+ * Sequence b's valid entries are positions kv_start[b] .. kv_start[b]+kv_len[b]-1
+ * (kv_start NULL = 0; a left-padded cache of the reference has kv_start = maxL - kv_len).
+ * new_k / new_v: device [B, Hkv, D] (nullable together): this step's key/value; they take
+ * part in the attention and are appended in place at position kv_start[b] + kv_len[b].
+ * out: device [B, Hq*D].  scale: softmax scale (D^-0.5 in the reference).
+ * workspace: device, msa_decode_workspace_bytes(...) bytes (needed when n_splits > 1).
+ */
+int64_t msa_decode_workspace_bytes(int32_t n_seq, int32_t n_q_heads, int32_t head_dim,
+                                   int32_t n_splits);
+
+int msa_sparse_decode_attn(const void* q, int32_t dtype, void* k_cache, void* v_cache,
+                           int64_t stride_b, int64_t stride_h, const int32_t* kv_start,
+                           const int32_t* kv_len, const void* new_k, const void* new_v,
+                           int32_t n_seq, int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim,
+                           float scale, void* out, void* workspace, int64_t workspace_bytes,
+                           int32_t n_splits, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MSA_B200_H */

@@ -1,0 +1,92 @@
+"""ctypes binding of ``libmsa_b200.so`` (declared in ``include/msa_b200.h``).
+
+There is no fallback: if the library is missing or a call fails, an exception is raised.
+Every wrapper takes torch tensors, checks device / dtype / contiguity, and passes raw
+pointers, sizes and the current CUDA stream to the C ABI.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libmsa_b200.so")
+
+MSA_F32, MSA_BF16 = 0, 1
+QREDUCE = {"max": 0, "mean": 1, "last": 2}
+ROUTE_FORCE_SIMT, ROUTE_NO_INIT = 1, 2
+
+EXPORTS = [
+    "msa_abi_version", "msa_last_error", "msa_chunk_bookkeeping", "msa_pool_chunks", "msa_fold_queries",
+    "msa_route_s_pad", "msa_route_scores", "msa_topk_select", "msa_topk_merge", "msa_gather_plan",
+    "msa_gather_run", "msa_decode_workspace_bytes", "msa_sparse_decode_attn",
+]
+
+
+class MsaError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m msa_b200.build` "
+                "(nvcc, sm_100a).  msa_b200 has no CPU or PyTorch fallback.")
+        l = C.CDLL(LIB_PATH)
+        vp, i32, i64, f32, u32 = C.c_void_p, C.c_int32, C.c_int64, C.c_float, C.c_uint32
+        l.msa_last_error.restype = C.c_char_p
+        l.msa_abi_version.restype = C.c_int
+        l.msa_chunk_bookkeeping.argtypes = [vp, vp, i32, i32, i32, vp, vp, vp, i32, vp, vp]
+        l.msa_pool_chunks.argtypes = [vp, i32, i64, i64, vp, vp, vp, i32, i32, i32, vp, i64, i64, i32, vp]
+        l.msa_fold_queries.argtypes = [vp, i32, i64, i64, i64, vp, i64, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp]
+        l.msa_route_s_pad.argtypes = [i32, i32]
+        l.msa_route_s_pad.restype = i32
+        l.msa_route_scores.argtypes = [vp, vp, i32, i32, i32, vp, i64, i32, i32, vp, f32, vp, i64, i32, f32, u32, vp, vp]
+        l.msa_topk_select.argtypes = [vp, i64, i32, i32, i32, vp, vp, vp, vp, vp]
+        l.msa_topk_merge.argtypes = [vp, vp, vp, i64, i32, i32, i32, i32, f32, vp, vp, vp, vp, vp]
+        l.msa_gather_plan.argtypes = [vp, vp, i32, i32, i32, vp, vp, vp, vp, i64, vp, vp, vp, vp, vp]
+        l.msa_gather_run.argtypes = [vp, i32, i32, i32, i32, vp, vp, i64, i64, vp]
+        l.msa_decode_workspace_bytes.argtypes = [i32, i32, i32, i32]
+        l.msa_decode_workspace_bytes.restype = i64
+        l.msa_sparse_decode_attn.argtypes = [vp, i32, vp, vp, i64, i64, vp, vp, vp, vp, i32, i32, i32, i32, f32, vp,
+                                             vp, i64, i32, vp]
+        for name in EXPORTS:
+            fn = getattr(l, name)
+            if fn.restype is C.c_int and name not in ("msa_abi_version",):
+                fn.restype = C.c_int
+        _lib = l
+    return _lib
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise MsaError(f"{what} failed ({rc}): {lib().msa_last_error().decode()}")
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return MSA_F32
+    if dt == torch.bfloat16:
+        return MSA_BF16
+    raise MsaError(f"unsupported dtype {dt}: the kernels take float32 or bfloat16")
+
+
+def ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def stream_ptr(device=None) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def need_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise MsaError("msa_b200 kernels take CUDA tensors; there is no CPU path")

@@ -1,0 +1,160 @@
+// Fetch of the selected documents' pooled K/V from the pinned host bank.
+//
+// The host bank keeps a document's chunks contiguous ([chunk][K|V][Hkv][D]), so one
+// selected document is one linear run of host memory.  The gather kernel reads it through
+// the device-visible mapping with 16-byte loads (PCIe reads, no staging copy, no host
+// thread involved) and scatters it into the head-major [Hkv, entries, D] layout the
+// attention path consumes.  Bound by PCIe bandwidth: 2*chunks*Hkv*D*e bytes per document.
+#include "common.cuh"
+
+namespace msa {
+
+constexpr int kPlanThreads = 256;
+constexpr int kPlanMaxK = 64;
+
+__global__ void __launch_bounds__(kPlanThreads)
+gather_plan_kernel(const int64_t* __restrict__ sel_local, const int32_t* __restrict__ sel_rank, int n_seq, int k,
+                   int world, const int64_t* __restrict__ shard_doc_base,
+                   const int64_t* __restrict__ doc_chunk_offset, const int32_t* __restrict__ doc_chunk_len,
+                   const uint64_t* __restrict__ shard_kv_base, long long chunk_bytes, int64_t* __restrict__ plan,
+                   int64_t* __restrict__ n_sel, int64_t* __restrict__ total, int64_t* total_host) {
+  __shared__ long long s_scan[kPlanThreads];
+  __shared__ long long s_carry;
+  if (threadIdx.x == 0) s_carry = 0;
+  __syncthreads();
+  for (int base = 0; base < n_seq; base += kPlanThreads) {
+    const int b = base + threadIdx.x;
+    long long mine = 0;
+    if (b < n_seq) {
+      // insertion sort of the sample's valid winners by (owner rank, local id)
+      long long key[kPlanMaxK];
+      int n = 0;
+      for (int j = 0; j < k; ++j) {
+        const long long lid = sel_local[(long long)b * k + j];
+        const int r = sel_rank ? sel_rank[(long long)b * k + j] : 0;
+        if (lid <= 0 || r < 0 || r >= world) continue;
+        const long long kk = ((long long)r << 40) | lid;
+        int p = n++;
+        while (p > 0 && key[p - 1] > kk) { key[p] = key[p - 1]; --p; }
+        key[p] = kk;
+      }
+      for (int j = 0; j < k; ++j) {
+        int64_t* row = plan + ((long long)b * k + j) * 4;
+        if (j < n) {
+          const int r = (int)(key[j] >> 40);
+          const long long lid = key[j] & ((1ll << 40) - 1);
+          const long long d = shard_doc_base[r] + lid;
+          const long long len = doc_chunk_len[d];
+          row[0] = (int64_t)(shard_kv_base[r] + (unsigned long long)(doc_chunk_offset[d] * chunk_bytes));
+          row[1] = len;
+          row[2] = mine;  // offset inside the sample; the sample base is added below
+          mine += len;
+        } else {
+          row[0] = 0; row[1] = 0; row[2] = 0;
+        }
+        row[3] = 0;
+      }
+      n_sel[b] = mine;
+    }
+    // exclusive scan of the per-sample totals across the CTA, carried between rounds
+    s_scan[threadIdx.x] = mine;
+    __syncthreads();
+    for (int d = 1; d < kPlanThreads; d <<= 1) {
+      const long long other = threadIdx.x >= d ? s_scan[threadIdx.x - d] : 0;
+      __syncthreads();
+      s_scan[threadIdx.x] += other;
+      __syncthreads();
+    }
+    const long long excl = s_carry + s_scan[threadIdx.x] - mine;
+    if (b < n_seq)
+      for (int j = 0; j < k; ++j) {
+        int64_t* row = plan + ((long long)b * k + j) * 4;
+        if (row[1] > 0) row[2] += excl;
+      }
+    __syncthreads();
+    if (threadIdx.x == kPlanThreads - 1) s_carry += s_scan[kPlanThreads - 1];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    total[0] = s_carry;
+    if (total_host) *reinterpret_cast<volatile int64_t*>(total_host) = s_carry;
+  }
+}
+
+constexpr int kGatherThreads = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kGatherThreads)
+gather_kernel(const int64_t* __restrict__ plan, int n_kv_heads, int head_dim, T* __restrict__ out_k,
+              T* __restrict__ out_v, long long out_head_stride, long long out_entries) {
+  constexpr int V = Elem<T>::kVec;
+  const int64_t* row = plan + (long long)blockIdx.x * 4;
+  const long long len = row[1];
+  if (len <= 0) return;
+  const uint4* src = reinterpret_cast<const uint4*>((uintptr_t)row[0]);
+  const long long dst0 = row[2];
+  const int vec_half = n_kv_heads * head_dim / V;  // 16-byte vectors in one chunk's K (or V)
+  const long long n_vec = len * 2 * vec_half;
+  // each thread keeps four independent 16-byte PCIe reads in flight
+  for (long long v0 = threadIdx.x; v0 < n_vec; v0 += 4ll * kGatherThreads) {
+    uint4 val[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long v = v0 + (long long)u * kGatherThreads;
+      if (v < n_vec) val[u] = src[v];
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long v = v0 + (long long)u * kGatherThreads;
+      if (v >= n_vec) continue;
+      const long long chunk = v / (2 * vec_half);
+      const int w = (int)(v % (2 * vec_half));
+      const int in_half = w % vec_half;
+      const int h = (in_half * V) / head_dim, d = (in_half * V) % head_dim;
+      const long long entry = dst0 + chunk;
+      if (entry >= out_entries) continue;
+      T* dst = (w < vec_half ? out_k : out_v) + (long long)h * out_head_stride + entry * head_dim + d;
+      *reinterpret_cast<uint4*>(dst) = val[u];
+    }
+  }
+}
+
+}  // namespace msa
+
+using namespace msa;
+
+extern "C" int msa_gather_plan(const int64_t* sel_local, const int32_t* sel_rank, int32_t n_seq, int32_t k,
+                               int32_t world, const int64_t* shard_doc_base, const int64_t* doc_chunk_offset,
+                               const int32_t* doc_chunk_len, const uint64_t* shard_kv_base, int64_t chunk_bytes,
+                               int64_t* plan, int64_t* n_sel, int64_t* total, int64_t* total_host_mapped,
+                               void* stream) {
+  MSA_REQUIRE(sel_local && shard_doc_base && doc_chunk_offset && doc_chunk_len && shard_kv_base && plan && n_sel &&
+                  total, "gather_plan: null pointer");
+  MSA_REQUIRE(n_seq >= 0 && k >= 1 && k <= kPlanMaxK && world >= 1, "gather_plan: bad sizes (k must be <= %d)",
+              kPlanMaxK);
+  MSA_REQUIRE(chunk_bytes > 0 && chunk_bytes % 16 == 0, "gather_plan: chunk_bytes must be a multiple of 16");
+  gather_plan_kernel<<<1, kPlanThreads, 0, (cudaStream_t)stream>>>(
+      sel_local, sel_rank, n_seq, k, world, shard_doc_base, doc_chunk_offset, doc_chunk_len, shard_kv_base,
+      chunk_bytes, plan, n_sel, total, total_host_mapped);
+  MSA_LAUNCH_OK("gather_plan_kernel");
+  return MSA_OK;
+}
+
+extern "C" int msa_gather_run(const int64_t* plan, int32_t n_items, int32_t dtype, int32_t n_kv_heads,
+                              int32_t head_dim, void* out_k, void* out_v, int64_t out_head_stride,
+                              int64_t out_entries, void* stream) {
+  MSA_REQUIRE(dtype_ok(dtype), "gather_run: unknown dtype %d", dtype);
+  MSA_REQUIRE(plan && n_items >= 0 && n_kv_heads > 0 && head_dim > 0, "gather_run: bad arguments");
+  const int vec = 16 / (int)dtype_size(dtype);
+  MSA_REQUIRE(head_dim % vec == 0 && out_head_stride % vec == 0, "gather_run: rows must be 16-byte multiples");
+  if (n_items == 0 || out_entries == 0) return MSA_OK;
+  MSA_REQUIRE(out_k && out_v && aligned16(out_k) && aligned16(out_v), "gather_run: bad output pointers");
+  if (dtype == MSA_BF16)
+    gather_kernel<__nv_bfloat16><<<n_items, kGatherThreads, 0, (cudaStream_t)stream>>>(
+        plan, n_kv_heads, head_dim, (__nv_bfloat16*)out_k, (__nv_bfloat16*)out_v, out_head_stride, out_entries);
+  else
+    gather_kernel<float><<<n_items, kGatherThreads, 0, (cudaStream_t)stream>>>(
+        plan, n_kv_heads, head_dim, (float*)out_k, (float*)out_v, out_head_stride, out_entries);
+  MSA_LAUNCH_OK("gather_kernel");
+  return MSA_OK;
+}

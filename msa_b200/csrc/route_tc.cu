@@ -1,0 +1,396 @@
+// Routing on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), bf16.
+//
+// The head-mean score of every (query token, chunk) pair is one 1024-wide dot product of
+// the folded query row with the chunk's pooled router key, so a layer's scoring is the
+// contraction  S[c, r] = sum_k Kr[c, k] * Qf[r, k]  followed by reductions.  The kernel
+// puts CHUNKS on the UMMA M axis (128 TMEM lanes = 128 chunks) and QUERY ROWS on the N
+// axis (TMEM columns): after tcgen05.ld each epilogue thread owns one chunk and sees all
+// query rows of the tile in its registers, so
+//     max over a sequence's tokens   = an in-thread max over columns  (no shuffles),
+//     max over a document's chunks   = one redux.sync over the lanes of that document,
+//     table update                   = one atomicMax on an order-preserving key per
+//                                      (sequence, document, warp).
+// Per-(token, chunk) scores therefore never leave the SM.
+//
+// Persistent, warp specialised: warps 0-3 epilogue (TMEM lane quarter = warp id), warp 4
+// TMA producer, warp 5 MMA issuer + TMEM owner.  Operands are streamed in 64-element
+// (128-byte, SWIZZLE_128B) K blocks through a ring of shared-memory stages; two TMEM
+// accumulators let the epilogue of tile i overlap the MMAs of tile i+1.  Loads are plain
+// per-CTA TMA (no cluster qualifiers).  Every mbarrier wait is bounded by a wall-clock
+// limit; on expiry the CTA raises status[0], drains what it has in flight, frees TMEM and
+// returns.
+//
+// Bounds: flops = 2*rows*chunks*kdim on the tensor pipe; bytes = chunks*kdim*2 (router keys,
+// once) + rows*kdim*2 (queries) from HBM.  Tensor bound when rows >~ 220, HBM bound below.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "route.cuh"
+
+namespace msa {
+
+constexpr int kBM = 128;        // chunks per tile (UMMA M)
+constexpr int kBK = 64;         // bf16 elements per K block = one 128-byte swizzle row
+constexpr int kUmmaK = 16;      // K of one tcgen05.mma (bf16)
+constexpr int kTcThreads = 192;
+constexpr int kEpiThreads = 128;
+constexpr int kMaxStages = 8;
+constexpr int kTmemCols = 512;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per barrier wait
+
+struct RouteTcParams {
+  int n_rows, n_seq, s_pad, bn, n_chunks, n_ctiles, n_qtiles, qgroup, k_blocks, stages;
+  float alpha;
+  const float* row_bias;
+  const int32_t* chunk_doc;
+  uint32_t* keys;
+  long long table_stride;
+  int32_t* status;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait.  Returns false (and raises the abort flag + status word) when the limit
+// runs out or another role of this CTA already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
+                                          int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 0) {
+      if (*abort_flag) return false;
+      if (global_ns() - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile in shared memory, rows of 128 bytes, SWIZZLE_128B: 8-row groups are
+// 1024 bytes apart (stride byte offset); the leading byte offset is unused for this layout.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;                // leading byte offset (16 B units), ignored
+  d |= (uint64_t)(1024u >> 4) << 32;     // stride byte offset
+  d |= (uint64_t)1 << 46;                // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                // SWIZZLE_128B
+  return d;
+}
+
+struct TileCoord { int ct, qt; };
+__device__ __forceinline__ TileCoord tile_coord(const RouteTcParams& p, long long t) {
+  // query tiles are walked in groups small enough to stay in L2 while every chunk tile passes
+  const long long per_group = (long long)p.n_ctiles * p.qgroup;
+  const int grp = (int)(t / per_group);
+  const long long r = t - grp * per_group;
+  const int gq = min(p.qgroup, p.n_qtiles - grp * p.qgroup);
+  return TileCoord{(int)(r / gq), grp * p.qgroup + (int)(r % gq)};
+}
+
+__global__ void __launch_bounds__(kTcThreads, 1)
+route_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_q,
+                const RouteTcParams p) {
+  extern __shared__ unsigned char smem_dyn[];
+  __shared__ uint64_t s_full[kMaxStages], s_empty[kMaxStages], s_acc_full[2], s_acc_empty[2], s_drain;
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+  __shared__ float s_bias[kEpiThreads / 32][kRouteMaxN];  // one private copy per epilogue warp
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  const uint32_t a_bytes = kBM * kBK * 2, b_bytes = (uint32_t)p.bn * kBK * 2, stage_bytes = a_bytes + b_bytes;
+  volatile int* abort_flag = &s_abort;
+  const long long n_tiles = (long long)p.n_ctiles * p.n_qtiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&s_acc_full[b], 1); mbar_init(&s_acc_empty[b], kEpiThreads / 32); }
+    mbar_init(&s_drain, 1);
+    s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
+                 "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+
+  if (warp == 4) {
+    // ------------------------------- TMA producer -------------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0, armed = 0, armed_parity = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+        const TileCoord tc = tile_coord(p, t);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!(ok = mbar_wait(&s_empty[stage], phase ^ 1u, abort_flag, p.status, 1))) break;
+          unsigned char* sa = tiles + (size_t)stage * stage_bytes;
+          mbar_expect_tx(&s_full[stage], stage_bytes);
+          tma_load_2d(sa, &tmap_k, kb * kBK, tc.ct * kBM, &s_full[stage]);
+          tma_load_2d(sa + a_bytes, &tmap_q, kb * kBK, tc.qt * p.bn, &s_full[stage]);
+          armed |= 1u << stage;
+          armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {  // gave up: let the copies already issued land before the CTA's smem is released
+        for (int s = 0; s < p.stages; ++s)
+          if (armed & (1u << s)) {
+            const unsigned long long t0 = global_ns();
+            while (!mbar_try_wait(&s_full[s], (armed_parity >> s) & 1u) && global_ns() - t0 < kWaitLimitNs) {}
+          }
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------- MMA issuer ----------------------------------------
+    if (lane == 0) {
+      // instruction descriptor: D=f32, A=B=bf16, both K-major, N=bn, M=128
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.bn >> 3) << 17) |
+                             ((uint32_t)(kBM >> 4) << 24);
+      int stage = 0;
+      uint32_t phase = 0;
+      long long it = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++it) {
+        const int buf = (int)(it & 1);
+        const uint32_t acc_phase = (uint32_t)((it >> 1) & 1);
+        if (!(ok = mbar_wait(&s_acc_empty[buf], acc_phase ^ 1u, abort_flag, p.status, 2))) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)buf * kRouteMaxN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!(ok = mbar_wait(&s_full[stage], phase, abort_flag, p.status, 3))) break;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(tiles + (size_t)stage * stage_bytes);
+          const uint64_t a_desc = make_smem_desc(sa), b_desc = make_smem_desc(sa + a_bytes);
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k)  // +32 bytes of K per step = +2 in the address field
+            tc_mma_bf16(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc,
+                        (kb > 0 || k > 0) ? 1u : 0u);
+          tc_commit(&s_empty[stage]);  // frees the stage once these MMAs have read it
+          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) tc_commit(&s_acc_full[buf]);
+      }
+      // drain: everything issued so far must retire before TMEM is freed
+      tc_commit(&s_drain);
+      const unsigned long long t0 = global_ns();
+      while (!mbar_try_wait(&s_drain, 0) && global_ns() - t0 < kWaitLimitNs) {}
+    }
+  } else {
+    // ------------------------------- epilogue (warps 0-3) ------------------------------
+    const int seg = min(p.s_pad, p.bn);  // columns of one sequence inside a tile
+    long long it = 0;
+    bool ok = true;
+    for (long long t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++it) {
+      const TileCoord tc = tile_coord(p, t);
+      const int buf = (int)(it & 1);
+      const uint32_t acc_phase = (uint32_t)((it >> 1) & 1);
+      const int q0 = tc.qt * p.bn;
+      float* bias = s_bias[warp];
+      __syncwarp();  // the previous tile's reads of this warp's bias copy are done
+      for (int j = lane; j < p.bn; j += 32) bias[j] = (q0 + j < p.n_rows) ? p.row_bias[q0 + j] : -INFINITY;
+      const int chunk = tc.ct * kBM + threadIdx.x;
+      const int doc = chunk < p.n_chunks ? p.chunk_doc[chunk] : -1 - lane;  // out-of-range lanes stay alone
+      const uint32_t seg_mask = __match_any_sync(0xffffffffu, doc);
+      const bool leader = doc > 0 && lane == (__ffs(seg_mask) - 1);
+      __syncwarp();
+      // every lane waits; the warp then agrees on the outcome so that it never diverges
+      ok = mbar_wait(&s_acc_full[buf], acc_phase, abort_flag, p.status, 4);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)buf * kRouteMaxN;
+
+      auto emit = [&](float v, int seq) {  // document max over this warp's lanes, then one atomic
+        const uint32_t key = __reduce_max_sync(seg_mask, float_to_key(v * p.alpha));
+        if (leader && seq < p.n_seq) atomicMax(p.keys + (long long)seq * p.table_stride + doc, key);
+      };
+      if (p.s_pad == 1) {
+        for (int c0 = 0; c0 < p.bn; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld16(taddr + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) emit(__uint_as_float(r[j]) + bias[c0 + j], q0 + c0 + j);
+        }
+      } else {
+        for (int s0 = 0; s0 < p.bn; s0 += seg) {
+          float run = -INFINITY;
+          for (int c0 = s0; c0 < s0 + seg; c0 += 16) {
+            uint32_t r[16];
+            tmem_ld16(taddr + c0, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) run = fmaxf(run, __uint_as_float(r[j]) + bias[c0 + j]);
+          }
+          emit(run, (q0 + s0) / p.s_pad);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_acc_empty[buf]);
+    }
+  }
+
+  // teardown: all roles meet, then the allocating warp returns TMEM
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 5)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+}
+
+// ---- host side ------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+static int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride_elems,
+                    uint32_t box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) { set_error("route: cuTensorMapEncodeTiled is not available from the driver"); return MSA_ERR_CUDA; }
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {row_stride_elems * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kBK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("route: cuTensorMapEncodeTiled failed with code %d", (int)r); return MSA_ERR_CUDA; }
+  return MSA_OK;
+}
+
+int launch_route_tc(const void* qf, const float* row_bias, int n_seq, int s_pad, const void* rk, int64_t rk_stride,
+                    int n_chunks, int kdim, const int32_t* chunk_doc, float alpha, uint32_t* keys,
+                    int64_t table_stride, int32_t* status, cudaStream_t stream) {
+  MSA_REQUIRE(kdim % kBK == 0, "route (tensor-core path): kdim=%d must be a multiple of %d", kdim, kBK);
+  MSA_REQUIRE(aligned16(qf) && aligned16(rk) && rk_stride % 8 == 0 && rk_stride >= kdim,
+              "route (tensor-core path): rows must be 16-byte aligned");
+  RouteTcParams p{};
+  p.n_seq = n_seq; p.s_pad = s_pad; p.n_rows = n_seq * s_pad; p.n_chunks = n_chunks;
+  if (s_pad == 1) {
+    p.bn = n_seq >= kRouteMaxN ? kRouteMaxN : (n_seq + 15) / 16 * 16;
+  } else {
+    MSA_REQUIRE(s_pad % 16 == 0, "route: s_pad=%d must be 1 or a multiple of 16 (see msa_route_s_pad)", s_pad);
+    if (s_pad <= kRouteMaxN) {
+      int per_tile = kRouteMaxN / s_pad;
+      if (per_tile > n_seq) per_tile = n_seq;
+      p.bn = s_pad * per_tile;
+    } else {
+      const int nt = (s_pad + kRouteMaxN - 1) / kRouteMaxN;
+      MSA_REQUIRE(s_pad % nt == 0 && (s_pad / nt) % 16 == 0,
+                  "route: s_pad=%d cannot be cut into equal 16-row-aligned tiles (see msa_route_s_pad)", s_pad);
+      p.bn = s_pad / nt;
+    }
+  }
+  p.n_ctiles = (n_chunks + kBM - 1) / kBM;
+  p.n_qtiles = (p.n_rows + p.bn - 1) / p.bn;
+  p.k_blocks = kdim / kBK;
+  const size_t stage_bytes = (size_t)kBM * kBK * 2 + (size_t)p.bn * kBK * 2;
+  p.stages = (int)((216 * 1024) / stage_bytes);
+  if (p.stages > kMaxStages) p.stages = kMaxStages;
+  MSA_REQUIRE(p.stages >= 2, "route: tile does not fit shared memory");
+  const size_t qtile_bytes = (size_t)p.bn * kdim * 2;
+  p.qgroup = (int)((32u << 20) / qtile_bytes);
+  if (p.qgroup < 1) p.qgroup = 1;
+  if (p.qgroup > p.n_qtiles) p.qgroup = p.n_qtiles;
+  p.alpha = alpha; p.row_bias = row_bias; p.chunk_doc = chunk_doc; p.keys = keys; p.table_stride = table_stride;
+  p.status = status;
+
+  CUtensorMap map_k, map_q;
+  int rc = make_map(&map_k, rk, (uint64_t)n_chunks, (uint64_t)kdim, (uint64_t)rk_stride, kBM);
+  if (rc != MSA_OK) return rc;
+  rc = make_map(&map_q, qf, (uint64_t)p.n_rows, (uint64_t)kdim, (uint64_t)kdim, (uint32_t)p.bn);
+  if (rc != MSA_OK) return rc;
+
+  static thread_local int n_sm = 0;
+  static thread_local size_t smem_set = 0;
+  if (n_sm == 0) {
+    int dev = 0;
+    MSA_CUDA_OK(cudaGetDevice(&dev));
+    MSA_CUDA_OK(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+  }
+  const size_t smem = (size_t)p.stages * stage_bytes + 1024;
+  if (smem > smem_set) {
+    MSA_CUDA_OK(cudaFuncSetAttribute(route_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    smem_set = smem;
+  }
+  const long long n_tiles = (long long)p.n_ctiles * p.n_qtiles;
+  const int grid = (int)(n_tiles < n_sm ? n_tiles : n_sm);
+  route_tc_kernel<<<grid, kTcThreads, smem, stream>>>(map_k, map_q, p);
+  MSA_LAUNCH_OK("route_tc_kernel");
+  return MSA_OK;
+}
+
+}  // namespace msa

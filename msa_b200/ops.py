@@ -1,0 +1,262 @@
+"""Functional wrappers: torch tensors in, torch tensors out, one C-ABI call each.
+
+These are what ``memory.py``, ``service.py`` and ``attention.py`` (the mirrors of the
+reference's ``Memory``, ``MSAService`` and ``MemorySparseAttention``) are built from.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import _cabi as A
+
+
+# ---------------------------------------------------------------------------------------
+# Stage 1
+# ---------------------------------------------------------------------------------------
+
+def chunk_bookkeeping(doc_ids: torch.Tensor, attention_mask: Optional[torch.Tensor], pooling_kernel_size: int,
+                      max_chunks: Optional[int] = None):
+    """Device version of src/msa/memory_sparse_attention.py:138-163.
+
+    doc_ids ``[B, T]`` int64 (CUDA).  Returns ``(token_index[Td] int32, chunk_offsets[C+1] int32,
+    pooled_doc_ids[C] int64)``.  Reads two integers back from the device to size the results
+    (the reference synchronises at the same spot through ``.item()``).
+    """
+    A.need_cuda(doc_ids, attention_mask)
+    doc_ids = doc_ids.contiguous()
+    if doc_ids.dtype != torch.int64:
+        raise A.MsaError("doc_ids must be int64")
+    if attention_mask is not None:
+        attention_mask = attention_mask.to(torch.int64).contiguous()
+    rows, row_len = doc_ids.shape
+    n = rows * row_len
+    if max_chunks is None:
+        # every document adds at most one partial chunk; a document has at least one token
+        max_chunks = n // pooling_kernel_size + min(n, int(doc_ids.max().item()) * rows if n else 0) + 1
+    dev = doc_ids.device
+    token_index = torch.empty(max(n, 1), dtype=torch.int32, device=dev)
+    chunk_offsets = torch.empty(max_chunks + 1, dtype=torch.int32, device=dev)
+    pooled = torch.empty(max(max_chunks, 1), dtype=torch.int64, device=dev)
+    counts = torch.zeros(4, dtype=torch.int32, device=dev)
+    A.check(A.lib().msa_chunk_bookkeeping(A.ptr(doc_ids), A.ptr(attention_mask), rows, row_len, pooling_kernel_size,
+                                          A.ptr(token_index), A.ptr(chunk_offsets), A.ptr(pooled), max_chunks,
+                                          A.ptr(counts), A.stream_ptr(dev)), "msa_chunk_bookkeeping")
+    n_tok, n_chunks, overflow, _ = counts.tolist()
+    if overflow:
+        raise A.MsaError(f"chunk_bookkeeping: more than max_chunks={max_chunks} chunks")
+    return token_index[:n_tok], chunk_offsets[: n_chunks + 1], pooled[:n_chunks]
+
+
+def pool_chunks(states: torch.Tensor, chunk_offsets: torch.Tensor, token_index: Optional[torch.Tensor] = None,
+                l2_normalize: bool = False, head_major_out: bool = False) -> torch.Tensor:
+    """Chunk mean of ``states``.
+
+    ``states`` is ``[1, H, T, D]`` (the layer's key/value states, head major) or ``[T, H, D]``.
+    Returns ``[C, H, D]`` (chunk major, the bank's layout) or, with ``head_major_out``,
+    ``[1, H, C, D]`` as the reference stores it (src/msa/memory_sparse_attention.py:173-174).
+    """
+    A.need_cuda(states, chunk_offsets, token_index)
+    if states.dim() == 4:
+        if states.shape[0] != 1:
+            raise A.MsaError("pool_chunks: a [B, H, T, D] input needs B == 1 (call it per row)")
+        _, h, t, d = states.shape
+        states = states.contiguous()
+        tok_stride, head_stride = d, t * d
+    elif states.dim() == 3:
+        t, h, d = states.shape
+        states = states.contiguous()
+        tok_stride, head_stride = h * d, d
+    else:
+        raise A.MsaError("pool_chunks: states must be [1, H, T, D] or [T, H, D]")
+    c = chunk_offsets.numel() - 1
+    dev = states.device
+    if head_major_out:
+        out = torch.empty((1, h, c, d), dtype=states.dtype, device=dev)
+        oc, oh = d, c * d
+    else:
+        out = torch.empty((c, h, d), dtype=states.dtype, device=dev)
+        oc, oh = h * d, d
+    if c > 0:
+        A.check(A.lib().msa_pool_chunks(A.ptr(states), A.dtype_code(states.dtype), tok_stride, head_stride,
+                                        A.ptr(token_index), A.ptr(chunk_offsets.contiguous()), None, c, h, d,
+                                        A.ptr(out), oc, oh, int(l2_normalize), A.stream_ptr(dev)), "msa_pool_chunks")
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+# Routing
+# ---------------------------------------------------------------------------------------
+
+def route_s_pad(seq_len: int, query_reduce: str = "max") -> int:
+    return int(A.lib().msa_route_s_pad(seq_len, A.QREDUCE[query_reduce]))
+
+
+def fold_queries(q: torch.Tensor, query_mask: torch.Tensor, num_kv_groups: int, l2_normalize: bool = False,
+                 query_reduce: str = "max", s_pad: Optional[int] = None):
+    """q ``[B, Hq, S, D]`` (any strides with D contiguous), query_mask ``[B, S]`` bool.
+    Returns ``(q_folded[B*s_pad, Hkv*D], row_bias[B*s_pad] f32, s_pad)``."""
+    A.need_cuda(q, query_mask)
+    b, hq, s, d = q.shape
+    if q.stride(3) != 1:
+        q = q.contiguous()
+    mask = query_mask.reshape(b, s).to(torch.uint8).contiguous()
+    if s_pad is None:
+        s_pad = route_s_pad(s, query_reduce)
+    hkv = hq // num_kv_groups
+    dev = q.device
+    qf = torch.empty((b * s_pad, hkv * d), dtype=q.dtype, device=dev)
+    bias = torch.empty((b * s_pad,), dtype=torch.float32, device=dev)
+    A.check(A.lib().msa_fold_queries(A.ptr(q), A.dtype_code(q.dtype), q.stride(0), q.stride(1), q.stride(2),
+                                     A.ptr(mask), s, b, hq, num_kv_groups, s, d, int(l2_normalize),
+                                     A.QREDUCE[query_reduce], s_pad, A.ptr(qf), A.ptr(bias), A.stream_ptr(dev)),
+            "msa_fold_queries")
+    return qf, bias, s_pad
+
+
+def route_scores(q_folded: torch.Tensor, row_bias: torch.Tensor, n_seq: int, s_pad: int, rk: torch.Tensor,
+                 chunk_doc: torch.Tensor, n_docs: int, alpha: float, min_val: Optional[float] = None,
+                 keys: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None, flags: int = 0):
+    """Score table as order-preserving keys: int32 storage ``[n_seq, n_docs + 1]``.
+    rk ``[C, Hkv*D]`` or ``[C, Hkv, D]`` (chunk major; the chunk stride may exceed the row)."""
+    A.need_cuda(q_folded, row_bias, rk, chunk_doc)
+    dev = rk.device
+    c = rk.shape[0]
+    rk2 = rk.reshape(c, -1) if rk.is_contiguous() else rk.flatten(1)
+    if rk2.stride(1) != 1 and c > 0:
+        raise A.MsaError("route_scores: router keys must have a contiguous feature axis")
+    kdim = rk2.shape[1]
+    if chunk_doc.dtype != torch.int32:
+        raise A.MsaError("route_scores: chunk_doc must be int32")
+    if min_val is None:
+        min_val = torch.finfo(rk.dtype).min
+    if keys is None:
+        keys = torch.empty((n_seq, n_docs + 1), dtype=torch.int32, device=dev)
+    if status is None:
+        status = torch.zeros(4, dtype=torch.int32, device=dev)
+    A.check(A.lib().msa_route_scores(A.ptr(q_folded), A.ptr(row_bias), A.dtype_code(rk.dtype), n_seq, s_pad,
+                                     A.ptr(rk2), rk2.stride(0) if c > 0 else kdim, c, kdim, A.ptr(chunk_doc),
+                                     float(alpha), A.ptr(keys), keys.stride(0), n_docs, float(min_val), flags,
+                                     A.ptr(status), A.stream_ptr(dev)), "msa_route_scores")
+    return keys, status
+
+
+def topk_select(keys: torch.Tensor, k: int, doc_ids_table: Optional[torch.Tensor] = None, n_cols: Optional[int] = None):
+    """Exact top-k of every row of a key table.  Returns ``(scores f32, local_ids i64, global_ids i64)``,
+    each ``[n_seq, min(k, n_cols)]``, sorted by descending score (ties: ascending column)."""
+    A.need_cuda(keys, doc_ids_table)
+    n_seq = keys.shape[0]
+    n_cols = keys.shape[1] if n_cols is None else n_cols
+    k_eff = min(k, n_cols)
+    dev = keys.device
+    scores = torch.empty((n_seq, k_eff), dtype=torch.float32, device=dev)
+    local = torch.empty((n_seq, k_eff), dtype=torch.int64, device=dev)
+    glob = torch.empty((n_seq, k_eff), dtype=torch.int64, device=dev)
+    A.check(A.lib().msa_topk_select(A.ptr(keys), keys.stride(0), n_seq, n_cols, k, A.ptr(doc_ids_table),
+                                    A.ptr(scores), A.ptr(local), A.ptr(glob), A.stream_ptr(dev)), "msa_topk_select")
+    return scores, local, glob
+
+
+def topk_merge(cand_scores: torch.Tensor, cand_local: torch.Tensor, cand_global: torch.Tensor, k: int,
+               seq_offset: int = 0, n_seq: Optional[int] = None, invalid_below: float = -1e9):
+    """cand_* ``[W, B_all, kc]`` contiguous; merges sequences ``seq_offset .. seq_offset+n_seq``.
+    Returns ``(scores[n_seq,k] f32, local[n_seq,k] i64 (-1 = invalid), global[n_seq,k] i64, rank[n_seq,k] i32)``."""
+    A.need_cuda(cand_scores, cand_local, cand_global)
+    w, b_all, kc = cand_scores.shape
+    n_seq = b_all - seq_offset if n_seq is None else n_seq
+    dev = cand_scores.device
+    k = min(k, w * kc)
+    cs, cl, cg = cand_scores.contiguous(), cand_local.contiguous(), cand_global.contiguous()
+    out_s = torch.empty((n_seq, k), dtype=torch.float32, device=dev)
+    out_l = torch.empty((n_seq, k), dtype=torch.int64, device=dev)
+    out_g = torch.empty((n_seq, k), dtype=torch.int64, device=dev)
+    out_r = torch.empty((n_seq, k), dtype=torch.int32, device=dev)
+    off = seq_offset * kc
+    A.check(A.lib().msa_topk_merge(A.ptr(cs) + off * 4, A.ptr(cl) + off * 8, A.ptr(cg) + off * 8, b_all * kc, w,
+                                   n_seq, kc, k, invalid_below, A.ptr(out_s), A.ptr(out_l), A.ptr(out_g),
+                                   A.ptr(out_r), A.stream_ptr(dev)), "msa_topk_merge")
+    return out_s, out_l, out_g, out_r
+
+
+# ---------------------------------------------------------------------------------------
+# Fetch
+# ---------------------------------------------------------------------------------------
+
+def gather_plan(sel_local: torch.Tensor, sel_rank: Optional[torch.Tensor], world: int, shard_doc_base: torch.Tensor,
+                doc_chunk_offset: torch.Tensor, doc_chunk_len: torch.Tensor, shard_kv_base: torch.Tensor,
+                chunk_bytes: int, total_host: Optional[torch.Tensor] = None):
+    A.need_cuda(sel_local, sel_rank, shard_doc_base, doc_chunk_offset, doc_chunk_len, shard_kv_base)
+    n_seq, k = sel_local.shape
+    dev = sel_local.device
+    plan = torch.empty((n_seq * k, 4), dtype=torch.int64, device=dev)
+    n_sel = torch.empty((n_seq,), dtype=torch.int64, device=dev)
+    total = torch.empty((1,), dtype=torch.int64, device=dev)
+    A.check(A.lib().msa_gather_plan(A.ptr(sel_local.contiguous()), A.ptr(sel_rank.contiguous() if sel_rank is not None else None),
+                                    n_seq, k, world, A.ptr(shard_doc_base), A.ptr(doc_chunk_offset),
+                                    A.ptr(doc_chunk_len), A.ptr(shard_kv_base), chunk_bytes, A.ptr(plan), A.ptr(n_sel),
+                                    A.ptr(total), A.ptr(total_host), A.stream_ptr(dev)), "msa_gather_plan")
+    return plan, n_sel, total
+
+
+def gather_run(plan: torch.Tensor, dtype: torch.dtype, n_kv_heads: int, head_dim: int, out_entries: int):
+    dev = plan.device
+    out_k = torch.empty((n_kv_heads, out_entries, head_dim), dtype=dtype, device=dev)
+    out_v = torch.empty((n_kv_heads, out_entries, head_dim), dtype=dtype, device=dev)
+    A.check(A.lib().msa_gather_run(A.ptr(plan), plan.shape[0], A.dtype_code(dtype), n_kv_heads, head_dim,
+                                   A.ptr(out_k), A.ptr(out_v), out_entries * head_dim, out_entries,
+                                   A.stream_ptr(dev)), "msa_gather_run")
+    return out_k, out_v
+
+
+# ---------------------------------------------------------------------------------------
+# Decode attention
+# ---------------------------------------------------------------------------------------
+
+def decode_splits(n_seq: int, n_kv_heads: int, max_len: int, n_sm: int = 148) -> int:
+    """Enough KV splits to put about two CTAs on every SM, each with at least 256 keys."""
+    want = max(1, (2 * n_sm + n_seq * n_kv_heads - 1) // max(1, n_seq * n_kv_heads))
+    return max(1, min(want, max(1, max_len // 256)))
+
+
+def sparse_decode_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kv_len: torch.Tensor,
+                       new_k: Optional[torch.Tensor] = None, new_v: Optional[torch.Tensor] = None,
+                       kv_start: Optional[torch.Tensor] = None, scale: Optional[float] = None,
+                       n_splits: Optional[int] = None, workspace: Optional[torch.Tensor] = None,
+                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q ``[B, Hq, D]``; caches ``[B, Hkv, Lcap, D]`` (position axis contiguous per head);
+    kv_len / kv_start ``[B]`` int32; new_k / new_v ``[B, Hkv, D]``.  Returns ``[B, Hq*D]``."""
+    A.need_cuda(q, k_cache, v_cache, kv_len, new_k, new_v, kv_start)
+    b, hq, d = q.shape
+    hkv, cap = k_cache.shape[1], k_cache.shape[2]
+    if k_cache.stride(3) != 1 or k_cache.stride(2) != d or v_cache.stride() != k_cache.stride():
+        raise A.MsaError("sparse_decode_attn: caches must be [B, Hkv, L, D] with contiguous (L, D)")
+    if kv_len.dtype != torch.int32 or (kv_start is not None and kv_start.dtype != torch.int32):
+        raise A.MsaError("sparse_decode_attn: kv_len / kv_start must be int32")
+    dev = q.device
+    q = q.contiguous()
+    if new_k is not None:
+        new_k, new_v = new_k.contiguous(), new_v.contiguous()
+    if n_splits is None:
+        n_splits = decode_splits(b, hkv, cap)
+    need = int(A.lib().msa_decode_workspace_bytes(b, hq, d, n_splits))
+    if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
+        workspace = torch.empty(need // 4, dtype=torch.float32, device=dev)
+    if out is None:
+        out = torch.empty((b, hq * d), dtype=q.dtype, device=dev)
+    scale = (1.0 / math.sqrt(d)) if scale is None else scale
+    A.check(A.lib().msa_sparse_decode_attn(A.ptr(q), A.dtype_code(q.dtype), A.ptr(k_cache), A.ptr(v_cache),
+                                           k_cache.stride(0), k_cache.stride(1), A.ptr(kv_start), A.ptr(kv_len),
+                                           A.ptr(new_k), A.ptr(new_v), b, hq, hkv, d, float(scale), A.ptr(out),
+                                           A.ptr(workspace), workspace.numel() * 4 if workspace is not None else 0,
+                                           n_splits, A.stream_ptr(dev)), "msa_sparse_decode_attn")
+    return out
+
+
+def keys_to_scores(keys: torch.Tensor) -> torch.Tensor:
+    """Decode a table of order-preserving keys (int32 storage) back to float32 scores."""
+    u = keys.to(torch.int64) & 0xFFFFFFFF
+    bits = torch.where((u & 0x80000000) != 0, u & 0x7FFFFFFF, (~u) & 0xFFFFFFFF)
+    bits = torch.where(bits >= 2 ** 31, bits - 2 ** 32, bits).to(torch.int32)
+    return bits.view(torch.float32)

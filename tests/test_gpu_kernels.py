@@ -1,0 +1,360 @@
+"""Parity of every CUDA kernel (through the C ABI) with the oracle and the golden fixtures.
+
+Tolerances are BASELINE.json's: pooling and attention 1e-5 (fp32) / 1e-2 (bf16) norm-wise
+relative error, routing scores 1e-3 absolute, top-k exact outside a 1e-3 score gap.
+"""
+import math
+
+import pytest
+import torch
+
+from oracle import msa_oracle as O
+from tests.util import T, check_topk, make_bank, ragged_docs, rel_err
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from msa_b200 import ops as _ops
+    return _ops
+
+
+# ----------------------------------------------------------------------------- stage 1
+def test_bookkeeping_golden(ops, golden):
+    g = golden("pooling_ragged")
+    doc_ids, am = T(g["doc_ids"]).to(DEV), T(g["attention_mask"]).to(DEV)
+    tok, off, pooled = ops.chunk_bookkeeping(doc_ids, am, int(g["pooling_kernel_size"]))
+    di, gci, ref_pooled, ref_len = O.chunk_bookkeeping(T(g["doc_ids"]), T(g["attention_mask"]), int(g["pooling_kernel_size"]))
+    assert tok.cpu().tolist() == di[:, 1].tolist()
+    assert (off[1:] - off[:-1]).cpu().tolist() == ref_len.tolist()
+    assert pooled.cpu().tolist() == ref_pooled.tolist()
+
+
+@pytest.mark.parametrize("rows", [1, 3])
+def test_bookkeeping_ragged_rows_and_padding(ops, rows):
+    g = torch.Generator().manual_seed(7 + rows)
+    p = 64
+    ids_rows, mask_rows = [], []
+    for r in range(rows):
+        lens = torch.randint(1, 400, (23,), generator=g).tolist()
+        ids = [-2] * 3
+        for i, n in enumerate(lens):
+            ids += [i + 1] * n
+        ids_rows.append(ids)
+    width = max(len(x) for x in ids_rows)
+    doc_ids = torch.zeros(rows, width, dtype=torch.long)
+    am = torch.zeros(rows, width, dtype=torch.long)
+    for r, ids in enumerate(ids_rows):
+        doc_ids[r, : len(ids)] = torch.tensor(ids)
+        am[r, : len(ids)] = 1
+    doc_ids[am == 0] = 5  # garbage under the padding must be ignored through the mask
+    tok, off, pooled = ops.chunk_bookkeeping(doc_ids.to(DEV), am.to(DEV), p)
+    di, gci, ref_pooled, ref_len = O.chunk_bookkeeping(doc_ids, am, p)
+    assert tok.cpu().tolist() == (di[:, 0] * width + di[:, 1]).tolist()
+    assert (off[1:] - off[:-1]).cpu().tolist() == ref_len.tolist()
+    assert pooled.cpu().tolist() == ref_pooled.tolist()
+
+
+def test_pooling_golden_fp32(ops, golden):
+    g = golden("pooling_ragged")
+    doc_ids, am = T(g["doc_ids"]).to(DEV), T(g["attention_mask"]).to(DEV)
+    tok, off, _ = ops.chunk_bookkeeping(doc_ids, am, int(g["pooling_kernel_size"]))
+    for name, ref in (("key_states", "pooled_k"), ("value_states", "pooled_v")):
+        out = ops.pool_chunks(T(g[name]).to(DEV), off, tok)
+        assert rel_err(out, T(g[ref])) < 1e-5
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 1e-2)])
+@pytest.mark.parametrize("head_major", [True, False])
+def test_pooling_real_shape(ops, dtype, tol, head_major):
+    g = torch.Generator().manual_seed(11)
+    lens = ragged_docs(37, 1, 700, seed=5) + [512, 64, 1]
+    ids = [-2, -2, -2]
+    for i, n in enumerate(lens):
+        ids += [i + 1] * n
+    doc_ids = torch.tensor([ids])
+    t = doc_ids.shape[1]
+    k = torch.randn(1, 8, t, 128, generator=g).to(dtype)
+    tok, off, pooled_ids = ops.chunk_bookkeeping(doc_ids.to(DEV), None, 64)
+    di, gci, ref_pooled, ref_len = O.chunk_bookkeeping(doc_ids, torch.ones_like(doc_ids), 64)
+    k_docs = k[0][:, di[:, 1]].transpose(0, 1)                       # [Td, H, D]
+    exact = O.pool_chunks_exact(k_docs, ref_len)
+    src = k.to(DEV) if head_major else k[0].transpose(0, 1).contiguous().to(DEV)
+    out = ops.pool_chunks(src, off, tok)
+    assert out.shape == (ref_len.numel(), 8, 128)
+    assert rel_err(out, exact) < tol
+    # the reference's own cumsum-difference formula is no closer to the exact mean
+    assert rel_err(O.pool_chunks_cumsum(k_docs.float(), ref_len), exact) < 1e-5
+    # reference layout + fused L2 normalisation of the router keys
+    outn = ops.pool_chunks(src, off, tok, l2_normalize=True, head_major_out=True)
+    ref_n = O.l2_normalize(exact.float()).transpose(0, 1).unsqueeze(0)
+    assert outn.shape == ref_n.shape and rel_err(outn, ref_n) < tol
+
+
+# ----------------------------------------------------------------------------- routing
+def _route(ops, q5, mask, rk_chd, pool_ids, n_docs, k, table=None, query_reduce="max", normalize=False, scale=1.0,
+           flags=0):
+    b, hkv, grp, s, d = q5.shape
+    q = q5.reshape(b, hkv * grp, s, d).to(DEV)
+    qf, bias, s_pad = ops.fold_queries(q, mask.to(DEV), grp, l2_normalize=normalize, query_reduce=query_reduce)
+    keys, status = ops.route_scores(qf, bias, b, s_pad, rk_chd.to(DEV), pool_ids.to(torch.int32).to(DEV), n_docs,
+                                    alpha=scale / (hkv * grp), min_val=torch.finfo(q5.dtype).min, flags=flags)
+    assert status.cpu().tolist()[0] == 0, "a barrier wait ran out inside the routing kernel"
+    return ops.topk_select(keys, k, None if table is None else table.to(DEV)), ops.keys_to_scores(keys)
+
+
+@pytest.mark.parametrize("name,qr", [("mean_max_max", "max"), ("cosine", "max"), ("mean_mean_max", "mean"),
+                                     ("mean_last_max", "last")])
+def test_routing_golden_fp32(ops, golden, name, qr):
+    g = golden("route_cases")
+    q, rk = T(g["q"]), T(g["rk"])
+    normalize = name == "cosine"
+    if normalize:
+        rk = O.l2_normalize(rk)
+    chunks = g["chunks_per_doc"].tolist()
+    pool_ids = torch.repeat_interleave(torch.arange(1, len(chunks) + 1), torch.tensor(chunks))
+    table = torch.tensor([0] + g["global_ids"].tolist())
+    (s, li, gi), _ = _route(ops, q, T(g["mask"]), rk.transpose(0, 1).contiguous(), pool_ids, len(chunks),
+                            int(g["top_k"]), table, query_reduce=qr, normalize=normalize)
+    ref_s = T(g[name + "__scores"])
+    valid = ref_s > -1e9
+    assert torch.allclose(s.cpu()[valid], ref_s[valid], atol=1e-4)
+    assert torch.equal(li.cpu()[valid], T(g[name + "__local_ids"])[valid])
+    assert torch.equal(gi.cpu()[valid], T(g[name + "__global_ids"])[valid])
+    if qr != "mean":   # no routing token at all -> every document sits at finfo.min
+        assert (s.cpu()[2] == torch.finfo(torch.float32).min).all()
+
+
+def test_routing_golden_k_larger_than_docs(ops, golden):
+    g = golden("route_cases")
+    pool_ids = torch.tensor([1, 1, 1, 1, 2])
+    table = torch.tensor([0] + g["global_ids"].tolist()[:2])
+    (s, li, gi), _ = _route(ops, T(g["q"]), T(g["mask"]), T(g["rk"])[:, :5].transpose(0, 1).contiguous(), pool_ids, 2,
+                            4, table)
+    assert s.shape == (3, 3)
+    assert torch.allclose(s.cpu()[:2], T(g["k_gt_docs__scores"])[:2], atol=1e-4)
+    assert torch.equal(li.cpu()[:2], T(g["k_gt_docs__local_ids"])[:2])
+    assert torch.equal(gi.cpu()[:2], T(g["k_gt_docs__global_ids"])[:2])
+
+
+ROUTE_SHAPES = [
+    # (B, S, groups, docs, chunk range, k)
+    (4, 128, 4, 150, (1, 12), 16),     # two sequences per 256-row tile
+    (3, 256, 4, 90, (8, 8), 16),       # one sequence per tile, uniform 8-chunk documents
+    (2, 300, 1, 64, (1, 20), 16),      # longer than a tile: sequence cut into two column tiles
+    (32, 1, 4, 333, (1, 9), 16),       # decode-time routing: one token per sequence
+    (5, 7, 4, 40, (1, 3), 8),          # short query padded to 16 rows
+    (2, 64, 1, 2000, (8, 8), 16),      # BASELINE config 1 shape (G = 1), 16,000 chunks
+    (6, 128, 4, 2600, (1, 16), 32),    # many tiles per CTA: exercises the ring and both accumulators
+]
+
+
+@pytest.mark.parametrize("shape", ROUTE_SHAPES)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_routing_vs_oracle(ops, shape, dtype):
+    b, s, grp, n_docs, (lo, hi), k = shape
+    if dtype == torch.float32 and n_docs > 2100:
+        pytest.skip("fp32 path is checked at the smaller banks")
+    chunks = ragged_docs(n_docs, lo, hi, seed=b * 1000 + s)
+    rk, pool_ids = make_bank(chunks, dtype=dtype, seed=s)
+    g = torch.Generator().manual_seed(99 + b)
+    q = torch.nn.functional.normalize(torch.randn(b, 8, grp, s, 128, generator=g), dim=-1).to(dtype)
+    mask = torch.ones(b, s, dtype=torch.bool)
+    if s > 4:
+        mask[0, s // 2:] = False          # right padding
+        mask[b - 1, : s // 3] = False     # left padding
+    table_ref = O.route_doc_scores(q.float(), mask, rk.float().transpose(0, 1), pool_ids, n_docs)
+    (sc, li, _), table = _route(ops, q, mask, rk, pool_ids, n_docs, k)
+    # the reference fills with finfo(dtype).min of the query dtype
+    assert torch.allclose(table.cpu()[:, 1:], table_ref[:, 1:], atol=1e-3, rtol=0)
+    assert (table.cpu()[:, 0] == torch.finfo(dtype).min).all()
+    check_topk(table_ref.clamp_min(torch.finfo(dtype).min), sc, li, k, tol=1e-3)
+    if dtype == torch.bfloat16:   # tensor-core kernel against the CUDA-core kernel on the same inputs
+        (_, _, _), table_simt = _route(ops, q, mask, rk, pool_ids, n_docs, k, flags=1)
+        assert torch.allclose(table, table_simt, atol=2e-5, rtol=0)
+
+
+def test_routing_scaled_dot_mode(ops):
+    """Un-normalised scores times head_dim^-0.5 (the mode the reference falls into when
+    aux_loss_method is not exactly "INFONCE", src/msa_service.py:318-321, 1095-1096)."""
+    chunks = ragged_docs(50, 1, 6, seed=3)
+    rk, pool_ids = make_bank(chunks, dtype=torch.bfloat16, seed=4, normalize=False)
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(2, 8, 4, 32, 128, generator=g).to(torch.bfloat16)
+    mask = torch.ones(2, 32, dtype=torch.bool)
+    scale = 128 ** -0.5
+    ref = O.route_doc_scores(q.float() * scale, mask, rk.float().transpose(0, 1), pool_ids, len(chunks))
+    (_, _, _), table = _route(ops, q, mask, rk, pool_ids, len(chunks), 4, scale=scale)
+    # scores are O(1) here: the 1e-3 bound is applied relative to the score scale
+    assert torch.allclose(table.cpu()[:, 1:], ref[:, 1:], atol=1e-3 * float(ref[:, 1:].abs().max()), rtol=0)
+
+
+def test_routing_fused_normalize_matches_prenormalized(ops):
+    chunks = [8] * 20
+    rk, pool_ids = make_bank(chunks, dtype=torch.bfloat16, seed=8)
+    g = torch.Generator().manual_seed(9)
+    raw = torch.randn(2, 8, 4, 16, 128, generator=g).to(torch.bfloat16)
+    mask = torch.ones(2, 16, dtype=torch.bool)
+    ref = O.route_doc_scores(O.l2_normalize(raw).float(), mask, rk.float().transpose(0, 1), pool_ids, len(chunks))
+    (_, _, _), table = _route(ops, raw, mask, rk, pool_ids, len(chunks), 4, normalize=True)
+    assert torch.allclose(table.cpu()[:, 1:], ref[:, 1:], atol=1e-3, rtol=0)
+
+
+# ----------------------------------------------------------------------------- top-k / merge
+@pytest.mark.parametrize("n_cols,k", [(1, 4), (5, 16), (257, 16), (24415, 32), (100000, 16), (3000, 1024)])
+def test_topk_select_exact_with_ties(ops, n_cols, k):
+    g = torch.Generator().manual_seed(n_cols)
+    b = 7
+    scores = torch.randn(b, n_cols, generator=g)
+    scores[1] = scores[1].round() + 0.0                 # heavy ties (and no -0.0)
+    scores[2] = -3.0                                    # all equal
+    scores[3, ::3] = torch.finfo(torch.float32).min     # untouched documents
+    scores[4] = scores[4].abs() * -1.0
+    scores[5, : min(5, n_cols)] = float("-inf")
+    from msa_b200 import ops as _o
+    keys = _float_to_keys(scores).to(DEV)
+    s, li, gi = ops.topk_select(keys, k)
+    k_eff = min(k, n_cols)
+    # reference order: score descending, column ascending among equal scores
+    order = torch.stack([torch.tensor(sorted(range(n_cols), key=lambda c: (-scores[i, c].item(), c))[:k_eff])
+                         for i in range(b)]) if n_cols <= 5000 else None
+    ref_s = scores.sort(dim=1, descending=True, stable=True).values[:, :k_eff]
+    assert torch.equal(s.cpu(), ref_s)
+    assert torch.equal(scores.gather(1, li.cpu()), ref_s)
+    if order is not None:
+        assert torch.equal(li.cpu(), order)
+    assert torch.equal(gi, li)
+
+
+def _float_to_keys(x: torch.Tensor) -> torch.Tensor:
+    bits = x.contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    keys = torch.where((bits & 0x80000000) != 0, (~bits) & 0xFFFFFFFF, bits | 0x80000000)
+    return torch.where(keys >= 2 ** 31, keys - 2 ** 32, keys).to(torch.int32)
+
+
+def test_keys_roundtrip(ops):
+    x = torch.tensor([[0.0, -0.0, 1.5, -1.5, float("inf"), float("-inf"), 3e38, -3.4e38]])
+    assert torch.equal(ops.keys_to_scores(_float_to_keys(x).to(DEV)).cpu(), x)
+
+
+@pytest.mark.parametrize("world,kc,k", [(1, 16, 16), (2, 32, 16), (8, 32, 16), (8, 16, 16)])
+def test_topk_merge(ops, world, kc, k):
+    g = torch.Generator().manual_seed(world * 100 + kc)
+    b_all = 12
+    cs = torch.randn(world, b_all, kc, generator=g).sort(dim=2, descending=True).values
+    cs[0, 3, kc // 2:] = torch.finfo(torch.float32).min       # shard with few documents
+    cs[:, 5] = torch.finfo(torch.bfloat16).min                # query without routing tokens: nothing is valid
+    cs[:, 7, 0] = 0.25                                        # exact tie across ranks -> lower rank first
+    cl = torch.randint(1, 1000, (world, b_all, kc), generator=g)
+    cg = cl + 10000 * torch.arange(world).view(world, 1, 1)
+    s, l, gl, r = ops.topk_merge(cs.to(DEV), cl.to(DEV), cg.to(DEV), k, seq_offset=2, n_seq=8)
+    flat_s = cs.transpose(0, 1).reshape(b_all, -1)[2:10]
+    flat_l = cl.transpose(0, 1).reshape(b_all, -1)[2:10]
+    flat_g = cg.transpose(0, 1).reshape(b_all, -1)[2:10]
+    ref_s, idx = flat_s.sort(dim=1, descending=True, stable=True)
+    ref_s, idx = ref_s[:, :k], idx[:, :k]
+    assert torch.equal(s.cpu(), ref_s)
+    assert torch.equal(gl.cpu(), flat_g.gather(1, idx))
+    assert torch.equal(r.cpu().long(), idx // kc)
+    ref_l = flat_l.gather(1, idx).masked_fill(~(ref_s > -1e9), -1)
+    assert torch.equal(l.cpu(), ref_l)
+    assert (l.cpu()[3] == -1).all()
+
+
+# ----------------------------------------------------------------------------- fetch
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_gather_from_pinned_host_bank(ops, dtype):
+    g = torch.Generator().manual_seed(21)
+    world, hkv, d, k = 3, 8, 128, 6
+    shards, bases, offs, lens, kv_ptrs = [], [0], [], [], []
+    for w in range(world):
+        chunks = ragged_docs(30 + w, 1, 9, seed=w)
+        c = sum(chunks)
+        bank = torch.randn(c, 2, hkv, d, generator=g).to(dtype).pin_memory()
+        shards.append((bank, chunks))
+        ln = torch.tensor([0] + chunks)
+        offs.append(torch.cumsum(torch.cat([torch.zeros(1, dtype=torch.long), ln[:-1]]), 0))
+        lens.append(ln)
+        bases.append(bases[-1] + len(chunks) + 1)
+        kv_ptrs.append(bank.data_ptr())
+    b = 9
+    sel_rank = torch.randint(0, world, (b, k), generator=g).to(torch.int32)
+    sel_local = torch.stack([torch.tensor([int(torch.randint(1, len(shards[int(r)][1]) + 1, (1,), generator=g))
+                                           for r in row]) for row in sel_rank])
+    for i in range(b):  # a sample's winners are distinct documents
+        seen = set()
+        for j in range(k):
+            while (int(sel_rank[i, j]), int(sel_local[i, j])) in seen:
+                sel_local[i, j] = sel_local[i, j] % len(shards[int(sel_rank[i, j])][1]) + 1
+            seen.add((int(sel_rank[i, j]), int(sel_local[i, j])))
+    sel_local[2, 1] = -1          # invalid winner
+    sel_local[4] = -1             # a sample that selects nothing
+    plan, n_sel, total = ops.gather_plan(
+        sel_local.to(DEV), sel_rank.to(DEV), world, torch.tensor(bases[:-1]).to(DEV), torch.cat(offs).to(DEV),
+        torch.cat(lens).to(torch.int32).to(DEV), torch.tensor(kv_ptrs, dtype=torch.int64).to(DEV),
+        2 * hkv * d * bank.element_size())
+    tot = int(total.item())
+    out_k, out_v = ops.gather_run(plan, dtype, hkv, d, tot)
+    ks, vs, ns = [], [], []
+    for i in range(b):
+        items = sorted((int(sel_rank[i, j]), int(sel_local[i, j])) for j in range(k) if sel_local[i, j] > 0)
+        n = 0
+        for r, lid in items:
+            bank, _ = shards[r]
+            o, ln = int(offs[r][lid]), int(lens[r][lid])
+            ks.append(bank[o:o + ln, 0]); vs.append(bank[o:o + ln, 1]); n += ln
+        ns.append(n)
+    assert n_sel.cpu().tolist() == ns and tot == sum(ns)
+    assert torch.equal(out_k.cpu(), torch.cat(ks).permute(1, 0, 2))
+    assert torch.equal(out_v.cpu(), torch.cat(vs).permute(1, 0, 2))
+
+
+# ----------------------------------------------------------------------------- decode attention
+def test_decode_golden_layer(ops, golden):
+    g = golden("layer_decode")
+    ck, cv, lens = T(g["cache_k"]), T(g["cache_v"]), T(g["kv_lengths"])
+    b, hkv, max_l, d = ck.shape
+    cap = max_l + 2
+    kc = torch.zeros(b, hkv, cap, d); vc = torch.zeros(b, hkv, cap, d)
+    kc[:, :, :max_l], vc[:, :, :max_l] = ck, cv
+    kc, vc = kc.to(DEV), vc.to(DEV)
+    start = (max_l - lens).to(torch.int32).to(DEV)       # the reference's cache is left padded
+    for step in range(2):
+        kv_len = (lens + step).to(torch.int32).to(DEV)
+        q = T(g[f"q{step}"])[:, :, 0].to(DEV)
+        nk, nv = T(g[f"k{step}"])[:, :, 0].to(DEV), T(g[f"v{step}"])[:, :, 0].to(DEV)
+        out = ops.sparse_decode_attn(q, kc, vc, kv_len, nk, nv, kv_start=start, n_splits=1 + step)
+        assert rel_err(out, T(g[f"out{step}"])[:, 0]) < 1e-5
+    # the step's K/V were appended in place right of the old entries
+    assert torch.equal(kc[:, :, max_l].cpu(), T(g["k0"])[:, :, 0])
+    assert torch.equal(vc[:, :, max_l + 1].cpu(), T(g["v1"])[:, :, 0])
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 1e-2)])
+@pytest.mark.parametrize("n_splits", [1, 3, 8])
+def test_decode_real_shape(ops, dtype, tol, n_splits):
+    g = torch.Generator().manual_seed(31 + n_splits)
+    b, hq, hkv, d = 5, 32, 8, 128
+    lens = torch.tensor([1155, 1, 64, 700, 2179])          # t + retrieved + local, ragged
+    max_l = int(lens.max())
+    ck = torch.randn(b, hkv, max_l, d, generator=g).to(dtype)
+    cv = torch.randn(b, hkv, max_l, d, generator=g).to(dtype)
+    q = torch.randn(b, hq, 1, d, generator=g).to(dtype)
+    nk = torch.randn(b, hkv, 1, d, generator=g).to(dtype)
+    nv = torch.randn(b, hkv, 1, d, generator=g).to(dtype)
+    # oracle wants the reference's left-padded layout
+    lk = torch.zeros_like(ck); lv = torch.zeros_like(cv)
+    for i, n in enumerate(lens.tolist()):
+        lk[i, :, max_l - n:], lv[i, :, max_l - n:] = ck[i, :, :n], cv[i, :, :n]
+    ref = O.decode_attention(q.float(), lk.float(), lv.float(), lens, nk.float(), nv.float())[:, 0]
+    kc = torch.zeros(b, hkv, max_l + 1, d, dtype=dtype); vc = torch.zeros(b, hkv, max_l + 1, d, dtype=dtype)
+    kc[:, :, :max_l], vc[:, :, :max_l] = ck, cv
+    kc, vc = kc.to(DEV), vc.to(DEV)
+    out = ops.sparse_decode_attn(q[:, :, 0].to(DEV), kc, vc, lens.to(torch.int32).to(DEV), nk[:, :, 0].to(DEV),
+                                 nv[:, :, 0].to(DEV), n_splits=n_splits)
+    assert rel_err(out, ref) < tol
+    for i, n in enumerate(lens.tolist()):
+        assert torch.equal(kc[i, :, n].cpu(), nk[i, :, 0])
