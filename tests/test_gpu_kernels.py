@@ -122,10 +122,14 @@ def test_routing_golden_fp32(ops, golden, name, qr):
     ref_s = T(g[name + "__scores"])
     valid = ref_s > -1e9
     assert torch.allclose(s.cpu()[valid], ref_s[valid], atol=1e-4)
-    assert torch.equal(li.cpu()[valid], T(g[name + "__local_ids"])[valid])
-    assert torch.equal(gi.cpu()[valid], T(g[name + "__global_ids"])[valid])
-    if qr != "mean":   # no routing token at all -> every document sits at finfo.min
+    # sample 2 has no routing token: all its documents tie (at 0 for "mean", else at finfo.min),
+    # and the order among exact ties is unspecified in the reference (torch.topk)
+    assert torch.equal(li.cpu()[:2], T(g[name + "__local_ids"])[:2])
+    assert torch.equal(gi.cpu()[:2], T(g[name + "__global_ids"])[:2])
+    if qr != "mean":
         assert (s.cpu()[2] == torch.finfo(torch.float32).min).all()
+    else:
+        assert (s.cpu()[2] == 0).all()
 
 
 def test_routing_golden_k_larger_than_docs(ops, golden):
@@ -188,8 +192,11 @@ def test_routing_scaled_dot_mode(ops):
     scale = 128 ** -0.5
     ref = O.route_doc_scores(q.float() * scale, mask, rk.float().transpose(0, 1), pool_ids, len(chunks))
     (_, _, _), table = _route(ops, q, mask, rk, pool_ids, len(chunks), 4, scale=scale)
-    # scores are O(1) here: the 1e-3 bound is applied relative to the score scale
-    assert torch.allclose(table.cpu()[:, 1:], ref[:, 1:], atol=1e-3 * float(ref[:, 1:].abs().max()), rtol=0)
+    # the 1e-3 bound is stated for cosine scores (per-head terms <= 1); here a per-head term is
+    # |q_h||k_h|*scale, so the bound is applied relative to that magnitude
+    per_head = float(q.float().norm(dim=-1).mean() * rk.float().norm(dim=-1).mean() * scale)
+    assert per_head > 1.0
+    assert torch.allclose(table.cpu()[:, 1:], ref[:, 1:], atol=1e-3 * per_head, rtol=0)
 
 
 def test_routing_fused_normalize_matches_prenormalized(ops):
