@@ -1,0 +1,356 @@
+"""Routing benchmark: queries/s over a 100M-token pooled memory bank (BASELINE.json config 4).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (fixed for every N, so scaling is STRONG): 195,313 documents x 8 chunks =
+1,562,504 pooled router keys per layer, 18 routing layers, bf16, sharded by document over
+the N ranks; 128 queries x 256 routing tokens, split over the ranks (each rank scores ALL
+queries against its shard).  A step = all 18 layers: fold -> (all-gather queries) -> fused
+score/reduce -> per-shard top-k -> (all-gather candidates) -> merge to the global top-16.
+Inputs are seeded synthetic (cosine mode: unit-norm heads; keys = per-document mean N(0,0.5)
++ noise of std 1/8 per chunk, the pooled statistics of BASELINE config 3's distribution).
+
+`value` times the step with queries resident in HBM; `e2e` times the same step through
+MSAService.route with the queries in pinned HOST memory (H2D of every layer's queries and
+D2H of every layer's winners inside the timed region).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_DOCS, CHUNKS_PER_DOC, N_LAYERS = 195_313, 8, 18
+N_QUERIES, Q_TOKENS, HQ, HKV, D, TOP_K = 128, 256, 32, 8, 128, 16
+METRIC = "routing queries/s over 100M-token memory"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--docs", type=int, default=N_DOCS, help="shrink the bank (development only)")
+    ap.add_argument("--layers", type=int, default=N_LAYERS)
+    ap.add_argument("--queries", type=int, default=N_QUERIES)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "tflops": p["bf16_tflops_sustained"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of GPU `index`, sampled during the timed region."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.proc, self.index = [], None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------
+def cpu_reference_sample(threads: int, target_s: float = 12.0):
+    """The oracle port of Memory.prefill_stage2 (matmul over all 32 heads, masked_fill, head mean,
+    token max, scatter amax, topk) on the host cores, fp32, on a bounded sample; extrapolated
+    linearly in chunks and layers to the full workload."""
+    import torch
+    from oracle import msa_oracle as O
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(4000)
+    n_q, docs = 2, 2048
+    chunks = docs * CHUNKS_PER_DOC
+    rk = torch.nn.functional.normalize(torch.randn(HKV, chunks, D, generator=g), dim=-1)
+    pool_ids = torch.repeat_interleave(torch.arange(1, docs + 1), CHUNKS_PER_DOC)
+    table = torch.arange(docs + 1)
+    q = torch.nn.functional.normalize(torch.randn(n_q, HKV, HQ // HKV, Q_TOKENS, D, generator=g), dim=-1)
+    mask = torch.ones(n_q, Q_TOKENS, dtype=torch.bool)
+
+    def once():
+        t0 = time.perf_counter()
+        O.prefill_stage2(q, mask, rk, pool_ids, table, TOP_K)
+        return time.perf_counter() - t0
+    once()
+    t1 = once()
+    reps = max(1, min(20, int(target_s / max(t1, 1e-3))))
+    t = statistics.median([once() for _ in range(reps)])
+    per_query_full = t / n_q * (N_DOCS * CHUNKS_PER_DOC / chunks) * N_LAYERS
+    sample = (f"oracle port of prefill_stage2, fp32, {n_q} queries x {Q_TOKENS} tokens x {chunks} chunks x 1 layer, "
+              f"median of {reps}, scaled x{N_DOCS * CHUNKS_PER_DOC / chunks:.1f} chunks x{N_LAYERS} layers")
+    return 1.0 / per_query_full, sample, t
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    vals, sample, t_last = [], "", 0.0
+    for i in range(args.warmup + args.steps):
+        v, sample, t_last = cpu_reference_sample(threads, target_s=2.0)
+        if i >= args.warmup:
+            vals.append(v)
+    v = statistics.median(vals)
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": v, "unit": "queries/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * N_QUERIES / v, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "BASELINE config 4: 100M-token bank, 18 layers, 128 queries x 256 tokens, top-16",
+                   "note": "CPU: bounded sample, extrapolated linearly"},
+        "cpu_baseline": {"value": v, "unit": "queries/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ------------------------------------------------------------------------------------------
+def make_bank(torch, dev, docs_local: int, layers: int, seed: int):
+    """Pooled router keys [C, Hkv, D] bf16 per layer, generated on the device in slices."""
+    out = []
+    g = torch.Generator(device=dev)
+    for layer in range(layers):
+        g.manual_seed(seed + layer)
+        rk = torch.empty((docs_local * CHUNKS_PER_DOC, HKV, D), dtype=torch.bfloat16, device=dev)
+        step = 8192
+        for d0 in range(0, docs_local, step):
+            n = min(step, docs_local - d0)
+            mu = torch.randn((n, 1, HKV, D), generator=g, device=dev) * 0.5
+            x = mu + torch.randn((n, CHUNKS_PER_DOC, HKV, D), generator=g, device=dev) * 0.125
+            x = torch.nn.functional.normalize(x, dim=-1)
+            rk[d0 * CHUNKS_PER_DOC:(d0 + n) * CHUNKS_PER_DOC] = x.view(-1, HKV, D).to(torch.bfloat16)
+        out.append(rk)
+    return out
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from msa_b200 import ops
+    from msa_b200.memory import AttentionGeometry, Document, ModelConfig
+    from msa_b200.service import MSAService, all_gather_cat, pack_candidates, unpack_candidates
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    n_docs, layers, n_q = args.docs, args.layers, args.queries
+    per = (n_docs + world - 1) // world
+    d_lo, d_hi = min(n_docs, rank * per), min(n_docs, (rank + 1) * per)
+    docs_local = d_hi - d_lo
+    b = n_q // world
+    assert b * world == n_q, "queries must divide over the ranks"
+    shard_k = TOP_K if world == 1 else 2 * TOP_K
+
+    model_cfg = ModelConfig(doc_top_k=TOP_K, router_layer_idx=",".join(str(18 + i) for i in range(layers)))
+    svc = MSAService(local_rank, None, model_cfg, None, AttentionGeometry(), world_size=world, rank=rank,
+                     shard_top_k=shard_k)
+    docs = [Document(doc_id=d_lo + i, num_chunks=CHUNKS_PER_DOC) for i in range(docs_local)]
+    svc.block_desc.init_docs(docs, dev)
+    svc.block_desc.pool_ids_from_docs(dev)
+    bank = make_bank(torch, dev, docs_local, layers, seed=4000 + 100 * rank)
+    for i, layer in enumerate(svc.router_layer_ids):
+        svc.blocks[layer].rk = bank[i]
+
+    # queries: pinned host copy (e2e) and device copy (kernel-resident value)
+    gq = torch.Generator(device=dev)
+    gq.manual_seed(504_000 + rank)
+    q_host, q_dev = [], []
+    for layer in range(layers):
+        q = torch.nn.functional.normalize(torch.randn((b, HQ, Q_TOKENS, D), generator=gq, device=dev), dim=-1)
+        q_dev.append(q.to(torch.bfloat16))
+        host = torch.empty(q.shape, dtype=torch.bfloat16).pin_memory()
+        host.copy_(q_dev[-1])
+        q_host.append(host)
+    mask_host = torch.ones((b, Q_TOKENS), dtype=torch.bool).pin_memory()
+    mask_dev = mask_host.to(dev)
+
+    n_all = n_q
+    s_pad = ops.route_s_pad(Q_TOKENS)
+    c_local = docs_local * CHUNKS_PER_DOC
+    keys = torch.empty((n_all, docs_local + 1), dtype=torch.int32, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    min_val = torch.finfo(torch.bfloat16).min
+    route_events = []
+    launches = [0]
+
+    def layer_resident(i, layer, timed):
+        qf, bias, _ = ops.fold_queries(q_dev[i], mask_dev, HQ // HKV, s_pad=s_pad)
+        if world > 1:
+            qf = all_gather_cat(qf, world).view(-1, qf.shape[1])
+            bias = all_gather_cat(bias, world).view(-1)
+        ops.route_table_reset(keys, docs_local, min_val, status)
+        if timed:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        ops.route_scores(qf, bias, n_all, s_pad, svc.blocks[layer].rk, svc.block_desc.chunk_doc, docs_local,
+                         alpha=1.0 / HQ, min_val=min_val, keys=keys, status=status, flags=2)
+        if timed:
+            e1.record()
+            route_events.append((e0, e1))
+        sc, li, gi = ops.topk_select(keys, shard_k, svc.block_desc.doc_ids)
+        if world > 1:
+            sc, li, gi = unpack_candidates(all_gather_cat(pack_candidates(sc, li, gi), world))
+        else:
+            sc, li, gi = sc.unsqueeze(0), li.unsqueeze(0), gi.unsqueeze(0)
+        launches[0] += 5
+        return ops.topk_merge(sc, li, gi, TOP_K, seq_offset=rank * b, n_seq=b)
+
+    def step_resident(timed):
+        out = None
+        for i, layer in enumerate(svc.router_layer_ids):
+            out = layer_resident(i, layer, timed)
+        return out
+
+    copy_stream = torch.cuda.Stream(dev)
+    stage = [torch.empty_like(q_dev[0]) for _ in range(2)]
+    res_host = [(torch.empty((b, TOP_K), dtype=torch.float32).pin_memory(),
+                 torch.empty((b, TOP_K), dtype=torch.int64).pin_memory()) for _ in range(layers)]
+
+    def step_e2e():
+        """Through MSAService.route with host-resident queries: the copy stream brings layer l+1's
+        queries over PCIe while layer l is scored; winners go back to pinned host memory."""
+        main = torch.cuda.current_stream(dev)
+        ready = [torch.cuda.Event() for _ in range(layers)]
+        freed = [torch.cuda.Event() for _ in range(layers)]
+        for i, layer in enumerate(svc.router_layer_ids):
+            with torch.cuda.stream(copy_stream):
+                if i >= 2:
+                    copy_stream.wait_event(freed[i - 2])
+                stage[i % 2].copy_(q_host[i], non_blocking=True)
+                ready[i].record(copy_stream)
+            main.wait_event(ready[i])
+            sc, li, gi, rk_ = svc.route(stage[i % 2], mask_dev, layer)
+            freed[i].record(main)
+            res_host[i][0].copy_(sc, non_blocking=True)
+            res_host[i][1].copy_(gi, non_blocking=True)
+
+    def sync_all():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+
+    def timed_region(fn, steps):
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        sync_all()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(args.warmup):
+        step_resident(False)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches[0] = 0
+    ms_total = timed_region(lambda: step_resident(True), args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    n_launch = launches[0]
+    svc._status = status
+    svc.check_status()
+    route_ms = [a.elapsed_time(b_) for a, b_ in route_events]
+    route_avg_ms = sum(route_ms) / len(route_ms)
+
+    for _ in range(max(1, args.warmup // 2)):
+        step_e2e()
+    ms_e2e = timed_region(step_e2e, args.steps)
+    svc.check_status()
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    pk = peaks()
+    ms_step = ms_total / args.steps
+    value = n_q / (ms_step / 1e3)
+    e2e_value = n_q / (ms_e2e / args.steps / 1e3)
+    flops = 2.0 * n_all * s_pad * c_local * (HKV * D)
+    achieved_tf = flops / (route_avg_ms / 1e3) / 1e12
+    alg_bytes = c_local * HKV * D * 2 + n_all * s_pad * HKV * D * 2
+    line = {
+        "metric": METRIC, "value": value, "unit": "queries/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"BASELINE config 4: {n_docs} docs x {CHUNKS_PER_DOC} chunks (100M tokens), {layers} routing "
+                               f"layers, {n_q} queries x {Q_TOKENS} tokens, top-{TOP_K}, cosine scores",
+                   "sharding": f"bank by document over {world} rank(s); every rank scores all queries; "
+                               f"per-shard top-{shard_k}, all-gather merge",
+                   "l2": "inputs per layer (router keys %.0f MB) exceed L2; 18 distinct layers per step" % (c_local * 2048 / 1e6)},
+        "e2e": {"value": e2e_value, "unit": "queries/s",
+                "h2d_bytes_per_step": layers * (q_host[0].numel() * 2) * world,
+                "d2h_bytes_per_step": layers * b * TOP_K * 12 * world},
+        "gpu_launches": n_launch,
+        "clocks": clocks,
+        "roofline": {"kernel": "route_tc_kernel", "bound": "tensor", "achieved": achieved_tf, "peak": pk["tflops"],
+                     "unit": "TFLOP/s", "frac": achieved_tf / pk["tflops"], "traffic": None,
+                     "peak_source": pk["source"] + " (bf16 sustained)", "avg_launch_ms": route_avg_ms,
+                     "flops_per_launch": flops,
+                     "hbm": {"algorithmic_bytes_per_launch": alg_bytes,
+                             "achieved_gbs": alg_bytes / (route_avg_ms / 1e3) / 1e9,
+                             "frac_of_hbm": alg_bytes / (route_avg_ms / 1e3) / 1e9 / pk["hbm_gbs"]}},
+    }
+    if not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        v, sample, _ = cpu_reference_sample(threads)
+        line["cpu_baseline"] = {"value": v, "unit": "queries/s", "cores": threads, "kind": "port", "sample": sample}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    a = parse()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)

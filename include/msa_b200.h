@@ -133,6 +133,13 @@ int msa_route_scores(const void* q_folded, const float* row_bias, int32_t dtype,
                      int64_t table_stride, int32_t n_docs, float min_val, uint32_t flags,
                      int32_t* status, void* stream);
 
+/* Resets a score table to min_val (and `status`, when given, to zero).  msa_route_scores does
+ * this itself unless MSA_ROUTE_NO_INIT is set; the separate entry point exists so that a bank
+ * scored in several calls (or a caller timing the scoring kernel alone) resets once.
+ * Counterpart of torch.full((bsz, total_docs), min_val) at src/msa_service.py:716-717. */
+int msa_route_table_reset(uint32_t* score_keys, int64_t table_stride, int32_t n_docs, int32_t n_seq,
+                          float min_val, int32_t* status, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * Routing, step 3: exact per-shard top-k (block radix select + sort of the winners).
  * Replaces torch.topk + create_global_doc_ids (src/msa_service.py:826-828).
@@ -176,6 +183,12 @@ int msa_topk_merge(const float* cand_scores, const int64_t* cand_local, const in
  * msa_gather_run: copies every planned document into out_k / out_v, device
  * [Hkv, out_entries, D] (entry stride = D, head stride = out_head_stride elements).
  */
+/* Pins and maps [host_ptr, host_ptr+bytes) (memory the caller allocated, e.g. a shared-memory
+ * file opened by every rank of the node; the reference pins its bank with pin_memory=True,
+ * src/msa_service.py:490-491) and returns the address the device uses for it. */
+int msa_bank_register_host(void* host_ptr, int64_t bytes, uint64_t* device_address);
+int msa_bank_unregister_host(void* host_ptr);
+
 int msa_gather_plan(const int64_t* sel_local, const int32_t* sel_rank, int32_t n_seq, int32_t k,
                     int32_t world, const int64_t* shard_doc_base, const int64_t* doc_chunk_offset,
                     const int32_t* doc_chunk_len, const uint64_t* shard_kv_base,

@@ -16,3 +16,20 @@ void set_error(const char* fmt, ...) {
 
 extern "C" const char* msa_last_error(void) { return msa::g_error; }
 extern "C" int msa_abi_version(void) { return MSA_ABI_VERSION; }
+
+// Pin and map a host range that was allocated elsewhere (for example a shared-memory file
+// that every rank of a node opens), so that msa_gather_run can read it from the device.
+extern "C" int msa_bank_register_host(void* host_ptr, int64_t bytes, uint64_t* device_address) {
+  MSA_REQUIRE(host_ptr && bytes > 0 && device_address, "bank_register_host: bad arguments");
+  MSA_CUDA_OK(cudaHostRegister(host_ptr, (size_t)bytes, cudaHostRegisterPortable | cudaHostRegisterMapped));
+  void* dev = nullptr;
+  MSA_CUDA_OK(cudaHostGetDevicePointer(&dev, host_ptr, 0));
+  *device_address = (uint64_t)(uintptr_t)dev;
+  return MSA_OK;
+}
+
+extern "C" int msa_bank_unregister_host(void* host_ptr) {
+  MSA_REQUIRE(host_ptr, "bank_unregister_host: null pointer");
+  MSA_CUDA_OK(cudaHostUnregister(host_ptr));
+  return MSA_OK;
+}

@@ -243,6 +243,16 @@ extern "C" int msa_fold_queries(const void* q, int32_t dtype, int64_t stride_b, 
   return MSA_OK;
 }
 
+extern "C" int msa_route_table_reset(uint32_t* score_keys, int64_t table_stride, int32_t n_docs, int32_t n_seq,
+                                     float min_val, int32_t* status, void* stream) {
+  MSA_REQUIRE(score_keys && n_docs >= 0 && n_seq >= 0 && table_stride >= (int64_t)n_docs + 1,
+              "route_table_reset: bad arguments");
+  int rc = reset_score_table(score_keys, table_stride, n_docs + 1, n_seq, min_val, (cudaStream_t)stream);
+  if (rc != MSA_OK) return rc;
+  if (status) MSA_CUDA_OK(cudaMemsetAsync(status, 0, 4 * sizeof(int32_t), (cudaStream_t)stream));
+  return MSA_OK;
+}
+
 extern "C" int msa_route_scores(const void* q_folded, const float* row_bias, int32_t dtype, int32_t n_seq,
                                 int32_t s_pad, const void* rk, int64_t rk_chunk_stride, int32_t n_chunks,
                                 int32_t kdim, const int32_t* chunk_doc, float alpha, uint32_t* score_keys,

@@ -1,0 +1,286 @@
+"""Per-GPU memory bank: the B200 counterpart of the reference's ``Memory`` worker.
+
+Mirrors ``src/msa_service.py``: ``Document`` (src/types.py:5-9), ``BlockDesc`` (:191-231),
+``BlockData`` (:234-242), ``Memory`` (:269-828).  Same method names and argument meaning;
+the bodies call the CUDA kernels of this package.
+
+Bank layout (differs from the reference's head-major ``[1, Hkv, C, D]`` on purpose):
+  * routing keys ``rk``: ``[C, Hkv, D]`` on the GPU, chunk major, so one chunk is one
+    contiguous 2 KiB row for TMA;
+  * content ``kv``: ``[C, 2, Hkv, D]`` in pinned host memory (K then V per chunk), so one
+    document is one contiguous run for the gather kernel.
+``BlockData.k / .v / .rk_head_major`` give reference-shaped views.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Iterable, List, Optional, Tuple
+
+import torch
+
+from . import _cabi as A
+from . import ops
+
+
+@dataclass
+class Document:
+    doc: str = ""
+    doc_id: int = 0
+    num_chunks: int = 0
+
+
+@dataclass
+class ModelConfig:
+    """The fields of the reference's ModelConfig (src/config/memory_config.py:28-46) this path reads."""
+    model_path: str = ""
+    doc_top_k: int = 16
+    pooling_kernel_size: int = 64
+    router_layer_idx: str = "all"
+    template_token_id: int = -2
+    template_id_num: int = 3
+
+
+@dataclass
+class MemoryConfig:
+    """src/config/memory_config.py:48-56.  ``slice_chunk_size`` is accepted and unused: the
+    fused kernel never materialises a score slice."""
+    block_size: int = 16000
+    slice_chunk_size: int = 16 * 1024
+    pooling_kernel_size: int = 64
+    memory_file_path: str = ""
+
+
+@dataclass
+class AttentionGeometry:
+    """What the reference reads from the checkpoint's MSAConfig (src/msa_service.py:286-321)."""
+    num_hidden_layers: int = 36
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 8
+    head_dim: int = 128
+    head_reduce_method: str = "mean"
+    query_reduce_method: str = "max"
+    chunk_reduce_method: str = "max"
+    aux_loss_method: str = "INFONCE"
+    decouple_router: bool = True
+    dtype: torch.dtype = torch.bfloat16
+
+
+class BlockDesc:
+    """Tables of one GPU's shard (src/msa_service.py:191-231)."""
+
+    def __init__(self):
+        self.docs: List[Document] = []
+        self.tmp_doc_ids: List[torch.Tensor] = []
+        self.pool_ids: Optional[torch.Tensor] = None        # [C] int64, 1-based local doc per chunk
+        self.chunk_doc: Optional[torch.Tensor] = None       # same, int32, what the kernels read
+        self.doc_ids: Optional[torch.Tensor] = None         # [N+1] local -> global, slot 0 dummy
+        self.doc_ids_cpu: Optional[torch.Tensor] = None
+        self.doc_offsets_cpu: Optional[torch.Tensor] = None
+        self.doc_lens_cpu: Optional[torch.Tensor] = None
+        self.doc_offsets: Optional[torch.Tensor] = None     # device copies for the gather plan
+        self.doc_lens: Optional[torch.Tensor] = None
+
+    def init_docs(self, docs: List[Document], device):
+        self.docs = docs
+        self.doc_ids_cpu = torch.tensor([0] + [d.doc_id for d in docs], dtype=torch.long)
+        self.doc_ids = self.doc_ids_cpu.to(device)
+        self.tmp_doc_ids = []
+        lens = [0] + [d.num_chunks for d in docs]
+        self.doc_lens_cpu = torch.tensor(lens, dtype=torch.long)
+        self.doc_offsets_cpu = torch.cumsum(torch.tensor([0] + lens[:-1], dtype=torch.long), dim=0)
+        self.doc_offsets = self.doc_offsets_cpu.to(device)
+        self.doc_lens = self.doc_lens_cpu.to(torch.int32).to(device)
+
+    def create_global_doc_ids(self, local_doc_ids):
+        return self.doc_ids[local_doc_ids]
+
+    def set_pool_ids(self, pool_ids: torch.Tensor, device):
+        self.pool_ids_cpu = pool_ids.cpu()
+        self.pool_ids = pool_ids.to(device)
+        self.chunk_doc = self.pool_ids.to(torch.int32)
+
+    def merge_poolig_doc_id(self, device):
+        """Concatenate the per-block ``pooled_doc_ids`` (each numbered from 1) into shard-wide
+        ids, as ``cumulative_concat`` does (src/utils/tools.py:34-55, src/msa_service.py:221-224)."""
+        out, base = [], 0
+        for t in self.tmp_doc_ids:
+            t = t.cpu().long()
+            out.append(t + base)
+            base += int(t[-1])
+        self.set_pool_ids(torch.cat(out) if out else torch.empty(0, dtype=torch.long), device)
+        self.tmp_doc_ids.clear()
+
+    def pool_ids_from_docs(self, device):
+        """pool_ids straight from the documents' chunk counts (equal to what ingestion yields)."""
+        ids = torch.repeat_interleave(torch.arange(1, len(self.docs) + 1), self.doc_lens_cpu[1:])
+        self.set_pool_ids(ids, device)
+
+    def chunks(self) -> int:
+        return sum(d.num_chunks for d in self.docs)
+
+    @property
+    def nr_docs(self) -> int:
+        return len(self.docs)
+
+
+@dataclass
+class BlockData:
+    rk: Optional[torch.Tensor] = None   # [C, Hkv, D] device
+    kv: Optional[torch.Tensor] = None   # [C, 2, Hkv, D] pinned host
+    kv_device_address: int = 0          # address the GPU uses for ``kv``
+
+    @property
+    def k(self):   # reference shape [1, Hkv, C, D] (a view of the pinned bank)
+        return self.kv[:, 0].permute(1, 0, 2).unsqueeze(0)
+
+    @property
+    def v(self):
+        return self.kv[:, 1].permute(1, 0, 2).unsqueeze(0)
+
+    @property
+    def rk_head_major(self):
+        return self.rk.permute(1, 0, 2).unsqueeze(0)
+
+    def get_router_k(self):
+        return self.rk
+
+
+class Memory:
+    """One GPU's bank plus local scoring and selection (src/msa_service.py:269-828)."""
+
+    def __init__(self, gpu_id: int, generate_config=None, model_config: Optional[ModelConfig] = None,
+                 memory_config: Optional[MemoryConfig] = None, geometry: Optional[AttentionGeometry] = None):
+        if not torch.cuda.is_available():
+            raise A.MsaError("msa_b200.Memory needs a CUDA device; there is no CPU path")
+        A.lib()  # fail now, loudly, if the kernels are not built
+        self.gpu_id = gpu_id
+        self.device = torch.device("cuda", gpu_id)
+        self.generate_config = generate_config
+        self.model_config = model_config or ModelConfig()
+        self.memory_config = memory_config or MemoryConfig()
+        self.geometry = geometry or AttentionGeometry()
+        g = self.geometry
+        ridx = self.model_config.router_layer_idx
+        self.router_layer_ids = sorted(range(g.num_hidden_layers) if ridx == "all" else map(int, ridx.split(",")))
+        self.num_key_value_groups = g.num_attention_heads // g.num_key_value_heads
+        self.head_reduce_method = g.head_reduce_method
+        self.query_reduce_method = g.query_reduce_method
+        self.chunk_reduce_method = g.chunk_reduce_method
+        self.aux_loss_method = g.aux_loss_method
+        self.decouple_router = g.decouple_router
+        if self.head_reduce_method != "mean" or self.chunk_reduce_method != "max":
+            raise A.MsaError(
+                f"head_reduce_method={self.head_reduce_method!r} / chunk_reduce_method={self.chunk_reduce_method!r} "
+                "are not supported: the fused kernel implements the shipped configuration (mean / max)")
+        if self.query_reduce_method not in A.QREDUCE:
+            raise A.MsaError(f"unknown query_reduce_method {self.query_reduce_method!r}")
+        # src/msa_service.py:318-321: -1 means "cosine mode, do not scale"
+        self.scaling = -1.0 if (self.aux_loss_method == "INFONCE" and self.decouple_router) else g.head_dim ** -0.5
+        self.blocks: Dict[int, BlockData] = {layer: BlockData() for layer in self.router_layer_ids}
+        self.block_desc = BlockDesc()
+        self.template_prefix_kvcache: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
+        self._kv_offset = 0
+        self._status = torch.zeros(4, dtype=torch.int32, device=self.device)
+
+    # ------------------------------------------------------------------ bank build
+    def _init_block_data(self, dtype: torch.dtype):
+        """Allocate the shard for every router layer (src/msa_service.py:481-492)."""
+        g = self.geometry
+        c = self.block_desc.chunks()
+        for layer in self.router_layer_ids:
+            blk = self.blocks[layer]
+            if blk.rk is None:
+                blk.rk = torch.empty((c, g.num_key_value_heads, g.head_dim), dtype=dtype, device=self.device)
+                blk.kv = torch.empty((c, 2, g.num_key_value_heads, g.head_dim), dtype=dtype, pin_memory=True)
+                blk.kv_device_address = blk.kv.data_ptr()  # pinned by the CUDA allocator: same address under UVA
+
+    def begin_blocks(self, docs: List[Document], dtype: Optional[torch.dtype] = None):
+        self.block_desc.init_docs(docs, self.device)
+        self._kv_offset = 0
+        self._init_block_data(dtype or self.geometry.dtype)
+
+    def ingest_meta(self, meta: dict):
+        """Store one stage-1 block.  ``meta`` is the PREFILL_WORKER_META payload
+        (src/prefill.py:152-157, 300-303); its cache answers ``get_kvcache`` /
+        ``get_router_kcache`` with ``[1, Hkv, c, D]`` tensors.  Body of the receive loop at
+        src/msa_service.py:519-571."""
+        cache = meta["past_key_values"]
+        if not self.template_prefix_kvcache:
+            kw = cache.cache_kwargs
+            self.template_prefix_kvcache = {
+                layer: (kw[layer]["template_prefix_kcache"].to(self.device),
+                        kw[layer]["template_prefix_vcache"].to(self.device))
+                for layer in kw if "template_prefix_kcache" in kw[layer]}
+        n = None
+        for layer in self.router_layer_ids:
+            k, v = cache.get_kvcache(layer)
+            rk = cache.get_router_kcache(layer)
+            if rk is None:
+                rk = k
+            n = k.shape[2] if n is None else n
+            assert n == k.shape[2] and self._kv_offset + n <= self.block_desc.chunks()
+            blk = self.blocks[layer]
+            sl = slice(self._kv_offset, self._kv_offset + n)
+            blk.rk[sl].copy_(rk[0].permute(1, 0, 2), non_blocking=True)
+            blk.kv[sl, 0].copy_(k[0].permute(1, 0, 2))
+            blk.kv[sl, 1].copy_(v[0].permute(1, 0, 2))
+            if layer == self.router_layer_ids[0]:
+                self.block_desc.tmp_doc_ids.append(cache.cache_kwargs[layer]["pooled_doc_ids"])
+        self._kv_offset += n or 0
+
+    def generate_blocks(self, docs: List[Document], metas: Optional[Iterable[dict]] = None):
+        """``Memory.generate_blocks`` (src/msa_service.py:497-582) with the stage-1 results handed in
+        as an iterable of META payloads instead of being pulled from a worker process."""
+        self.begin_blocks(docs)
+        for meta in metas or ():
+            self.ingest_meta(meta)
+        self.block_desc.merge_poolig_doc_id(self.device)
+        return self._post_process()
+
+    def load_pooled(self, docs: List[Document], layers: Dict[int, Tuple[torch.Tensor, torch.Tensor, torch.Tensor]]):
+        """Fill the bank from already pooled tensors: ``layers[l] = (k, v, rk)`` each ``[C, Hkv, D]``."""
+        first = next(iter(layers.values()))
+        self.begin_blocks(docs, first[2].dtype)
+        for layer, (k, v, rk) in layers.items():
+            blk = self.blocks[layer]
+            blk.rk.copy_(rk)
+            blk.kv[:, 0].copy_(k)
+            blk.kv[:, 1].copy_(v)
+        self.block_desc.pool_ids_from_docs(self.device)
+        return self._post_process()
+
+    def _post_process(self):
+        first = self.blocks[self.router_layer_ids[0]]
+        kv_bytes = first.rk.nbytes * len(self.router_layer_ids)
+        return kv_bytes, tuple(first.rk_head_major.shape)
+
+    def get_max_local_pool_doc_id(self) -> int:
+        return int(self.block_desc.pool_ids_cpu[-1])
+
+    def get_template_prefix_kvcaches(self, layer_idx: int):
+        return self.template_prefix_kvcache[layer_idx]
+
+    # ------------------------------------------------------------------ scoring + selection
+    def score_folded(self, layer_idx: int, q_folded, row_bias, n_seq: int, s_pad: int, n_heads: int, top_k: int,
+                     scale: float = 1.0):
+        """Score ``n_seq`` folded sequences against this shard and select ``top_k`` documents each."""
+        desc = self.block_desc
+        blk = self.blocks[layer_idx]
+        keys, _ = ops.route_scores(q_folded, row_bias, n_seq, s_pad, blk.rk, desc.chunk_doc, desc.nr_docs,
+                                   alpha=scale / n_heads, min_val=torch.finfo(blk.rk.dtype).min, status=self._status)
+        return ops.topk_select(keys, top_k, desc.doc_ids)
+
+    def prefill_stage2(self, layer_idx: int, query_states: torch.Tensor, query_mask: torch.Tensor):
+        """src/msa_service.py:703-828.  query_states ``[B, Hkv, G, S, D]``, query_mask
+        ``[B, 1, 1, S, 1]`` bool.  Returns ``(scores[B,k'], local_ids[B,k'], global_ids[B,k'])``,
+        ``k' = min(doc_top_k, nr_docs + 1)``; scores are float32."""
+        b, hkv, grp, s, d = query_states.shape
+        q = query_states.reshape(b, hkv * grp, s, d)
+        qf, bias, s_pad = ops.fold_queries(q, query_mask.reshape(b, s), grp, query_reduce=self.query_reduce_method)
+        return self.score_folded(layer_idx, qf, bias, b, s_pad, hkv * grp, self.model_config.doc_top_k)
+
+    def check_status(self):
+        """Raise if a kernel reported a barrier wait that ran out (reads 16 bytes back)."""
+        st = self._status.cpu().tolist()
+        if st[0] != 0:
+            raise A.MsaError(f"routing kernel gave up on a barrier wait (code {st[0]})")

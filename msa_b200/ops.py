@@ -143,6 +143,12 @@ def route_scores(q_folded: torch.Tensor, row_bias: torch.Tensor, n_seq: int, s_p
     return keys, status
 
 
+def route_table_reset(keys: torch.Tensor, n_docs: int, min_val: float, status: Optional[torch.Tensor] = None):
+    A.need_cuda(keys, status)
+    A.check(A.lib().msa_route_table_reset(A.ptr(keys), keys.stride(0), n_docs, keys.shape[0], float(min_val),
+                                          A.ptr(status), A.stream_ptr(keys.device)), "msa_route_table_reset")
+
+
 def topk_select(keys: torch.Tensor, k: int, doc_ids_table: Optional[torch.Tensor] = None, n_cols: Optional[int] = None):
     """Exact top-k of every row of a key table.  Returns ``(scores f32, local_ids i64, global_ids i64)``,
     each ``[n_seq, min(k, n_cols)]``, sorted by descending score (ties: ascending column)."""
