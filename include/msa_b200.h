@@ -224,6 +224,34 @@ int msa_sparse_decode_attn(const void* q, int32_t dtype, void* k_cache, void* v_
                            float scale, void* out, void* workspace, int64_t workspace_bytes,
                            int32_t n_splits, void* stream);
 
+/* ---------------------------------------------------------------------------------------
+ * Decode attention without any allocation.  (No counterpart in the reference: this entry
+ * point exists for hosts of this library that cannot allocate device memory when a decode
+ * step runs -- a serving loop whose pool already owns the whole GPU, a plugin that is handed
+ * only its inputs and outputs, a policy that forbids allocation after start-up.)
+ *
+ * Same computation and arguments as msa_sparse_decode_attn, but the split-KV partials go to
+ * an 8 MiB array built into the library (msa_decode_static_scratch_bytes()); every GPU that
+ * loads the library holds that array until the process exits.  A call whose
+ * msa_decode_workspace_bytes(n_seq, n_q_heads, head_dim, n_splits) exceeds it is rejected
+ * with MSA_ERR_ARG before anything is launched.  The call itself performs no cudaMalloc,
+ * cudaFree or other allocating call.
+ *
+ * The first call on each device resolves the array's device address (with that device
+ * current) and caches it; make that first call outside of any stream capture.
+ * All calls on a device share the one array.  Nothing in it has to start at zero -- every
+ * launch rewrites every partial it later reads -- but two calls whose kernels overlap on the
+ * GPU (different streams, no ordering between them) race on it: order them.
+ */
+int64_t msa_decode_static_scratch_bytes(void);
+
+int msa_sparse_decode_attn_static(const void* q, int32_t dtype, void* k_cache, void* v_cache,
+                                  int64_t stride_b, int64_t stride_h, const int32_t* kv_start,
+                                  const int32_t* kv_len, const void* new_k, const void* new_v,
+                                  int32_t n_seq, int32_t n_q_heads, int32_t n_kv_heads,
+                                  int32_t head_dim, float scale, void* out, int32_t n_splits,
+                                  void* stream);
+
 #ifdef __cplusplus
 }
 #endif

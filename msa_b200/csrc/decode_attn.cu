@@ -269,3 +269,49 @@ extern "C" int msa_sparse_decode_attn(const void* q, int32_t dtype, void* k_cach
              : launch_decode<float>(q, k_cache, v_cache, stride_b, stride_h, kv_start, kv_len, new_k, new_v, n_seq,
                                     n_q_heads, n_kv_heads, head_dim, scale, out, workspace, n_splits, st);
 }
+
+// ---------------------------------------------------------------------------------------
+// Decode attention for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc at the point where a decode step runs:
+// a serving loop whose memory pool has already claimed the whole GPU, a plugin that is only
+// handed input and output buffers by its framework, or code running under a policy that
+// forbids allocation after start-up.  For them the split-KV partials live in the fixed array
+// below instead of a caller-provided workspace.  The array is part of the library image, so
+// every GPU that loads the library holds kStaticScratchFloats*4 bytes (8 MiB) until exit.
+// ---------------------------------------------------------------------------------------
+namespace msa {
+constexpr long long kStaticScratchFloats = 2ll * 1024 * 1024;  // 8 MiB
+static __device__ __align__(256) float g_decode_scratch[kStaticScratchFloats];
+constexpr int kMaxDevices = 64;
+static float* g_scratch_addr[kMaxDevices] = {nullptr};
+}  // namespace msa
+
+extern "C" int64_t msa_decode_static_scratch_bytes(void) { return msa::kStaticScratchFloats * (int64_t)sizeof(float); }
+
+extern "C" int msa_sparse_decode_attn_static(const void* q, int32_t dtype, void* k_cache, void* v_cache,
+                                             int64_t stride_b, int64_t stride_h, const int32_t* kv_start,
+                                             const int32_t* kv_len, const void* new_k, const void* new_v,
+                                             int32_t n_seq, int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim,
+                                             float scale, void* out, int32_t n_splits, void* stream) {
+  MSA_REQUIRE(n_seq >= 0 && n_q_heads > 0 && head_dim > 0 && n_splits >= 1, "decode (static scratch): bad sizes");
+  const int64_t need = msa_decode_workspace_bytes(n_seq, n_q_heads, head_dim, n_splits);
+  MSA_REQUIRE(need <= msa_decode_static_scratch_bytes(),
+              "decode (static scratch): n_seq*n_q_heads*n_splits*(head_dim+2)*4 = %lld bytes exceeds the built-in "
+              "%lld-byte scratch; use fewer splits or msa_sparse_decode_attn with your own workspace",
+              (long long)need, (long long)msa_decode_static_scratch_bytes());
+  int dev = -1;
+  MSA_CUDA_OK(cudaGetDevice(&dev));
+  MSA_REQUIRE(dev >= 0 && dev < kMaxDevices, "decode (static scratch): device ordinal %d out of range", dev);
+  if (g_scratch_addr[dev] == nullptr) {
+    // First call on this device: resolve the array's address on the CURRENT device.  The symbol
+    // name is only a host-side handle; the kernel must be given the address obtained here.
+    float* p = nullptr;
+    MSA_CUDA_OK(cudaGetSymbolAddress((void**)&p, g_decode_scratch));
+    MSA_REQUIRE(p != nullptr, "decode (static scratch): could not resolve the scratch array");
+    g_scratch_addr[dev] = p;
+  }
+  return msa_sparse_decode_attn(q, dtype, k_cache, v_cache, stride_b, stride_h, kv_start, kv_len, new_k, new_v, n_seq,
+                                n_q_heads, n_kv_heads, head_dim, scale, out, g_scratch_addr[dev], need, n_splits,
+                                stream);
+}
