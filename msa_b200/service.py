@@ -173,6 +173,44 @@ class MSAService(Memory, MemoryClientBase):
             kv_base[layer] = torch.tensor(addrs, dtype=torch.int64, device=self.device)
         self._directory = (base.to(self.device), offs.to(self.device), ln.to(self.device), kv_base)
 
+    def share_host_banks(self, tag: str, shm_dir: str = "/dev/shm"):
+        """Move this rank's K/V banks into shared-memory files, map and pin every peer's files, and
+        publish the node-wide directory.  Collective: every rank calls it after building its shard."""
+        g = self.geometry
+        sizes = [self.block_desc.chunks()]
+        if self.world_size > 1:
+            sizes = [None] * self.world_size
+            dist.all_gather_object(sizes, self.block_desc.chunks(), group=self.group)
+        path = lambda w, layer: os.path.join(shm_dir, f"msa_b200_{tag}_r{w}_l{layer}.bank")
+        shape = lambda w: (sizes[w], 2, g.num_key_value_heads, g.head_dim)
+        own = {}
+        for layer in self.router_layer_ids:
+            blk = self.blocks[layer]
+            bank = SharedHostBank(path(self.rank, layer), shape(self.rank), blk.kv.dtype, create=True)
+            bank.tensor.copy_(blk.kv)
+            blk.kv = bank.tensor
+            own[layer] = bank
+        if self.world_size > 1:
+            dist.barrier(group=self.group)
+        self._shared_banks, addresses = [], {}
+        for layer in self.router_layer_ids:
+            banks = [own[layer] if w == self.rank else
+                     SharedHostBank(path(w, layer), shape(w), self.blocks[layer].kv.dtype, create=False)
+                     for w in range(self.world_size)]
+            addresses[layer] = [b.register() for b in banks]
+            self.blocks[layer].kv_device_address = addresses[layer][self.rank]
+            self._shared_banks.extend(banks)
+        self.publish_directory(peer_kv_addresses=addresses)
+
+    def close_host_banks(self):
+        """Unpin and (for the owner) unlink the shared banks.  Collective when world_size > 1."""
+        torch.cuda.synchronize(self.device)
+        if self.world_size > 1:
+            dist.barrier(group=self.group)
+        for b in getattr(self, "_shared_banks", []):
+            b.close()
+        self._shared_banks = []
+
     # ------------------------------------------------------------------ the layer-facing call
     def _gather_querys(self, query_states: torch.Tensor, query_mask: torch.Tensor):
         """Fold local queries, agree on the padded length, all-gather (:1088-1131).

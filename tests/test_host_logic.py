@@ -1,0 +1,96 @@
+"""Host-side logic that needs no GPU: ABI surface, partitioning, directory, candidate packing,
+and the all-gather layouts of the Memory-Parallel exchange on 2 gloo ranks."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_loads_and_exports_every_declared_symbol():
+    from msa_b200 import _cabi as A
+    from msa_b200.build import build
+    build()
+    lib = A.lib()
+    header = open(os.path.join(ROOT, "include", "msa_b200.h")).read()
+    declared = set(re.findall(r"\b(msa_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    assert declared == set(A.EXPORTS)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert lib.msa_abi_version() == 1
+    assert lib.msa_route_s_pad(256, 0) == 256 and lib.msa_route_s_pad(100, 0) == 112
+    assert lib.msa_route_s_pad(300, 0) == 320 and lib.msa_route_s_pad(1, 0) == 1 and lib.msa_route_s_pad(77, 1) == 1
+    assert lib.msa_decode_workspace_bytes(2, 32, 128, 4) == 2 * 32 * 4 * 130 * 4
+
+
+def test_argument_errors_are_reported_before_any_launch():
+    from msa_b200 import _cabi as A
+    lib = A.lib()
+    assert lib.msa_pool_chunks(None, 1, 0, 0, None, None, None, 1, 8, 128, None, 0, 0, 0, None) == -1
+    assert b"null pointer" in lib.msa_last_error()
+    assert lib.msa_topk_select(1, 8, 1, 4, 5000, None, 1, 1, None, None) == -1
+    assert b"exceeds the supported maximum" in lib.msa_last_error()
+    with pytest.raises(A.MsaError, match="CUDA tensors"):
+        from msa_b200 import ops
+        ops.pool_chunks(torch.zeros(4, 8, 128), torch.tensor([0, 4], dtype=torch.int32))
+
+
+def test_balanced_bucket_partition_and_directory():
+    from msa_b200.memory import Document
+    from msa_b200.service import balanced_bucket_partition, build_directory
+    docs = [Document(doc_id=i, num_chunks=n) for i, n in enumerate([9, 1, 1, 8, 3, 3, 7, 2])]
+    buckets = balanced_bucket_partition(docs, 3)
+    loads = [sum(d.num_chunks for d in b) for b in buckets]
+    assert sorted(d.doc_id for b in buckets for d in b) == list(range(8))
+    assert max(loads) - min(loads) <= 2
+    base, offs, lens = build_directory([[0, 2, 3], [0, 5], [0]])
+    assert base.tolist() == [0, 3, 5]
+    assert lens.tolist() == [0, 2, 3, 0, 5, 0] and offs.tolist() == [0, 0, 2, 0, 0, 0]
+
+
+def test_candidate_packing_roundtrip():
+    from msa_b200.service import pack_candidates, unpack_candidates
+    s = torch.tensor([[0.5, -3.4e38, float("-inf")], [1e-9, -0.0, 7.0]])
+    l = torch.tensor([[1, 2, 0], [9, 8, 7]])
+    g = l + 100
+    s2, l2, g2 = unpack_candidates(pack_candidates(s, l, g))
+    assert torch.equal(s2.view(torch.int32), s.view(torch.int32)) and torch.equal(l2, l) and torch.equal(g2, g)
+
+
+def _rank(rank, world, port, ret):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from msa_b200.service import all_gather_cat, build_directory, pack_candidates, unpack_candidates
+    b, k = 3, 4
+    # every rank scored ALL world*b queries against its shard; candidates are gathered to [W, B_all, k]
+    scores = torch.arange(world * b * k, dtype=torch.float32).view(world * b, k) + 1000 * rank
+    local = torch.full((world * b, k), rank + 1)
+    packed = all_gather_cat(pack_candidates(scores, local, local + 10), world)
+    s, l, g = unpack_candidates(packed)
+    lens = [None] * world
+    dist.all_gather_object(lens, [0] + [rank + 1] * (rank + 2))
+    base, offs, ln = build_directory(lens)
+    ret[rank] = (s.clone(), l.clone(), base.tolist(), ln.tolist())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_exchange_layout_two_gloo_ranks():
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_rank, args=(world, 29733, ret), nprocs=world, join=True)
+    for rank in range(world):
+        s, l, base, ln = ret[rank]
+        assert s.shape == (world, world * 3, 4)
+        for owner in range(world):
+            assert (l[owner] == owner + 1).all()
+            assert s[owner, 0, 0] == 1000 * owner
+        assert base == [0, 3] and ln == [0, 1, 1, 0, 2, 2, 2]
+    assert torch.equal(ret[0][0], ret[1][0])
