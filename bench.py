@@ -44,6 +44,8 @@ def parse():
     ap.add_argument("--layers", type=int, default=N_LAYERS)
     ap.add_argument("--queries", type=int, default=N_QUERIES)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="routing", choices=["routing", "pooling", "decode", "fetch", "route-decode"],
+                    help="routing = the headline (default); the others time one secondary kernel each")
     return ap.parse_args()
 
 
@@ -348,9 +350,165 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------------------
+# Secondary kernels: one JSON line each (single GPU), HBM or PCIe roofline.
+# ------------------------------------------------------------------------------------------
+def _time_ms(torch, fn, steps, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def _secondary_line(args, metric, unit, value, ms, workload, kernel, alg_bytes, peak, peak_name, clocks, launches,
+                    extra=None):
+    gbs = alg_bytes / (ms / 1e3) / 1e9
+    line = {"metric": metric, "value": value, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": {"workload": workload}, "gpu_launches": launches, "clocks": clocks,
+            "roofline": {"kernel": kernel, "bound": "hbm" if peak_name == "hbm" else peak_name, "achieved": gbs,
+                         "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None,
+                         "algorithmic_bytes_per_step": alg_bytes}}
+    if extra:
+        line.update(extra)
+    print(json.dumps(line))
+
+
+def run_secondary(args):
+    import torch
+    from msa_b200 import ops
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    pk = peaks()
+    g = torch.Generator(device=dev)
+    g.manual_seed(2000)
+    sampler = ClockSampler(0)
+    steps, warmup = max(args.steps, 5), max(args.warmup, 3)
+    args.steps, args.warmup = steps, warmup
+
+    if args.workload == "pooling":
+        # BASELINE config 2: 2,048 documents x 512 tokens, K / V / K_r bf16 [1, 8, T, 128], chunk 64
+        n_docs, doc_len, p = 2048, 512, 64
+        t = n_docs * doc_len
+        doc_ids = torch.arange(1, n_docs + 1, device=dev).repeat_interleave(doc_len).view(1, t)
+        tok, off, pooled = ops.chunk_bookkeeping(doc_ids, None, p)
+        ms_bk = _time_ms(torch, lambda: ops.chunk_bookkeeping(doc_ids, None, p, max_chunks=t // p + 1), 3, 1)
+        states = [torch.randn((1, HKV, t, D), generator=g, device=dev).to(torch.bfloat16) for _ in range(3)]
+
+        def step():
+            ops.pool_chunks(states[0], off, tok)
+            ops.pool_chunks(states[1], off, tok)
+            ops.pool_chunks(states[2], off, tok, l2_normalize=True)
+        sampler.start()
+        ms = _time_ms(torch, step, steps, warmup)
+        clocks = sampler.stop()
+        c = off.numel() - 1
+        alg = 3 * (t * HKV * D * 2 + c * HKV * D * 2)
+        _secondary_line(args, "chunk-mean pooling tokens/s (K, V, K_r)", "tokens/s", t / (ms / 1e3), ms,
+                        f"BASELINE config 2: {n_docs} docs x {doc_len} tokens, chunk {p}, bf16, 3 tensors "
+                        f"(2.15 GB each, > L2)", "pool_kernel", alg, pk["hbm_gbs"], "hbm", clocks, 3 * steps,
+                        {"bookkeeping_ms": ms_bk})
+
+    elif args.workload == "decode":
+        # BASELINE config 5: batch 32, 32 q / 8 kv heads, L = 3 template + 128 retrieved + 2048 local
+        b, L, n_layers = 32, 3 + 128 + 2048, 4
+        caches = [(torch.randn((b, HKV, L + 8, D), generator=g, device=dev).to(torch.bfloat16),
+                   torch.randn((b, HKV, L + 8, D), generator=g, device=dev).to(torch.bfloat16)) for _ in range(n_layers)]
+        q = torch.randn((b, HQ, D), generator=g, device=dev).to(torch.bfloat16)
+        nk = torch.randn((b, HKV, D), generator=g, device=dev).to(torch.bfloat16)
+        nv = torch.randn((b, HKV, D), generator=g, device=dev).to(torch.bfloat16)
+        kv_len = torch.full((b,), L, dtype=torch.int32, device=dev)
+        n_splits = ops.decode_splits(b, HKV, L)
+        ws = torch.empty(max(1, int(b * HQ * n_splits * (D + 2))), dtype=torch.float32, device=dev)
+        out = torch.empty((b, HQ * D), dtype=torch.bfloat16, device=dev)
+
+        def step():
+            for kc, vc in caches:
+                ops.sparse_decode_attn(q, kc, vc, kv_len, nk, nv, n_splits=n_splits, workspace=ws, out=out)
+        sampler.start()
+        ms = _time_ms(torch, step, steps, warmup) / n_layers
+        clocks = sampler.stop()
+        alg = 2 * b * (L + 1) * HKV * D * 2
+        _secondary_line(args, "sparse decode attention layer-steps/s", "layer-steps/s", 1e3 / ms, ms,
+                        f"BASELINE config 5 layer: batch {b}, L={L}+1, 32q/8kv heads, d=128, bf16, {n_splits} KV "
+                        f"splits, {n_layers} distinct caches of 285 MB rotate (> L2)", "decode_split_kernel", alg,
+                        pk["hbm_gbs"], "hbm", clocks, 3 * n_layers * steps)
+
+    elif args.workload == "fetch":
+        # host bank of 32,768 documents x 8 chunks (1.07 GB pinned); 128 queries x 16 winners per layer
+        n_docs, b, k = 32768, N_QUERIES, TOP_K
+        bank = torch.empty((n_docs * CHUNKS_PER_DOC, 2, HKV, D), dtype=torch.bfloat16).pin_memory()
+        bank.copy_(torch.randn(bank.shape, generator=g, device=dev).to(torch.bfloat16))
+        lens = torch.tensor([0] + [CHUNKS_PER_DOC] * n_docs, dtype=torch.int32, device=dev)
+        offs = torch.cumsum(torch.cat([torch.zeros(1, dtype=torch.long, device=dev), lens[:-1].long()]), 0)
+        base = torch.zeros(1, dtype=torch.long, device=dev)
+        kv_base = torch.tensor([bank.data_ptr()], dtype=torch.int64, device=dev)
+        gsel = torch.Generator().manual_seed(7)
+        sels = [torch.stack([torch.randperm(n_docs, generator=gsel)[:k] + 1 for _ in range(b)]).to(dev) for _ in range(4)]
+        n_entries = b * k * CHUNKS_PER_DOC
+        state = {"i": 0}
+
+        def step():
+            sel = sels[state["i"] % len(sels)]
+            state["i"] += 1
+            plan, n_sel, total = ops.gather_plan(sel, None, 1, base, offs, lens, kv_base, 2 * HKV * D * 2)
+            ops.gather_run(plan, torch.bfloat16, HKV, D, n_entries)
+        sampler.start()
+        ms = _time_ms(torch, step, steps, warmup)
+        clocks = sampler.stop()
+        alg = n_entries * 2 * HKV * D * 2
+        _secondary_line(args, "host K/V fetch documents/s", "documents/s", b * k / (ms / 1e3), ms,
+                        f"{b} queries x top-{k} documents x {CHUNKS_PER_DOC} chunks = {alg / 1e6:.0f} MB per layer from a "
+                        f"1.07 GB pinned host bank (plan + gather)", "gather_kernel", alg, 55.0, "pcie", clocks,
+                        2 * steps, {"note": "peak = 55 GB/s, a nominal PCIe Gen5 x16 payload rate (not measured)"})
+
+    else:  # route-decode: BASELINE config 5 per-step routing on one of 8 shards
+        b, docs_local = 32, (N_DOCS + 7) // 8
+        c = docs_local * CHUNKS_PER_DOC
+        n_layers = 4
+        banks = make_bank(torch, dev, docs_local, n_layers, seed=9000)
+        chunk_doc = torch.arange(1, docs_local + 1, device=dev, dtype=torch.int32).repeat_interleave(CHUNKS_PER_DOC)
+        q = torch.nn.functional.normalize(torch.randn((b, HQ, 1, D), generator=g, device=dev), dim=-1).to(torch.bfloat16)
+        mask = torch.ones((b, 1), dtype=torch.bool, device=dev)
+        keys = torch.empty((b, docs_local + 1), dtype=torch.int32, device=dev)
+        status = torch.zeros(4, dtype=torch.int32, device=dev)
+        ev = []
+
+        def step():
+            for rk in banks:
+                qf, bias, s_pad = ops.fold_queries(q, mask, HQ // HKV)
+                ops.route_table_reset(keys, docs_local, torch.finfo(torch.bfloat16).min, status)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                ops.route_scores(qf, bias, b, s_pad, rk, chunk_doc, docs_local, 1.0 / HQ, keys=keys, status=status,
+                                 flags=2)
+                e1.record()
+                ev.append((e0, e1))
+                ops.topk_select(keys, TOP_K)
+        sampler.start()
+        ms = _time_ms(torch, step, steps, warmup) / n_layers
+        clocks = sampler.stop()
+        route_ms = statistics.mean([a.elapsed_time(b_) for a, b_ in ev[-steps * n_layers:]])
+        alg = c * HKV * D * 2 + b * HKV * D * 2
+        _secondary_line(args, "decode-time routing layer-steps/s (one of 8 shards)", "layer-steps/s", 1e3 / ms, ms,
+                        f"BASELINE config 5 per-step routing: {b} sequences x 1 token against {c} chunks (400 MB shard), "
+                        f"{n_layers} distinct layers rotate", "route_tc_kernel", alg, pk["hbm_gbs"], "hbm", clocks,
+                        4 * n_layers * steps, {"route_kernel_ms": route_ms,
+                                               "route_kernel_gbs": alg / (route_ms / 1e3) / 1e9,
+                                               "route_kernel_frac": alg / (route_ms / 1e3) / 1e9 / pk["hbm_gbs"]})
+
+
 if __name__ == "__main__":
     a = parse()
     if a.impl == "reference":
         run_reference(a)
+    elif a.workload != "routing":
+        run_secondary(a)
     else:
         run_ours(a)

@@ -124,10 +124,12 @@ def route_scores(q_folded: torch.Tensor, row_bias: torch.Tensor, n_seq: int, s_p
     A.need_cuda(q_folded, row_bias, rk, chunk_doc)
     dev = rk.device
     c = rk.shape[0]
-    rk2 = rk.reshape(c, -1) if rk.is_contiguous() else rk.flatten(1)
-    if rk2.stride(1) != 1 and c > 0:
+    kdim = 1
+    for n in rk.shape[1:]:
+        kdim *= n
+    rk2 = rk.reshape(c, kdim) if rk.is_contiguous() else rk.flatten(1)
+    if c > 0 and rk2.stride(1) != 1:
         raise A.MsaError("route_scores: router keys must have a contiguous feature axis")
-    kdim = rk2.shape[1]
     if chunk_doc.dtype != torch.int32:
         raise A.MsaError("route_scores: chunk_doc must be int32")
     if min_val is None:
