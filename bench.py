@@ -431,8 +431,13 @@ def run_secondary(args):
         def step():
             for kc, vc in caches:
                 ops.sparse_decode_attn(q, kc, vc, kv_len, nk, nv, n_splits=n_splits, workspace=ws, out=out)
+        _time_ms(torch, step, 2, 2)
+        graph = torch.cuda.CUDAGraph()      # a decode loop replays its token step from a CUDA graph
+        with torch.cuda.graph(graph):
+            step()
+        kv_len.fill_(L)
         sampler.start()
-        ms = _time_ms(torch, step, steps, warmup) / n_layers
+        ms = _time_ms(torch, graph.replay, 20 * steps, warmup) / n_layers
         clocks = sampler.stop()
         alg = 2 * b * (L + 1) * HKV * D * 2
         _secondary_line(args, "sparse decode attention layer-steps/s", "layer-steps/s", 1e3 / ms, ms,
@@ -480,26 +485,36 @@ def run_secondary(args):
         status = torch.zeros(4, dtype=torch.int32, device=dev)
         ev = []
 
-        def step():
+        def step(timed=False):
             for rk in banks:
                 qf, bias, s_pad = ops.fold_queries(q, mask, HQ // HKV)
                 ops.route_table_reset(keys, docs_local, torch.finfo(torch.bfloat16).min, status)
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
+                if timed:
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
                 ops.route_scores(qf, bias, b, s_pad, rk, chunk_doc, docs_local, 1.0 / HQ, keys=keys, status=status,
                                  flags=2)
-                e1.record()
-                ev.append((e0, e1))
+                if timed:
+                    e1.record()
+                    ev.append((e0, e1))
                 ops.topk_select(keys, TOP_K)
-        sampler.start()
-        ms = _time_ms(torch, step, steps, warmup) / n_layers
-        clocks = sampler.stop()
+        # the scoring kernel alone, eagerly, with events around each launch
+        _time_ms(torch, lambda: step(True), steps, warmup)
         route_ms = statistics.mean([a.elapsed_time(b_) for a, b_ in ev[-steps * n_layers:]])
+        # the whole layer-step replayed from a CUDA graph: at ~100 us per layer the Python
+        # launch path would otherwise be the bottleneck, as it would be in a real decode loop
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step(False)
+        sampler.start()
+        ms = _time_ms(torch, graph.replay, 20 * steps, warmup) / n_layers
+        clocks = sampler.stop()
         alg = c * HKV * D * 2 + b * HKV * D * 2
         _secondary_line(args, "decode-time routing layer-steps/s (one of 8 shards)", "layer-steps/s", 1e3 / ms, ms,
                         f"BASELINE config 5 per-step routing: {b} sequences x 1 token against {c} chunks (400 MB shard), "
                         f"{n_layers} distinct layers rotate", "route_tc_kernel", alg, pk["hbm_gbs"], "hbm", clocks,
-                        4 * n_layers * steps, {"route_kernel_ms": route_ms,
+                        5 * n_layers * 20 * steps, {"launch": "one CUDA graph per step (fold, reset, score, 2-level top-k)",
+                                                    "route_kernel_ms": route_ms,
                                                "route_kernel_gbs": alg / (route_ms / 1e3) / 1e9,
                                                "route_kernel_frac": alg / (route_ms / 1e3) / 1e9 / pk["hbm_gbs"]})
 

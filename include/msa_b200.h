@@ -42,7 +42,9 @@ enum msa_query_reduce { MSA_QREDUCE_MAX = 0, MSA_QREDUCE_MEAN = 1, MSA_QREDUCE_L
 
 /* flags of msa_route_scores */
 #define MSA_ROUTE_FORCE_SIMT 1u /* use the CUDA-core kernel even for bf16 (cross-checks) */
-#define MSA_ROUTE_NO_INIT 2u    /* do not reset the score table first (accumulate slices) */
+#define MSA_ROUTE_NO_INIT 2u    /* do not reset the score table first: it was reset by
+                                   msa_route_table_reset or holds the scores of other chunk ranges.
+                                   Every call must then cover whole documents. */
 
 int msa_abi_version(void);
 const char* msa_last_error(void);
@@ -141,15 +143,20 @@ int msa_route_table_reset(uint32_t* score_keys, int64_t table_stride, int32_t n_
                           float min_val, int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------------------------------
- * Routing, step 3: exact per-shard top-k (block radix select + sort of the winners).
+ * Routing, step 3: exact per-shard top-k (two levels of a shared-memory bitonic sort).
  * Replaces torch.topk + create_global_doc_ids (src/msa_service.py:826-828).
  * Selects k_eff = min(k, n_cols) columns per row, sorted by descending score; equal scores
  * are ordered by ascending column.  out_* are [n_seq, k_eff].  doc_ids_table (nullable) is the
  * local->global table (BlockDesc.doc_ids, src/msa_service.py:199-201, 218-219).
+ * workspace: device, msa_topk_workspace_bytes(n_seq, n_cols, k) bytes (0 for rows up to 2048).
+ * Limits: k <= 1024, n_seq <= 65535, n_cols * k <= 2^26.
  */
+int64_t msa_topk_workspace_bytes(int32_t n_seq, int32_t n_cols, int32_t k);
+
 int msa_topk_select(const uint32_t* score_keys, int64_t table_stride, int32_t n_seq,
                     int32_t n_cols, int32_t k, const int64_t* doc_ids_table, float* out_scores,
-                    int64_t* out_local_ids, int64_t* out_global_ids, void* stream);
+                    int64_t* out_local_ids, int64_t* out_global_ids, void* workspace,
+                    int64_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Cross-rank merge of the per-shard candidates.

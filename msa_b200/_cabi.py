@@ -20,7 +20,7 @@ ROUTE_FORCE_SIMT, ROUTE_NO_INIT = 1, 2
 
 EXPORTS = [
     "msa_abi_version", "msa_last_error", "msa_chunk_bookkeeping", "msa_pool_chunks", "msa_fold_queries",
-    "msa_route_s_pad", "msa_route_table_reset", "msa_route_scores", "msa_topk_select", "msa_topk_merge", "msa_gather_plan",
+    "msa_route_s_pad", "msa_route_table_reset", "msa_route_scores", "msa_topk_workspace_bytes", "msa_topk_select", "msa_topk_merge", "msa_gather_plan",
     "msa_gather_run", "msa_bank_register_host", "msa_bank_unregister_host", "msa_decode_workspace_bytes", "msa_sparse_decode_attn",
     "msa_decode_static_scratch_bytes", "msa_sparse_decode_attn_static",
 ]
@@ -51,7 +51,9 @@ def lib() -> C.CDLL:
         l.msa_route_s_pad.restype = i32
         l.msa_route_scores.argtypes = [vp, vp, i32, i32, i32, vp, i64, i32, i32, vp, f32, vp, i64, i32, f32, u32, vp, vp]
         l.msa_route_table_reset.argtypes = [vp, i64, i32, i32, f32, vp, vp]
-        l.msa_topk_select.argtypes = [vp, i64, i32, i32, i32, vp, vp, vp, vp, vp]
+        l.msa_topk_workspace_bytes.argtypes = [i32, i32, i32]
+        l.msa_topk_workspace_bytes.restype = i64
+        l.msa_topk_select.argtypes = [vp, i64, i32, i32, i32, vp, vp, vp, vp, vp, i64, vp]
         l.msa_topk_merge.argtypes = [vp, vp, vp, i64, i32, i32, i32, i32, f32, vp, vp, vp, vp, vp]
         l.msa_gather_plan.argtypes = [vp, vp, i32, i32, i32, vp, vp, vp, vp, i64, vp, vp, vp, vp, vp]
         l.msa_gather_run.argtypes = [vp, i32, i32, i32, i32, vp, vp, i64, i64, vp]

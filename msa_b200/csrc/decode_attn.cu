@@ -7,6 +7,7 @@
 // merges the splits.  The new token's K/V takes part straight from its own buffer and is
 // appended to the cache in place, which replaces the reference's per-step torch.cat.
 #include "common.cuh"
+#include "decode_mma.cuh"
 
 namespace msa {
 
@@ -230,6 +231,34 @@ int launch_decode(const void* q, void* k_cache, void* v_cache, int64_t stride_b,
   return MSA_OK;
 }
 
+// bf16, head_dim 128, group size <= 8: the tensor-core fragment kernel of decode_mma.cuh.
+int launch_decode_mma(const void* q, void* k_cache, void* v_cache, int64_t stride_b, int64_t stride_h,
+                      const int32_t* kv_start, const int32_t* kv_len, const void* new_k, const void* new_v, int n_seq,
+                      int n_q_heads, int n_kv_heads, float scale, void* out, void* workspace, int n_splits,
+                      cudaStream_t stream) {
+  using T = __nv_bfloat16;
+  if (new_k) {
+    append_kv_kernel<T><<<dim3(n_kv_heads, n_seq), 128, 0, stream>>>(
+        (T*)k_cache, (T*)v_cache, stride_b, stride_h, kv_start, kv_len, (const T*)new_k, (const T*)new_v,
+        n_kv_heads, kMmaD);
+    MSA_LAUNCH_OK("append_kv_kernel");
+  }
+  static thread_local bool configured = false;
+  if (!configured) {
+    MSA_CUDA_OK(cudaFuncSetAttribute(decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMmaSmemBytes));
+    configured = true;
+  }
+  decode_mma_kernel<<<dim3(n_splits, n_kv_heads, n_seq), kMmaWarps * 32, kMmaSmemBytes, stream>>>(
+      (const T*)q, (const T*)k_cache, (const T*)v_cache, stride_b, stride_h, kv_start, kv_len, (const T*)new_k,
+      (const T*)new_v, n_q_heads, n_kv_heads, scale * 1.4426950408889634f, (T*)out, (float*)workspace, n_splits);
+  MSA_LAUNCH_OK("decode_mma_kernel");
+  if (n_splits > 1) {
+    decode_combine_kernel<T><<<n_seq * n_q_heads, 128, 0, stream>>>((const float*)workspace, kMmaD, n_splits, (T*)out);
+    MSA_LAUNCH_OK("decode_combine_kernel");
+  }
+  return MSA_OK;
+}
+
 }  // namespace msa
 
 using namespace msa;
@@ -263,6 +292,9 @@ extern "C" int msa_sparse_decode_attn(const void* q, int32_t dtype, void* k_cach
               "decode: workspace too small for %d splits", n_splits);
   if (n_seq == 0) return MSA_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == MSA_BF16 && head_dim == kMmaD && n_q_heads / n_kv_heads <= 8)
+    return launch_decode_mma(q, k_cache, v_cache, stride_b, stride_h, kv_start, kv_len, new_k, new_v, n_seq, n_q_heads,
+                             n_kv_heads, scale, out, workspace, n_splits, st);
   return dtype == MSA_BF16
              ? launch_decode<__nv_bfloat16>(q, k_cache, v_cache, stride_b, stride_h, kv_start, kv_len, new_k, new_v,
                                             n_seq, n_q_heads, n_kv_heads, head_dim, scale, out, workspace, n_splits, st)

@@ -14,7 +14,7 @@ int launch_route_simt(int32_t dtype, const void* qf, const float* row_bias, int 
                       uint32_t* keys, int64_t table_stride, cudaStream_t stream);
 
 int launch_route_tc(const void* qf, const float* row_bias, int n_seq, int s_pad, const void* rk, int64_t rk_stride,
-                    int n_chunks, int kdim, const int32_t* chunk_doc, float alpha, uint32_t* keys,
+                    int n_chunks, int kdim, const int32_t* chunk_doc, float alpha, float min_val, uint32_t* keys,
                     int64_t table_stride, int32_t* status, cudaStream_t stream);
 
 }  // namespace msa

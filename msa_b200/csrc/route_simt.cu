@@ -273,7 +273,7 @@ extern "C" int msa_route_scores(const void* q_folded, const float* row_bias, int
   if (n_seq == 0 || n_chunks == 0) return MSA_OK;
   if (dtype == MSA_BF16 && !(flags & MSA_ROUTE_FORCE_SIMT))
     return launch_route_tc(q_folded, row_bias, n_seq, s_pad, rk, rk_chunk_stride, n_chunks, kdim, chunk_doc, alpha,
-                           score_keys, table_stride, status, st);
+                           min_val, score_keys, table_stride, status, st);
   return launch_route_simt(dtype, q_folded, row_bias, n_seq, s_pad, rk, rk_chunk_stride, n_chunks, kdim, chunk_doc,
                            alpha, score_keys, table_stride, st);
 }

@@ -40,6 +40,7 @@ constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per barrier w
 
 struct RouteTcParams {
   int n_rows, n_seq, s_pad, bn, n_chunks, n_ctiles, n_qtiles, qgroup, k_blocks, stages;
+  uint32_t min_key;
   float alpha;
   const float* row_bias;
   const int32_t* chunk_doc;
@@ -250,8 +251,25 @@ route_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constan
       for (int j = lane; j < p.bn; j += 32) bias[j] = (q0 + j < p.n_rows) ? p.row_bias[q0 + j] : -INFINITY;
       const int chunk = tc.ct * kBM + threadIdx.x;
       const int doc = chunk < p.n_chunks ? p.chunk_doc[chunk] : -1 - lane;  // out-of-range lanes stay alone
-      const uint32_t seg_mask = __match_any_sync(0xffffffffu, doc);
-      const bool leader = doc > 0 && lane == (__ffs(seg_mask) - 1);
+      // Segments = runs of lanes holding chunks of one document.  `dist` is the distance to the
+      // segment's first lane; the last lane of a segment publishes the document's score.  A
+      // document that lies wholly inside this warp's 32 chunks (and whose sequence is not cut
+      // over several column tiles) has no other writer: a plain store replaces the atomic.
+      const int doc_up = __shfl_up_sync(0xffffffffu, doc, 1), doc_dn = __shfl_down_sync(0xffffffffu, doc, 1);
+      const bool head = lane == 0 || doc_up != doc, tail = lane == 31 || doc_dn != doc;
+      const uint32_t heads = __ballot_sync(0xffffffffu, head);
+      const int head_lane = 31 - __clz(heads & (0xffffffffu >> (31 - lane)));
+      const int dist = lane - head_lane;
+      int max_len = dist + 1;  // longest segment in this warp
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) max_len = max(max_len, __shfl_xor_sync(0xffffffffu, max_len, o));
+      bool starts_here = true, ends_here = true;                     // does the document cross the warp's edges?
+      if (lane == 0 && chunk > 0 && chunk < p.n_chunks) starts_here = p.chunk_doc[chunk - 1] != doc;
+      if (lane == 31 && chunk + 1 < p.n_chunks) ends_here = p.chunk_doc[chunk + 1] != doc;
+      const bool open_lo = !__shfl_sync(0xffffffffu, starts_here, 0), open_hi = !__shfl_sync(0xffffffffu, ends_here, 31);
+      const bool crosses = (open_lo && head_lane == 0) || (open_hi && (heads >> lane) <= 1u);
+      const bool publish = tail && doc > 0;
+      const bool exclusive = !crosses && p.s_pad <= p.bn;
       __syncwarp();
       // every lane waits; the warp then agrees on the outcome so that it never diverges
       ok = mbar_wait(&s_acc_full[buf], acc_phase, abort_flag, p.status, 4);
@@ -260,29 +278,53 @@ route_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constan
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)buf * kRouteMaxN;
 
-      auto emit = [&](float v, int seq) {  // document max over this warp's lanes, then one atomic
-        const uint32_t key = __reduce_max_sync(seg_mask, float_to_key(v * p.alpha));
-        if (leader && seq < p.n_seq) atomicMax(p.keys + (long long)seq * p.table_stride + doc, key);
-      };
-      if (p.s_pad == 1) {
-        for (int c0 = 0; c0 < p.bn; c0 += 16) {
-          uint32_t r[16];
-          tmem_ld16(taddr + c0, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 16; ++j) emit(__uint_as_float(r[j]) + bias[c0 + j], q0 + c0 + j);
+      auto publish_score = [&](float v, int seq) {
+        if (seq < p.n_seq) {
+          const uint32_t key = float_to_key(v * p.alpha);
+          uint32_t* dst = p.keys + (long long)seq * p.table_stride + doc;
+          if (exclusive) *dst = max(key, p.min_key);
+          else atomicMax(dst, key);
         }
-      } else {
+      };
+      auto load16 = [&](int c0, float (&v)[16]) {
+        uint32_t r[16];
+        tmem_ld16(taddr + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]) + bias[c0 + j];
+      };
+      // Segmented max over the lanes of a document: log2(longest segment) shuffle steps, done
+      // for a whole batch of independent values at a time so that the shuffles pipeline.
+      if (p.s_pad == 1) {  // every column is its own sequence
+        for (int c0 = 0; c0 < p.bn; c0 += 16) {
+          float v[16];
+          load16(c0, v);
+          for (int d = 1; d < max_len; d <<= 1) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float o = __shfl_up_sync(0xffffffffu, v[j], d);
+              if (dist >= d) v[j] = fmaxf(v[j], o);
+            }
+          }
+          if (publish) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) publish_score(v[j], q0 + c0 + j);
+          }
+        }
+      } else {             // `seg` consecutive columns belong to one sequence: in-thread max first
         for (int s0 = 0; s0 < p.bn; s0 += seg) {
           float run = -INFINITY;
           for (int c0 = s0; c0 < s0 + seg; c0 += 16) {
-            uint32_t r[16];
-            tmem_ld16(taddr + c0, r);
-            tmem_ld_wait();
+            float v[16];
+            load16(c0, v);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) run = fmaxf(run, __uint_as_float(r[j]) + bias[c0 + j]);
+            for (int j = 0; j < 16; ++j) run = fmaxf(run, v[j]);
           }
-          emit(run, (q0 + s0) / p.s_pad);
+          for (int d = 1; d < max_len; d <<= 1) {
+            const float o = __shfl_up_sync(0xffffffffu, run, d);
+            if (dist >= d) run = fmaxf(run, o);
+          }
+          if (publish) publish_score(run, (q0 + s0) / p.s_pad);
         }
       }
       tc_fence_before();
@@ -332,7 +374,7 @@ static int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t 
 }
 
 int launch_route_tc(const void* qf, const float* row_bias, int n_seq, int s_pad, const void* rk, int64_t rk_stride,
-                    int n_chunks, int kdim, const int32_t* chunk_doc, float alpha, uint32_t* keys,
+                    int n_chunks, int kdim, const int32_t* chunk_doc, float alpha, float min_val, uint32_t* keys,
                     int64_t table_stride, int32_t* status, cudaStream_t stream) {
   MSA_REQUIRE(kdim % kBK == 0, "route (tensor-core path): kdim=%d must be a multiple of %d", kdim, kBK);
   MSA_REQUIRE(aligned16(qf) && aligned16(rk) && rk_stride % 8 == 0 && rk_stride >= kdim,
@@ -367,6 +409,7 @@ int launch_route_tc(const void* qf, const float* row_bias, int n_seq, int s_pad,
   if (p.qgroup > p.n_qtiles) p.qgroup = p.n_qtiles;
   p.alpha = alpha; p.row_bias = row_bias; p.chunk_doc = chunk_doc; p.keys = keys; p.table_stride = table_stride;
   p.status = status;
+  p.min_key = float_to_key(min_val);
 
   CUtensorMap map_k, map_q;
   int rc = make_map(&map_k, rk, (uint64_t)n_chunks, (uint64_t)kdim, (uint64_t)rk_stride, kBM);

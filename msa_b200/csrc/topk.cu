@@ -1,116 +1,158 @@
-// Exact top-k over the document score table (block radix select) and the cross-rank merge.
+// Exact top-k over the document score table, and the cross-rank merge.
 //
-// Scores live in the table as order-preserving uint32 keys, so selection is four 8-bit radix
-// passes over one row per CTA: each pass histograms the next byte of the keys that still
-// match the prefix found so far and narrows the prefix to the bucket holding the k-th
-// largest key.  The winners are then gathered and sorted in shared memory.  HBM/L2 bound:
-// 5 reads of the row, nothing written but the k results.
+// Scores live in the table as order-preserving uint32 keys.  Selection is two levels of the
+// same kernel: every CTA sorts one slice of a row (composite 64-bit items: key high, inverted
+// column low, so equal scores order by ascending column) with a bitonic network in shared
+// memory and keeps the slice's best k; a second launch sorts the survivors of all slices of a
+// row and writes the result.  Rows are cut into slices so that even a handful of queries
+// (decode-time routing) spreads over the whole GPU.  One read of the table, k results written.
 #include "common.cuh"
 
 namespace msa {
 
-constexpr int kSelThreads = 256;
-constexpr int kSelWarps = kSelThreads / 32;
+constexpr int kSortThreads = 256;
 constexpr int kMaxK = 1024;
+constexpr int kMinSlice = 2048;   // items per CTA at level 1 (power of two)
+constexpr int kMaxSlice = 8192;   // 64 KiB of shared memory
 
-__global__ void __launch_bounds__(kSelThreads)
-topk_select_kernel(const uint32_t* __restrict__ keys, long long table_stride, int n_cols, int k,
-                   const int64_t* __restrict__ doc_ids_table, float* __restrict__ out_scores,
-                   int64_t* __restrict__ out_local, int64_t* __restrict__ out_global) {
-  __shared__ unsigned int s_hist[kSelWarps][256];
-  __shared__ unsigned int s_prefix, s_krem, s_count_gt, s_count_eq;
-  __shared__ unsigned int s_warp_eq[kSelWarps];
-  __shared__ unsigned long long s_win[kMaxK];
-  const uint32_t* row = keys + (long long)blockIdx.x * table_stride;
-  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-  const int k_eff = min(k, n_cols);
-
-  uint32_t prefix = 0, mask = 0;
-  unsigned int k_rem = k_eff;
-  for (int shift = 24; shift >= 0; shift -= 8) {
-    for (int i = tid; i < kSelWarps * 256; i += kSelThreads) (&s_hist[0][0])[i] = 0;
-    __syncthreads();
-    for (int i = tid; i < n_cols; i += kSelThreads) {
-      const uint32_t key = row[i];
-      if ((key & mask) == prefix) atomicAdd(&s_hist[warp][(key >> shift) & 0xffu], 1u);
-    }
-    __syncthreads();
-    // thread b owns bucket b: suffix counts via a shared-memory scan from the top bucket down
-    unsigned int mine = 0;
-    for (int w = 0; w < kSelWarps; ++w) mine += s_hist[w][tid];
-    __syncthreads();
-    s_hist[0][tid] = mine;
-    __syncthreads();
-    for (int d = 1; d < 256; d <<= 1) {  // inclusive suffix sum
-      unsigned int other = (tid + d < 256) ? s_hist[0][tid + d] : 0u;
-      __syncthreads();
-      s_hist[0][tid] += other;
-      __syncthreads();
-    }
-    const unsigned int ge = s_hist[0][tid], gt = ge - mine;
-    if (gt < k_rem && k_rem <= ge) {  // exactly one bucket satisfies this
-      s_prefix = prefix | ((uint32_t)tid << shift);
-      s_krem = k_rem - gt;
-    }
-    __syncthreads();
-    prefix = s_prefix;
-    k_rem = s_krem;
-    mask |= 0xffu << shift;
-    __syncthreads();
-  }
-  // prefix is now the k-th largest key; take everything above it and the first k_rem equal to it
-  if (tid == 0) { s_count_gt = 0; s_count_eq = 0; }
-  __syncthreads();
-  const unsigned int n_gt = k_eff - k_rem;
-  for (int base = 0; base < n_cols; base += kSelThreads) {
-    const int i = base + tid;
-    const uint32_t key = i < n_cols ? row[i] : 0u;
-    const bool gt = i < n_cols && key > prefix;
-    const bool eq = i < n_cols && key == prefix;
-    if (gt) {
-      const unsigned int slot = atomicAdd(&s_count_gt, 1u);
-      s_win[slot] = ((unsigned long long)key << 32) | (0xffffffffu - (uint32_t)i);
-    }
-    const unsigned int bal = __ballot_sync(0xffffffffu, eq);
-    if (lane == 0) s_warp_eq[warp] = __popc(bal);
-    __syncthreads();
-    unsigned int before = s_count_eq;
-    for (int w = 0; w < warp; ++w) before += s_warp_eq[w];
-    const unsigned int ord = before + __popc(bal & ((1u << lane) - 1u));
-    if (eq && ord < k_rem) s_win[n_gt + ord] = ((unsigned long long)key << 32) | (0xffffffffu - (uint32_t)i);
-    __syncthreads();
-    if (tid == 0) {
-      unsigned int tot = 0;
-      for (int w = 0; w < kSelWarps; ++w) tot += s_warp_eq[w];
-      s_count_eq += tot;
-    }
-    __syncthreads();
-  }
-  // bitonic sort, descending, of the winners (key high, inverted column low => ties by column asc)
-  int n2 = 1;
-  while (n2 < k_eff) n2 <<= 1;
-  for (int i = k_eff + tid; i < n2; i += kSelThreads) s_win[i] = 0ull;
-  __syncthreads();
+__device__ __forceinline__ void bitonic_sort_desc(unsigned long long* s, int n2) {
   for (int size = 2; size <= n2; size <<= 1)
     for (int stride = size >> 1; stride > 0; stride >>= 1) {
-      for (int i = tid; i < n2; i += kSelThreads) {
+      for (int i = threadIdx.x; i < n2; i += kSortThreads) {
         const int j = i ^ stride;
         if (j > i) {
           const bool desc = (i & size) == 0;
-          const unsigned long long a = s_win[i], b = s_win[j];
-          if (desc ? a < b : a > b) { s_win[i] = b; s_win[j] = a; }
+          const unsigned long long a = s[i], b = s[j];
+          if (desc ? a < b : a > b) { s[i] = b; s[j] = a; }
         }
       }
       __syncthreads();
     }
-  for (int i = tid; i < k_eff; i += kSelThreads) {
-    const unsigned long long w = s_win[i];
-    const long long col = 0xffffffffu - (uint32_t)(w & 0xffffffffull);
-    const long long o = (long long)blockIdx.x * k_eff + i;
-    out_scores[o] = key_to_float((uint32_t)(w >> 32));
-    out_local[o] = col;
-    if (out_global) out_global[o] = doc_ids_table ? doc_ids_table[col] : col;
+}
+
+// grid (n_slices, n_rows).  FROM_KEYS: items come from a slice of the key table; otherwise from
+// `cand` (n_in composite items per row).  The best `keep` items go to `cand_out` (level 1) or,
+// when cand_out is null, to the result arrays (final level).
+template <bool FROM_KEYS>
+__global__ void __launch_bounds__(kSortThreads)
+sort_topk_kernel(const uint32_t* __restrict__ keys, long long table_stride, int n_cols, int slice,
+                 const unsigned long long* __restrict__ cand, int n_in, int n2, int keep,
+                 unsigned long long* __restrict__ cand_out, const int64_t* __restrict__ doc_ids_table,
+                 float* __restrict__ out_scores, int64_t* __restrict__ out_local, int64_t* __restrict__ out_global) {
+  extern __shared__ unsigned long long s_items[];
+  const int row = blockIdx.y, sl = blockIdx.x;
+  if (FROM_KEYS) {
+    const int c0 = sl * slice;
+    const uint32_t* src = keys + (long long)row * table_stride;
+    for (int i = threadIdx.x; i < n2; i += kSortThreads) {
+      const int c = c0 + i;
+      s_items[i] = (i < slice && c < n_cols) ? (((unsigned long long)src[c] << 32) | (0xffffffffu - (uint32_t)c)) : 0ull;
+    }
+  } else {
+    const unsigned long long* src = cand + (long long)row * n_in;
+    for (int i = threadIdx.x; i < n2; i += kSortThreads) s_items[i] = i < n_in ? src[i] : 0ull;
   }
+  __syncthreads();
+  bitonic_sort_desc(s_items, n2);
+  if (cand_out) {
+    unsigned long long* dst = cand_out + ((long long)row * gridDim.x + sl) * keep;
+    for (int i = threadIdx.x; i < keep; i += kSortThreads) dst[i] = s_items[i];
+  } else {
+    for (int i = threadIdx.x; i < keep; i += kSortThreads) {
+      const unsigned long long w = s_items[i];
+      const long long col = 0xffffffffu - (uint32_t)(w & 0xffffffffull);
+      const long long o = (long long)row * keep + i;
+      out_scores[o] = key_to_float((uint32_t)(w >> 32));
+      out_local[o] = col;
+      if (out_global) out_global[o] = doc_ids_table ? doc_ids_table[col] : col;
+    }
+  }
+}
+
+// Small k (<= kSelectMaxK): no sort.  Each warp extracts the k largest items of its eighth of the
+// slice by k rounds of a warp arg-max (shuffles only, no CTA barrier); warp 0 then extracts the
+// final k from the 8*k survivors.  Output order is descending by construction.
+constexpr int kSelectMaxK = 64;
+
+__device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, v, o);
+    v = other > v ? other : v;
+  }
+  return v;
+}
+
+// k rounds over items[0..n) (shared memory, owned by this warp): writes the k largest, in order.
+__device__ __forceinline__ void warp_extract_topk(unsigned long long* items, int n, int k, unsigned long long* out) {
+  const int lane = threadIdx.x & 31;
+  for (int r = 0; r < k; ++r) {
+    unsigned long long best = 0ull;
+    int best_i = -1;
+    for (int i = lane; i < n; i += 32) {
+      const unsigned long long v = items[i];
+      if (v > best) { best = v; best_i = i; }
+    }
+    const unsigned long long top = warp_max_u64(best);
+    if (top != 0ull && best == top) items[best_i] = 0ull;   // composite items are unique: one lane matches
+    if (lane == 0) out[r] = top;
+    __syncwarp();
+  }
+}
+
+template <bool FROM_KEYS>
+__global__ void __launch_bounds__(kSortThreads)
+select_topk_kernel(const uint32_t* __restrict__ keys, long long table_stride, int n_cols, int slice,
+                   const unsigned long long* __restrict__ cand, int n_in, int n2, int keep,
+                   unsigned long long* __restrict__ cand_out, const int64_t* __restrict__ doc_ids_table,
+                   float* __restrict__ out_scores, int64_t* __restrict__ out_local, int64_t* __restrict__ out_global) {
+  extern __shared__ unsigned long long s_items[];
+  __shared__ unsigned long long s_win[(kSortThreads / 32) * kSelectMaxK];
+  __shared__ unsigned long long s_final[kSelectMaxK];
+  const int row = blockIdx.y, sl = blockIdx.x, warp = threadIdx.x >> 5, n_warps = kSortThreads / 32;
+  if (FROM_KEYS) {
+    const int c0 = sl * slice;
+    const uint32_t* src = keys + (long long)row * table_stride;
+    for (int i = threadIdx.x; i < n2; i += kSortThreads) {
+      const int c = c0 + i;
+      s_items[i] = (i < slice && c < n_cols) ? (((unsigned long long)src[c] << 32) | (0xffffffffu - (uint32_t)c)) : 0ull;
+    }
+  } else {
+    const unsigned long long* src = cand + (long long)row * n_in;
+    for (int i = threadIdx.x; i < n2; i += kSortThreads) s_items[i] = i < n_in ? src[i] : 0ull;
+  }
+  __syncthreads();
+  const int seg = (n2 + n_warps - 1) / n_warps;
+  const int lo = min(n2, warp * seg), hi = min(n2, lo + seg);
+  warp_extract_topk(s_items + lo, hi - lo, keep, s_win + warp * keep);
+  __syncthreads();
+  if (warp == 0) warp_extract_topk(s_win, n_warps * keep, keep, s_final);
+  __syncthreads();
+  if (cand_out) {
+    unsigned long long* dst = cand_out + ((long long)row * gridDim.x + sl) * keep;
+    for (int i = threadIdx.x; i < keep; i += kSortThreads) dst[i] = s_final[i];
+  } else {
+    for (int i = threadIdx.x; i < keep; i += kSortThreads) {
+      const unsigned long long w = s_final[i];
+      const long long col = 0xffffffffu - (uint32_t)(w & 0xffffffffull);
+      const long long o = (long long)row * keep + i;
+      out_scores[o] = key_to_float((uint32_t)(w >> 32));
+      out_local[o] = col;
+      if (out_global) out_global[o] = doc_ids_table ? doc_ids_table[col] : col;
+    }
+  }
+}
+
+static inline int pow2_ceil(int v) { int p = 1; while (p < v) p <<= 1; return p; }
+
+// Slice length and slice count for a row of n_cols with k winners: slices are at least
+// kMinSlice (and 2k) long, and few enough that all survivors fit one final sort.
+static void topk_plan(int n_cols, int k, int* slice, int* n_slices) {
+  const int k_eff = k < n_cols ? k : n_cols;
+  int sl = pow2_ceil(2 * k_eff) > kMinSlice ? pow2_ceil(2 * k_eff) : kMinSlice;
+  while ((long long)((n_cols + sl - 1) / sl) * k_eff > kMaxSlice && sl < kMaxSlice) sl <<= 1;
+  *slice = sl;
+  *n_slices = (n_cols + sl - 1) / sl;
 }
 
 // One CTA per query: rank every candidate by counting the candidates that beat it.
@@ -151,17 +193,56 @@ topk_merge_kernel(const float* __restrict__ cand_scores, const int64_t* __restri
 
 using namespace msa;
 
+extern "C" int64_t msa_topk_workspace_bytes(int32_t n_seq, int32_t n_cols, int32_t k) {
+  if (n_seq <= 0 || n_cols <= 0 || k <= 0) return 0;
+  int slice, n_slices;
+  topk_plan(n_cols, k, &slice, &n_slices);
+  if (n_slices <= 1) return 0;
+  return (int64_t)n_seq * n_slices * (k < n_cols ? k : n_cols) * (int64_t)sizeof(unsigned long long);
+}
+
 extern "C" int msa_topk_select(const uint32_t* score_keys, int64_t table_stride, int32_t n_seq, int32_t n_cols,
                                int32_t k, const int64_t* doc_ids_table, float* out_scores, int64_t* out_local_ids,
-                               int64_t* out_global_ids, void* stream) {
+                               int64_t* out_global_ids, void* workspace, int64_t workspace_bytes, void* stream) {
   MSA_REQUIRE(score_keys && out_scores && out_local_ids, "topk_select: null pointer");
   MSA_REQUIRE(n_seq >= 0 && n_cols >= 1 && k >= 1, "topk_select: bad sizes (n_cols=%d k=%d)", n_cols, k);
   MSA_REQUIRE(k <= kMaxK, "topk_select: k=%d exceeds the supported maximum %d", k, kMaxK);
   MSA_REQUIRE(table_stride >= n_cols, "topk_select: table_stride < n_cols");
+  MSA_REQUIRE(n_seq <= 65535, "topk_select: at most 65535 rows per call");
   if (n_seq == 0) return MSA_OK;
-  topk_select_kernel<<<n_seq, kSelThreads, 0, (cudaStream_t)stream>>>(
-      score_keys, table_stride, n_cols, k, doc_ids_table, out_scores, out_local_ids, out_global_ids);
-  MSA_LAUNCH_OK("topk_select_kernel");
+  const int k_eff = k < n_cols ? k : n_cols;
+  int slice, n_slices;
+  topk_plan(n_cols, k, &slice, &n_slices);
+  MSA_REQUIRE((long long)n_slices * k_eff <= kMaxSlice, "topk_select: n_cols=%d with k=%d is too large for two levels",
+              n_cols, k);
+  cudaStream_t st = (cudaStream_t)stream;
+  static thread_local bool configured = false;
+  if (!configured) {
+    MSA_CUDA_OK(cudaFuncSetAttribute(sort_topk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSlice * 8));
+    MSA_CUDA_OK(cudaFuncSetAttribute(sort_topk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSlice * 8));
+    MSA_CUDA_OK(cudaFuncSetAttribute(select_topk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSlice * 8));
+    MSA_CUDA_OK(cudaFuncSetAttribute(select_topk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSlice * 8));
+    configured = true;
+  }
+  const bool small_k = k_eff <= kSelectMaxK;
+  if (n_slices == 1) {
+    const int n2 = pow2_ceil(n_cols);
+    (small_k ? select_topk_kernel<true> : sort_topk_kernel<true>)<<<dim3(1, n_seq), kSortThreads, (size_t)n2 * 8, st>>>(
+        score_keys, table_stride, n_cols, n2, nullptr, 0, n2, k_eff, nullptr, doc_ids_table, out_scores, out_local_ids,
+        out_global_ids);
+    MSA_LAUNCH_OK("sort_topk_kernel");
+    return MSA_OK;
+  }
+  MSA_REQUIRE(workspace && workspace_bytes >= msa_topk_workspace_bytes(n_seq, n_cols, k),
+              "topk_select: workspace of %lld bytes needed", (long long)msa_topk_workspace_bytes(n_seq, n_cols, k));
+  unsigned long long* cand = (unsigned long long*)workspace;
+  (small_k ? select_topk_kernel<true> : sort_topk_kernel<true>)<<<dim3(n_slices, n_seq), kSortThreads, (size_t)slice * 8, st>>>(
+      score_keys, table_stride, n_cols, slice, nullptr, 0, slice, k_eff, cand, nullptr, nullptr, nullptr, nullptr);
+  MSA_LAUNCH_OK("sort_topk_kernel (slices)");
+  const int n_in = n_slices * k_eff, n2 = pow2_ceil(n_in);
+  (small_k ? select_topk_kernel<false> : sort_topk_kernel<false>)<<<dim3(1, n_seq), kSortThreads, (size_t)n2 * 8, st>>>(
+      nullptr, 0, 0, 0, cand, n_in, n2, k_eff, nullptr, doc_ids_table, out_scores, out_local_ids, out_global_ids);
+  MSA_LAUNCH_OK("sort_topk_kernel (final)");
   return MSA_OK;
 }
 

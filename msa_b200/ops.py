@@ -151,7 +151,8 @@ def route_table_reset(keys: torch.Tensor, n_docs: int, min_val: float, status: O
                                           A.ptr(status), A.stream_ptr(keys.device)), "msa_route_table_reset")
 
 
-def topk_select(keys: torch.Tensor, k: int, doc_ids_table: Optional[torch.Tensor] = None, n_cols: Optional[int] = None):
+def topk_select(keys: torch.Tensor, k: int, doc_ids_table: Optional[torch.Tensor] = None, n_cols: Optional[int] = None,
+                workspace: Optional[torch.Tensor] = None):
     """Exact top-k of every row of a key table.  Returns ``(scores f32, local_ids i64, global_ids i64)``,
     each ``[n_seq, min(k, n_cols)]``, sorted by descending score (ties: ascending column)."""
     A.need_cuda(keys, doc_ids_table)
@@ -162,8 +163,13 @@ def topk_select(keys: torch.Tensor, k: int, doc_ids_table: Optional[torch.Tensor
     scores = torch.empty((n_seq, k_eff), dtype=torch.float32, device=dev)
     local = torch.empty((n_seq, k_eff), dtype=torch.int64, device=dev)
     glob = torch.empty((n_seq, k_eff), dtype=torch.int64, device=dev)
+    need = int(A.lib().msa_topk_workspace_bytes(n_seq, n_cols, k))
+    if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
+        workspace = torch.empty(need // 8, dtype=torch.int64, device=dev)
     A.check(A.lib().msa_topk_select(A.ptr(keys), keys.stride(0), n_seq, n_cols, k, A.ptr(doc_ids_table),
-                                    A.ptr(scores), A.ptr(local), A.ptr(glob), A.stream_ptr(dev)), "msa_topk_select")
+                                    A.ptr(scores), A.ptr(local), A.ptr(glob), A.ptr(workspace),
+                                    workspace.numel() * workspace.element_size() if workspace is not None else 0,
+                                    A.stream_ptr(dev)), "msa_topk_select")
     return scores, local, glob
 
 
@@ -223,8 +229,13 @@ def gather_run(plan: torch.Tensor, dtype: torch.dtype, n_kv_heads: int, head_dim
 # ---------------------------------------------------------------------------------------
 
 def decode_splits(n_seq: int, n_kv_heads: int, max_len: int, n_sm: int = 148) -> int:
-    """Enough KV splits to put about two CTAs on every SM, each with at least 256 keys."""
-    want = max(1, (2 * n_sm + n_seq * n_kv_heads - 1) // max(1, n_seq * n_kv_heads))
+    """KV splits for the decode kernel: one CTA per (sequence, kv head) already fills the GPU when
+    there are at least n_sm of them (measured best on B200); smaller batches are split so that
+    about two CTAs land on every SM, each keeping at least 256 keys."""
+    ctas = max(1, n_seq * n_kv_heads)
+    if ctas >= n_sm:
+        return 1
+    want = (2 * n_sm + ctas - 1) // ctas
     return max(1, min(want, max(1, max_len // 256)))
 
 

@@ -115,7 +115,8 @@ def test_doc_query_single_rank_vs_oracle(dtype):
 
 def test_empty_shard_and_all_masked_queries():
     """A shard without documents and a batch whose queries have no routing token."""
-    svc = _service([], [], torch.zeros(0, 8, 128), torch.zeros(0, 8, 128), torch.zeros(0, 8, 128), 4, torch.bfloat16)
+    svc = _service([], [], torch.zeros(0, 8, 128, dtype=torch.bfloat16), torch.zeros(0, 8, 128, dtype=torch.bfloat16),
+                   torch.zeros(0, 8, 128, dtype=torch.bfloat16), 4, torch.bfloat16)
     q = torch.randn(2, 32, 16, 128).to(torch.bfloat16).to(DEV)
     mask = torch.zeros(2, 16, dtype=torch.bool, device=DEV)
     fk, fv, fs, n_sel, wg = svc.doc_query(q, mask, 0)

@@ -34,7 +34,7 @@ def test_argument_errors_are_reported_before_any_launch():
     lib = A.lib()
     assert lib.msa_pool_chunks(None, 1, 0, 0, None, None, None, 1, 8, 128, None, 0, 0, 0, None) == -1
     assert b"null pointer" in lib.msa_last_error()
-    assert lib.msa_topk_select(1, 8, 1, 4, 5000, None, 1, 1, None, None) == -1
+    assert lib.msa_topk_select(1, 8, 1, 4, 5000, None, 1, 1, None, None, 0, None) == -1
     assert b"exceeds the supported maximum" in lib.msa_last_error()
     with pytest.raises(A.MsaError, match="CUDA tensors"):
         from msa_b200 import ops
