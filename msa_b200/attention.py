@@ -1,0 +1,309 @@
+"""``MemorySparseAttention``: the B200 counterpart of the reference's attention layer for inference.
+
+Mirrors ``src/msa/memory_sparse_attention.py:20-405`` (constructor, ``set_memory_client``,
+``forward`` dispatch on the stage recorded in the cache, the three inference branches).  Same
+constructor arguments, same module / parameter names (so a reference checkpoint's state dict
+loads), same cache protocol (``cache_kwargs`` / ``meta`` / ``record_kwargs`` / ``update`` /
+``update_router_kcache``).
+
+What runs where:
+  * stage 1: projections, norms, RoPE and the intra-document attention stay PyTorch / library
+    calls as in the reference; chunk bookkeeping, chunk-mean pooling of K, V, K_r and the L2
+    normalisation of K_r run on this package's kernels;
+  * stage 2: routing, merge and fetch happen inside ``memory_client.doc_query`` (this package's
+    ``MSAService``); the context assembly and the prefill attention follow the reference with
+    library calls, and the compact cache is allocated with room to append in place;
+  * decode: this package's flash-decode kernel, in-place append, no ``torch.cat`` / ``repeat_kv``.
+The training forward (``_forward``) is out of scope and raises.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from transformers.models.qwen3.modeling_qwen3 import Qwen3Attention, apply_rotary_pos_emb
+
+from . import _cabi as A
+from . import ops
+
+try:  # third-party, exactly as the reference uses it (src/msa/memory_sparse_attention.py:13-17)
+    from flash_attn import flash_attn_varlen_func as _flash_varlen
+except Exception:  # pragma: no cover - depends on the image
+    _flash_varlen = None
+
+
+def varlen_attention(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal=True):
+    """Variable-length causal attention with bottom-right aligned masking: ``flash_attn_varlen_func``
+    when it can run on these tensors, else an SDPA loop over the sequences.  Library call in both
+    cases, as in the reference (this piece is not one of this package's kernels)."""
+    if _flash_varlen is not None and q.is_cuda and q.dtype in (torch.float16, torch.bfloat16):
+        return _flash_varlen(q, k, v, cu_seqlens_q=cu_seqlens_q, cu_seqlens_k=cu_seqlens_k,
+                             max_seqlen_q=max_seqlen_q, max_seqlen_k=max_seqlen_k, dropout_p=0.0, causal=causal)
+    outs = []
+    cq, ck = cu_seqlens_q.tolist(), cu_seqlens_k.tolist()
+    for i in range(len(cq) - 1):
+        qi = q[cq[i]:cq[i + 1]].transpose(0, 1)
+        ki = k[ck[i]:ck[i + 1]].transpose(0, 1)
+        vi = v[ck[i]:ck[i + 1]].transpose(0, 1)
+        if ki.shape[0] != qi.shape[0]:
+            rep = qi.shape[0] // ki.shape[0]
+            ki, vi = ki.repeat_interleave(rep, 0), vi.repeat_interleave(rep, 0)
+        lq, lk = qi.shape[1], ki.shape[1]
+        mask = torch.ones(lq, lk, dtype=torch.bool, device=q.device).tril(diagonal=lk - lq) if causal else None
+        outs.append(F.scaled_dot_product_attention(qi, ki, vi, attn_mask=mask).transpose(0, 1))
+    return torch.cat(outs, 0) if outs else q.new_zeros(q.shape)
+
+
+class MemorySparseAttention(Qwen3Attention):
+    #: extra cache positions reserved for tokens appended during decode
+    decode_reserve = 512
+
+    def __init__(self, config, layer_idx: int):
+        super().__init__(config=config, layer_idx=layer_idx)
+        A.lib()  # no kernels, no layer
+        mc = config.msa_config
+        self.layer_idx = layer_idx
+        self.top_k_docs = mc.top_k_docs
+        self.pooling_kernel_size = mc.pooling_kernel_size
+        ridx = mc.router_layer_idx
+        self.router_layer_idx = list(range(config.num_hidden_layers)) if ridx == "all" else [int(i) for i in ridx.split(",")]
+        self.is_router_layer = self.layer_idx in self.router_layer_idx
+        self.head_reduce_method = mc.head_reduce_method
+        self.query_reduce_method = mc.query_reduce_method
+        self.chunk_reduce_method = mc.chunk_reduce_method
+        self.decouple_pooling_mode = mc.decouple_pooling_mode
+        self.aux_loss_method = mc.aux_loss_method
+        self.decouple_router = mc.decouple_router
+        if self.is_router_layer and self.decouple_router:
+            self.router_k_proj = nn.Sequential(
+                nn.Linear(config.hidden_size, config.num_key_value_heads * self.head_dim, bias=False))
+            self.router_q_proj = nn.Sequential(
+                nn.Linear(config.hidden_size, config.num_attention_heads * self.head_dim, bias=False))
+        self.num_kv_heads = config.num_key_value_heads
+        self.template_prefix_kcache = None
+        self.template_prefix_vcache = None
+        self.memory_client = None
+
+    def set_memory_client(self, memory_client):
+        self.memory_client = memory_client
+
+    def forward(self, hidden_states, doc_ids, attention_mask=None, position_embeddings=None, past_key_value=None,
+                **kwargs):
+        if self.training:
+            raise NotImplementedError("msa_b200.MemorySparseAttention implements the inference branches only")
+        if past_key_value is None:
+            raise Exception("error!")  # the reference's message (memory_sparse_attention.py:97)
+        return self.forward_with_kvcache_for_batch_parrallel(hidden_states, doc_ids, attention_mask,
+                                                             position_embeddings, past_key_value, **kwargs)
+
+    # ------------------------------------------------------------------------------------
+    def forward_with_kvcache_for_batch_parrallel(self, hidden_states, doc_ids, attention_mask=None,
+                                                 position_embeddings=None, past_key_value=None, **kwargs):
+        bsz, q_len, _ = hidden_states.shape
+        hidden_shape = (bsz, q_len, -1, self.head_dim)
+        query_states = self.q_norm(self.q_proj(hidden_states).view(hidden_shape)).transpose(1, 2)
+        key_states = self.k_norm(self.k_proj(hidden_states).view(hidden_shape)).transpose(1, 2)
+        value_states = self.v_proj(hidden_states).view(hidden_shape).transpose(1, 2)
+        cos, sin = position_embeddings
+        query_states, key_states = apply_rotary_pos_emb(query_states, key_states, cos, sin)
+        stage = past_key_value.cache_kwargs[self.layer_idx]["stage"]
+        if stage == "prefill_stage1":
+            return self._stage1(hidden_states, doc_ids, attention_mask, past_key_value, query_states, key_states,
+                                value_states)
+        if stage == "prefill_stage2":
+            return self._stage2(hidden_states, doc_ids, attention_mask, past_key_value, query_states, key_states,
+                                value_states)
+        return self._decode(attention_mask, past_key_value, query_states, key_states, value_states)
+
+    # ------------------------------------------------------------------------------------ stage 1
+    def _bookkeeping(self, doc_ids, attention_mask, cache):
+        """Chunk tables of this block; computed once and shared by every layer through cache.meta."""
+        key = (doc_ids.data_ptr(), tuple(doc_ids.shape))
+        hit = cache.meta.get("_msa_b200_bookkeeping")
+        if hit is None or hit[0] != key:
+            tok, off, pooled = ops.chunk_bookkeeping(doc_ids, attention_mask, self.pooling_kernel_size)
+            hit = (key, tok, off, pooled)
+            cache.meta["_msa_b200_bookkeeping"] = hit
+        return hit[1], hit[2], hit[3]
+
+    def _stage1(self, hidden_states, doc_ids, attention_mask, cache, query_states, key_states, value_states):
+        """src/msa/memory_sparse_attention.py:137-243."""
+        bsz, q_len, _ = hidden_states.shape
+        device, dtype = hidden_states.device, hidden_states.dtype
+        hidden_shape = (bsz, q_len, -1, self.head_dim)
+        doc_token_mask = (doc_ids > 0) & (attention_mask == 1)
+        pooled_k = pooled_v = pooled_rk = pooled_doc_ids = None
+        if self.is_router_layer:
+            if bsz != 1:
+                raise A.MsaError("stage 1 pools one block per call (the reference's worker uses batch size 1)")
+            tok, off, pooled_doc_ids = self._bookkeeping(doc_ids, attention_mask, cache)
+            pooled_k = ops.pool_chunks(key_states, off, tok, head_major_out=True)
+            pooled_v = ops.pool_chunks(value_states, off, tok, head_major_out=True)
+            cosine = self.aux_loss_method == "INFONCE"
+            if self.decouple_router:
+                r_k_raw = self.router_k_proj(hidden_states).view(hidden_shape).transpose(1, 2)
+                pooled_rk = ops.pool_chunks(r_k_raw, off, tok, l2_normalize=cosine, head_major_out=True)
+            elif cosine:
+                pooled_rk = F.normalize(pooled_k, p=2, dim=-1)
+        n_template = int((doc_ids == -2).sum())
+        kw = {"template_prefix_kcache": key_states[:, :, :n_template],
+              "template_prefix_vcache": value_states[:, :, :n_template]}
+        if self.is_router_layer:
+            pooled_k, pooled_v = cache.update(pooled_k, pooled_v, self.layer_idx)
+            kw.update({"doc_id_bias": doc_ids.shape[1], "pooled_doc_ids": pooled_doc_ids,
+                       "prefill_stage1_kvcache_size": pooled_k.shape[2]})
+            if pooled_rk is not None:
+                cache.update_router_kcache(pooled_rk, self.layer_idx)
+        cache.record_kwargs(self.layer_idx, kw)
+
+        # intra-document and template causal attention: library calls, as in the reference (:216-241)
+        n_heads = self.config.num_attention_heads
+        attn_output = torch.zeros((bsz, q_len, n_heads * self.head_dim), device=device, dtype=dtype)
+        q_t, k_t, v_t = query_states.transpose(1, 2), key_states.transpose(1, 2), value_states.transpose(1, 2)
+        if doc_token_mask.any():
+            idx = torch.nonzero(doc_token_mask, as_tuple=False)
+            gid = idx[:, 0] * (int(doc_ids.max().item()) + 1) + doc_ids[doc_token_mask]
+            _, counts = torch.unique_consecutive(gid, return_counts=True)
+            cu = F.pad(torch.cumsum(counts, 0, dtype=torch.int32), (1, 0))
+            out = varlen_attention(q_t[doc_token_mask], k_t[doc_token_mask], v_t[doc_token_mask], cu, cu,
+                                   int(counts.max()), int(counts.max()))
+            attn_output[doc_token_mask] = out.reshape(-1, n_heads * self.head_dim)
+        template_mask = (doc_ids == -2) & (attention_mask == 1)
+        if template_mask.any():
+            counts = template_mask.sum(dim=1)
+            cu = F.pad(torch.cumsum(counts, 0, dtype=torch.int32), (1, 0))
+            out = varlen_attention(q_t[template_mask], k_t[template_mask], v_t[template_mask], cu, cu,
+                                   int(counts.max()), int(counts.max()))
+            attn_output[template_mask] = out.reshape(-1, n_heads * self.head_dim)
+        return self.o_proj(attn_output), None
+
+    # ------------------------------------------------------------------------------------ stage 2
+    def _stage2(self, hidden_states, doc_ids, attention_mask, cache, query_states, key_states, value_states):
+        """src/msa/memory_sparse_attention.py:245-359."""
+        bsz, q_len, _ = hidden_states.shape
+        device, dtype = hidden_states.device, hidden_states.dtype
+        hidden_shape = (bsz, q_len, -1, self.head_dim)
+        n_heads, n_kv, d = self.config.num_attention_heads, self.config.num_key_value_heads, self.head_dim
+        cache_kwargs = cache.cache_kwargs[self.layer_idx]
+        if self.memory_client is not None:
+            if self.template_prefix_kcache is None:
+                tk, tv = self.memory_client.get_template_prefix_kvcaches(self.layer_idx)
+                self.template_prefix_kcache, self.template_prefix_vcache = tk.to(device), tv.to(device)
+            template_k, template_v = self.template_prefix_kcache, self.template_prefix_vcache
+        else:
+            template_k = cache_kwargs["template_prefix_kcache"].to(device)
+            template_v = cache_kwargs["template_prefix_vcache"].to(device)
+
+        final_k = final_v = None
+        if self.is_router_layer:
+            routing_q = (self.router_q_proj(hidden_states).view(hidden_shape).transpose(1, 2)
+                         if self.decouple_router else query_states)
+            if self.aux_loss_method == "INFONCE":
+                routing_q = F.normalize(routing_q, p=2, dim=-1)
+            query_mask = (doc_ids == 0) & (attention_mask == 1)
+            final_k, final_v, final_scores, n_sel, final_ids = self.memory_client.doc_query(routing_q, query_mask,
+                                                                                          self.layer_idx)
+            if cache.meta.get("require_recall_topk", False):
+                ids, scores = final_ids.cpu().tolist(), final_scores.cpu().tolist()
+                cache_kwargs["recall_topk"] = [{"topk_doc_ids": ids[i], "score": scores[i]} for i in range(bsz)]
+        else:
+            n_sel = torch.zeros(bsz, dtype=torch.long, device=device)
+
+        num_q = attention_mask.sum(dim=1)
+        t_len = template_k.shape[2]
+        kv_lengths = t_len + n_sel + num_q
+        cu_q = F.pad(num_q.cumsum(0, dtype=torch.int32), (1, 0))
+        cu_kv = F.pad(kv_lengths.cumsum(0, dtype=torch.int32), (1, 0))
+        total_kv = int(cu_kv[-1].item())
+        valid_q = attention_mask == 1
+        q_final = query_states.permute(0, 2, 1, 3)[valid_q]
+        k_flat = torch.empty((n_kv, total_kv, d), device=device, dtype=dtype)
+        v_flat = torch.empty((n_kv, total_kv, d), device=device, dtype=dtype)
+        start = cu_kv[:-1].long()
+        t_idx = (torch.arange(t_len, device=device).unsqueeze(0) + start.unsqueeze(1)).flatten()
+        k_flat[:, t_idx] = template_k.expand(bsz, -1, -1, -1).permute(1, 0, 2, 3).reshape(n_kv, -1, d)
+        v_flat[:, t_idx] = template_v.expand(bsz, -1, -1, -1).permute(1, 0, 2, 3).reshape(n_kv, -1, d)
+        if final_k is not None and final_k.shape[1] > 0:
+            owner = torch.arange(bsz, device=device).repeat_interleave(n_sel)
+            first = F.pad(n_sel.cumsum(0), (1, 0))[:-1]
+            rank = torch.arange(owner.numel(), device=device) - first[owner]
+            dest = start[owner] + t_len + rank
+            k_flat[:, dest] = final_k
+            v_flat[:, dest] = final_v.to(device)
+        q_owner = torch.arange(bsz, device=device).repeat_interleave(num_q)
+        q_rank = (torch.cumsum(valid_q.int(), dim=1) - 1)[valid_q]
+        q_dest = (start + t_len + n_sel)[q_owner] + q_rank
+        k_flat[:, q_dest] = key_states.permute(1, 0, 2, 3).reshape(n_kv, -1, d)[:, valid_q.flatten()]
+        v_flat[:, q_dest] = value_states.permute(1, 0, 2, 3).reshape(n_kv, -1, d)[:, valid_q.flatten()]
+
+        out_flat = varlen_attention(q_final, k_flat.transpose(0, 1), v_flat.transpose(0, 1), cu_q, cu_kv,
+                                    int(num_q.max()), int(kv_lengths.max())).reshape(-1, n_heads * d)
+        attn_output = torch.zeros((bsz, q_len, n_heads * d), device=device, dtype=dtype)
+        attn_output[valid_q] = out_flat
+
+        # compact cache: left-padded like the reference (:344-356) plus room to append in place
+        max_kv = int(kv_lengths.max())
+        cap = max_kv + int(cache.meta.get("max_generate_tokens", self.decode_reserve))
+        k_store = torch.zeros((bsz, n_kv, cap, d), dtype=dtype, device=device)
+        v_store = torch.zeros((bsz, n_kv, cap, d), dtype=dtype, device=device)
+        left_pad_mask = torch.arange(max_kv, device=device).unsqueeze(0) >= (max_kv - kv_lengths.unsqueeze(1))
+        k_store[:, :, :max_kv].permute(0, 2, 1, 3)[left_pad_mask] = k_flat.permute(1, 0, 2)
+        v_store[:, :, :max_kv].permute(0, 2, 1, 3)[left_pad_mask] = v_flat.permute(1, 0, 2)
+        cache_kwargs.update({
+            "compacked_key_cache": k_store[:, :, :max_kv], "compacked_value_cache": v_store[:, :, :max_kv],
+            "kv_lengths": kv_lengths, "attention_mask": left_pad_mask,
+            "_msa_b200_store": (k_store, v_store, (max_kv - kv_lengths).to(torch.int32), kv_lengths.to(torch.int32)),
+        })
+        cache.record_kwargs(self.layer_idx, cache_kwargs)
+        return self.o_proj(attn_output), None
+
+    # ------------------------------------------------------------------------------------ decode
+    def _decode(self, attention_mask, cache, query_states, key_states, value_states):
+        """src/msa/memory_sparse_attention.py:361-405."""
+        cache_kwargs = cache.cache_kwargs[self.layer_idx]
+        if "compacked_key_cache" not in cache_kwargs:
+            raise ValueError("compact KV cache not found: did prefill stage 2 run?")
+        bsz, n_heads, q_len, d = query_states.shape
+        store = cache_kwargs.get("_msa_b200_store")
+        cur_len = cache_kwargs["compacked_key_cache"].shape[2]
+        if store is None or cur_len + q_len > store[0].shape[2]:
+            store = self._adopt_cache(cache_kwargs, q_len)
+        k_store, v_store, kv_start, kv_len = store
+        if q_len == 1 and not cache.meta.get("qa_mode", False):
+            out = ops.sparse_decode_attn(query_states[:, :, 0], k_store, v_store, kv_len, key_states[:, :, 0],
+                                         value_states[:, :, 0], kv_start=kv_start)
+            attn_output = out.view(bsz, 1, n_heads * d)
+            kv_len = kv_len + 1
+            cache_kwargs["kv_lengths"] = cache_kwargs["kv_lengths"] + 1
+        else:
+            # multi-token segments of qa_mode are non-causal inside the segment (:375-380): library path
+            k_store[:, :, cur_len:cur_len + q_len] = key_states
+            v_store[:, :, cur_len:cur_len + q_len] = value_states
+            mask = cache_kwargs["attention_mask"]
+            mask = torch.cat([mask, attention_mask.to(mask.dtype)], dim=1)
+            cache_kwargs["attention_mask"] = mask
+            g = n_heads // k_store.shape[1]
+            kk = k_store[:, :, :cur_len + q_len].repeat_interleave(g, dim=1)
+            vv = v_store[:, :, :cur_len + q_len].repeat_interleave(g, dim=1)
+            attn_output = F.scaled_dot_product_attention(query_states, kk, vv, attn_mask=mask[:, None, None, :])
+            attn_output = attn_output.transpose(1, 2).reshape(bsz, q_len, -1)
+            kv_len = kv_len + q_len
+        cache_kwargs["compacked_key_cache"] = k_store[:, :, :cur_len + q_len]
+        cache_kwargs["compacked_value_cache"] = v_store[:, :, :cur_len + q_len]
+        cache_kwargs["_msa_b200_store"] = (k_store, v_store, kv_start, kv_len)
+        cache.record_kwargs(self.layer_idx, cache_kwargs)
+        return self.o_proj(attn_output), None
+
+    def _adopt_cache(self, cache_kwargs, q_len):
+        """Take over a compact cache that was built elsewhere (or has run out of room): copy it once
+        into storage with spare positions; from then on tokens are appended in place."""
+        ck, cv = cache_kwargs["compacked_key_cache"], cache_kwargs["compacked_value_cache"]
+        b, h, cur, d = ck.shape
+        cap = cur + max(q_len, self.decode_reserve)
+        k_store = torch.zeros((b, h, cap, d), dtype=ck.dtype, device=ck.device)
+        v_store = torch.zeros((b, h, cap, d), dtype=cv.dtype, device=cv.device)
+        k_store[:, :, :cur], v_store[:, :, :cur] = ck, cv
+        kv_len = cache_kwargs["kv_lengths"].to(torch.int32)
+        return k_store, v_store, (cur - kv_len).to(torch.int32), kv_len

@@ -199,6 +199,99 @@ def gen_layer(svc, msa_layer, MSAConfig):
     save("layer_decode", cache_k=ck, cache_v=cv, kv_lengths=kv_lengths, **steps)
 
 
+def gen_layer_e2e(svc, msa_layer, MSAConfig):
+    """One reference layer through the whole path: stage 1 (encode a block, pool), a reference
+    MSAService built from that stage-1 cache (one gloo rank), stage 2 (route, fetch, assemble,
+    prefill attention, compact cache) for a left-padded batch, then two decode steps.  The layer's
+    weights are stored so that the same module can be rebuilt without the reference."""
+    import torch.distributed as dist
+    from transformers.models.qwen3.modeling_qwen3 import Qwen3RotaryEmbedding
+    msa_layer.flash_attn_varlen_func = sdpa_varlen
+    torch.manual_seed(505)
+    hq, hkv, d, top_k, pool = 4, 2, 16, 2, 8
+    cfg = MSAConfig(
+        msa_config=dict(router_layer_idx="0", aux_loss=False, aux_loss_method="INFONCE", decouple_router=True,
+                        top_k_docs=top_k, pooling_kernel_size=pool, head_reduce_method="mean",
+                        query_reduce_method="max", chunk_reduce_method="max", decouple_pooling_mode="mean"),
+        hidden_size=hq * d, num_attention_heads=hq, num_key_value_heads=hkv, head_dim=d,
+        num_hidden_layers=1, intermediate_size=64, vocab_size=32, max_position_embeddings=512)
+    cfg._attn_implementation = "eager"
+    layer = msa_layer.MemorySparseAttention(cfg, 0).eval()
+    rope = Qwen3RotaryEmbedding(cfg)
+    arrays = {"w__" + k: v for k, v in layer.state_dict().items()}
+    arrays.update(hq=hq, hkv=hkv, d=d, top_k=top_k, pooling_kernel_size=pool,
+                  rope_theta=float(getattr(cfg, "rope_theta", 0.0) or cfg.rope_parameters["rope_theta"]))
+
+    # ---- stage 1: template head + 5 ragged documents
+    doc_lens = [20, 8, 13, 30, 5]
+    gids = [40, 41, 42, 43, 44]
+    ids, pos = [-2, -2, -2], [0, 1, 2]
+    for i, n in enumerate(doc_lens):
+        ids += [i + 1] * n
+        pos += list(range(n))
+    doc_ids, position_ids = torch.tensor([ids]), torch.tensor([pos])
+    t = doc_ids.shape[1]
+    hidden = torch.randn(1, t, hq * d)
+    am = torch.ones(1, t, dtype=torch.long)
+    cache1 = StubCache()
+    cache1.record_kwargs(0, {"stage": "prefill_stage1"})
+    with torch.no_grad():
+        out1, _ = layer(hidden, doc_ids, am, rope(hidden, position_ids), cache1)
+    kw = cache1.cache_kwargs[0]
+    arrays.update(s1_hidden=hidden, s1_doc_ids=doc_ids, s1_attention_mask=am, s1_position_ids=position_ids,
+                  s1_out=out1, s1_pooled_k=cache1.kv[0][0], s1_pooled_v=cache1.kv[0][1], s1_pooled_rk=cache1.rk[0],
+                  s1_pooled_doc_ids=kw["pooled_doc_ids"], s1_template_k=kw["template_prefix_kcache"],
+                  s1_template_v=kw["template_prefix_vcache"], doc_global_ids=gids)
+
+    # ---- the reference service over that bank (single rank)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29613")
+    dist.init_process_group("gloo", rank=0, world_size=1)
+    if not torch.cuda.is_available():
+        torch.cuda.current_stream = lambda *a, **k: SimpleNamespace(synchronize=lambda: None)
+    chunks = [(n + pool - 1) // pool for n in doc_lens]
+    service = make_memory(svc, chunks, gids, cache1.rk[0], cache1.kv[0][0], cache1.kv[0][1], top_k=top_k,
+                          cls=svc.MSAService)
+    service.block_desc.pool_ids = kw["pooled_doc_ids"]
+    service._generate_slice(16)
+    service.world_size, service.num_key_value_groups, service.scaling = 1, hq // hkv, -1.0
+    service.template_prefix_kvcache = {0: (kw["template_prefix_kcache"], kw["template_prefix_vcache"])}
+    layer.set_memory_client(service)
+
+    # ---- stage 2: two prompts, left padded; question tokens 0, template tail -2, response head -1
+    rows = [[0] * 9 + [-2, -2] + [-1], [0] * 5 + [-2, -2] + [-1]]
+    width = max(len(r) for r in rows)
+    d2 = torch.tensor([[0] * (width - len(r)) + r for r in rows])
+    a2 = torch.tensor([[0] * (width - len(r)) + [1] * len(r) for r in rows])
+    p0 = 3 + top_k
+    p2 = torch.tensor([[p0] * (width - len(r)) + list(range(p0, p0 + len(r))) for r in rows])
+    hidden2 = torch.randn(2, width, hq * d)
+    cache2 = StubCache()
+    cache2.meta["require_recall_topk"] = True
+    cache2.record_kwargs(0, {"stage": "prefill_stage2"})
+    with torch.no_grad():
+        out2, _ = layer(hidden2, d2, a2, rope(hidden2, p2), cache2)
+    kw2 = cache2.cache_kwargs[0]
+    arrays.update(s2_hidden=hidden2, s2_doc_ids=d2, s2_attention_mask=a2, s2_position_ids=p2, s2_out=out2,
+                  s2_cache_k=kw2["compacked_key_cache"], s2_cache_v=kw2["compacked_value_cache"],
+                  s2_kv_lengths=kw2["kv_lengths"], s2_mask=kw2["attention_mask"],
+                  s2_recall_ids=[r["topk_doc_ids"] for r in kw2["recall_topk"]],
+                  s2_recall_scores=[r["score"] for r in kw2["recall_topk"]])
+
+    # ---- decode: two steps on the cache stage 2 left behind
+    cache2.record_kwargs(0, {"stage": "generate"})
+    next_pos = p2[:, -1:] + 1
+    for step in range(2):
+        h = torch.randn(2, 1, hq * d)
+        with torch.no_grad():
+            o, _ = layer(h, torch.full((2, 1), -1), torch.ones(2, 1, dtype=torch.long), rope(h, next_pos + step), cache2)
+        arrays.update({f"dec{step}_hidden": h, f"dec{step}_position_ids": next_pos + step, f"dec{step}_out": o})
+    arrays.update(dec_final_cache_k=cache2.cache_kwargs[0]["compacked_key_cache"],
+                  dec_final_kv_lengths=cache2.cache_kwargs[0]["kv_lengths"])
+    dist.destroy_process_group()
+    save("layer_e2e", **arrays)
+
+
 def gen_routing(svc):
     g = torch.Generator().manual_seed(303)
     chunks = [4, 1, 3, 8, 2, 8, 8, 5, 1, 7]          # ragged documents, 47 chunks, cut into 2 slices
@@ -300,4 +393,5 @@ if __name__ == "__main__":
     gen_pooling(svc, msa_layer)
     gen_layer(svc, msa_layer, MSAConfig)
     gen_routing(svc)
+    gen_layer_e2e(svc, msa_layer, MSAConfig)
     gen_doc_query(a.reference)
