@@ -252,12 +252,56 @@ def run_ours(args):
     res_host = [(torch.empty((b, TOP_K), dtype=torch.float32).pin_memory(),
                  torch.empty((b, TOP_K), dtype=torch.int64).pin_memory()) for _ in range(layers)]
 
+    # host-resident content bank (K then V per chunk), one layer's worth shared by all layers:
+    # docs_local x 8 chunks x 4 KiB per rank (6.4 GB over all ranks), mapped by every rank
+    fetch_note = None
+    try:
+        g_kv = torch.Generator(device=dev)
+        g_kv.manual_seed(77 + rank)
+        for layer in svc.router_layer_ids[:1]:
+            kv = torch.empty((c_local, 2, HKV, D), dtype=torch.bfloat16).pin_memory()
+            step_c = 1 << 18
+            for c0 in range(0, c_local, step_c):
+                n = min(step_c, c_local - c0)
+                kv[c0:c0 + n].copy_(torch.randn((n, 2, HKV, D), generator=g_kv, device=dev).to(torch.bfloat16))
+            svc.blocks[layer].kv = kv
+            svc.blocks[layer].kv_device_address = kv.data_ptr()
+        first = svc.router_layer_ids[0]
+        for layer in svc.router_layer_ids[1:]:
+            svc.blocks[layer].kv = svc.blocks[first].kv
+            svc.blocks[layer].kv_device_address = svc.blocks[first].kv_device_address
+        if world > 1:
+            shm = "/dev/shm"
+            need = c_local * 2 * HKV * D * 2
+            st = os.statvfs(shm)
+            if st.f_bavail * st.f_frsize < need * 1.1:
+                raise RuntimeError(f"{shm} has {st.f_bavail * st.f_frsize >> 20} MiB free, {need >> 20} MiB needed")
+            keep_ids = svc.router_layer_ids
+            svc.router_layer_ids = keep_ids[:1]          # one bank file per rank
+            svc.share_host_banks(tag=f"bench{os.environ.get('MASTER_PORT', '0')}")
+            svc.router_layer_ids = keep_ids
+            base_, offs_, ln_, kvb = svc._directory
+            svc._directory = (base_, offs_, ln_, {layer: kvb[first] for layer in keep_ids})
+            for layer in keep_ids[1:]:
+                svc.blocks[layer].kv = svc.blocks[first].kv
+        else:
+            svc.publish_directory()
+    except Exception as e:  # the routing numbers stand without the fetch leg
+        fetch_note = f"fetch leg skipped: {e}"
+    fetch_stream = torch.cuda.Stream(dev)
+    max_entries = b * TOP_K * CHUNKS_PER_DOC
+    timeline = {}
+
     def step_e2e():
-        """Through MSAService.route with host-resident queries: the copy stream brings layer l+1's
-        queries over PCIe while layer l is scored; winners go back to pinned host memory."""
+        """Through MSAService.route / .fetch with host-resident queries: the copy stream brings layer
+        l+1's queries over PCIe while layer l is scored; layer l's winners' K/V are fetched from the
+        pinned host bank on a side stream while layer l+1 is scored; winners go back to host memory."""
         main = torch.cuda.current_stream(dev)
         ready = [torch.cuda.Event() for _ in range(layers)]
         freed = [torch.cuda.Event() for _ in range(layers)]
+        ev = {k_: [torch.cuda.Event(enable_timing=True) for _ in range(layers)] for k_ in ("rs", "re", "fs", "fe")}
+        t0 = torch.cuda.Event(enable_timing=True)
+        t0.record(main)
         for i, layer in enumerate(svc.router_layer_ids):
             with torch.cuda.stream(copy_stream):
                 if i >= 2:
@@ -265,10 +309,22 @@ def run_ours(args):
                 stage[i % 2].copy_(q_host[i], non_blocking=True)
                 ready[i].record(copy_stream)
             main.wait_event(ready[i])
+            ev["rs"][i].record(main)
             sc, li, gi, rk_ = svc.route(stage[i % 2], mask_dev, layer)
+            ev["re"][i].record(main)
             freed[i].record(main)
             res_host[i][0].copy_(sc, non_blocking=True)
             res_host[i][1].copy_(gi, non_blocking=True)
+            if fetch_note is None:
+                fetch_stream.wait_event(ev["re"][i])
+                with torch.cuda.stream(fetch_stream):
+                    ev["fs"][i].record(fetch_stream)
+                    fk, fv, n_sel, total = svc.fetch(li, rk_, layer, max_entries=max_entries)
+                    ev["fe"][i].record(fetch_stream)
+                    for t_ in (li, rk_, fk, fv):
+                        t_.record_stream(fetch_stream)
+        main.wait_stream(fetch_stream)
+        timeline["ev"], timeline["t0"] = ev, t0
 
     def sync_all():
         torch.cuda.synchronize(dev)
@@ -308,6 +364,26 @@ def run_ours(args):
     ms_e2e = timed_region(step_e2e, args.steps)
     svc.check_status()
 
+    fetch_report = {"note": fetch_note}
+    if fetch_note is None:
+        ev, t0 = timeline["ev"], timeline["t0"]
+        rs = [t0.elapsed_time(e) for e in ev["rs"]]
+        re_ = [t0.elapsed_time(e) for e in ev["re"]]
+        fs = [t0.elapsed_time(e) for e in ev["fs"]]
+        fe = [t0.elapsed_time(e) for e in ev["fe"]]
+        fetch_ms = [b_ - a_ for a_, b_ in zip(fs, fe)]
+        hidden = sum(1 for i in range(layers - 1) if fe[i] <= re_[i + 1])
+        fetch_bytes = b * TOP_K * CHUNKS_PER_DOC * 2 * HKV * D * 2
+        fetch_report = {
+            "bytes_per_layer_per_gpu": fetch_bytes, "avg_ms": sum(fetch_ms) / layers,
+            "pcie_gbs": fetch_bytes / (sum(fetch_ms) / layers / 1e3) / 1e9,
+            "layers_hidden_behind_next_layer_scoring": f"{hidden}/{layers - 1}",
+            "exposed_ms_after_last_layer": max(0.0, fe[-1] - re_[-1]),
+            "timeline_ms_first_3_layers": [{"route": [round(rs[i], 3), round(re_[i], 3)],
+                                            "fetch": [round(fs[i], 3), round(fe[i], 3)]} for i in range(min(3, layers))],
+            "host_bank": "one layer's K/V bank (docs x 8 chunks x 4 KiB), pinned, shared by the 18 layers"}
+        if world > 1:
+            svc.close_host_banks()
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -330,8 +406,10 @@ def run_ours(args):
                    "l2": "inputs per layer (router keys %.0f MB) exceed L2; 18 distinct layers per step" % (c_local * 2048 / 1e6)},
         "e2e": {"value": e2e_value, "unit": "queries/s",
                 "h2d_bytes_per_step": layers * (q_host[0].numel() * 2) * world,
-                "d2h_bytes_per_step": layers * b * TOP_K * 12 * world},
+                "d2h_bytes_per_step": layers * b * TOP_K * 12 * world,
+                "host_to_device_fetch_bytes_per_step": 0 if fetch_note else layers * world * b * TOP_K * CHUNKS_PER_DOC * 2 * HKV * D * 2},
         "gpu_launches": n_launch,
+        "fetch": fetch_report,
         "clocks": clocks,
         "roofline": {"kernel": "route_tc_kernel", "bound": "tensor", "achieved": achieved_tf, "peak": pk["tflops"],
                      "unit": "TFLOP/s", "frac": achieved_tf / pk["tflops"], "traffic": None,
