@@ -68,9 +68,13 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
+            t0 = time.time()
+            while not self.rows and time.time() - t0 < 2.0:   # sampling is live before the timed region starts
+                time.sleep(0.02)
+            self.rows.clear()
         except OSError:
             self.proc = None
 
@@ -467,12 +471,12 @@ def run_secondary(args):
     g = torch.Generator(device=dev)
     g.manual_seed(2000)
     sampler = ClockSampler(0)
-    steps, warmup = max(args.steps, 5), max(args.warmup, 3)
+    steps, warmup = max(args.steps, 50), max(args.warmup, 3)   # short kernels: time many launches
     args.steps, args.warmup = steps, warmup
 
     if args.workload == "pooling":
         # BASELINE config 2: 2,048 documents x 512 tokens, K / V / K_r bf16 [1, 8, T, 128], chunk 64
-        n_docs, doc_len, p = 2048, 512, 64
+        n_docs, doc_len, p = (2048 if args.docs == N_DOCS else args.docs), 512, 64
         t = n_docs * doc_len
         doc_ids = torch.arange(1, n_docs + 1, device=dev).repeat_interleave(doc_len).view(1, t)
         tok, off, pooled = ops.chunk_bookkeeping(doc_ids, None, p)
@@ -490,7 +494,7 @@ def run_secondary(args):
         alg = 3 * (t * HKV * D * 2 + c * HKV * D * 2)
         _secondary_line(args, "chunk-mean pooling tokens/s (K, V, K_r)", "tokens/s", t / (ms / 1e3), ms,
                         f"BASELINE config 2: {n_docs} docs x {doc_len} tokens, chunk {p}, bf16, 3 tensors "
-                        f"(2.15 GB each, > L2)", "pool_kernel", alg, pk["hbm_gbs"], "hbm", clocks, 3 * steps,
+                        f"({t * HKV * D * 2 / 1e9:.2f} GB each, > L2)", "pool_kernel", alg, pk["hbm_gbs"], "hbm", clocks, 3 * steps,
                         {"bookkeeping_ms": ms_bk})
 
     elif args.workload == "decode":
@@ -515,12 +519,12 @@ def run_secondary(args):
             step()
         kv_len.fill_(L)
         sampler.start()
-        ms = _time_ms(torch, graph.replay, 20 * steps, warmup) / n_layers
+        ms = _time_ms(torch, graph.replay, 10 * steps, warmup) / n_layers
         clocks = sampler.stop()
         alg = 2 * b * (L + 1) * HKV * D * 2
         _secondary_line(args, "sparse decode attention layer-steps/s", "layer-steps/s", 1e3 / ms, ms,
                         f"BASELINE config 5 layer: batch {b}, L={L}+1, 32q/8kv heads, d=128, bf16, {n_splits} KV "
-                        f"splits, {n_layers} distinct caches of 285 MB rotate (> L2)", "decode_split_kernel", alg,
+                        f"splits, {n_layers} distinct caches of 285 MB rotate (> L2)", "decode_mma_kernel", alg,
                         pk["hbm_gbs"], "hbm", clocks, 3 * n_layers * steps)
 
     elif args.workload == "fetch":
@@ -577,21 +581,21 @@ def run_secondary(args):
                     ev.append((e0, e1))
                 ops.topk_select(keys, TOP_K)
         # the scoring kernel alone, eagerly, with events around each launch
-        _time_ms(torch, lambda: step(True), steps, warmup)
-        route_ms = statistics.mean([a.elapsed_time(b_) for a, b_ in ev[-steps * n_layers:]])
+        _time_ms(torch, lambda: step(True), 5, warmup)
+        route_ms = statistics.mean([a.elapsed_time(b_) for a, b_ in ev[-5 * n_layers:]])
         # the whole layer-step replayed from a CUDA graph: at ~100 us per layer the Python
         # launch path would otherwise be the bottleneck, as it would be in a real decode loop
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             step(False)
         sampler.start()
-        ms = _time_ms(torch, graph.replay, 20 * steps, warmup) / n_layers
+        ms = _time_ms(torch, graph.replay, 10 * steps, warmup) / n_layers
         clocks = sampler.stop()
         alg = c * HKV * D * 2 + b * HKV * D * 2
         _secondary_line(args, "decode-time routing layer-steps/s (one of 8 shards)", "layer-steps/s", 1e3 / ms, ms,
                         f"BASELINE config 5 per-step routing: {b} sequences x 1 token against {c} chunks (400 MB shard), "
                         f"{n_layers} distinct layers rotate", "route_tc_kernel", alg, pk["hbm_gbs"], "hbm", clocks,
-                        5 * n_layers * 20 * steps, {"launch": "one CUDA graph per step (fold, reset, score, 2-level top-k)",
+                        5 * n_layers * 10 * steps, {"launch": "one CUDA graph per step (fold, reset, score, 2-level top-k)",
                                                     "route_kernel_ms": route_ms,
                                                "route_kernel_gbs": alg / (route_ms / 1e3) / 1e9,
                                                "route_kernel_frac": alg / (route_ms / 1e3) / 1e9 / pk["hbm_gbs"]})

@@ -135,6 +135,13 @@ int msa_route_scores(const void* q_folded, const float* row_bias, int32_t dtype,
                      int64_t table_stride, int32_t n_docs, float min_val, uint32_t flags,
                      int32_t* status, void* stream);
 
+/* Failure-path self-test: launches one CTA that waits, with the routing kernel's bounded-wait
+ * routine and the given limit (<= 1 s), on a barrier that nothing completes.  After the stream
+ * drains, status[0] == 9 and status[1] == 1: the wait gave up and the kernel returned; the
+ * context stays usable.  (No counterpart in the reference, whose waits are unbounded:
+ * src/msa_service.py:1427-1442, 1904.) */
+int msa_selftest_bounded_wait(int64_t limit_ns, int32_t* status, void* stream);
+
 /* Resets a score table to min_val (and `status`, when given, to zero).  msa_route_scores does
  * this itself unless MSA_ROUTE_NO_INIT is set; the separate entry point exists so that a bank
  * scored in several calls (or a caller timing the scoring kernel alone) resets once.

@@ -20,7 +20,7 @@ ROUTE_FORCE_SIMT, ROUTE_NO_INIT = 1, 2
 
 EXPORTS = [
     "msa_abi_version", "msa_last_error", "msa_chunk_bookkeeping", "msa_pool_chunks", "msa_fold_queries",
-    "msa_route_s_pad", "msa_route_table_reset", "msa_route_scores", "msa_topk_workspace_bytes", "msa_topk_select", "msa_topk_merge", "msa_gather_plan",
+    "msa_route_s_pad", "msa_selftest_bounded_wait", "msa_route_table_reset", "msa_route_scores", "msa_topk_workspace_bytes", "msa_topk_select", "msa_topk_merge", "msa_gather_plan",
     "msa_gather_run", "msa_bank_register_host", "msa_bank_unregister_host", "msa_decode_workspace_bytes", "msa_sparse_decode_attn",
     "msa_decode_static_scratch_bytes", "msa_sparse_decode_attn_static",
 ]
@@ -50,6 +50,7 @@ def lib() -> C.CDLL:
         l.msa_route_s_pad.argtypes = [i32, i32]
         l.msa_route_s_pad.restype = i32
         l.msa_route_scores.argtypes = [vp, vp, i32, i32, i32, vp, i64, i32, i32, vp, f32, vp, i64, i32, f32, u32, vp, vp]
+        l.msa_selftest_bounded_wait.argtypes = [i64, vp, vp]
         l.msa_route_table_reset.argtypes = [vp, i64, i32, i32, f32, vp, vp]
         l.msa_topk_workspace_bytes.argtypes = [i32, i32, i32]
         l.msa_topk_workspace_bytes.restype = i64

@@ -78,14 +78,14 @@ __device__ __forceinline__ unsigned long long global_ns() {
 // Bounded wait.  Returns false (and raises the abort flag + status word) when the limit
 // runs out or another role of this CTA already gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
-                                          int code) {
+                                          int code, unsigned long long limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_ns();
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 255u) == 0) {
       if (*abort_flag) return false;
-      if (global_ns() - t0 > kWaitLimitNs) {
+      if (global_ns() - t0 > limit_ns) {
         *abort_flag = 1;
         atomicCAS(status, 0, code);
         return false;
@@ -341,6 +341,21 @@ route_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constan
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
 }
 
+// The bounded wait on its own: one CTA waits on a barrier that nothing ever completes, with the
+// caller's limit, and reports through `status` exactly as the routing kernel would.
+__global__ void wait_selftest_kernel(unsigned long long limit_ns, int32_t* status) {
+  __shared__ uint64_t s_bar;
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) {
+    mbar_init(&s_bar, 1);
+    s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  const bool ok = mbar_wait(&s_bar, 0, &s_abort, status, 9, limit_ns);
+  if (!ok && threadIdx.x == 0) atomicExch(status + 1, 1);
+}
+
 // ---- host side ------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -437,3 +452,11 @@ int launch_route_tc(const void* qf, const float* row_bias, int n_seq, int s_pad,
 }
 
 }  // namespace msa
+
+extern "C" int msa_selftest_bounded_wait(int64_t limit_ns, int32_t* status, void* stream) {
+  MSA_REQUIRE(status && limit_ns > 0 && limit_ns <= 1000000000ll, "selftest: limit must be in (0, 1e9] ns");
+  MSA_CUDA_OK(cudaMemsetAsync(status, 0, 4 * sizeof(int32_t), (cudaStream_t)stream));
+  msa::wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((unsigned long long)limit_ns, status);
+  MSA_LAUNCH_OK("wait_selftest_kernel");
+  return MSA_OK;
+}

@@ -127,3 +127,26 @@ def test_empty_shard_and_all_masked_queries():
     svc = _service(chunks, [7, 9], rk, rk, rk, 4, torch.bfloat16)
     fk, fv, fs, n_sel, wg = svc.doc_query(q, mask, 0)
     assert (fs.cpu() <= -1e9).all() and n_sel.cpu().tolist() == [0, 0] and fk.shape[1] == 0
+
+
+def test_bounded_wait_gives_up_and_reports():
+    """A barrier wait that can never complete runs into its limit: the kernel returns, the status
+    words say so, and the context keeps working (no trap, no hang)."""
+    import time
+    from msa_b200 import _cabi as A, ops
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    t0 = time.perf_counter()
+    A.check(A.lib().msa_selftest_bounded_wait(20_000_000, A.ptr(status), A.stream_ptr(status.device)), "selftest")
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    assert status.cpu().tolist()[:2] == [9, 1]
+    assert 0.015 < dt < 1.0
+    # the device is still usable afterwards
+    keys = torch.zeros((2, 5), dtype=torch.int32, device=DEV)
+    ops.route_table_reset(keys, 4, -1.0)
+    assert (ops.keys_to_scores(keys).cpu() == -1.0).all()
+    # and Memory.check_status turns a non-zero status word into an exception
+    svc = _service([1], [5], torch.zeros(1, 8, 128), torch.zeros(1, 8, 128), torch.zeros(1, 8, 128), 1, torch.float32)
+    svc._status.copy_(status)
+    with pytest.raises(A.MsaError, match="gave up"):
+        svc.check_status()
