@@ -44,7 +44,8 @@ def parse():
     ap.add_argument("--layers", type=int, default=N_LAYERS)
     ap.add_argument("--queries", type=int, default=N_QUERIES)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="routing", choices=["routing", "pooling", "decode", "fetch", "route-decode"],
+    ap.add_argument("--new-tokens", type=int, default=256, help="generate workload: tokens to decode")
+    ap.add_argument("--workload", default="routing", choices=["routing", "pooling", "decode", "fetch", "route-decode", "generate"],
                     help="routing = the headline (default); the others time one secondary kernel each")
     return ap.parse_args()
 
@@ -601,10 +602,155 @@ def run_secondary(args):
                                                "route_kernel_frac": alg / (route_ms / 1e3) / 1e9 / pk["hbm_gbs"]})
 
 
+# ------------------------------------------------------------------------------------------
+# BASELINE config 5: end-to-end sparse generation step (Qwen3-4B-shaped decoder, random weights)
+# ------------------------------------------------------------------------------------------
+def run_generate(args):
+    import torch
+    import torch.distributed as dist
+    from msa_b200.decoder import DecoderShape, SparseDecodeModel
+    from msa_b200.memory import AttentionGeometry, Document, ModelConfig
+    from msa_b200.service import MSAService
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    n_docs, batch_total, local_ctx, new_tokens = args.docs, 32, 2048, args.new_tokens
+    router_ids = list(range(18, 36))
+    per = (n_docs + world - 1) // world
+    d_lo, d_hi = min(n_docs, rank * per), min(n_docs, (rank + 1) * per)
+    docs_local, b = d_hi - d_lo, batch_total // world
+    c_local = docs_local * CHUNKS_PER_DOC
+    shard_k = TOP_K if world == 1 else 2 * TOP_K
+    svc = MSAService(local_rank, None, ModelConfig(doc_top_k=TOP_K, router_layer_idx=",".join(map(str, router_ids))),
+                     None, AttentionGeometry(), world_size=world, rank=rank, shard_top_k=shard_k)
+    svc.uniform_seqlen = True
+    svc.block_desc.init_docs([Document(doc_id=d_lo + i, num_chunks=CHUNKS_PER_DOC) for i in range(docs_local)], dev)
+    svc.block_desc.pool_ids_from_docs(dev)
+    bank = make_bank(torch, dev, docs_local, len(router_ids), seed=4000 + 100 * rank)
+    g_kv = torch.Generator(device=dev)
+    g_kv.manual_seed(77 + rank)
+    kv = torch.empty((c_local, 2, HKV, D), dtype=torch.bfloat16).pin_memory()
+    for c0 in range(0, c_local, 1 << 18):
+        n = min(1 << 18, c_local - c0)
+        kv[c0:c0 + n].copy_(torch.randn((n, 2, HKV, D), generator=g_kv, device=dev).to(torch.bfloat16))
+    for i, layer in enumerate(router_ids):
+        svc.blocks[layer].rk, svc.blocks[layer].kv, svc.blocks[layer].kv_device_address = bank[i], kv, kv.data_ptr()
+    first = router_ids[0]
+    if world > 1:
+        svc.router_layer_ids = router_ids[:1]
+        svc.share_host_banks(tag=f"gen{os.environ.get('MASTER_PORT', '0')}")
+        svc.router_layer_ids = router_ids
+        base_, offs_, ln_, kvb = svc._directory
+        svc._directory = (base_, offs_, ln_, {layer: kvb[first] for layer in router_ids})
+        for layer in router_ids[1:]:
+            svc.blocks[layer].kv = svc.blocks[first].kv
+    else:
+        svc.publish_directory()
+
+    model = SparseDecodeModel(DecoderShape(), svc, router_ids, b, local_ctx, new_tokens + 8,
+                              TOP_K * CHUNKS_PER_DOC, dev, seed=10 + rank)
+
+    def sync_all():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+
+    # eager: warm up, then one profiled step for the per-layer breakdown
+    for _ in range(2):
+        model.step()
+    model.probe = {}
+    t0 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    model.step()
+    torch.cuda.synchronize(dev)
+    pr, model.probe = model.probe, None
+    route_ms = [pr["route_start"][l].elapsed_time(pr["route_end"][l]) for l in router_ids]
+    attn_ms = [pr["attn_start"][l].elapsed_time(pr["attn_end"][l]) for l in range(36)]
+    svc.check_status()
+
+    def timed_run(with_fetch: bool):
+        """Capture one step in a CUDA graph (eager launches if capture is refused) and time new_tokens steps."""
+        model.fetch_enabled = with_fetch
+        mode = "cuda-graph"
+        graph = torch.cuda.CUDAGraph()
+        try:
+            with torch.cuda.graph(graph):
+                model.step()
+            run = graph.replay
+        except Exception as e:  # e.g. a collective that cannot be captured
+            mode, run, graph = f"eager ({type(e).__name__})", model.step, None
+            torch.cuda.synchronize(dev)
+        model.reset()
+        for _ in range(3):
+            run()
+        model.reset()
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(new_tokens):
+            run()
+        e1.record()
+        sync_all()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        del graph
+        torch.cuda.synchronize(dev)
+        return float(t.item()), mode
+
+    ms_nofetch, _ = timed_run(False)       # same step without the host fetch: what the fetch may hide behind
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms_total, mode = timed_run(True)
+    clocks = sampler.stop() if rank == 0 else None
+    svc.check_status()
+    tokens_host = model.tokens.cpu()
+    if world > 1:
+        svc.close_host_banks()
+    if rank == 0:
+        value = batch_total * new_tokens / (ms_total / 1e3)
+        per_step_bytes = (sum(p_.numel() for l_ in model.layers for p_ in l_.values()) + model.lm_head.numel()) * 2
+        print(json.dumps({
+            "metric": "sparse generation tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": new_tokens, "warmup": 3, "ms_per_step": ms_total / new_tokens, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"BASELINE config 5: Qwen3-4B-shaped decoder (36 layers, hidden 2560, 32q/8kv, d 128, FFN 9728, "
+                                   f"vocab 151936, random weights), routing in layers 18-35 every step against {n_docs} docs x "
+                                   f"{CHUNKS_PER_DOC} chunks, top-{TOP_K}, batch {batch_total}, {local_ctx}-token local context, "
+                                   f"{new_tokens} new tokens", "launch": mode,
+                       "parallelism": f"sequences and bank split over {world} rank(s); weights replicated"},
+            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                    "note": "tokens are produced and consumed on the device; the only host traffic is the K/V fetch",
+                    "host_to_device_fetch_bytes_per_step": 18 * batch_total * TOP_K * CHUNKS_PER_DOC * 2 * HKV * D * 2},
+            "per_layer": {"routing_ms_avg": sum(route_ms) / len(route_ms), "attention_ms_avg": sum(attn_ms) / len(attn_ms),
+                          "measured": "eager step, CUDA events"},
+            "fetch": {"ms_per_step_with_fetch": ms_total / new_tokens, "ms_per_step_without_fetch": ms_nofetch / new_tokens,
+                      "exposed_ms_per_step": max(0.0, (ms_total - ms_nofetch) / new_tokens),
+                      "pcie_bytes_per_step_per_gpu": 18 * b * TOP_K * CHUNKS_PER_DOC * 2 * HKV * D * 2},
+            "dense_weight_bytes_per_step": per_step_bytes, "clocks": clocks,
+            "gpu_launches": new_tokens * (36 * 3 + 18 * 7), "last_tokens": tokens_host[:4].tolist()}), flush=True)
+    if world > 1:
+        # graphs that captured NCCL kernels were alive in this process: leave without tearing the
+        # communicator down (its destructor can wait forever on them)
+        dist.barrier()
+        torch.cuda.synchronize(dev)
+        sys.stdout.flush()
+        os._exit(0)
+
+
 if __name__ == "__main__":
     a = parse()
     if a.impl == "reference":
         run_reference(a)
+    elif a.workload == "generate":
+        run_generate(a)
     elif a.workload != "routing":
         run_secondary(a)
     else:

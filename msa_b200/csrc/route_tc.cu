@@ -24,6 +24,8 @@
 // once) + rows*kdim*2 (queries) from HBM.  Tensor bound when rows >~ 220, HBM bound below.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "route.cuh"
 
@@ -142,6 +144,87 @@ __device__ __forceinline__ TileCoord tile_coord(const RouteTcParams& p, long lon
   return TileCoord{(int)(r / gq), grp * p.qgroup + (int)(r % gq)};
 }
 
+// ---- epilogue pieces shared by the 1-CTA and the 2-CTA kernel ---------------------------
+// Segments = runs of lanes holding chunks of one document.  `dist` is the distance to the
+// segment's first lane; the last lane of a segment publishes the document's score.  A document
+// that lies wholly inside this warp's 32 chunks (and whose sequence is not cut over several
+// column tiles) has no other writer: a plain store replaces the atomic.
+struct SegInfo { int doc, dist, max_len; bool publish, exclusive; };
+
+__device__ __forceinline__ SegInfo seg_info(const RouteTcParams& p, int chunk, int lane) {
+  const int doc = chunk < p.n_chunks ? p.chunk_doc[chunk] : -1 - lane;  // out-of-range lanes stay alone
+  const int doc_up = __shfl_up_sync(0xffffffffu, doc, 1), doc_dn = __shfl_down_sync(0xffffffffu, doc, 1);
+  const bool head = lane == 0 || doc_up != doc, tail = lane == 31 || doc_dn != doc;
+  const uint32_t heads = __ballot_sync(0xffffffffu, head);
+  const int head_lane = 31 - __clz(heads & (0xffffffffu >> (31 - lane)));
+  const int dist = lane - head_lane;
+  int max_len = dist + 1;  // longest segment in this warp
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) max_len = max(max_len, __shfl_xor_sync(0xffffffffu, max_len, o));
+  bool starts_here = true, ends_here = true;  // does the document cross the warp's edges?
+  if (lane == 0 && chunk > 0 && chunk < p.n_chunks) starts_here = p.chunk_doc[chunk - 1] != doc;
+  if (lane == 31 && chunk + 1 < p.n_chunks) ends_here = p.chunk_doc[chunk + 1] != doc;
+  const bool open_lo = !__shfl_sync(0xffffffffu, starts_here, 0), open_hi = !__shfl_sync(0xffffffffu, ends_here, 31);
+  const bool crosses = (open_lo && head_lane == 0) || (open_hi && (heads >> lane) <= 1u);
+  return SegInfo{doc, dist, max_len, tail && doc > 0, !crosses && p.s_pad <= p.bn};
+}
+
+// Reads this warp's 32 accumulator rows (one chunk per lane, p.bn columns) and publishes the
+// per-(sequence, document) maxima.
+__device__ __forceinline__ void epilogue_compute(const RouteTcParams& p, const SegInfo& si, const float* bias,
+                                                 uint32_t taddr, int q0) {
+  const int seg = min(p.s_pad, p.bn);  // columns of one sequence inside a tile
+  auto publish_score = [&](float v, int seq) {
+    if (seq < p.n_seq) {
+      const uint32_t key = float_to_key(v * p.alpha);
+      uint32_t* dst = p.keys + (long long)seq * p.table_stride + si.doc;
+      if (si.exclusive) *dst = max(key, p.min_key);
+      else atomicMax(dst, key);
+    }
+  };
+  auto load16 = [&](int c0, float (&v)[16]) {
+    uint32_t r[16];
+    tmem_ld16(taddr + c0, r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]) + bias[c0 + j];
+  };
+  // Segmented max over the lanes of a document: log2(longest segment) shuffle steps, done for a
+  // whole batch of independent values at a time so that the shuffles pipeline.
+  if (p.s_pad == 1) {  // every column is its own sequence
+    for (int c0 = 0; c0 < p.bn; c0 += 16) {
+      float v[16];
+      load16(c0, v);
+      for (int d = 1; d < si.max_len; d <<= 1) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float o = __shfl_up_sync(0xffffffffu, v[j], d);
+          if (si.dist >= d) v[j] = fmaxf(v[j], o);
+        }
+      }
+      if (si.publish) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) publish_score(v[j], q0 + c0 + j);
+      }
+    }
+  } else {             // `seg` consecutive columns belong to one sequence: in-thread max first
+    for (int s0 = 0; s0 < p.bn; s0 += seg) {
+      float run = -INFINITY;
+      for (int c0 = s0; c0 < s0 + seg; c0 += 16) {
+        float v[16];
+        load16(c0, v);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) run = fmaxf(run, v[j]);
+      }
+      for (int d = 1; d < si.max_len; d <<= 1) {
+        const float o = __shfl_up_sync(0xffffffffu, run, d);
+        if (si.dist >= d) run = fmaxf(run, o);
+      }
+      if (si.publish) publish_score(run, (q0 + s0) / p.s_pad);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kTcThreads, 1)
 route_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_q,
                 const RouteTcParams p) {
@@ -238,7 +321,6 @@ route_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constan
     }
   } else {
     // ------------------------------- epilogue (warps 0-3) ------------------------------
-    const int seg = min(p.s_pad, p.bn);  // columns of one sequence inside a tile
     long long it = 0;
     bool ok = true;
     for (long long t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++it) {
@@ -249,27 +331,7 @@ route_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constan
       float* bias = s_bias[warp];
       __syncwarp();  // the previous tile's reads of this warp's bias copy are done
       for (int j = lane; j < p.bn; j += 32) bias[j] = (q0 + j < p.n_rows) ? p.row_bias[q0 + j] : -INFINITY;
-      const int chunk = tc.ct * kBM + threadIdx.x;
-      const int doc = chunk < p.n_chunks ? p.chunk_doc[chunk] : -1 - lane;  // out-of-range lanes stay alone
-      // Segments = runs of lanes holding chunks of one document.  `dist` is the distance to the
-      // segment's first lane; the last lane of a segment publishes the document's score.  A
-      // document that lies wholly inside this warp's 32 chunks (and whose sequence is not cut
-      // over several column tiles) has no other writer: a plain store replaces the atomic.
-      const int doc_up = __shfl_up_sync(0xffffffffu, doc, 1), doc_dn = __shfl_down_sync(0xffffffffu, doc, 1);
-      const bool head = lane == 0 || doc_up != doc, tail = lane == 31 || doc_dn != doc;
-      const uint32_t heads = __ballot_sync(0xffffffffu, head);
-      const int head_lane = 31 - __clz(heads & (0xffffffffu >> (31 - lane)));
-      const int dist = lane - head_lane;
-      int max_len = dist + 1;  // longest segment in this warp
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) max_len = max(max_len, __shfl_xor_sync(0xffffffffu, max_len, o));
-      bool starts_here = true, ends_here = true;                     // does the document cross the warp's edges?
-      if (lane == 0 && chunk > 0 && chunk < p.n_chunks) starts_here = p.chunk_doc[chunk - 1] != doc;
-      if (lane == 31 && chunk + 1 < p.n_chunks) ends_here = p.chunk_doc[chunk + 1] != doc;
-      const bool open_lo = !__shfl_sync(0xffffffffu, starts_here, 0), open_hi = !__shfl_sync(0xffffffffu, ends_here, 31);
-      const bool crosses = (open_lo && head_lane == 0) || (open_hi && (heads >> lane) <= 1u);
-      const bool publish = tail && doc > 0;
-      const bool exclusive = !crosses && p.s_pad <= p.bn;
+      const SegInfo si = seg_info(p, tc.ct * kBM + (int)threadIdx.x, lane);
       __syncwarp();
       // every lane waits; the warp then agrees on the outcome so that it never diverges
       ok = mbar_wait(&s_acc_full[buf], acc_phase, abort_flag, p.status, 4);
@@ -278,55 +340,7 @@ route_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constan
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)buf * kRouteMaxN;
 
-      auto publish_score = [&](float v, int seq) {
-        if (seq < p.n_seq) {
-          const uint32_t key = float_to_key(v * p.alpha);
-          uint32_t* dst = p.keys + (long long)seq * p.table_stride + doc;
-          if (exclusive) *dst = max(key, p.min_key);
-          else atomicMax(dst, key);
-        }
-      };
-      auto load16 = [&](int c0, float (&v)[16]) {
-        uint32_t r[16];
-        tmem_ld16(taddr + c0, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]) + bias[c0 + j];
-      };
-      // Segmented max over the lanes of a document: log2(longest segment) shuffle steps, done
-      // for a whole batch of independent values at a time so that the shuffles pipeline.
-      if (p.s_pad == 1) {  // every column is its own sequence
-        for (int c0 = 0; c0 < p.bn; c0 += 16) {
-          float v[16];
-          load16(c0, v);
-          for (int d = 1; d < max_len; d <<= 1) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const float o = __shfl_up_sync(0xffffffffu, v[j], d);
-              if (dist >= d) v[j] = fmaxf(v[j], o);
-            }
-          }
-          if (publish) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) publish_score(v[j], q0 + c0 + j);
-          }
-        }
-      } else {             // `seg` consecutive columns belong to one sequence: in-thread max first
-        for (int s0 = 0; s0 < p.bn; s0 += seg) {
-          float run = -INFINITY;
-          for (int c0 = s0; c0 < s0 + seg; c0 += 16) {
-            float v[16];
-            load16(c0, v);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) run = fmaxf(run, v[j]);
-          }
-          for (int d = 1; d < max_len; d <<= 1) {
-            const float o = __shfl_up_sync(0xffffffffu, run, d);
-            if (dist >= d) run = fmaxf(run, o);
-          }
-          if (publish) publish_score(run, (q0 + s0) / p.s_pad);
-        }
-      }
+      epilogue_compute(p, si, bias, taddr, q0);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_acc_empty[buf]);
@@ -339,6 +353,188 @@ route_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constan
   tc_fence_after();
   if (warp == 5)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+}
+
+// =========================================================================================
+// 2-CTA variant (cta_group::2) for full 256-row query tiles.
+//
+// A cluster of two CTAs on neighbouring SMs computes a 256-chunk x 256-row tile with one
+// tcgen05.mma.cta_group::2 stream issued by the leader (cluster rank 0).  Each CTA stages only
+// ITS 128 chunks and ITS 128 query rows per K block (32 KB instead of 48 KB), and the pair's
+// MMA reads both halves from both shared memories: a third less L2 -> SM operand traffic per
+// flop, which is what limits the 1-CTA kernel (64 % of crossbar peak at 86 % tensor activity).
+// Each CTA's TMEM holds the 128 accumulator rows of its own chunks, so the epilogue is the same.
+//
+// Cross-CTA signalling, all with plain (non-multicast) forms:
+//   * both CTAs' TMA loads complete on the LEADER's `full` barrier (cta_group::2 load, barrier
+//     address mapped into the leader's shared memory);
+//   * the leader's tcgen05.commit is issued twice, once per CTA, for `empty` and `acc_full`;
+//   * every epilogue warp of both CTAs arrives on the leader's `acc_empty`.
+// =========================================================================================
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y,
+                                                 uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+constexpr int kPairBN = 256;  // query rows per cluster tile
+constexpr int kPairBM = 256;  // chunks per cluster tile (128 per CTA)
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads, 1)
+route_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_q,
+                     const RouteTcParams p) {
+  extern __shared__ unsigned char smem_dyn[];
+  __shared__ uint64_t s_full[kMaxStages], s_empty[kMaxStages], s_acc_full[2], s_acc_empty[2], s_drain;
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+  __shared__ float s_bias[kEpiThreads / 32][kRouteMaxN];
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  const uint32_t half_bytes = kBM * kBK * 2, stage_bytes = 2 * half_bytes;  // 128 chunks + 128 query rows
+  volatile int* abort_flag = &s_abort;
+  const long long n_tiles = (long long)p.n_ctiles * p.n_qtiles;  // counted in cluster tiles
+  const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&s_acc_full[b], 1); mbar_init(&s_acc_empty[b], 2 * (kEpiThreads / 32)); }
+    mbar_init(&s_drain, 1);
+    s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 5) {  // both CTAs of the pair allocate, with the same destination offset
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
+                 "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anything remote touches them
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+
+  if (warp == 4) {
+    // ------------------------------- TMA producer (each CTA loads its halves) ----------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long t = cluster_id; t < n_tiles && ok; t += n_clusters) {
+        const TileCoord tc = tile_coord(p, t);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!(ok = mbar_wait(&s_empty[stage], phase ^ 1u, abort_flag, p.status, 1))) break;
+          unsigned char* sa = tiles + (size_t)stage * stage_bytes;
+          if (leader) mbar_expect_tx(&s_full[stage], 2 * stage_bytes);  // both CTAs' bytes land on this barrier
+          const uint32_t bar = map_to_cta(smem_u32(&s_full[stage]), 0);
+          tma_load_2d_pair(sa, &tmap_k, kb * kBK, tc.ct * kPairBM + (int)rank * kBM, bar);
+          tma_load_2d_pair(sa + half_bytes, &tmap_q, kb * kBK, tc.qt * kPairBN + (int)rank * (kPairBN / 2), bar);
+          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      // on give-up the copies in flight are drained by the cluster-wide teardown wait below
+    }
+  } else if (warp == 5) {
+    // ------------------------------- MMA issuer (leader CTA only) ----------------------
+    if (lane == 0 && leader) {
+      // instruction descriptor: D=f32, A=B=bf16, both K-major, N=256, M=256 (128 rows per CTA)
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kPairBN >> 3) << 17) |
+                             ((uint32_t)(kPairBM >> 4) << 24);
+      int stage = 0;
+      uint32_t phase = 0;
+      long long it = 0;
+      bool ok = true;
+      for (long long t = cluster_id; t < n_tiles && ok; t += n_clusters, ++it) {
+        const int buf = (int)(it & 1);
+        const uint32_t acc_phase = (uint32_t)((it >> 1) & 1);
+        if (!(ok = mbar_wait(&s_acc_empty[buf], acc_phase ^ 1u, abort_flag, p.status, 2))) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)buf * kRouteMaxN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!(ok = mbar_wait(&s_full[stage], phase, abort_flag, p.status, 3))) break;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(tiles + (size_t)stage * stage_bytes);
+          const uint64_t a_desc = make_smem_desc(sa), b_desc = make_smem_desc(sa + half_bytes);
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k)
+            tc_mma_bf16_pair(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc,
+                             (kb > 0 || k > 0) ? 1u : 0u);
+          tc_commit_pair(smem_u32(&s_empty[stage]));                  // this CTA's stage
+          tc_commit_pair(map_to_cta(smem_u32(&s_empty[stage]), 1));   // the partner's stage
+          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) {
+          tc_commit_pair(smem_u32(&s_acc_full[buf]));
+          tc_commit_pair(map_to_cta(smem_u32(&s_acc_full[buf]), 1));
+        }
+      }
+      tc_commit_pair(smem_u32(&s_drain));
+      const unsigned long long t0 = global_ns();
+      while (!mbar_try_wait(&s_drain, 0) && global_ns() - t0 < kWaitLimitNs) {}
+    }
+  } else {
+    // ------------------------------- epilogue (warps 0-3 of both CTAs) -----------------
+    long long it = 0;
+    bool ok = true;
+    for (long long t = cluster_id; t < n_tiles && ok; t += n_clusters, ++it) {
+      const TileCoord tc = tile_coord(p, t);
+      const int buf = (int)(it & 1);
+      const uint32_t acc_phase = (uint32_t)((it >> 1) & 1);
+      const int q0 = tc.qt * kPairBN;
+      float* bias = s_bias[warp];
+      __syncwarp();
+      for (int j = lane; j < kPairBN; j += 32) bias[j] = (q0 + j < p.n_rows) ? p.row_bias[q0 + j] : -INFINITY;
+      const SegInfo si = seg_info(p, tc.ct * kPairBM + (int)rank * kBM + (int)threadIdx.x, lane);
+      __syncwarp();
+      ok = mbar_wait(&s_acc_full[buf], acc_phase, abort_flag, p.status, 4);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)buf * kRouteMaxN;
+      epilogue_compute(p, si, bias, taddr, q0);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&s_acc_empty[buf]), 0));
+    }
+  }
+
+  // teardown: the pair meets (the leader has drained its MMAs), then both CTAs return TMEM
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  if (warp == 5)
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
 }
 
 // The bounded wait on its own: one CTA waits on a barrier that nothing ever completes, with the
@@ -445,6 +641,28 @@ int launch_route_tc(const void* qf, const float* row_bias, int n_seq, int s_pad,
     smem_set = smem;
   }
   const long long n_tiles = (long long)p.n_ctiles * p.n_qtiles;
+  // Tensor-bound shapes (full 256-row query tiles, enough chunk tiles to fill the GPU) run on CTA pairs.
+  static const bool pair_off = getenv("MSA_B200_ROUTE_NO_PAIR") != nullptr;
+  if (!pair_off && p.bn == kPairBN && p.n_rows % kPairBN == 0 && n_tiles >= 2ll * n_sm) {
+    RouteTcParams p2 = p;
+    p2.n_ctiles = (n_chunks + kPairBM - 1) / kPairBM;
+    p2.stages = 6;  // 6 x 32 KB
+    CUtensorMap map_q2;
+    rc = make_map(&map_q2, qf, (uint64_t)p.n_rows, (uint64_t)kdim, (uint64_t)kdim, (uint32_t)(kPairBN / 2));
+    if (rc != MSA_OK) return rc;
+    const size_t smem2 = (size_t)p2.stages * 2 * kBM * kBK * 2 + 1024;
+    static thread_local bool pair_set = false;
+    if (!pair_set) {
+      MSA_CUDA_OK(cudaFuncSetAttribute(route_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2));
+      pair_set = true;
+    }
+    const long long tiles2 = (long long)p2.n_ctiles * p2.n_qtiles;
+    long long clusters = n_sm / 2;
+    if (clusters > tiles2) clusters = tiles2;
+    route_tc_pair_kernel<<<(int)(2 * clusters), kTcThreads, smem2, stream>>>(map_k, map_q2, p2);
+    MSA_LAUNCH_OK("route_tc_pair_kernel");
+    return MSA_OK;
+  }
   const int grid = (int)(n_tiles < n_sm ? n_tiles : n_sm);
   route_tc_kernel<<<grid, kTcThreads, smem, stream>>>(map_k, map_q, p);
   MSA_LAUNCH_OK("route_tc_kernel");

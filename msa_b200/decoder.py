@@ -1,0 +1,173 @@
+"""A Qwen3-shaped decoder whose attention layers decode over the MSA sparse context.
+
+This is the decode loop of the reference (``src/msa/generate.py:101-186`` driving
+``MSADeocoderLayer`` / ``MemorySparseAttention`` in its "generate" stage,
+``src/msa/model.py:67-135``, ``src/msa/memory_sparse_attention.py:361-405``) reduced to what a
+throughput measurement needs: random-initialised weights of the real shapes, greedy sampling, no
+tokenizer and no string handling.  Dense algebra (projections, MLP, lm_head, RMSNorm, RoPE) is
+PyTorch / cuBLAS as in the reference; attention runs on this package's flash-decode kernel with
+in-place append, and the router layers route every step through ``MSAService``:
+
+    route(step t, layer l)  ->  fetch of the winners' pooled K/V from the pinned host bank on a
+    side stream  ->  written into the "retrieved" segment of layer l's cache, where the attention
+    of step t+1 reads it.
+
+So the host fetch never sits on the critical path: it overlaps the rest of the step.  (The
+reference routes once per round, in prefill stage 2; per-step routing is the variant BASELINE
+config 5 asks to time.)  KV layout per layer: ``[template t | retrieved k*c | local + generated]``.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import ops
+from .service import MSAService
+
+
+@dataclass
+class DecoderShape:
+    num_layers: int = 36
+    hidden: int = 2560
+    n_q_heads: int = 32
+    n_kv_heads: int = 8
+    head_dim: int = 128
+    ffn: int = 9728
+    vocab: int = 151_936
+    rope_theta: float = 1_000_000.0
+    rms_eps: float = 1e-6
+    template_len: int = 3
+
+
+class SparseDecodeModel:
+    def __init__(self, shape: DecoderShape, service: Optional[MSAService], router_layers: List[int], batch: int,
+                 local_ctx: int, max_new: int, retrieved_entries: int, device, dtype=torch.bfloat16, seed: int = 0):
+        self.s, self.svc, self.device, self.dtype = shape, service, device, dtype
+        self.router_layers = set(router_layers)
+        self.batch, self.max_new, self.retrieved = batch, max_new, retrieved_entries
+        s = shape
+        g = torch.Generator(device=device)
+        g.manual_seed(seed)
+
+        def w(*dims, scale=None):
+            scale = scale if scale is not None else 1.0 / math.sqrt(dims[0])
+            return (torch.randn(dims, generator=g, device=device, dtype=torch.float32) * scale).to(dtype)
+
+        qkv_out = (s.n_q_heads + 2 * s.n_kv_heads) * s.head_dim
+        self.layers = []
+        for l in range(s.num_layers):
+            extra = s.n_q_heads * s.head_dim if l in self.router_layers else 0
+            self.layers.append(dict(
+                w_in=torch.ones(s.hidden, device=device, dtype=dtype),
+                w_qkv=w(s.hidden, qkv_out + extra),            # q | k | v | (router q): one GEMM
+                q_norm=torch.ones(s.head_dim, device=device, dtype=dtype),
+                k_norm=torch.ones(s.head_dim, device=device, dtype=dtype),
+                w_o=w(s.n_q_heads * s.head_dim, s.hidden),
+                w_post=torch.ones(s.hidden, device=device, dtype=dtype),
+                w_gate_up=w(s.hidden, 2 * s.ffn),
+                w_down=w(s.ffn, s.hidden),
+            ))
+        self.embed = w(s.vocab, s.hidden, scale=1.0)
+        self.w_final = torch.ones(s.hidden, device=device, dtype=dtype)
+        self.lm_head = w(s.hidden, s.vocab)
+
+        # caches: [template | retrieved | local context + generated tokens], filled synthetically
+        self.ctx0 = s.template_len + retrieved_entries + local_ctx
+        cap = self.ctx0 + max_new + 1
+        self.k_cache = [torch.randn((batch, s.n_kv_heads, cap, s.head_dim), generator=g, device=device,
+                                    dtype=torch.float32).to(dtype) for _ in range(s.num_layers)]
+        self.v_cache = [torch.randn((batch, s.n_kv_heads, cap, s.head_dim), generator=g, device=device,
+                                    dtype=torch.float32).to(dtype) for _ in range(s.num_layers)]
+        self.kv_len = torch.full((batch,), self.ctx0, dtype=torch.int32, device=device)
+        self.positions = torch.full((batch,), s.template_len + 16 + local_ctx, dtype=torch.long, device=device)
+        self.inv_freq = 1.0 / (s.rope_theta ** (torch.arange(0, s.head_dim, 2, device=device, dtype=torch.float32)
+                                                / s.head_dim))
+        self.tokens = torch.randint(0, s.vocab, (batch,), generator=g, device=device)
+        self.query_mask = torch.ones((batch, 1), dtype=torch.bool, device=device)
+        self.n_splits = ops.decode_splits(batch, s.n_kv_heads, cap)
+        need = batch * s.n_q_heads * self.n_splits * (s.head_dim + 2)
+        self.workspace = torch.empty(max(need, 1), dtype=torch.float32, device=device)
+        self.attn_out = torch.empty((batch, s.n_q_heads * s.head_dim), dtype=dtype, device=device)
+        self.fetch_stream = torch.cuda.Stream(device, priority=-1)   # its small copies go ahead of queued compute
+        self.fetch_enabled = True
+        self.probe = None  # set to a dict to collect per-layer CUDA events (eager profiling step)
+
+    # ------------------------------------------------------------------------------------
+    def _rope(self, x, cos, sin):
+        d = x.shape[-1]
+        rot = torch.cat([-x[..., d // 2:], x[..., : d // 2]], dim=-1)
+        return x * cos + rot * sin
+
+    def _mark(self, name, layer):
+        if self.probe is not None:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            self.probe.setdefault(name, {})[layer] = e
+
+    def step(self):
+        """One decode step for the whole batch; returns the next tokens ``[B]``."""
+        s, B = self.s, self.batch
+        main = torch.cuda.current_stream(self.device)
+        x = self.embed[self.tokens]
+        ang = self.positions.to(torch.float32).unsqueeze(-1) * self.inv_freq
+        emb = torch.cat([ang, ang], dim=-1)
+        cos, sin = emb.cos().to(self.dtype).unsqueeze(1), emb.sin().to(self.dtype).unsqueeze(1)
+        nq, nkv, d = s.n_q_heads, s.n_kv_heads, s.head_dim
+        fetch_done = []
+        for l, p in enumerate(self.layers):
+            h = F.rms_norm(x, (s.hidden,), p["w_in"], s.rms_eps)
+            qkv = h @ p["w_qkv"]
+            q = qkv[:, : nq * d].view(B, nq, d)
+            k = qkv[:, nq * d: (nq + nkv) * d].view(B, nkv, d)
+            v = qkv[:, (nq + nkv) * d: (nq + 2 * nkv) * d].reshape(B, nkv, d)
+            q = self._rope(F.rms_norm(q, (d,), p["q_norm"], s.rms_eps), cos, sin)
+            k = self._rope(F.rms_norm(k, (d,), p["k_norm"], s.rms_eps), cos, sin)
+            routed = None
+            if l in self.router_layers and self.svc is not None:
+                self._mark("route_start", l)
+                rq = F.normalize(qkv[:, (nq + 2 * nkv) * d:].view(B, nq, 1, d), p=2, dim=-1)
+                routed = self.svc.route(rq, self.query_mask, l)
+                self._mark("route_end", l)
+            self._mark("attn_start", l)
+            ops.sparse_decode_attn(q, self.k_cache[l], self.v_cache[l], self.kv_len, k, v, n_splits=self.n_splits,
+                                   workspace=self.workspace, out=self.attn_out)
+            self._mark("attn_end", l)
+            if routed is not None and self.fetch_enabled:
+                # fetch the winners' K/V on the side stream and refresh the retrieved segment; it may
+                # only be overwritten once this step's attention has read it
+                _, local, _, rank = routed
+                after_attn = torch.cuda.Event()
+                after_attn.record(main)
+                self.fetch_stream.wait_event(after_attn)
+                with torch.cuda.stream(self.fetch_stream):
+                    fk, fv, n_sel, total = self.svc.fetch(local, rank, l, max_entries=B * self.retrieved)
+                    lo, hi = s.template_len, s.template_len + self.retrieved
+                    self.k_cache[l][:, :, lo:hi].copy_(fk.view(nkv, B, self.retrieved, d).permute(1, 0, 2, 3))
+                    self.v_cache[l][:, :, lo:hi].copy_(fv.view(nkv, B, self.retrieved, d).permute(1, 0, 2, 3))
+                    for t_ in (local, rank, fk, fv):
+                        t_.record_stream(self.fetch_stream)
+                    done = torch.cuda.Event(enable_timing=self.probe is not None)
+                    done.record(self.fetch_stream)
+                    fetch_done.append(done)
+            x = x + self.attn_out @ p["w_o"]
+            h = F.rms_norm(x, (s.hidden,), p["w_post"], s.rms_eps)
+            gu = h @ p["w_gate_up"]
+            x = x + (F.silu(gu[:, : s.ffn]) * gu[:, s.ffn:]) @ p["w_down"]
+        x = F.rms_norm(x, (s.hidden,), self.w_final, s.rms_eps)
+        nxt = (x @ self.lm_head).argmax(dim=-1)
+        self._mark("compute_end", 0)
+        main.wait_stream(self.fetch_stream)      # the step ends when the refreshed segments are in place
+        if self.probe is not None:
+            self.probe["fetch_done"] = fetch_done
+        self.tokens.copy_(nxt)
+        self.kv_len += 1
+        self.positions += 1
+        return nxt
+
+    def reset(self):
+        self.kv_len.fill_(self.ctx0)
+        self.positions.fill_(self.s.template_len + 16 + (self.ctx0 - self.s.template_len - self.retrieved))

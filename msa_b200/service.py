@@ -140,6 +140,7 @@ class MSAService(Memory, MemoryClientBase):
         if world_size > 1 and not dist.is_initialized():
             raise A.MsaError("world_size > 1 needs an initialised torch.distributed process group (NCCL)")
         self.shard_top_k = shard_top_k or self.model_config.doc_top_k
+        self.uniform_seqlen = False   # set when every rank is known to pass queries of equal length
         self._directory = None
         self._total_pinned = torch.zeros(1, dtype=torch.int64).pin_memory()
 
@@ -218,7 +219,7 @@ class MSAService(Memory, MemoryClientBase):
         b, hq, s, d = query_states.shape
         qr = self.query_reduce_method
         s_common = s
-        if self.world_size > 1 and qr == "max":
+        if self.world_size > 1 and qr == "max" and not self.uniform_seqlen:
             lens = all_gather_cat(torch.tensor([s], device=self.device, dtype=torch.long), self.world_size, self.group)
             s_common = int(lens.max().item())
         s_pad = ops.route_s_pad(s_common, qr)
