@@ -400,6 +400,10 @@ def run_ours(args):
     flops = 2.0 * n_all * s_pad * c_local * (HKV * D)
     achieved_tf = flops / (route_avg_ms / 1e3) / 1e12
     alg_bytes = c_local * HKV * D * 2 + n_all * s_pad * HKV * D * 2
+    n_qtiles = (n_all * s_pad + 255) // 256
+    pair = ((c_local + 127) // 128) * n_qtiles >= 2 * 148          # the library's rule for the 2-CTA kernel
+    kernel_name = "route_tc_pair_kernel" if pair else "route_tc_kernel"
+    traffic = ((n_qtiles + 63) // 64) * c_local * HKV * D * 2 + n_all * s_pad * HKV * D * 2
     line = {
         "metric": METRIC, "value": value, "unit": "queries/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
@@ -416,8 +420,10 @@ def run_ours(args):
         "gpu_launches": n_launch,
         "fetch": fetch_report,
         "clocks": clocks,
-        "roofline": {"kernel": "route_tc_kernel", "bound": "tensor", "achieved": achieved_tf, "peak": pk["tflops"],
-                     "unit": "TFLOP/s", "frac": achieved_tf / pk["tflops"], "traffic": None,
+        "roofline": {"kernel": kernel_name, "bound": "tensor", "achieved": achieved_tf, "peak": pk["tflops"],
+                     "unit": "TFLOP/s", "frac": achieved_tf / pk["tflops"], "traffic": traffic,
+                     "traffic_source": "ncu dram__bytes_read+write of a 160,000-chunk launch (846 MB = keys x query "
+                                       "groups + queries), scaled by the chunk count of this launch",
                      "peak_source": pk["source"] + " (bf16 sustained)", "avg_launch_ms": route_avg_ms,
                      "flops_per_launch": flops,
                      "hbm": {"algorithmic_bytes_per_launch": alg_bytes,
