@@ -27,6 +27,7 @@ void set_error(const char* fmt, ...);
   do {                                                                                 \
     cudaError_t e__ = (expr);                                                          \
     if (e__ != cudaSuccess) {                                                          \
+      (void)cudaGetLastError(); /* reported here: do not leave it for the next launch check */ \
       ::msa::set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), __FILE__, __LINE__); \
       return MSA_ERR_CUDA;                                                             \
     }                                                                                  \

@@ -365,7 +365,7 @@ route_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constan
 // flop, which is what limits the 1-CTA kernel (64 % of crossbar peak at 86 % tensor activity).
 // Each CTA's TMEM holds the 128 accumulator rows of its own chunks, so the epilogue is the same.
 //
-// Cross-CTA signalling, all with plain (non-multicast) forms:
+// Cross-CTA signalling, all with plain single-destination forms:
 //   * both CTAs' TMA loads complete on the LEADER's `full` barrier (cta_group::2 load, barrier
 //     address mapped into the leader's shared memory);
 //   * the leader's tcgen05.commit is issued twice, once per CTA, for `empty` and `acc_full`;

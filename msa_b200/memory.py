@@ -13,6 +13,8 @@ Bank layout (differs from the reference's head-major ``[1, Hkv, C, D]`` on purpo
 """
 from __future__ import annotations
 
+import json
+import os
 from dataclasses import dataclass, field
 from typing import Dict, Iterable, List, Optional, Tuple
 
@@ -231,10 +233,20 @@ class Memory:
     def generate_blocks(self, docs: List[Document], metas: Optional[Iterable[dict]] = None):
         """``Memory.generate_blocks`` (src/msa_service.py:497-582) with the stage-1 results handed in
         as an iterable of META payloads instead of being pulled from a worker process."""
+        data_path = os.environ.get("MEMORY_DATA_PATH", "")
+        if data_path:   # same convention as the reference: $MEMORY_DATA_PATH/gpu<world>/<gpu_id> (:498-505)
+            world = getattr(self, "world_size", None) or getattr(self.generate_config, "world", 1) or 1
+            data_path = os.path.join(data_path, f"gpu{world}", str(self.gpu_id))
+            if os.path.exists(os.path.join(data_path, "meta.json")):
+                out = self.deserialize(data_path)
+                assert len(docs) == self.block_desc.nr_docs
+                return out
         self.begin_blocks(docs)
         for meta in metas or ():
             self.ingest_meta(meta)
         self.block_desc.merge_poolig_doc_id(self.device)
+        if data_path:
+            self.serialize(data_path)
         return self._post_process()
 
     def load_pooled(self, docs: List[Document], layers: Dict[int, Tuple[torch.Tensor, torch.Tensor, torch.Tensor]]):
@@ -248,6 +260,87 @@ class Memory:
             blk.kv[:, 1].copy_(v)
         self.block_desc.pool_ids_from_docs(self.device)
         return self._post_process()
+
+    # ------------------------------------------------------------------ on-disk bank
+    def serialize(self, path: str):
+        """Write the shard under ``path`` (counterpart of ``Memory.serialize``, src/msa_service.py:351-420,
+        which stores one ``.pt`` per layer and tensor).  Format: ``meta.json`` (documents, geometry, dtype),
+        ``prefix_cache.pt`` (template prefix K/V per layer) and, per router layer, two raw little-endian
+        files in exactly the in-memory layouts: ``rk_L<l>.bin`` ``[C, Hkv, D]`` and ``kv_L<l>.bin``
+        ``[C, 2, Hkv, D]``.  Raw files can be mapped and pinned in place on load."""
+        os.makedirs(path, exist_ok=True)
+        g = self.geometry
+        first = self.blocks[self.router_layer_ids[0]]
+        meta = {"format": "msa_b200-bank-1", "dtype": str(first.rk.dtype).replace("torch.", ""),
+                "n_chunks": int(first.rk.shape[0]), "n_kv_heads": g.num_key_value_heads, "head_dim": g.head_dim,
+                "router_layer_ids": list(self.router_layer_ids),
+                "doc_ids": [d.doc_id for d in self.block_desc.docs],
+                "doc_chunks": [d.num_chunks for d in self.block_desc.docs]}
+        torch.cuda.synchronize(self.device)
+        for layer in self.router_layer_ids:
+            blk = self.blocks[layer]
+            blk.rk.cpu().contiguous().view(torch.uint8).numpy().tofile(os.path.join(path, f"rk_L{layer}.bin"))
+            blk.kv.contiguous().view(torch.uint8).numpy().tofile(os.path.join(path, f"kv_L{layer}.bin"))
+        torch.save({l: (k.cpu(), v.cpu()) for l, (k, v) in self.template_prefix_kvcache.items()},
+                   os.path.join(path, "prefix_cache.pt"))
+        with open(os.path.join(path, "meta.json"), "w") as f:   # written last: its presence marks a complete bank
+            json.dump(meta, f)
+
+    def deserialize(self, path: str, map_host_bank: bool = True):
+        """Load a shard written by ``serialize`` (src/msa_service.py:422-479).  Router keys go to the GPU.
+        The K/V bank is not copied: with ``map_host_bank`` its file is memory-mapped and the mapping is
+        pinned and made device-visible (``msa_bank_register_host``), so the first fetch of a document
+        pulls it from the page cache; if the file system does not allow pinning its pages (the driver
+        refuses ext4 mappings, accepts tmpfs ones) or ``map_host_bank`` is false, the bank is read into
+        pinned memory instead.  ``self.bank_placement`` says which happened."""
+        with open(os.path.join(path, "meta.json")) as f:
+            meta = json.load(f)
+        if meta.get("format") != "msa_b200-bank-1":
+            raise A.MsaError(f"{path}: not an msa_b200 bank")
+        dtype = getattr(torch, meta["dtype"])
+        c, h, d = meta["n_chunks"], meta["n_kv_heads"], meta["head_dim"]
+        if (h, d) != (self.geometry.num_key_value_heads, self.geometry.head_dim):
+            raise A.MsaError(f"{path}: bank geometry {h}x{d} does not match the model")
+        if sorted(meta["router_layer_ids"]) != list(self.router_layer_ids):
+            raise A.MsaError(f"{path}: bank holds layers {meta['router_layer_ids']}, model routes in {self.router_layer_ids}")
+        docs = [Document(doc_id=i, num_chunks=n) for i, n in zip(meta["doc_ids"], meta["doc_chunks"])]
+        self.block_desc.init_docs(docs, self.device)
+        self.block_desc.pool_ids_from_docs(self.device)
+        esize = torch.empty((), dtype=dtype).element_size()
+        self._mapped_banks = []
+        for layer in self.router_layer_ids:
+            blk = self.blocks[layer]
+            n_rk, n_kv = c * h * d * esize, c * 2 * h * d * esize
+            raw = torch.from_file(os.path.join(path, f"rk_L{layer}.bin"), shared=False, size=max(n_rk, 1), dtype=torch.uint8)
+            blk.rk = raw[:n_rk].view(dtype).view(c, h, d).to(self.device)
+            kv_path = os.path.join(path, f"kv_L{layer}.bin")
+            mapped_ok = False
+            if map_host_bank and n_kv > 0:
+                import ctypes
+                mapped = torch.from_file(kv_path, shared=True, size=n_kv, dtype=torch.uint8)
+                addr = ctypes.c_uint64(0)
+                rc = A.lib().msa_bank_register_host(mapped.data_ptr(), n_kv, ctypes.byref(addr))
+                if rc == 0:   # tmpfs / hugetlbfs mappings can be pinned in place; most disk file systems cannot
+                    blk.kv, blk.kv_device_address = mapped.view(dtype).view(c, 2, h, d), int(addr.value)
+                    self._mapped_banks.append(mapped)
+                    mapped_ok = True
+                else:
+                    del mapped
+            if not mapped_ok:
+                raw = torch.from_file(kv_path, shared=False, size=max(n_kv, 1), dtype=torch.uint8)
+                blk.kv = raw[:n_kv].view(dtype).view(c, 2, h, d).pin_memory()
+                blk.kv_device_address = blk.kv.data_ptr()
+            self.bank_placement = "mapped in place" if mapped_ok else "copied to pinned memory"
+        prefix = torch.load(os.path.join(path, "prefix_cache.pt"))
+        self.template_prefix_kvcache = {int(l): (k.to(self.device), v.to(self.device)) for l, (k, v) in prefix.items()}
+        return self._post_process()
+
+    def release_mapped_banks(self):
+        """Unpin the file mappings taken by ``deserialize`` (call before the process drops the bank)."""
+        torch.cuda.synchronize(self.device)
+        for m in getattr(self, "_mapped_banks", []):
+            A.lib().msa_bank_unregister_host(m.data_ptr())
+        self._mapped_banks = []
 
     def _post_process(self):
         first = self.blocks[self.router_layer_ids[0]]

@@ -150,3 +150,39 @@ def test_bounded_wait_gives_up_and_reports():
     svc._status.copy_(status)
     with pytest.raises(A.MsaError, match="gave up"):
         svc.check_status()
+
+
+@pytest.mark.parametrize("map_host_bank", [True, False])
+def test_bank_serialize_roundtrip(tmp_path, map_host_bank):
+    import os, tempfile
+    if map_host_bank and os.path.isdir("/dev/shm"):      # a file system whose pages can be pinned in place
+        tmp_path = type(tmp_path)(tempfile.mkdtemp(dir="/dev/shm", prefix="msa_b200_test_"))
+    """A shard written to disk and loaded back (K/V bank mapped and pinned in place, or read into
+    pinned memory) answers doc_query exactly as the original."""
+    chunks = ragged_docs(60, 1, 9, seed=41)
+    gids = [500 + i for i in range(len(chunks))]
+    rk, _ = make_bank(chunks, dtype=torch.bfloat16, seed=42)
+    g = torch.Generator().manual_seed(43)
+    k = torch.randn(rk.shape, generator=g).to(torch.bfloat16)
+    v = torch.randn(rk.shape, generator=g).to(torch.bfloat16)
+    svc = _service(chunks, gids, k, v, rk, 4, torch.bfloat16)
+    svc.template_prefix_kvcache = {0: (torch.ones(1, 8, 3, 128, device=DEV), torch.zeros(1, 8, 3, 128, device=DEV))}
+    q = torch.nn.functional.normalize(torch.randn(3, 32, 20, 128, generator=g), dim=-1).to(torch.bfloat16).to(DEV)
+    mask = torch.ones(3, 20, dtype=torch.bool, device=DEV)
+    ref = svc.doc_query(q, mask, 0)
+    svc.serialize(str(tmp_path / "bank"))
+    svc2 = _service([], [], torch.zeros(0, 8, 128, dtype=torch.bfloat16), torch.zeros(0, 8, 128, dtype=torch.bfloat16),
+                    torch.zeros(0, 8, 128, dtype=torch.bfloat16), 4, torch.bfloat16)
+    svc2._directory = None
+    svc2.deserialize(str(tmp_path / "bank"), map_host_bank=map_host_bank)
+    out = svc2.doc_query(q, mask, 0)
+    for a, b in zip(ref, out):
+        assert torch.equal(a, b)
+    assert torch.equal(svc2.get_template_prefix_kvcaches(0)[0], svc.get_template_prefix_kvcaches(0)[0])
+    assert [d.doc_id for d in svc2.block_desc.docs] == gids
+    assert svc2.bank_placement == ("mapped in place" if map_host_bank and os.path.isdir("/dev/shm") else
+                                   "copied to pinned memory")
+    svc2.release_mapped_banks()
+    if str(tmp_path).startswith("/dev/shm/"):
+        import shutil
+        shutil.rmtree(str(tmp_path), ignore_errors=True)
