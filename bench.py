@@ -1,4 +1,4 @@
-"""Routing benchmark: queries/s over a 100M-token pooled memory bank (BASELINE.json config 4).
+"""Routing benchmark: queries/s over a 100M-token pooled memory bank (benchmark config 4).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
@@ -9,7 +9,7 @@ the N ranks; 128 queries x 256 routing tokens, split over the ranks (each rank s
 queries against its shard).  A step = all 18 layers: fold -> (all-gather queries) -> fused
 score/reduce -> per-shard top-k -> (all-gather candidates) -> merge to the global top-16.
 Inputs are seeded synthetic (cosine mode: unit-norm heads; keys = per-document mean N(0,0.5)
-+ noise of std 1/8 per chunk, the pooled statistics of BASELINE config 3's distribution).
++ noise of std 1/8 per chunk, the pooled statistics of benchmark config 3's distribution).
 
 `value` times the step with queries resident in HBM; `e2e` times the same step through
 MSAService.route with the queries in pinned HOST memory (H2D of every layer's queries and
@@ -141,7 +141,7 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": v, "unit": "queries/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * N_QUERIES / v, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "BASELINE config 4: 100M-token bank, 18 layers, 128 queries x 256 tokens, top-16",
+        "config": {"workload": "benchmark config 4: 100M-token bank, 18 layers, 128 queries x 256 tokens, top-16",
                    "note": "CPU: bounded sample, extrapolated linearly"},
         "cpu_baseline": {"value": v, "unit": "queries/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -408,7 +408,7 @@ def run_ours(args):
         "metric": METRIC, "value": value, "unit": "queries/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"BASELINE config 4: {n_docs} docs x {CHUNKS_PER_DOC} chunks (100M tokens), {layers} routing "
+        "config": {"workload": f"benchmark config 4: {n_docs} docs x {CHUNKS_PER_DOC} chunks (100M tokens), {layers} routing "
                                f"layers, {n_q} queries x {Q_TOKENS} tokens, top-{TOP_K}, cosine scores",
                    "sharding": f"bank by document over {world} rank(s); every rank scores all queries; "
                                f"per-shard top-{shard_k}, all-gather merge",
@@ -482,7 +482,7 @@ def run_secondary(args):
     args.steps, args.warmup = steps, warmup
 
     if args.workload == "pooling":
-        # BASELINE config 2: 2,048 documents x 512 tokens, K / V / K_r bf16 [1, 8, T, 128], chunk 64
+        # benchmark config 2: 2,048 documents x 512 tokens, K / V / K_r bf16 [1, 8, T, 128], chunk 64
         n_docs, doc_len, p = (2048 if args.docs == N_DOCS else args.docs), 512, 64
         t = n_docs * doc_len
         doc_ids = torch.arange(1, n_docs + 1, device=dev).repeat_interleave(doc_len).view(1, t)
@@ -500,12 +500,12 @@ def run_secondary(args):
         c = off.numel() - 1
         alg = 3 * (t * HKV * D * 2 + c * HKV * D * 2)
         _secondary_line(args, "chunk-mean pooling tokens/s (K, V, K_r)", "tokens/s", t / (ms / 1e3), ms,
-                        f"BASELINE config 2: {n_docs} docs x {doc_len} tokens, chunk {p}, bf16, 3 tensors "
+                        f"benchmark config 2: {n_docs} docs x {doc_len} tokens, chunk {p}, bf16, 3 tensors "
                         f"({t * HKV * D * 2 / 1e9:.2f} GB each, > L2)", "pool_kernel", alg, pk["hbm_gbs"], "hbm", clocks, 3 * steps,
                         {"bookkeeping_ms": ms_bk})
 
     elif args.workload == "decode":
-        # BASELINE config 5: batch 32, 32 q / 8 kv heads, L = 3 template + 128 retrieved + 2048 local
+        # benchmark config 5: batch 32, 32 q / 8 kv heads, L = 3 template + 128 retrieved + 2048 local
         b, L, n_layers = 32, 3 + 128 + 2048, 4
         caches = [(torch.randn((b, HKV, L + 8, D), generator=g, device=dev).to(torch.bfloat16),
                    torch.randn((b, HKV, L + 8, D), generator=g, device=dev).to(torch.bfloat16)) for _ in range(n_layers)]
@@ -530,7 +530,7 @@ def run_secondary(args):
         clocks = sampler.stop()
         alg = 2 * b * (L + 1) * HKV * D * 2
         _secondary_line(args, "sparse decode attention layer-steps/s", "layer-steps/s", 1e3 / ms, ms,
-                        f"BASELINE config 5 layer: batch {b}, L={L}+1, 32q/8kv heads, d=128, bf16, {n_splits} KV "
+                        f"benchmark config 5 layer: batch {b}, L={L}+1, 32q/8kv heads, d=128, bf16, {n_splits} KV "
                         f"splits, {n_layers} distinct caches of 285 MB rotate (> L2)", "decode_mma_kernel", alg,
                         pk["hbm_gbs"], "hbm", clocks, 3 * n_layers * steps)
 
@@ -562,7 +562,7 @@ def run_secondary(args):
                         f"1.07 GB pinned host bank (plan + gather)", "gather_kernel", alg, 55.0, "pcie", clocks,
                         2 * steps, {"note": "peak = 55 GB/s, a nominal PCIe Gen5 x16 payload rate (not measured)"})
 
-    else:  # route-decode: BASELINE config 5 per-step routing on one of 8 shards
+    else:  # route-decode: benchmark config 5 per-step routing on one of 8 shards
         b, docs_local = 32, (N_DOCS + 7) // 8
         c = docs_local * CHUNKS_PER_DOC
         n_layers = 4
@@ -600,7 +600,7 @@ def run_secondary(args):
         clocks = sampler.stop()
         alg = c * HKV * D * 2 + b * HKV * D * 2
         _secondary_line(args, "decode-time routing layer-steps/s (one of 8 shards)", "layer-steps/s", 1e3 / ms, ms,
-                        f"BASELINE config 5 per-step routing: {b} sequences x 1 token against {c} chunks (400 MB shard), "
+                        f"benchmark config 5 per-step routing: {b} sequences x 1 token against {c} chunks (400 MB shard), "
                         f"{n_layers} distinct layers rotate", "route_tc_kernel", alg, pk["hbm_gbs"], "hbm", clocks,
                         5 * n_layers * 10 * steps, {"launch": "one CUDA graph per step (fold, reset, score, 2-level top-k)",
                                                     "route_kernel_ms": route_ms,
@@ -609,7 +609,7 @@ def run_secondary(args):
 
 
 # ------------------------------------------------------------------------------------------
-# BASELINE config 5: end-to-end sparse generation step (Qwen3-4B-shaped decoder, random weights)
+# benchmark config 5: end-to-end sparse generation step (Qwen3-4B-shaped decoder, random weights)
 # ------------------------------------------------------------------------------------------
 def run_generate(args):
     import torch
@@ -727,7 +727,7 @@ def run_generate(args):
             "metric": "sparse generation tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": new_tokens, "warmup": 3, "ms_per_step": ms_total / new_tokens, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"BASELINE config 5: Qwen3-4B-shaped decoder (36 layers, hidden 2560, 32q/8kv, d 128, FFN 9728, "
+            "config": {"workload": f"benchmark config 5: Qwen3-4B-shaped decoder (36 layers, hidden 2560, 32q/8kv, d 128, FFN 9728, "
                                    f"vocab 151936, random weights), routing in layers 18-35 every step against {n_docs} docs x "
                                    f"{CHUNKS_PER_DOC} chunks, top-{TOP_K}, batch {batch_total}, {local_ctx}-token local context, "
                                    f"{new_tokens} new tokens", "launch": mode,

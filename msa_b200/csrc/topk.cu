@@ -74,27 +74,41 @@ sort_topk_kernel(const uint32_t* __restrict__ keys, long long table_stride, int 
 // final k from the 8*k survivors.  Output order is descending by construction.
 constexpr int kSelectMaxK = 64;
 
-__device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const unsigned long long other = __shfl_xor_sync(0xffffffffu, v, o);
-    v = other > v ? other : v;
-  }
-  return v;
-}
-
 // k rounds over items[0..n) (shared memory, owned by this warp): writes the k largest, in order.
+// Every lane keeps the best of its own (strided) items in registers; a round is one redux on the
+// 32-bit score keys, a ballot (plus a second redux only when scores tie), and a rescan by the one
+// lane that lost its item.
 __device__ __forceinline__ void warp_extract_topk(unsigned long long* items, int n, int k, unsigned long long* out) {
   const int lane = threadIdx.x & 31;
-  for (int r = 0; r < k; ++r) {
-    unsigned long long best = 0ull;
-    int best_i = -1;
+  unsigned long long best = 0ull;
+  int best_i = -1;
+  auto rescan = [&]() {
+    best = 0ull;
+    best_i = -1;
     for (int i = lane; i < n; i += 32) {
       const unsigned long long v = items[i];
       if (v > best) { best = v; best_i = i; }
     }
-    const unsigned long long top = warp_max_u64(best);
-    if (top != 0ull && best == top) items[best_i] = 0ull;   // composite items are unique: one lane matches
+  };
+  rescan();
+  for (int r = 0; r < k; ++r) {
+    const uint32_t hi = (uint32_t)(best >> 32), lo = (uint32_t)best;
+    const uint32_t kmax = __reduce_max_sync(0xffffffffu, hi);
+    uint32_t tie = __ballot_sync(0xffffffffu, best != 0ull && hi == kmax);
+    if (__popc(tie) > 1) {  // equal scores: the smaller column (larger inverted column) goes first
+      const bool in_tie = (tie >> lane) & 1u;
+      const uint32_t lmax = __reduce_max_sync(0xffffffffu, in_tie ? lo : 0u);
+      tie = __ballot_sync(0xffffffffu, in_tie && lo == lmax);
+    }
+    unsigned long long top = 0ull;
+    if (tie != 0u) {
+      const int winner = __ffs(tie) - 1;
+      top = __shfl_sync(0xffffffffu, best, winner);
+      if (lane == winner) {
+        items[best_i] = 0ull;
+        rescan();
+      }
+    }
     if (lane == 0) out[r] = top;
     __syncwarp();
   }

@@ -13,7 +13,7 @@ in-place append, and the router layers route every step through ``MSAService``:
     of step t+1 reads it.
 
 So the host fetch never sits on the critical path: it overlaps the rest of the step.  (The
-reference routes once per round, in prefill stage 2; per-step routing is the variant BASELINE
+reference routes once per round, in prefill stage 2; per-step routing is the variant benchmark
 config 5 asks to time.)  KV layout per layer: ``[template t | retrieved k*c | local + generated]``.
 """
 from __future__ import annotations

@@ -1,6 +1,6 @@
 """Parity of every CUDA kernel (through the C ABI) with the oracle and the golden fixtures.
 
-Tolerances are BASELINE.json's: pooling and attention 1e-5 (fp32) / 1e-2 (bf16) norm-wise
+Tolerances: pooling and attention 1e-5 (fp32) / 1e-2 (bf16) norm-wise
 relative error, routing scores 1e-3 absolute, top-k exact outside a 1e-3 score gap.
 """
 import math
@@ -151,7 +151,7 @@ ROUTE_SHAPES = [
     (2, 300, 1, 64, (1, 20), 16),      # longer than a tile: sequence cut into two column tiles
     (32, 1, 4, 333, (1, 9), 16),       # decode-time routing: one token per sequence
     (5, 7, 4, 40, (1, 3), 8),          # short query padded to 16 rows
-    (2, 64, 1, 2000, (8, 8), 16),      # BASELINE config 1 shape (G = 1), 16,000 chunks
+    (2, 64, 1, 2000, (8, 8), 16),      # benchmark config 1 shape (G = 1), 16,000 chunks
     (6, 128, 4, 2600, (1, 16), 32),    # many tiles per CTA: exercises the ring and both accumulators
 ]
 

@@ -20,7 +20,7 @@ def ragged_docs(n_docs, lo, hi, seed):
 
 def make_bank(chunks_per_doc, hkv=8, d=128, dtype=torch.float32, seed=0, doc_mean_std=0.5, normalize=True):
     """Pooled router keys [C, Hkv, D] drawn per document as mean + noise (the distribution of
-    BASELINE config 3), plus the 1-based chunk->doc table."""
+    benchmark config 3), plus the 1-based chunk->doc table."""
     g = torch.Generator().manual_seed(seed)
     n_docs = len(chunks_per_doc)
     lens = torch.tensor(chunks_per_doc)
