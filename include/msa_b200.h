@@ -61,12 +61,15 @@ const char* msa_last_error(void);
  * pooled_doc_ids[c] = doc id owning chunk c; counts[0] = #document tokens,
  * counts[1] = #chunks, counts[2] = 1 if max_chunks was too small (outputs truncated).
  * token_index needs n_rows*row_len entries, chunk_offsets max_chunks+1, pooled_doc_ids
- * max_chunks.
+ * max_chunks.  workspace: device, 8-byte aligned, msa_bookkeeping_workspace_bytes() bytes
+ * (per-tile summaries of the multi-CTA scan).
  */
+int64_t msa_bookkeeping_workspace_bytes(int32_t n_rows, int32_t row_len);
+
 int msa_chunk_bookkeeping(const int64_t* doc_ids, const int64_t* attention_mask, int32_t n_rows,
                           int32_t row_len, int32_t pooling_kernel_size, int32_t* token_index,
                           int32_t* chunk_offsets, int64_t* pooled_doc_ids, int32_t max_chunks,
-                          int32_t* counts, void* stream);
+                          int32_t* counts, void* workspace, int64_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Stage 1: chunk-mean pooling (+ optional L2 normalisation of the pooled rows).

@@ -19,7 +19,7 @@ QREDUCE = {"max": 0, "mean": 1, "last": 2}
 ROUTE_FORCE_SIMT, ROUTE_NO_INIT = 1, 2
 
 EXPORTS = [
-    "msa_abi_version", "msa_last_error", "msa_chunk_bookkeeping", "msa_pool_chunks", "msa_fold_queries",
+    "msa_abi_version", "msa_last_error", "msa_bookkeeping_workspace_bytes", "msa_chunk_bookkeeping", "msa_pool_chunks", "msa_fold_queries",
     "msa_route_s_pad", "msa_selftest_bounded_wait", "msa_route_table_reset", "msa_route_scores", "msa_topk_workspace_bytes", "msa_topk_select", "msa_topk_merge", "msa_gather_plan",
     "msa_gather_run", "msa_bank_register_host", "msa_bank_unregister_host", "msa_decode_workspace_bytes", "msa_sparse_decode_attn",
     "msa_decode_static_scratch_bytes", "msa_sparse_decode_attn_static",
@@ -44,7 +44,9 @@ def lib() -> C.CDLL:
         vp, i32, i64, f32, u32 = C.c_void_p, C.c_int32, C.c_int64, C.c_float, C.c_uint32
         l.msa_last_error.restype = C.c_char_p
         l.msa_abi_version.restype = C.c_int
-        l.msa_chunk_bookkeeping.argtypes = [vp, vp, i32, i32, i32, vp, vp, vp, i32, vp, vp]
+        l.msa_bookkeeping_workspace_bytes.argtypes = [i32, i32]
+        l.msa_bookkeeping_workspace_bytes.restype = i64
+        l.msa_chunk_bookkeeping.argtypes = [vp, vp, i32, i32, i32, vp, vp, vp, i32, vp, vp, i64, vp]
         l.msa_pool_chunks.argtypes = [vp, i32, i64, i64, vp, vp, vp, i32, i32, i32, vp, i64, i64, i32, vp]
         l.msa_fold_queries.argtypes = [vp, i32, i64, i64, i64, vp, i64, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp]
         l.msa_route_s_pad.argtypes = [i32, i32]

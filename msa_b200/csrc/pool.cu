@@ -1,4 +1,4 @@
-// Stage-1 chunk bookkeeping and chunk-mean pooling.
+// Stage-1 chunk-mean pooling (the chunk tables it reads come from bookkeeping.cu).
 //
 // Pooling is a pure streaming reduction: every document token's [Hkv*D] row is read once
 // with 16-byte loads and a chunk's mean is written once, so the kernel is bound by HBM
@@ -6,120 +6,6 @@
 #include "common.cuh"
 
 namespace msa {
-
-// ---------------------------------------------------------------------------------------
-// Bookkeeping: one CTA walks the doc_ids of a block in three scan phases.
-// ---------------------------------------------------------------------------------------
-constexpr int kBkThreads = 1024;
-
-template <typename T, typename Op>
-__device__ inline T block_exclusive_scan(T v, T identity, Op op, T* smem, T* total) {
-  const int t = threadIdx.x;
-  smem[t] = v;
-  __syncthreads();
-  for (int d = 1; d < kBkThreads; d <<= 1) {
-    T other = (t >= d) ? smem[t - d] : identity;
-    __syncthreads();
-    smem[t] = op(other, smem[t]);
-    __syncthreads();
-  }
-  T incl_prev = (t > 0) ? smem[t - 1] : identity;
-  if (total) *total = smem[kBkThreads - 1];
-  __syncthreads();
-  return incl_prev;
-}
-
-struct LastGid {  // right-biased "last document token seen"
-  long long gid;
-  int has;
-};
-
-__global__ void __launch_bounds__(kBkThreads)
-bookkeeping_kernel(const int64_t* __restrict__ doc_ids, const int64_t* __restrict__ attn, int n_rows,
-                   int row_len, int P, int32_t* __restrict__ token_index,
-                   int32_t* __restrict__ chunk_offsets, int64_t* __restrict__ pooled_doc_ids,
-                   int max_chunks, int32_t* __restrict__ counts) {
-  __shared__ long long s_ll[kBkThreads];
-  __shared__ int s_int[kBkThreads];
-  __shared__ LastGid s_gid[kBkThreads];
-  const long long n = (long long)n_rows * row_len;
-  const long long seg = (n + kBkThreads - 1) / kBkThreads;
-  const long long lo = min(n, seg * threadIdx.x), hi = min(n, lo + seg);
-  auto is_doc = [&](long long i) { return doc_ids[i] > 0 && (attn == nullptr || attn[i] == 1); };
-  auto gid_of = [&](long long i) { return (long long)(i / row_len) * (1ll << 40) + doc_ids[i]; };
-
-  // phase 1: compact index of every document token, and the last document token before it
-  int cnt = 0;
-  LastGid last{0, 0};
-  for (long long i = lo; i < hi; ++i)
-    if (is_doc(i)) { ++cnt; last = LastGid{gid_of(i), 1}; }
-  int total_tokens;
-  int ci0 = block_exclusive_scan<int>(cnt, 0, [](int a, int b) { return a + b; }, s_int, &total_tokens);
-  LastGid prev0 = block_exclusive_scan<LastGid>(
-      last, LastGid{0, 0}, [](LastGid a, LastGid b) { return b.has ? b : a; }, s_gid, nullptr);
-
-  // phase 2: compact index at which the current document started
-  long long ds_local = -1;
-  {
-    int ci = ci0;
-    LastGid prev = prev0;
-    for (long long i = lo; i < hi; ++i)
-      if (is_doc(i)) {
-        long long g = gid_of(i);
-        if (!prev.has || prev.gid != g) ds_local = ci;
-        prev = LastGid{g, 1};
-        ++ci;
-      }
-  }
-  long long ds0 = block_exclusive_scan<long long>(
-      ds_local, -1ll, [](long long a, long long b) { return a > b ? a : b; }, s_ll, nullptr);
-
-  // phase 3: chunk starts
-  int nchunk_local = 0;
-  {
-    int ci = ci0;
-    LastGid prev = prev0;
-    long long ds = ds0;
-    for (long long i = lo; i < hi; ++i)
-      if (is_doc(i)) {
-        long long g = gid_of(i);
-        if (!prev.has || prev.gid != g) ds = ci;
-        prev = LastGid{g, 1};
-        if ((ci - ds) % P == 0) ++nchunk_local;
-        ++ci;
-      }
-  }
-  int total_chunks;
-  int ch0 = block_exclusive_scan<int>(nchunk_local, 0, [](int a, int b) { return a + b; }, s_int,
-                                      &total_chunks);
-  {
-    int ci = ci0, ch = ch0;
-    LastGid prev = prev0;
-    long long ds = ds0;
-    for (long long i = lo; i < hi; ++i)
-      if (is_doc(i)) {
-        long long g = gid_of(i);
-        if (!prev.has || prev.gid != g) ds = ci;
-        prev = LastGid{g, 1};
-        token_index[ci] = (int32_t)i;
-        if ((ci - ds) % P == 0) {
-          if (ch < max_chunks) {
-            chunk_offsets[ch] = ci;
-            pooled_doc_ids[ch] = doc_ids[i];
-          }
-          ++ch;
-        }
-        ++ci;
-      }
-  }
-  if (threadIdx.x == 0) {
-    const bool overflow = total_chunks > max_chunks;
-    chunk_offsets[overflow ? max_chunks : total_chunks] = total_tokens;
-    counts[0] = total_tokens;
-    counts[1] = overflow ? max_chunks : total_chunks;
-    counts[2] = overflow ? 1 : 0;
-  }
-}
 
 // ---------------------------------------------------------------------------------------
 // Pooling: one CTA per chunk, 256 threads, each thread owns one 16-byte column of the row.
@@ -198,20 +84,6 @@ pool_kernel(const T* __restrict__ states, long long token_stride, long long head
 }  // namespace msa
 
 using namespace msa;
-
-extern "C" int msa_chunk_bookkeeping(const int64_t* doc_ids, const int64_t* attention_mask, int32_t n_rows,
-                                     int32_t row_len, int32_t pooling_kernel_size, int32_t* token_index,
-                                     int32_t* chunk_offsets, int64_t* pooled_doc_ids, int32_t max_chunks,
-                                     int32_t* counts, void* stream) {
-  MSA_REQUIRE(doc_ids && token_index && chunk_offsets && pooled_doc_ids && counts, "bookkeeping: null pointer");
-  MSA_REQUIRE(n_rows >= 0 && row_len >= 0 && (int64_t)n_rows * row_len < (1ll << 31), "bookkeeping: bad sizes");
-  MSA_REQUIRE(pooling_kernel_size > 0 && max_chunks >= 0, "bookkeeping: pooling_kernel_size must be > 0");
-  bookkeeping_kernel<<<1, kBkThreads, 0, (cudaStream_t)stream>>>(doc_ids, attention_mask, n_rows, row_len,
-                                                                 pooling_kernel_size, token_index, chunk_offsets,
-                                                                 pooled_doc_ids, max_chunks, counts);
-  MSA_LAUNCH_OK("bookkeeping_kernel");
-  return MSA_OK;
-}
 
 extern "C" int msa_pool_chunks(const void* states, int32_t dtype, int64_t token_stride, int64_t head_stride,
                                const int32_t* token_index, const int32_t* chunk_offsets,

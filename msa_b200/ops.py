@@ -41,9 +41,12 @@ def chunk_bookkeeping(doc_ids: torch.Tensor, attention_mask: Optional[torch.Tens
     chunk_offsets = torch.empty(max_chunks + 1, dtype=torch.int32, device=dev)
     pooled = torch.empty(max(max_chunks, 1), dtype=torch.int64, device=dev)
     counts = torch.zeros(4, dtype=torch.int32, device=dev)
+    ws_bytes = int(A.lib().msa_bookkeeping_workspace_bytes(rows, row_len))
+    workspace = torch.empty((ws_bytes + 7) // 8, dtype=torch.int64, device=dev)
     A.check(A.lib().msa_chunk_bookkeeping(A.ptr(doc_ids), A.ptr(attention_mask), rows, row_len, pooling_kernel_size,
                                           A.ptr(token_index), A.ptr(chunk_offsets), A.ptr(pooled), max_chunks,
-                                          A.ptr(counts), A.stream_ptr(dev)), "msa_chunk_bookkeeping")
+                                          A.ptr(counts), A.ptr(workspace), workspace.numel() * 8, A.stream_ptr(dev)),
+            "msa_chunk_bookkeeping")
     n_tok, n_chunks, overflow, _ = counts.tolist()
     if overflow:
         raise A.MsaError(f"chunk_bookkeeping: more than max_chunks={max_chunks} chunks")

@@ -58,6 +58,31 @@ def test_bookkeeping_ragged_rows_and_padding(ops, rows):
     assert pooled.cpu().tolist() == ref_pooled.tolist()
 
 
+@pytest.mark.parametrize("p", [64, 7])
+def test_bookkeeping_long_documents_across_tiles(ops, p):
+    """Documents much longer than one 2048-token tile, single-token documents, masked tokens inside
+    documents and a document id that repeats after a gap: every tile boundary case of the multi-CTA scan."""
+    g = torch.Generator().manual_seed(p)
+    lens = [9000, 1, 1, 2047, 2049, 1, 4096, 3, 64, 63, 65, 5000] + torch.randint(1, 300, (200,), generator=g).tolist()
+    ids = [-2, -2, -2]
+    for i, n in enumerate(lens):
+        ids += [i + 1] * n
+        if i % 7 == 3:
+            ids += [0, 0, -1]                      # non-document tokens between documents
+    ids += [5] * 10                                # an id seen before, far away: a new document
+    doc_ids = torch.tensor([ids])
+    am = torch.ones_like(doc_ids)
+    am[0, 100:105] = 0                             # masked tokens inside the first document
+    am[0, 9003 + 2] = 0
+    tok, off, pooled = ops.chunk_bookkeeping(doc_ids.to(DEV), am.to(DEV), p)
+    di, gci, ref_pooled, ref_len = O.chunk_bookkeeping(doc_ids, am, p)
+    assert torch.equal(tok.cpu().long(), di[:, 1])
+    assert torch.equal((off[1:] - off[:-1]).cpu().long(), ref_len)
+    assert torch.equal(pooled.cpu(), ref_pooled)
+    with pytest.raises(Exception, match="max_chunks"):
+        ops.chunk_bookkeeping(doc_ids.to(DEV), am.to(DEV), p, max_chunks=5)
+
+
 def test_pooling_golden_fp32(ops, golden):
     g = golden("pooling_ragged")
     doc_ids, am = T(g["doc_ids"]).to(DEV), T(g["attention_mask"]).to(DEV)
