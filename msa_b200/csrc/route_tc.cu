@@ -149,9 +149,14 @@ __device__ __forceinline__ TileCoord tile_coord(const RouteTcParams& p, long lon
 // segment's first lane; the last lane of a segment publishes the document's score.  A document
 // that lies wholly inside this warp's 32 chunks (and whose sequence is not cut over several
 // column tiles) has no other writer: a plain store replaces the atomic.
-struct SegInfo { int doc, dist, max_len; bool publish, exclusive; };
+struct SegInfo { int doc, dist, max_len, n_seg; bool publish, exclusive; };
+struct SegEntry { int start, len, doc, exclusive; };   // one document's lanes inside a warp
+struct EpiScratch {                                      // per epilogue warp
+  float xpose[16][33];                                   // 16 columns x 32 lanes (+1 pad)
+  SegEntry seg[32];
+};
 
-__device__ __forceinline__ SegInfo seg_info(const RouteTcParams& p, int chunk, int lane) {
+__device__ __forceinline__ SegInfo seg_info(const RouteTcParams& p, int chunk, int lane, EpiScratch& scr) {
   const int doc = chunk < p.n_chunks ? p.chunk_doc[chunk] : -1 - lane;  // out-of-range lanes stay alone
   const int doc_up = __shfl_up_sync(0xffffffffu, doc, 1), doc_dn = __shfl_down_sync(0xffffffffu, doc, 1);
   const bool head = lane == 0 || doc_up != doc, tail = lane == 31 || doc_dn != doc;
@@ -166,13 +171,22 @@ __device__ __forceinline__ SegInfo seg_info(const RouteTcParams& p, int chunk, i
   if (lane == 31 && chunk + 1 < p.n_chunks) ends_here = p.chunk_doc[chunk + 1] != doc;
   const bool open_lo = !__shfl_sync(0xffffffffu, starts_here, 0), open_hi = !__shfl_sync(0xffffffffu, ends_here, 31);
   const bool crosses = (open_lo && head_lane == 0) || (open_hi && (heads >> lane) <= 1u);
-  return SegInfo{doc, dist, max_len, tail && doc > 0, !crosses && p.s_pad <= p.bn};
+  const bool exclusive = !crosses && p.s_pad <= p.bn;
+  // segment table: entry i describes the i-th run of lanes (documents and out-of-range lanes alike)
+  const int seg_idx = __popc(heads & ((1u << lane) - 1u));
+  if (head) {
+    const uint32_t later = lane == 31 ? 0u : (heads >> (lane + 1));
+    const int len = later ? __ffs(later) : 32 - lane;
+    scr.seg[seg_idx] = SegEntry{lane, len, doc, exclusive ? 1 : 0};
+  }
+  __syncwarp();
+  return SegInfo{doc, dist, max_len, __popc(heads), tail && doc > 0, exclusive};
 }
 
 // Reads this warp's 32 accumulator rows (one chunk per lane, p.bn columns) and publishes the
 // per-(sequence, document) maxima.
 __device__ __forceinline__ void epilogue_compute(const RouteTcParams& p, const SegInfo& si, const float* bias,
-                                                 uint32_t taddr, int q0) {
+                                                 uint32_t taddr, int q0, EpiScratch& scr, int lane) {
   const int seg = min(p.s_pad, p.bn);  // columns of one sequence inside a tile
   auto publish_score = [&](float v, int seq) {
     if (seq < p.n_seq) {
@@ -192,20 +206,32 @@ __device__ __forceinline__ void epilogue_compute(const RouteTcParams& p, const S
   // Segmented max over the lanes of a document: log2(longest segment) shuffle steps, done for a
   // whole batch of independent values at a time so that the shuffles pipeline.
   if (p.s_pad == 1) {  // every column is its own sequence
+    // 16 columns at a time go through shared memory: lane = chunk writes its 16 values, then the
+    // (document, column) pairs are dealt out over the lanes, so every lane reduces and publishes
+    // distinct pairs instead of all lanes shuffling every column.
+    const int n_items = si.n_seg * 16;
     for (int c0 = 0; c0 < p.bn; c0 += 16) {
       float v[16];
       load16(c0, v);
-      for (int d = 1; d < si.max_len; d <<= 1) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float o = __shfl_up_sync(0xffffffffu, v[j], d);
-          if (si.dist >= d) v[j] = fmaxf(v[j], o);
+      for (int j = 0; j < 16; ++j) scr.xpose[j][lane] = v[j];
+      __syncwarp();
+      for (int item = lane; item < n_items; item += 32) {
+        const SegEntry e = scr.seg[item >> 4];
+        const int j = item & 15;
+        if (e.doc > 0) {
+          float m = scr.xpose[j][e.start];
+          for (int t = 1; t < e.len; ++t) m = fmaxf(m, scr.xpose[j][e.start + t]);
+          const int seq = q0 + c0 + j;
+          if (seq < p.n_seq) {
+            const uint32_t key = float_to_key(m * p.alpha);
+            uint32_t* dst = p.keys + (long long)seq * p.table_stride + e.doc;
+            if (e.exclusive) *dst = max(key, p.min_key);
+            else atomicMax(dst, key);
+          }
         }
       }
-      if (si.publish) {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) publish_score(v[j], q0 + c0 + j);
-      }
+      __syncwarp();
     }
   } else {             // `seg` consecutive columns belong to one sequence: in-thread max first
     for (int s0 = 0; s0 < p.bn; s0 += seg) {
@@ -233,6 +259,7 @@ route_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constan
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
   __shared__ float s_bias[kEpiThreads / 32][kRouteMaxN];  // one private copy per epilogue warp
+  __shared__ EpiScratch s_epi[kEpiThreads / 32];
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
@@ -331,7 +358,7 @@ route_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constan
       float* bias = s_bias[warp];
       __syncwarp();  // the previous tile's reads of this warp's bias copy are done
       for (int j = lane; j < p.bn; j += 32) bias[j] = (q0 + j < p.n_rows) ? p.row_bias[q0 + j] : -INFINITY;
-      const SegInfo si = seg_info(p, tc.ct * kBM + (int)threadIdx.x, lane);
+      const SegInfo si = seg_info(p, tc.ct * kBM + (int)threadIdx.x, lane, s_epi[warp]);
       __syncwarp();
       // every lane waits; the warp then agrees on the outcome so that it never diverges
       ok = mbar_wait(&s_acc_full[buf], acc_phase, abort_flag, p.status, 4);
@@ -340,7 +367,7 @@ route_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constan
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)buf * kRouteMaxN;
 
-      epilogue_compute(p, si, bias, taddr, q0);
+      epilogue_compute(p, si, bias, taddr, q0, s_epi[warp], lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_acc_empty[buf]);
@@ -416,6 +443,7 @@ route_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
   __shared__ float s_bias[kEpiThreads / 32][kRouteMaxN];
+  __shared__ EpiScratch s_epi[kEpiThreads / 32];
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const uint32_t rank = cluster_ctarank();
@@ -514,14 +542,14 @@ route_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
       float* bias = s_bias[warp];
       __syncwarp();
       for (int j = lane; j < kPairBN; j += 32) bias[j] = (q0 + j < p.n_rows) ? p.row_bias[q0 + j] : -INFINITY;
-      const SegInfo si = seg_info(p, tc.ct * kPairBM + (int)rank * kBM + (int)threadIdx.x, lane);
+      const SegInfo si = seg_info(p, tc.ct * kPairBM + (int)rank * kBM + (int)threadIdx.x, lane, s_epi[warp]);
       __syncwarp();
       ok = mbar_wait(&s_acc_full[buf], acc_phase, abort_flag, p.status, 4);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)buf * kRouteMaxN;
-      epilogue_compute(p, si, bias, taddr, q0);
+      epilogue_compute(p, si, bias, taddr, q0, s_epi[warp], lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&s_acc_empty[buf]), 0));
@@ -611,7 +639,7 @@ int launch_route_tc(const void* qf, const float* row_bias, int n_seq, int s_pad,
   p.n_qtiles = (p.n_rows + p.bn - 1) / p.bn;
   p.k_blocks = kdim / kBK;
   const size_t stage_bytes = (size_t)kBM * kBK * 2 + (size_t)p.bn * kBK * 2;
-  p.stages = (int)((216 * 1024) / stage_bytes);
+  p.stages = (int)((204 * 1024) / stage_bytes);
   if (p.stages > kMaxStages) p.stages = kMaxStages;
   MSA_REQUIRE(p.stages >= 2, "route: tile does not fit shared memory");
   const size_t qtile_bytes = (size_t)p.bn * kdim * 2;
