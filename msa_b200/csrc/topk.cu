@@ -114,15 +114,53 @@ __device__ __forceinline__ void warp_extract_topk(unsigned long long* items, int
   }
 }
 
+// k <= 32 without serial rounds.  The k-th largest of the 32 per-lane maxima is a lower bound T of the
+// k-th largest item (k items are >= T), so only items >= T can win: they are compacted in place
+// (typically a few more than k survive) and ordered by counting.  `scratch` holds 32 items.
+__device__ __forceinline__ void warp_filter_topk(unsigned long long* items, int n, int k, unsigned long long* out,
+                                                 unsigned long long* scratch) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t lt_mask = (1u << lane) - 1u;
+  unsigned long long best = 0ull;
+  for (int i = lane; i < n; i += 32) best = items[i] > best ? items[i] : best;
+  scratch[lane] = best;
+  __syncwarp();
+  int rank = 0;
+#pragma unroll 8
+  for (int j = 0; j < 32; ++j) rank += (scratch[j] > best || (scratch[j] == best && j < lane)) ? 1 : 0;
+  const uint32_t kth = __ballot_sync(0xffffffffu, rank == k - 1);
+  const unsigned long long threshold = __shfl_sync(0xffffffffu, best, __ffs(kth) - 1);   // may be 0: keep everything
+  int n_c = 0;
+  for (int i0 = 0; i0 < n; i0 += 32) {
+    const int i = i0 + lane;
+    const unsigned long long v = i < n ? items[i] : 0ull;
+    const bool keep = v != 0ull && v >= threshold;
+    const uint32_t bal = __ballot_sync(0xffffffffu, keep);
+    __syncwarp();                                   // this row is in registers: its slots may be overwritten
+    if (keep) items[n_c + __popc(bal & lt_mask)] = v;
+    n_c += __popc(bal);
+  }
+  __syncwarp();
+  for (int c = lane; c < n_c; c += 32) {
+    const unsigned long long mine = items[c];
+    int r = 0;
+    for (int j = 0; j < n_c; ++j) r += items[j] > mine ? 1 : 0;   // composite items are unique
+    if (r < k) out[r] = mine;
+  }
+  for (int r = n_c + lane; r < k; r += 32) out[r] = 0ull;
+  __syncwarp();
+}
+
 template <bool FROM_KEYS>
 __global__ void __launch_bounds__(kSortThreads)
 select_topk_kernel(const uint32_t* __restrict__ keys, long long table_stride, int n_cols, int slice,
                    const unsigned long long* __restrict__ cand, int n_in, int n2, int keep,
-                   unsigned long long* __restrict__ cand_out, const int64_t* __restrict__ doc_ids_table,
-                   float* __restrict__ out_scores, int64_t* __restrict__ out_local, int64_t* __restrict__ out_global) {
+                   unsigned long long* __restrict__ cand_out, const int64_t* __restrict__ doc_ids_table, float* __restrict__ out_scores,
+                   int64_t* __restrict__ out_local, int64_t* __restrict__ out_global) {
   extern __shared__ unsigned long long s_items[];
   __shared__ unsigned long long s_win[(kSortThreads / 32) * kSelectMaxK];
   __shared__ unsigned long long s_final[kSelectMaxK];
+  __shared__ unsigned long long s_scratch[kSortThreads / 32][32];
   const int row = blockIdx.y, sl = blockIdx.x, warp = threadIdx.x >> 5, n_warps = kSortThreads / 32;
   if (FROM_KEYS) {
     const int c0 = sl * slice;
@@ -136,24 +174,31 @@ select_topk_kernel(const uint32_t* __restrict__ keys, long long table_stride, in
     for (int i = threadIdx.x; i < n2; i += kSortThreads) s_items[i] = i < n_in ? src[i] : 0ull;
   }
   __syncthreads();
-  const int seg = (n2 + n_warps - 1) / n_warps;
-  const int lo = min(n2, warp * seg), hi = min(n2, lo + seg);
-  warp_extract_topk(s_items + lo, hi - lo, keep, s_win + warp * keep);
-  __syncthreads();
-  if (warp == 0) warp_extract_topk(s_win, n_warps * keep, keep, s_final);
-  __syncthreads();
+  auto cta_select = [&](int n_items) {   // best `keep` of s_items[0..n_items) -> s_final, in order
+    const int seg = (n_items + n_warps - 1) / n_warps;
+    const int lo = min(n_items, warp * seg), hi = min(n_items, lo + seg);
+    if (keep <= 32) warp_filter_topk(s_items + lo, hi - lo, keep, s_win + warp * keep, s_scratch[warp]);
+    else warp_extract_topk(s_items + lo, hi - lo, keep, s_win + warp * keep);
+    __syncthreads();
+    if (warp == 0) {
+      if (keep <= 32) warp_filter_topk(s_win, n_warps * keep, keep, s_final, s_scratch[0]);
+      else warp_extract_topk(s_win, n_warps * keep, keep, s_final);
+    }
+    __syncthreads();
+  };
+  cta_select(n2);
   if (cand_out) {
     unsigned long long* dst = cand_out + ((long long)row * gridDim.x + sl) * keep;
     for (int i = threadIdx.x; i < keep; i += kSortThreads) dst[i] = s_final[i];
-  } else {
-    for (int i = threadIdx.x; i < keep; i += kSortThreads) {
-      const unsigned long long w = s_final[i];
-      const long long col = 0xffffffffu - (uint32_t)(w & 0xffffffffull);
-      const long long o = (long long)row * keep + i;
-      out_scores[o] = key_to_float((uint32_t)(w >> 32));
-      out_local[o] = col;
-      if (out_global) out_global[o] = doc_ids_table ? doc_ids_table[col] : col;
-    }
+    return;
+  }
+  for (int i = threadIdx.x; i < keep; i += kSortThreads) {
+    const unsigned long long w = s_final[i];
+    const long long col = 0xffffffffu - (uint32_t)(w & 0xffffffffull);
+    const long long o = (long long)row * keep + i;
+    out_scores[o] = key_to_float((uint32_t)(w >> 32));
+    out_local[o] = col;
+    if (out_global) out_global[o] = doc_ids_table ? doc_ids_table[col] : col;
   }
 }
 
@@ -241,21 +286,35 @@ extern "C" int msa_topk_select(const uint32_t* score_keys, int64_t table_stride,
   const bool small_k = k_eff <= kSelectMaxK;
   if (n_slices == 1) {
     const int n2 = pow2_ceil(n_cols);
-    (small_k ? select_topk_kernel<true> : sort_topk_kernel<true>)<<<dim3(1, n_seq), kSortThreads, (size_t)n2 * 8, st>>>(
-        score_keys, table_stride, n_cols, n2, nullptr, 0, n2, k_eff, nullptr, doc_ids_table, out_scores, out_local_ids,
-        out_global_ids);
-    MSA_LAUNCH_OK("sort_topk_kernel");
+    if (small_k)
+      select_topk_kernel<true><<<dim3(1, n_seq), kSortThreads, (size_t)n2 * 8, st>>>(
+          score_keys, table_stride, n_cols, n2, nullptr, 0, n2, k_eff, nullptr, doc_ids_table, out_scores,
+          out_local_ids, out_global_ids);
+    else
+      sort_topk_kernel<true><<<dim3(1, n_seq), kSortThreads, (size_t)n2 * 8, st>>>(
+          score_keys, table_stride, n_cols, n2, nullptr, 0, n2, k_eff, nullptr, doc_ids_table, out_scores,
+          out_local_ids, out_global_ids);
+    MSA_LAUNCH_OK("topk kernel");
     return MSA_OK;
   }
   MSA_REQUIRE(workspace && workspace_bytes >= msa_topk_workspace_bytes(n_seq, n_cols, k),
               "topk_select: workspace of %lld bytes needed", (long long)msa_topk_workspace_bytes(n_seq, n_cols, k));
   unsigned long long* cand = (unsigned long long*)workspace;
-  (small_k ? select_topk_kernel<true> : sort_topk_kernel<true>)<<<dim3(n_slices, n_seq), kSortThreads, (size_t)slice * 8, st>>>(
-      score_keys, table_stride, n_cols, slice, nullptr, 0, slice, k_eff, cand, nullptr, nullptr, nullptr, nullptr);
-  MSA_LAUNCH_OK("sort_topk_kernel (slices)");
   const int n_in = n_slices * k_eff, n2 = pow2_ceil(n_in);
-  (small_k ? select_topk_kernel<false> : sort_topk_kernel<false>)<<<dim3(1, n_seq), kSortThreads, (size_t)n2 * 8, st>>>(
-      nullptr, 0, 0, 0, cand, n_in, n2, k_eff, nullptr, doc_ids_table, out_scores, out_local_ids, out_global_ids);
+  if (small_k) {
+    select_topk_kernel<true><<<dim3(n_slices, n_seq), kSortThreads, (size_t)slice * 8, st>>>(
+        score_keys, table_stride, n_cols, slice, nullptr, 0, slice, k_eff, cand, nullptr, nullptr, nullptr, nullptr);
+    MSA_LAUNCH_OK("select_topk_kernel (slices)");
+    select_topk_kernel<false><<<dim3(1, n_seq), kSortThreads, (size_t)n2 * 8, st>>>(
+        nullptr, 0, 0, 0, cand, n_in, n2, k_eff, nullptr, doc_ids_table, out_scores, out_local_ids,
+        out_global_ids);
+  } else {
+    sort_topk_kernel<true><<<dim3(n_slices, n_seq), kSortThreads, (size_t)slice * 8, st>>>(
+        score_keys, table_stride, n_cols, slice, nullptr, 0, slice, k_eff, cand, nullptr, nullptr, nullptr, nullptr);
+    MSA_LAUNCH_OK("sort_topk_kernel (slices)");
+    sort_topk_kernel<false><<<dim3(1, n_seq), kSortThreads, (size_t)n2 * 8, st>>>(
+        nullptr, 0, 0, 0, cand, n_in, n2, k_eff, nullptr, doc_ids_table, out_scores, out_local_ids, out_global_ids);
+  }
   MSA_LAUNCH_OK("sort_topk_kernel (final)");
   return MSA_OK;
 }

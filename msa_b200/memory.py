@@ -361,7 +361,11 @@ class Memory:
         blk = self.blocks[layer_idx]
         keys, _ = ops.route_scores(q_folded, row_bias, n_seq, s_pad, blk.rk, desc.chunk_doc, desc.nr_docs,
                                    alpha=scale / n_heads, min_val=torch.finfo(blk.rk.dtype).min, status=self._status)
-        return ops.topk_select(keys, top_k, desc.doc_ids)
+        need = ops.topk_workspace_bytes(n_seq, desc.nr_docs + 1, top_k)
+        ws = getattr(self, "_topk_ws", None)
+        if need and (ws is None or ws.numel() * 8 < need):
+            ws = self._topk_ws = torch.empty((need + 7) // 8, dtype=torch.int64, device=self.device)
+        return ops.topk_select(keys, top_k, desc.doc_ids, workspace=ws if need else None)
 
     def prefill_stage2(self, layer_idx: int, query_states: torch.Tensor, query_mask: torch.Tensor):
         """src/msa_service.py:703-828.  query_states ``[B, Hkv, G, S, D]``, query_mask

@@ -154,6 +154,10 @@ def route_table_reset(keys: torch.Tensor, n_docs: int, min_val: float, status: O
                                           A.ptr(status), A.stream_ptr(keys.device)), "msa_route_table_reset")
 
 
+def topk_workspace_bytes(n_seq: int, n_cols: int, k: int) -> int:
+    return int(A.lib().msa_topk_workspace_bytes(n_seq, n_cols, k))
+
+
 def topk_select(keys: torch.Tensor, k: int, doc_ids_table: Optional[torch.Tensor] = None, n_cols: Optional[int] = None,
                 workspace: Optional[torch.Tensor] = None):
     """Exact top-k of every row of a key table.  Returns ``(scores f32, local_ids i64, global_ids i64)``,
@@ -168,7 +172,7 @@ def topk_select(keys: torch.Tensor, k: int, doc_ids_table: Optional[torch.Tensor
     glob = torch.empty((n_seq, k_eff), dtype=torch.int64, device=dev)
     need = int(A.lib().msa_topk_workspace_bytes(n_seq, n_cols, k))
     if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
-        workspace = torch.empty(need // 8, dtype=torch.int64, device=dev)
+        workspace = torch.empty((need + 7) // 8, dtype=torch.int64, device=dev)
     A.check(A.lib().msa_topk_select(A.ptr(keys), keys.stride(0), n_seq, n_cols, k, A.ptr(doc_ids_table),
                                     A.ptr(scores), A.ptr(local), A.ptr(glob), A.ptr(workspace),
                                     workspace.numel() * workspace.element_size() if workspace is not None else 0,
