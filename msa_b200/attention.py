@@ -11,8 +11,9 @@ What runs where:
     calls as in the reference; chunk bookkeeping, chunk-mean pooling of K, V, K_r and the L2
     normalisation of K_r run on this package's kernels;
   * stage 2: routing, merge and fetch happen inside ``memory_client.doc_query`` (this package's
-    ``MSAService``); the context assembly and the prefill attention follow the reference with
-    library calls, and the compact cache is allocated with room to append in place;
+    ``MSAService``); one kernel assembles [template | retrieved | query] into the left-padded
+    compact cache (allocated with room to append in place) and, for bf16 / head_dim 128, this
+    package's prefill attention kernel reads it there (other shapes: library attention call);
   * decode: this package's flash-decode kernel, in-place append, no ``torch.cat`` / ``repeat_kv``.
 The training forward (``_forward``) is out of scope and raises.
 """
@@ -211,50 +212,34 @@ class MemorySparseAttention(Qwen3Attention):
         else:
             n_sel = torch.zeros(bsz, dtype=torch.long, device=device)
 
-        num_q = attention_mask.sum(dim=1)
+        # One kernel builds the left-padded compact cache (reference :299-351) in storage with room to
+        # append decode tokens; attention then reads it in place (bf16 / head_dim 128: own kernel).
+        valid_q = attention_mask == 1
+        num_q = valid_q.sum(dim=1)
         t_len = template_k.shape[2]
         kv_lengths = t_len + n_sel + num_q
-        cu_q = F.pad(num_q.cumsum(0, dtype=torch.int32), (1, 0))
-        cu_kv = F.pad(kv_lengths.cumsum(0, dtype=torch.int32), (1, 0))
-        total_kv = int(cu_kv[-1].item())
-        valid_q = attention_mask == 1
-        q_final = query_states.permute(0, 2, 1, 3)[valid_q]
-        k_flat = torch.empty((n_kv, total_kv, d), device=device, dtype=dtype)
-        v_flat = torch.empty((n_kv, total_kv, d), device=device, dtype=dtype)
-        start = cu_kv[:-1].long()
-        t_idx = (torch.arange(t_len, device=device).unsqueeze(0) + start.unsqueeze(1)).flatten()
-        k_flat[:, t_idx] = template_k.expand(bsz, -1, -1, -1).permute(1, 0, 2, 3).reshape(n_kv, -1, d)
-        v_flat[:, t_idx] = template_v.expand(bsz, -1, -1, -1).permute(1, 0, 2, 3).reshape(n_kv, -1, d)
-        if final_k is not None and final_k.shape[1] > 0:
-            owner = torch.arange(bsz, device=device).repeat_interleave(n_sel)
-            first = F.pad(n_sel.cumsum(0), (1, 0))[:-1]
-            rank = torch.arange(owner.numel(), device=device) - first[owner]
-            dest = start[owner] + t_len + rank
-            k_flat[:, dest] = final_k
-            v_flat[:, dest] = final_v.to(device)
-        q_owner = torch.arange(bsz, device=device).repeat_interleave(num_q)
-        q_rank = (torch.cumsum(valid_q.int(), dim=1) - 1)[valid_q]
-        q_dest = (start + t_len + n_sel)[q_owner] + q_rank
-        k_flat[:, q_dest] = key_states.permute(1, 0, 2, 3).reshape(n_kv, -1, d)[:, valid_q.flatten()]
-        v_flat[:, q_dest] = value_states.permute(1, 0, 2, 3).reshape(n_kv, -1, d)[:, valid_q.flatten()]
-
-        out_flat = varlen_attention(q_final, k_flat.transpose(0, 1), v_flat.transpose(0, 1), cu_q, cu_kv,
-                                    int(num_q.max()), int(kv_lengths.max())).reshape(-1, n_heads * d)
-        attn_output = torch.zeros((bsz, q_len, n_heads * d), device=device, dtype=dtype)
-        attn_output[valid_q] = out_flat
-
-        # compact cache: left-padded like the reference (:344-356) plus room to append in place
         max_kv = int(kv_lengths.max())
-        cap = max_kv + int(cache.meta.get("max_generate_tokens", self.decode_reserve))
-        k_store = torch.zeros((bsz, n_kv, cap, d), dtype=dtype, device=device)
-        v_store = torch.zeros((bsz, n_kv, cap, d), dtype=dtype, device=device)
+        reserve = int(cache.meta.get("max_generate_tokens", self.decode_reserve))
+        k_store, v_store, kv_start, kv_len, q_tok, n_valid, _ = ops.assemble_context(
+            template_k, template_v, final_k, None if final_v is None else final_v.to(device), n_sel, key_states,
+            value_states, valid_q, max_kv, reserve)
         left_pad_mask = torch.arange(max_kv, device=device).unsqueeze(0) >= (max_kv - kv_lengths.unsqueeze(1))
-        k_store[:, :, :max_kv].permute(0, 2, 1, 3)[left_pad_mask] = k_flat.permute(1, 0, 2)
-        v_store[:, :, :max_kv].permute(0, 2, 1, 3)[left_pad_mask] = v_flat.permute(1, 0, 2)
+        if dtype == torch.bfloat16 and d == 128:
+            attn_output = ops.sparse_prefill_attn(query_states, k_store, v_store, kv_start, kv_len, q_tok, n_valid,
+                                                  self.scaling)
+        else:
+            cu_q = F.pad(num_q.cumsum(0, dtype=torch.int32), (1, 0))
+            cu_kv = F.pad(kv_lengths.cumsum(0, dtype=torch.int32), (1, 0))
+            k_flat = k_store[:, :, :max_kv].permute(0, 2, 1, 3)[left_pad_mask]
+            v_flat = v_store[:, :, :max_kv].permute(0, 2, 1, 3)[left_pad_mask]
+            out_flat = varlen_attention(query_states.permute(0, 2, 1, 3)[valid_q], k_flat, v_flat, cu_q, cu_kv,
+                                        int(num_q.max()), max_kv).reshape(-1, n_heads * d)
+            attn_output = torch.zeros((bsz, q_len, n_heads * d), device=device, dtype=dtype)
+            attn_output[valid_q] = out_flat
         cache_kwargs.update({
             "compacked_key_cache": k_store[:, :, :max_kv], "compacked_value_cache": v_store[:, :, :max_kv],
             "kv_lengths": kv_lengths, "attention_mask": left_pad_mask,
-            "_msa_b200_store": (k_store, v_store, (max_kv - kv_lengths).to(torch.int32), kv_lengths.to(torch.int32)),
+            "_msa_b200_store": (k_store, v_store, kv_start, kv_len),
         })
         cache.record_kwargs(self.layer_idx, cache_kwargs)
         return self.o_proj(attn_output), None

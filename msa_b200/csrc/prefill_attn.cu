@@ -1,0 +1,329 @@
+// Stage-2 sparse prefill: context assembly and causal attention over [template | retrieved | query].
+//
+// assemble_kernel builds, per sequence, the left-padded compact cache the reference assembles with
+// a dozen index_put / boolean-mask copies (src/msa/memory_sparse_attention.py:299-351), directly in
+// storage that has room to append decode tokens, and the rank -> token map of the valid query tokens.
+// prefill_attn_kernel is a flash-attention forward over that cache (bf16, head_dim 128): CTA = 64
+// query tokens of one head, 4 warps x 16 rows, K/V tiles of 64 keys double-buffered with cp.async,
+// mma.sync.m16n8k16, online softmax on the fragments, bottom-right aligned causal mask (a query token
+// sees the template, every retrieved entry and the query tokens up to itself).  The contexts are a few
+// hundred keys long, so the kernel is latency bound; the point is one launch instead of the gather /
+// scatter / re-pack sequence around a library call.
+#include "common.cuh"
+#include "mma_helpers.cuh"
+
+namespace msa {
+
+constexpr int kAsmThreads = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kAsmThreads)
+assemble_kernel(const T* __restrict__ tmpl_k, const T* __restrict__ tmpl_v, int t_len, const T* __restrict__ sel_k,
+                const T* __restrict__ sel_v, long long sel_head_stride, const int64_t* __restrict__ n_sel,
+                const T* __restrict__ q_k, const T* __restrict__ q_v, long long qs_b, long long qs_h, long long qs_s,
+                const uint8_t* __restrict__ valid, int S, int n_kv, int D, int max_kv, T* __restrict__ k_store,
+                T* __restrict__ v_store, long long st_b, long long st_h, int32_t* __restrict__ kv_start,
+                int32_t* __restrict__ kv_len, int32_t* __restrict__ q_tok, int32_t* __restrict__ num_q_out,
+                int32_t* __restrict__ error_flag) {
+  constexpr int V = Elem<T>::kVec;
+  __shared__ int s_warp[kAsmThreads / 32];
+  __shared__ int s_base;
+  __shared__ long long s_sel_off;
+  const int b = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    s_base = 0;
+    long long off = 0;
+    for (int i = 0; i < b; ++i) off += n_sel[i];
+    s_sel_off = off;
+  }
+  __syncthreads();
+  // rank -> token map of the valid query tokens (ordered compaction, 256 tokens per round)
+  for (int s0 = 0; s0 < S; s0 += kAsmThreads) {
+    const int s = s0 + tid;
+    const bool keep = s < S && valid[(long long)b * S + s] != 0;
+    const uint32_t bal = __ballot_sync(0xffffffffu, keep);
+    if (lane == 0) s_warp[warp] = __popc(bal);
+    __syncthreads();
+    int before = s_base;
+    for (int w = 0; w < warp; ++w) before += s_warp[w];
+    if (keep) q_tok[(long long)b * S + before + __popc(bal & ((1u << lane) - 1u))] = s;
+    __syncthreads();
+    if (tid == 0) {
+      int tot = 0;
+      for (int w = 0; w < kAsmThreads / 32; ++w) tot += s_warp[w];
+      s_base += tot;
+    }
+    __syncthreads();
+  }
+  const int num_q = s_base, ns = (int)n_sel[b];
+  const int len = t_len + ns + num_q;
+  const int start = max_kv - len;
+  if (tid == 0) {
+    kv_len[b] = len;
+    kv_start[b] = start;
+    num_q_out[b] = num_q;
+    if (start < 0) atomicExch(error_flag, 1);
+  }
+  if (start < 0) return;
+  __syncthreads();  // q_tok of this block is read back below
+  const int vec_row = D / V;
+  const long long total = (long long)n_kv * len * vec_row;
+  for (long long i = tid; i < total; i += kAsmThreads) {
+    const int dv = (int)(i % vec_row) * V;
+    const int e = (int)((i / vec_row) % len);
+    const int h = (int)(i / ((long long)vec_row * len));
+    const T *sk, *sv;
+    if (e < t_len) {
+      sk = tmpl_k + ((long long)h * t_len + e) * D + dv;
+      sv = tmpl_v + ((long long)h * t_len + e) * D + dv;
+    } else if (e < t_len + ns) {
+      const long long o = (long long)h * sel_head_stride + (s_sel_off + e - t_len) * D + dv;
+      sk = sel_k + o;
+      sv = sel_v + o;
+    } else {
+      const int tok = q_tok[(long long)b * S + (e - t_len - ns)];
+      const long long o = (long long)b * qs_b + (long long)h * qs_h + (long long)tok * qs_s + dv;
+      sk = q_k + o;
+      sv = q_v + o;
+    }
+    const long long d = (long long)b * st_b + (long long)h * st_h + (long long)(start + e) * D + dv;
+    *reinterpret_cast<uint4*>(k_store + d) = *reinterpret_cast<const uint4*>(sk);
+    *reinterpret_cast<uint4*>(v_store + d) = *reinterpret_cast<const uint4*>(sv);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+constexpr int kPfRows = 64;    // query tokens per CTA (16 per warp)
+constexpr int kPfKeys = 64;    // keys per tile
+constexpr int kPfTile = kPfKeys * kMmaRow;                 // one staged K (or V) tile
+constexpr int kPfSmem = kPfRows * kMmaRow + 4 * kPfTile;   // Q + 2 x (K, V)
+
+__device__ __forceinline__ void mma_bf16_full(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(128, 2)
+prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, long long q_sb, long long q_sh, long long q_ss,
+                    const __nv_bfloat16* __restrict__ k_store, const __nv_bfloat16* __restrict__ v_store, long long st_b,
+                    long long st_h, const int32_t* __restrict__ kv_start, const int32_t* __restrict__ kv_len,
+                    const int32_t* __restrict__ q_tok, const int32_t* __restrict__ num_q_arr, int S, int n_q_heads,
+                    int n_kv_heads, float scale_log2e, __nv_bfloat16* __restrict__ out) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int b = blockIdx.z, hq = blockIdx.y, r0 = blockIdx.x * kPfRows;
+  const int num_q = num_q_arr[b];
+  if (r0 >= num_q) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, quad = lane & 3;
+  const int len = kv_len[b], base_keys = len - num_q;   // keys every query token sees
+  const int hk = hq / (n_q_heads / n_kv_heads);
+  const long long kv_base = (long long)b * st_b + (long long)hk * st_h + (long long)kv_start[b] * kMmaD;
+  const int last_row = min(r0 + kPfRows, num_q) - 1;
+  const int n_keys = base_keys + last_row + 1;
+  const int n_tiles = (n_keys + kPfKeys - 1) / kPfKeys;
+
+  const uint32_t s_q = (uint32_t)__cvta_generic_to_shared(smem);
+  const uint32_t s_kv = s_q + kPfRows * kMmaRow;
+  // stage Q (rows beyond num_q are zero-filled)
+  for (int i = threadIdx.x; i < kPfRows * 16; i += 128) {
+    const int r = i >> 4, ch = i & 15;
+    const bool ok = r0 + r < num_q;
+    const int tok = ok ? q_tok[(long long)b * S + r0 + r] : 0;
+    cp_async16(s_q + r * kMmaRow + ch * 16, q + (long long)b * q_sb + (long long)hq * q_sh + (long long)tok * q_ss + ch * 8,
+               ok ? 16u : 0u);
+  }
+  auto issue = [&](int tile, int buf) {
+    const uint32_t kd = s_kv + buf * 2 * kPfTile, vd = kd + kPfTile;
+    for (int i = threadIdx.x; i < kPfKeys * 16; i += 128) {
+      const int r = i >> 4, ch = i & 15;
+      const int key = tile * kPfKeys + r;
+      const bool ok = key < n_keys;
+      const long long o = kv_base + (long long)(ok ? key : 0) * kMmaD + ch * 8;
+      cp_async16(kd + r * kMmaRow + ch * 16, k_store + o, ok ? 16u : 0u);
+      cp_async16(vd + r * kMmaRow + ch * 16, v_store + o, ok ? 16u : 0u);
+    }
+  };
+  issue(0, 0);
+  cp_async_commit();
+
+  float o[kMmaD / 8][4];
+#pragma unroll
+  for (int i = 0; i < kMmaD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const int row_rank[2] = {min(r0 + warp * 16 + g, num_q - 1), min(r0 + warp * 16 + g + 8, num_q - 1)};
+  const int limit[2] = {base_keys + row_rank[0], base_keys + row_rank[1]};   // last visible key of each row
+  uint32_t qa[kMmaD / 16][4];
+
+  for (int t = 0; t < n_tiles; ++t) {
+    const int buf = t & 1;
+    if (t + 1 < n_tiles) issue(t + 1, buf ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    if (t == 0) {   // query fragments, once
+      const int mi = lane >> 3, r = lane & 7;
+      const uint32_t a = s_q + (warp * 16 + (mi & 1) * 8 + r) * kMmaRow + (mi >> 1) * 16;
+#pragma unroll
+      for (int j = 0; j < kMmaD / 16; ++j) ldmatrix_x4(a + j * 32, qa[j][0], qa[j][1], qa[j][2], qa[j][3]);
+    }
+    const uint32_t kbuf = s_kv + buf * 2 * kPfTile, vbuf = kbuf + kPfTile;
+    // S = Q K^T : 16 rows x 64 keys per warp
+    float s[kPfKeys / 8][4];
+#pragma unroll
+    for (int nb = 0; nb < kPfKeys / 8; ++nb) { s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f; }
+    {
+      const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+      for (int nb = 0; nb < kPfKeys / 8; nb += 2) {
+        const uint32_t a = kbuf + ((nb + (mi >> 1)) * 8 + r) * kMmaRow + (mi & 1) * 16;
+#pragma unroll
+        for (int j = 0; j < kMmaD / 16; ++j) {
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4(a + j * 32, b0, b1, b2, b3);
+          mma_bf16_full(s[nb], qa[j], b0, b1);
+          mma_bf16_full(s[nb + 1], qa[j], b2, b3);
+        }
+      }
+    }
+    // causal mask + online softmax (rows g and g + 8 of this warp)
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nb = 0; nb < kPfKeys / 8; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = t * kPfKeys + nb * 8 + 2 * quad + (e & 1);
+        const int rr = e >> 1;
+        s[nb][e] = key <= limit[rr] ? s[nb][e] * scale_log2e : -INFINITY;
+        mx[rr] = fmaxf(mx[rr], s[nb][e]);
+      }
+    float f[2];
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
+      mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
+      const float m_new = fmaxf(m_run[rr], mx[rr]);   // finite from the first tile on: key 0 is visible to every row
+      f[rr] = exp2f(m_run[rr] - m_new);
+      m_run[rr] = m_new;
+    }
+    float sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nb = 0; nb < kPfKeys / 8; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        s[nb][e] = exp2f(s[nb][e] - m_run[e >> 1]);
+        sum[e >> 1] += s[nb][e];
+      }
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      sum[rr] += __shfl_xor_sync(0xffffffffu, sum[rr], 1);
+      sum[rr] += __shfl_xor_sync(0xffffffffu, sum[rr], 2);
+      l_run[rr] = l_run[rr] * f[rr] + sum[rr];
+    }
+#pragma unroll
+    for (int nb = 0; nb < kMmaD / 8; ++nb) { o[nb][0] *= f[0]; o[nb][1] *= f[0]; o[nb][2] *= f[1]; o[nb][3] *= f[1]; }
+    // O += P V
+    {
+      const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+      for (int kk = 0; kk < kPfKeys / 16; ++kk) {
+        uint32_t pa[4] = {pack_bf16(s[2 * kk][0], s[2 * kk][1]), pack_bf16(s[2 * kk][2], s[2 * kk][3]),
+                          pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3])};
+        const uint32_t a = vbuf + (kk * 16 + (mi & 1) * 8 + r) * kMmaRow + (mi >> 1) * 16;
+#pragma unroll
+        for (int nb = 0; nb < kMmaD / 8; nb += 2) {
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4_trans(a + nb * 16, b0, b1, b2, b3);
+          mma_bf16_full(o[nb], pa, b0, b1);
+          mma_bf16_full(o[nb + 1], pa, b2, b3);
+        }
+      }
+    }
+    __syncthreads();   // the tile's buffers may be refilled
+  }
+  cp_async_wait<0>();
+  // normalise and scatter to the tokens' positions
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    const int rank = r0 + warp * 16 + g + rr * 8;
+    if (rank >= num_q) continue;
+    const int tok = q_tok[(long long)b * S + rank];
+    const float inv = 1.f / l_run[rr];
+    __nv_bfloat16* dst = out + ((long long)b * S + tok) * n_q_heads * kMmaD + (long long)hq * kMmaD;
+#pragma unroll
+    for (int nb = 0; nb < kMmaD / 8; ++nb)
+      *reinterpret_cast<uint32_t*>(dst + nb * 8 + 2 * quad) = pack_bf16(o[nb][2 * rr] * inv, o[nb][2 * rr + 1] * inv);
+  }
+}
+
+}  // namespace msa
+
+using namespace msa;
+
+extern "C" int msa_assemble_context(const void* template_k, const void* template_v, int32_t template_len,
+                                    const void* sel_k, const void* sel_v, int64_t sel_head_stride, const int64_t* n_sel,
+                                    const void* q_k, const void* q_v, int64_t q_stride_b, int64_t q_stride_h,
+                                    int64_t q_stride_s, const uint8_t* valid, int32_t n_seq, int32_t seq_len,
+                                    int32_t n_kv_heads, int32_t head_dim, int32_t dtype, int32_t max_kv, void* k_store,
+                                    void* v_store, int64_t store_stride_b, int64_t store_stride_h, int32_t* kv_start,
+                                    int32_t* kv_len, int32_t* q_tok, int32_t* num_q, int32_t* error_flag, void* stream) {
+  MSA_REQUIRE(dtype_ok(dtype), "assemble: unknown dtype %d", dtype);
+  MSA_REQUIRE(n_sel && q_k && q_v && valid && k_store && v_store && kv_start && kv_len && q_tok && num_q && error_flag,
+              "assemble: null pointer");
+  MSA_REQUIRE(template_len == 0 || (template_k && template_v), "assemble: template pointers missing");
+  MSA_REQUIRE(n_seq >= 0 && seq_len >= 0 && n_kv_heads > 0 && head_dim > 0 && max_kv >= 0 && template_len >= 0,
+              "assemble: bad sizes");
+  const int vec = 16 / (int)dtype_size(dtype);
+  MSA_REQUIRE(head_dim % vec == 0 && q_stride_b % vec == 0 && q_stride_h % vec == 0 && q_stride_s % vec == 0 &&
+                  sel_head_stride % vec == 0 && store_stride_b % vec == 0 && store_stride_h % vec == 0,
+              "assemble: rows must keep 16-byte alignment");
+  MSA_REQUIRE(aligned16(q_k) && aligned16(q_v) && aligned16(k_store) && aligned16(v_store) &&
+                  (!sel_k || (aligned16(sel_k) && aligned16(sel_v))) &&
+                  (!template_k || (aligned16(template_k) && aligned16(template_v))),
+              "assemble: pointers must be 16-byte aligned");
+  if (n_seq == 0) return MSA_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  MSA_CUDA_OK(cudaMemsetAsync(error_flag, 0, sizeof(int32_t), st));
+  if (dtype == MSA_BF16)
+    assemble_kernel<__nv_bfloat16><<<n_seq, kAsmThreads, 0, st>>>(
+        (const __nv_bfloat16*)template_k, (const __nv_bfloat16*)template_v, template_len, (const __nv_bfloat16*)sel_k,
+        (const __nv_bfloat16*)sel_v, sel_head_stride, n_sel, (const __nv_bfloat16*)q_k, (const __nv_bfloat16*)q_v,
+        q_stride_b, q_stride_h, q_stride_s, valid, seq_len, n_kv_heads, head_dim, max_kv, (__nv_bfloat16*)k_store,
+        (__nv_bfloat16*)v_store, store_stride_b, store_stride_h, kv_start, kv_len, q_tok, num_q, error_flag);
+  else
+    assemble_kernel<float><<<n_seq, kAsmThreads, 0, st>>>(
+        (const float*)template_k, (const float*)template_v, template_len, (const float*)sel_k, (const float*)sel_v,
+        sel_head_stride, n_sel, (const float*)q_k, (const float*)q_v, q_stride_b, q_stride_h, q_stride_s, valid, seq_len,
+        n_kv_heads, head_dim, max_kv, (float*)k_store, (float*)v_store, store_stride_b, store_stride_h, kv_start,
+        kv_len, q_tok, num_q, error_flag);
+  MSA_LAUNCH_OK("assemble_kernel");
+  return MSA_OK;
+}
+
+extern "C" int msa_sparse_prefill_attn(const void* q, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                                       const void* k_store, const void* v_store, int64_t store_stride_b,
+                                       int64_t store_stride_h, const int32_t* kv_start, const int32_t* kv_len,
+                                       const int32_t* q_tok, const int32_t* num_q, int32_t n_seq, int32_t seq_len,
+                                       int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim, int32_t dtype,
+                                       float scale, void* out, void* stream) {
+  MSA_REQUIRE(q && k_store && v_store && kv_start && kv_len && q_tok && num_q && out, "prefill: null pointer");
+  MSA_REQUIRE(dtype == MSA_BF16 && head_dim == kMmaD,
+              "prefill: this kernel takes bf16 with head_dim 128 (other shapes use the library attention path)");
+  MSA_REQUIRE(n_seq >= 0 && seq_len >= 0 && n_q_heads > 0 && n_kv_heads > 0 && n_q_heads % n_kv_heads == 0 &&
+                  n_q_heads <= 65535 && n_seq <= 65535, "prefill: bad sizes");
+  MSA_REQUIRE(q_stride_b % 8 == 0 && q_stride_h % 8 == 0 && q_stride_s % 8 == 0 && store_stride_b % 8 == 0 &&
+                  store_stride_h % 8 == 0 && aligned16(q) && aligned16(k_store) && aligned16(v_store) && aligned16(out),
+              "prefill: rows must be 16-byte aligned");
+  if (n_seq == 0 || seq_len == 0) return MSA_OK;
+  static thread_local bool configured = false;
+  if (!configured) {
+    MSA_CUDA_OK(cudaFuncSetAttribute(prefill_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
+    configured = true;
+  }
+  dim3 grid((seq_len + kPfRows - 1) / kPfRows, n_q_heads, n_seq);
+  prefill_attn_kernel<<<grid, 128, kPfSmem, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)q, q_stride_b, q_stride_h, q_stride_s, (const __nv_bfloat16*)k_store,
+      (const __nv_bfloat16*)v_store, store_stride_b, store_stride_h, kv_start, kv_len, q_tok, num_q, seq_len, n_q_heads,
+      n_kv_heads, scale * 1.4426950408889634f, (__nv_bfloat16*)out);
+  MSA_LAUNCH_OK("prefill_attn_kernel");
+  return MSA_OK;
+}
