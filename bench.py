@@ -681,22 +681,27 @@ def run_generate(args):
     attn_ms = [pr["attn_start"][l].elapsed_time(pr["attn_end"][l]) for l in range(36)]
     svc.check_status()
 
-    def timed_run(with_fetch: bool):
-        """Capture one step in a CUDA graph (eager launches if capture is refused) and time new_tokens steps."""
+    def timed_run(with_fetch: bool, pipelined: bool = True):
+        """Capture one step in a CUDA graph (eager launches if capture is refused) and time new_tokens steps.
+        pipelined: the loop rotated to start at the first router layer (same tokens, one token per call)."""
         model.fetch_enabled = with_fetch
+        one_step = model.step_pipelined if pipelined else model.step
         mode = "cuda-graph"
         graph = torch.cuda.CUDAGraph()
+        model.prime()
         try:
             with torch.cuda.graph(graph):
-                model.step()
+                one_step()
             run = graph.replay
         except Exception as e:  # e.g. a collective that cannot be captured
-            mode, run, graph = f"eager ({type(e).__name__})", model.step, None
+            mode, run, graph = f"eager ({type(e).__name__})", one_step, None
             torch.cuda.synchronize(dev)
         model.reset()
+        model.prime()
         for _ in range(3):
             run()
         model.reset()
+        model.prime()               # outside the timed region: every timed call still runs all 36 layers
         sync_all()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -712,6 +717,7 @@ def run_generate(args):
         return float(t.item()), mode
 
     ms_nofetch, _ = timed_run(False)       # same step without the host fetch: what the fetch may hide behind
+    ms_plain, _ = timed_run(True, pipelined=False)   # unrotated loop: the fetch has only the rest of its own step
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -739,6 +745,9 @@ def run_generate(args):
             "per_layer": {"routing_ms_avg": sum(route_ms) / len(route_ms), "attention_ms_avg": sum(attn_ms) / len(attn_ms),
                           "measured": "eager step, CUDA events"},
             "fetch": {"ms_per_step_with_fetch": ms_total / new_tokens, "ms_per_step_without_fetch": ms_nofetch / new_tokens,
+                      "ms_per_step_unrotated_loop": ms_plain / new_tokens,
+                      "loop": "rotated to start at the first router layer: layers 18-35 of step t, sampling, layers 0-17 "
+                              "of step t+1; the fetch issued in step t is needed by layer 18 of step t+1",
                       "exposed_ms_per_step": max(0.0, (ms_total - ms_nofetch) / new_tokens),
                       "pcie_bytes_per_step_per_gpu": 18 * b * TOP_K * CHUNKS_PER_DOC * 2 * HKV * D * 2},
             "dense_weight_bytes_per_step": per_step_bytes, "clocks": clocks,

@@ -5,6 +5,8 @@
 // the device-visible mapping with 16-byte loads (PCIe reads, no staging copy, no host
 // thread involved) and scatters it into the head-major [Hkv, entries, D] layout the
 // attention path consumes.  Bound by PCIe bandwidth: 2*chunks*Hkv*D*e bytes per document.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace msa {
@@ -85,15 +87,16 @@ constexpr int kGatherThreads = 256;
 
 template <typename T>
 __global__ void __launch_bounds__(kGatherThreads)
-gather_kernel(const int64_t* __restrict__ plan, int n_kv_heads, int head_dim, T* __restrict__ out_k,
+gather_kernel(const int64_t* __restrict__ plan, int n_items, int n_kv_heads, int head_dim, T* __restrict__ out_k,
               T* __restrict__ out_v, long long out_head_stride, long long out_entries) {
   constexpr int V = Elem<T>::kVec;
-  const int64_t* row = plan + (long long)blockIdx.x * 4;
+  const int vec_half = n_kv_heads * head_dim / V;  // 16-byte vectors in one chunk's K (or V)
+  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+  const int64_t* row = plan + (long long)item * 4;
   const long long len = row[1];
-  if (len <= 0) return;
+  if (len <= 0) continue;
   const uint4* src = reinterpret_cast<const uint4*>((uintptr_t)row[0]);
   const long long dst0 = row[2];
-  const int vec_half = n_kv_heads * head_dim / V;  // 16-byte vectors in one chunk's K (or V)
   const long long n_vec = len * 2 * vec_half;
   // each thread keeps four independent 16-byte PCIe reads in flight
   for (long long v0 = threadIdx.x; v0 < n_vec; v0 += 4ll * kGatherThreads) {
@@ -117,6 +120,21 @@ gather_kernel(const int64_t* __restrict__ plan, int n_kv_heads, int head_dim, T*
       *reinterpret_cast<uint4*>(dst) = val[u];
     }
   }
+  }
+}
+
+// CTAs of one gather launch.  The link is saturated by a few hundred KB of reads in flight (16 KB per
+// CTA); more resident CTAs only queue reads inside the GPU, where they get in the way of the HBM traffic
+// of whatever kernel the fetch is meant to hide behind.  Measured on B200 (32 KiB documents): 49.8 GB/s
+// alone from 12 CTAs up; the HBM-bound decode-time scoring next to it loses 0.18 ms per layer with 512
+// CTAs and 0.05 ms with 16-32.  MSA_B200_GATHER_CTAS overrides the cap (tuning only).
+inline int gather_ctas(int n_items) {
+  static const int cap = [] {
+    const char* e = getenv("MSA_B200_GATHER_CTAS");
+    const int v = e ? atoi(e) : 0;
+    return v > 0 ? v : 24;
+  }();
+  return n_items < cap ? n_items : cap;
 }
 
 }  // namespace msa
@@ -150,11 +168,11 @@ extern "C" int msa_gather_run(const int64_t* plan, int32_t n_items, int32_t dtyp
   if (n_items == 0 || out_entries == 0) return MSA_OK;
   MSA_REQUIRE(out_k && out_v && aligned16(out_k) && aligned16(out_v), "gather_run: bad output pointers");
   if (dtype == MSA_BF16)
-    gather_kernel<__nv_bfloat16><<<n_items, kGatherThreads, 0, (cudaStream_t)stream>>>(
-        plan, n_kv_heads, head_dim, (__nv_bfloat16*)out_k, (__nv_bfloat16*)out_v, out_head_stride, out_entries);
+    gather_kernel<__nv_bfloat16><<<gather_ctas(n_items), kGatherThreads, 0, (cudaStream_t)stream>>>(
+        plan, n_items, n_kv_heads, head_dim, (__nv_bfloat16*)out_k, (__nv_bfloat16*)out_v, out_head_stride, out_entries);
   else
-    gather_kernel<float><<<n_items, kGatherThreads, 0, (cudaStream_t)stream>>>(
-        plan, n_kv_heads, head_dim, (float*)out_k, (float*)out_v, out_head_stride, out_entries);
+    gather_kernel<float><<<gather_ctas(n_items), kGatherThreads, 0, (cudaStream_t)stream>>>(
+        plan, n_items, n_kv_heads, head_dim, (float*)out_k, (float*)out_v, out_head_stride, out_entries);
   MSA_LAUNCH_OK("gather_kernel");
   return MSA_OK;
 }

@@ -12,7 +12,9 @@ in-place append, and the router layers route every step through ``MSAService``:
     side stream  ->  written into the "retrieved" segment of layer l's cache, where the attention
     of step t+1 reads it.
 
-So the host fetch never sits on the critical path: it overlaps the rest of the step.  (The
+So the host fetch never sits on the critical path: it overlaps the rest of the step, and with
+``step_pipelined`` (the loop rotated to start at the first router layer) also the router-free lower
+layers of the next step.  (The
 reference routes once per round, in prefill stage 2; per-step routing is the variant benchmark
 config 5 asks to time.)  KV layout per layer: ``[template t | retrieved k*c | local + generated]``.
 """
@@ -94,6 +96,11 @@ class SparseDecodeModel:
         self.attn_out = torch.empty((batch, s.n_q_heads * s.head_dim), dtype=dtype, device=device)
         self.fetch_stream = torch.cuda.Stream(device, priority=-1)   # its small copies go ahead of queued compute
         self.fetch_enabled = True
+        # the decode loop is cut at the first router layer (see step_pipelined)
+        self.split_layer = min(self.router_layers) if (self.router_layers and service is not None) else s.num_layers
+        self._x_mid = torch.zeros((batch, s.hidden), dtype=dtype, device=device)
+        self._cos = torch.zeros((batch, 1, s.head_dim), dtype=dtype, device=device)
+        self._sin = torch.zeros((batch, 1, s.head_dim), dtype=dtype, device=device)
         self.probe = None  # set to a dict to collect per-layer CUDA events (eager profiling step)
 
     # ------------------------------------------------------------------------------------
@@ -108,17 +115,13 @@ class SparseDecodeModel:
             e.record()
             self.probe.setdefault(name, {})[layer] = e
 
-    def step(self):
-        """One decode step for the whole batch; returns the next tokens ``[B]``."""
+    def _layers(self, x, lo, hi, fetch_done):
         s, B = self.s, self.batch
         main = torch.cuda.current_stream(self.device)
-        x = self.embed[self.tokens]
-        ang = self.positions.to(torch.float32).unsqueeze(-1) * self.inv_freq
-        emb = torch.cat([ang, ang], dim=-1)
-        cos, sin = emb.cos().to(self.dtype).unsqueeze(1), emb.sin().to(self.dtype).unsqueeze(1)
+        cos, sin = self._cos, self._sin
         nq, nkv, d = s.n_q_heads, s.n_kv_heads, s.head_dim
-        fetch_done = []
-        for l, p in enumerate(self.layers):
+        for l in range(lo, hi):
+            p = self.layers[l]
             h = F.rms_norm(x, (s.hidden,), p["w_in"], s.rms_eps)
             qkv = h @ p["w_qkv"]
             q = qkv[:, : nq * d].view(B, nq, d)
@@ -145,9 +148,9 @@ class SparseDecodeModel:
                 self.fetch_stream.wait_event(after_attn)
                 with torch.cuda.stream(self.fetch_stream):
                     fk, fv, n_sel, total = self.svc.fetch(local, rank, l, max_entries=B * self.retrieved)
-                    lo, hi = s.template_len, s.template_len + self.retrieved
-                    self.k_cache[l][:, :, lo:hi].copy_(fk.view(nkv, B, self.retrieved, d).permute(1, 0, 2, 3))
-                    self.v_cache[l][:, :, lo:hi].copy_(fv.view(nkv, B, self.retrieved, d).permute(1, 0, 2, 3))
+                    lo_, hi_ = s.template_len, s.template_len + self.retrieved
+                    self.k_cache[l][:, :, lo_:hi_].copy_(fk.view(nkv, B, self.retrieved, d).permute(1, 0, 2, 3))
+                    self.v_cache[l][:, :, lo_:hi_].copy_(fv.view(nkv, B, self.retrieved, d).permute(1, 0, 2, 3))
                     for t_ in (local, rank, fk, fv):
                         t_.record_stream(self.fetch_stream)
                     done = torch.cuda.Event(enable_timing=self.probe is not None)
@@ -157,15 +160,51 @@ class SparseDecodeModel:
             h = F.rms_norm(x, (s.hidden,), p["w_post"], s.rms_eps)
             gu = h @ p["w_gate_up"]
             x = x + (F.silu(gu[:, : s.ffn]) * gu[:, s.ffn:]) @ p["w_down"]
+        return x
+
+    def _front(self):
+        """Embedding, rotary tables and the layers below the first router layer -> ``self._x_mid``."""
+        ang = self.positions.to(torch.float32).unsqueeze(-1) * self.inv_freq
+        emb = torch.cat([ang, ang], dim=-1)
+        self._cos.copy_(emb.cos().unsqueeze(1))
+        self._sin.copy_(emb.sin().unsqueeze(1))
+        self._x_mid.copy_(self._layers(self.embed[self.tokens], 0, self.split_layer, []))
+
+    def _back(self):
+        """Router layers and everything above them, lm_head, greedy token, cache-length update."""
+        s = self.s
+        fetch_done = []
+        x = self._layers(self._x_mid, self.split_layer, s.num_layers, fetch_done)
         x = F.rms_norm(x, (s.hidden,), self.w_final, s.rms_eps)
         nxt = (x @ self.lm_head).argmax(dim=-1)
         self._mark("compute_end", 0)
-        main.wait_stream(self.fetch_stream)      # the step ends when the refreshed segments are in place
         if self.probe is not None:
             self.probe["fetch_done"] = fetch_done
         self.tokens.copy_(nxt)
         self.kv_len += 1
         self.positions += 1
+        return nxt
+
+    def step(self):
+        """One decode step for the whole batch; returns the next tokens ``[B]``.  The step ends when
+        the refreshed retrieved segments are in place."""
+        self._front()
+        nxt = self._back()
+        torch.cuda.current_stream(self.device).wait_stream(self.fetch_stream)
+        return nxt
+
+    def prime(self):
+        """Run the lower layers of the first step, so that ``step_pipelined`` can start at the router layers."""
+        self._front()
+
+    def step_pipelined(self):
+        """The same decode loop rotated by half a step: [router layers and above of step t, sampling, lower
+        layers of step t+1].  The tokens are those of ``step``; the host fetch issued by step t's router layers
+        now has the lower (router-free) layers of step t+1 to hide behind before anything reads what it
+        refreshes.  Call ``prime`` once before the first call.  One call = one token per sequence."""
+        nxt = self._back()
+        self._front()
+        torch.cuda.current_stream(self.device).wait_stream(self.fetch_stream)
         return nxt
 
     def reset(self):

@@ -64,3 +64,70 @@ def test_decode_step_matches_fp32_restatement():
             assert float((got - k_ref[l][:, :, L]).norm() / k_ref[l][:, :, L].norm()) < 2e-2
         tokens, kv_len, positions = nxt, kv_len + 1, positions + 1
         assert torch.equal(m.kv_len.cpu(), kv_len)
+
+
+def _routed_model(seed):
+    from msa_b200.decoder import DecoderShape, SparseDecodeModel
+    from msa_b200.memory import AttentionGeometry, Document, ModelConfig
+    from msa_b200.service import MSAService
+    from tests.util import make_bank
+    n_docs, cpd, top_k, hkv, d = 40, 4, 4, 8, 128
+    geo = AttentionGeometry(num_hidden_layers=4, num_attention_heads=32, num_key_value_heads=hkv, head_dim=d,
+                            dtype=torch.bfloat16)
+    svc = MSAService(0, None, ModelConfig(doc_top_k=top_k, router_layer_idx="2,3"), None, geo, world_size=1, rank=0)
+    svc.uniform_seqlen = True
+    docs = [Document(doc_id=i, num_chunks=cpd) for i in range(n_docs)]
+    layers = {}
+    for l in (2, 3):
+        rk, _ = make_bank([cpd] * n_docs, hkv, d, torch.bfloat16, seed=l)
+        g = torch.Generator().manual_seed(100 + l)
+        k = torch.randn(n_docs * cpd, hkv, d, generator=g).to(torch.bfloat16)
+        v = torch.randn(n_docs * cpd, hkv, d, generator=g).to(torch.bfloat16)
+        layers[l] = (k.to(DEV), v.to(DEV), rk.to(DEV))
+    svc.load_pooled(docs, layers)
+    shape = DecoderShape(num_layers=4, hidden=256, n_q_heads=32, n_kv_heads=hkv, head_dim=d, ffn=512, vocab=1000)
+    return SparseDecodeModel(shape, svc, [2, 3], batch=3, local_ctx=40, max_new=12, retrieved_entries=top_k * cpd,
+                             device=DEV, seed=seed)
+
+
+def test_pipelined_loop_produces_the_same_tokens_and_caches():
+    """step_pipelined is step rotated to start at the first router layer: same tokens, same caches (the
+    retrieved segments included), eagerly and replayed from a CUDA graph."""
+    a, b, c = _routed_model(9), _routed_model(9), _routed_model(9)
+    n = 5
+    toks_a = [a.step().cpu() for _ in range(n)]
+    b.prime()
+    toks_b = [b.step_pipelined().cpu() for _ in range(n)]
+    torch.cuda.synchronize()
+    for x, y in zip(toks_a, toks_b):
+        assert torch.equal(x, y)
+    for l in range(4):
+        # b has already run the lower layers of the next step: compare the positions both have written
+        L = int(a.kv_len[0])
+        assert torch.equal(a.k_cache[l][:, :, :L], b.k_cache[l][:, :, :L])
+        assert torch.equal(a.v_cache[l][:, :, :L], b.v_cache[l][:, :, :L])
+    # the retrieved segment really changed (the fetch ran)
+    fresh = _routed_model(9)
+    lo, hi = a.s.template_len, a.s.template_len + a.retrieved
+    assert not torch.equal(fresh.k_cache[2][:, :, lo:hi], a.k_cache[2][:, :, lo:hi])
+    # graph replay of the rotated loop
+    c.prime()
+    c.step_pipelined()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        c.step_pipelined()
+    c.reset()
+    c.tokens.copy_(_routed_model(9).tokens)
+    fresh2 = _routed_model(9)
+    for l in range(4):
+        c.k_cache[l].copy_(fresh2.k_cache[l])
+        c.v_cache[l].copy_(fresh2.v_cache[l])
+    c.prime()
+    toks_c = []
+    for _ in range(n):
+        graph.replay()
+        toks_c.append(c.tokens.cpu().clone())
+    for x, y in zip(toks_a, toks_c):
+        assert torch.equal(x, y)
+    a.svc.check_status()
