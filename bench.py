@@ -45,7 +45,7 @@ def parse():
     ap.add_argument("--queries", type=int, default=N_QUERIES)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--new-tokens", type=int, default=256, help="generate workload: tokens to decode")
-    ap.add_argument("--workload", default="routing", choices=["routing", "pooling", "decode", "fetch", "route-decode", "generate"],
+    ap.add_argument("--workload", default="routing", choices=["routing", "pooling", "decode", "fetch", "route-decode", "prefill", "generate"],
                     help="routing = the headline (default); the others time one secondary kernel each")
     return ap.parse_args()
 
@@ -561,6 +561,67 @@ def run_secondary(args):
                         f"{b} queries x top-{k} documents x {CHUNKS_PER_DOC} chunks = {alg / 1e6:.0f} MB per layer from a "
                         f"1.07 GB pinned host bank (plan + gather)", "gather_kernel", alg, 55.0, "pcie", clocks,
                         2 * steps, {"note": "peak = 55 GB/s, a nominal PCIe Gen5 x16 payload rate (not measured)"})
+
+    elif args.workload == "prefill":
+        # stage 2 of one layer: 32 queries x 128 tokens, each with 3 template entries and 16 documents x 8 chunks
+        # retrieved -> contexts of 259 keys; several layers' tensors rotate so that inputs exceed L2
+        b, s_q, t_len, n_ret, n_layers = 32, 128, 3, TOP_K * CHUNKS_PER_DOC, 6
+        layers = []
+        for _ in range(n_layers):
+            layers.append(dict(
+                q=torch.randn((b, HQ, s_q, D), generator=g, device=dev).to(torch.bfloat16),
+                k=torch.randn((b, HKV, s_q, D), generator=g, device=dev).to(torch.bfloat16),
+                v=torch.randn((b, HKV, s_q, D), generator=g, device=dev).to(torch.bfloat16),
+                tk=torch.randn((1, HKV, t_len, D), generator=g, device=dev).to(torch.bfloat16),
+                tv=torch.randn((1, HKV, t_len, D), generator=g, device=dev).to(torch.bfloat16),
+                sk=torch.randn((HKV, b * n_ret, D), generator=g, device=dev).to(torch.bfloat16),
+                sv=torch.randn((HKV, b * n_ret, D), generator=g, device=dev).to(torch.bfloat16)))
+        valid = torch.ones((b, s_q), dtype=torch.bool, device=dev)
+        n_sel = torch.full((b,), n_ret, dtype=torch.int64, device=dev)
+        max_kv = t_len + n_ret + s_q
+        ev = []
+
+        def step(timed=False):
+            for L in layers:
+                ks, vs, st, ln, qt, nq, _ = ops.assemble_context(L["tk"], L["tv"], L["sk"], L["sv"], n_sel, L["k"], L["v"],
+                                                                 valid, max_kv, 0)
+                if timed:
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                ops.sparse_prefill_attn(L["q"], ks, vs, st, ln, qt, nq)
+                if timed:
+                    e1.record()
+                    ev.append((e0, e1))
+        _time_ms(torch, lambda: step(True), 5, warmup)
+        attn_ms = statistics.mean([a.elapsed_time(b_) for a, b_ in ev[-5 * n_layers:]])
+        lib_ms = None
+        try:    # the library call the reference makes at this point, on the same packed shapes (context only)
+            from flash_attn import flash_attn_varlen_func
+            cu_q = torch.arange(0, (b + 1) * s_q, s_q, dtype=torch.int32, device=dev)
+            cu_k = torch.arange(0, (b + 1) * max_kv, max_kv, dtype=torch.int32, device=dev)
+            qp = torch.randn((b * s_q, HQ, D), generator=g, device=dev).to(torch.bfloat16)
+            kp = torch.randn((b * max_kv, HKV, D), generator=g, device=dev).to(torch.bfloat16)
+            vp = torch.randn((b * max_kv, HKV, D), generator=g, device=dev).to(torch.bfloat16)
+            lib_ms = _time_ms(torch, lambda: flash_attn_varlen_func(qp, kp, vp, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k,
+                                                                    max_seqlen_q=s_q, max_seqlen_k=max_kv, causal=True),
+                              steps, warmup)
+        except Exception:
+            pass
+        sampler.start()
+        ms = _time_ms(torch, step, steps, warmup) / n_layers
+        clocks = sampler.stop()
+        # bytes one layer must move: q read + out written, K/V of template/retrieved/query read and written once by
+        # the assembly and read once more by the attention (they stay in L2 in between)
+        kv_bytes = 2 * b * max_kv * HKV * D * 2
+        alg = 2 * b * HQ * s_q * D * 2 + 2 * kv_bytes
+        flops = 4.0 * b * HQ * D * sum(t_len + n_ret + i + 1 for i in range(s_q))
+        _secondary_line(args, "stage-2 sparse prefill layer-steps/s (assembly + attention)", "layer-steps/s", 1e3 / ms, ms,
+                        f"{b} queries x {s_q} tokens, {t_len} template + {n_ret} retrieved entries, 32q/8kv heads, d=128, "
+                        f"bf16, {n_layers} layers' tensors rotate (> L2)", "prefill_attn_kernel", alg, pk["hbm_gbs"], "hbm",
+                        clocks, 2 * n_layers * steps,
+                        {"attention_kernel_ms": attn_ms, "attention_tflops": flops / (attn_ms / 1e3) / 1e12,
+                         "library_varlen_attention_ms": lib_ms,
+                         "note": "contexts of a few hundred keys: the kernel is latency / issue bound, far from either roof"})
 
     else:  # route-decode: benchmark config 5 per-step routing on one of 8 shards
         b, docs_local = 32, (N_DOCS + 7) // 8

@@ -249,24 +249,26 @@ int msa_sparse_decode_attn(const void* q, int32_t dtype, void* k_cache, void* v_
  * msa_assemble_context writes, for sequence b, the entries [template | its n_sel[b] retrieved
  * entries | its valid query tokens] into k_store / v_store (element (b, h, pos, d) at
  * b*store_stride_b + h*store_stride_h + pos*D + d) at positions max_kv-len_b .. max_kv-1, i.e.
- * left padded like the reference's compact cache but inside storage that may be longer, so
- * decode can append in place.  template_*: [Hkv, t, D] contiguous; sel_*: [Hkv, sum(n_sel), D]
+ * left padded like the reference's compact cache but inside storage of store_len >= max_kv
+ * positions, so decode can append in place; every other position of the storage is zero-filled
+ * (the storage may be handed over uninitialised).  template_*: [Hkv, t, D] contiguous; sel_*: [Hkv, sum(n_sel), D]
  * with head stride sel_head_stride (msa_gather_run's output); q_k / q_v: this step's key/value
  * states [B, Hkv, S, D] by strides; valid: uint8 [B, S].  Outputs: kv_start[B], kv_len[B],
- * num_q[B] (valid query tokens), q_tok[B, S] (token index of the r-th valid token), error_flag
- * (1 if some len_b exceeds max_kv: nothing is written for that sequence).
+ * num_q[B] (valid query tokens), q_tok[B, S] (token index of the r-th valid token for r < num_q[b],
+ * then the other tokens in order), error_flag
+ * (1 if some len_b exceeds max_kv: that sequence's storage is zero-filled and its kv_start is negative).
  *
  * msa_sparse_prefill_attn (bf16, head_dim 128): out[b, tok, hq*D + d] for every valid query
  * token, attending to the template, all retrieved entries and the query tokens up to itself
  * (bottom-right aligned causal mask); q: [B, Hq, S, D] by strides; out: [B, S, Hq*D]
- * contiguous, positions of invalid tokens are left untouched.
+ * contiguous; the rows of invalid tokens are zero-filled.
  */
 int msa_assemble_context(const void* template_k, const void* template_v, int32_t template_len,
                          const void* sel_k, const void* sel_v, int64_t sel_head_stride,
                          const int64_t* n_sel, const void* q_k, const void* q_v, int64_t q_stride_b,
                          int64_t q_stride_h, int64_t q_stride_s, const uint8_t* valid, int32_t n_seq,
                          int32_t seq_len, int32_t n_kv_heads, int32_t head_dim, int32_t dtype,
-                         int32_t max_kv, void* k_store, void* v_store, int64_t store_stride_b,
+                         int32_t max_kv, int32_t store_len, void* k_store, void* v_store, int64_t store_stride_b,
                          int64_t store_stride_h, int32_t* kv_start, int32_t* kv_len, int32_t* q_tok,
                          int32_t* num_q, int32_t* error_flag, void* stream);
 

@@ -67,7 +67,7 @@ def lib() -> C.CDLL:
         l.msa_sparse_decode_attn.argtypes = [vp, i32, vp, vp, i64, i64, vp, vp, vp, vp, i32, i32, i32, i32, f32, vp,
                                              vp, i64, i32, vp]
         l.msa_assemble_context.argtypes = [vp, vp, i32, vp, vp, i64, vp, vp, vp, i64, i64, i64, vp, i32, i32, i32, i32, i32,
-                                           i32, vp, vp, i64, i64, vp, vp, vp, vp, vp, vp]
+                                           i32, i32, vp, vp, i64, i64, vp, vp, vp, vp, vp, vp]
         l.msa_sparse_prefill_attn.argtypes = [vp, i64, i64, i64, vp, vp, i64, i64, vp, vp, vp, vp, i32, i32, i32, i32, i32,
                                               i32, f32, vp, vp]
         l.msa_decode_static_scratch_bytes.restype = i64

@@ -4,10 +4,12 @@
 // a dozen index_put / boolean-mask copies (src/msa/memory_sparse_attention.py:299-351), directly in
 // storage that has room to append decode tokens, and the rank -> token map of the valid query tokens.
 // prefill_attn_kernel is a flash-attention forward over that cache (bf16, head_dim 128): CTA = 64
-// query tokens of one head, 4 warps x 16 rows, K/V tiles of 64 keys double-buffered with cp.async,
+// query tokens of one head, 4 warps x 16 rows, K/V tiles of 32 keys double-buffered with cp.async,
 // mma.sync.m16n8k16, online softmax on the fragments, bottom-right aligned causal mask (a query token
 // sees the template, every retrieved entry and the query tokens up to itself).  The contexts are a few
-// hundred keys long, so the kernel is latency bound; the point is one launch instead of the gather /
+// hundred keys long, so the kernel is latency bound: small tiles and query fragments re-read from
+// shared memory keep it at 128 registers and 51 KB, i.e. four CTAs per SM (two at 64-key tiles with
+// the query in registers measured 20 % slower).  The point is one launch instead of the gather /
 // scatter / re-pack sequence around a library call.
 #include "common.cuh"
 #include "mma_helpers.cuh"
@@ -15,21 +17,28 @@
 namespace msa {
 
 constexpr int kAsmThreads = 256;
+constexpr int kAsmSlices = 16;   // CTAs per sequence: the copy loop is dealt over them
 
+// Grid (kAsmSlices, B).  Every CTA of a sequence recomputes the (cheap) token compaction so that no CTA
+// waits for another; slice 0 publishes the lengths and the rank -> token map.  Positions outside
+// [start, max_kv) of the [0, cap) storage rows are zero-filled here, so the caller hands over
+// uninitialised storage.
 template <typename T>
 __global__ void __launch_bounds__(kAsmThreads)
 assemble_kernel(const T* __restrict__ tmpl_k, const T* __restrict__ tmpl_v, int t_len, const T* __restrict__ sel_k,
                 const T* __restrict__ sel_v, long long sel_head_stride, const int64_t* __restrict__ n_sel,
                 const T* __restrict__ q_k, const T* __restrict__ q_v, long long qs_b, long long qs_h, long long qs_s,
-                const uint8_t* __restrict__ valid, int S, int n_kv, int D, int max_kv, T* __restrict__ k_store,
+                const uint8_t* __restrict__ valid, int S, int n_kv, int D, int max_kv, int cap, T* __restrict__ k_store,
                 T* __restrict__ v_store, long long st_b, long long st_h, int32_t* __restrict__ kv_start,
                 int32_t* __restrict__ kv_len, int32_t* __restrict__ q_tok, int32_t* __restrict__ num_q_out,
                 int32_t* __restrict__ error_flag) {
   constexpr int V = Elem<T>::kVec;
+  extern __shared__ int32_t s_tok[];   // [S] rank -> token: the valid tokens in order, then the others in order
+  int32_t* s_pref = s_tok + S;         // [S] valid tokens before token s
   __shared__ int s_warp[kAsmThreads / 32];
   __shared__ int s_base;
   __shared__ long long s_sel_off;
-  const int b = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int b = blockIdx.y, slice = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     s_base = 0;
     long long off = 0;
@@ -46,7 +55,9 @@ assemble_kernel(const T* __restrict__ tmpl_k, const T* __restrict__ tmpl_v, int 
     __syncthreads();
     int before = s_base;
     for (int w = 0; w < warp; ++w) before += s_warp[w];
-    if (keep) q_tok[(long long)b * S + before + __popc(bal & ((1u << lane) - 1u))] = s;
+    const int mine = before + __popc(bal & ((1u << lane) - 1u));
+    if (keep) s_tok[mine] = s;
+    if (s < S) s_pref[s] = keep ? -1 : mine;
     __syncthreads();
     if (tid == 0) {
       int tot = 0;
@@ -56,22 +67,34 @@ assemble_kernel(const T* __restrict__ tmpl_k, const T* __restrict__ tmpl_v, int 
     __syncthreads();
   }
   const int num_q = s_base, ns = (int)n_sel[b];
+  for (int t = tid; t < S; t += kAsmThreads)
+    if (s_pref[t] >= 0) s_tok[num_q + t - s_pref[t]] = t;
+  __syncthreads();
   const int len = t_len + ns + num_q;
   const int start = max_kv - len;
-  if (tid == 0) {
-    kv_len[b] = len;
-    kv_start[b] = start;
-    num_q_out[b] = num_q;
-    if (start < 0) atomicExch(error_flag, 1);
+  if (slice == 0) {
+    if (tid == 0) {
+      kv_len[b] = len;
+      kv_start[b] = start;
+      num_q_out[b] = num_q;
+      if (start < 0) atomicExch(error_flag, 1);
+    }
+    for (int r = tid; r < S; r += kAsmThreads) q_tok[(long long)b * S + r] = s_tok[r];
   }
-  if (start < 0) return;
-  __syncthreads();  // q_tok of this block is read back below
   const int vec_row = D / V;
-  const long long total = (long long)n_kv * len * vec_row;
-  for (long long i = tid; i < total; i += kAsmThreads) {
+  const long long total = (long long)n_kv * cap * vec_row;
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  for (long long i = (long long)slice * kAsmThreads + tid; i < total; i += (long long)kAsmSlices * kAsmThreads) {
     const int dv = (int)(i % vec_row) * V;
-    const int e = (int)((i / vec_row) % len);
-    const int h = (int)(i / ((long long)vec_row * len));
+    const int pos = (int)((i / vec_row) % cap);
+    const int h = (int)(i / ((long long)vec_row * cap));
+    const long long d = (long long)b * st_b + (long long)h * st_h + (long long)pos * D + dv;
+    const int e = pos - start;
+    if (start < 0 || e < 0 || pos >= max_kv) {   // padding, reserve, or a sequence that does not fit
+      *reinterpret_cast<uint4*>(k_store + d) = zero;
+      *reinterpret_cast<uint4*>(v_store + d) = zero;
+      continue;
+    }
     const T *sk, *sv;
     if (e < t_len) {
       sk = tmpl_k + ((long long)h * t_len + e) * D + dv;
@@ -81,12 +104,10 @@ assemble_kernel(const T* __restrict__ tmpl_k, const T* __restrict__ tmpl_v, int 
       sk = sel_k + o;
       sv = sel_v + o;
     } else {
-      const int tok = q_tok[(long long)b * S + (e - t_len - ns)];
-      const long long o = (long long)b * qs_b + (long long)h * qs_h + (long long)tok * qs_s + dv;
+      const long long o = (long long)b * qs_b + (long long)h * qs_h + (long long)s_tok[e - t_len - ns] * qs_s + dv;
       sk = q_k + o;
       sv = q_v + o;
     }
-    const long long d = (long long)b * st_b + (long long)h * st_h + (long long)(start + e) * D + dv;
     *reinterpret_cast<uint4*>(k_store + d) = *reinterpret_cast<const uint4*>(sk);
     *reinterpret_cast<uint4*>(v_store + d) = *reinterpret_cast<const uint4*>(sv);
   }
@@ -94,7 +115,7 @@ assemble_kernel(const T* __restrict__ tmpl_k, const T* __restrict__ tmpl_v, int 
 
 // ---------------------------------------------------------------------------------------
 constexpr int kPfRows = 64;    // query tokens per CTA (16 per warp)
-constexpr int kPfKeys = 64;    // keys per tile
+constexpr int kPfKeys = 32;    // keys per tile
 constexpr int kPfTile = kPfKeys * kMmaRow;                 // one staged K (or V) tile
 constexpr int kPfSmem = kPfRows * kMmaRow + 4 * kPfTile;   // Q + 2 x (K, V)
 
@@ -104,7 +125,7 @@ __device__ __forceinline__ void mma_bf16_full(float (&c)[4], const uint32_t (&a)
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-__global__ void __launch_bounds__(128, 2)
+__global__ void __launch_bounds__(128, 4)
 prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, long long q_sb, long long q_sh, long long q_ss,
                     const __nv_bfloat16* __restrict__ k_store, const __nv_bfloat16* __restrict__ v_store, long long st_b,
                     long long st_h, const int32_t* __restrict__ kv_start, const int32_t* __restrict__ kv_len,
@@ -113,6 +134,13 @@ prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, long long q_sb, long lo
   extern __shared__ __align__(128) unsigned char smem[];
   const int b = blockIdx.z, hq = blockIdx.y, r0 = blockIdx.x * kPfRows;
   const int num_q = num_q_arr[b];
+  // ranks >= num_q are the tokens that take no part: their output rows are zero
+  for (int i = threadIdx.x; i < kPfRows * 16; i += 128) {
+    const int r = r0 + (i >> 4), ch = i & 15;
+    if (r >= num_q && r < S)
+      *reinterpret_cast<uint4*>(out + ((long long)b * S + q_tok[(long long)b * S + r]) * n_q_heads * kMmaD +
+                                (long long)hq * kMmaD + ch * 8) = make_uint4(0u, 0u, 0u, 0u);
+  }
   if (r0 >= num_q) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, quad = lane & 3;
   const int len = kv_len[b], base_keys = len - num_q;   // keys every query token sees
@@ -152,7 +180,8 @@ prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, long long q_sb, long lo
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const int row_rank[2] = {min(r0 + warp * 16 + g, num_q - 1), min(r0 + warp * 16 + g + 8, num_q - 1)};
   const int limit[2] = {base_keys + row_rank[0], base_keys + row_rank[1]};   // last visible key of each row
-  uint32_t qa[kMmaD / 16][4];
+  const int warp_limit = base_keys + min(r0 + warp * 16 + 15, num_q - 1);
+  const uint32_t q_frag = s_q + (warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * kMmaRow + (lane >> 4) * 16;
 
   for (int t = 0; t < n_tiles; ++t) {
     const int buf = t & 1;
@@ -160,12 +189,7 @@ prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, long long q_sb, long lo
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
-    if (t == 0) {   // query fragments, once
-      const int mi = lane >> 3, r = lane & 7;
-      const uint32_t a = s_q + (warp * 16 + (mi & 1) * 8 + r) * kMmaRow + (mi >> 1) * 16;
-#pragma unroll
-      for (int j = 0; j < kMmaD / 16; ++j) ldmatrix_x4(a + j * 32, qa[j][0], qa[j][1], qa[j][2], qa[j][3]);
-    }
+    if (t * kPfKeys <= warp_limit) {   // later tiles are wholly masked for every row of this warp
     const uint32_t kbuf = s_kv + buf * 2 * kPfTile, vbuf = kbuf + kPfTile;
     // S = Q K^T : 16 rows x 64 keys per warp
     float s[kPfKeys / 8][4];
@@ -173,15 +197,17 @@ prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, long long q_sb, long lo
     for (int nb = 0; nb < kPfKeys / 8; ++nb) { s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f; }
     {
       const int mi = lane >> 3, r = lane & 7;
+      const uint32_t a = kbuf + ((mi >> 1) * 8 + r) * kMmaRow + (mi & 1) * 16;
 #pragma unroll
-      for (int nb = 0; nb < kPfKeys / 8; nb += 2) {
-        const uint32_t a = kbuf + ((nb + (mi >> 1)) * 8 + r) * kMmaRow + (mi & 1) * 16;
+      for (int j = 0; j < kMmaD / 16; ++j) {   // independent accumulator chains per k-step
+        uint32_t qa[4];
+        ldmatrix_x4(q_frag + j * 32, qa[0], qa[1], qa[2], qa[3]);
 #pragma unroll
-        for (int j = 0; j < kMmaD / 16; ++j) {
+        for (int nb = 0; nb < kPfKeys / 8; nb += 2) {
           uint32_t b0, b1, b2, b3;
-          ldmatrix_x4(a + j * 32, b0, b1, b2, b3);
-          mma_bf16_full(s[nb], qa[j], b0, b1);
-          mma_bf16_full(s[nb + 1], qa[j], b2, b3);
+          ldmatrix_x4(a + nb * 8 * kMmaRow + j * 32, b0, b1, b2, b3);
+          mma_bf16_full(s[nb], qa, b0, b1);
+          mma_bf16_full(s[nb + 1], qa, b2, b3);
         }
       }
     }
@@ -214,11 +240,7 @@ prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, long long q_sb, long lo
         sum[e >> 1] += s[nb][e];
       }
 #pragma unroll
-    for (int rr = 0; rr < 2; ++rr) {
-      sum[rr] += __shfl_xor_sync(0xffffffffu, sum[rr], 1);
-      sum[rr] += __shfl_xor_sync(0xffffffffu, sum[rr], 2);
-      l_run[rr] = l_run[rr] * f[rr] + sum[rr];
-    }
+    for (int rr = 0; rr < 2; ++rr) l_run[rr] = l_run[rr] * f[rr] + sum[rr];   // this thread's share of the row sum
 #pragma unroll
     for (int nb = 0; nb < kMmaD / 8; ++nb) { o[nb][0] *= f[0]; o[nb][1] *= f[0]; o[nb][2] *= f[1]; o[nb][3] *= f[1]; }
     // O += P V
@@ -238,16 +260,20 @@ prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, long long q_sb, long lo
         }
       }
     }
+    }
     __syncthreads();   // the tile's buffers may be refilled
   }
   cp_async_wait<0>();
   // normalise and scatter to the tokens' positions
 #pragma unroll
   for (int rr = 0; rr < 2; ++rr) {
+    float l = l_run[rr];   // whole warp: the quad holds the four shares of a row's sum
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
     const int rank = r0 + warp * 16 + g + rr * 8;
     if (rank >= num_q) continue;
     const int tok = q_tok[(long long)b * S + rank];
-    const float inv = 1.f / l_run[rr];
+    const float inv = 1.f / l;
     __nv_bfloat16* dst = out + ((long long)b * S + tok) * n_q_heads * kMmaD + (long long)hq * kMmaD;
 #pragma unroll
     for (int nb = 0; nb < kMmaD / 8; ++nb)
@@ -263,15 +289,16 @@ extern "C" int msa_assemble_context(const void* template_k, const void* template
                                     const void* sel_k, const void* sel_v, int64_t sel_head_stride, const int64_t* n_sel,
                                     const void* q_k, const void* q_v, int64_t q_stride_b, int64_t q_stride_h,
                                     int64_t q_stride_s, const uint8_t* valid, int32_t n_seq, int32_t seq_len,
-                                    int32_t n_kv_heads, int32_t head_dim, int32_t dtype, int32_t max_kv, void* k_store,
-                                    void* v_store, int64_t store_stride_b, int64_t store_stride_h, int32_t* kv_start,
+                                    int32_t n_kv_heads, int32_t head_dim, int32_t dtype, int32_t max_kv,
+                                    int32_t store_len, void* k_store, void* v_store, int64_t store_stride_b, int64_t store_stride_h, int32_t* kv_start,
                                     int32_t* kv_len, int32_t* q_tok, int32_t* num_q, int32_t* error_flag, void* stream) {
   MSA_REQUIRE(dtype_ok(dtype), "assemble: unknown dtype %d", dtype);
   MSA_REQUIRE(n_sel && q_k && q_v && valid && k_store && v_store && kv_start && kv_len && q_tok && num_q && error_flag,
               "assemble: null pointer");
   MSA_REQUIRE(template_len == 0 || (template_k && template_v), "assemble: template pointers missing");
-  MSA_REQUIRE(n_seq >= 0 && seq_len >= 0 && n_kv_heads > 0 && head_dim > 0 && max_kv >= 0 && template_len >= 0,
-              "assemble: bad sizes");
+  MSA_REQUIRE(n_seq >= 0 && seq_len >= 0 && n_kv_heads > 0 && head_dim > 0 && max_kv >= 0 && template_len >= 0 &&
+                  store_len >= max_kv && n_seq <= 65535, "assemble: bad sizes");
+  MSA_REQUIRE((size_t)seq_len * 2 * sizeof(int32_t) <= 40 * 1024, "assemble: seq_len %d above 5120 tokens", seq_len);
   const int vec = 16 / (int)dtype_size(dtype);
   MSA_REQUIRE(head_dim % vec == 0 && q_stride_b % vec == 0 && q_stride_h % vec == 0 && q_stride_s % vec == 0 &&
                   sel_head_stride % vec == 0 && store_stride_b % vec == 0 && store_stride_h % vec == 0,
@@ -284,16 +311,17 @@ extern "C" int msa_assemble_context(const void* template_k, const void* template
   cudaStream_t st = (cudaStream_t)stream;
   MSA_CUDA_OK(cudaMemsetAsync(error_flag, 0, sizeof(int32_t), st));
   if (dtype == MSA_BF16)
-    assemble_kernel<__nv_bfloat16><<<n_seq, kAsmThreads, 0, st>>>(
+    assemble_kernel<__nv_bfloat16><<<dim3(kAsmSlices, n_seq), kAsmThreads, 2 * seq_len * sizeof(int32_t), st>>>(
         (const __nv_bfloat16*)template_k, (const __nv_bfloat16*)template_v, template_len, (const __nv_bfloat16*)sel_k,
         (const __nv_bfloat16*)sel_v, sel_head_stride, n_sel, (const __nv_bfloat16*)q_k, (const __nv_bfloat16*)q_v,
-        q_stride_b, q_stride_h, q_stride_s, valid, seq_len, n_kv_heads, head_dim, max_kv, (__nv_bfloat16*)k_store,
+        q_stride_b, q_stride_h, q_stride_s, valid, seq_len, n_kv_heads, head_dim, max_kv, store_len,
+        (__nv_bfloat16*)k_store,
         (__nv_bfloat16*)v_store, store_stride_b, store_stride_h, kv_start, kv_len, q_tok, num_q, error_flag);
   else
-    assemble_kernel<float><<<n_seq, kAsmThreads, 0, st>>>(
+    assemble_kernel<float><<<dim3(kAsmSlices, n_seq), kAsmThreads, 2 * seq_len * sizeof(int32_t), st>>>(
         (const float*)template_k, (const float*)template_v, template_len, (const float*)sel_k, (const float*)sel_v,
         sel_head_stride, n_sel, (const float*)q_k, (const float*)q_v, q_stride_b, q_stride_h, q_stride_s, valid, seq_len,
-        n_kv_heads, head_dim, max_kv, (float*)k_store, (float*)v_store, store_stride_b, store_stride_h, kv_start,
+        n_kv_heads, head_dim, max_kv, store_len, (float*)k_store, (float*)v_store, store_stride_b, store_stride_h, kv_start,
         kv_len, q_tok, num_q, error_flag);
   MSA_LAUNCH_OK("assemble_kernel");
   return MSA_OK;

@@ -285,32 +285,38 @@ def assemble_context(template_k, template_v, sel_k, sel_v, n_sel, key_states, va
     """Build the compact stage-2 cache.  template_* ``[1, Hkv, t, D]``; sel_* ``[Hkv, sumN, D]`` (or None);
     n_sel ``[B]`` int64; key_states / value_states ``[B, Hkv, S, D]``; valid ``[B, S]`` bool.
     Returns ``(k_store, v_store [B, Hkv, max_kv + reserve, D], kv_start, kv_len, q_tok, num_q, error_flag)``;
-    ``error_flag`` is 1 when some sequence is longer than ``max_kv`` (that sequence is left unwritten)."""
+    ``error_flag`` is 1 when some sequence is longer than ``max_kv`` (that sequence's storage is zeroed).
+    ``q_tok[b]`` lists the valid tokens in order, then the others."""
     A.need_cuda(template_k, sel_k, n_sel, key_states, valid)
     b, hkv, s, d = key_states.shape
     dev, dt = key_states.device, key_states.dtype
     if key_states.stride(3) != 1 or value_states.stride() != key_states.stride():
         key_states, value_states = key_states.contiguous(), value_states.contiguous()
     t_len = template_k.shape[2]
-    tk, tv = template_k.reshape(hkv, t_len, d).contiguous(), template_v.reshape(hkv, t_len, d).contiguous()
+    tk, tv = template_k.reshape(hkv, t_len, d), template_v.reshape(hkv, t_len, d)
+    if not tk.is_contiguous() or not tv.is_contiguous():
+        tk, tv = tk.contiguous(), tv.contiguous()
     if sel_k is not None and sel_k.shape[1] > 0:
-        sel_k, sel_v = sel_k.contiguous(), sel_v.contiguous()
+        if sel_k.stride(2) != 1 or sel_k.stride(1) != d or sel_v.stride() != sel_k.stride():
+            sel_k, sel_v = sel_k.contiguous(), sel_v.contiguous()
         sel_stride = sel_k.stride(0)
     else:
         sel_k = sel_v = None
         sel_stride = 0
-    k_store = torch.zeros((b, hkv, max_kv + reserve, d), dtype=dt, device=dev)
-    v_store = torch.zeros((b, hkv, max_kv + reserve, d), dtype=dt, device=dev)
-    kv_start = torch.empty(b, dtype=torch.int32, device=dev)
-    kv_len = torch.empty(b, dtype=torch.int32, device=dev)
-    num_q = torch.empty(b, dtype=torch.int32, device=dev)
-    q_tok = torch.zeros((b, max(s, 1)), dtype=torch.int32, device=dev)
-    err = torch.zeros(1, dtype=torch.int32, device=dev)
-    vmask = valid.reshape(b, s).to(torch.uint8).contiguous()
+    cap = max_kv + reserve
+    store = torch.empty((2, b, hkv, cap, d), dtype=dt, device=dev)     # the kernel writes every position
+    k_store, v_store = store[0], store[1]
+    meta = torch.empty(3 * b + 1, dtype=torch.int32, device=dev)
+    kv_start, kv_len, num_q, err = meta[:b], meta[b:2 * b], meta[2 * b:3 * b], meta[3 * b:]
+    q_tok = torch.empty((b, max(s, 1)), dtype=torch.int32, device=dev)
+    vmask = valid.reshape(b, s)
+    vmask = vmask.contiguous().view(torch.uint8) if vmask.dtype == torch.bool else vmask.to(torch.uint8).contiguous()
+    if n_sel.dtype != torch.int64 or not n_sel.is_contiguous():
+        n_sel = n_sel.to(torch.int64).contiguous()
     A.check(A.lib().msa_assemble_context(
-        A.ptr(tk), A.ptr(tv), t_len, A.ptr(sel_k), A.ptr(sel_v), sel_stride, A.ptr(n_sel.to(torch.int64).contiguous()),
+        A.ptr(tk), A.ptr(tv), t_len, A.ptr(sel_k), A.ptr(sel_v), sel_stride, A.ptr(n_sel),
         A.ptr(key_states), A.ptr(value_states), key_states.stride(0), key_states.stride(1), key_states.stride(2),
-        A.ptr(vmask), b, s, hkv, d, A.dtype_code(dt), max_kv, A.ptr(k_store), A.ptr(v_store), k_store.stride(0),
+        A.ptr(vmask), b, s, hkv, d, A.dtype_code(dt), max_kv, cap, A.ptr(k_store), A.ptr(v_store), k_store.stride(0),
         k_store.stride(1), A.ptr(kv_start), A.ptr(kv_len), A.ptr(q_tok), A.ptr(num_q), A.ptr(err), A.stream_ptr(dev)),
         "msa_assemble_context")
     return k_store, v_store, kv_start, kv_len, q_tok, num_q, err
@@ -318,13 +324,14 @@ def assemble_context(template_k, template_v, sel_k, sel_v, n_sel, key_states, va
 
 def sparse_prefill_attn(q: torch.Tensor, k_store, v_store, kv_start, kv_len, q_tok, num_q, scale: Optional[float] = None,
                         out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """q ``[B, Hq, S, D]`` (bf16, D = 128).  Returns ``[B, S, Hq*D]``; rows of invalid tokens are zero."""
+    """q ``[B, Hq, S, D]`` (bf16, D = 128).  Returns ``[B, S, Hq*D]``; rows of invalid tokens are zero
+    (written by the kernel: ``out`` may be uninitialised)."""
     A.need_cuda(q, k_store, v_store)
     b, hq, s, d = q.shape
     if q.stride(3) != 1:
         q = q.contiguous()
     if out is None:
-        out = torch.zeros((b, s, hq * d), dtype=q.dtype, device=q.device)
+        out = torch.empty((b, s, hq * d), dtype=q.dtype, device=q.device)
     scale = (1.0 / math.sqrt(d)) if scale is None else scale
     A.check(A.lib().msa_sparse_prefill_attn(
         A.ptr(q), q.stride(0), q.stride(1), q.stride(2), A.ptr(k_store), A.ptr(v_store), k_store.stride(0),
