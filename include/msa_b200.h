@@ -280,6 +280,29 @@ int msa_sparse_prefill_attn(const void* q, int64_t q_stride_b, int64_t q_stride_
                             float scale, void* out, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Stage-1 attention inside every document, with the chunk means of K and V as a by-product.
+ * Replaces flash_attn_varlen_func over the document tokens and the K / V pooling of
+ * src/msa/memory_sparse_attention.py:216-241 and :166-176 (bf16, head_dim 128).
+ *
+ * token_index[Td]: flat positions b*seq_len + s of the tokens that take part, document after
+ * document (msa_chunk_bookkeeping's order); seg_offsets[n_segments + 1]: where each document starts
+ * in token_index.  q: [B, Hq, S, D], k / v: [B, Hkv, S, D] by strides.  out: [B, S, Hq*D]
+ * contiguous; only the rows of listed tokens are written.  A token attends to the tokens of its own
+ * segment up to itself.  With chunk_offsets != NULL (msa_chunk_bookkeeping's table, n_chunks + 1
+ * entries, every document starting a chunk), pooled_k / pooled_v receive the mean K and V of every
+ * chunk (element (c, h, d) at c*pool_chunk_stride + h*pool_head_stride + d), accumulated in fp32 and
+ * rounded once; pool_size must be a multiple of 32.  K_r is not read by attention and is pooled by
+ * msa_pool_chunks.  At most 65535 segments per call.
+ */
+int msa_doc_attention_pool(const void* q, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                           const void* k, const void* v, int64_t k_stride_b, int64_t k_stride_h,
+                           int64_t k_stride_s, const int32_t* token_index, const int32_t* seg_offsets,
+                           int32_t n_segments, int32_t max_segment_len, int32_t seq_len, int32_t n_q_heads,
+                           int32_t n_kv_heads, int32_t head_dim, int32_t dtype, float scale, void* out,
+                           const int32_t* chunk_offsets, int32_t n_chunks, int32_t pool_size, void* pooled_k,
+                           void* pooled_v, int64_t pool_chunk_stride, int64_t pool_head_stride, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * Decode attention without any allocation.  (No counterpart in the reference: this entry
  * point exists for hosts of this library that cannot allocate device memory when a decode
  * step runs -- a serving loop whose pool already owns the whole GPU, a plugin that is handed

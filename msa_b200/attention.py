@@ -7,9 +7,10 @@ loads), same cache protocol (``cache_kwargs`` / ``meta`` / ``record_kwargs`` / `
 ``update_router_kcache``).
 
 What runs where:
-  * stage 1: projections, norms, RoPE and the intra-document attention stay PyTorch / library
-    calls as in the reference; chunk bookkeeping, chunk-mean pooling of K, V, K_r and the L2
-    normalisation of K_r run on this package's kernels;
+  * stage 1: projections, norms and RoPE stay PyTorch as in the reference; chunk bookkeeping, the
+    intra-document causal attention with the chunk means of K and V taken in the same pass (bf16,
+    head_dim 128; other shapes: library attention + the pooling kernel), the pooling of K_r and its
+    L2 normalisation run on this package's kernels;
   * stage 2: routing, merge and fetch happen inside ``memory_client.doc_query`` (this package's
     ``MSAService``); one kernel assembles [template | retrieved | query] into the left-padded
     compact cache (allocated with room to append in place) and, for bf16 / head_dim 128, this
@@ -129,19 +130,76 @@ class MemorySparseAttention(Qwen3Attention):
             cache.meta["_msa_b200_bookkeeping"] = hit
         return hit[1], hit[2], hit[3]
 
+    def _segments(self, doc_ids, attention_mask, cache):
+        """Token lists and segment offsets of the document tokens and of the template tokens of this block
+        (one segment per (row, document) run / per row); computed once and shared by every layer."""
+        key = (doc_ids.data_ptr(), attention_mask.data_ptr(), tuple(doc_ids.shape))
+        hit = cache.meta.get("_msa_b200_segments")
+        if hit is None or hit[0] != key:
+            s = doc_ids.shape[1]
+            valid = attention_mask == 1
+
+            def table(mask, ids):
+                tok = torch.nonzero(mask.flatten()).flatten()
+                if tok.numel() == 0:
+                    return tok.to(torch.int32), torch.zeros(1, dtype=torch.int32, device=tok.device), 0
+                gid = (tok // s) * (int(ids.max().item()) + 2) + ids.flatten()[tok]
+                _, counts = torch.unique_consecutive(gid, return_counts=True)
+                return (tok.to(torch.int32), F.pad(counts.cumsum(0), (1, 0)).to(torch.int32), int(counts.max().item()))
+            hit = (key, table((doc_ids > 0) & valid, doc_ids), table((doc_ids == -2) & valid, torch.zeros_like(doc_ids)))
+            cache.meta["_msa_b200_segments"] = hit
+        return hit[1], hit[2]
+
     def _stage1(self, hidden_states, doc_ids, attention_mask, cache, query_states, key_states, value_states):
         """src/msa/memory_sparse_attention.py:137-243."""
         bsz, q_len, _ = hidden_states.shape
         device, dtype = hidden_states.device, hidden_states.dtype
         hidden_shape = (bsz, q_len, -1, self.head_dim)
-        doc_token_mask = (doc_ids > 0) & (attention_mask == 1)
+        n_heads = self.config.num_attention_heads
+        own_attention = dtype == torch.bfloat16 and self.head_dim == 128
+        if self.is_router_layer and bsz != 1:
+            raise A.MsaError("stage 1 pools one block per call (the reference's worker uses batch size 1)")
+
+        # intra-document and template causal attention (:216-241)
+        attn_output = torch.zeros((bsz, q_len, n_heads * self.head_dim), device=device, dtype=dtype)
         pooled_k = pooled_v = pooled_rk = pooled_doc_ids = None
+        if own_attention:
+            (tok_d, off_d, max_d), (tok_t, off_t, max_t) = self._segments(doc_ids, attention_mask, cache)
+            if self.is_router_layer and self.pooling_kernel_size % 32 == 0:
+                # K and V are pooled from the tiles the attention kernel stages anyway
+                tok, off, pooled_doc_ids = self._bookkeeping(doc_ids, attention_mask, cache)
+                _, pooled_k, pooled_v = ops.doc_attention_pool(
+                    query_states, key_states, value_states, tok, off_d, max_d, out=attn_output, chunk_offsets=off,
+                    pool_size=self.pooling_kernel_size, head_major_out=True, scale=self.scaling)
+            else:
+                ops.doc_attention_pool(query_states, key_states, value_states, tok_d, off_d, max_d, out=attn_output,
+                                       scale=self.scaling)
+            ops.doc_attention_pool(query_states, key_states, value_states, tok_t, off_t, max_t, out=attn_output,
+                                   scale=self.scaling)
+        else:   # library calls, as in the reference
+            doc_token_mask = (doc_ids > 0) & (attention_mask == 1)
+            q_t, k_t, v_t = query_states.transpose(1, 2), key_states.transpose(1, 2), value_states.transpose(1, 2)
+            if doc_token_mask.any():
+                idx = torch.nonzero(doc_token_mask, as_tuple=False)
+                gid = idx[:, 0] * (int(doc_ids.max().item()) + 1) + doc_ids[doc_token_mask]
+                _, counts = torch.unique_consecutive(gid, return_counts=True)
+                cu = F.pad(torch.cumsum(counts, 0, dtype=torch.int32), (1, 0))
+                out = varlen_attention(q_t[doc_token_mask], k_t[doc_token_mask], v_t[doc_token_mask], cu, cu,
+                                       int(counts.max()), int(counts.max()))
+                attn_output[doc_token_mask] = out.reshape(-1, n_heads * self.head_dim)
+            template_mask = (doc_ids == -2) & (attention_mask == 1)
+            if template_mask.any():
+                counts = template_mask.sum(dim=1)
+                cu = F.pad(torch.cumsum(counts, 0, dtype=torch.int32), (1, 0))
+                out = varlen_attention(q_t[template_mask], k_t[template_mask], v_t[template_mask], cu, cu,
+                                       int(counts.max()), int(counts.max()))
+                attn_output[template_mask] = out.reshape(-1, n_heads * self.head_dim)
+
         if self.is_router_layer:
-            if bsz != 1:
-                raise A.MsaError("stage 1 pools one block per call (the reference's worker uses batch size 1)")
             tok, off, pooled_doc_ids = self._bookkeeping(doc_ids, attention_mask, cache)
-            pooled_k = ops.pool_chunks(key_states, off, tok, head_major_out=True)
-            pooled_v = ops.pool_chunks(value_states, off, tok, head_major_out=True)
+            if pooled_k is None:
+                pooled_k = ops.pool_chunks(key_states, off, tok, head_major_out=True)
+                pooled_v = ops.pool_chunks(value_states, off, tok, head_major_out=True)
             cosine = self.aux_loss_method == "INFONCE"
             if self.decouple_router:
                 r_k_raw = self.router_k_proj(hidden_states).view(hidden_shape).transpose(1, 2)
@@ -158,29 +216,8 @@ class MemorySparseAttention(Qwen3Attention):
             if pooled_rk is not None:
                 cache.update_router_kcache(pooled_rk, self.layer_idx)
         cache.record_kwargs(self.layer_idx, kw)
-
-        # intra-document and template causal attention: library calls, as in the reference (:216-241)
-        n_heads = self.config.num_attention_heads
-        attn_output = torch.zeros((bsz, q_len, n_heads * self.head_dim), device=device, dtype=dtype)
-        q_t, k_t, v_t = query_states.transpose(1, 2), key_states.transpose(1, 2), value_states.transpose(1, 2)
-        if doc_token_mask.any():
-            idx = torch.nonzero(doc_token_mask, as_tuple=False)
-            gid = idx[:, 0] * (int(doc_ids.max().item()) + 1) + doc_ids[doc_token_mask]
-            _, counts = torch.unique_consecutive(gid, return_counts=True)
-            cu = F.pad(torch.cumsum(counts, 0, dtype=torch.int32), (1, 0))
-            out = varlen_attention(q_t[doc_token_mask], k_t[doc_token_mask], v_t[doc_token_mask], cu, cu,
-                                   int(counts.max()), int(counts.max()))
-            attn_output[doc_token_mask] = out.reshape(-1, n_heads * self.head_dim)
-        template_mask = (doc_ids == -2) & (attention_mask == 1)
-        if template_mask.any():
-            counts = template_mask.sum(dim=1)
-            cu = F.pad(torch.cumsum(counts, 0, dtype=torch.int32), (1, 0))
-            out = varlen_attention(q_t[template_mask], k_t[template_mask], v_t[template_mask], cu, cu,
-                                   int(counts.max()), int(counts.max()))
-            attn_output[template_mask] = out.reshape(-1, n_heads * self.head_dim)
         return self.o_proj(attn_output), None
 
-    # ------------------------------------------------------------------------------------ stage 2
     def _stage2(self, hidden_states, doc_ids, attention_mask, cache, query_states, key_states, value_states):
         """src/msa/memory_sparse_attention.py:245-359."""
         bsz, q_len, _ = hidden_states.shape

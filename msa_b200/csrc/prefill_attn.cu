@@ -125,6 +125,108 @@ __device__ __forceinline__ void mma_bf16_full(float (&c)[4], const uint32_t (&a)
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// Running state of one warp's 16 query rows (this thread: rows g and g + 8, columns of its quad).
+struct AttnState {
+  float o[kMmaD / 8][4];
+  float m_run[2], l_run[2];   // l_run: this thread's share of the row sum (reduced over the quad at the end)
+  __device__ __forceinline__ void init() {
+#pragma unroll
+    for (int i = 0; i < kMmaD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    m_run[0] = m_run[1] = -INFINITY;
+    l_run[0] = l_run[1] = 0.f;
+  }
+};
+
+// One tile of kPfKeys keys against the warp's 16 rows: S = Q K^T, causal limit per row, online softmax,
+// O += P V.  q_frag / kbuf / vbuf are shared-memory addresses; key0 is the tile's first key; limit[rr]
+// is the last key row rr may see.  Key 0 is visible to every row, so the running maximum is finite from
+// the first tile on.
+__device__ __forceinline__ void attn_tile(AttnState& st, uint32_t q_frag, uint32_t kbuf, uint32_t vbuf, int key0,
+                                          const int (&limit)[2], float scale_log2e, int lane) {
+  const int quad = lane & 3, mi = lane >> 3, r = lane & 7;
+  float s[kPfKeys / 8][4];
+#pragma unroll
+  for (int nb = 0; nb < kPfKeys / 8; ++nb) { s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f; }
+  {
+    const uint32_t a = kbuf + ((mi >> 1) * 8 + r) * kMmaRow + (mi & 1) * 16;
+#pragma unroll
+    for (int j = 0; j < kMmaD / 16; ++j) {   // independent accumulator chains per k-step
+      uint32_t qa[4];
+      ldmatrix_x4(q_frag + j * 32, qa[0], qa[1], qa[2], qa[3]);
+#pragma unroll
+      for (int nb = 0; nb < kPfKeys / 8; nb += 2) {
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(a + nb * 8 * kMmaRow + j * 32, b0, b1, b2, b3);
+        mma_bf16_full(s[nb], qa, b0, b1);
+        mma_bf16_full(s[nb + 1], qa, b2, b3);
+      }
+    }
+  }
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int nb = 0; nb < kPfKeys / 8; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int key = key0 + nb * 8 + 2 * quad + (e & 1);
+      const int rr = e >> 1;
+      s[nb][e] = key <= limit[rr] ? s[nb][e] * scale_log2e : -INFINITY;
+      mx[rr] = fmaxf(mx[rr], s[nb][e]);
+    }
+  float f[2];
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
+    mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
+    const float m_new = fmaxf(st.m_run[rr], mx[rr]);
+    f[rr] = exp2f(st.m_run[rr] - m_new);
+    st.m_run[rr] = m_new;
+  }
+  float sum[2] = {0.f, 0.f};
+#pragma unroll
+  for (int nb = 0; nb < kPfKeys / 8; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      s[nb][e] = exp2f(s[nb][e] - st.m_run[e >> 1]);
+      sum[e >> 1] += s[nb][e];
+    }
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) st.l_run[rr] = st.l_run[rr] * f[rr] + sum[rr];
+#pragma unroll
+  for (int nb = 0; nb < kMmaD / 8; ++nb) {
+    st.o[nb][0] *= f[0]; st.o[nb][1] *= f[0]; st.o[nb][2] *= f[1]; st.o[nb][3] *= f[1];
+  }
+#pragma unroll
+  for (int kk = 0; kk < kPfKeys / 16; ++kk) {
+    uint32_t pa[4] = {pack_bf16(s[2 * kk][0], s[2 * kk][1]), pack_bf16(s[2 * kk][2], s[2 * kk][3]),
+                      pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3])};
+    const uint32_t a = vbuf + (kk * 16 + (mi & 1) * 8 + r) * kMmaRow + (mi >> 1) * 16;
+#pragma unroll
+    for (int nb = 0; nb < kMmaD / 8; nb += 2) {
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4_trans(a + nb * 16, b0, b1, b2, b3);
+      mma_bf16_full(st.o[nb], pa, b0, b1);
+      mma_bf16_full(st.o[nb + 1], pa, b2, b3);
+    }
+  }
+}
+
+// Normalise the warp's rows and write row rr of this thread to dst[rr] (nullptr: the row does not exist).
+__device__ __forceinline__ void attn_store(const AttnState& st, __nv_bfloat16* const (&dst)[2], int lane) {
+  const int quad = lane & 3;
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    float l = st.l_run[rr];   // whole warp: the quad holds the four shares of a row's sum
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (dst[rr] == nullptr) continue;
+    const float inv = 1.f / l;
+#pragma unroll
+    for (int nb = 0; nb < kMmaD / 8; ++nb)
+      *reinterpret_cast<uint32_t*>(dst[rr] + nb * 8 + 2 * quad) =
+          pack_bf16(st.o[nb][2 * rr] * inv, st.o[nb][2 * rr + 1] * inv);
+  }
+}
+
 __global__ void __launch_bounds__(128, 4)
 prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, long long q_sb, long long q_sh, long long q_ss,
                     const __nv_bfloat16* __restrict__ k_store, const __nv_bfloat16* __restrict__ v_store, long long st_b,
@@ -142,7 +244,7 @@ prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, long long q_sb, long lo
                                 (long long)hq * kMmaD + ch * 8) = make_uint4(0u, 0u, 0u, 0u);
   }
   if (r0 >= num_q) return;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, quad = lane & 3;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2;
   const int len = kv_len[b], base_keys = len - num_q;   // keys every query token sees
   const int hk = hq / (n_q_heads / n_kv_heads);
   const long long kv_base = (long long)b * st_b + (long long)hk * st_h + (long long)kv_start[b] * kMmaD;
@@ -174,10 +276,8 @@ prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, long long q_sb, long lo
   issue(0, 0);
   cp_async_commit();
 
-  float o[kMmaD / 8][4];
-#pragma unroll
-  for (int i = 0; i < kMmaD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  AttnState st;
+  st.init();
   const int row_rank[2] = {min(r0 + warp * 16 + g, num_q - 1), min(r0 + warp * 16 + g + 8, num_q - 1)};
   const int limit[2] = {base_keys + row_rank[0], base_keys + row_rank[1]};   // last visible key of each row
   const int warp_limit = base_keys + min(r0 + warp * 16 + 15, num_q - 1);
@@ -190,95 +290,131 @@ prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, long long q_sb, long lo
     cp_async_wait<1>();
     __syncthreads();
     if (t * kPfKeys <= warp_limit) {   // later tiles are wholly masked for every row of this warp
-    const uint32_t kbuf = s_kv + buf * 2 * kPfTile, vbuf = kbuf + kPfTile;
-    // S = Q K^T : 16 rows x 64 keys per warp
-    float s[kPfKeys / 8][4];
-#pragma unroll
-    for (int nb = 0; nb < kPfKeys / 8; ++nb) { s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f; }
-    {
-      const int mi = lane >> 3, r = lane & 7;
-      const uint32_t a = kbuf + ((mi >> 1) * 8 + r) * kMmaRow + (mi & 1) * 16;
-#pragma unroll
-      for (int j = 0; j < kMmaD / 16; ++j) {   // independent accumulator chains per k-step
-        uint32_t qa[4];
-        ldmatrix_x4(q_frag + j * 32, qa[0], qa[1], qa[2], qa[3]);
-#pragma unroll
-        for (int nb = 0; nb < kPfKeys / 8; nb += 2) {
-          uint32_t b0, b1, b2, b3;
-          ldmatrix_x4(a + nb * 8 * kMmaRow + j * 32, b0, b1, b2, b3);
-          mma_bf16_full(s[nb], qa, b0, b1);
-          mma_bf16_full(s[nb + 1], qa, b2, b3);
-        }
-      }
-    }
-    // causal mask + online softmax (rows g and g + 8 of this warp)
-    float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-    for (int nb = 0; nb < kPfKeys / 8; ++nb)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = t * kPfKeys + nb * 8 + 2 * quad + (e & 1);
-        const int rr = e >> 1;
-        s[nb][e] = key <= limit[rr] ? s[nb][e] * scale_log2e : -INFINITY;
-        mx[rr] = fmaxf(mx[rr], s[nb][e]);
-      }
-    float f[2];
-#pragma unroll
-    for (int rr = 0; rr < 2; ++rr) {
-      mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
-      mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
-      const float m_new = fmaxf(m_run[rr], mx[rr]);   // finite from the first tile on: key 0 is visible to every row
-      f[rr] = exp2f(m_run[rr] - m_new);
-      m_run[rr] = m_new;
-    }
-    float sum[2] = {0.f, 0.f};
-#pragma unroll
-    for (int nb = 0; nb < kPfKeys / 8; ++nb)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        s[nb][e] = exp2f(s[nb][e] - m_run[e >> 1]);
-        sum[e >> 1] += s[nb][e];
-      }
-#pragma unroll
-    for (int rr = 0; rr < 2; ++rr) l_run[rr] = l_run[rr] * f[rr] + sum[rr];   // this thread's share of the row sum
-#pragma unroll
-    for (int nb = 0; nb < kMmaD / 8; ++nb) { o[nb][0] *= f[0]; o[nb][1] *= f[0]; o[nb][2] *= f[1]; o[nb][3] *= f[1]; }
-    // O += P V
-    {
-      const int mi = lane >> 3, r = lane & 7;
-#pragma unroll
-      for (int kk = 0; kk < kPfKeys / 16; ++kk) {
-        uint32_t pa[4] = {pack_bf16(s[2 * kk][0], s[2 * kk][1]), pack_bf16(s[2 * kk][2], s[2 * kk][3]),
-                          pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3])};
-        const uint32_t a = vbuf + (kk * 16 + (mi & 1) * 8 + r) * kMmaRow + (mi >> 1) * 16;
-#pragma unroll
-        for (int nb = 0; nb < kMmaD / 8; nb += 2) {
-          uint32_t b0, b1, b2, b3;
-          ldmatrix_x4_trans(a + nb * 16, b0, b1, b2, b3);
-          mma_bf16_full(o[nb], pa, b0, b1);
-          mma_bf16_full(o[nb + 1], pa, b2, b3);
-        }
-      }
-    }
+      const uint32_t kbuf = s_kv + buf * 2 * kPfTile;
+      attn_tile(st, q_frag, kbuf, kbuf + kPfTile, t * kPfKeys, limit, scale_log2e, lane);
     }
     __syncthreads();   // the tile's buffers may be refilled
   }
   cp_async_wait<0>();
-  // normalise and scatter to the tokens' positions
+  __nv_bfloat16* dst[2];
 #pragma unroll
   for (int rr = 0; rr < 2; ++rr) {
-    float l = l_run[rr];   // whole warp: the quad holds the four shares of a row's sum
-    l += __shfl_xor_sync(0xffffffffu, l, 1);
-    l += __shfl_xor_sync(0xffffffffu, l, 2);
     const int rank = r0 + warp * 16 + g + rr * 8;
-    if (rank >= num_q) continue;
-    const int tok = q_tok[(long long)b * S + rank];
-    const float inv = 1.f / l;
-    __nv_bfloat16* dst = out + ((long long)b * S + tok) * n_q_heads * kMmaD + (long long)hq * kMmaD;
-#pragma unroll
-    for (int nb = 0; nb < kMmaD / 8; ++nb)
-      *reinterpret_cast<uint32_t*>(dst + nb * 8 + 2 * quad) = pack_bf16(o[nb][2 * rr] * inv, o[nb][2 * rr + 1] * inv);
+    dst[rr] = rank < num_q ? out + ((long long)b * S + q_tok[(long long)b * S + rank]) * n_q_heads * kMmaD +
+                                 (long long)hq * kMmaD
+                           : nullptr;
   }
+  attn_store(st, dst, lane);
+}
+
+// ---------------------------------------------------------------------------------------
+// Stage 1: causal attention inside every document, with the chunk means of K and V taken from the
+// tiles the kernel has staged anyway (src/msa/memory_sparse_attention.py:216-241 and :166-176).
+//
+// A segment is a run seg_off[i] .. seg_off[i+1] of token_index (flat positions b*S + s of the tokens
+// of one document, in order).  CTA = 64 query tokens of one head of one segment; K/V rows are fetched
+// through the index, so masked tokens inside a document simply do not appear.  The CTA of a segment's
+// last row block walks over every key of the document: for the first head of each kv group it also
+// sums the staged rows per chunk (pool_size keys, a multiple of the tile) in fp32 and writes the
+// chunk's mean, rounded once, to the bank's pooled K and V.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128, 4)
+doc_attn_pool_kernel(const __nv_bfloat16* __restrict__ q, long long q_sb, long long q_sh, long long q_ss,
+                     const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v, long long k_sb,
+                     long long k_sh, long long k_ss, const int32_t* __restrict__ token_index,
+                     const int32_t* __restrict__ seg_off, int S, int n_q_heads, int n_kv_heads, float scale_log2e,
+                     __nv_bfloat16* __restrict__ out, const int32_t* __restrict__ chunk_offsets, int n_chunks,
+                     int pool_size, __nv_bfloat16* __restrict__ pooled_k, __nv_bfloat16* __restrict__ pooled_v,
+                     long long pool_chunk_stride, long long pool_head_stride) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int seg = blockIdx.z, hq = blockIdx.y, r0 = blockIdx.x * kPfRows;
+  const int t0 = seg_off[seg], len = seg_off[seg + 1] - t0;
+  if (r0 >= len) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2;
+  const int grp = n_q_heads / n_kv_heads, hk = hq / grp;
+  const int last_row = min(r0 + kPfRows, len) - 1;
+  const int n_keys = last_row + 1;
+  const int n_tiles = (n_keys + kPfKeys - 1) / kPfKeys;
+  const bool pools = chunk_offsets != nullptr && last_row == len - 1 && hq % grp == 0;
+  const int32_t* tix = token_index + t0;
+
+  const uint32_t s_q = (uint32_t)__cvta_generic_to_shared(smem);
+  const uint32_t s_kv = s_q + kPfRows * kMmaRow;
+  for (int i = threadIdx.x; i < kPfRows * 16; i += 128) {
+    const int r = i >> 4, ch = i & 15;
+    const bool ok = r0 + r < len;
+    const int tok = ok ? tix[r0 + r] : 0;
+    cp_async16(s_q + r * kMmaRow + ch * 16,
+               q + (long long)(tok / S) * q_sb + (long long)hq * q_sh + (long long)(tok % S) * q_ss + ch * 8, ok ? 16u : 0u);
+  }
+  auto issue = [&](int tile, int buf) {
+    const uint32_t kd = s_kv + buf * 2 * kPfTile, vd = kd + kPfTile;
+    for (int i = threadIdx.x; i < kPfKeys * 16; i += 128) {
+      const int r = i >> 4, ch = i & 15;
+      const int key = tile * kPfKeys + r;
+      const bool ok = key < n_keys;
+      const int tok = ok ? tix[key] : 0;
+      const long long o = (long long)(tok / S) * k_sb + (long long)hk * k_sh + (long long)(tok % S) * k_ss + ch * 8;
+      cp_async16(kd + r * kMmaRow + ch * 16, k + o, ok ? 16u : 0u);
+      cp_async16(vd + r * kMmaRow + ch * 16, v + o, ok ? 16u : 0u);
+    }
+  };
+  issue(0, 0);
+  cp_async_commit();
+
+  // first chunk of this document: the chunk whose first token is the segment's first token
+  int chunk0 = 0;
+  if (pools) {
+    int lo = 0, hi = n_chunks;   // chunk_offsets is ascending; find the entry equal to t0
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (chunk_offsets[mid] < t0) lo = mid + 1; else hi = mid;
+    }
+    chunk0 = lo;
+  }
+  float pk = 0.f, pv = 0.f;   // thread d: running sums of column d over the current chunk
+
+  AttnState st;
+  st.init();
+  const int limit[2] = {min(r0 + warp * 16 + g, len - 1), min(r0 + warp * 16 + g + 8, len - 1)};
+  const int warp_limit = min(r0 + warp * 16 + 15, len - 1);
+  const uint32_t q_frag = s_q + (warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * kMmaRow + (lane >> 4) * 16;
+
+  for (int t = 0; t < n_tiles; ++t) {
+    const int buf = t & 1;
+    if (t + 1 < n_tiles) issue(t + 1, buf ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const uint32_t kbuf = s_kv + buf * 2 * kPfTile;
+    if (t * kPfKeys <= warp_limit) attn_tile(st, q_frag, kbuf, kbuf + kPfTile, t * kPfKeys, limit, scale_log2e, lane);
+    if (pools) {   // CTA-uniform; rows past the document's end are zero in shared memory
+      const unsigned char* kb = smem + kPfRows * kMmaRow + buf * 2 * kPfTile + threadIdx.x * 2;
+#pragma unroll 8
+      for (int r = 0; r < kPfKeys; ++r) {
+        pk += __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(kb + r * kMmaRow));
+        pv += __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(kb + kPfTile + r * kMmaRow));
+      }
+      const int key_end = min((t + 1) * kPfKeys, len);
+      if (key_end % pool_size == 0 || key_end == len) {   // the chunk is complete
+        const int c = (key_end - 1) / pool_size;
+        const float inv = 1.f / (float)(key_end - c * pool_size);
+        const long long o = (long long)(chunk0 + c) * pool_chunk_stride + (long long)hk * pool_head_stride + threadIdx.x;
+        pooled_k[o] = __float2bfloat16_rn(pk * inv);
+        pooled_v[o] = __float2bfloat16_rn(pv * inv);
+        pk = pv = 0.f;
+      }
+    }
+    __syncthreads();   // the tile's buffers may be refilled
+  }
+  cp_async_wait<0>();
+  __nv_bfloat16* dst[2];
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    const int rank = r0 + warp * 16 + g + rr * 8;
+    dst[rr] = rank < len ? out + (long long)tix[rank] * n_q_heads * kMmaD + (long long)hq * kMmaD : nullptr;
+  }
+  attn_store(st, dst, lane);
 }
 
 }  // namespace msa
@@ -353,5 +489,43 @@ extern "C" int msa_sparse_prefill_attn(const void* q, int64_t q_stride_b, int64_
       (const __nv_bfloat16*)v_store, store_stride_b, store_stride_h, kv_start, kv_len, q_tok, num_q, seq_len, n_q_heads,
       n_kv_heads, scale * 1.4426950408889634f, (__nv_bfloat16*)out);
   MSA_LAUNCH_OK("prefill_attn_kernel");
+  return MSA_OK;
+}
+
+extern "C" int msa_doc_attention_pool(const void* q, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                                      const void* k, const void* v, int64_t k_stride_b, int64_t k_stride_h,
+                                      int64_t k_stride_s, const int32_t* token_index, const int32_t* seg_offsets,
+                                      int32_t n_segments, int32_t max_segment_len, int32_t seq_len, int32_t n_q_heads,
+                                      int32_t n_kv_heads, int32_t head_dim, int32_t dtype, float scale, void* out,
+                                      const int32_t* chunk_offsets, int32_t n_chunks, int32_t pool_size, void* pooled_k,
+                                      void* pooled_v, int64_t pool_chunk_stride, int64_t pool_head_stride, void* stream) {
+  MSA_REQUIRE(q && k && v && token_index && seg_offsets && out, "doc_attention: null pointer");
+  MSA_REQUIRE(dtype == MSA_BF16 && head_dim == kMmaD,
+              "doc_attention: this kernel takes bf16 with head_dim 128 (other shapes use the library attention path)");
+  MSA_REQUIRE(n_segments >= 0 && max_segment_len >= 0 && seq_len > 0 && n_q_heads > 0 && n_kv_heads > 0 &&
+                  n_q_heads % n_kv_heads == 0 && n_q_heads <= 65535 && n_segments <= 65535,
+              "doc_attention: bad sizes (at most 65535 segments per call)");
+  MSA_REQUIRE(q_stride_b % 8 == 0 && q_stride_h % 8 == 0 && q_stride_s % 8 == 0 && k_stride_b % 8 == 0 &&
+                  k_stride_h % 8 == 0 && k_stride_s % 8 == 0 && aligned16(q) && aligned16(k) && aligned16(v) &&
+                  aligned16(out), "doc_attention: rows must be 16-byte aligned");
+  if (chunk_offsets) {
+    MSA_REQUIRE(pooled_k && pooled_v && n_chunks >= 0, "doc_attention: pooled outputs missing");
+    MSA_REQUIRE(pool_size > 0 && pool_size % kPfKeys == 0,
+                "doc_attention: pooling_kernel_size %d is not a multiple of %d (pool with msa_pool_chunks instead)",
+                pool_size, kPfKeys);
+  }
+  if (n_segments == 0 || max_segment_len == 0) return MSA_OK;
+  static thread_local bool configured = false;
+  if (!configured) {
+    MSA_CUDA_OK(cudaFuncSetAttribute(doc_attn_pool_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
+    configured = true;
+  }
+  dim3 grid((max_segment_len + kPfRows - 1) / kPfRows, n_q_heads, n_segments);
+  doc_attn_pool_kernel<<<grid, 128, kPfSmem, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)q, q_stride_b, q_stride_h, q_stride_s, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
+      k_stride_b, k_stride_h, k_stride_s, token_index, seg_offsets, seq_len, n_q_heads, n_kv_heads,
+      scale * 1.4426950408889634f, (__nv_bfloat16*)out, chunk_offsets, n_chunks, pool_size, (__nv_bfloat16*)pooled_k,
+      (__nv_bfloat16*)pooled_v, pool_chunk_stride, pool_head_stride);
+  MSA_LAUNCH_OK("doc_attn_pool_kernel");
   return MSA_OK;
 }

@@ -340,6 +340,48 @@ def sparse_prefill_attn(q: torch.Tensor, k_store, v_store, kv_start, kv_len, q_t
     return out
 
 
+def doc_attention_pool(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, token_index: torch.Tensor,
+                       seg_offsets: torch.Tensor, max_segment_len: int, out: Optional[torch.Tensor] = None,
+                       chunk_offsets: Optional[torch.Tensor] = None, pool_size: int = 64, head_major_out: bool = False,
+                       scale: Optional[float] = None):
+    """Causal attention inside every segment of ``token_index`` (bf16, D = 128) and, when ``chunk_offsets`` is
+    given, the chunk means of K and V from the same pass.  q ``[B, Hq, S, D]``; k, v ``[B, Hkv, S, D]``;
+    token_index ``[Td]`` int32 flat positions; seg_offsets ``[n+1]`` int32.  ``out`` ``[B, S, Hq*D]`` keeps its
+    content on rows that no segment lists (zeros when allocated here).
+    Returns ``(out, pooled_k, pooled_v)``; pooled ``[C, Hkv, D]`` or, head major, ``[1, Hkv, C, D]`` (None without pooling)."""
+    A.need_cuda(q, k, v, token_index, seg_offsets, chunk_offsets)
+    b, hq, s, d = q.shape
+    hkv = k.shape[1]
+    if q.stride(3) != 1:
+        q = q.contiguous()
+    if k.stride(3) != 1 or v.stride() != k.stride():
+        k, v = k.contiguous(), v.contiguous()
+    if token_index.dtype != torch.int32 or seg_offsets.dtype != torch.int32:
+        raise A.MsaError("doc_attention_pool: token_index and seg_offsets must be int32")
+    if out is None:
+        out = torch.zeros((b, s, hq * d), dtype=q.dtype, device=q.device)
+    n_seg = seg_offsets.numel() - 1
+    pooled_k = pooled_v = None
+    cs = hs = n_chunks = 0
+    if chunk_offsets is not None:
+        n_chunks = chunk_offsets.numel() - 1
+        shape = (1, hkv, n_chunks, d) if head_major_out else (n_chunks, hkv, d)
+        pooled_k = torch.empty(shape, dtype=q.dtype, device=q.device)
+        pooled_v = torch.empty(shape, dtype=q.dtype, device=q.device)
+        cs, hs = (d, n_chunks * d) if head_major_out else (hkv * d, d)
+    scale = (1.0 / math.sqrt(d)) if scale is None else scale
+    for lo in range(0, max(n_seg, 1), 65535):      # grid.z limit
+        n = min(65535, n_seg - lo)
+        if n <= 0:
+            break
+        A.check(A.lib().msa_doc_attention_pool(
+            A.ptr(q), q.stride(0), q.stride(1), q.stride(2), A.ptr(k), A.ptr(v), k.stride(0), k.stride(1), k.stride(2),
+            A.ptr(token_index), A.ptr(seg_offsets) + 4 * lo, n, int(max_segment_len), s, hq, hkv, d,
+            A.dtype_code(q.dtype), float(scale), A.ptr(out), A.ptr(chunk_offsets), n_chunks, int(pool_size),
+            A.ptr(pooled_k), A.ptr(pooled_v), cs, hs, A.stream_ptr(q.device)), "msa_doc_attention_pool")
+    return out, pooled_k, pooled_v
+
+
 def keys_to_scores(keys: torch.Tensor) -> torch.Tensor:
     """Decode a table of order-preserving keys (int32 storage) back to float32 scores."""
     u = keys.to(torch.int64) & 0xFFFFFFFF

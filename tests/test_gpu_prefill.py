@@ -119,3 +119,164 @@ def test_prefill_rejects_other_shapes():
     qt = torch.zeros(1, 8, dtype=torch.int32, device=dev)
     with pytest.raises(MsaError):
         ops.sparse_prefill_attn(q, ks, ks, z, z, qt, z)
+
+
+# ----------------------------------------------------------------------------------------------
+# stage 1: attention inside every document with the K / V chunk means from the same pass
+# (src/msa/memory_sparse_attention.py:216-241, :166-176)
+# ----------------------------------------------------------------------------------------------
+def _stage1_case(seed, doc_lens, n_template, hq, hkv, pad, drop):
+    """One block row: [template | documents | padding]; `drop` masks a few tokens inside documents."""
+    g = torch.Generator().manual_seed(seed)
+    ids = [-2] * n_template
+    for i, n in enumerate(doc_lens):
+        ids += [i + 1] * n
+    ids += [0] * pad
+    s = len(ids)
+    doc_ids = torch.tensor(ids).view(1, s)
+    mask = torch.ones(1, s, dtype=torch.long)
+    if pad:
+        mask[0, -pad:] = 0
+    for t in drop:
+        mask[0, t] = 0
+    q = torch.randn(1, hq, s, 128, generator=g).to(torch.bfloat16)
+    k = torch.randn(1, hkv, s, 128, generator=g).to(torch.bfloat16)
+    v = torch.randn(1, hkv, s, 128, generator=g).to(torch.bfloat16)
+    return doc_ids, mask, q, k, v
+
+
+def _segment_reference(q, k, v, tokens, scale):
+    """fp32 causal attention of one segment; q [Hq,S,D], k/v [Hkv,S,D]; returns [n, Hq*D]."""
+    hq, hkv = q.shape[0], k.shape[0]
+    qq = q[:, tokens].float()
+    kk = k[:, tokens].float().repeat_interleave(hq // hkv, 0)
+    vv = v[:, tokens].float().repeat_interleave(hq // hkv, 0)
+    n = len(tokens)
+    att = torch.einsum("hqd,hkd->hqk", qq, kk) * scale
+    att = att.masked_fill(torch.ones(n, n, dtype=torch.bool).triu(1), float("-inf"))
+    return torch.einsum("hqk,hkd->hqd", att.softmax(-1), vv).permute(1, 0, 2).reshape(n, -1)
+
+
+@pytest.mark.parametrize("doc_lens,drop,p", [
+    ([512, 64, 1, 65, 130], [], 64),
+    ([100, 300, 31], [5, 6, 150, 151, 152], 64),      # masked tokens inside documents
+    ([200, 40], [], 32),
+])
+def test_doc_attention_pool_matches_restatement(doc_lens, drop, p):
+    from msa_b200 import ops
+    from oracle import msa_oracle as O
+    dev = torch.device("cuda:0")
+    hq, hkv, n_t = 8, 2, 3
+    drop = [n_t + t for t in drop]
+    doc_ids, mask, q, k, v = _stage1_case(3, doc_lens, n_t, hq, hkv, pad=9, drop=drop)
+    s = doc_ids.shape[1]
+    tok, off, pooled_ids = ops.chunk_bookkeeping(doc_ids.to(dev), mask.to(dev), p)
+    valid = (doc_ids[0] > 0) & (mask[0] == 1)
+    segs = [[t for t in range(s) if valid[t] and doc_ids[0, t] == i + 1] for i in range(len(doc_lens))]
+    seg_off = torch.tensor([0] + [len(x) for x in segs]).cumsum(0).to(torch.int32).to(dev)
+    assert tok.cpu().tolist() == [t for x in segs for t in x]
+    scale = 128 ** -0.5
+    out, pk, pv = ops.doc_attention_pool(q.to(dev), k.to(dev), v.to(dev), tok, seg_off, max(len(x) for x in segs),
+                                         chunk_offsets=off, pool_size=p, scale=scale)
+    # template segment through the same kernel, no pooling
+    t_tok = torch.arange(n_t, dtype=torch.int32, device=dev)
+    ops.doc_attention_pool(q.to(dev), k.to(dev), v.to(dev), t_tok, torch.tensor([0, n_t], dtype=torch.int32, device=dev),
+                           n_t, out=out, scale=scale)
+    torch.cuda.synchronize()
+    ref = torch.zeros(s, hq * 128)
+    for x in segs + [list(range(n_t))]:
+        ref[x] = _segment_reference(q[0], k[0], v[0], x, scale)
+    got = out[0].float().cpu()
+    assert (got - ref).norm() / ref.norm() < 1e-2
+    untouched = [t for t in range(n_t, s) if not valid[t]]
+    assert got[untouched].abs().sum() == 0
+    # pooled K / V: the oracle's exact chunk means (bf16 rounding: 1e-2), and the pooling kernel bit for bit
+    # up to one rounding step of the fp32 sum order
+    lens = (off[1:] - off[:-1]).cpu().long()
+    flat = torch.tensor([t for x in segs for t in x])
+    for pooled, states in ((pk, k), (pv, v)):
+        exact = O.pool_chunks_exact(states[0][:, flat].permute(1, 0, 2).float(), lens).float()
+        assert (pooled.float().cpu() - exact).norm() / exact.norm() < 1e-2
+        alone = ops.pool_chunks(states.to(dev), off, tok)
+        assert (pooled.float() - alone.float()).abs().max().item() <= 2 ** -7 * alone.float().abs().max().item()
+        assert (pooled == alone).float().mean().item() > 0.99
+
+
+def test_layer_bf16_on_own_kernels_matches_fp32_layer_on_library_path():
+    """The layer mirror with head_dim 128: in bf16 stage 1 and stage 2 run on this package's attention kernels
+    (fused K/V pooling, one-launch assembly), in fp32 on the library path.  Same weights, same inputs."""
+    from transformers.models.qwen3.modeling_qwen3 import Qwen3RotaryEmbedding
+    from msa_b200.attention import MemorySparseAttention
+    from msa_b200.cache import SparseCache, SparseCacheOnCPU
+    from msa_b200.configuration import MSAConfig
+    from msa_b200.memory import AttentionGeometry, Document, ModelConfig
+    from msa_b200.service import MSAService
+    dev = "cuda:0"
+    hq, hkv, d, pool, top_k = 8, 2, 128, 64, 3
+    cfg = MSAConfig(
+        msa_config=dict(router_layer_idx="0", aux_loss=False, aux_loss_method="INFONCE", decouple_router=True,
+                        top_k_docs=top_k, pooling_kernel_size=pool, head_reduce_method="mean",
+                        query_reduce_method="max", chunk_reduce_method="max", decouple_pooling_mode="mean"),
+        hidden_size=256, num_attention_heads=hq, num_key_value_heads=hkv, head_dim=d, num_hidden_layers=1,
+        intermediate_size=64, vocab_size=32, max_position_embeddings=1024)
+    cfg._attn_implementation = "eager"
+    torch.manual_seed(3)
+    layer32 = MemorySparseAttention(cfg, 0).eval().to(dev)
+    layer16 = MemorySparseAttention(cfg, 0).eval().to(dev)
+    layer16.load_state_dict(layer32.state_dict())
+    layer16.to(torch.bfloat16)
+    rope = Qwen3RotaryEmbedding(cfg).to(dev)
+
+    doc_lens = [130, 64, 77]
+    doc_ids, mask, _, _, _ = _stage1_case(4, doc_lens, 3, hq, hkv, pad=0, drop=[])
+    s = doc_ids.shape[1]
+    g = torch.Generator().manual_seed(12)
+    hidden = torch.randn(1, s, 256, generator=g).to(dev)
+    pos = torch.cat([torch.arange(3)] + [torch.arange(n) for n in doc_lens]).view(1, s).to(dev)
+    b2, s2 = 2, 12
+    hidden2 = torch.randn(b2, s2, 256, generator=g).to(dev)
+    ids2 = torch.zeros(b2, s2, dtype=torch.long, device=dev)
+    mask2 = torch.ones(b2, s2, dtype=torch.long, device=dev)
+    mask2[1, :5] = 0
+    pos2 = (torch.arange(s2).view(1, s2) + 3 + top_k).expand(b2, s2).contiguous().to(dev)
+
+    results = []
+    for layer, dt in ((layer32, torch.float32), (layer16, torch.bfloat16)):
+        cache1 = SparseCacheOnCPU()
+        cache1.record_kwargs(0, {"stage": "prefill_stage1"})
+        h = hidden.to(dt)
+        with torch.no_grad():
+            out1, _ = layer(h, doc_ids.to(dev), mask.to(dev), rope(h, pos), cache1)
+        kw = cache1.cache_kwargs[0]
+        pk, pv = cache1.get_kvcache(0)
+        prk = cache1.get_router_kcache(0)
+        chunks = torch.unique_consecutive(kw["pooled_doc_ids"], return_counts=True)[1].tolist()
+        docs = [Document(doc_id=10 + i, num_chunks=n) for i, n in enumerate(chunks)]
+        geo = AttentionGeometry(num_hidden_layers=1, num_attention_heads=hq, num_key_value_heads=hkv, head_dim=d, dtype=dt)
+        svc = MSAService(0, None, ModelConfig(doc_top_k=top_k, pooling_kernel_size=pool, router_layer_idx="0"), None,
+                         geo, world_size=1, rank=0)
+        svc.generate_blocks(docs, metas=[{"past_key_values": cache1, "nr_docs": len(docs), "chunk_sizes": chunks,
+                                          "doc_ids": [dd.doc_id for dd in docs], "nr_chunks": chunks}])
+        svc.setup_memory_client(layer)
+        cache2 = SparseCache()
+        cache2.meta["max_generate_tokens"] = 4
+        cache2.record_kwargs(0, {"stage": "prefill_stage2"})
+        h2 = hidden2.to(dt)
+        with torch.no_grad():
+            out2, _ = layer(h2, ids2, mask2, rope(h2, pos2), cache2)
+        svc.check_status()
+        kw2 = cache2.cache_kwargs[0]
+        results.append(dict(out1=out1.float().cpu(), pk=pk.float().cpu(), pv=pv.float().cpu(), prk=prk.float().cpu(),
+                            out2=out2.float().cpu(), kv_lengths=kw2["kv_lengths"].cpu(),
+                            ck=kw2["compacked_key_cache"].float().cpu(), cv=kw2["compacked_value_cache"].float().cpu(),
+                            pad=kw2["attention_mask"].cpu()))
+    a, b_ = results
+
+    def rel(x, y):
+        return float((x - y).norm() / y.norm().clamp_min(1e-9))
+    assert rel(b_["out1"], a["out1"]) < 3e-2
+    assert rel(b_["pk"], a["pk"]) < 2e-2 and rel(b_["pv"], a["pv"]) < 2e-2 and rel(b_["prk"], a["prk"]) < 2e-2
+    assert torch.equal(a["kv_lengths"], b_["kv_lengths"]) and torch.equal(a["pad"], b_["pad"])   # every document selected
+    assert rel(b_["ck"], a["ck"]) < 2e-2 and rel(b_["cv"], a["cv"]) < 2e-2
+    valid = mask2.bool().cpu()
+    assert rel(b_["out2"][valid], a["out2"][valid]) < 3e-2
