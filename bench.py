@@ -45,7 +45,7 @@ def parse():
     ap.add_argument("--queries", type=int, default=N_QUERIES)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--new-tokens", type=int, default=256, help="generate workload: tokens to decode")
-    ap.add_argument("--workload", default="routing", choices=["routing", "pooling", "decode", "fetch", "route-decode", "prefill", "generate"],
+    ap.add_argument("--workload", default="routing", choices=["routing", "pooling", "decode", "fetch", "route-decode", "prefill", "stage1", "generate"],
                     help="routing = the headline (default); the others time one secondary kernel each")
     return ap.parse_args()
 
@@ -622,6 +622,48 @@ def run_secondary(args):
                         {"attention_kernel_ms": attn_ms, "attention_tflops": flops / (attn_ms / 1e3) / 1e12,
                          "library_varlen_attention_ms": lib_ms,
                          "note": "contexts of a few hundred keys: the kernel is latency / issue bound, far from either roof"})
+
+    elif args.workload == "stage1":
+        # benchmark config 2 shapes: documents of 512 tokens, 32 q / 8 kv heads, d = 128, chunk 64; one block row.
+        # 512 documents (262,144 tokens: q and out 2.1 GB each) keep the run short; time scales linearly in documents.
+        n_docs, doc_len, p = (512 if args.docs == N_DOCS else args.docs), 512, 64
+        t = n_docs * doc_len
+        doc_ids = torch.arange(1, n_docs + 1, device=dev).repeat_interleave(doc_len).view(1, t)
+        tok, off, _ = ops.chunk_bookkeeping(doc_ids, None, p)
+        seg = torch.arange(0, t + 1, doc_len, dtype=torch.int32, device=dev)
+        q = torch.randn((1, HQ, t, D), generator=g, device=dev).to(torch.bfloat16)
+        k = torch.randn((1, HKV, t, D), generator=g, device=dev).to(torch.bfloat16)
+        v = torch.randn((1, HKV, t, D), generator=g, device=dev).to(torch.bfloat16)
+        out = torch.zeros((1, t, HQ * D), dtype=torch.bfloat16, device=dev)
+
+        def step():
+            ops.doc_attention_pool(q, k, v, tok, seg, doc_len, out=out, chunk_offsets=off, pool_size=p)
+        lib_ms = pool_ms = None
+        try:    # what the reference does at this point: the library's varlen attention, then K and V pooled separately
+            from flash_attn import flash_attn_varlen_func
+            qp, kp, vp = q[0].transpose(0, 1).contiguous(), k[0].transpose(0, 1).contiguous(), v[0].transpose(0, 1).contiguous()
+            lib_ms = _time_ms(torch, lambda: flash_attn_varlen_func(qp, kp, vp, cu_seqlens_q=seg, cu_seqlens_k=seg,
+                                                                    max_seqlen_q=doc_len, max_seqlen_k=doc_len, causal=True),
+                              10, 3)
+            del qp, kp, vp
+        except Exception:
+            pass
+        pool_ms = _time_ms(torch, lambda: (ops.pool_chunks(k, off, tok), ops.pool_chunks(v, off, tok)), 10, 3)
+        steps = min(steps, 20)
+        args.steps = steps
+        sampler.start()
+        ms = _time_ms(torch, step, steps, warmup)
+        clocks = sampler.stop()
+        flops = 4.0 * n_docs * HQ * D * (doc_len * (doc_len + 1) / 2)
+        alg = 2 * t * HQ * D * 2 + 2 * t * HKV * D * 2 + 2 * (t // p) * HKV * D * 2
+        _secondary_line(args, "stage-1 document attention + K/V pooling tokens/s", "tokens/s", t / (ms / 1e3), ms,
+                        f"{n_docs} documents x {doc_len} tokens in one block row, 32q/8kv heads, d=128, chunk {p}, bf16 "
+                        f"(q and out {t * HQ * D * 2 / 1e9:.1f} GB each, > L2)", "doc_attn_pool_kernel", alg, pk["hbm_gbs"],
+                        "hbm", clocks, steps,
+                        {"attention_tflops": flops / (ms / 1e3) / 1e12, "library_varlen_attention_ms": lib_ms,
+                         "separate_kv_pooling_ms": pool_ms,
+                         "note": "mma.sync flash kernel: compute bound on the legacy tensor path, the HBM fraction is "
+                                 "reported for completeness"})
 
     else:  # route-decode: benchmark config 5 per-step routing on one of 8 shards
         b, docs_local = 32, (N_DOCS + 7) // 8

@@ -11,6 +11,8 @@
 // shared memory keep it at 128 registers and 51 KB, i.e. four CTAs per SM (two at 64-key tiles with
 // the query in registers measured 20 % slower).  The point is one launch instead of the gather /
 // scatter / re-pack sequence around a library call.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "mma_helpers.cuh"
 
@@ -139,8 +141,11 @@ struct AttnState {
 
 // One tile of kPfKeys keys against the warp's 16 rows: S = Q K^T, causal limit per row, online softmax,
 // O += P V.  q_frag / kbuf / vbuf are shared-memory addresses; key0 is the tile's first key; limit[rr]
-// is the last key row rr may see.  Key 0 is visible to every row, so the running maximum is finite from
-// the first tile on.
+// is the last key row rr may see (kMasked = false: the caller knows every key of the tile is visible to
+// every row of the warp).  m_run is kept in raw score units; the softmax scale (times log2 e) enters
+// through one fused multiply-add per element.  Key 0 is visible to every row, so the running maximum is
+// finite from the first tile on.
+template <bool kMasked>
 __device__ __forceinline__ void attn_tile(AttnState& st, uint32_t q_frag, uint32_t kbuf, uint32_t vbuf, int key0,
                                           const int (&limit)[2], float scale_log2e, int lane) {
   const int quad = lane & 3, mi = lane >> 3, r = lane & 7;
@@ -167,33 +172,37 @@ __device__ __forceinline__ void attn_tile(AttnState& st, uint32_t q_frag, uint32
   for (int nb = 0; nb < kPfKeys / 8; ++nb)
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const int key = key0 + nb * 8 + 2 * quad + (e & 1);
-      const int rr = e >> 1;
-      s[nb][e] = key <= limit[rr] ? s[nb][e] * scale_log2e : -INFINITY;
-      mx[rr] = fmaxf(mx[rr], s[nb][e]);
+      if (kMasked) {
+        const int key = key0 + nb * 8 + 2 * quad + (e & 1);
+        if (key > limit[e >> 1]) s[nb][e] = -INFINITY;
+      }
+      mx[e >> 1] = fmaxf(mx[e >> 1], s[nb][e]);
     }
-  float f[2];
+  float f[2], neg_m[2];
 #pragma unroll
   for (int rr = 0; rr < 2; ++rr) {
     mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
     mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
     const float m_new = fmaxf(st.m_run[rr], mx[rr]);
-    f[rr] = exp2f(st.m_run[rr] - m_new);
+    f[rr] = exp2f((st.m_run[rr] - m_new) * scale_log2e);
     st.m_run[rr] = m_new;
+    neg_m[rr] = -m_new * scale_log2e;
   }
   float sum[2] = {0.f, 0.f};
 #pragma unroll
   for (int nb = 0; nb < kPfKeys / 8; ++nb)
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      s[nb][e] = exp2f(s[nb][e] - st.m_run[e >> 1]);
+      s[nb][e] = exp2f(fmaf(s[nb][e], scale_log2e, neg_m[e >> 1]));
       sum[e >> 1] += s[nb][e];
     }
 #pragma unroll
   for (int rr = 0; rr < 2; ++rr) st.l_run[rr] = st.l_run[rr] * f[rr] + sum[rr];
+  if (!__all_sync(0xffffffffu, f[0] == 1.f && f[1] == 1.f)) {   // some row's maximum moved: rescale the outputs
 #pragma unroll
-  for (int nb = 0; nb < kMmaD / 8; ++nb) {
-    st.o[nb][0] *= f[0]; st.o[nb][1] *= f[0]; st.o[nb][2] *= f[1]; st.o[nb][3] *= f[1];
+    for (int nb = 0; nb < kMmaD / 8; ++nb) {
+      st.o[nb][0] *= f[0]; st.o[nb][1] *= f[0]; st.o[nb][2] *= f[1]; st.o[nb][3] *= f[1];
+    }
   }
 #pragma unroll
   for (int kk = 0; kk < kPfKeys / 16; ++kk) {
@@ -208,6 +217,14 @@ __device__ __forceinline__ void attn_tile(AttnState& st, uint32_t q_frag, uint32
       mma_bf16_full(st.o[nb + 1], pa, b2, b3);
     }
   }
+}
+
+// Dispatch on whether the tile crosses the diagonal of any row of the warp (first_limit: the smallest
+// limit among the warp's rows).
+__device__ __forceinline__ void attn_tile_auto(AttnState& st, uint32_t q_frag, uint32_t kbuf, uint32_t vbuf, int key0,
+                                               const int (&limit)[2], int first_limit, float scale_log2e, int lane) {
+  if (key0 + kPfKeys - 1 <= first_limit) attn_tile<false>(st, q_frag, kbuf, vbuf, key0, limit, scale_log2e, lane);
+  else attn_tile<true>(st, q_frag, kbuf, vbuf, key0, limit, scale_log2e, lane);
 }
 
 // Normalise the warp's rows and write row rr of this thread to dst[rr] (nullptr: the row does not exist).
@@ -291,7 +308,8 @@ prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, long long q_sb, long lo
     __syncthreads();
     if (t * kPfKeys <= warp_limit) {   // later tiles are wholly masked for every row of this warp
       const uint32_t kbuf = s_kv + buf * 2 * kPfTile;
-      attn_tile(st, q_frag, kbuf, kbuf + kPfTile, t * kPfKeys, limit, scale_log2e, lane);
+      attn_tile_auto(st, q_frag, kbuf, kbuf + kPfTile, t * kPfKeys, limit, base_keys + min(r0 + warp * 16, num_q - 1),
+                     scale_log2e, lane);
     }
     __syncthreads();   // the tile's buffers may be refilled
   }
@@ -318,11 +336,13 @@ prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, long long q_sb, long lo
 // sums the staged rows per chunk (pool_size keys, a multiple of the tile) in fp32 and writes the
 // chunk's mean, rounded once, to the bank's pooled K and V.
 // ---------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(128, 4)
+template <int kCtasPerSm>
+__global__ void __launch_bounds__(128, kCtasPerSm)
 doc_attn_pool_kernel(const __nv_bfloat16* __restrict__ q, long long q_sb, long long q_sh, long long q_ss,
                      const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v, long long k_sb,
                      long long k_sh, long long k_ss, const int32_t* __restrict__ token_index,
-                     const int32_t* __restrict__ seg_off, int S, int n_q_heads, int n_kv_heads, float scale_log2e,
+                     const int32_t* __restrict__ seg_off, int S, uint32_t div_mul, uint32_t div_shift, int n_q_heads,
+                     int n_kv_heads, float scale_log2e,
                      __nv_bfloat16* __restrict__ out, const int32_t* __restrict__ chunk_offsets, int n_chunks,
                      int pool_size, __nv_bfloat16* __restrict__ pooled_k, __nv_bfloat16* __restrict__ pooled_v,
                      long long pool_chunk_stride, long long pool_head_stride) {
@@ -337,6 +357,11 @@ doc_attn_pool_kernel(const __nv_bfloat16* __restrict__ q, long long q_sb, long l
   const int n_tiles = (n_keys + kPfKeys - 1) / kPfKeys;
   const bool pools = chunk_offsets != nullptr && last_row == len - 1 && hq % grp == 0;
   const int32_t* tix = token_index + t0;
+  // flat token position -> element offset inside a [B, H, S, D] tensor; tok / S by multiply-high and shift
+  auto offset = [&](int tok, long long sb, long long ss) {
+    const uint32_t bi = (__umulhi((uint32_t)tok, div_mul) + (uint32_t)tok) >> div_shift;
+    return (long long)bi * sb + (long long)(tok - (int)bi * S) * ss;
+  };
 
   const uint32_t s_q = (uint32_t)__cvta_generic_to_shared(smem);
   const uint32_t s_kv = s_q + kPfRows * kMmaRow;
@@ -344,17 +369,24 @@ doc_attn_pool_kernel(const __nv_bfloat16* __restrict__ q, long long q_sb, long l
     const int r = i >> 4, ch = i & 15;
     const bool ok = r0 + r < len;
     const int tok = ok ? tix[r0 + r] : 0;
-    cp_async16(s_q + r * kMmaRow + ch * 16,
-               q + (long long)(tok / S) * q_sb + (long long)hq * q_sh + (long long)(tok % S) * q_ss + ch * 8, ok ? 16u : 0u);
+    cp_async16(s_q + r * kMmaRow + ch * 16, q + offset(tok, q_sb, q_ss) + (long long)hq * q_sh + ch * 8, ok ? 16u : 0u);
   }
+  // A document without masked tokens is a run of consecutive positions of one row: its keys are
+  // addressed without the index (token_index is ascending, so first/last decide it).
+  const int tok0 = tix[0];
+  const bool run = tix[len - 1] - tok0 == len - 1 &&
+                   ((__umulhi((uint32_t)tok0, div_mul) + (uint32_t)tok0) >> div_shift) ==
+                       ((__umulhi((uint32_t)(tok0 + len - 1), div_mul) + (uint32_t)(tok0 + len - 1)) >> div_shift);
+  const long long run_base = offset(tok0, k_sb, k_ss) + (long long)hk * k_sh;
   auto issue = [&](int tile, int buf) {
     const uint32_t kd = s_kv + buf * 2 * kPfTile, vd = kd + kPfTile;
     for (int i = threadIdx.x; i < kPfKeys * 16; i += 128) {
       const int r = i >> 4, ch = i & 15;
       const int key = tile * kPfKeys + r;
       const bool ok = key < n_keys;
-      const int tok = ok ? tix[key] : 0;
-      const long long o = (long long)(tok / S) * k_sb + (long long)hk * k_sh + (long long)(tok % S) * k_ss + ch * 8;
+      long long o;
+      if (run) o = run_base + (long long)(ok ? key : 0) * k_ss + ch * 8;
+      else o = offset(ok ? tix[key] : 0, k_sb, k_ss) + (long long)hk * k_sh + ch * 8;
       cp_async16(kd + r * kMmaRow + ch * 16, k + o, ok ? 16u : 0u);
       cp_async16(vd + r * kMmaRow + ch * 16, v + o, ok ? 16u : 0u);
     }
@@ -387,7 +419,8 @@ doc_attn_pool_kernel(const __nv_bfloat16* __restrict__ q, long long q_sb, long l
     cp_async_wait<1>();
     __syncthreads();
     const uint32_t kbuf = s_kv + buf * 2 * kPfTile;
-    if (t * kPfKeys <= warp_limit) attn_tile(st, q_frag, kbuf, kbuf + kPfTile, t * kPfKeys, limit, scale_log2e, lane);
+    if (t * kPfKeys <= warp_limit)
+      attn_tile_auto(st, q_frag, kbuf, kbuf + kPfTile, t * kPfKeys, limit, min(r0 + warp * 16, len - 1), scale_log2e, lane);
     if (pools) {   // CTA-uniform; rows past the document's end are zero in shared memory
       const unsigned char* kb = smem + kPfRows * kMmaRow + buf * 2 * kPfTile + threadIdx.x * 2;
 #pragma unroll 8
@@ -515,15 +548,25 @@ extern "C" int msa_doc_attention_pool(const void* q, int64_t q_stride_b, int64_t
                 pool_size, kPfKeys);
   }
   if (n_segments == 0 || max_segment_len == 0) return MSA_OK;
+  static const int occ = [] {   // tuning only: CTAs per SM the kernel is compiled for (register cap 128 or 168)
+    const char* e = getenv("MSA_B200_ATTN_CTAS_PER_SM");
+    return e && atoi(e) == 3 ? 3 : 4;
+  }();
+  auto kernel = occ == 3 ? doc_attn_pool_kernel<3> : doc_attn_pool_kernel<4>;
   static thread_local bool configured = false;
   if (!configured) {
-    MSA_CUDA_OK(cudaFuncSetAttribute(doc_attn_pool_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
+    MSA_CUDA_OK(cudaFuncSetAttribute(doc_attn_pool_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
+    MSA_CUDA_OK(cudaFuncSetAttribute(doc_attn_pool_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
     configured = true;
   }
+  // tok / seq_len for tok < 2^31: (mulhi(tok, mul) + tok) >> shift with shift = ceil(log2 seq_len)
+  uint32_t div_shift = 0;
+  while ((1ull << div_shift) < (uint64_t)seq_len) ++div_shift;
+  const uint32_t div_mul = (uint32_t)((((1ull << div_shift) - (uint64_t)seq_len) << 32) / (uint64_t)seq_len + 1);
   dim3 grid((max_segment_len + kPfRows - 1) / kPfRows, n_q_heads, n_segments);
-  doc_attn_pool_kernel<<<grid, 128, kPfSmem, (cudaStream_t)stream>>>(
+  kernel<<<grid, 128, kPfSmem, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)q, q_stride_b, q_stride_h, q_stride_s, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
-      k_stride_b, k_stride_h, k_stride_s, token_index, seg_offsets, seq_len, n_q_heads, n_kv_heads,
+      k_stride_b, k_stride_h, k_stride_s, token_index, seg_offsets, seq_len, div_mul, div_shift, n_q_heads, n_kv_heads,
       scale * 1.4426950408889634f, (__nv_bfloat16*)out, chunk_offsets, n_chunks, pool_size, (__nv_bfloat16*)pooled_k,
       (__nv_bfloat16*)pooled_v, pool_chunk_stride, pool_head_stride);
   MSA_LAUNCH_OK("doc_attn_pool_kernel");
