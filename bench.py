@@ -819,6 +819,7 @@ def run_generate(args):
         torch.cuda.synchronize(dev)
         return float(t.item()), mode
 
+    timed_run(False)                       # settles lazily initialised communicators and the clocks
     ms_nofetch, _ = timed_run(False)       # same step without the host fetch: what the fetch may hide behind
     ms_plain, _ = timed_run(True, pipelined=False)   # unrotated loop: the fetch has only the rest of its own step
     sampler = ClockSampler(local_rank)

@@ -303,6 +303,26 @@ int msa_doc_attention_pool(const void* q, int64_t q_stride_b, int64_t q_stride_h
                            void* pooled_v, int64_t pool_chunk_stride, int64_t pool_head_stride, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Dense glue of a decode step (bf16).  No single reference function: they replace the chains of
+ * elementwise torch kernels that transformers' Qwen3 modules issue between the GEMMs of a layer as
+ * driven by src/msa/model.py:67-135 (Qwen3RMSNorm on q / k heads + apply_rotary_pos_emb; residual add
+ * + Qwen3RMSNorm; SiLU(gate) * up).  Each computes in fp32 and rounds once per module boundary.
+ *
+ * msa_qk_norm_rope: qkv row b = [n_q_heads*128 | n_kv_heads*128 | ...] (row_stride elements apart);
+ *   q_out[b, h, :] = rope(rmsnorm(q head) * q_weight), k_out likewise; cos_table / sin_table: [n_seq, 128]
+ *   (rotate-half convention, the sequence's position already applied).  head_dim must be 128.
+ * msa_add_rmsnorm: x_out = x + y (y, x_out may be NULL: no add), h_out = rmsnorm(x_out) * weight; rows of
+ *   `hidden` contiguous elements.
+ * msa_silu_mul: out[r, j] = silu(gate_up[r, j]) * gate_up[r, ffn + j], out rows contiguous.
+ */
+int msa_qk_norm_rope(const void* qkv, int64_t row_stride, int32_t n_seq, int32_t n_q_heads, int32_t n_kv_heads,
+                     int32_t head_dim, const void* q_weight, const void* k_weight, float eps,
+                     const void* cos_table, const void* sin_table, void* q_out, void* k_out, void* stream);
+int msa_add_rmsnorm(const void* x, const void* y, const void* weight, float eps, int32_t n_rows, int32_t hidden,
+                    void* x_out, void* h_out, void* stream);
+int msa_silu_mul(const void* gate_up, int64_t row_stride, int32_t n_rows, int32_t ffn, void* out, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * Decode attention without any allocation.  (No counterpart in the reference: this entry
  * point exists for hosts of this library that cannot allocate device memory when a decode
  * step runs -- a serving loop whose pool already owns the whole GPU, a plugin that is handed

@@ -4,8 +4,9 @@ This is the decode loop of the reference (``src/msa/generate.py:101-186`` drivin
 ``MSADeocoderLayer`` / ``MemorySparseAttention`` in its "generate" stage,
 ``src/msa/model.py:67-135``, ``src/msa/memory_sparse_attention.py:361-405``) reduced to what a
 throughput measurement needs: random-initialised weights of the real shapes, greedy sampling, no
-tokenizer and no string handling.  Dense algebra (projections, MLP, lm_head, RMSNorm, RoPE) is
-PyTorch / cuBLAS as in the reference; attention runs on this package's flash-decode kernel with
+tokenizer and no string handling.  The GEMMs (projections, MLP, lm_head) are cuBLAS as in the reference;
+the elementwise work between them (RMSNorm, q/k norm + RoPE, residual adds, SiLU*up) runs on three small
+fused kernels; attention runs on this package's flash-decode kernel with
 in-place append, and the router layers route every step through ``MSAService``:
 
     route(step t, layer l)  ->  fetch of the winners' pooled K/V from the pinned host bank on a
@@ -99,6 +100,9 @@ class SparseDecodeModel:
         # the decode loop is cut at the first router layer (see step_pipelined)
         self.split_layer = min(self.router_layers) if (self.router_layers and service is not None) else s.num_layers
         self._x_mid = torch.zeros((batch, s.hidden), dtype=dtype, device=device)
+        self._pending_mid = torch.zeros((batch, s.hidden), dtype=dtype, device=device)
+        # norms, rotary embedding, residual adds and SiLU*up on this package's fused kernels (bf16, head_dim 128)
+        self.fused = dtype == torch.bfloat16 and s.head_dim == 128 and s.hidden % 2 == 0 and s.ffn % 2 == 0
         self._cos = torch.zeros((batch, 1, s.head_dim), dtype=dtype, device=device)
         self._sin = torch.zeros((batch, 1, s.head_dim), dtype=dtype, device=device)
         self.probe = None  # set to a dict to collect per-layer CUDA events (eager profiling step)
@@ -115,25 +119,34 @@ class SparseDecodeModel:
             e.record()
             self.probe.setdefault(name, {})[layer] = e
 
-    def _layers(self, x, lo, hi, fetch_done):
+    def _layers(self, x, pending, lo, hi, fetch_done):
+        """Layers lo..hi-1.  ``x`` is the residual stream, ``pending`` a branch output not yet added to it
+        (None at the start); returns the same pair, so that the add fuses with the next RMSNorm."""
         s, B = self.s, self.batch
         main = torch.cuda.current_stream(self.device)
         cos, sin = self._cos, self._sin
         nq, nkv, d = s.n_q_heads, s.n_kv_heads, s.head_dim
         for l in range(lo, hi):
             p = self.layers[l]
-            h = F.rms_norm(x, (s.hidden,), p["w_in"], s.rms_eps)
+            if self.fused:
+                x, h = ops.add_rmsnorm(x, pending, p["w_in"], s.rms_eps)
+            else:
+                x = x if pending is None else x + pending
+                h = F.rms_norm(x, (s.hidden,), p["w_in"], s.rms_eps)
             qkv = h @ p["w_qkv"]
-            q = qkv[:, : nq * d].view(B, nq, d)
-            k = qkv[:, nq * d: (nq + nkv) * d].view(B, nkv, d)
             v = qkv[:, (nq + nkv) * d: (nq + 2 * nkv) * d].reshape(B, nkv, d)
-            q = self._rope(F.rms_norm(q, (d,), p["q_norm"], s.rms_eps), cos, sin)
-            k = self._rope(F.rms_norm(k, (d,), p["k_norm"], s.rms_eps), cos, sin)
+            if self.fused:
+                q, k = ops.qk_norm_rope(qkv, nq, nkv, p["q_norm"], p["k_norm"], s.rms_eps, cos, sin)
+            else:
+                q = qkv[:, : nq * d].view(B, nq, d)
+                k = qkv[:, nq * d: (nq + nkv) * d].view(B, nkv, d)
+                q = self._rope(F.rms_norm(q, (d,), p["q_norm"], s.rms_eps), cos, sin)
+                k = self._rope(F.rms_norm(k, (d,), p["k_norm"], s.rms_eps), cos, sin)
             routed = None
             if l in self.router_layers and self.svc is not None:
                 self._mark("route_start", l)
-                rq = F.normalize(qkv[:, (nq + 2 * nkv) * d:].view(B, nq, 1, d), p=2, dim=-1)
-                routed = self.svc.route(rq, self.query_mask, l)
+                rq = qkv[:, (nq + 2 * nkv) * d:].view(B, nq, 1, d)      # L2-normalised inside the fold kernel
+                routed = self.svc.route(rq, self.query_mask, l, l2_normalize=True)
                 self._mark("route_end", l)
             self._mark("attn_start", l)
             ops.sparse_decode_attn(q, self.k_cache[l], self.v_cache[l], self.kv_len, k, v, n_splits=self.n_splits,
@@ -156,11 +169,16 @@ class SparseDecodeModel:
                     done = torch.cuda.Event(enable_timing=self.probe is not None)
                     done.record(self.fetch_stream)
                     fetch_done.append(done)
-            x = x + self.attn_out @ p["w_o"]
-            h = F.rms_norm(x, (s.hidden,), p["w_post"], s.rms_eps)
-            gu = h @ p["w_gate_up"]
-            x = x + (F.silu(gu[:, : s.ffn]) * gu[:, s.ffn:]) @ p["w_down"]
-        return x
+            attn = self.attn_out @ p["w_o"]
+            if self.fused:
+                x, h = ops.add_rmsnorm(x, attn, p["w_post"], s.rms_eps)
+                pending = ops.silu_mul(h @ p["w_gate_up"], s.ffn) @ p["w_down"]
+            else:
+                x = x + attn
+                h = F.rms_norm(x, (s.hidden,), p["w_post"], s.rms_eps)
+                gu = h @ p["w_gate_up"]
+                pending = (F.silu(gu[:, : s.ffn]) * gu[:, s.ffn:]) @ p["w_down"]
+        return x, pending
 
     def _front(self):
         """Embedding, rotary tables and the layers below the first router layer -> ``self._x_mid``."""
@@ -168,14 +186,21 @@ class SparseDecodeModel:
         emb = torch.cat([ang, ang], dim=-1)
         self._cos.copy_(emb.cos().unsqueeze(1))
         self._sin.copy_(emb.sin().unsqueeze(1))
-        self._x_mid.copy_(self._layers(self.embed[self.tokens], 0, self.split_layer, []))
+        x, pending = self._layers(self.embed[self.tokens], None, 0, self.split_layer, [])
+        self._x_mid.copy_(x)
+        if pending is not None:
+            self._pending_mid.copy_(pending)
 
     def _back(self):
         """Router layers and everything above them, lm_head, greedy token, cache-length update."""
         s = self.s
         fetch_done = []
-        x = self._layers(self._x_mid, self.split_layer, s.num_layers, fetch_done)
-        x = F.rms_norm(x, (s.hidden,), self.w_final, s.rms_eps)
+        x, pending = self._layers(self._x_mid, self._pending_mid if self.split_layer > 0 else None, self.split_layer,
+                                  s.num_layers, fetch_done)
+        if self.fused:
+            _, x = ops.add_rmsnorm(x, pending, self.w_final, s.rms_eps)
+        else:
+            x = F.rms_norm(x if pending is None else x + pending, (s.hidden,), self.w_final, s.rms_eps)
         nxt = (x @ self.lm_head).argmax(dim=-1)
         self._mark("compute_end", 0)
         if self.probe is not None:

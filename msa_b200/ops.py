@@ -382,6 +382,55 @@ def doc_attention_pool(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, token_
     return out, pooled_k, pooled_v
 
 
+def qk_norm_rope(qkv: torch.Tensor, n_q_heads: int, n_kv_heads: int, q_weight: torch.Tensor, k_weight: torch.Tensor,
+                 eps: float, cos: torch.Tensor, sin: torch.Tensor, q_out: Optional[torch.Tensor] = None,
+                 k_out: Optional[torch.Tensor] = None):
+    """Per-head RMSNorm + rotary embedding of the q and k heads of a fused projection output ``[B, >= (Hq+Hkv)*128]``
+    (bf16).  cos / sin ``[B, 128]``.  Returns ``(q[B, Hq, 128], k[B, Hkv, 128])``."""
+    A.need_cuda(qkv, q_weight, k_weight, cos, sin)
+    b = qkv.shape[0]
+    if qkv.dtype != torch.bfloat16 or qkv.stride(1) != 1:
+        raise A.MsaError("qk_norm_rope: qkv must be bf16 with a contiguous feature axis")
+    cos, sin = cos.reshape(b, 128), sin.reshape(b, 128)
+    if not cos.is_contiguous() or not sin.is_contiguous():
+        cos, sin = cos.contiguous(), sin.contiguous()
+    if q_out is None:
+        q_out = torch.empty((b, n_q_heads, 128), dtype=qkv.dtype, device=qkv.device)
+    if k_out is None:
+        k_out = torch.empty((b, n_kv_heads, 128), dtype=qkv.dtype, device=qkv.device)
+    A.check(A.lib().msa_qk_norm_rope(A.ptr(qkv), qkv.stride(0), b, n_q_heads, n_kv_heads, 128, A.ptr(q_weight),
+                                     A.ptr(k_weight), float(eps), A.ptr(cos), A.ptr(sin), A.ptr(q_out), A.ptr(k_out),
+                                     A.stream_ptr(qkv.device)), "msa_qk_norm_rope")
+    return q_out, k_out
+
+
+def add_rmsnorm(x: torch.Tensor, y: Optional[torch.Tensor], weight: torch.Tensor, eps: float):
+    """``x_new = x + y`` (``y`` None: ``x``), ``h = rmsnorm(x_new) * weight``; rows ``[n, hidden]`` bf16 contiguous.
+    Returns ``(x_new, h)``."""
+    A.need_cuda(x, y, weight)
+    if x.dtype != torch.bfloat16 or not x.is_contiguous() or (y is not None and not y.is_contiguous()):
+        raise A.MsaError("add_rmsnorm: bf16 contiguous rows expected")
+    n, hidden = x.shape
+    x_new = torch.empty_like(x) if y is not None else x
+    h = torch.empty_like(x)
+    A.check(A.lib().msa_add_rmsnorm(A.ptr(x), A.ptr(y), A.ptr(weight), float(eps), n, hidden,
+                                    A.ptr(x_new) if y is not None else 0, A.ptr(h), A.stream_ptr(x.device)),
+            "msa_add_rmsnorm")
+    return x_new, h
+
+
+def silu_mul(gate_up: torch.Tensor, ffn: int) -> torch.Tensor:
+    """``silu(gate_up[:, :ffn]) * gate_up[:, ffn:]`` (bf16)."""
+    A.need_cuda(gate_up)
+    if gate_up.dtype != torch.bfloat16 or gate_up.stride(1) != 1:
+        raise A.MsaError("silu_mul: bf16 rows with a contiguous feature axis expected")
+    n = gate_up.shape[0]
+    out = torch.empty((n, ffn), dtype=gate_up.dtype, device=gate_up.device)
+    A.check(A.lib().msa_silu_mul(A.ptr(gate_up), gate_up.stride(0), n, ffn, A.ptr(out), A.stream_ptr(gate_up.device)),
+            "msa_silu_mul")
+    return out
+
+
 def keys_to_scores(keys: torch.Tensor) -> torch.Tensor:
     """Decode a table of order-preserving keys (int32 storage) back to float32 scores."""
     u = keys.to(torch.int64) & 0xFFFFFFFF

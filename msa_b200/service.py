@@ -213,7 +213,7 @@ class MSAService(Memory, MemoryClientBase):
         self._shared_banks = []
 
     # ------------------------------------------------------------------ the layer-facing call
-    def _gather_querys(self, query_states: torch.Tensor, query_mask: torch.Tensor):
+    def _gather_querys(self, query_states: torch.Tensor, query_mask: torch.Tensor, l2_normalize: bool = False):
         """Fold local queries, agree on the padded length, all-gather (:1088-1131).
         Returns ``(q_folded_all[W*B*s_pad, Hkv*D], row_bias_all, s_pad, B)``."""
         b, hq, s, d = query_states.shape
@@ -224,17 +224,19 @@ class MSAService(Memory, MemoryClientBase):
             s_common = int(lens.max().item())
         s_pad = ops.route_s_pad(s_common, qr)
         qf, bias, _ = ops.fold_queries(query_states, query_mask, self.num_key_value_groups, query_reduce=qr,
-                                       s_pad=s_pad)
+                                       s_pad=s_pad, l2_normalize=l2_normalize)
         if self.world_size > 1:
             qf = all_gather_cat(qf, self.world_size, self.group).view(-1, qf.shape[1])
             bias = all_gather_cat(bias, self.world_size, self.group).view(-1)
         return qf, bias, s_pad, b
 
-    def route(self, query_states: torch.Tensor, query_mask: torch.Tensor, layer_idx: int):
+    def route(self, query_states: torch.Tensor, query_mask: torch.Tensor, layer_idx: int, l2_normalize: bool = False):
         """Steps 1-4 of ``doc_query`` (:1149-1191): returns the merged winners of this rank's own
-        queries ``(scores[B,k], local_ids[B,k] (-1 invalid), global_ids[B,k], owner_rank[B,k])``."""
+        queries ``(scores[B,k], local_ids[B,k] (-1 invalid), global_ids[B,k], owner_rank[B,k])``.
+        ``l2_normalize``: the queries are raw projections; normalise every head inside the fold kernel
+        (what the layer does with ``F.normalize`` before calling ``doc_query`` in cosine mode)."""
         b, hq, s, d = query_states.shape
-        qf, bias, s_pad, _ = self._gather_querys(query_states, query_mask)
+        qf, bias, s_pad, _ = self._gather_querys(query_states, query_mask, l2_normalize)
         scale = self.scaling if self.scaling > 0 else 1.0
         n_all = self.world_size * b
         sc, li, gi = self.score_folded(layer_idx, qf, bias, n_all, s_pad, hq, self.shard_top_k, scale=scale)

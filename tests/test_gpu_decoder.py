@@ -131,3 +131,46 @@ def test_pipelined_loop_produces_the_same_tokens_and_caches():
     for x, y in zip(toks_a, toks_c):
         assert torch.equal(x, y)
     a.svc.check_status()
+
+
+def test_dense_glue_kernels_match_torch():
+    """q/k norm + RoPE, residual add + RMSNorm and SiLU*up against the torch ops they replace (bf16 inputs,
+    fp32 restatement, one bf16 rounding step of tolerance)."""
+    from msa_b200 import ops
+    g = torch.Generator().manual_seed(4)
+    b, nq, nkv, d, hidden, ffn, eps = 5, 8, 2, 128, 2560, 1024, 1e-6
+    qkv = torch.randn(b, (nq + 2 * nkv + nq) * d, generator=g).to(torch.bfloat16).to(DEV)
+    qw = (1 + 0.1 * torch.randn(d, generator=g)).to(torch.bfloat16).to(DEV)
+    kw = (1 + 0.1 * torch.randn(d, generator=g)).to(torch.bfloat16).to(DEV)
+    ang = torch.rand(b, d // 2, generator=g) * 6.28
+    emb = torch.cat([ang, ang], -1)
+    cos, sin = emb.cos().to(torch.bfloat16).to(DEV), emb.sin().to(torch.bfloat16).to(DEV)
+    q, k = ops.qk_norm_rope(qkv, nq, nkv, qw, kw, eps, cos, sin)
+
+    def ref_heads(x, w):
+        x = x.float()
+        x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+        return O.rope_rotate_half(x, cos.float().unsqueeze(1), sin.float().unsqueeze(1))
+    q_ref = ref_heads(qkv[:, : nq * d].view(b, nq, d), qw)
+    k_ref = ref_heads(qkv[:, nq * d:(nq + nkv) * d].view(b, nkv, d), kw)
+    assert (q.float() - q_ref).abs().max().item() < 3e-2 and rel(q.float(), q_ref) < 8e-3
+    assert (k.float() - k_ref).abs().max().item() < 3e-2 and rel(k.float(), k_ref) < 8e-3
+
+    x = torch.randn(b, hidden, generator=g).to(torch.bfloat16).to(DEV)
+    y = torch.randn(b, hidden, generator=g).to(torch.bfloat16).to(DEV)
+    w = (1 + 0.1 * torch.randn(hidden, generator=g)).to(torch.bfloat16).to(DEV)
+    x_new, h = ops.add_rmsnorm(x, y, w, eps)
+    assert torch.equal(x_new, x + y)
+    xs = (x + y).float()
+    h_ref = xs * torch.rsqrt(xs.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+    assert rel(h.float(), h_ref) < 8e-3
+    x_same, h2 = ops.add_rmsnorm(x, None, w, eps)
+    assert x_same is x and rel(h2.float(), F.rms_norm(x.float(), (hidden,), w.float(), eps)) < 8e-3
+
+    gu = torch.randn(b, 2 * ffn, generator=g).to(torch.bfloat16).to(DEV)
+    out = ops.silu_mul(gu, ffn)
+    assert rel(out.float(), F.silu(gu[:, :ffn].float()) * gu[:, ffn:].float()) < 8e-3
+
+
+def rel(a, b):
+    return float((a - b).norm() / b.norm())
