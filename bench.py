@@ -819,14 +819,14 @@ def run_generate(args):
         torch.cuda.synchronize(dev)
         return float(t.item()), mode
 
-    timed_run(False)                       # settles lazily initialised communicators and the clocks
-    ms_nofetch, _ = timed_run(False)       # same step without the host fetch: what the fetch may hide behind
-    ms_plain, _ = timed_run(True, pipelined=False)   # unrotated loop: the fetch has only the rest of its own step
+    timed_run(True)                        # untimed pass: settles lazily initialised communicators and the clocks
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     ms_total, mode = timed_run(True)
     clocks = sampler.stop() if rank == 0 else None
+    ms_plain, _ = timed_run(True, pipelined=False)   # unrotated loop: the fetch has only the rest of its own step
+    ms_nofetch, _ = timed_run(False)       # same step without the host fetch: what the fetch may hide behind
     svc.check_status()
     tokens_host = model.tokens.cpu()
     if world > 1:
