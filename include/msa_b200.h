@@ -302,6 +302,21 @@ int msa_doc_attention_pool(const void* q, int64_t q_stride_b, int64_t q_stride_h
                            const int32_t* chunk_offsets, int32_t n_chunks, int32_t pool_size, void* pooled_k,
                            void* pooled_v, int64_t pool_chunk_stride, int64_t pool_head_stride, void* stream);
 
+/* msa_doc_attention_tc: the same attention as msa_doc_attention_pool (without the pooling by-product) on
+ * tcgen05 tensor cores, for segments that are runs of CONSECUTIVE tokens of one row (token_index of a
+ * segment ascending by one; the caller checks this, e.g. documents without masked tokens).  q, k, v must
+ * be token-major ([B, S, H, D] storage viewed as [B, H, S, D]; the row stride may exceed H*D) or contiguous
+ * head-major tensors; anything else is rejected with MSA_ERR_ARG and belongs to msa_doc_attention_pool.
+ * status: int32[4], zeroed by the caller; status[0] != 0 after completion means a bounded barrier wait ran
+ * out inside the kernel (output invalid).
+ */
+int msa_doc_attention_tc(const void* q, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s, const void* k,
+                         const void* v, int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s,
+                         const int32_t* token_index, const int32_t* seg_offsets, int32_t n_segments,
+                         int32_t max_segment_len, int32_t n_seq, int32_t seq_len, int32_t n_q_heads,
+                         int32_t n_kv_heads, int32_t head_dim, int32_t dtype, float scale, void* out,
+                         int32_t* status, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * Dense glue of a decode step (bf16).  No single reference function: they replace the chains of
  * elementwise torch kernels that transformers' Qwen3 modules issue between the GEMMs of a layer as

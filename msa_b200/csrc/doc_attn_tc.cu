@@ -1,0 +1,383 @@
+// Stage-1 attention inside every document on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), bf16,
+// head_dim 128, for documents that are runs of consecutive tokens of one row.
+//
+// CTA = 128 query tokens of one head of one document; 192 threads: warps 0-3 softmax (thread = query row =
+// TMEM lane), warp 4 TMA producer, warp 5 MMA issuer + TMEM owner.  Per 128-key tile:
+//     S = Q K^T        tcgen05.mma, A = Q and B = K both K-major in shared memory, fp32 into TMEM (two S buffers:
+//                      the MMA of tile t+1 runs while the threads are in the softmax of tile t);
+//     softmax          each thread reads its row of S with tcgen05.ld (two passes: maximum, then exponentials),
+//                      keeps the running maximum and sum, and writes P as packed bf16 back to TMEM (tcgen05.st);
+//     O_t = P V        tcgen05.mma with A = P read from TMEM and B = V as an MN-major shared-memory operand (V's
+//                      rows are keys, the reduction axis, so the tile TMA delivers IS the MN-major image);
+//     O = O f + O_t    in registers (128 fp32 per thread), f = exp2(m_old - m_new).
+// Causality: key tile j <= row block index; only the last tile of a CTA is masked.  Keys past the document's
+// end are rows of the next document (or TMA's zero fill) and sit above the diagonal of every valid row.
+// Every mbarrier wait is bounded; on expiry the CTA raises status[0], drains and frees TMEM.
+//
+// Bounds: flops 4*128*128*128 per tile pair; the exponentials (16 per clock per SM) take about as long as the
+// two MMAs, so the kernel is bound by MUFU + tensor pipe in alternation, not by HBM.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace msa {
+
+constexpr int kAtRows = 128, kAtKeys = 128, kAtD = 128;
+constexpr int kAtThreads = 192;
+constexpr int kAtBlk = kAtRows * 64 * 2;                 // one 64-column block of a 128-row tile: 16 KB
+constexpr int kAtTile = 2 * kAtBlk;                      // a [128 x 128] bf16 tile
+constexpr int kAtStages = 2;
+constexpr int kAtSmem = kAtTile + kAtStages * 2 * kAtTile + 1024;
+constexpr uint32_t kColS = 0, kColP = 256, kColO = 320;  // TMEM columns: S0 0..127, S1 128..255, P 256..319, O 320..447
+
+struct DocAttnTcParams {
+  const int32_t* token_index;   // flat position of every listed token; a segment's tokens are consecutive
+  const int32_t* seg_off;
+  int S, n_q_heads, n_kv_heads;
+  int q_yb, q_yh, q_xh;         // q tile coordinates: y = b*q_yb + h*q_yh + s, x = h*q_xh + 64*block
+  int k_yb, k_yh, k_xh;
+  uint32_t div_mul, div_shift;  // tok / S
+  float scale_log2e;
+  __nv_bfloat16* out;
+  int32_t* status;
+};
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// tcgen05.mma with the A operand in tensor memory.
+__device__ __forceinline__ void tc_mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// MN-major operand tile in shared memory, SWIZZLE_128B: rows are indices of the reduction axis (keys), each
+// row holds 64 consecutive MN elements (128 bytes); 8 rows form a 1024-byte swizzle atom (stride byte offset
+// = distance between 8-row groups); the next 64 MN elements are a separate block (leading byte offset).
+__device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t smem_addr, uint32_t lbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)(1024u >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(kAtThreads, 1)
+doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                   const __grid_constant__ CUtensorMap tmap_v, const DocAttnTcParams p) {
+  extern __shared__ unsigned char smem_dyn[];
+  __shared__ uint64_t s_q_full, s_kv_full[kAtStages], s_kv_empty[kAtStages], s_s_full[2], s_p_full, s_o_full, s_drain;
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  const int seg = blockIdx.z, hq = blockIdx.y;
+  const int t0 = p.seg_off[seg], len = p.seg_off[seg + 1] - t0;
+  const int n_mb = (len + kAtRows - 1) / kAtRows;
+  if ((int)blockIdx.x >= n_mb) return;                 // whole CTA, before anything is allocated
+  const int mb = n_mb - 1 - (int)blockIdx.x;           // long row blocks first
+  const int r0 = mb * kAtRows, n_kt = mb + 1;
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int tok0 = p.token_index[t0];
+  const int b = (int)((__umulhi((uint32_t)tok0, p.div_mul) + (uint32_t)tok0) >> p.div_shift);
+  const int s0 = tok0 - b * p.S;
+  const int hk = hq / (p.n_q_heads / p.n_kv_heads);
+  unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  unsigned char* q_smem = tiles;
+  unsigned char* kv_smem = tiles + kAtTile;              // stage s: K at s*2*tile, V right after
+  volatile int* abort_flag = &s_abort;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&s_q_full, 1);
+    for (int s = 0; s < kAtStages; ++s) { mbar_init(&s_kv_full[s], 1); mbar_init(&s_kv_empty[s], 1); }
+    mbar_init(&s_s_full[0], 1); mbar_init(&s_s_full[1], 1);
+    mbar_init(&s_p_full, 4);
+    mbar_init(&s_o_full, 1);
+    mbar_init(&s_drain, 1);
+    s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
+                 "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+
+  if (warp == 4) {
+    // ------------------------------- TMA producer -------------------------------------
+    if (lane == 0) {
+      const int qy = b * p.q_yb + hq * p.q_yh + s0 + r0, qx = hq * p.q_xh;
+      const int ky = b * p.k_yb + hk * p.k_yh + s0, kx = hk * p.k_xh;
+      mbar_expect_tx(&s_q_full, kAtTile);
+      tma_load_2d(q_smem, &tmap_q, qx, qy, &s_q_full);
+      tma_load_2d(q_smem + kAtBlk, &tmap_q, qx + 64, qy, &s_q_full);
+      bool ok = true;
+      uint32_t armed = 0, armed_parity = 0;
+      for (int t = 0; t < n_kt && ok; ++t) {
+        const int stage = t % kAtStages;
+        const uint32_t phase = (uint32_t)((t / kAtStages) & 1);
+        if (!(ok = mbar_wait(&s_kv_empty[stage], phase ^ 1u, abort_flag, p.status, 1))) break;
+        unsigned char* ks = kv_smem + (size_t)stage * 2 * kAtTile;
+        mbar_expect_tx(&s_kv_full[stage], 2 * kAtTile);
+        tma_load_2d(ks, &tmap_k, kx, ky + t * kAtKeys, &s_kv_full[stage]);
+        tma_load_2d(ks + kAtBlk, &tmap_k, kx + 64, ky + t * kAtKeys, &s_kv_full[stage]);
+        tma_load_2d(ks + kAtTile, &tmap_v, kx, ky + t * kAtKeys, &s_kv_full[stage]);
+        tma_load_2d(ks + kAtTile + kAtBlk, &tmap_v, kx + 64, ky + t * kAtKeys, &s_kv_full[stage]);
+        armed |= 1u << stage;
+        armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+      }
+      if (!ok) {   // gave up: let the copies already issued land before shared memory is released
+        for (int s = 0; s < kAtStages; ++s)
+          if (armed & (1u << s)) {
+            const unsigned long long w0 = global_ns();
+            while (!mbar_try_wait(&s_kv_full[s], (armed_parity >> s) & 1u) && global_ns() - w0 < kWaitLimitNs) {}
+          }
+      }
+      {            // the query tile is always in flight once
+        const unsigned long long w0 = global_ns();
+        while (!mbar_try_wait(&s_q_full, 0) && global_ns() - w0 < kWaitLimitNs) {}
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------- MMA issuer ----------------------------------------
+    if (lane == 0) {
+      // D = f32, A = B = bf16, M = 128, N = 128; S: both operands K-major; PV: B (= V) MN-major
+      const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kAtKeys >> 3) << 17) |
+                               ((uint32_t)(kAtRows >> 4) << 24);
+      const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(kAtD >> 3) << 17) |
+                                ((uint32_t)(kAtRows >> 4) << 24);
+      const uint32_t qa = smem_u32(q_smem);
+      auto issue_s = [&](int t) {   // S(t) into buffer t & 1
+        const uint32_t ks = smem_u32(kv_smem + (size_t)(t % kAtStages) * 2 * kAtTile);
+        const uint32_t d_tmem = tmem_base + kColS + (uint32_t)(t & 1) * kAtKeys;
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb) {
+          const uint64_t a_desc = make_smem_desc(qa + kb * kAtBlk), b_desc = make_smem_desc(ks + kb * kAtBlk);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            tc_mma_bf16(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc_s, (kb > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(&s_s_full[t & 1]);
+      };
+      bool ok = mbar_wait(&s_q_full, 0, abort_flag, p.status, 2);
+      if (ok) ok = mbar_wait(&s_kv_full[0], 0, abort_flag, p.status, 3);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+      }
+      for (int t = 0; t < n_kt && ok; ++t) {
+        if (t + 1 < n_kt) {   // S of the next tile runs under this tile's softmax
+          const int st = (t + 1) % kAtStages;
+          if (!(ok = mbar_wait(&s_kv_full[st], (uint32_t)(((t + 1) / kAtStages) & 1), abort_flag, p.status, 3))) break;
+          tc_fence_after();
+          issue_s(t + 1);
+        }
+        if (!(ok = mbar_wait(&s_p_full, (uint32_t)(t & 1), abort_flag, p.status, 4))) break;
+        tc_fence_after();
+        const uint32_t vs = smem_u32(kv_smem + (size_t)(t % kAtStages) * 2 * kAtTile + kAtTile);
+#pragma unroll
+        for (int j = 0; j < kAtKeys / 16; ++j)   // 16 keys per step: 8 TMEM columns of P, two 8-key groups of V
+          tc_mma_bf16_ts(tmem_base + kColO, tmem_base + kColP + (uint32_t)(8 * j),
+                         make_smem_desc_mn(vs + j * 2048, kAtBlk), idesc_pv, j > 0 ? 1u : 0u);
+        tc_commit(&s_o_full);
+        tc_commit(&s_kv_empty[t % kAtStages]);
+      }
+      tc_commit(&s_drain);   // everything issued so far must retire before TMEM is freed
+      const unsigned long long w0 = global_ns();
+      while (!mbar_try_wait(&s_drain, 0) && global_ns() - w0 < kWaitLimitNs) {}
+    }
+  } else {
+    // ------------------------------- softmax / output (warps 0-3) ----------------------
+    const int row = r0 + warp * 32 + lane;               // row of the document; TMEM lane = warp*32 + lane
+    const int limit = min(row, len - 1);                 // last visible key
+    const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+    float o[kAtD];
+#pragma unroll
+    for (int i = 0; i < kAtD; ++i) o[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int t = 0; t < n_kt; ++t) {
+      ok = mbar_wait(&s_s_full[t & 1], (uint32_t)((t >> 1) & 1), abort_flag, p.status, 5);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t s_addr = lane_base + kColS + (uint32_t)(t & 1) * kAtKeys;
+      const int key0 = t * kAtKeys;
+      const bool diag = t == n_kt - 1;
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(s_addr + 32 * c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float x = __uint_as_float(v[i]);
+          mx = fmaxf(mx, (!diag || key0 + 32 * c + i <= limit) ? x : -INFINITY);
+        }
+      }
+      const float m_new = fmaxf(m_run, mx);              // finite: key 0 is visible to every row
+      const float f = exp2f((m_run - m_new) * p.scale_log2e);
+      const float neg_m = -m_new * p.scale_log2e;
+      m_run = m_new;
+      // pass 2: exponentials, row sum, P as packed bf16 into TMEM
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32], pk[16];
+        tmem_ld32(s_addr + 32 * c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float e0 = exp2f(fmaf(__uint_as_float(v[i]), p.scale_log2e, neg_m));
+          float e1 = exp2f(fmaf(__uint_as_float(v[i + 1]), p.scale_log2e, neg_m));
+          if (diag) {
+            if (key0 + 32 * c + i > limit) e0 = 0.f;
+            if (key0 + 32 * c + i + 1 > limit) e1 = 0.f;
+          }
+          sum += e0 + e1;
+          pk[i >> 1] = pack2_bf16(e0, e1);
+        }
+        tmem_st16(lane_base + kColP + 16 * c, pk);
+      }
+      l_run = l_run * f + sum;
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_p_full);
+      // O_t from the tensor pipe, folded into the running output
+      ok = mbar_wait(&s_o_full, (uint32_t)(t & 1), abort_flag, p.status, 6);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(lane_base + kColO + 32 * c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[32 * c + i] = fmaf(o[32 * c + i], f, __uint_as_float(v[i]));
+      }
+      tc_fence_before();
+    }
+    if (ok && row < len) {
+      const float inv = 1.f / l_run;
+      __nv_bfloat16* dst = p.out + ((long long)tok0 + row) * p.n_q_heads * kAtD + (long long)hq * kAtD;
+#pragma unroll
+      for (int i = 0; i < kAtD; i += 8) {
+        uint4 w;
+        w.x = pack2_bf16(o[i] * inv, o[i + 1] * inv);
+        w.y = pack2_bf16(o[i + 2] * inv, o[i + 3] * inv);
+        w.z = pack2_bf16(o[i + 4] * inv, o[i + 5] * inv);
+        w.w = pack2_bf16(o[i + 6] * inv, o[i + 7] * inv);
+        *reinterpret_cast<uint4*>(dst + i) = w;
+      }
+    }
+  }
+
+  // teardown: all roles meet, then the allocating warp returns TMEM
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 5)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+}
+
+}  // namespace msa
+
+using namespace msa;
+
+namespace {
+// A [B, H, S, D] tensor given by strides as a 2-D tensor map with one row per token.
+// Token major (projection output, heads side by side in a row): rows B*S, columns H*D.
+// Head major (contiguous [B, H, S, D]): rows B*H*S, columns D.
+struct View2D { uint64_t rows, cols, row_stride; int yb, yh, xh; bool ok; };
+View2D view_2d(int64_t sb, int64_t sh, int64_t ss, int B, int H, int S, int D) {
+  View2D v{};
+  if (sh == D && ss >= (int64_t)H * D && (B == 1 || sb == (int64_t)S * ss)) {
+    v = View2D{(uint64_t)B * S, (uint64_t)H * D, (uint64_t)ss, S, 0, D, true};
+  } else if (ss >= D && sh == (int64_t)S * ss && (B == 1 || sb == (int64_t)H * sh)) {
+    v = View2D{(uint64_t)B * H * S, (uint64_t)D, (uint64_t)ss, H * S, S, 0, true};
+  }
+  return v;
+}
+}  // namespace
+
+extern "C" int msa_doc_attention_tc(const void* q, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                                    const void* k, const void* v, int64_t k_stride_b, int64_t k_stride_h,
+                                    int64_t k_stride_s, const int32_t* token_index, const int32_t* seg_offsets,
+                                    int32_t n_segments, int32_t max_segment_len, int32_t n_seq, int32_t seq_len,
+                                    int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim, int32_t dtype, float scale,
+                                    void* out, int32_t* status, void* stream) {
+  MSA_REQUIRE(q && k && v && token_index && seg_offsets && out && status, "doc_attention_tc: null pointer");
+  MSA_REQUIRE(dtype == MSA_BF16 && head_dim == kAtD, "doc_attention_tc: bf16 with head_dim 128 only");
+  MSA_REQUIRE(n_segments >= 0 && n_segments <= 65535 && max_segment_len >= 0 && n_seq > 0 && seq_len > 0 &&
+                  n_q_heads > 0 && n_kv_heads > 0 && n_q_heads % n_kv_heads == 0 && n_q_heads <= 65535,
+              "doc_attention_tc: bad sizes (at most 65535 segments per call)");
+  MSA_REQUIRE((long long)n_seq * seq_len * n_q_heads < (1ll << 31), "doc_attention_tc: more than 2^31 token rows");
+  MSA_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) && q_stride_s % 8 == 0 &&
+                  k_stride_s % 8 == 0, "doc_attention_tc: rows must be 16-byte aligned");
+  const View2D vq = view_2d(q_stride_b, q_stride_h, q_stride_s, n_seq, n_q_heads, seq_len, head_dim);
+  const View2D vk = view_2d(k_stride_b, k_stride_h, k_stride_s, n_seq, n_kv_heads, seq_len, head_dim);
+  MSA_REQUIRE(vq.ok && vk.ok, "doc_attention_tc: q / k / v must be token-major or contiguous head-major tensors");
+  if (n_segments == 0 || max_segment_len == 0) return MSA_OK;
+
+  CUtensorMap map_q, map_k, map_v;
+  int rc = make_map(&map_q, q, vq.rows, vq.cols, vq.row_stride, 64, kAtRows);
+  if (rc != MSA_OK) return rc;
+  rc = make_map(&map_k, k, vk.rows, vk.cols, vk.row_stride, 64, kAtKeys);
+  if (rc != MSA_OK) return rc;
+  rc = make_map(&map_v, v, vk.rows, vk.cols, vk.row_stride, 64, kAtKeys);
+  if (rc != MSA_OK) return rc;
+
+  DocAttnTcParams p{};
+  p.token_index = token_index; p.seg_off = seg_offsets; p.S = seq_len; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
+  p.q_yb = vq.yb; p.q_yh = vq.yh; p.q_xh = vq.xh; p.k_yb = vk.yb; p.k_yh = vk.yh; p.k_xh = vk.xh;
+  uint32_t shift = 0;
+  while ((1ull << shift) < (uint64_t)seq_len) ++shift;
+  p.div_shift = shift;
+  p.div_mul = (uint32_t)((((1ull << shift) - (uint64_t)seq_len) << 32) / (uint64_t)seq_len + 1);
+  p.scale_log2e = scale * 1.4426950408889634f;
+  p.out = (__nv_bfloat16*)out;
+  p.status = status;
+
+  static thread_local bool configured = false;
+  if (!configured) {
+    MSA_CUDA_OK(cudaFuncSetAttribute(doc_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAtSmem));
+    configured = true;
+  }
+  dim3 grid((max_segment_len + kAtRows - 1) / kAtRows, n_q_heads, n_segments);
+  doc_attn_tc_kernel<<<grid, kAtThreads, kAtSmem, (cudaStream_t)stream>>>(map_q, map_k, map_v, p);
+  MSA_LAUNCH_OK("doc_attn_tc_kernel");
+  return MSA_OK;
+}

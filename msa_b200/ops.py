@@ -382,6 +382,35 @@ def doc_attention_pool(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, token_
     return out, pooled_k, pooled_v
 
 
+def doc_attention_tc(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, token_index: torch.Tensor,
+                     seg_offsets: torch.Tensor, max_segment_len: int, out: Optional[torch.Tensor] = None,
+                     scale: Optional[float] = None, status: Optional[torch.Tensor] = None):
+    """``doc_attention_pool`` without pooling on the tcgen05 kernel: every segment must be a run of consecutive
+    tokens of one row, and q / k / v token-major or contiguous head-major (no copies are made here; other
+    layouts raise).  Returns ``(out, status)``; ``status[0] != 0`` after a sync means the kernel gave up."""
+    A.need_cuda(q, k, v, token_index, seg_offsets)
+    b, hq, s, d = q.shape
+    hkv = k.shape[1]
+    if v.stride() != k.stride() or q.stride(3) != 1 or k.stride(3) != 1:
+        raise A.MsaError("doc_attention_tc: k and v must share strides and the feature axis must be contiguous")
+    if token_index.dtype != torch.int32 or seg_offsets.dtype != torch.int32:
+        raise A.MsaError("doc_attention_tc: token_index and seg_offsets must be int32")
+    if out is None:
+        out = torch.zeros((b, s, hq * d), dtype=q.dtype, device=q.device)
+    if status is None:
+        status = torch.zeros(4, dtype=torch.int32, device=q.device)
+    scale = (1.0 / math.sqrt(d)) if scale is None else scale
+    n_seg = seg_offsets.numel() - 1
+    for lo in range(0, n_seg, 65535):
+        n = min(65535, n_seg - lo)
+        A.check(A.lib().msa_doc_attention_tc(
+            A.ptr(q), q.stride(0), q.stride(1), q.stride(2), A.ptr(k), A.ptr(v), k.stride(0), k.stride(1), k.stride(2),
+            A.ptr(token_index), A.ptr(seg_offsets) + 4 * lo, n, int(max_segment_len), b, s, hq, hkv, d,
+            A.dtype_code(q.dtype), float(scale), A.ptr(out), A.ptr(status), A.stream_ptr(q.device)),
+            "msa_doc_attention_tc")
+    return out, status
+
+
 def qk_norm_rope(qkv: torch.Tensor, n_q_heads: int, n_kv_heads: int, q_weight: torch.Tensor, k_weight: torch.Tensor,
                  eps: float, cos: torch.Tensor, sin: torch.Tensor, q_out: Optional[torch.Tensor] = None,
                  k_out: Optional[torch.Tensor] = None):

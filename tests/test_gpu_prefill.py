@@ -280,3 +280,40 @@ def test_layer_bf16_on_own_kernels_matches_fp32_layer_on_library_path():
     assert rel(b_["ck"], a["ck"]) < 2e-2 and rel(b_["cv"], a["cv"]) < 2e-2
     valid = mask2.bool().cpu()
     assert rel(b_["out2"][valid], a["out2"][valid]) < 3e-2
+
+
+@pytest.mark.parametrize("layout", ["token_major", "head_major"])
+@pytest.mark.parametrize("doc_lens", [[100], [128, 64, 1, 65, 130, 512, 300], [700, 257]])
+def test_doc_attention_tc_matches_restatement(doc_lens, layout):
+    """The tcgen05 document attention kernel: single-tile and multi-tile documents, partial row blocks, neighbours
+    whose rows fall into the same TMA boxes, both tensor layouts."""
+    from msa_b200 import ops
+    dev = torch.device("cuda:0")
+    hq, hkv, n_t = 8, 2, 3
+    doc_ids, mask, q, k, v = _stage1_case(7, doc_lens, n_t, hq, hkv, pad=5, drop=[])
+    s = doc_ids.shape[1]
+    if layout == "token_major":      # [B, S, H, D] storage viewed as [B, H, S, D], as the layer produces it
+        q, k, v = [x.transpose(1, 2).contiguous().transpose(1, 2) for x in (q, k, v)]
+    q, k, v = q.to(dev), k.to(dev), v.to(dev)
+    tok, off, _ = ops.chunk_bookkeeping(doc_ids.to(dev), mask.to(dev), 64)
+    bounds = [n_t]
+    for n in doc_lens:
+        bounds.append(bounds[-1] + n)
+    seg_off = (torch.tensor(bounds) - n_t).to(torch.int32).to(dev)
+    scale = 128 ** -0.5
+    out, status = ops.doc_attention_tc(q, k, v, tok, seg_off, max(doc_lens), scale=scale)
+    torch.cuda.synchronize()
+    assert status.cpu().tolist()[0] == 0
+    ref = torch.zeros(s, hq * 128)
+    for i in range(len(doc_lens)):
+        x = list(range(bounds[i], bounds[i + 1]))
+        ref[x] = _segment_reference(q[0].cpu(), k[0].cpu(), v[0].cpu(), x, scale)
+    got = out[0].float().cpu()
+    assert (got - ref).norm() / ref.norm() < 1e-2
+    worst = ((got - ref).norm(dim=1) / ref.norm(dim=1).clamp_min(1e-3)).max().item()
+    assert worst < 3e-2, worst
+    outside = [t for t in range(s) if t < n_t or t >= bounds[-1]]
+    assert got[outside].abs().sum() == 0
+    # and against the mma.sync kernel
+    alt, _, _ = ops.doc_attention_pool(q, k, v, tok, seg_off, max(doc_lens), scale=scale)
+    assert (got - alt[0].float().cpu()).norm() / ref.norm() < 1e-2
