@@ -649,6 +649,9 @@ def run_secondary(args):
         except Exception:
             pass
         pool_ms = _time_ms(torch, lambda: (ops.pool_chunks(k, off, tok), ops.pool_chunks(v, off, tok)), 10, 3)
+        tc_status = torch.zeros(4, dtype=torch.int32, device=dev)
+        tc_ms = _time_ms(torch, lambda: ops.doc_attention_tc(q, k, v, tok, seg, doc_len, out=out, status=tc_status), 10, 3)
+        assert tc_status.cpu().tolist()[0] == 0, "a bounded wait ran out inside doc_attn_tc_kernel"
         steps = min(steps, 20)
         args.steps = steps
         sampler.start()
@@ -661,7 +664,8 @@ def run_secondary(args):
                         f"(q and out {t * HQ * D * 2 / 1e9:.1f} GB each, > L2)", "doc_attn_pool_kernel", alg, pk["hbm_gbs"],
                         "hbm", clocks, steps,
                         {"attention_tflops": flops / (ms / 1e3) / 1e12, "library_varlen_attention_ms": lib_ms,
-                         "separate_kv_pooling_ms": pool_ms,
+                         "separate_kv_pooling_ms": pool_ms, "tcgen05_attention_ms": tc_ms,
+                         "tcgen05_attention_tflops": flops / (tc_ms / 1e3) / 1e12,
                          "note": "mma.sync flash kernel: compute bound on the legacy tensor path, the HBM fraction is "
                                  "reported for completeness"})
 

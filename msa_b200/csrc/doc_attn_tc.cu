@@ -2,20 +2,25 @@
 // head_dim 128, for documents that are runs of consecutive tokens of one row.
 //
 // CTA = 128 query tokens of one head of one document; 192 threads: warps 0-3 softmax (thread = query row =
-// TMEM lane), warp 4 TMA producer, warp 5 MMA issuer + TMEM owner.  Per 128-key tile:
-//     S = Q K^T        tcgen05.mma, A = Q and B = K both K-major in shared memory, fp32 into TMEM (two S buffers:
-//                      the MMA of tile t+1 runs while the threads are in the softmax of tile t);
-//     softmax          each thread reads its row of S with tcgen05.ld (two passes: maximum, then exponentials),
-//                      keeps the running maximum and sum, and writes P as packed bf16 back to TMEM (tcgen05.st);
-//     O_t = P V        tcgen05.mma with A = P read from TMEM and B = V as an MN-major shared-memory operand (V's
-//                      rows are keys, the reduction axis, so the tile TMA delivers IS the MN-major image);
-//     O = O f + O_t    in registers (128 fp32 per thread), f = exp2(m_old - m_new).
+// TMEM lane), warp 4 TMA producer, warp 5 MMA issuer + TMEM owner.  Two CTAs share an SM (97 KB of shared
+// memory and 256 TMEM columns each), so one CTA's MMAs run under the other's softmax.  Per 128-key tile:
+//     S = Q K^T        tcgen05.mma, A = Q and B = K both K-major in shared memory, fp32 into TMEM columns 0..127;
+//     softmax          each thread reads its row of S with tcgen05.ld (two passes: maximum, then exponentials)
+//                      and writes P as packed bf16 over the S columns it has consumed (tcgen05.st);
+//     O += P V         tcgen05.mma with A = P read from TMEM and B = V as an MN-major shared-memory operand (V's
+//                      rows are keys, the reduction axis, so the tile TMA delivers IS the MN-major image); O
+//                      stays in TMEM columns 128..255 for the whole row block.
+// The running maximum a row's exponentials refer to is only advanced when the true maximum has moved by more
+// than 2^8 (then the warp rescales its rows of O in TMEM and its sums); the final division uses the same
+// reference, so the result is exact while almost every tile skips the rescale.
 // Causality: key tile j <= row block index; only the last tile of a CTA is masked.  Keys past the document's
 // end are rows of the next document (or TMA's zero fill) and sit above the diagonal of every valid row.
-// Every mbarrier wait is bounded; on expiry the CTA raises status[0], drains and frees TMEM.
+// K and V have one buffer each with their own barriers: K of tile t+1 lands during the softmax of tile t, V of
+// tile t+1 during S and softmax of tile t+1.  Every mbarrier wait is bounded; on expiry the CTA raises
+// status[0], drains and frees TMEM.
 //
-// Bounds: flops 4*128*128*128 per tile pair; the exponentials (16 per clock per SM) take about as long as the
-// two MMAs, so the kernel is bound by MUFU + tensor pipe in alternation, not by HBM.
+// Bounds: 4*128*128*128 flops per tile on the tensor pipe (0.28 us per SM at the measured peak) and 16,384
+// exponentials (16 per clock per SM: 0.54 us), so the kernel is bound by the exponentials.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -27,9 +32,9 @@ constexpr int kAtRows = 128, kAtKeys = 128, kAtD = 128;
 constexpr int kAtThreads = 192;
 constexpr int kAtBlk = kAtRows * 64 * 2;                 // one 64-column block of a 128-row tile: 16 KB
 constexpr int kAtTile = 2 * kAtBlk;                      // a [128 x 128] bf16 tile
-constexpr int kAtStages = 2;
-constexpr int kAtSmem = kAtTile + kAtStages * 2 * kAtTile + 1024;
-constexpr uint32_t kColS = 0, kColP = 256, kColO = 320;  // TMEM columns: S0 0..127, S1 128..255, P 256..319, O 320..447
+constexpr int kAtSmem = 3 * kAtTile + 1024;              // Q, K, V
+constexpr uint32_t kColS = 0, kColO = 128, kAtTmemCols = 256;   // TMEM columns: S (P written over it) 0..127, O 128..255
+constexpr float kRescaleStep = 8.f;                      // log2 units the row maximum may run ahead of its reference
 
 struct DocAttnTcParams {
   const int32_t* token_index;   // flat position of every listed token; a segment's tokens are consecutive
@@ -88,11 +93,11 @@ __device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-__global__ void __launch_bounds__(kAtThreads, 1)
+__global__ void __launch_bounds__(kAtThreads, 2)
 doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                    const __grid_constant__ CUtensorMap tmap_v, const DocAttnTcParams p) {
   extern __shared__ unsigned char smem_dyn[];
-  __shared__ uint64_t s_q_full, s_kv_full[kAtStages], s_kv_empty[kAtStages], s_s_full[2], s_p_full, s_o_full, s_drain;
+  __shared__ uint64_t s_q_full, s_k_full, s_k_empty, s_v_full, s_v_empty, s_s_full, s_p_full, s_o_full, s_drain;
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
 
@@ -108,14 +113,14 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   const int s0 = tok0 - b * p.S;
   const int hk = hq / (p.n_q_heads / p.n_kv_heads);
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
-  unsigned char* q_smem = tiles;
-  unsigned char* kv_smem = tiles + kAtTile;              // stage s: K at s*2*tile, V right after
+  unsigned char *q_smem = tiles, *k_smem = tiles + kAtTile, *v_smem = tiles + 2 * kAtTile;
   volatile int* abort_flag = &s_abort;
 
   if (threadIdx.x == 0) {
     mbar_init(&s_q_full, 1);
-    for (int s = 0; s < kAtStages; ++s) { mbar_init(&s_kv_full[s], 1); mbar_init(&s_kv_empty[s], 1); }
-    mbar_init(&s_s_full[0], 1); mbar_init(&s_s_full[1], 1);
+    mbar_init(&s_k_full, 1); mbar_init(&s_k_empty, 1);
+    mbar_init(&s_v_full, 1); mbar_init(&s_v_empty, 1);
+    mbar_init(&s_s_full, 1);
     mbar_init(&s_p_full, 4);
     mbar_init(&s_o_full, 1);
     mbar_init(&s_drain, 1);
@@ -124,7 +129,7 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   }
   if (warp == 5) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
-                 "r"(512) : "memory");
+                 "r"(kAtTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -141,26 +146,26 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       tma_load_2d(q_smem, &tmap_q, qx, qy, &s_q_full);
       tma_load_2d(q_smem + kAtBlk, &tmap_q, qx + 64, qy, &s_q_full);
       bool ok = true;
-      uint32_t armed = 0, armed_parity = 0;
+      int k_armed = -1, v_armed = -1;    // last tile whose copy was issued
       for (int t = 0; t < n_kt && ok; ++t) {
-        const int stage = t % kAtStages;
-        const uint32_t phase = (uint32_t)((t / kAtStages) & 1);
-        if (!(ok = mbar_wait(&s_kv_empty[stage], phase ^ 1u, abort_flag, p.status, 1))) break;
-        unsigned char* ks = kv_smem + (size_t)stage * 2 * kAtTile;
-        mbar_expect_tx(&s_kv_full[stage], 2 * kAtTile);
-        tma_load_2d(ks, &tmap_k, kx, ky + t * kAtKeys, &s_kv_full[stage]);
-        tma_load_2d(ks + kAtBlk, &tmap_k, kx + 64, ky + t * kAtKeys, &s_kv_full[stage]);
-        tma_load_2d(ks + kAtTile, &tmap_v, kx, ky + t * kAtKeys, &s_kv_full[stage]);
-        tma_load_2d(ks + kAtTile + kAtBlk, &tmap_v, kx + 64, ky + t * kAtKeys, &s_kv_full[stage]);
-        armed |= 1u << stage;
-        armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+        const uint32_t phase = (uint32_t)(t & 1);
+        if (!(ok = mbar_wait(&s_k_empty, phase ^ 1u, abort_flag, p.status, 1))) break;
+        mbar_expect_tx(&s_k_full, kAtTile);
+        tma_load_2d(k_smem, &tmap_k, kx, ky + t * kAtKeys, &s_k_full);
+        tma_load_2d(k_smem + kAtBlk, &tmap_k, kx + 64, ky + t * kAtKeys, &s_k_full);
+        k_armed = t;
+        if (!(ok = mbar_wait(&s_v_empty, phase ^ 1u, abort_flag, p.status, 1))) break;
+        mbar_expect_tx(&s_v_full, kAtTile);
+        tma_load_2d(v_smem, &tmap_v, kx, ky + t * kAtKeys, &s_v_full);
+        tma_load_2d(v_smem + kAtBlk, &tmap_v, kx + 64, ky + t * kAtKeys, &s_v_full);
+        v_armed = t;
       }
       if (!ok) {   // gave up: let the copies already issued land before shared memory is released
-        for (int s = 0; s < kAtStages; ++s)
-          if (armed & (1u << s)) {
-            const unsigned long long w0 = global_ns();
-            while (!mbar_try_wait(&s_kv_full[s], (armed_parity >> s) & 1u) && global_ns() - w0 < kWaitLimitNs) {}
-          }
+        const unsigned long long w0 = global_ns();
+        if (k_armed >= 0)
+          while (!mbar_try_wait(&s_k_full, (uint32_t)(k_armed & 1)) && global_ns() - w0 < kWaitLimitNs) {}
+        if (v_armed >= 0)
+          while (!mbar_try_wait(&s_v_full, (uint32_t)(v_armed & 1)) && global_ns() - w0 < kWaitLimitNs) {}
       }
       {            // the query tile is always in flight once
         const unsigned long long w0 = global_ns();
@@ -175,41 +180,32 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                                ((uint32_t)(kAtRows >> 4) << 24);
       const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(kAtD >> 3) << 17) |
                                 ((uint32_t)(kAtRows >> 4) << 24);
-      const uint32_t qa = smem_u32(q_smem);
-      auto issue_s = [&](int t) {   // S(t) into buffer t & 1
-        const uint32_t ks = smem_u32(kv_smem + (size_t)(t % kAtStages) * 2 * kAtTile);
-        const uint32_t d_tmem = tmem_base + kColS + (uint32_t)(t & 1) * kAtKeys;
+      const uint32_t qa = smem_u32(q_smem), ka = smem_u32(k_smem), va = smem_u32(v_smem);
+      bool ok = mbar_wait(&s_q_full, 0, abort_flag, p.status, 2);
+      for (int t = 0; t < n_kt && ok; ++t) {
+        const uint32_t phase = (uint32_t)(t & 1);
+        if (!(ok = mbar_wait(&s_k_full, phase, abort_flag, p.status, 3))) break;
+        tc_fence_after();
+        // S(t) overwrites P(t-1): issued after PV(t-1), and MMAs of one thread run in order
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb) {
-          const uint64_t a_desc = make_smem_desc(qa + kb * kAtBlk), b_desc = make_smem_desc(ks + kb * kAtBlk);
+          const uint64_t a_desc = make_smem_desc(qa + kb * kAtBlk), b_desc = make_smem_desc(ka + kb * kAtBlk);
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            tc_mma_bf16(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc_s, (kb > 0 || k > 0) ? 1u : 0u);
+            tc_mma_bf16(tmem_base + kColS, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc_s,
+                        (kb > 0 || k > 0) ? 1u : 0u);
         }
-        tc_commit(&s_s_full[t & 1]);
-      };
-      bool ok = mbar_wait(&s_q_full, 0, abort_flag, p.status, 2);
-      if (ok) ok = mbar_wait(&s_kv_full[0], 0, abort_flag, p.status, 3);
-      if (ok) {
+        tc_commit(&s_s_full);
+        tc_commit(&s_k_empty);     // K of the next tile may land while this tile's softmax runs
+        if (!(ok = mbar_wait(&s_v_full, phase, abort_flag, p.status, 3))) break;
+        if (!(ok = mbar_wait(&s_p_full, phase, abort_flag, p.status, 4))) break;
         tc_fence_after();
-        issue_s(0);
-      }
-      for (int t = 0; t < n_kt && ok; ++t) {
-        if (t + 1 < n_kt) {   // S of the next tile runs under this tile's softmax
-          const int st = (t + 1) % kAtStages;
-          if (!(ok = mbar_wait(&s_kv_full[st], (uint32_t)(((t + 1) / kAtStages) & 1), abort_flag, p.status, 3))) break;
-          tc_fence_after();
-          issue_s(t + 1);
-        }
-        if (!(ok = mbar_wait(&s_p_full, (uint32_t)(t & 1), abort_flag, p.status, 4))) break;
-        tc_fence_after();
-        const uint32_t vs = smem_u32(kv_smem + (size_t)(t % kAtStages) * 2 * kAtTile + kAtTile);
 #pragma unroll
         for (int j = 0; j < kAtKeys / 16; ++j)   // 16 keys per step: 8 TMEM columns of P, two 8-key groups of V
-          tc_mma_bf16_ts(tmem_base + kColO, tmem_base + kColP + (uint32_t)(8 * j),
-                         make_smem_desc_mn(vs + j * 2048, kAtBlk), idesc_pv, j > 0 ? 1u : 0u);
+          tc_mma_bf16_ts(tmem_base + kColO, tmem_base + kColS + (uint32_t)(8 * j),
+                         make_smem_desc_mn(va + j * 2048, kAtBlk), idesc_pv, (t > 0 || j > 0) ? 1u : 0u);
         tc_commit(&s_o_full);
-        tc_commit(&s_kv_empty[t % kAtStages]);
+        tc_commit(&s_v_empty);
       }
       tc_commit(&s_drain);   // everything issued so far must retire before TMEM is freed
       const unsigned long long w0 = global_ns();
@@ -220,17 +216,14 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const int row = r0 + warp * 32 + lane;               // row of the document; TMEM lane = warp*32 + lane
     const int limit = min(row, len - 1);                 // last visible key
     const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
-    float o[kAtD];
-#pragma unroll
-    for (int i = 0; i < kAtD; ++i) o[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    float m_ref = -INFINITY, l_run = 0.f;                // m_ref: the maximum the exponentials refer to
     bool ok = true;
     for (int t = 0; t < n_kt; ++t) {
-      ok = mbar_wait(&s_s_full[t & 1], (uint32_t)((t >> 1) & 1), abort_flag, p.status, 5);
+      ok = mbar_wait(&s_s_full, (uint32_t)(t & 1), abort_flag, p.status, 5);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t s_addr = lane_base + kColS + (uint32_t)(t & 1) * kAtKeys;
+      const uint32_t s_addr = lane_base + kColS;
       const int key0 = t * kAtKeys;
       const bool diag = t == n_kt - 1;
       // pass 1: row maximum
@@ -240,17 +233,38 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         uint32_t v[32];
         tmem_ld32(s_addr + 32 * c, v);
         tmem_ld_wait();
+        if (diag) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float x = __uint_as_float(v[i]);
-          mx = fmaxf(mx, (!diag || key0 + 32 * c + i <= limit) ? x : -INFINITY);
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, key0 + 32 * c + i <= limit ? __uint_as_float(v[i]) : -INFINITY);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
         }
       }
-      const float m_new = fmaxf(m_run, mx);              // finite: key 0 is visible to every row
-      const float f = exp2f((m_run - m_new) * p.scale_log2e);
-      const float neg_m = -m_new * p.scale_log2e;
-      m_run = m_new;
-      // pass 2: exponentials, row sum, P as packed bf16 into TMEM
+      // advance the reference only when the maximum ran ahead by more than the step (always on the first tile)
+      const bool move = (mx - m_ref) * p.scale_log2e > kRescaleStep;
+      if (__any_sync(0xffffffffu, move)) {
+        if (t > 0) {   // O of the previous tiles is complete: this warp's rows are rescaled in place
+          ok = mbar_wait(&s_o_full, (uint32_t)((t - 1) & 1), abort_flag, p.status, 6);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+          const float f = move ? exp2f((m_ref - mx) * p.scale_log2e) : 1.f;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            uint32_t v[16];
+            tmem_ld16(lane_base + kColO + 16 * c, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+            tmem_st16(lane_base + kColO + 16 * c, v);
+          }
+          l_run *= f;
+        }
+        if (move) m_ref = mx;
+      }
+      const float neg_m = -m_ref * p.scale_log2e;
+      // pass 2: exponentials, row sum, P as packed bf16 over the consumed S columns
       float sum = 0.f;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -268,40 +282,40 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           sum += e0 + e1;
           pk[i >> 1] = pack2_bf16(e0, e1);
         }
-        tmem_st16(lane_base + kColP + 16 * c, pk);
+        tmem_st16(s_addr + 16 * c, pk);
       }
-      l_run = l_run * f + sum;
+      l_run += sum;
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_p_full);
-      // O_t from the tensor pipe, folded into the running output
-      ok = mbar_wait(&s_o_full, (uint32_t)(t & 1), abort_flag, p.status, 6);
+    }
+    if (ok) {
+      ok = mbar_wait(&s_o_full, (uint32_t)((n_kt - 1) & 1), abort_flag, p.status, 6);
       ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+    }
+    if (ok) {
       tc_fence_after();
+      const float inv = 1.f / l_run;
+      __nv_bfloat16* dst = p.out + ((long long)tok0 + row) * p.n_q_heads * kAtD + (long long)hq * kAtD;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
         tmem_ld32(lane_base + kColO + 32 * c, v);
         tmem_ld_wait();
+        if (row < len) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[32 * c + i] = fmaf(o[32 * c + i], f, __uint_as_float(v[i]));
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            w.x = pack2_bf16(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+            w.y = pack2_bf16(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+            w.z = pack2_bf16(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
+            w.w = pack2_bf16(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + 32 * c + i) = w;
+          }
+        }
       }
       tc_fence_before();
-    }
-    if (ok && row < len) {
-      const float inv = 1.f / l_run;
-      __nv_bfloat16* dst = p.out + ((long long)tok0 + row) * p.n_q_heads * kAtD + (long long)hq * kAtD;
-#pragma unroll
-      for (int i = 0; i < kAtD; i += 8) {
-        uint4 w;
-        w.x = pack2_bf16(o[i] * inv, o[i + 1] * inv);
-        w.y = pack2_bf16(o[i + 2] * inv, o[i + 3] * inv);
-        w.z = pack2_bf16(o[i + 4] * inv, o[i + 5] * inv);
-        w.w = pack2_bf16(o[i + 6] * inv, o[i + 7] * inv);
-        *reinterpret_cast<uint4*>(dst + i) = w;
-      }
     }
   }
 
@@ -310,7 +324,7 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   __syncthreads();
   tc_fence_after();
   if (warp == 5)
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kAtTmemCols) : "memory");
 }
 
 }  // namespace msa
