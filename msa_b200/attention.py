@@ -8,9 +8,11 @@ loads), same cache protocol (``cache_kwargs`` / ``meta`` / ``record_kwargs`` / `
 
 What runs where:
   * stage 1: projections, norms and RoPE stay PyTorch as in the reference; chunk bookkeeping, the
-    intra-document causal attention with the chunk means of K and V taken in the same pass (bf16,
-    head_dim 128; other shapes: library attention + the pooling kernel), the pooling of K_r and its
-    L2 normalisation run on this package's kernels;
+    intra-document causal attention and all pooling run on this package's kernels.  In bf16 with
+    head_dim 128: documents without masked tokens go to the tcgen05 attention kernel (K, V, K_r pooled
+    by the pooling kernel), blocks with masked tokens inside documents to the mma.sync kernel that
+    takes the K / V chunk means in the same pass; other dtypes / head sizes: library attention + the
+    pooling kernel;
   * stage 2: routing, merge and fetch happen inside ``memory_client.doc_query`` (this package's
     ``MSAService``); one kernel assembles [template | retrieved | query] into the left-padded
     compact cache (allocated with room to append in place) and, for bf16 / head_dim 128, this
@@ -132,7 +134,11 @@ class MemorySparseAttention(Qwen3Attention):
 
     def _segments(self, doc_ids, attention_mask, cache):
         """Token lists and segment offsets of the document tokens and of the template tokens of this block
-        (one segment per (row, document) run / per row); computed once and shared by every layer."""
+        (one segment per (row, document) run / per row), the longest segment and whether every segment is a
+        run of consecutive tokens; computed once and shared by every layer."""
+        prev = cache.meta.get("_msa_b200_attn_status")
+        if prev is not None and int(prev[0].item()) != 0:
+            raise A.MsaError("a bounded barrier wait ran out inside doc_attn_tc_kernel (stage-1 attention output invalid)")
         key = (doc_ids.data_ptr(), attention_mask.data_ptr(), tuple(doc_ids.shape))
         hit = cache.meta.get("_msa_b200_segments")
         if hit is None or hit[0] != key:
@@ -142,10 +148,13 @@ class MemorySparseAttention(Qwen3Attention):
             def table(mask, ids):
                 tok = torch.nonzero(mask.flatten()).flatten()
                 if tok.numel() == 0:
-                    return tok.to(torch.int32), torch.zeros(1, dtype=torch.int32, device=tok.device), 0
+                    return tok.to(torch.int32), torch.zeros(1, dtype=torch.int32, device=tok.device), 0, True
                 gid = (tok // s) * (int(ids.max().item()) + 2) + ids.flatten()[tok]
                 _, counts = torch.unique_consecutive(gid, return_counts=True)
-                return (tok.to(torch.int32), F.pad(counts.cumsum(0), (1, 0)).to(torch.int32), int(counts.max().item()))
+                off = F.pad(counts.cumsum(0), (1, 0))
+                first, last = tok[off[:-1]], tok[off[1:] - 1]
+                runs = bool(((last - first == counts - 1) & (first // s == last // s)).all().item())
+                return tok.to(torch.int32), off.to(torch.int32), int(counts.max().item()), runs
             hit = (key, table((doc_ids > 0) & valid, doc_ids), table((doc_ids == -2) & valid, torch.zeros_like(doc_ids)))
             cache.meta["_msa_b200_segments"] = hit
         return hit[1], hit[2]
@@ -164,8 +173,13 @@ class MemorySparseAttention(Qwen3Attention):
         attn_output = torch.zeros((bsz, q_len, n_heads * self.head_dim), device=device, dtype=dtype)
         pooled_k = pooled_v = pooled_rk = pooled_doc_ids = None
         if own_attention:
-            (tok_d, off_d, max_d), (tok_t, off_t, max_t) = self._segments(doc_ids, attention_mask, cache)
-            if self.is_router_layer and self.pooling_kernel_size % 32 == 0:
+            (tok_d, off_d, max_d, runs_d), (tok_t, off_t, max_t, _) = self._segments(doc_ids, attention_mask, cache)
+            if runs_d and max_d >= 128 and ops.doc_attention_tc_supported(query_states, key_states, value_states):
+                # unmasked documents: attention on the tcgen05 kernel (K and V are pooled by the pooling kernel below)
+                status = cache.meta.setdefault("_msa_b200_attn_status", torch.zeros(4, dtype=torch.int32, device=device))
+                ops.doc_attention_tc(query_states, key_states, value_states, tok_d, off_d, max_d, out=attn_output,
+                                     scale=self.scaling, status=status)
+            elif self.is_router_layer and self.pooling_kernel_size % 32 == 0:
                 # K and V are pooled from the tiles the attention kernel stages anyway
                 tok, off, pooled_doc_ids = self._bookkeeping(doc_ids, attention_mask, cache)
                 _, pooled_k, pooled_v = ops.doc_attention_pool(

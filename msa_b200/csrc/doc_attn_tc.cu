@@ -226,19 +226,22 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       const uint32_t s_addr = lane_base + kColS;
       const int key0 = t * kAtKeys;
       const bool diag = t == n_kt - 1;
-      // pass 1: row maximum
+      // pass 1: row maximum.  The load of the next 32 columns is in flight while these are reduced.
       float mx = -INFINITY;
+      uint32_t va[32], vb[32];
+      tmem_ld32(s_addr, va);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(s_addr + 32 * c, v);
+        uint32_t(&cur)[32] = (c & 1) ? vb : va;
+        uint32_t(&nxt)[32] = (c & 1) ? va : vb;
         tmem_ld_wait();
+        if (c < 3) tmem_ld32(s_addr + 32 * (c + 1), nxt);
         if (diag) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, key0 + 32 * c + i <= limit ? __uint_as_float(v[i]) : -INFINITY);
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, key0 + 32 * c + i <= limit ? __uint_as_float(cur[i]) : -INFINITY);
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(cur[i]));
         }
       }
       // advance the reference only when the maximum ran ahead by more than the step (always on the first tile)
@@ -264,17 +267,21 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         if (move) m_ref = mx;
       }
       const float neg_m = -m_ref * p.scale_log2e;
-      // pass 2: exponentials, row sum, P as packed bf16 over the consumed S columns
+      // pass 2: exponentials, row sum, P as packed bf16 over the consumed S columns (chunk c of P lands on
+      // columns 16c..16c+15, all below the 32(c+1) columns already read, also by the load in flight)
       float sum = 0.f;
+      tmem_ld32(s_addr, va);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t v[32], pk[16];
-        tmem_ld32(s_addr + 32 * c, v);
+        uint32_t(&cur)[32] = (c & 1) ? vb : va;
+        uint32_t(&nxt)[32] = (c & 1) ? va : vb;
+        uint32_t pk[16];
         tmem_ld_wait();
+        if (c < 3) tmem_ld32(s_addr + 32 * (c + 1), nxt);   // in flight under the exponentials of this chunk
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float e0 = exp2f(fmaf(__uint_as_float(v[i]), p.scale_log2e, neg_m));
-          float e1 = exp2f(fmaf(__uint_as_float(v[i + 1]), p.scale_log2e, neg_m));
+          float e0 = exp2f(fmaf(__uint_as_float(cur[i]), p.scale_log2e, neg_m));
+          float e1 = exp2f(fmaf(__uint_as_float(cur[i + 1]), p.scale_log2e, neg_m));
           if (diag) {
             if (key0 + 32 * c + i > limit) e0 = 0.f;
             if (key0 + 32 * c + i + 1 > limit) e1 = 0.f;

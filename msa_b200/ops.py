@@ -382,6 +382,23 @@ def doc_attention_pool(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, token_
     return out, pooled_k, pooled_v
 
 
+def _tc_view_ok(t: torch.Tensor) -> bool:
+    """Token-major ([B, S, H, D] storage viewed as [B, H, S, D]) or contiguous head-major, rows 16-byte aligned."""
+    b, h, s, d = t.shape
+    sb, sh, ss, sd = t.stride()
+    if sd != 1 or ss % 8 != 0 or t.data_ptr() % 16 != 0:
+        return False
+    token_major = sh == d and ss >= h * d and (b == 1 or sb == s * ss)
+    head_major = ss >= d and sh == s * ss and (b == 1 or sb == h * sh)
+    return token_major or head_major
+
+
+def doc_attention_tc_supported(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
+    """Whether ``doc_attention_tc`` takes these tensors as they are (dtype, head size, layouts)."""
+    return (q.dtype == torch.bfloat16 and q.shape[-1] == 128 and k.stride() == v.stride() and _tc_view_ok(q)
+            and _tc_view_ok(k) and v.data_ptr() % 16 == 0 and q.shape[0] * q.shape[1] * q.shape[2] < 2 ** 31)
+
+
 def doc_attention_tc(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, token_index: torch.Tensor,
                      seg_offsets: torch.Tensor, max_segment_len: int, out: Optional[torch.Tensor] = None,
                      scale: Optional[float] = None, status: Optional[torch.Tensor] = None):
