@@ -1,9 +1,11 @@
 // Stage-1 attention inside every document on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), bf16,
 // head_dim 128, for documents that are runs of consecutive tokens of one row.
 //
-// CTA = 128 query tokens of one head of one document; 192 threads: warps 0-3 softmax (thread = query row =
-// TMEM lane), warp 4 TMA producer, warp 5 MMA issuer + TMEM owner.  Two CTAs share an SM (97 KB of shared
-// memory and 256 TMEM columns each), so one CTA's MMAs run under the other's softmax.  Per 128-key tile:
+// Work item = 128 query tokens of one head of one document.  Persistent CTAs (two per SM: 97 KB of shared
+// memory and 256 TMEM columns each, so one CTA's MMAs run under the other's softmax) walk the items with a
+// fixed stride; 192 threads: warps 0-3 softmax (thread = query row = TMEM lane), warp 4 TMA producer, warp 5
+// MMA issuer + TMEM owner.  The next item's queries and first keys are loaded under the current item's last
+// softmax, PV and output.  Per 128-key tile:
 //     S = Q K^T        tcgen05.mma, A = Q and B = K both K-major in shared memory, fp32 into TMEM columns 0..127;
 //     softmax          each thread reads its row of S with tcgen05.ld (two passes: maximum, then exponentials)
 //                      and writes P as packed bf16 over the S columns it has consumed (tcgen05.st);
@@ -44,6 +46,9 @@ struct DocAttnTcParams {
   int k_yb, k_yh, k_xh;
   uint32_t div_mul, div_shift;  // tok / S
   float scale_log2e;
+  int max_mb;                   // row blocks of the longest segment
+  long long n_sh;               // n_segments * n_q_heads
+  long long n_items;            // n_sh * max_mb
   __nv_bfloat16* out;
   int32_t* status;
 };
@@ -93,31 +98,46 @@ __device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// One work item = (document, head, row block).  Items are numbered w = x * (n_segments * n_q_heads) + seg *
+// n_q_heads + hq with x counting a document's row blocks from its last (longest) one: the fixed-stride walk
+// of the persistent CTAs then hands every CTA the same mix of long and short items, and the heads of a kv
+// group run side by side and share K / V through L2.  Item w of a document with fewer row blocks is skipped.
+struct AtItem { int len, r0, n_kt, hq, hk, tok0, b, s0; bool valid; };
+__device__ __forceinline__ AtItem at_item(const DocAttnTcParams& p, long long w) {
+  AtItem it;
+  const int x = (int)(w / p.n_sh);
+  const long long sh = w % p.n_sh;
+  it.hq = (int)(sh % p.n_q_heads);
+  const int seg = (int)(sh / p.n_q_heads);
+  const int t0 = p.seg_off[seg];
+  it.len = p.seg_off[seg + 1] - t0;
+  const int n_mb = (it.len + kAtRows - 1) / kAtRows;
+  it.valid = x < n_mb;
+  const int mb = n_mb - 1 - x;
+  it.r0 = mb * kAtRows;
+  it.n_kt = mb + 1;
+  it.hk = it.hq / (p.n_q_heads / p.n_kv_heads);
+  it.tok0 = it.valid ? p.token_index[t0] : 0;
+  it.b = (int)((__umulhi((uint32_t)it.tok0, p.div_mul) + (uint32_t)it.tok0) >> p.div_shift);
+  it.s0 = it.tok0 - it.b * p.S;
+  return it;
+}
+
 __global__ void __launch_bounds__(kAtThreads, 2)
 doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                    const __grid_constant__ CUtensorMap tmap_v, const DocAttnTcParams p) {
   extern __shared__ unsigned char smem_dyn[];
-  __shared__ uint64_t s_q_full, s_k_full, s_k_empty, s_v_full, s_v_empty, s_s_full, s_p_full, s_o_full, s_drain;
+  __shared__ uint64_t s_q_full, s_q_empty, s_k_full, s_k_empty, s_v_full, s_v_empty, s_s_full, s_p_full, s_o_full, s_drain;
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
 
-  const int seg = blockIdx.z, hq = blockIdx.y;
-  const int t0 = p.seg_off[seg], len = p.seg_off[seg + 1] - t0;
-  const int n_mb = (len + kAtRows - 1) / kAtRows;
-  if ((int)blockIdx.x >= n_mb) return;                 // whole CTA, before anything is allocated
-  const int mb = n_mb - 1 - (int)blockIdx.x;           // long row blocks first
-  const int r0 = mb * kAtRows, n_kt = mb + 1;
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int tok0 = p.token_index[t0];
-  const int b = (int)((__umulhi((uint32_t)tok0, p.div_mul) + (uint32_t)tok0) >> p.div_shift);
-  const int s0 = tok0 - b * p.S;
-  const int hk = hq / (p.n_q_heads / p.n_kv_heads);
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
   unsigned char *q_smem = tiles, *k_smem = tiles + kAtTile, *v_smem = tiles + 2 * kAtTile;
   volatile int* abort_flag = &s_abort;
 
   if (threadIdx.x == 0) {
-    mbar_init(&s_q_full, 1);
+    mbar_init(&s_q_full, 1); mbar_init(&s_q_empty, 1);
     mbar_init(&s_k_full, 1); mbar_init(&s_k_empty, 1);
     mbar_init(&s_v_full, 1); mbar_init(&s_v_empty, 1);
     mbar_init(&s_s_full, 1);
@@ -137,39 +157,38 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = s_tmem_base;
 
+  // Every role walks the same items in the same order; `n_it` counts the valid items and `n_t` the key tiles this
+  // CTA has gone through, and every barrier's phase follows from those two counters.
   if (warp == 4) {
     // ------------------------------- TMA producer -------------------------------------
     if (lane == 0) {
-      const int qy = b * p.q_yb + hq * p.q_yh + s0 + r0, qx = hq * p.q_xh;
-      const int ky = b * p.k_yb + hk * p.k_yh + s0, kx = hk * p.k_xh;
-      mbar_expect_tx(&s_q_full, kAtTile);
-      tma_load_2d(q_smem, &tmap_q, qx, qy, &s_q_full);
-      tma_load_2d(q_smem + kAtBlk, &tmap_q, qx + 64, qy, &s_q_full);
+      uint32_t n_it = 0, n_t = 0;
       bool ok = true;
-      int k_armed = -1, v_armed = -1;    // last tile whose copy was issued
-      for (int t = 0; t < n_kt && ok; ++t) {
-        const uint32_t phase = (uint32_t)(t & 1);
-        if (!(ok = mbar_wait(&s_k_empty, phase ^ 1u, abort_flag, p.status, 1))) break;
-        mbar_expect_tx(&s_k_full, kAtTile);
-        tma_load_2d(k_smem, &tmap_k, kx, ky + t * kAtKeys, &s_k_full);
-        tma_load_2d(k_smem + kAtBlk, &tmap_k, kx + 64, ky + t * kAtKeys, &s_k_full);
-        k_armed = t;
-        if (!(ok = mbar_wait(&s_v_empty, phase ^ 1u, abort_flag, p.status, 1))) break;
-        mbar_expect_tx(&s_v_full, kAtTile);
-        tma_load_2d(v_smem, &tmap_v, kx, ky + t * kAtKeys, &s_v_full);
-        tma_load_2d(v_smem + kAtBlk, &tmap_v, kx + 64, ky + t * kAtKeys, &s_v_full);
-        v_armed = t;
+      for (long long w = blockIdx.x; w < p.n_items && ok; w += gridDim.x) {
+        const AtItem it = at_item(p, w);
+        if (!it.valid) continue;
+        const int qy = it.b * p.q_yb + it.hq * p.q_yh + it.s0 + it.r0, qx = it.hq * p.q_xh;
+        const int ky = it.b * p.k_yb + it.hk * p.k_yh + it.s0, kx = it.hk * p.k_xh;
+        // the query buffer is free once the last S of the previous item has been issued and has completed
+        if (!(ok = mbar_wait(&s_q_empty, (n_it & 1u) ^ 1u, abort_flag, p.status, 1))) break;
+        mbar_expect_tx(&s_q_full, kAtTile);
+        tma_load_2d(q_smem, &tmap_q, qx, qy, &s_q_full);
+        tma_load_2d(q_smem + kAtBlk, &tmap_q, qx + 64, qy, &s_q_full);
+        for (int t = 0; t < it.n_kt; ++t, ++n_t) {
+          if (!(ok = mbar_wait(&s_k_empty, (n_t & 1u) ^ 1u, abort_flag, p.status, 1))) break;
+          mbar_expect_tx(&s_k_full, kAtTile);
+          tma_load_2d(k_smem, &tmap_k, kx, ky + t * kAtKeys, &s_k_full);
+          tma_load_2d(k_smem + kAtBlk, &tmap_k, kx + 64, ky + t * kAtKeys, &s_k_full);
+          if (!(ok = mbar_wait(&s_v_empty, (n_t & 1u) ^ 1u, abort_flag, p.status, 1))) break;
+          mbar_expect_tx(&s_v_full, kAtTile);
+          tma_load_2d(v_smem, &tmap_v, kx, ky + t * kAtKeys, &s_v_full);
+          tma_load_2d(v_smem + kAtBlk, &tmap_v, kx + 64, ky + t * kAtKeys, &s_v_full);
+        }
+        ++n_it;
       }
-      if (!ok) {   // gave up: let the copies already issued land before shared memory is released
+      if (!ok) {   // gave up: give the copies already issued time to land before shared memory is released
         const unsigned long long w0 = global_ns();
-        if (k_armed >= 0)
-          while (!mbar_try_wait(&s_k_full, (uint32_t)(k_armed & 1)) && global_ns() - w0 < kWaitLimitNs) {}
-        if (v_armed >= 0)
-          while (!mbar_try_wait(&s_v_full, (uint32_t)(v_armed & 1)) && global_ns() - w0 < kWaitLimitNs) {}
-      }
-      {            // the query tile is always in flight once
-        const unsigned long long w0 = global_ns();
-        while (!mbar_try_wait(&s_q_full, 0) && global_ns() - w0 < kWaitLimitNs) {}
+        while (global_ns() - w0 < 1000000ull) {}   // 1 ms, far above any copy's latency
       }
     }
   } else if (warp == 5) {
@@ -181,31 +200,39 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(kAtD >> 3) << 17) |
                                 ((uint32_t)(kAtRows >> 4) << 24);
       const uint32_t qa = smem_u32(q_smem), ka = smem_u32(k_smem), va = smem_u32(v_smem);
-      bool ok = mbar_wait(&s_q_full, 0, abort_flag, p.status, 2);
-      for (int t = 0; t < n_kt && ok; ++t) {
-        const uint32_t phase = (uint32_t)(t & 1);
-        if (!(ok = mbar_wait(&s_k_full, phase, abort_flag, p.status, 3))) break;
-        tc_fence_after();
-        // S(t) overwrites P(t-1): issued after PV(t-1), and MMAs of one thread run in order
+      uint32_t n_it = 0, n_t = 0;
+      bool ok = true;
+      for (long long w = blockIdx.x; w < p.n_items && ok; w += gridDim.x) {
+        const AtItem it = at_item(p, w);
+        if (!it.valid) continue;
+        if (!(ok = mbar_wait(&s_q_full, n_it & 1u, abort_flag, p.status, 2))) break;
+        for (int t = 0; t < it.n_kt; ++t, ++n_t) {
+          const uint32_t phase = n_t & 1u;
+          if (!(ok = mbar_wait(&s_k_full, phase, abort_flag, p.status, 3))) break;
+          tc_fence_after();
+          // S overwrites the previous tile's P: issued after that tile's PV, and MMAs of one thread run in order
 #pragma unroll
-        for (int kb = 0; kb < 2; ++kb) {
-          const uint64_t a_desc = make_smem_desc(qa + kb * kAtBlk), b_desc = make_smem_desc(ka + kb * kAtBlk);
+          for (int kb = 0; kb < 2; ++kb) {
+            const uint64_t a_desc = make_smem_desc(qa + kb * kAtBlk), b_desc = make_smem_desc(ka + kb * kAtBlk);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            tc_mma_bf16(tmem_base + kColS, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc_s,
-                        (kb > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < 4; ++k)
+              tc_mma_bf16(tmem_base + kColS, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc_s,
+                          (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(&s_s_full);
+          tc_commit(&s_k_empty);                        // the next K may land while this tile's softmax runs
+          if (t == it.n_kt - 1) tc_commit(&s_q_empty);  // and the next item's queries under this item's tail
+          if (!(ok = mbar_wait(&s_v_full, phase, abort_flag, p.status, 3))) break;
+          if (!(ok = mbar_wait(&s_p_full, phase, abort_flag, p.status, 4))) break;
+          tc_fence_after();
+#pragma unroll
+          for (int j = 0; j < kAtKeys / 16; ++j)   // 16 keys per step: 8 TMEM columns of P, two 8-key groups of V
+            tc_mma_bf16_ts(tmem_base + kColO, tmem_base + kColS + (uint32_t)(8 * j),
+                           make_smem_desc_mn(va + j * 2048, kAtBlk), idesc_pv, (t > 0 || j > 0) ? 1u : 0u);
+          tc_commit(&s_o_full);
+          tc_commit(&s_v_empty);
         }
-        tc_commit(&s_s_full);
-        tc_commit(&s_k_empty);     // K of the next tile may land while this tile's softmax runs
-        if (!(ok = mbar_wait(&s_v_full, phase, abort_flag, p.status, 3))) break;
-        if (!(ok = mbar_wait(&s_p_full, phase, abort_flag, p.status, 4))) break;
-        tc_fence_after();
-#pragma unroll
-        for (int j = 0; j < kAtKeys / 16; ++j)   // 16 keys per step: 8 TMEM columns of P, two 8-key groups of V
-          tc_mma_bf16_ts(tmem_base + kColO, tmem_base + kColS + (uint32_t)(8 * j),
-                         make_smem_desc_mn(va + j * 2048, kAtBlk), idesc_pv, (t > 0 || j > 0) ? 1u : 0u);
-        tc_commit(&s_o_full);
-        tc_commit(&s_v_empty);
+        ++n_it;
       }
       tc_commit(&s_drain);   // everything issued so far must retire before TMEM is freed
       const unsigned long long w0 = global_ns();
@@ -213,116 +240,120 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     }
   } else {
     // ------------------------------- softmax / output (warps 0-3) ----------------------
-    const int row = r0 + warp * 32 + lane;               // row of the document; TMEM lane = warp*32 + lane
-    const int limit = min(row, len - 1);                 // last visible key
     const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
-    float m_ref = -INFINITY, l_run = 0.f;                // m_ref: the maximum the exponentials refer to
+    const uint32_t s_addr = lane_base + kColS;
+    uint32_t n_t = 0;
     bool ok = true;
-    for (int t = 0; t < n_kt; ++t) {
-      ok = mbar_wait(&s_s_full, (uint32_t)(t & 1), abort_flag, p.status, 5);
+    for (long long w = blockIdx.x; w < p.n_items && ok; w += gridDim.x) {
+      const AtItem it = at_item(p, w);
+      if (!it.valid) continue;
+      const int row = it.r0 + warp * 32 + lane;            // row of the document; TMEM lane = warp*32 + lane
+      const int limit = min(row, it.len - 1);              // last visible key
+      float m_ref = -INFINITY, l_run = 0.f;                // m_ref: the maximum the exponentials refer to
+      for (int t = 0; t < it.n_kt; ++t, ++n_t) {
+        ok = mbar_wait(&s_s_full, n_t & 1u, abort_flag, p.status, 5);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        const int key0 = t * kAtKeys;
+        const bool diag = t == it.n_kt - 1;
+        // pass 1: row maximum.  The load of the next 32 columns is in flight while these are reduced.
+        float mx = -INFINITY;
+        uint32_t va[32], vb[32];
+        tmem_ld32(s_addr, va);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t(&cur)[32] = (c & 1) ? vb : va;
+          uint32_t(&nxt)[32] = (c & 1) ? va : vb;
+          tmem_ld_wait();
+          if (c < 3) tmem_ld32(s_addr + 32 * (c + 1), nxt);
+          if (diag) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, key0 + 32 * c + i <= limit ? __uint_as_float(cur[i]) : -INFINITY);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(cur[i]));
+          }
+        }
+        // advance the reference only when the maximum ran ahead by more than the step (always on the first tile)
+        const bool move = (mx - m_ref) * p.scale_log2e > kRescaleStep;
+        if (__any_sync(0xffffffffu, move)) {
+          if (t > 0) {   // O of the previous tiles is complete: this warp's rows are rescaled in place
+            ok = mbar_wait(&s_o_full, (n_t - 1u) & 1u, abort_flag, p.status, 6);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const float f = move ? exp2f((m_ref - mx) * p.scale_log2e) : 1.f;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              uint32_t v[16];
+              tmem_ld16(lane_base + kColO + 16 * c, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+              tmem_st16(lane_base + kColO + 16 * c, v);
+            }
+            l_run *= f;
+          }
+          if (move) m_ref = mx;
+        }
+        const float neg_m = -m_ref * p.scale_log2e;
+        // pass 2: exponentials, row sum, P as packed bf16 over the consumed S columns (chunk c of P lands on
+        // columns 16c..16c+15, all below the 32(c+1) columns already read, also by the load in flight)
+        float sum = 0.f;
+        tmem_ld32(s_addr, va);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t(&cur)[32] = (c & 1) ? vb : va;
+          uint32_t(&nxt)[32] = (c & 1) ? va : vb;
+          uint32_t pk[16];
+          tmem_ld_wait();
+          if (c < 3) tmem_ld32(s_addr + 32 * (c + 1), nxt);   // in flight under the exponentials of this chunk
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float e0 = exp2f(fmaf(__uint_as_float(cur[i]), p.scale_log2e, neg_m));
+            float e1 = exp2f(fmaf(__uint_as_float(cur[i + 1]), p.scale_log2e, neg_m));
+            if (diag) {
+              if (key0 + 32 * c + i > limit) e0 = 0.f;
+              if (key0 + 32 * c + i + 1 > limit) e1 = 0.f;
+            }
+            sum += e0 + e1;
+            pk[i >> 1] = pack2_bf16(e0, e1);
+          }
+          tmem_st16(s_addr + 16 * c, pk);
+        }
+        l_run += sum;
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_p_full);
+      }
+      if (!ok) break;
+      // the item's output: O is complete after the last PV
+      ok = mbar_wait(&s_o_full, (n_t - 1u) & 1u, abort_flag, p.status, 6);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t s_addr = lane_base + kColS;
-      const int key0 = t * kAtKeys;
-      const bool diag = t == n_kt - 1;
-      // pass 1: row maximum.  The load of the next 32 columns is in flight while these are reduced.
-      float mx = -INFINITY;
-      uint32_t va[32], vb[32];
-      tmem_ld32(s_addr, va);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t(&cur)[32] = (c & 1) ? vb : va;
-        uint32_t(&nxt)[32] = (c & 1) ? va : vb;
-        tmem_ld_wait();
-        if (c < 3) tmem_ld32(s_addr + 32 * (c + 1), nxt);
-        if (diag) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, key0 + 32 * c + i <= limit ? __uint_as_float(cur[i]) : -INFINITY);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(cur[i]));
-        }
-      }
-      // advance the reference only when the maximum ran ahead by more than the step (always on the first tile)
-      const bool move = (mx - m_ref) * p.scale_log2e > kRescaleStep;
-      if (__any_sync(0xffffffffu, move)) {
-        if (t > 0) {   // O of the previous tiles is complete: this warp's rows are rescaled in place
-          ok = mbar_wait(&s_o_full, (uint32_t)((t - 1) & 1), abort_flag, p.status, 6);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after();
-          const float f = move ? exp2f((m_ref - mx) * p.scale_log2e) : 1.f;
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            uint32_t v[16];
-            tmem_ld16(lane_base + kColO + 16 * c, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
-            tmem_st16(lane_base + kColO + 16 * c, v);
-          }
-          l_run *= f;
-        }
-        if (move) m_ref = mx;
-      }
-      const float neg_m = -m_ref * p.scale_log2e;
-      // pass 2: exponentials, row sum, P as packed bf16 over the consumed S columns (chunk c of P lands on
-      // columns 16c..16c+15, all below the 32(c+1) columns already read, also by the load in flight)
-      float sum = 0.f;
-      tmem_ld32(s_addr, va);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t(&cur)[32] = (c & 1) ? vb : va;
-        uint32_t(&nxt)[32] = (c & 1) ? va : vb;
-        uint32_t pk[16];
-        tmem_ld_wait();
-        if (c < 3) tmem_ld32(s_addr + 32 * (c + 1), nxt);   // in flight under the exponentials of this chunk
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float e0 = exp2f(fmaf(__uint_as_float(cur[i]), p.scale_log2e, neg_m));
-          float e1 = exp2f(fmaf(__uint_as_float(cur[i + 1]), p.scale_log2e, neg_m));
-          if (diag) {
-            if (key0 + 32 * c + i > limit) e0 = 0.f;
-            if (key0 + 32 * c + i + 1 > limit) e1 = 0.f;
-          }
-          sum += e0 + e1;
-          pk[i >> 1] = pack2_bf16(e0, e1);
-        }
-        tmem_st16(s_addr + 16 * c, pk);
-      }
-      l_run += sum;
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_p_full);
-    }
-    if (ok) {
-      ok = mbar_wait(&s_o_full, (uint32_t)((n_kt - 1) & 1), abort_flag, p.status, 6);
-      ok = __all_sync(0xffffffffu, ok);
-    }
-    if (ok) {
-      tc_fence_after();
       const float inv = 1.f / l_run;
-      __nv_bfloat16* dst = p.out + ((long long)tok0 + row) * p.n_q_heads * kAtD + (long long)hq * kAtD;
+      __nv_bfloat16* dst = p.out + ((long long)it.tok0 + row) * p.n_q_heads * kAtD + (long long)it.hq * kAtD;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
         tmem_ld32(lane_base + kColO + 32 * c, v);
         tmem_ld_wait();
-        if (row < len) {
+        if (row < it.len) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
-            uint4 w;
-            w.x = pack2_bf16(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
-            w.y = pack2_bf16(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
-            w.z = pack2_bf16(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
-            w.w = pack2_bf16(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + 32 * c + i) = w;
+            uint4 o;
+            o.x = pack2_bf16(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+            o.y = pack2_bf16(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+            o.z = pack2_bf16(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
+            o.w = pack2_bf16(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + 32 * c + i) = o;
           }
         }
       }
-      tc_fence_before();
+      tc_fence_before();   // the next item's first PV (gated by this warp's next arrival) overwrites O
     }
   }
 
@@ -362,9 +393,8 @@ extern "C" int msa_doc_attention_tc(const void* q, int64_t q_stride_b, int64_t q
                                     void* out, int32_t* status, void* stream) {
   MSA_REQUIRE(q && k && v && token_index && seg_offsets && out && status, "doc_attention_tc: null pointer");
   MSA_REQUIRE(dtype == MSA_BF16 && head_dim == kAtD, "doc_attention_tc: bf16 with head_dim 128 only");
-  MSA_REQUIRE(n_segments >= 0 && n_segments <= 65535 && max_segment_len >= 0 && n_seq > 0 && seq_len > 0 &&
-                  n_q_heads > 0 && n_kv_heads > 0 && n_q_heads % n_kv_heads == 0 && n_q_heads <= 65535,
-              "doc_attention_tc: bad sizes (at most 65535 segments per call)");
+  MSA_REQUIRE(n_segments >= 0 && max_segment_len >= 0 && n_seq > 0 && seq_len > 0 && n_q_heads > 0 &&
+                  n_kv_heads > 0 && n_q_heads % n_kv_heads == 0, "doc_attention_tc: bad sizes");
   MSA_REQUIRE((long long)n_seq * seq_len * n_q_heads < (1ll << 31), "doc_attention_tc: more than 2^31 token rows");
   MSA_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) && q_stride_s % 8 == 0 &&
                   k_stride_s % 8 == 0, "doc_attention_tc: rows must be 16-byte aligned");
@@ -397,8 +427,17 @@ extern "C" int msa_doc_attention_tc(const void* q, int64_t q_stride_b, int64_t q
     MSA_CUDA_OK(cudaFuncSetAttribute(doc_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAtSmem));
     configured = true;
   }
-  dim3 grid((max_segment_len + kAtRows - 1) / kAtRows, n_q_heads, n_segments);
-  doc_attn_tc_kernel<<<grid, kAtThreads, kAtSmem, (cudaStream_t)stream>>>(map_q, map_k, map_v, p);
+  p.max_mb = (max_segment_len + kAtRows - 1) / kAtRows;
+  p.n_sh = (long long)n_segments * n_q_heads;
+  p.n_items = p.n_sh * p.max_mb;
+  static thread_local int n_sm = 0;
+  if (n_sm == 0) {
+    int dev = 0;
+    MSA_CUDA_OK(cudaGetDevice(&dev));
+    MSA_CUDA_OK(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+  }
+  const long long grid = p.n_items < 2ll * n_sm ? p.n_items : 2ll * n_sm;   // persistent: two CTAs per SM
+  doc_attn_tc_kernel<<<(unsigned)grid, kAtThreads, kAtSmem, (cudaStream_t)stream>>>(map_q, map_k, map_v, p);
   MSA_LAUNCH_OK("doc_attn_tc_kernel");
   return MSA_OK;
 }

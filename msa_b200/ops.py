@@ -417,14 +417,11 @@ def doc_attention_tc(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, token_in
     if status is None:
         status = torch.zeros(4, dtype=torch.int32, device=q.device)
     scale = (1.0 / math.sqrt(d)) if scale is None else scale
-    n_seg = seg_offsets.numel() - 1
-    for lo in range(0, n_seg, 65535):
-        n = min(65535, n_seg - lo)
-        A.check(A.lib().msa_doc_attention_tc(
-            A.ptr(q), q.stride(0), q.stride(1), q.stride(2), A.ptr(k), A.ptr(v), k.stride(0), k.stride(1), k.stride(2),
-            A.ptr(token_index), A.ptr(seg_offsets) + 4 * lo, n, int(max_segment_len), b, s, hq, hkv, d,
-            A.dtype_code(q.dtype), float(scale), A.ptr(out), A.ptr(status), A.stream_ptr(q.device)),
-            "msa_doc_attention_tc")
+    A.check(A.lib().msa_doc_attention_tc(
+        A.ptr(q), q.stride(0), q.stride(1), q.stride(2), A.ptr(k), A.ptr(v), k.stride(0), k.stride(1), k.stride(2),
+        A.ptr(token_index), A.ptr(seg_offsets), seg_offsets.numel() - 1, int(max_segment_len), b, s, hq, hkv, d,
+        A.dtype_code(q.dtype), float(scale), A.ptr(out), A.ptr(status), A.stream_ptr(q.device)),
+        "msa_doc_attention_tc")
     return out, status
 
 
