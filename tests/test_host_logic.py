@@ -94,3 +94,18 @@ def test_exchange_layout_two_gloo_ranks():
             assert s[owner, 0, 0] == 1000 * owner
         assert base == [0, 3] and ln == [0, 1, 1, 0, 2, 2, 2]
     assert torch.equal(ret[0][0], ret[1][0])
+
+
+def test_tensor_layouts_the_tcgen05_attention_accepts():
+    """ops._tc_view_ok: token-major views (what the layer's projections give) and contiguous head-major tensors."""
+    import torch
+    from msa_b200 import ops
+    b, h, s, d = 2, 4, 24, 128
+    token_major = torch.zeros(b, s, h, d, dtype=torch.bfloat16).transpose(1, 2)
+    head_major = torch.zeros(b, h, s, d, dtype=torch.bfloat16)
+    fused = torch.zeros(b, s, 3 * h * d, dtype=torch.bfloat16)[:, :, h * d: 2 * h * d].view(b, s, h, d).transpose(1, 2)
+    assert ops._tc_view_ok(token_major) and ops._tc_view_ok(head_major) and ops._tc_view_ok(fused)
+    assert ops._tc_view_ok(head_major[:, :, ::2])                        # every other token: still one stride per row
+    assert not ops._tc_view_ok(head_major[:, :, :10])                    # a window of tokens: heads no longer evenly spaced
+    assert not ops._tc_view_ok(torch.zeros(b, h, d, s, dtype=torch.bfloat16).transpose(2, 3))   # feature axis not contiguous
+    assert not ops._tc_view_ok(head_major.permute(1, 0, 2, 3).contiguous().permute(1, 0, 2, 3))  # batch inside heads
