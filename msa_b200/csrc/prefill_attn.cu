@@ -336,8 +336,7 @@ prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, long long q_sb, long lo
 // sums the staged rows per chunk (pool_size keys, a multiple of the tile) in fp32 and writes the
 // chunk's mean, rounded once, to the bank's pooled K and V.
 // ---------------------------------------------------------------------------------------
-template <int kCtasPerSm>
-__global__ void __launch_bounds__(128, kCtasPerSm)
+__global__ void __launch_bounds__(128, 4)
 doc_attn_pool_kernel(const __nv_bfloat16* __restrict__ q, long long q_sb, long long q_sh, long long q_ss,
                      const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v, long long k_sb,
                      long long k_sh, long long k_ss, const int32_t* __restrict__ token_index,
@@ -548,15 +547,9 @@ extern "C" int msa_doc_attention_pool(const void* q, int64_t q_stride_b, int64_t
                 pool_size, kPfKeys);
   }
   if (n_segments == 0 || max_segment_len == 0) return MSA_OK;
-  static const int occ = [] {   // tuning only: CTAs per SM the kernel is compiled for (register cap 128 or 168)
-    const char* e = getenv("MSA_B200_ATTN_CTAS_PER_SM");
-    return e && atoi(e) == 3 ? 3 : 4;
-  }();
-  auto kernel = occ == 3 ? doc_attn_pool_kernel<3> : doc_attn_pool_kernel<4>;
   static thread_local bool configured = false;
   if (!configured) {
-    MSA_CUDA_OK(cudaFuncSetAttribute(doc_attn_pool_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
-    MSA_CUDA_OK(cudaFuncSetAttribute(doc_attn_pool_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
+    MSA_CUDA_OK(cudaFuncSetAttribute(doc_attn_pool_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
     configured = true;
   }
   // tok / seq_len for tok < 2^31: (mulhi(tok, mul) + tok) >> shift with shift = ceil(log2 seq_len)
@@ -564,7 +557,7 @@ extern "C" int msa_doc_attention_pool(const void* q, int64_t q_stride_b, int64_t
   while ((1ull << div_shift) < (uint64_t)seq_len) ++div_shift;
   const uint32_t div_mul = (uint32_t)((((1ull << div_shift) - (uint64_t)seq_len) << 32) / (uint64_t)seq_len + 1);
   dim3 grid((max_segment_len + kPfRows - 1) / kPfRows, n_q_heads, n_segments);
-  kernel<<<grid, 128, kPfSmem, (cudaStream_t)stream>>>(
+  doc_attn_pool_kernel<<<grid, 128, kPfSmem, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)q, q_stride_b, q_stride_h, q_stride_s, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
       k_stride_b, k_stride_h, k_stride_s, token_index, seg_offsets, seq_len, div_mul, div_shift, n_q_heads, n_kv_heads,
       scale * 1.4426950408889634f, (__nv_bfloat16*)out, chunk_offsets, n_chunks, pool_size, (__nv_bfloat16*)pooled_k,

@@ -317,3 +317,43 @@ def test_doc_attention_tc_matches_restatement(doc_lens, layout):
     # and against the mma.sync kernel
     alt, _, _ = ops.doc_attention_pool(q, k, v, tok, seg_off, max(doc_lens), scale=scale)
     assert (got - alt[0].float().cpu()).norm() / ref.norm() < 1e-2
+
+
+def test_doc_attention_kernels_with_several_block_rows():
+    """Two block rows with different document layouts: the flat token positions carry the row, and both kernels
+    must address q / k / v of the second row correctly (token-major tensors, as the layer produces them)."""
+    from msa_b200 import ops
+    dev = torch.device("cuda:0")
+    hq, hkv, s = 8, 2, 400
+    g = torch.Generator().manual_seed(21)
+    doc_ids = torch.zeros(2, s, dtype=torch.long)
+    rows = [[(0, 140), (140, 300), (300, 400)], [(10, 200), (200, 330)]]      # (start, end) of every document
+    for r, docs in enumerate(rows):
+        for i, (a, b) in enumerate(docs):
+            doc_ids[r, a:b] = i + 1
+    mask = torch.ones(2, s, dtype=torch.long)
+    q, k, v = [torch.randn(2, s, h, 128, generator=g).to(torch.bfloat16).to(dev).transpose(1, 2) for h in (hq, hkv, hkv)]
+    tok, off, _ = ops.chunk_bookkeeping(doc_ids.to(dev), mask.to(dev), 64)
+    lens = [b - a for docs in rows for (a, b) in docs]
+    seg_off = torch.tensor([0] + lens).cumsum(0).to(torch.int32).to(dev)
+    scale = 128 ** -0.5
+    out_tc, status = ops.doc_attention_tc(q, k, v, tok, seg_off, max(lens), scale=scale)
+    out_mma, pk, pv = ops.doc_attention_pool(q, k, v, tok, seg_off, max(lens), chunk_offsets=off, pool_size=64, scale=scale)
+    torch.cuda.synchronize()
+    assert status.cpu().tolist()[0] == 0
+    ref = torch.zeros(2, s, hq * 128)
+    for r, docs in enumerate(rows):
+        for (a, b) in docs:
+            ref[r, a:b] = _segment_reference(q[r].cpu(), k[r].cpu(), v[r].cpu(), list(range(a, b)), scale)
+    for out in (out_tc, out_mma):
+        got = out.float().cpu()
+        assert (got - ref).norm() / ref.norm() < 1e-2
+        assert got[1, :10].abs().sum() == 0 and got[1, 330:].abs().sum() == 0
+    # the fused K / V chunk means across both rows against the oracle's exact means
+    from oracle import msa_oracle as O
+    flat = tok.cpu().long()
+    clen = (off[1:] - off[:-1]).cpu().long()
+    for pooled, states in ((pk, k), (pv, v)):
+        rows_ = states.cpu()[flat // s, :, flat % s]                       # [Td, Hkv, D]
+        exact = O.pool_chunks_exact(rows_.float(), clen).float()
+        assert (pooled.float().cpu() - exact).norm() / exact.norm() < 1e-2
