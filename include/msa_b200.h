@@ -199,6 +199,10 @@ int msa_topk_merge(const float* cand_scores, const int64_t* cand_local, const in
  * [n_seq]; total device int64 [1] (also written to *total_host_mapped when non-NULL).
  * msa_gather_run: copies every planned document into out_k / out_v, device
  * [Hkv, out_entries, D] (entry stride = D, head stride = out_head_stride elements).
+ * max_ctas: 0 = one CTA per document (fastest next to compute-bound kernels: 35 GB/s under the
+ * prefill routing kernel); a small cap (24 measured best) when the fetch runs beside kernels that
+ * saturate HBM, as in a decode step: the link is full from about a dozen CTAs, and reads queued
+ * beyond that inside the GPU only delay the neighbours' memory traffic.
  */
 /* Pins and maps [host_ptr, host_ptr+bytes) (memory the caller allocated, e.g. a shared-memory
  * file opened by every rank of the node; the reference pins its bank with pin_memory=True,
@@ -214,7 +218,7 @@ int msa_gather_plan(const int64_t* sel_local, const int32_t* sel_rank, int32_t n
 
 int msa_gather_run(const int64_t* plan, int32_t n_items, int32_t dtype, int32_t n_kv_heads,
                    int32_t head_dim, void* out_k, void* out_v, int64_t out_head_stride,
-                   int64_t out_entries, void* stream);
+                   int64_t out_entries, int32_t max_ctas, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Decode attention over the sparse context (split-KV flash-decode, GQA).

@@ -5,8 +5,6 @@
 // the device-visible mapping with 16-byte loads (PCIe reads, no staging copy, no host
 // thread involved) and scatters it into the head-major [Hkv, entries, D] layout the
 // attention path consumes.  Bound by PCIe bandwidth: 2*chunks*Hkv*D*e bytes per document.
-#include <cstdlib>
-
 #include "common.cuh"
 
 namespace msa {
@@ -123,20 +121,6 @@ gather_kernel(const int64_t* __restrict__ plan, int n_items, int n_kv_heads, int
   }
 }
 
-// CTAs of one gather launch.  The link is saturated by a few hundred KB of reads in flight (16 KB per
-// CTA); more resident CTAs only queue reads inside the GPU, where they get in the way of the HBM traffic
-// of whatever kernel the fetch is meant to hide behind.  Measured on B200 (32 KiB documents): 49.8 GB/s
-// alone from 12 CTAs up; the HBM-bound decode-time scoring next to it loses 0.18 ms per layer with 512
-// CTAs and 0.05 ms with 16-32.  MSA_B200_GATHER_CTAS overrides the cap (tuning only).
-inline int gather_ctas(int n_items) {
-  static const int cap = [] {
-    const char* e = getenv("MSA_B200_GATHER_CTAS");
-    const int v = e ? atoi(e) : 0;
-    return v > 0 ? v : 24;
-  }();
-  return n_items < cap ? n_items : cap;
-}
-
 }  // namespace msa
 
 using namespace msa;
@@ -160,18 +144,23 @@ extern "C" int msa_gather_plan(const int64_t* sel_local, const int32_t* sel_rank
 
 extern "C" int msa_gather_run(const int64_t* plan, int32_t n_items, int32_t dtype, int32_t n_kv_heads,
                               int32_t head_dim, void* out_k, void* out_v, int64_t out_head_stride,
-                              int64_t out_entries, void* stream) {
+                              int64_t out_entries, int32_t max_ctas, void* stream) {
   MSA_REQUIRE(dtype_ok(dtype), "gather_run: unknown dtype %d", dtype);
-  MSA_REQUIRE(plan && n_items >= 0 && n_kv_heads > 0 && head_dim > 0, "gather_run: bad arguments");
+  MSA_REQUIRE(plan && n_items >= 0 && n_kv_heads > 0 && head_dim > 0 && max_ctas >= 0, "gather_run: bad arguments");
+  // The link is saturated by a few hundred KB of reads in flight (16 KB per CTA).  Measured on B200 with
+  // 32 KiB documents: 49.8 GB/s alone from 12 CTAs up; next to the HBM-bound decode-time scoring the
+  // neighbour loses 0.18 ms per layer with 512 CTAs and 0.05 ms with 16-32; next to the tensor-bound prefill
+  // scoring one CTA per document is best (35 GB/s against 20 GB/s at 24 CTAs).
+  const int grid = (max_ctas > 0 && max_ctas < n_items) ? max_ctas : n_items;
   const int vec = 16 / (int)dtype_size(dtype);
   MSA_REQUIRE(head_dim % vec == 0 && out_head_stride % vec == 0, "gather_run: rows must be 16-byte multiples");
   if (n_items == 0 || out_entries == 0) return MSA_OK;
   MSA_REQUIRE(out_k && out_v && aligned16(out_k) && aligned16(out_v), "gather_run: bad output pointers");
   if (dtype == MSA_BF16)
-    gather_kernel<__nv_bfloat16><<<gather_ctas(n_items), kGatherThreads, 0, (cudaStream_t)stream>>>(
+    gather_kernel<__nv_bfloat16><<<grid, kGatherThreads, 0, (cudaStream_t)stream>>>(
         plan, n_items, n_kv_heads, head_dim, (__nv_bfloat16*)out_k, (__nv_bfloat16*)out_v, out_head_stride, out_entries);
   else
-    gather_kernel<float><<<gather_ctas(n_items), kGatherThreads, 0, (cudaStream_t)stream>>>(
+    gather_kernel<float><<<grid, kGatherThreads, 0, (cudaStream_t)stream>>>(
         plan, n_items, n_kv_heads, head_dim, (float*)out_k, (float*)out_v, out_head_stride, out_entries);
   MSA_LAUNCH_OK("gather_kernel");
   return MSA_OK;

@@ -160,7 +160,7 @@ class SparseDecodeModel:
                 after_attn.record(main)
                 self.fetch_stream.wait_event(after_attn)
                 with torch.cuda.stream(self.fetch_stream):
-                    fk, fv, n_sel, total = self.svc.fetch(local, rank, l, max_entries=B * self.retrieved)
+                    fk, fv, n_sel, total = self.svc.fetch(local, rank, l, max_entries=B * self.retrieved, max_ctas=24)
                     lo_, hi_ = s.template_len, s.template_len + self.retrieved
                     self.k_cache[l][:, :, lo_:hi_].copy_(fk.view(nkv, B, self.retrieved, d).permute(1, 0, 2, 3))
                     self.v_cache[l][:, :, lo_:hi_].copy_(fv.view(nkv, B, self.retrieved, d).permute(1, 0, 2, 3))

@@ -221,12 +221,15 @@ def gather_plan(sel_local: torch.Tensor, sel_rank: Optional[torch.Tensor], world
     return plan, n_sel, total
 
 
-def gather_run(plan: torch.Tensor, dtype: torch.dtype, n_kv_heads: int, head_dim: int, out_entries: int):
+def gather_run(plan: torch.Tensor, dtype: torch.dtype, n_kv_heads: int, head_dim: int, out_entries: int,
+               max_ctas: int = 0):
+    """Run a gather plan.  ``max_ctas``: 0 = one CTA per document; a small cap (24) when the fetch runs
+    beside HBM-bound kernels, e.g. inside a decode step."""
     dev = plan.device
     out_k = torch.empty((n_kv_heads, out_entries, head_dim), dtype=dtype, device=dev)
     out_v = torch.empty((n_kv_heads, out_entries, head_dim), dtype=dtype, device=dev)
     A.check(A.lib().msa_gather_run(A.ptr(plan), plan.shape[0], A.dtype_code(dtype), n_kv_heads, head_dim,
-                                   A.ptr(out_k), A.ptr(out_v), out_entries * head_dim, out_entries,
+                                   A.ptr(out_k), A.ptr(out_v), out_entries * head_dim, out_entries, int(max_ctas),
                                    A.stream_ptr(dev)), "msa_gather_run")
     return out_k, out_v
 

@@ -248,12 +248,13 @@ class MSAService(Memory, MemoryClientBase):
         return ops.topk_merge(sc, li, gi, self.model_config.doc_top_k, seq_offset=self.rank * b, n_seq=b)
 
     def fetch(self, winner_local: torch.Tensor, winner_rank: torch.Tensor, layer_idx: int,
-              max_entries: Optional[int] = None):
+              max_entries: Optional[int] = None, max_ctas: int = 0):
         """Steps 5-8 of ``doc_query`` (:1193-1312): K/V of the winners from the pinned host banks.
         Returns ``(final_k[Hkv, sumN, D], final_v, n_sel[B])``.  By default one 8-byte read-back sizes
         the result (the reference synchronises five times here).  With ``max_entries`` the outputs
         are allocated for that many entries instead, nothing is read back and the call never blocks
-        the host: ``(final_k[Hkv, max_entries, D], final_v, n_sel[B], total[1])``."""
+        the host: ``(final_k[Hkv, max_entries, D], final_v, n_sel[B], total[1])``.  ``max_ctas`` caps the
+        gather's grid (see ``ops.gather_run``): leave 0 next to prefill kernels, 24 inside a decode step."""
         if self._directory is None:
             self.publish_directory()
         base, offs, ln, kv_base = self._directory
@@ -263,12 +264,12 @@ class MSAService(Memory, MemoryClientBase):
         plan, n_sel, total = ops.gather_plan(winner_local, winner_rank, self.world_size, base, offs, ln,
                                              kv_base[layer_idx], chunk_bytes, total_host=None)
         if max_entries is not None:
-            k, v = ops.gather_run(plan, blk.kv.dtype, g.num_key_value_heads, g.head_dim, max_entries)
+            k, v = ops.gather_run(plan, blk.kv.dtype, g.num_key_value_heads, g.head_dim, max_entries, max_ctas)
             return k, v, n_sel, total
         self._total_pinned.copy_(total, non_blocking=True)
         torch.cuda.current_stream(self.device).synchronize()
         n = int(self._total_pinned.item())
-        k, v = ops.gather_run(plan, blk.kv.dtype, g.num_key_value_heads, g.head_dim, n)
+        k, v = ops.gather_run(plan, blk.kv.dtype, g.num_key_value_heads, g.head_dim, n, max_ctas)
         return k, v, n_sel
 
     def doc_query(self, query_states: torch.Tensor, query_mask: torch.Tensor, layer_idx: int):
