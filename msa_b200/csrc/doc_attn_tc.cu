@@ -2,27 +2,28 @@
 // head_dim 128, for documents that are runs of consecutive tokens of one row.
 //
 // Work item = 128 query tokens of one head of one document.  Persistent CTAs (two per SM: 97 KB of shared
-// memory and 256 TMEM columns each, so one CTA's MMAs run under the other's softmax) walk the items with a
-// fixed stride; 192 threads: warps 0-3 softmax (thread = query row = TMEM lane), warp 4 TMA producer, warp 5
-// MMA issuer + TMEM owner.  The next item's queries and first keys are loaded under the current item's last
-// softmax, PV and output.  Per 128-key tile:
-//     S = Q K^T        tcgen05.mma, A = Q and B = K both K-major in shared memory, fp32 into TMEM columns 0..127;
-//     softmax          each thread reads its row of S with tcgen05.ld (two passes: maximum, then exponentials)
-//                      and writes P as packed bf16 over the S columns it has consumed (tcgen05.st);
+// memory and 256 TMEM columns each) walk the items with a fixed stride; 192 threads: warps 0-3 softmax (thread
+// = query row = TMEM lane), warp 4 TMA producer, warp 5 MMA issuer + TMEM owner.  Per 64-key tile:
+//     S = Q K^T        tcgen05.mma, A = Q and B = K both K-major in shared memory, fp32 into one of two 64-column
+//                      TMEM buffers: S of tile t+1 (and t+2's keys) are ready before the softmax of tile t ends;
+//     softmax          each thread loads its 64 scores once with tcgen05.ld, takes the maximum, and writes P as
+//                      packed bf16 over the columns it has consumed (tcgen05.st); it then goes straight on to the
+//                      next tile's S without waiting for the tensor pipe;
 //     O += P V         tcgen05.mma with A = P read from TMEM and B = V as an MN-major shared-memory operand (V's
 //                      rows are keys, the reduction axis, so the tile TMA delivers IS the MN-major image); O
-//                      stays in TMEM columns 128..255 for the whole row block.
+//                      stays in TMEM columns 128..255 for the whole row block.  MMAs of one thread run in order,
+//                      so S of tile t+2 overwrites the buffer of P(t) only after PV(t) has read it.
 // The running maximum a row's exponentials refer to is only advanced when the true maximum has moved by more
-// than 2^8 (then the warp rescales its rows of O in TMEM and its sums); the final division uses the same
-// reference, so the result is exact while almost every tile skips the rescale.
-// Causality: key tile j <= row block index; only the last tile of a CTA is masked.  Keys past the document's
-// end are rows of the next document (or TMA's zero fill) and sit above the diagonal of every valid row.
-// K and V have one buffer each with their own barriers: K of tile t+1 lands during the softmax of tile t, V of
-// tile t+1 during S and softmax of tile t+1.  Every mbarrier wait is bounded; on expiry the CTA raises
-// status[0], drains and frees TMEM.
+// than 2^8 (then the warp waits for the PV in flight and rescales its rows of O in TMEM and its sums); the final
+// division uses the same reference, so the result is exact while almost every tile skips the rescale.
+// Causality: a 32-key chunk is fully visible, cut by the diagonal, or hidden for a whole warp (32 rows), decided
+// from the chunk's offset to the warp's rows; keys past the document's end are rows of the next document (or TMA's
+// zero fill) and sit above the diagonal of every valid row.  K and V are double buffered.  The next item's queries
+// are loaded once the current item's last S has been issued.  Every mbarrier wait is bounded; on expiry the CTA
+// raises status[0], drains and frees TMEM.
 //
-// Bounds: 4*128*128*128 flops per tile on the tensor pipe (0.28 us per SM at the measured peak) and 16,384
-// exponentials (16 per clock per SM: 0.54 us), so the kernel is bound by the exponentials.
+// Bounds: 4*128*64*128 flops per tile on the tensor pipe (0.14 us per SM at the measured peak) and 8,192
+// exponentials (16 per clock per SM: 0.27 us), so the kernel is bound by the exponentials.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -30,12 +31,14 @@
 
 namespace msa {
 
-constexpr int kAtRows = 128, kAtKeys = 128, kAtD = 128;
+constexpr int kAtRows = 128, kAtKeys = 64, kAtD = 128;
 constexpr int kAtThreads = 192;
-constexpr int kAtBlk = kAtRows * 64 * 2;                 // one 64-column block of a 128-row tile: 16 KB
-constexpr int kAtTile = 2 * kAtBlk;                      // a [128 x 128] bf16 tile
-constexpr int kAtSmem = 3 * kAtTile + 1024;              // Q, K, V
-constexpr uint32_t kColS = 0, kColO = 128, kAtTmemCols = 256;   // TMEM columns: S (P written over it) 0..127, O 128..255
+constexpr int kAtBlk = kAtRows * 64 * 2;                 // one 64-column block of the 128-row query tile: 16 KB
+constexpr int kAtTile = 2 * kAtBlk;                      // the [128 x 128] bf16 query tile
+constexpr int kAtKvBlk = kAtKeys * 64 * 2;               // one 64-column block of a 64-key K or V tile: 8 KB
+constexpr int kAtKvTile = 2 * kAtKvBlk;                  // a [64 x 128] bf16 K or V tile
+constexpr int kAtSmem = kAtTile + 4 * kAtKvTile + 1024;  // Q, 2 x (K, V)
+constexpr uint32_t kColS = 0, kColO = 128, kAtTmemCols = 256;   // TMEM columns: S0 0..63, S1 64..127 (P over them), O 128..255
 constexpr float kRescaleStep = 8.f;                      // log2 units the row maximum may run ahead of its reference
 
 struct DocAttnTcParams {
@@ -115,7 +118,7 @@ __device__ __forceinline__ AtItem at_item(const DocAttnTcParams& p, long long w)
   it.valid = x < n_mb;
   const int mb = n_mb - 1 - x;
   it.r0 = mb * kAtRows;
-  it.n_kt = mb + 1;
+  it.n_kt = 2 * (mb + 1);              // 64-key tiles up to the end of the row block
   it.hk = it.hq / (p.n_q_heads / p.n_kv_heads);
   it.tok0 = it.valid ? p.token_index[t0] : 0;
   it.b = (int)((__umulhi((uint32_t)it.tok0, p.div_mul) + (uint32_t)it.tok0) >> p.div_shift);
@@ -127,22 +130,26 @@ __global__ void __launch_bounds__(kAtThreads, 2)
 doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                    const __grid_constant__ CUtensorMap tmap_v, const DocAttnTcParams p) {
   extern __shared__ unsigned char smem_dyn[];
-  __shared__ uint64_t s_q_full, s_q_empty, s_k_full, s_k_empty, s_v_full, s_v_empty, s_s_full, s_p_full, s_o_full, s_drain;
+  __shared__ uint64_t s_q_full, s_q_empty, s_k_full[2], s_k_empty[2], s_v_full[2], s_v_empty[2], s_s_full[2], s_p_full[2],
+      s_o_full[2], s_drain;
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
-  unsigned char *q_smem = tiles, *k_smem = tiles + kAtTile, *v_smem = tiles + 2 * kAtTile;
+  unsigned char* q_smem = tiles;
+  unsigned char* kv_smem = tiles + kAtTile;      // stage s: K at s * 2 * kAtKvTile, V right after it
   volatile int* abort_flag = &s_abort;
 
   if (threadIdx.x == 0) {
     mbar_init(&s_q_full, 1); mbar_init(&s_q_empty, 1);
-    mbar_init(&s_k_full, 1); mbar_init(&s_k_empty, 1);
-    mbar_init(&s_v_full, 1); mbar_init(&s_v_empty, 1);
-    mbar_init(&s_s_full, 1);
-    mbar_init(&s_p_full, 4);
-    mbar_init(&s_o_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_k_full[i], 1); mbar_init(&s_k_empty[i], 1);
+      mbar_init(&s_v_full[i], 1); mbar_init(&s_v_empty[i], 1);
+      mbar_init(&s_s_full[i], 1);
+      mbar_init(&s_p_full[i], 4);
+      mbar_init(&s_o_full[i], 1);
+    }
     mbar_init(&s_drain, 1);
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -157,8 +164,10 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = s_tmem_base;
 
-  // Every role walks the same items in the same order; `n_it` counts the valid items and `n_t` the key tiles this
-  // CTA has gone through, and every barrier's phase follows from those two counters.
+  // Every role walks the same items in the same order.  n_it counts the valid items and n_t the key tiles this
+  // CTA has gone through; tile n_t uses stage / S buffer / barrier set n_t & 1 for the (n_t >> 1)-th time, and
+  // every barrier's phase follows from those counters.  The softmax may be up to two tiles ahead of the PVs, which
+  // is why P-ready and O-ready also come in pairs: within one barrier a waiter is never more than one phase behind.
   if (warp == 4) {
     // ------------------------------- TMA producer -------------------------------------
     if (lane == 0) {
@@ -169,20 +178,22 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         if (!it.valid) continue;
         const int qy = it.b * p.q_yb + it.hq * p.q_yh + it.s0 + it.r0, qx = it.hq * p.q_xh;
         const int ky = it.b * p.k_yb + it.hk * p.k_yh + it.s0, kx = it.hk * p.k_xh;
-        // the query buffer is free once the last S of the previous item has been issued and has completed
+        // the query buffer is free once the previous item's last S has completed
         if (!(ok = mbar_wait(&s_q_empty, (n_it & 1u) ^ 1u, abort_flag, p.status, 1))) break;
         mbar_expect_tx(&s_q_full, kAtTile);
         tma_load_2d(q_smem, &tmap_q, qx, qy, &s_q_full);
         tma_load_2d(q_smem + kAtBlk, &tmap_q, qx + 64, qy, &s_q_full);
         for (int t = 0; t < it.n_kt; ++t, ++n_t) {
-          if (!(ok = mbar_wait(&s_k_empty, (n_t & 1u) ^ 1u, abort_flag, p.status, 1))) break;
-          mbar_expect_tx(&s_k_full, kAtTile);
-          tma_load_2d(k_smem, &tmap_k, kx, ky + t * kAtKeys, &s_k_full);
-          tma_load_2d(k_smem + kAtBlk, &tmap_k, kx + 64, ky + t * kAtKeys, &s_k_full);
-          if (!(ok = mbar_wait(&s_v_empty, (n_t & 1u) ^ 1u, abort_flag, p.status, 1))) break;
-          mbar_expect_tx(&s_v_full, kAtTile);
-          tma_load_2d(v_smem, &tmap_v, kx, ky + t * kAtKeys, &s_v_full);
-          tma_load_2d(v_smem + kAtBlk, &tmap_v, kx + 64, ky + t * kAtKeys, &s_v_full);
+          const uint32_t st = n_t & 1u, ph = (n_t >> 1) & 1u;
+          unsigned char* ks = kv_smem + (size_t)st * 2 * kAtKvTile;
+          if (!(ok = mbar_wait(&s_k_empty[st], ph ^ 1u, abort_flag, p.status, 1))) break;
+          mbar_expect_tx(&s_k_full[st], kAtKvTile);
+          tma_load_2d(ks, &tmap_k, kx, ky + t * kAtKeys, &s_k_full[st]);
+          tma_load_2d(ks + kAtKvBlk, &tmap_k, kx + 64, ky + t * kAtKeys, &s_k_full[st]);
+          if (!(ok = mbar_wait(&s_v_empty[st], ph ^ 1u, abort_flag, p.status, 1))) break;
+          mbar_expect_tx(&s_v_full[st], kAtKvTile);
+          tma_load_2d(ks + kAtKvTile, &tmap_v, kx, ky + t * kAtKeys, &s_v_full[st]);
+          tma_load_2d(ks + kAtKvTile + kAtKvBlk, &tmap_v, kx + 64, ky + t * kAtKeys, &s_v_full[st]);
         }
         ++n_it;
       }
@@ -194,43 +205,54 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   } else if (warp == 5) {
     // ------------------------------- MMA issuer ----------------------------------------
     if (lane == 0) {
-      // D = f32, A = B = bf16, M = 128, N = 128; S: both operands K-major; PV: B (= V) MN-major
+      // D = f32, A = B = bf16, M = 128; S: N = 64 keys, both operands K-major; PV: N = 128, B (= V) MN-major
       const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kAtKeys >> 3) << 17) |
                                ((uint32_t)(kAtRows >> 4) << 24);
       const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(kAtD >> 3) << 17) |
                                 ((uint32_t)(kAtRows >> 4) << 24);
-      const uint32_t qa = smem_u32(q_smem), ka = smem_u32(k_smem), va = smem_u32(v_smem);
-      uint32_t n_it = 0, n_t = 0;
+      const uint32_t qa = smem_u32(q_smem), kva = smem_u32(kv_smem);
+      uint32_t n_it = 0, n_t = 0;     // n_t: tiles whose PV has been issued
       bool ok = true;
+      // S of tile g (global count) of the current item; `last` = the item's last tile
+      auto issue_s = [&](uint32_t g, bool last) -> bool {
+        const uint32_t st = g & 1u, ph = (g >> 1) & 1u;
+        if (!mbar_wait(&s_k_full[st], ph, abort_flag, p.status, 3)) return false;
+        tc_fence_after();
+        const uint32_t ka = kva + st * 2 * kAtKvTile;
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb) {
+          const uint64_t a_desc = make_smem_desc(qa + kb * kAtBlk), b_desc = make_smem_desc(ka + kb * kAtKvBlk);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            tc_mma_bf16(tmem_base + kColS + st * kAtKeys, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc_s,
+                        (kb > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(&s_s_full[st]);
+        tc_commit(&s_k_empty[st]);
+        if (last) tc_commit(&s_q_empty);   // the next item's queries may land under this item's tail
+        return true;
+      };
       for (long long w = blockIdx.x; w < p.n_items && ok; w += gridDim.x) {
         const AtItem it = at_item(p, w);
         if (!it.valid) continue;
         if (!(ok = mbar_wait(&s_q_full, n_it & 1u, abort_flag, p.status, 2))) break;
+        // two S tiles run ahead of the softmax (n_kt is even: a row block spans whole pairs of key tiles)
+        if (!(ok = issue_s(n_t, it.n_kt == 1))) break;
+        if (it.n_kt > 1 && !(ok = issue_s(n_t + 1, it.n_kt == 2))) break;
         for (int t = 0; t < it.n_kt; ++t, ++n_t) {
-          const uint32_t phase = n_t & 1u;
-          if (!(ok = mbar_wait(&s_k_full, phase, abort_flag, p.status, 3))) break;
+          const uint32_t st = n_t & 1u, ph = (n_t >> 1) & 1u;
+          if (!(ok = mbar_wait(&s_v_full[st], ph, abort_flag, p.status, 3))) break;
+          if (!(ok = mbar_wait(&s_p_full[st], ph, abort_flag, p.status, 4))) break;
           tc_fence_after();
-          // S overwrites the previous tile's P: issued after that tile's PV, and MMAs of one thread run in order
-#pragma unroll
-          for (int kb = 0; kb < 2; ++kb) {
-            const uint64_t a_desc = make_smem_desc(qa + kb * kAtBlk), b_desc = make_smem_desc(ka + kb * kAtBlk);
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-              tc_mma_bf16(tmem_base + kColS, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc_s,
-                          (kb > 0 || k > 0) ? 1u : 0u);
-          }
-          tc_commit(&s_s_full);
-          tc_commit(&s_k_empty);                        // the next K may land while this tile's softmax runs
-          if (t == it.n_kt - 1) tc_commit(&s_q_empty);  // and the next item's queries under this item's tail
-          if (!(ok = mbar_wait(&s_v_full, phase, abort_flag, p.status, 3))) break;
-          if (!(ok = mbar_wait(&s_p_full, phase, abort_flag, p.status, 4))) break;
-          tc_fence_after();
+          const uint32_t va = kva + st * 2 * kAtKvTile + kAtKvTile;
 #pragma unroll
           for (int j = 0; j < kAtKeys / 16; ++j)   // 16 keys per step: 8 TMEM columns of P, two 8-key groups of V
-            tc_mma_bf16_ts(tmem_base + kColO, tmem_base + kColS + (uint32_t)(8 * j),
-                           make_smem_desc_mn(va + j * 2048, kAtBlk), idesc_pv, (t > 0 || j > 0) ? 1u : 0u);
-          tc_commit(&s_o_full);
-          tc_commit(&s_v_empty);
+            tc_mma_bf16_ts(tmem_base + kColO, tmem_base + kColS + st * kAtKeys + (uint32_t)(8 * j),
+                           make_smem_desc_mn(va + j * 2048, kAtKvBlk), idesc_pv, (t > 0 || j > 0) ? 1u : 0u);
+          tc_commit(&s_o_full[st]);
+          tc_commit(&s_v_empty[st]);
+          // S of tile t+2 reuses this tile's buffer: in order after the PV that read P from it
+          if (t + 2 < it.n_kt && !(ok = issue_s(n_t + 2, t + 3 == it.n_kt))) break;
         }
         ++n_it;
       }
@@ -241,45 +263,48 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   } else {
     // ------------------------------- softmax / output (warps 0-3) ----------------------
     const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
-    const uint32_t s_addr = lane_base + kColS;
     uint32_t n_t = 0;
     bool ok = true;
     for (long long w = blockIdx.x; w < p.n_items && ok; w += gridDim.x) {
       const AtItem it = at_item(p, w);
       if (!it.valid) continue;
       const int row = it.r0 + warp * 32 + lane;            // row of the document; TMEM lane = warp*32 + lane
-      const int limit = min(row, it.len - 1);              // last visible key
       float m_ref = -INFINITY, l_run = 0.f;                // m_ref: the maximum the exponentials refer to
       for (int t = 0; t < it.n_kt; ++t, ++n_t) {
-        ok = mbar_wait(&s_s_full, n_t & 1u, abort_flag, p.status, 5);
+        const uint32_t st = n_t & 1u;
+        ok = mbar_wait(&s_s_full[st], (n_t >> 1) & 1u, abort_flag, p.status, 5);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        const int key0 = t * kAtKeys;
-        const bool diag = t == it.n_kt - 1;
-        // pass 1: row maximum.  The load of the next 32 columns is in flight while these are reduced.
-        float mx = -INFINITY;
+        const uint32_t s_addr = lane_base + kColS + st * kAtKeys;
+        // Visibility of the two 32-key chunks for this warp's 32 rows: d = (first row of the warp) - (first key
+        // of the chunk); d >= 32: every key visible, d == 0: key i visible to lanes >= i, d < 0: hidden.
+        const int d0 = it.r0 + warp * 32 - t * kAtKeys, d1 = d0 - 32;
         uint32_t va[32], vb[32];
         tmem_ld32(s_addr, va);
+        tmem_ld32(s_addr + 32, vb);
+        tmem_ld_wait();
+        float mx = -INFINITY;
+        if (d0 >= 32) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t(&cur)[32] = (c & 1) ? vb : va;
-          uint32_t(&nxt)[32] = (c & 1) ? va : vb;
-          tmem_ld_wait();
-          if (c < 3) tmem_ld32(s_addr + 32 * (c + 1), nxt);
-          if (diag) {
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(va[i]));
+        } else if (d0 == 0) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, key0 + 32 * c + i <= limit ? __uint_as_float(cur[i]) : -INFINITY);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(cur[i]));
-          }
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, i <= lane ? __uint_as_float(va[i]) : -INFINITY);
         }
-        // advance the reference only when the maximum ran ahead by more than the step (always on the first tile)
+        if (d1 >= 32) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(vb[i]));
+        } else if (d1 == 0) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, i <= lane ? __uint_as_float(vb[i]) : -INFINITY);
+        }
+        // advance the reference only when the maximum ran ahead by more than the step (always on the first tile;
+        // never on a tile this warp does not see at all, where mx is -inf)
         const bool move = (mx - m_ref) * p.scale_log2e > kRescaleStep;
         if (__any_sync(0xffffffffu, move)) {
-          if (t > 0) {   // O of the previous tiles is complete: this warp's rows are rescaled in place
-            ok = mbar_wait(&s_o_full, (n_t - 1u) & 1u, abort_flag, p.status, 6);
+          if (t > 0) {   // wait for the PV in flight, then rescale this warp's rows of O in place
+            ok = mbar_wait(&s_o_full[(n_t - 1u) & 1u], ((n_t - 1u) >> 1) & 1u, abort_flag, p.status, 6);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
@@ -298,39 +323,52 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           if (move) m_ref = mx;
         }
         const float neg_m = -m_ref * p.scale_log2e;
-        // pass 2: exponentials, row sum, P as packed bf16 over the consumed S columns (chunk c of P lands on
-        // columns 16c..16c+15, all below the 32(c+1) columns already read, also by the load in flight)
+        // exponentials, row sum, P as packed bf16 over the consumed columns of this buffer
         float sum = 0.f;
-        tmem_ld32(s_addr, va);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t(&cur)[32] = (c & 1) ? vb : va;
-          uint32_t(&nxt)[32] = (c & 1) ? va : vb;
-          uint32_t pk[16];
-          tmem_ld_wait();
-          if (c < 3) tmem_ld32(s_addr + 32 * (c + 1), nxt);   // in flight under the exponentials of this chunk
+        uint32_t pk[16];
+        if (d0 >= 0) {
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            float e0 = exp2f(fmaf(__uint_as_float(cur[i]), p.scale_log2e, neg_m));
-            float e1 = exp2f(fmaf(__uint_as_float(cur[i + 1]), p.scale_log2e, neg_m));
-            if (diag) {
-              if (key0 + 32 * c + i > limit) e0 = 0.f;
-              if (key0 + 32 * c + i + 1 > limit) e1 = 0.f;
+            float e0 = exp2f(fmaf(__uint_as_float(va[i]), p.scale_log2e, neg_m));
+            float e1 = exp2f(fmaf(__uint_as_float(va[i + 1]), p.scale_log2e, neg_m));
+            if (d0 == 0) {
+              if (i > lane) e0 = 0.f;
+              if (i + 1 > lane) e1 = 0.f;
             }
             sum += e0 + e1;
             pk[i >> 1] = pack2_bf16(e0, e1);
           }
-          tmem_st16(s_addr + 16 * c, pk);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pk[i] = 0u;
         }
+        tmem_st16(s_addr, pk);
+        if (d1 >= 0) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float e0 = exp2f(fmaf(__uint_as_float(vb[i]), p.scale_log2e, neg_m));
+            float e1 = exp2f(fmaf(__uint_as_float(vb[i + 1]), p.scale_log2e, neg_m));
+            if (d1 == 0) {
+              if (i > lane) e0 = 0.f;
+              if (i + 1 > lane) e1 = 0.f;
+            }
+            sum += e0 + e1;
+            pk[i >> 1] = pack2_bf16(e0, e1);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pk[i] = 0u;
+        }
+        tmem_st16(s_addr + 16, pk);
         l_run += sum;
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&s_p_full);
+        if (lane == 0) mbar_arrive(&s_p_full[st]);
       }
       if (!ok) break;
       // the item's output: O is complete after the last PV
-      ok = mbar_wait(&s_o_full, (n_t - 1u) & 1u, abort_flag, p.status, 6);
+      ok = mbar_wait(&s_o_full[(n_t - 1u) & 1u], ((n_t - 1u) >> 1) & 1u, abort_flag, p.status, 6);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
