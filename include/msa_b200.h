@@ -311,6 +311,9 @@ int msa_doc_attention_pool(const void* q, int64_t q_stride_b, int64_t q_stride_h
  * segment ascending by one; the caller checks this, e.g. documents without masked tokens).  q, k, v must
  * be token-major ([B, S, H, D] storage viewed as [B, H, S, D]; the row stride may exceed H*D) or contiguous
  * head-major tensors; anything else is rejected with MSA_ERR_ARG and belongs to msa_doc_attention_pool.
+ * The tiles TMA brings in reach up to 127 positions past a document's end (the next document's rows, padding
+ * positions, or zero fill past the tensor): their scores are masked, but V rows there are multiplied by zero
+ * probabilities, so they must hold finite numbers (projections of any token do).
  * status: int32[4], zeroed by the caller; status[0] != 0 after completion means a bounded barrier wait ran
  * out inside the kernel (output invalid).
  */

@@ -407,7 +407,8 @@ def doc_attention_tc(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, token_in
                      scale: Optional[float] = None, status: Optional[torch.Tensor] = None):
     """``doc_attention_pool`` without pooling on the tcgen05 kernel: every segment must be a run of consecutive
     tokens of one row, and q / k / v token-major or contiguous head-major (no copies are made here; other
-    layouts raise).  Returns ``(out, status)``; ``status[0] != 0`` after a sync means the kernel gave up."""
+    layouts raise).  Positions up to 127 tokens past a document's end must hold finite k / v values (they meet zero
+    probabilities).  Returns ``(out, status)``; ``status[0] != 0`` after a sync means the kernel gave up."""
     A.need_cuda(q, k, v, token_index, seg_offsets)
     b, hq, s, d = q.shape
     hkv = k.shape[1]
