@@ -875,7 +875,9 @@ def run_generate(args):
                       "exposed_ms_per_step": max(0.0, (ms_total - ms_nofetch) / new_tokens),
                       "pcie_bytes_per_step_per_gpu": 18 * b * TOP_K * CHUNKS_PER_DOC * 2 * HKV * D * 2},
             "dense_weight_bytes_per_step": per_step_bytes, "clocks": clocks,
-            "gpu_launches": new_tokens * (36 * 3 + 18 * 7), "last_tokens": tokens_host[:4].tolist()}), flush=True)
+            # this package's kernels per step: per layer add+norm x2, q/k norm+rope, decode attention (+ combine),
+            # SiLU*up; per router layer fold, table fill, scoring, top-k x2, merge, gather plan, gather; final norm
+            "gpu_launches": new_tokens * (36 * 5 + 18 * 8 + 1), "last_tokens": tokens_host[:4].tolist()}), flush=True)
     if world > 1:
         # graphs that captured NCCL kernels were alive in this process: leave without tearing the
         # communicator down (its destructor can wait forever on them)
