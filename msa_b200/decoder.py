@@ -146,7 +146,7 @@ class SparseDecodeModel:
             if l in self.router_layers and self.svc is not None:
                 self._mark("route_start", l)
                 rq = qkv[:, (nq + 2 * nkv) * d:].view(B, nq, 1, d)      # L2-normalised inside the fold kernel
-                routed = self.svc.route(rq, self.query_mask, l, l2_normalize=True)
+                routed = self.svc.route(rq, self.query_mask, l, l2_normalize=True, all_valid=True)
                 self._mark("route_end", l)
             self._mark("attn_start", l)
             ops.sparse_decode_attn(q, self.k_cache[l], self.v_cache[l], self.kv_len, k, v, n_splits=self.n_splits,

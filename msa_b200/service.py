@@ -213,7 +213,8 @@ class MSAService(Memory, MemoryClientBase):
         self._shared_banks = []
 
     # ------------------------------------------------------------------ the layer-facing call
-    def _gather_querys(self, query_states: torch.Tensor, query_mask: torch.Tensor, l2_normalize: bool = False):
+    def _gather_querys(self, query_states: torch.Tensor, query_mask: torch.Tensor, l2_normalize: bool = False,
+                       all_valid: bool = False):
         """Fold local queries, agree on the padded length, all-gather (:1088-1131).
         Returns ``(q_folded_all[W*B*s_pad, Hkv*D], row_bias_all, s_pad, B)``."""
         b, hq, s, d = query_states.shape
@@ -227,16 +228,27 @@ class MSAService(Memory, MemoryClientBase):
                                        s_pad=s_pad, l2_normalize=l2_normalize)
         if self.world_size > 1:
             qf = all_gather_cat(qf, self.world_size, self.group).view(-1, qf.shape[1])
-            bias = all_gather_cat(bias, self.world_size, self.group).view(-1)
+            if all_valid and s == s_pad:
+                # every rank's mask is all ones and nothing is padded: the gathered bias is zero, no collective needed
+                key = (self.world_size * b * s_pad,)
+                cached = self.__dict__.get("_zero_bias")
+                if cached is None or cached.shape != key:
+                    cached = self._zero_bias = torch.zeros(key, dtype=torch.float32, device=self.device)
+                bias = cached
+            else:
+                bias = all_gather_cat(bias, self.world_size, self.group).view(-1)
         return qf, bias, s_pad, b
 
-    def route(self, query_states: torch.Tensor, query_mask: torch.Tensor, layer_idx: int, l2_normalize: bool = False):
+    def route(self, query_states: torch.Tensor, query_mask: torch.Tensor, layer_idx: int, l2_normalize: bool = False,
+              all_valid: bool = False):
         """Steps 1-4 of ``doc_query`` (:1149-1191): returns the merged winners of this rank's own
         queries ``(scores[B,k], local_ids[B,k] (-1 invalid), global_ids[B,k], owner_rank[B,k])``.
         ``l2_normalize``: the queries are raw projections; normalise every head inside the fold kernel
-        (what the layer does with ``F.normalize`` before calling ``doc_query`` in cosine mode)."""
+        (what the layer does with ``F.normalize`` before calling ``doc_query`` in cosine mode).
+        ``all_valid``: the caller guarantees that every rank's ``query_mask`` is all ones (a decode step), which
+        saves the all-gather of the row bias."""
         b, hq, s, d = query_states.shape
-        qf, bias, s_pad, _ = self._gather_querys(query_states, query_mask, l2_normalize)
+        qf, bias, s_pad, _ = self._gather_querys(query_states, query_mask, l2_normalize, all_valid)
         scale = self.scaling if self.scaling > 0 else 1.0
         n_all = self.world_size * b
         sc, li, gi = self.score_folded(layer_idx, qf, bias, n_all, s_pad, hq, self.shard_top_k, scale=scale)

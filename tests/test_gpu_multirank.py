@@ -35,6 +35,12 @@ def _rank(rank, world, port, ret):
     for _ in range(2):   # twice: the second call reuses every cached table
         fk, fv, fs, n_sel, wg = svc.doc_query(T("q").to(dev), T("mask").to(dev), 0)
         outs.append([x.cpu() for x in (fk, fv, fs, n_sel, wg)])
+    # a decode-shaped call (one token per sequence, every mask all ones): the bias all-gather may be skipped
+    q1 = T("q")[:, :, :1].contiguous().to(dev)
+    m1 = torch.ones(q1.shape[0], 1, dtype=torch.bool, device=dev)
+    a = svc.route(q1, m1, 0)
+    b = svc.route(q1, m1, 0, all_valid=True)
+    assert all(torch.equal(x, y) for x, y in zip(a, b))
     svc.check_status()
     svc.close_host_banks()
     ret[rank] = outs
