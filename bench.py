@@ -172,7 +172,7 @@ def run_ours(args):
     import torch.distributed as dist
     from msa_b200 import ops
     from msa_b200.memory import AttentionGeometry, Document, ModelConfig
-    from msa_b200.service import MSAService, all_gather_cat, pack_candidates, unpack_candidates
+    from msa_b200.service import MSAService, all_gather_cat
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -223,6 +223,7 @@ def run_ours(args):
     min_val = torch.finfo(torch.bfloat16).min
     route_events = []
     launches = [0]
+    cand = ops.candidate_buffer(n_all, min(shard_k, docs_local + 1), dev) if world > 1 else None
 
     def layer_resident(i, layer, timed):
         qf, bias, _ = ops.fold_queries(q_dev[i], mask_dev, HQ // HKV, s_pad=s_pad)
@@ -238,10 +239,11 @@ def run_ours(args):
         if timed:
             e1.record()
             route_events.append((e0, e1))
-        sc, li, gi = ops.topk_select(keys, shard_k, svc.block_desc.doc_ids)
         if world > 1:
-            sc, li, gi = unpack_candidates(all_gather_cat(pack_candidates(sc, li, gi), world))
+            ops.topk_select(keys, shard_k, svc.block_desc.doc_ids, out=cand[1:])
+            sc, li, gi = ops.candidate_views(all_gather_cat(cand[0], world))
         else:
+            sc, li, gi = ops.topk_select(keys, shard_k, svc.block_desc.doc_ids)
             sc, li, gi = sc.unsqueeze(0), li.unsqueeze(0), gi.unsqueeze(0)
         launches[0] += 5
         return ops.topk_merge(sc, li, gi, TOP_K, seq_offset=rank * b, n_seq=b)

@@ -173,12 +173,14 @@ int msa_topk_select(const uint32_t* score_keys, int64_t table_stride, int32_t n_
  * Replaces steps 4-5 of MSAService.doc_query (src/msa_service.py:1174-1196): top-k over
  * the W*kc candidates of each query, owner rank of each winner, invalidation of winners
  * whose score is <= invalid_below (-1e9 in the reference, :1190).
- * cand_*: device, candidate (w, b, j) at index w*stride_w + b*kc + j.
+ * cand_*: device, candidate (w, b, j) at element index w*stride_w + b*kc + j of cand_scores and at
+ * w*stride_w_ids + b*kc + j of cand_local / cand_global (two strides, so that the three arrays can be
+ * planes of one all-gathered buffer: float scores and 64-bit ids have different element sizes).
  * Outputs [n_seq, k]: scores, local ids (-1 where invalid), global ids, owner ranks.
  * Ties: lower rank, then lower position first.  Requires W*kc <= 4096.
  */
 int msa_topk_merge(const float* cand_scores, const int64_t* cand_local, const int64_t* cand_global,
-                   int64_t stride_w, int32_t world, int32_t n_seq, int32_t kc, int32_t k,
+                   int64_t stride_w, int64_t stride_w_ids, int32_t world, int32_t n_seq, int32_t kc, int32_t k,
                    float invalid_below, float* out_scores, int64_t* out_local, int64_t* out_global,
                    int32_t* out_rank, void* stream);
 

@@ -57,7 +57,7 @@ def lib() -> C.CDLL:
         l.msa_topk_workspace_bytes.argtypes = [i32, i32, i32]
         l.msa_topk_workspace_bytes.restype = i64
         l.msa_topk_select.argtypes = [vp, i64, i32, i32, i32, vp, vp, vp, vp, vp, i64, vp]
-        l.msa_topk_merge.argtypes = [vp, vp, vp, i64, i32, i32, i32, i32, f32, vp, vp, vp, vp, vp]
+        l.msa_topk_merge.argtypes = [vp, vp, vp, i64, i64, i32, i32, i32, i32, f32, vp, vp, vp, vp, vp]
         l.msa_gather_plan.argtypes = [vp, vp, i32, i32, i32, vp, vp, vp, vp, i64, vp, vp, vp, vp, vp]
         l.msa_gather_run.argtypes = [vp, i32, i32, i32, i32, vp, vp, i64, i64, i32, vp]
         l.msa_bank_register_host.argtypes = [vp, i64, vp]

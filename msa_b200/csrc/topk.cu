@@ -220,7 +220,7 @@ constexpr int kMergeMax = 4096;
 
 __global__ void __launch_bounds__(kMergeThreads)
 topk_merge_kernel(const float* __restrict__ cand_scores, const int64_t* __restrict__ cand_local,
-                  const int64_t* __restrict__ cand_global, long long stride_w, int world, int kc, int k,
+                  const int64_t* __restrict__ cand_global, long long stride_w, long long stride_w_ids, int world, int kc, int k,
                   float invalid_below, float* __restrict__ out_scores, int64_t* __restrict__ out_local,
                   int64_t* __restrict__ out_global, int32_t* __restrict__ out_rank) {
   __shared__ unsigned long long s_key[kMergeMax];
@@ -237,8 +237,8 @@ topk_merge_kernel(const float* __restrict__ cand_scores, const int64_t* __restri
     for (int o = 0; o < n; ++o) rank += s_key[o] > mine ? 1 : 0;
     if (rank < k) {
       const int w = p / kc, j = p % kc;
-      const long long src = (long long)w * stride_w + (long long)b * kc + j;
-      const float s = cand_scores[src];
+      const float s = cand_scores[(long long)w * stride_w + (long long)b * kc + j];
+      const long long src = (long long)w * stride_w_ids + (long long)b * kc + j;
       const long long o = (long long)b * k + rank;
       out_scores[o] = s;
       out_local[o] = s > invalid_below ? cand_local[src] : -1;
@@ -320,7 +320,7 @@ extern "C" int msa_topk_select(const uint32_t* score_keys, int64_t table_stride,
 }
 
 extern "C" int msa_topk_merge(const float* cand_scores, const int64_t* cand_local, const int64_t* cand_global,
-                              int64_t stride_w, int32_t world, int32_t n_seq, int32_t kc, int32_t k,
+                              int64_t stride_w, int64_t stride_w_ids, int32_t world, int32_t n_seq, int32_t kc, int32_t k,
                               float invalid_below, float* out_scores, int64_t* out_local, int64_t* out_global,
                               int32_t* out_rank, void* stream) {
   MSA_REQUIRE(cand_scores && cand_local && cand_global && out_scores && out_local && out_global && out_rank,
@@ -331,7 +331,7 @@ extern "C" int msa_topk_merge(const float* cand_scores, const int64_t* cand_loca
   MSA_REQUIRE(k <= world * kc, "topk_merge: k=%d exceeds the %d candidates per query", k, world * kc);
   if (n_seq == 0) return MSA_OK;
   topk_merge_kernel<<<n_seq, kMergeThreads, 0, (cudaStream_t)stream>>>(
-      cand_scores, cand_local, cand_global, stride_w, world, kc, k, invalid_below, out_scores, out_local,
+      cand_scores, cand_local, cand_global, stride_w, stride_w_ids, world, kc, k, invalid_below, out_scores, out_local,
       out_global, out_rank);
   MSA_LAUNCH_OK("topk_merge_kernel");
   return MSA_OK;

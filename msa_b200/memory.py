@@ -355,8 +355,9 @@ class Memory:
 
     # ------------------------------------------------------------------ scoring + selection
     def score_folded(self, layer_idx: int, q_folded, row_bias, n_seq: int, s_pad: int, n_heads: int, top_k: int,
-                     scale: float = 1.0):
-        """Score ``n_seq`` folded sequences against this shard and select ``top_k`` documents each."""
+                     scale: float = 1.0, out=None):
+        """Score ``n_seq`` folded sequences against this shard and select ``top_k`` documents each
+        (``out``: see ``ops.topk_select``)."""
         desc = self.block_desc
         blk = self.blocks[layer_idx]
         keys, _ = ops.route_scores(q_folded, row_bias, n_seq, s_pad, blk.rk, desc.chunk_doc, desc.nr_docs,
@@ -365,7 +366,7 @@ class Memory:
         ws = getattr(self, "_topk_ws", None)
         if need and (ws is None or ws.numel() * 8 < need):
             ws = self._topk_ws = torch.empty((need + 7) // 8, dtype=torch.int64, device=self.device)
-        return ops.topk_select(keys, top_k, desc.doc_ids, workspace=ws if need else None)
+        return ops.topk_select(keys, top_k, desc.doc_ids, workspace=ws if need else None, out=out)
 
     def prefill_stage2(self, layer_idx: int, query_states: torch.Tensor, query_mask: torch.Tensor):
         """src/msa_service.py:703-828.  query_states ``[B, Hkv, G, S, D]``, query_mask

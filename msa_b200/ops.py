@@ -159,17 +159,24 @@ def topk_workspace_bytes(n_seq: int, n_cols: int, k: int) -> int:
 
 
 def topk_select(keys: torch.Tensor, k: int, doc_ids_table: Optional[torch.Tensor] = None, n_cols: Optional[int] = None,
-                workspace: Optional[torch.Tensor] = None):
+                workspace: Optional[torch.Tensor] = None, out=None):
     """Exact top-k of every row of a key table.  Returns ``(scores f32, local_ids i64, global_ids i64)``,
-    each ``[n_seq, min(k, n_cols)]``, sorted by descending score (ties: ascending column)."""
+    each ``[n_seq, min(k, n_cols)]``, sorted by descending score (ties: ascending column).
+    ``out``: three contiguous tensors of those shapes to write into (e.g. the planes of ``candidate_buffer``)."""
     A.need_cuda(keys, doc_ids_table)
     n_seq = keys.shape[0]
     n_cols = keys.shape[1] if n_cols is None else n_cols
     k_eff = min(k, n_cols)
     dev = keys.device
-    scores = torch.empty((n_seq, k_eff), dtype=torch.float32, device=dev)
-    local = torch.empty((n_seq, k_eff), dtype=torch.int64, device=dev)
-    glob = torch.empty((n_seq, k_eff), dtype=torch.int64, device=dev)
+    if out is not None:
+        scores, local, glob = out
+        if not (scores.is_contiguous() and local.is_contiguous() and glob.is_contiguous()) or \
+                tuple(scores.shape) != (n_seq, k_eff) or scores.dtype != torch.float32 or local.dtype != torch.int64:
+            raise A.MsaError("topk_select: out must be contiguous (float32, int64, int64) tensors of shape [n_seq, k_eff]")
+    else:
+        scores = torch.empty((n_seq, k_eff), dtype=torch.float32, device=dev)
+        local = torch.empty((n_seq, k_eff), dtype=torch.int64, device=dev)
+        glob = torch.empty((n_seq, k_eff), dtype=torch.int64, device=dev)
     need = int(A.lib().msa_topk_workspace_bytes(n_seq, n_cols, k))
     if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
         workspace = torch.empty((need + 7) // 8, dtype=torch.int64, device=dev)
@@ -180,22 +187,46 @@ def topk_select(keys: torch.Tensor, k: int, doc_ids_table: Optional[torch.Tensor
     return scores, local, glob
 
 
+def candidate_buffer(n_seq: int, k: int, device):
+    """One int64 buffer ``[3, n_seq, k]`` that one collective can move: plane 0 holds the float32 scores in its
+    first half, planes 1 and 2 the local and global ids.  Returns ``(buffer, scores, local, global)`` (views)."""
+    buf = torch.empty((3, n_seq, k), dtype=torch.int64, device=device)
+    scores = buf[0].view(torch.float32).view(-1)[: n_seq * k].view(n_seq, k)
+    return buf, scores, buf[1], buf[2]
+
+
+def candidate_views(gathered: torch.Tensor):
+    """Views ``(scores, local, global)``, each ``[W, n_seq, k]``, of all-gathered candidate buffers ``[W, 3, n_seq, k]``."""
+    w, _, n_seq, k = gathered.shape
+    scores = gathered[:, 0].reshape(w, -1).view(torch.float32)[:, : n_seq * k].view(w, n_seq, k)
+    return scores, gathered[:, 1], gathered[:, 2]
+
+
 def topk_merge(cand_scores: torch.Tensor, cand_local: torch.Tensor, cand_global: torch.Tensor, k: int,
                seq_offset: int = 0, n_seq: Optional[int] = None, invalid_below: float = -1e9):
-    """cand_* ``[W, B_all, kc]`` contiguous; merges sequences ``seq_offset .. seq_offset+n_seq``.
+    """cand_* ``[W, B_all, kc]``, each rank's ``[B_all, kc]`` block contiguous (the rank stride is free, so the
+    three may be planes of one all-gathered buffer); merges sequences ``seq_offset .. seq_offset+n_seq``.
     Returns ``(scores[n_seq,k] f32, local[n_seq,k] i64 (-1 = invalid), global[n_seq,k] i64, rank[n_seq,k] i32)``."""
     A.need_cuda(cand_scores, cand_local, cand_global)
     w, b_all, kc = cand_scores.shape
     n_seq = b_all - seq_offset if n_seq is None else n_seq
     dev = cand_scores.device
     k = min(k, w * kc)
-    cs, cl, cg = cand_scores.contiguous(), cand_local.contiguous(), cand_global.contiguous()
+
+    def blocks_ok(t):
+        return t.stride(2) == 1 and t.stride(1) == kc
+    cs = cand_scores if blocks_ok(cand_scores) else cand_scores.contiguous()
+    cl = cand_local if blocks_ok(cand_local) else cand_local.contiguous()
+    cg = cand_global if blocks_ok(cand_global) else cand_global.contiguous()
+    if w > 1 and cl.stride(0) != cg.stride(0):
+        cl, cg = cl.contiguous(), cg.contiguous()
     out_s = torch.empty((n_seq, k), dtype=torch.float32, device=dev)
     out_l = torch.empty((n_seq, k), dtype=torch.int64, device=dev)
     out_g = torch.empty((n_seq, k), dtype=torch.int64, device=dev)
     out_r = torch.empty((n_seq, k), dtype=torch.int32, device=dev)
     off = seq_offset * kc
-    A.check(A.lib().msa_topk_merge(A.ptr(cs) + off * 4, A.ptr(cl) + off * 8, A.ptr(cg) + off * 8, b_all * kc, w,
+    A.check(A.lib().msa_topk_merge(A.ptr(cs) + off * 4, A.ptr(cl) + off * 8, A.ptr(cg) + off * 8,
+                                   cs.stride(0) if w > 1 else b_all * kc, cl.stride(0) if w > 1 else b_all * kc, w,
                                    n_seq, kc, k, invalid_below, A.ptr(out_s), A.ptr(out_l), A.ptr(out_g),
                                    A.ptr(out_r), A.stream_ptr(dev)), "msa_topk_merge")
     return out_s, out_l, out_g, out_r

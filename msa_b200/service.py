@@ -8,7 +8,7 @@ layer, :1105-1283):
      folded queries in local HBM (reference: all-gather of unfolded, zero-padded q and mask);
   2. the fused kernel scores ALL ranks' queries against the local shard and selects the
      shard's top-k' per query;
-  3. ONE all-gather of packed candidates ``[B_all, k', 3]`` (score bits, local id, global id)
+  3. ONE all-gather of the candidates ``[3, B_all, k']`` (scores, local ids, global ids as planes of one buffer)
      replaces the two all-to-alls of candidates and the all-to-all of requests: every rank
      merges its own queries and knows each winner's owner;
   4. the requester reads the winners' K/V straight from the pinned host bank (every rank of
@@ -52,17 +52,6 @@ def balanced_bucket_partition(docs: Sequence[Document], n_buckets: int) -> List[
         buckets[i].append(d)
         loads[i] += d.num_chunks
     return buckets
-
-
-def pack_candidates(scores: torch.Tensor, local_ids: torch.Tensor, global_ids: torch.Tensor) -> torch.Tensor:
-    """``[B, k', 3]`` int64: float32 score bits, local id, global id -- one buffer, one collective."""
-    bits = scores.contiguous().view(torch.int32).to(torch.int64)
-    return torch.stack([bits, local_ids, global_ids], dim=-1).contiguous()
-
-
-def unpack_candidates(packed: torch.Tensor):
-    scores = packed[..., 0].to(torch.int32).view(torch.float32)
-    return scores.contiguous(), packed[..., 1].contiguous(), packed[..., 2].contiguous()
 
 
 def all_gather_cat(t: torch.Tensor, world: int, group=None) -> torch.Tensor:
@@ -251,11 +240,17 @@ class MSAService(Memory, MemoryClientBase):
         qf, bias, s_pad, _ = self._gather_querys(query_states, query_mask, l2_normalize, all_valid)
         scale = self.scaling if self.scaling > 0 else 1.0
         n_all = self.world_size * b
-        sc, li, gi = self.score_folded(layer_idx, qf, bias, n_all, s_pad, hq, self.shard_top_k, scale=scale)
         if self.world_size > 1:
-            packed = all_gather_cat(pack_candidates(sc, li, gi), self.world_size, self.group)
-            sc, li, gi = unpack_candidates(packed)          # [W, B_all, k']
+            # the selection writes straight into one buffer (scores, local ids, global ids as planes), ONE
+            # all-gather moves it, and the merge reads the gathered planes in place
+            k_eff = min(self.shard_top_k, self.block_desc.nr_docs + 1)
+            cb = self.__dict__.get("_cand_buf")
+            if cb is None or tuple(cb[0].shape) != (3, n_all, k_eff):
+                cb = self._cand_buf = ops.candidate_buffer(n_all, k_eff, self.device)
+            self.score_folded(layer_idx, qf, bias, n_all, s_pad, hq, self.shard_top_k, scale=scale, out=cb[1:])
+            sc, li, gi = ops.candidate_views(all_gather_cat(cb[0], self.world_size, self.group))   # [W, B_all, k']
         else:
+            sc, li, gi = self.score_folded(layer_idx, qf, bias, n_all, s_pad, hq, self.shard_top_k, scale=scale)
             sc, li, gi = sc.unsqueeze(0), li.unsqueeze(0), gi.unsqueeze(0)
         return ops.topk_merge(sc, li, gi, self.model_config.doc_top_k, seq_offset=self.rank * b, n_seq=b)
 

@@ -54,25 +54,35 @@ def test_balanced_bucket_partition_and_directory():
     assert lens.tolist() == [0, 2, 3, 0, 5, 0] and offs.tolist() == [0, 0, 2, 0, 0, 0]
 
 
-def test_candidate_packing_roundtrip():
-    from msa_b200.service import pack_candidates, unpack_candidates
+def test_candidate_buffer_roundtrip():
+    """Scores and ids written into the planes of one buffer come back bit for bit from a stack of such buffers."""
+    from msa_b200 import ops
     s = torch.tensor([[0.5, -3.4e38, float("-inf")], [1e-9, -0.0, 7.0]])
     l = torch.tensor([[1, 2, 0], [9, 8, 7]])
-    g = l + 100
-    s2, l2, g2 = unpack_candidates(pack_candidates(s, l, g))
-    assert torch.equal(s2.view(torch.int32), s.view(torch.int32)) and torch.equal(l2, l) and torch.equal(g2, g)
+    bufs = []
+    for w in range(3):
+        buf, sv, lv, gv = ops.candidate_buffer(2, 3, "cpu")
+        sv.copy_(s + w); lv.copy_(l + w); gv.copy_(l + 100 + w)
+        bufs.append(buf)
+    s2, l2, g2 = ops.candidate_views(torch.stack(bufs))
+    for w in range(3):
+        assert torch.equal(s2[w].contiguous().view(torch.int32), (s + w).view(torch.int32))
+        assert torch.equal(l2[w], l + w) and torch.equal(g2[w], l + 100 + w)
+    assert s2.stride(2) == 1 and s2.stride(1) == 3 and l2.stride(1) == 3     # what the merge kernel requires
 
 
 def _rank(rank, world, port, ret):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    from msa_b200.service import all_gather_cat, build_directory, pack_candidates, unpack_candidates
+    from msa_b200 import ops
+    from msa_b200.service import all_gather_cat, build_directory
     b, k = 3, 4
     # every rank scored ALL world*b queries against its shard; candidates are gathered to [W, B_all, k]
     scores = torch.arange(world * b * k, dtype=torch.float32).view(world * b, k) + 1000 * rank
     local = torch.full((world * b, k), rank + 1)
-    packed = all_gather_cat(pack_candidates(scores, local, local + 10), world)
-    s, l, g = unpack_candidates(packed)
+    buf, sv, lv, gv = ops.candidate_buffer(world * b, k, "cpu")
+    sv.copy_(scores); lv.copy_(local); gv.copy_(local + 10)
+    s, l, g = ops.candidate_views(all_gather_cat(buf, world))
     lens = [None] * world
     dist.all_gather_object(lens, [0] + [rank + 1] * (rank + 2))
     base, offs, ln = build_directory(lens)

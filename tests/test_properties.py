@@ -3,7 +3,8 @@ import torch
 from hypothesis import given, settings, strategies as st
 
 from msa_b200.memory import Document
-from msa_b200.service import balanced_bucket_partition, build_directory, pack_candidates, unpack_candidates
+from msa_b200 import ops
+from msa_b200.service import balanced_bucket_partition, build_directory
 from oracle import msa_oracle as O
 
 doc_lens = st.lists(st.integers(min_value=1, max_value=40), min_size=1, max_size=30)
@@ -50,8 +51,12 @@ def test_oracle_bookkeeping_matches_a_plain_loop(lens, p):
 
 @settings(max_examples=40, deadline=None)
 @given(st.lists(st.floats(width=32, allow_nan=False), min_size=1, max_size=12))
-def test_candidate_packing_is_lossless(vals):
+def test_candidate_buffer_is_lossless(vals):
     s = torch.tensor([vals], dtype=torch.float32)
     l = torch.arange(len(vals)).view(1, -1)
-    s2, l2, g2 = unpack_candidates(pack_candidates(s, l, l + 7))
-    assert torch.equal(s2.view(torch.int32), s.view(torch.int32)) and torch.equal(l2, l) and torch.equal(g2, l + 7)
+    buf, sv, lv, gv = ops.candidate_buffer(1, len(vals), "cpu")
+    sv.copy_(s); lv.copy_(l); gv.copy_(l + 7)
+    s2, l2, g2 = ops.candidate_views(torch.stack([buf, buf.clone()]))
+    for w in range(2):
+        assert torch.equal(s2[w].contiguous().view(torch.int32), s.view(torch.int32))
+        assert torch.equal(l2[w], l) and torch.equal(g2[w], l + 7)
