@@ -875,6 +875,7 @@ def run_generate(args):
                       "loop": "rotated to start at the first router layer: layers 18-35 of step t, sampling, layers 0-17 "
                               "of step t+1; the fetch issued in step t is needed by layer 18 of step t+1",
                       "exposed_ms_per_step": max(0.0, (ms_total - ms_nofetch) / new_tokens),
+                      "note": "the run without the fetch is a diagnostic; on 8 GPUs it has measured slower than the run with it",
                       "pcie_bytes_per_step_per_gpu": 18 * b * TOP_K * CHUNKS_PER_DOC * 2 * HKV * D * 2},
             "dense_weight_bytes_per_step": per_step_bytes, "clocks": clocks,
             # this package's kernels per step: per layer add+norm x2, q/k norm+rope, decode attention (+ combine),
