@@ -22,8 +22,6 @@ The training forward (``_forward``) is out of scope and raises.
 """
 from __future__ import annotations
 
-from typing import Optional, Tuple
-
 import torch
 import torch.nn as nn
 import torch.nn.functional as F

@@ -6,7 +6,7 @@ reference's ``Memory``, ``MSAService`` and ``MemorySparseAttention``) are built 
 from __future__ import annotations
 
 import math
-from typing import Optional, Tuple
+from typing import Optional
 
 import torch
 

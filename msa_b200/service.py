@@ -18,7 +18,7 @@ layer, :1105-1283):
 from __future__ import annotations
 
 import os
-from typing import List, Optional, Sequence, Tuple
+from typing import List, Optional, Sequence
 
 import torch
 import torch.distributed as dist

@@ -24,7 +24,7 @@ function below against those files.
 from __future__ import annotations
 
 import math
-from typing import List, Optional, Sequence, Tuple
+from typing import List, Optional, Sequence
 
 import torch
 import torch.nn.functional as F

@@ -1,7 +1,6 @@
 """The config-5 decode loop (msa_b200.decoder.SparseDecodeModel) against a plain PyTorch fp32
 restatement of the same step built on the oracle's decode attention: same random weights, same
 synthetic caches, two steps, no routing service (router layers are covered by the service tests)."""
-import math
 
 import pytest
 import torch

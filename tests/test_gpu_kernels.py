@@ -3,7 +3,6 @@
 Tolerances: pooling and attention 1e-5 (fp32) / 1e-2 (bf16) norm-wise
 relative error, routing scores 1e-3 absolute, top-k exact outside a 1e-3 score gap.
 """
-import math
 
 import pytest
 import torch
@@ -246,7 +245,6 @@ def test_topk_select_exact_with_ties(ops, n_cols, k):
     scores[3, ::3] = torch.finfo(torch.float32).min     # untouched documents
     scores[4] = scores[4].abs() * -1.0
     scores[5, : min(5, n_cols)] = float("-inf")
-    from msa_b200 import ops as _o
     keys = _float_to_keys(scores).to(DEV)
     s, li, gi = ops.topk_select(keys, k)
     k_eff = min(k, n_cols)

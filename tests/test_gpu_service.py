@@ -8,7 +8,7 @@ import pytest
 import torch
 
 from oracle import msa_oracle as O
-from tests.util import T, check_topk, make_bank, ragged_docs, rel_err
+from tests.util import T, make_bank, ragged_docs
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"

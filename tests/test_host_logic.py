@@ -1,6 +1,5 @@
 """Host-side logic that needs no GPU: ABI surface, partitioning, directory, candidate packing,
 and the all-gather layouts of the Memory-Parallel exchange on 2 gloo ranks."""
-import ctypes
 import os
 import re
 

@@ -11,7 +11,6 @@ point, plus the rejection of a problem too large for the built-in array.
 This file is collected last on purpose: a run that stops at the first failure has then
 already run every other test.
 """
-import ctypes
 import math
 
 import pytest
