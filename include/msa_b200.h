@@ -13,6 +13,10 @@
  *     message for the calling thread.  Argument errors are detected before any launch.
  *   - Kernels that wait on hardware barriers bound every wait; a wait that runs out sets
  *     a non-zero word in the caller's `status` buffer instead of hanging.
+ *   - `status` buffers are device int32[4]: word 0 = code of a barrier wait that ran out (0 = none),
+ *     word 1 = used by msa_selftest_bounded_wait, word 2 = number of indices a kernel found outside
+ *     their table and skipped (chunk -> document ids in routing, winners in msa_gather_plan),
+ *     word 3 = reserved.  Nothing is read or written through an index that failed its check.
  *
  * Reference interfaces are cited by path inside the EverMind-AI/MSA repository.
  */
@@ -25,7 +29,7 @@
 extern "C" {
 #endif
 
-#define MSA_ABI_VERSION 1
+#define MSA_ABI_VERSION 2
 
 enum msa_status {
   MSA_OK = 0,
@@ -39,6 +43,10 @@ enum msa_dtype { MSA_F32 = 0, MSA_BF16 = 1 };
 
 /* query_reduce_method of the reference (src/msa_service.py:749-780) */
 enum msa_query_reduce { MSA_QREDUCE_MAX = 0, MSA_QREDUCE_MEAN = 1, MSA_QREDUCE_LAST = 2 };
+
+/* head_reduce_method / chunk_reduce_method of the reference (src/msa_service.py:740-745, 787-812) */
+enum msa_head_reduce { MSA_HREDUCE_MEAN = 0, MSA_HREDUCE_MAX = 1 };
+enum msa_chunk_reduce { MSA_CREDUCE_MAX = 0, MSA_CREDUCE_MEAN = 1 };
 
 /* flags of msa_route_scores */
 #define MSA_ROUTE_FORCE_SIMT 1u /* use the CUDA-core kernel even for bf16 (cross-checks) */
@@ -124,7 +132,8 @@ int32_t msa_route_s_pad(int32_t seq_len, int32_t query_reduce);
  * q_folded / row_bias: output of msa_fold_queries (n_seq sequences of s_pad rows).
  * rk: device pooled router keys, chunk c at rk + c*rk_chunk_stride, kdim contiguous elements.
  * chunk_doc: device int32 [n_chunks], 1-based local doc id of each chunk (the reference's
- * BlockDesc.pool_ids, src/msa_service.py:196-198), non-decreasing.
+ * BlockDesc.pool_ids, src/msa_service.py:196-198), non-decreasing.  An id outside 1..n_docs is never
+ * used as a column: the chunk is skipped and counted in status[2].
  * score_keys: device uint32 [n_seq, table_stride]; column d (0..n_docs) receives the
  * order-preserving key of max(min_val, alpha * max_tokens max_chunks dot).  Column 0 is the
  * reference's dummy document (src/msa_service.py:716-717).  Decode with msa_topk_select.
@@ -137,6 +146,34 @@ int msa_route_scores(const void* q_folded, const float* row_bias, int32_t dtype,
                      int32_t kdim, const int32_t* chunk_doc, float alpha, uint32_t* score_keys,
                      int64_t table_stride, int32_t n_docs, float min_val, uint32_t flags,
                      int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Routing in the other reduce modes of Memory.prefill_stage2 (src/msa_service.py:740-745 head_reduce
+ * "max", :794-812 chunk_reduce "mean").  Both go through a per-(sequence, chunk) table of keys,
+ * chunk_keys uint32 [n_seq, chunk_table_stride] with chunk c in column c + 1 (column 0 unused):
+ *
+ *   - head "mean": fill it with msa_route_scores, passing chunk_doc[c] = c + 1 and n_docs = n_chunks
+ *     (every chunk its own document), i.e. on the tensor-core kernel for bf16;
+ *   - head "max": msa_route_chunk_scores computes, per (sequence, chunk), the query_reduce over the valid
+ *     tokens of the max (or mean) over all n_q_heads of q[b, head, s, :] . rk[chunk, head / n_groups, :], times
+ *     `scale`, on CUDA cores.  q is the UNFOLDED query [B, Hq, S, D] by strides; rk chunk major as in
+ *     msa_route_scores.  Writes max(min_val, score) as keys, every (sequence, chunk) exactly once;
+ *   - msa_route_reduce_chunks then reduces the chunks of every document (runs of equal ids in chunk_doc) with
+ *     max or mean into score_keys [n_seq, table_stride] (atomicMax: reset it first with
+ *     msa_route_table_reset).  With "mean" a document must lie wholly inside one call.  Ids outside 1..n_docs
+ *     are skipped and counted in status[2] (status may be NULL).
+ */
+int msa_route_chunk_scores(const void* q, int32_t dtype, int64_t stride_b, int64_t stride_h, int64_t stride_s,
+                           const uint8_t* query_mask, int64_t mask_stride_b, int32_t n_seq, int32_t n_q_heads,
+                           int32_t n_groups, int32_t seq_len, int32_t head_dim, int32_t head_reduce,
+                           int32_t query_reduce, const void* rk, int64_t rk_chunk_stride, int32_t n_chunks,
+                           float scale, float min_val, uint32_t* chunk_keys, int64_t chunk_table_stride,
+                           void* stream);
+
+int msa_route_reduce_chunks(const uint32_t* chunk_keys, int64_t chunk_table_stride, int32_t n_seq,
+                            int32_t n_chunks, const int32_t* chunk_doc, int32_t n_docs, int32_t chunk_reduce,
+                            float min_val, uint32_t* score_keys, int64_t table_stride, int32_t* status,
+                            void* stream);
 
 /* Failure-path self-test: launches one CTA that waits, with the routing kernel's bounded-wait
  * routine and the given limit (<= 1 s), on a barrier that nothing completes.  After the stream
@@ -153,7 +190,10 @@ int msa_route_table_reset(uint32_t* score_keys, int64_t table_stride, int32_t n_
                           float min_val, int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------------------------------
- * Routing, step 3: exact per-shard top-k (two levels of a shared-memory bitonic sort).
+ * Routing, step 3: exact per-shard top-k in two levels: every CTA keeps the best k of one
+ * 2048-column slice of a row, a second launch reduces the survivors.  k <= 32: threshold at the
+ * k-th largest lane maximum, compaction, ranks by counting; k <= 64: rounds of a warp arg-max;
+ * larger k: a shared-memory bitonic sort.
  * Replaces torch.topk + create_global_doc_ids (src/msa_service.py:826-828).
  * Selects k_eff = min(k, n_cols) columns per row, sorted by descending score; equal scores
  * are ordered by ascending column.  out_* are [n_seq, k_eff].  doc_ids_table (nullable) is the
@@ -197,10 +237,22 @@ int msa_topk_merge(const float* cand_scores, const int64_t* cand_local, const in
  *
  * msa_gather_plan: orders each sample's valid winners by (owner rank, local id), as the
  * reference's exchange does, and computes where their chunks go.  plan is device int64
- * [n_seq*k, 4] = (source address, chunks, destination entry, unused); n_sel device int64
+ * [n_seq*k, 4] = (source address, chunks, destination entry, sample); n_sel device int64
  * [n_seq]; total device int64 [1] (also written to *total_host_mapped when non-NULL).
- * msa_gather_run: copies every planned document into out_k / out_v, device
- * [Hkv, out_entries, D] (entry stride = D, head stride = out_head_stride elements).
+ * n_dir_rows = number of rows of doc_chunk_offset / doc_chunk_len; shard w owns rows
+ * shard_doc_base[w] .. shard_doc_base[w+1]-1 (the last shard up to n_dir_rows-1).  A winner whose
+ * owner rank is not in 0..world-1 or whose local id is not a row of its shard is dropped and counted
+ * in status[2] (status may be NULL); local ids <= 0 (dummy document, invalidated winner) select nothing.
+ * sample_stride == 0: samples are packed one after another (destination entry counts from the start of
+ * the output).  sample_stride > 0: destination entries count from the start of the SAMPLE and a sample
+ * takes at most sample_stride entries (documents beyond that are cut); pass the same layout to
+ * msa_gather_run through out_sample_stride.
+ * msa_gather_run: copies every planned document into out_k / out_v.  Packed (out_sample_stride == 0):
+ * device [Hkv, out_entries, D] (entry stride = D, head stride = out_head_stride elements).  Per sample
+ * (out_sample_stride > 0, in elements): entry e of sample b, head h goes to
+ * out + b*out_sample_stride + h*out_head_stride + e*D and out_entries is the room of ONE sample, so the
+ * gather can write straight into the retrieved segment of a [B, Hkv, L, D] cache.  Entries that have no
+ * room are not read.
  * max_ctas: 0 = one CTA per document (fastest next to compute-bound kernels: 35 GB/s under the
  * prefill routing kernel); a small cap (24 measured best) when the fetch runs beside kernels that
  * saturate HBM, as in a decode step: the link is full from about a dozen CTAs, and reads queued
@@ -213,14 +265,15 @@ int msa_bank_register_host(void* host_ptr, int64_t bytes, uint64_t* device_addre
 int msa_bank_unregister_host(void* host_ptr);
 
 int msa_gather_plan(const int64_t* sel_local, const int32_t* sel_rank, int32_t n_seq, int32_t k,
-                    int32_t world, const int64_t* shard_doc_base, const int64_t* doc_chunk_offset,
-                    const int32_t* doc_chunk_len, const uint64_t* shard_kv_base,
-                    int64_t chunk_bytes, int64_t* plan, int64_t* n_sel, int64_t* total,
-                    int64_t* total_host_mapped, void* stream);
+                    int32_t world, const int64_t* shard_doc_base, int64_t n_dir_rows,
+                    const int64_t* doc_chunk_offset, const int32_t* doc_chunk_len,
+                    const uint64_t* shard_kv_base, int64_t chunk_bytes, int64_t sample_stride,
+                    int64_t* plan, int64_t* n_sel, int64_t* total, int64_t* total_host_mapped,
+                    int32_t* status, void* stream);
 
 int msa_gather_run(const int64_t* plan, int32_t n_items, int32_t dtype, int32_t n_kv_heads,
                    int32_t head_dim, void* out_k, void* out_v, int64_t out_head_stride,
-                   int64_t out_entries, int32_t max_ctas, void* stream);
+                   int64_t out_entries, int64_t out_sample_stride, int32_t max_ctas, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Decode attention over the sparse context (split-KV flash-decode, GQA).

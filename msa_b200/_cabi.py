@@ -16,11 +16,13 @@ LIB_PATH = os.path.join(_HERE, "libmsa_b200.so")
 
 MSA_F32, MSA_BF16 = 0, 1
 QREDUCE = {"max": 0, "mean": 1, "last": 2}
+HREDUCE = {"mean": 0, "max": 1}
+CREDUCE = {"max": 0, "mean": 1}
 ROUTE_FORCE_SIMT, ROUTE_NO_INIT = 1, 2
 
 EXPORTS = [
     "msa_abi_version", "msa_last_error", "msa_bookkeeping_workspace_bytes", "msa_chunk_bookkeeping", "msa_pool_chunks", "msa_fold_queries",
-    "msa_route_s_pad", "msa_selftest_bounded_wait", "msa_route_table_reset", "msa_route_scores", "msa_topk_workspace_bytes", "msa_topk_select", "msa_topk_merge", "msa_gather_plan",
+    "msa_route_s_pad", "msa_selftest_bounded_wait", "msa_route_table_reset", "msa_route_scores", "msa_route_chunk_scores", "msa_route_reduce_chunks", "msa_topk_workspace_bytes", "msa_topk_select", "msa_topk_merge", "msa_gather_plan",
     "msa_gather_run", "msa_bank_register_host", "msa_bank_unregister_host", "msa_assemble_context", "msa_sparse_prefill_attn", "msa_doc_attention_pool", "msa_doc_attention_tc", "msa_qk_norm_rope", "msa_add_rmsnorm", "msa_silu_mul", "msa_decode_workspace_bytes", "msa_sparse_decode_attn",
     "msa_decode_static_scratch_bytes", "msa_sparse_decode_attn_static",
 ]
@@ -52,14 +54,17 @@ def lib() -> C.CDLL:
         l.msa_route_s_pad.argtypes = [i32, i32]
         l.msa_route_s_pad.restype = i32
         l.msa_route_scores.argtypes = [vp, vp, i32, i32, i32, vp, i64, i32, i32, vp, f32, vp, i64, i32, f32, u32, vp, vp]
+        l.msa_route_chunk_scores.argtypes = [vp, i32, i64, i64, i64, vp, i64, i32, i32, i32, i32, i32, i32, i32, vp, i64, i32,
+                                             f32, f32, vp, i64, vp]
+        l.msa_route_reduce_chunks.argtypes = [vp, i64, i32, i32, vp, i32, i32, f32, vp, i64, vp, vp]
         l.msa_selftest_bounded_wait.argtypes = [i64, vp, vp]
         l.msa_route_table_reset.argtypes = [vp, i64, i32, i32, f32, vp, vp]
         l.msa_topk_workspace_bytes.argtypes = [i32, i32, i32]
         l.msa_topk_workspace_bytes.restype = i64
         l.msa_topk_select.argtypes = [vp, i64, i32, i32, i32, vp, vp, vp, vp, vp, i64, vp]
         l.msa_topk_merge.argtypes = [vp, vp, vp, i64, i64, i32, i32, i32, i32, f32, vp, vp, vp, vp, vp]
-        l.msa_gather_plan.argtypes = [vp, vp, i32, i32, i32, vp, vp, vp, vp, i64, vp, vp, vp, vp, vp]
-        l.msa_gather_run.argtypes = [vp, i32, i32, i32, i32, vp, vp, i64, i64, i32, vp]
+        l.msa_gather_plan.argtypes = [vp, vp, i32, i32, i32, vp, i64, vp, vp, vp, i64, i64, vp, vp, vp, vp, vp, vp]
+        l.msa_gather_run.argtypes = [vp, i32, i32, i32, i32, vp, vp, i64, i64, i64, i32, vp]
         l.msa_bank_register_host.argtypes = [vp, i64, vp]
         l.msa_bank_unregister_host.argtypes = [vp]
         l.msa_decode_workspace_bytes.argtypes = [i32, i32, i32, i32]

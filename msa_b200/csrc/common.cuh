@@ -42,6 +42,33 @@ void set_error(const char* fmt, ...);
     }                                                                                  \
   } while (0)
 
+// Per-device launch state.  The opt-in dynamic shared-memory size of a kernel and the SM count are
+// properties of a (kernel, device) pair, not of the calling thread: a host thread that drives a second
+// GPU has to set them there too.  Every launcher keeps one DeviceSmem per kernel, indexed by the
+// current device's ordinal.
+constexpr int kMaxDevices = 64;
+struct DeviceSmem { size_t enabled[kMaxDevices]; };
+
+int current_device(int* dev);   // cudaGetDevice + range check (ordinal < kMaxDevices)
+int device_sm_count(int* n_sm); // SM count of the current device (cached per device)
+
+template <typename Kernel>
+inline int ensure_dynamic_smem(Kernel kernel, size_t bytes, DeviceSmem& state) {
+  int dev = 0;
+  const int rc = current_device(&dev);
+  if (rc != MSA_OK) return rc;
+  if (bytes > state.enabled[dev]) {
+    MSA_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    state.enabled[dev] = bytes;
+  }
+  return MSA_OK;
+}
+#define MSA_OK_OR_RETURN(expr)        \
+  do {                                \
+    const int rc__ = (expr);          \
+    if (rc__ != MSA_OK) return rc__;  \
+  } while (0)
+
 inline size_t dtype_size(int32_t dtype) { return dtype == MSA_BF16 ? 2 : 4; }
 inline bool dtype_ok(int32_t dtype) { return dtype == MSA_F32 || dtype == MSA_BF16; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

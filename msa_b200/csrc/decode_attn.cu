@@ -213,11 +213,8 @@ int launch_decode(const void* q, void* k_cache, void* v_cache, int64_t stride_b,
   const size_t smem = (size_t)KT * (head_dim + V) * sizeof(T) + (size_t)KT * head_dim * sizeof(T) +
                       ((size_t)G * head_dim + (size_t)G * KT + 3 * G) * sizeof(float);
   MSA_REQUIRE(smem <= 200 * 1024, "decode: head_dim/group size need %zu bytes of shared memory", smem);
-  static thread_local size_t configured = 0;
-  if (smem > 48 * 1024 && smem > configured) {
-    MSA_CUDA_OK(cudaFuncSetAttribute(decode_split_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = smem;
-  }
+  static DeviceSmem configured{};
+  if (smem > 48 * 1024) MSA_OK_OR_RETURN(ensure_dynamic_smem(decode_split_kernel<T>, smem, configured));
   const float scale_log2e = scale * 1.4426950408889634f;
   decode_split_kernel<T><<<dim3(n_splits, n_kv_heads, n_seq), kDecThreads, smem, stream>>>(
       (const T*)q, (const T*)k_cache, (const T*)v_cache, stride_b, stride_h, kv_start, kv_len, (const T*)new_k,
@@ -243,11 +240,8 @@ int launch_decode_mma(const void* q, void* k_cache, void* v_cache, int64_t strid
         n_kv_heads, kMmaD);
     MSA_LAUNCH_OK("append_kv_kernel");
   }
-  static thread_local bool configured = false;
-  if (!configured) {
-    MSA_CUDA_OK(cudaFuncSetAttribute(decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMmaSmemBytes));
-    configured = true;
-  }
+  static DeviceSmem configured{};
+  MSA_OK_OR_RETURN(ensure_dynamic_smem(decode_mma_kernel, kMmaSmemBytes, configured));
   decode_mma_kernel<<<dim3(n_splits, n_kv_heads, n_seq), kMmaWarps * 32, kMmaSmemBytes, stream>>>(
       (const T*)q, (const T*)k_cache, (const T*)v_cache, stride_b, stride_h, kv_start, kv_len, (const T*)new_k,
       (const T*)new_v, n_q_heads, n_kv_heads, scale * 1.4426950408889634f, (T*)out, (float*)workspace, n_splits);
@@ -315,7 +309,6 @@ extern "C" int msa_sparse_decode_attn(const void* q, int32_t dtype, void* k_cach
 namespace msa {
 constexpr long long kStaticScratchFloats = 2ll * 1024 * 1024;  // 8 MiB
 static __device__ __align__(256) float g_decode_scratch[kStaticScratchFloats];
-constexpr int kMaxDevices = 64;
 static float* g_scratch_addr[kMaxDevices] = {nullptr};
 }  // namespace msa
 
@@ -333,8 +326,7 @@ extern "C" int msa_sparse_decode_attn_static(const void* q, int32_t dtype, void*
               "%lld-byte scratch; use fewer splits or msa_sparse_decode_attn with your own workspace",
               (long long)need, (long long)msa_decode_static_scratch_bytes());
   int dev = -1;
-  MSA_CUDA_OK(cudaGetDevice(&dev));
-  MSA_REQUIRE(dev >= 0 && dev < kMaxDevices, "decode (static scratch): device ordinal %d out of range", dev);
+  MSA_OK_OR_RETURN(current_device(&dev));
   if (g_scratch_addr[dev] == nullptr) {
     // First call on this device: resolve the array's address on the CURRENT device.  The symbol
     // name is only a host-side handle; the kernel must be given the address obtained here.

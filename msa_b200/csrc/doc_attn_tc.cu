@@ -460,20 +460,13 @@ extern "C" int msa_doc_attention_tc(const void* q, int64_t q_stride_b, int64_t q
   p.out = (__nv_bfloat16*)out;
   p.status = status;
 
-  static thread_local bool configured = false;
-  if (!configured) {
-    MSA_CUDA_OK(cudaFuncSetAttribute(doc_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAtSmem));
-    configured = true;
-  }
+  static DeviceSmem configured{};
+  MSA_OK_OR_RETURN(ensure_dynamic_smem(doc_attn_tc_kernel, kAtSmem, configured));
   p.max_mb = (max_segment_len + kAtRows - 1) / kAtRows;
   p.n_sh = (long long)n_segments * n_q_heads;
   p.n_items = p.n_sh * p.max_mb;
-  static thread_local int n_sm = 0;
-  if (n_sm == 0) {
-    int dev = 0;
-    MSA_CUDA_OK(cudaGetDevice(&dev));
-    MSA_CUDA_OK(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
-  }
+  int n_sm = 0;
+  MSA_OK_OR_RETURN(device_sm_count(&n_sm));
   const long long grid = p.n_items < 2ll * n_sm ? p.n_items : 2ll * n_sm;   // persistent: two CTAs per SM
   doc_attn_tc_kernel<<<(unsigned)grid, kAtThreads, kAtSmem, (cudaStream_t)stream>>>(map_q, map_k, map_v, p);
   MSA_LAUNCH_OK("doc_attn_tc_kernel");

@@ -510,11 +510,8 @@ extern "C" int msa_sparse_prefill_attn(const void* q, int64_t q_stride_b, int64_
                   store_stride_h % 8 == 0 && aligned16(q) && aligned16(k_store) && aligned16(v_store) && aligned16(out),
               "prefill: rows must be 16-byte aligned");
   if (n_seq == 0 || seq_len == 0) return MSA_OK;
-  static thread_local bool configured = false;
-  if (!configured) {
-    MSA_CUDA_OK(cudaFuncSetAttribute(prefill_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
-    configured = true;
-  }
+  static DeviceSmem configured{};
+  MSA_OK_OR_RETURN(ensure_dynamic_smem(prefill_attn_kernel, kPfSmem, configured));
   dim3 grid((seq_len + kPfRows - 1) / kPfRows, n_q_heads, n_seq);
   prefill_attn_kernel<<<grid, 128, kPfSmem, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)q, q_stride_b, q_stride_h, q_stride_s, (const __nv_bfloat16*)k_store,
@@ -547,11 +544,8 @@ extern "C" int msa_doc_attention_pool(const void* q, int64_t q_stride_b, int64_t
                 pool_size, kPfKeys);
   }
   if (n_segments == 0 || max_segment_len == 0) return MSA_OK;
-  static thread_local bool configured = false;
-  if (!configured) {
-    MSA_CUDA_OK(cudaFuncSetAttribute(doc_attn_pool_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
-    configured = true;
-  }
+  static DeviceSmem configured{};
+  MSA_OK_OR_RETURN(ensure_dynamic_smem(doc_attn_pool_kernel, kPfSmem, configured));
   // tok / seq_len for tok < 2^31: (mulhi(tok, mul) + tok) >> shift with shift = ceil(log2 seq_len)
   uint32_t div_shift = 0;
   while ((1ull << div_shift) < (uint64_t)seq_len) ++div_shift;

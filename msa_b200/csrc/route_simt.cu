@@ -109,8 +109,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 route_simt_kernel(const T* __restrict__ qf, const float* __restrict__ row_bias, int n_rows, int s_pad,
                   const T* __restrict__ rk, long long rk_stride, int n_chunks, int kdim,
-                  const int32_t* __restrict__ chunk_doc, float alpha, uint32_t* __restrict__ keys,
-                  long long table_stride) {
+                  const int32_t* __restrict__ chunk_doc, int n_docs, float alpha, uint32_t* __restrict__ keys,
+                  long long table_stride, int32_t* __restrict__ status) {
   __shared__ float s_a[kStepK][kTile + 4];  // chunks
   __shared__ float s_b[kStepK][kTile + 4];  // query rows
   __shared__ float s_c[kTile][kTile + 1];   // [row][chunk]
@@ -166,32 +166,37 @@ route_simt_kernel(const T* __restrict__ qf, const float* __restrict__ row_bias, 
     const int ra = max(sq * s_pad, r0) - r0, rb = min((sq + 1) * s_pad, r0 + rows_here) - r0;
     float m = -INFINITY;
     for (int r = ra; r < rb; ++r) m = fmaxf(m, s_c[r][cc]);
-    atomicMax(keys + (long long)sq * table_stride + chunk_doc[c0 + cc], float_to_key(m * alpha));
+    const int doc = chunk_doc[c0 + cc];
+    if (doc < 1 || doc > n_docs) {   // an id outside the table: counted, never used as a column
+      atomicAdd(status + 2, 1);
+      continue;
+    }
+    atomicMax(keys + (long long)sq * table_stride + doc, float_to_key(m * alpha));
   }
 }
 
 template <typename T>
 int launch_route_simt_t(const void* qf, const float* row_bias, int n_seq, int s_pad, const void* rk,
-                        int64_t rk_stride, int n_chunks, int kdim, const int32_t* chunk_doc, float alpha,
-                        uint32_t* keys, int64_t table_stride, cudaStream_t stream) {
+                        int64_t rk_stride, int n_chunks, int kdim, const int32_t* chunk_doc, int n_docs, float alpha,
+                        uint32_t* keys, int64_t table_stride, int32_t* status, cudaStream_t stream) {
   const int n_rows = n_seq * s_pad;
   if (n_rows == 0 || n_chunks == 0) return MSA_OK;
   dim3 grid((n_chunks + kTile - 1) / kTile, (n_rows + kTile - 1) / kTile);
   MSA_REQUIRE(grid.y <= 65535, "route (CUDA-core path): too many query rows (%d)", n_rows);
   route_simt_kernel<T><<<grid, 256, 0, stream>>>((const T*)qf, row_bias, n_rows, s_pad, (const T*)rk, rk_stride,
-                                                 n_chunks, kdim, chunk_doc, alpha, keys, table_stride);
+                                                 n_chunks, kdim, chunk_doc, n_docs, alpha, keys, table_stride, status);
   MSA_LAUNCH_OK("route_simt_kernel");
   return MSA_OK;
 }
 
 int launch_route_simt(int32_t dtype, const void* qf, const float* row_bias, int n_seq, int s_pad, const void* rk,
-                      int64_t rk_stride, int n_chunks, int kdim, const int32_t* chunk_doc, float alpha,
-                      uint32_t* keys, int64_t table_stride, cudaStream_t stream) {
+                      int64_t rk_stride, int n_chunks, int kdim, const int32_t* chunk_doc, int n_docs, float alpha,
+                      uint32_t* keys, int64_t table_stride, int32_t* status, cudaStream_t stream) {
   return dtype == MSA_BF16
              ? launch_route_simt_t<__nv_bfloat16>(qf, row_bias, n_seq, s_pad, rk, rk_stride, n_chunks, kdim,
-                                                  chunk_doc, alpha, keys, table_stride, stream)
+                                                  chunk_doc, n_docs, alpha, keys, table_stride, status, stream)
              : launch_route_simt_t<float>(qf, row_bias, n_seq, s_pad, rk, rk_stride, n_chunks, kdim, chunk_doc,
-                                          alpha, keys, table_stride, stream);
+                                          n_docs, alpha, keys, table_stride, status, stream);
 }
 
 }  // namespace msa
@@ -272,8 +277,8 @@ extern "C" int msa_route_scores(const void* q_folded, const float* row_bias, int
   }
   if (n_seq == 0 || n_chunks == 0) return MSA_OK;
   if (dtype == MSA_BF16 && !(flags & MSA_ROUTE_FORCE_SIMT))
-    return launch_route_tc(q_folded, row_bias, n_seq, s_pad, rk, rk_chunk_stride, n_chunks, kdim, chunk_doc, alpha,
-                           min_val, score_keys, table_stride, status, st);
+    return launch_route_tc(q_folded, row_bias, n_seq, s_pad, rk, rk_chunk_stride, n_chunks, kdim, chunk_doc, n_docs,
+                           alpha, min_val, score_keys, table_stride, status, st);
   return launch_route_simt(dtype, q_folded, row_bias, n_seq, s_pad, rk, rk_chunk_stride, n_chunks, kdim, chunk_doc,
-                           alpha, score_keys, table_stride, st);
+                           n_docs, alpha, score_keys, table_stride, status, st);
 }

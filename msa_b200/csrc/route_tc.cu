@@ -7,9 +7,11 @@
 // axis (TMEM columns): after tcgen05.ld each epilogue thread owns one chunk and sees all
 // query rows of the tile in its registers, so
 //     max over a sequence's tokens   = an in-thread max over columns  (no shuffles),
-//     max over a document's chunks   = one redux.sync over the lanes of that document,
-//     table update                   = one atomicMax on an order-preserving key per
-//                                      (sequence, document, warp).
+//     max over a document's chunks   = a shuffle scan over the lanes that hold that document (batched
+//                                      over 16 columns; with one row per sequence: a shared-memory
+//                                      transpose that deals (document, column) pairs over the lanes),
+//     table update                   = a plain store for documents no other warp touches, else one
+//                                      atomicMax on an order-preserving key per (sequence, document, warp).
 // Per-(token, chunk) scores therefore never leave the SM.
 //
 // Persistent, warp specialised: warps 0-3 epilogue (TMEM lane quarter = warp id), warp 4
@@ -41,7 +43,7 @@ constexpr int kMaxStages = 8;
 constexpr int kTmemCols = 512;
 
 struct RouteTcParams {
-  int n_rows, n_seq, s_pad, bn, n_chunks, n_ctiles, n_qtiles, qgroup, k_blocks, stages;
+  int n_rows, n_seq, s_pad, bn, n_chunks, n_docs, n_ctiles, n_qtiles, qgroup, k_blocks, stages;
   uint32_t min_key;
   float alpha;
   const float* row_bias;
@@ -74,7 +76,11 @@ struct EpiScratch {                                      // per epilogue warp
 };
 
 __device__ __forceinline__ SegInfo seg_info(const RouteTcParams& p, int chunk, int lane, EpiScratch& scr) {
-  const int doc = chunk < p.n_chunks ? p.chunk_doc[chunk] : -1 - lane;  // out-of-range lanes stay alone
+  int doc = chunk < p.n_chunks ? p.chunk_doc[chunk] : -1 - lane;  // out-of-range lanes stay alone
+  if (chunk < p.n_chunks && (doc < 1 || doc > p.n_docs)) {  // an id outside the table: counted, never used as a column
+    atomicAdd(p.status + 2, 1);
+    doc = -1 - lane;
+  }
   const int doc_up = __shfl_up_sync(0xffffffffu, doc, 1), doc_dn = __shfl_down_sync(0xffffffffu, doc, 1);
   const bool head = lane == 0 || doc_up != doc, tail = lane == 31 || doc_dn != doc;
   const uint32_t heads = __ballot_sync(0xffffffffu, head);
@@ -499,13 +505,13 @@ __global__ void wait_selftest_kernel(unsigned long long limit_ns, int32_t* statu
 
 // ---- host side ------------------------------------------------------------------------
 int launch_route_tc(const void* qf, const float* row_bias, int n_seq, int s_pad, const void* rk, int64_t rk_stride,
-                    int n_chunks, int kdim, const int32_t* chunk_doc, float alpha, float min_val, uint32_t* keys,
-                    int64_t table_stride, int32_t* status, cudaStream_t stream) {
+                    int n_chunks, int kdim, const int32_t* chunk_doc, int n_docs, float alpha, float min_val,
+                    uint32_t* keys, int64_t table_stride, int32_t* status, cudaStream_t stream) {
   MSA_REQUIRE(kdim % kBK == 0, "route (tensor-core path): kdim=%d must be a multiple of %d", kdim, kBK);
   MSA_REQUIRE(aligned16(qf) && aligned16(rk) && rk_stride % 8 == 0 && rk_stride >= kdim,
               "route (tensor-core path): rows must be 16-byte aligned");
   RouteTcParams p{};
-  p.n_seq = n_seq; p.s_pad = s_pad; p.n_rows = n_seq * s_pad; p.n_chunks = n_chunks;
+  p.n_seq = n_seq; p.s_pad = s_pad; p.n_rows = n_seq * s_pad; p.n_chunks = n_chunks; p.n_docs = n_docs;
   if (s_pad == 1) {
     p.bn = n_seq >= kRouteMaxN ? kRouteMaxN : (n_seq + 15) / 16 * 16;
   } else {
@@ -542,18 +548,11 @@ int launch_route_tc(const void* qf, const float* row_bias, int n_seq, int s_pad,
   rc = make_map(&map_q, qf, (uint64_t)p.n_rows, (uint64_t)kdim, (uint64_t)kdim, kBK, (uint32_t)p.bn);
   if (rc != MSA_OK) return rc;
 
-  static thread_local int n_sm = 0;
-  static thread_local size_t smem_set = 0;
-  if (n_sm == 0) {
-    int dev = 0;
-    MSA_CUDA_OK(cudaGetDevice(&dev));
-    MSA_CUDA_OK(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
-  }
+  int n_sm = 0;
+  MSA_OK_OR_RETURN(device_sm_count(&n_sm));
+  static DeviceSmem smem_set{}, pair_set{};
   const size_t smem = (size_t)p.stages * stage_bytes + 1024;
-  if (smem > smem_set) {
-    MSA_CUDA_OK(cudaFuncSetAttribute(route_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    smem_set = smem;
-  }
+  MSA_OK_OR_RETURN(ensure_dynamic_smem(route_tc_kernel, smem, smem_set));
   const long long n_tiles = (long long)p.n_ctiles * p.n_qtiles;
   // Tensor-bound shapes (full 256-row query tiles, enough chunk tiles to fill the GPU) run on CTA pairs.
   static const bool pair_off = getenv("MSA_B200_ROUTE_NO_PAIR") != nullptr;
@@ -565,11 +564,7 @@ int launch_route_tc(const void* qf, const float* row_bias, int n_seq, int s_pad,
     rc = make_map(&map_q2, qf, (uint64_t)p.n_rows, (uint64_t)kdim, (uint64_t)kdim, kBK, (uint32_t)(kPairBN / 2));
     if (rc != MSA_OK) return rc;
     const size_t smem2 = (size_t)p2.stages * 2 * kBM * kBK * 2 + 1024;
-    static thread_local bool pair_set = false;
-    if (!pair_set) {
-      MSA_CUDA_OK(cudaFuncSetAttribute(route_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2));
-      pair_set = true;
-    }
+    MSA_OK_OR_RETURN(ensure_dynamic_smem(route_tc_pair_kernel, smem2, pair_set));
     const long long tiles2 = (long long)p2.n_ctiles * p2.n_qtiles;
     long long clusters = n_sm / 2;
     if (clusters > tiles2) clusters = tiles2;

@@ -275,14 +275,11 @@ extern "C" int msa_topk_select(const uint32_t* score_keys, int64_t table_stride,
   MSA_REQUIRE((long long)n_slices * k_eff <= kMaxSlice, "topk_select: n_cols=%d with k=%d is too large for two levels",
               n_cols, k);
   cudaStream_t st = (cudaStream_t)stream;
-  static thread_local bool configured = false;
-  if (!configured) {
-    MSA_CUDA_OK(cudaFuncSetAttribute(sort_topk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSlice * 8));
-    MSA_CUDA_OK(cudaFuncSetAttribute(sort_topk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSlice * 8));
-    MSA_CUDA_OK(cudaFuncSetAttribute(select_topk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSlice * 8));
-    MSA_CUDA_OK(cudaFuncSetAttribute(select_topk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSlice * 8));
-    configured = true;
-  }
+  static DeviceSmem configured[4] = {};
+  MSA_OK_OR_RETURN(ensure_dynamic_smem(sort_topk_kernel<true>, kMaxSlice * 8, configured[0]));
+  MSA_OK_OR_RETURN(ensure_dynamic_smem(sort_topk_kernel<false>, kMaxSlice * 8, configured[1]));
+  MSA_OK_OR_RETURN(ensure_dynamic_smem(select_topk_kernel<true>, kMaxSlice * 8, configured[2]));
+  MSA_OK_OR_RETURN(ensure_dynamic_smem(select_topk_kernel<false>, kMaxSlice * 8, configured[3]));
   const bool small_k = k_eff <= kSelectMaxK;
   if (n_slices == 1) {
     const int n2 = pow2_ceil(n_cols);

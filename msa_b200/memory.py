@@ -170,10 +170,10 @@ class Memory:
         self.chunk_reduce_method = g.chunk_reduce_method
         self.aux_loss_method = g.aux_loss_method
         self.decouple_router = g.decouple_router
-        if self.head_reduce_method != "mean" or self.chunk_reduce_method != "max":
-            raise A.MsaError(
-                f"head_reduce_method={self.head_reduce_method!r} / chunk_reduce_method={self.chunk_reduce_method!r} "
-                "are not supported: the fused kernel implements the shipped configuration (mean / max)")
+        if self.head_reduce_method not in A.HREDUCE:
+            raise A.MsaError(f"unknown head_reduce_method {self.head_reduce_method!r}")
+        if self.chunk_reduce_method not in A.CREDUCE:
+            raise A.MsaError(f"unknown chunk_reduce_method {self.chunk_reduce_method!r}")
         if self.query_reduce_method not in A.QREDUCE:
             raise A.MsaError(f"unknown query_reduce_method {self.query_reduce_method!r}")
         # src/msa_service.py:318-321: -1 means "cosine mode, do not scale"
@@ -356,12 +356,40 @@ class Memory:
     # ------------------------------------------------------------------ scoring + selection
     def score_folded(self, layer_idx: int, q_folded, row_bias, n_seq: int, s_pad: int, n_heads: int, top_k: int,
                      scale: float = 1.0, out=None):
-        """Score ``n_seq`` folded sequences against this shard and select ``top_k`` documents each
-        (``out``: see ``ops.topk_select``)."""
+        """Score ``n_seq`` folded sequences (head_reduce "mean") against this shard and select ``top_k``
+        documents each (``out``: see ``ops.topk_select``).  chunk_reduce "max" is one fused kernel; "mean"
+        fills a per-chunk table with the same kernel (every chunk its own document) and reduces it."""
         desc = self.block_desc
         blk = self.blocks[layer_idx]
-        keys, _ = ops.route_scores(q_folded, row_bias, n_seq, s_pad, blk.rk, desc.chunk_doc, desc.nr_docs,
-                                   alpha=scale / n_heads, min_val=torch.finfo(blk.rk.dtype).min, status=self._status)
+        min_val = torch.finfo(blk.rk.dtype).min
+        if self.chunk_reduce_method == "max":
+            keys, _ = ops.route_scores(q_folded, row_bias, n_seq, s_pad, blk.rk, desc.chunk_doc, desc.nr_docs,
+                                       alpha=scale / n_heads, min_val=min_val, status=self._status)
+        else:
+            c = blk.rk.shape[0]
+            ident = self.__dict__.get("_identity_ids")
+            if ident is None or ident.numel() != c:
+                ident = self._identity_ids = torch.arange(1, c + 1, dtype=torch.int32, device=self.device)
+            chunk_keys, _ = ops.route_scores(q_folded, row_bias, n_seq, s_pad, blk.rk, ident, c, alpha=scale / n_heads,
+                                             min_val=min_val, status=self._status)
+            keys = ops.route_reduce_chunks(chunk_keys, desc.chunk_doc, desc.nr_docs, "mean", min_val, status=self._status)
+        return self._select(keys, n_seq, top_k, out)
+
+    def score_unfolded(self, layer_idx: int, query_states, query_mask, top_k: int, scale: float = 1.0, out=None):
+        """head_reduce "max": the heads cannot be folded, so the unfolded queries ``[B, Hq, S, D]`` are scored per
+        head (``ops.route_chunk_scores``) and the chunk table is reduced to documents."""
+        desc = self.block_desc
+        blk = self.blocks[layer_idx]
+        min_val = torch.finfo(blk.rk.dtype).min
+        self._status.zero_()
+        chunk_keys = ops.route_chunk_scores(query_states, query_mask, self.num_key_value_groups, blk.rk,
+                                            self.head_reduce_method, self.query_reduce_method, scale, min_val)
+        keys = ops.route_reduce_chunks(chunk_keys, desc.chunk_doc, desc.nr_docs, self.chunk_reduce_method, min_val,
+                                       status=self._status)
+        return self._select(keys, query_states.shape[0], top_k, out)
+
+    def _select(self, keys, n_seq: int, top_k: int, out=None):
+        desc = self.block_desc
         need = ops.topk_workspace_bytes(n_seq, desc.nr_docs + 1, top_k)
         ws = getattr(self, "_topk_ws", None)
         if need and (ws is None or ws.numel() * 8 < need):
@@ -374,11 +402,20 @@ class Memory:
         ``k' = min(doc_top_k, nr_docs + 1)``; scores are float32."""
         b, hkv, grp, s, d = query_states.shape
         q = query_states.reshape(b, hkv * grp, s, d)
+        if self.head_reduce_method == "max":
+            return self.score_unfolded(layer_idx, q, query_mask.reshape(b, s), self.model_config.doc_top_k)
         qf, bias, s_pad = ops.fold_queries(q, query_mask.reshape(b, s), grp, query_reduce=self.query_reduce_method)
         return self.score_folded(layer_idx, qf, bias, b, s_pad, hkv * grp, self.model_config.doc_top_k)
 
-    def check_status(self):
-        """Raise if a kernel reported a barrier wait that ran out (reads 16 bytes back)."""
-        st = self._status.cpu().tolist()
+    @staticmethod
+    def _raise_on_status(st):
         if st[0] != 0:
-            raise A.MsaError(f"routing kernel gave up on a barrier wait (code {st[0]})")
+            raise A.MsaError(f"routing kernel gave up on a barrier wait (code {st[0]}): the score table is incomplete")
+        if st[2] != 0:
+            raise A.MsaError(f"{st[2]} out-of-range index(es) were skipped on the device (chunk -> document ids outside "
+                             "1..nr_docs, or winners outside the directory): bank tables and directory disagree")
+
+    def check_status(self):
+        """Raise if a kernel reported a barrier wait that ran out or an index outside its table (reads 16
+        bytes back).  ``MSAService.fetch`` / ``doc_query`` check the same words in the read-back they make anyway."""
+        self._raise_on_status(self._status.cpu().tolist())

@@ -148,6 +148,50 @@ def route_scores(q_folded: torch.Tensor, row_bias: torch.Tensor, n_seq: int, s_p
     return keys, status
 
 
+def route_chunk_scores(q: torch.Tensor, query_mask: torch.Tensor, num_kv_groups: int, rk: torch.Tensor,
+                       head_reduce: str = "max", query_reduce: str = "max", scale: float = 1.0,
+                       min_val: Optional[float] = None, chunk_keys: Optional[torch.Tensor] = None):
+    """Per-(sequence, chunk) scores for the reduce modes that cannot fold the heads (head_reduce "max";
+    src/msa_service.py:740-780).  q ``[B, Hq, S, D]`` UNFOLDED, query_mask ``[B, S]``, rk ``[C, Hkv, D]`` chunk major.
+    Returns keys ``[B, C + 1]`` (int32 storage), chunk c in column c + 1."""
+    A.need_cuda(q, query_mask, rk, chunk_keys)
+    b, hq, s, d = q.shape
+    if q.stride(3) != 1:
+        q = q.contiguous()
+    c = rk.shape[0]
+    rk2 = rk.reshape(c, -1) if rk.is_contiguous() else rk.flatten(1)
+    if rk2.dtype != q.dtype:
+        raise A.MsaError("route_chunk_scores: queries and router keys must share a dtype")
+    mask = query_mask.reshape(b, s).to(torch.uint8).contiguous()
+    if min_val is None:
+        min_val = torch.finfo(rk.dtype).min
+    if chunk_keys is None:
+        chunk_keys = torch.empty((b, c + 1), dtype=torch.int32, device=q.device)
+    A.check(A.lib().msa_route_chunk_scores(A.ptr(q), A.dtype_code(q.dtype), q.stride(0), q.stride(1), q.stride(2),
+                                           A.ptr(mask), s, b, hq, num_kv_groups, s, d, A.HREDUCE[head_reduce],
+                                           A.QREDUCE[query_reduce], A.ptr(rk2), rk2.stride(0) if c > 0 else hq * d, c,
+                                           float(scale), float(min_val), A.ptr(chunk_keys), chunk_keys.stride(0),
+                                           A.stream_ptr(q.device)), "msa_route_chunk_scores")
+    return chunk_keys
+
+
+def route_reduce_chunks(chunk_keys: torch.Tensor, chunk_doc: torch.Tensor, n_docs: int, chunk_reduce: str,
+                        min_val: float, keys: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None):
+    """Chunk -> document reduction ("max" or "mean", src/msa_service.py:787-812) of a chunk key table
+    ``[B, C + 1]`` into a document key table ``[B, n_docs + 1]`` (allocated and reset here when not given)."""
+    A.need_cuda(chunk_keys, chunk_doc, keys, status)
+    if chunk_doc.dtype != torch.int32:
+        raise A.MsaError("route_reduce_chunks: chunk_doc must be int32")
+    n_seq, c = chunk_keys.shape[0], chunk_doc.numel()
+    if keys is None:
+        keys = torch.empty((n_seq, n_docs + 1), dtype=torch.int32, device=chunk_keys.device)
+        route_table_reset(keys, n_docs, min_val)
+    A.check(A.lib().msa_route_reduce_chunks(A.ptr(chunk_keys), chunk_keys.stride(0), n_seq, c, A.ptr(chunk_doc), n_docs,
+                                            A.CREDUCE[chunk_reduce], float(min_val), A.ptr(keys), keys.stride(0),
+                                            A.ptr(status), A.stream_ptr(chunk_keys.device)), "msa_route_reduce_chunks")
+    return keys
+
+
 def route_table_reset(keys: torch.Tensor, n_docs: int, min_val: float, status: Optional[torch.Tensor] = None):
     A.need_cuda(keys, status)
     A.check(A.lib().msa_route_table_reset(A.ptr(keys), keys.stride(0), n_docs, keys.shape[0], float(min_val),
@@ -238,29 +282,50 @@ def topk_merge(cand_scores: torch.Tensor, cand_local: torch.Tensor, cand_global:
 
 def gather_plan(sel_local: torch.Tensor, sel_rank: Optional[torch.Tensor], world: int, shard_doc_base: torch.Tensor,
                 doc_chunk_offset: torch.Tensor, doc_chunk_len: torch.Tensor, shard_kv_base: torch.Tensor,
-                chunk_bytes: int, total_host: Optional[torch.Tensor] = None):
-    A.need_cuda(sel_local, sel_rank, shard_doc_base, doc_chunk_offset, doc_chunk_len, shard_kv_base)
+                chunk_bytes: int, total_host: Optional[torch.Tensor] = None, sample_stride: int = 0,
+                status: Optional[torch.Tensor] = None):
+    """Plan the fetch of the winners ``sel_local[B, k]`` (owner ranks ``sel_rank``).  ``sample_stride`` 0 packs
+    the samples one after another; > 0 gives every sample that many entries of room (see ``gather_run``).
+    Winners outside the directory are dropped and counted in ``status[2]``.
+    Returns ``(plan[B*k, 4], n_sel[B], total[1])``."""
+    A.need_cuda(sel_local, sel_rank, shard_doc_base, doc_chunk_offset, doc_chunk_len, shard_kv_base, status)
     n_seq, k = sel_local.shape
     dev = sel_local.device
+    if shard_doc_base.numel() != world or shard_kv_base.numel() != world:
+        raise A.MsaError("gather_plan: shard_doc_base / shard_kv_base must have one entry per rank")
+    if doc_chunk_offset.numel() != doc_chunk_len.numel():
+        raise A.MsaError("gather_plan: doc_chunk_offset and doc_chunk_len differ in length")
     plan = torch.empty((n_seq * k, 4), dtype=torch.int64, device=dev)
     n_sel = torch.empty((n_seq,), dtype=torch.int64, device=dev)
     total = torch.empty((1,), dtype=torch.int64, device=dev)
     A.check(A.lib().msa_gather_plan(A.ptr(sel_local.contiguous()), A.ptr(sel_rank.contiguous() if sel_rank is not None else None),
-                                    n_seq, k, world, A.ptr(shard_doc_base), A.ptr(doc_chunk_offset),
-                                    A.ptr(doc_chunk_len), A.ptr(shard_kv_base), chunk_bytes, A.ptr(plan), A.ptr(n_sel),
-                                    A.ptr(total), A.ptr(total_host), A.stream_ptr(dev)), "msa_gather_plan")
+                                    n_seq, k, world, A.ptr(shard_doc_base), doc_chunk_len.numel(), A.ptr(doc_chunk_offset),
+                                    A.ptr(doc_chunk_len), A.ptr(shard_kv_base), chunk_bytes, int(sample_stride),
+                                    A.ptr(plan), A.ptr(n_sel), A.ptr(total), A.ptr(total_host), A.ptr(status),
+                                    A.stream_ptr(dev)), "msa_gather_plan")
     return plan, n_sel, total
 
 
 def gather_run(plan: torch.Tensor, dtype: torch.dtype, n_kv_heads: int, head_dim: int, out_entries: int,
-               max_ctas: int = 0):
+               max_ctas: int = 0, out=None):
     """Run a gather plan.  ``max_ctas``: 0 = one CTA per document; a small cap (24) when the fetch runs
-    beside HBM-bound kernels, e.g. inside a decode step."""
+    beside HBM-bound kernels, e.g. inside a decode step.  By default the result is packed
+    ``[Hkv, out_entries, D]``.  ``out = (k_cache, v_cache, first_position)`` writes a plan made with
+    ``sample_stride = out_entries`` straight into positions ``first_position ..`` of ``[B, Hkv, L, D]`` caches."""
     dev = plan.device
-    out_k = torch.empty((n_kv_heads, out_entries, head_dim), dtype=dtype, device=dev)
-    out_v = torch.empty((n_kv_heads, out_entries, head_dim), dtype=dtype, device=dev)
+    if out is None:
+        out_k = torch.empty((n_kv_heads, out_entries, head_dim), dtype=dtype, device=dev)
+        out_v = torch.empty((n_kv_heads, out_entries, head_dim), dtype=dtype, device=dev)
+        pk, pv, head_stride, sample_stride = A.ptr(out_k), A.ptr(out_v), out_entries * head_dim, 0
+    else:
+        out_k, out_v, first = out
+        if out_k.stride() != out_v.stride() or out_k.stride(3) != 1 or out_k.stride(2) != head_dim or \
+                first + out_entries > out_k.shape[2] or out_k.dtype != dtype:
+            raise A.MsaError("gather_run: caches must be [B, Hkv, L, D] with contiguous (L, D) and room for the entries")
+        off = first * head_dim * out_k.element_size()
+        pk, pv, head_stride, sample_stride = A.ptr(out_k) + off, A.ptr(out_v) + off, out_k.stride(1), out_k.stride(0)
     A.check(A.lib().msa_gather_run(A.ptr(plan), plan.shape[0], A.dtype_code(dtype), n_kv_heads, head_dim,
-                                   A.ptr(out_k), A.ptr(out_v), out_entries * head_dim, out_entries, int(max_ctas),
+                                   pk, pv, head_stride, out_entries, sample_stride, int(max_ctas),
                                    A.stream_ptr(dev)), "msa_gather_run")
     return out_k, out_v
 

@@ -132,6 +132,7 @@ class MSAService(Memory, MemoryClientBase):
         self.uniform_seqlen = False   # set when every rank is known to pass queries of equal length
         self._directory = None
         self._total_pinned = torch.zeros(1, dtype=torch.int64).pin_memory()
+        self._status_pinned = torch.zeros(4, dtype=torch.int32).pin_memory()
 
     def setup_memory_client(self, model):
         """Inject this service into every module that has ``set_memory_client`` (:1057-1067)."""
@@ -237,9 +238,11 @@ class MSAService(Memory, MemoryClientBase):
         ``all_valid``: the caller guarantees that every rank's ``query_mask`` is all ones (a decode step), which
         saves the all-gather of the row bias."""
         b, hq, s, d = query_states.shape
-        qf, bias, s_pad, _ = self._gather_querys(query_states, query_mask, l2_normalize, all_valid)
         scale = self.scaling if self.scaling > 0 else 1.0
         n_all = self.world_size * b
+        if self.head_reduce_method == "max":
+            return self._route_unfolded(query_states, query_mask, layer_idx, l2_normalize, scale)
+        qf, bias, s_pad, _ = self._gather_querys(query_states, query_mask, l2_normalize, all_valid)
         if self.world_size > 1:
             # the selection writes straight into one buffer (scores, local ids, global ids as planes), ONE
             # all-gather moves it, and the merge reads the gathered planes in place
@@ -251,6 +254,36 @@ class MSAService(Memory, MemoryClientBase):
             sc, li, gi = ops.candidate_views(all_gather_cat(cb[0], self.world_size, self.group))   # [W, B_all, k']
         else:
             sc, li, gi = self.score_folded(layer_idx, qf, bias, n_all, s_pad, hq, self.shard_top_k, scale=scale)
+            sc, li, gi = sc.unsqueeze(0), li.unsqueeze(0), gi.unsqueeze(0)
+        return ops.topk_merge(sc, li, gi, self.model_config.doc_top_k, seq_offset=self.rank * b, n_seq=b)
+
+    def _route_unfolded(self, query_states, query_mask, layer_idx: int, l2_normalize: bool, scale: float):
+        """``route`` for head_reduce "max": a max over heads cannot be folded into one contraction, so the
+        UNFOLDED queries and their masks are all-gathered (padded to the longest query, as the reference does,
+        :1088-1131) and scored per head."""
+        b, hq, s, d = query_states.shape
+        if l2_normalize:
+            query_states = torch.nn.functional.normalize(query_states, p=2, dim=-1)
+        mask = query_mask.reshape(b, s)
+        if self.world_size > 1:
+            s_common = s
+            if not self.uniform_seqlen:
+                lens = all_gather_cat(torch.tensor([s], device=self.device, dtype=torch.long), self.world_size, self.group)
+                s_common = int(lens.max().item())
+            if s_common > s:
+                query_states = torch.nn.functional.pad(query_states, (0, 0, 0, s_common - s))
+                mask = torch.nn.functional.pad(mask, (0, s_common - s), value=False)
+            q_all = all_gather_cat(query_states.contiguous(), self.world_size, self.group).view(-1, hq, s_common, d)
+            m_all = all_gather_cat(mask.to(torch.uint8).contiguous(), self.world_size, self.group).view(-1, s_common)
+            k_eff = min(self.shard_top_k, self.block_desc.nr_docs + 1)
+            n_all = self.world_size * b
+            cb = self.__dict__.get("_cand_buf")
+            if cb is None or tuple(cb[0].shape) != (3, n_all, k_eff):
+                cb = self._cand_buf = ops.candidate_buffer(n_all, k_eff, self.device)
+            self.score_unfolded(layer_idx, q_all, m_all, self.shard_top_k, scale=scale, out=cb[1:])
+            sc, li, gi = ops.candidate_views(all_gather_cat(cb[0], self.world_size, self.group))
+        else:
+            sc, li, gi = self.score_unfolded(layer_idx, query_states, mask, self.shard_top_k, scale=scale)
             sc, li, gi = sc.unsqueeze(0), li.unsqueeze(0), gi.unsqueeze(0)
         return ops.topk_merge(sc, li, gi, self.model_config.doc_top_k, seq_offset=self.rank * b, n_seq=b)
 
@@ -269,12 +302,15 @@ class MSAService(Memory, MemoryClientBase):
         blk = self.blocks[layer_idx]
         chunk_bytes = 2 * g.num_key_value_heads * g.head_dim * blk.kv.element_size()
         plan, n_sel, total = ops.gather_plan(winner_local, winner_rank, self.world_size, base, offs, ln,
-                                             kv_base[layer_idx], chunk_bytes, total_host=None)
+                                             kv_base[layer_idx], chunk_bytes, total_host=None, status=self._status)
         if max_entries is not None:
             k, v = ops.gather_run(plan, blk.kv.dtype, g.num_key_value_heads, g.head_dim, max_entries, max_ctas)
             return k, v, n_sel, total
+        # one read-back sizes the result; the status words of this layer's routing and plan ride along
         self._total_pinned.copy_(total, non_blocking=True)
+        self._status_pinned.copy_(self._status, non_blocking=True)
         torch.cuda.current_stream(self.device).synchronize()
+        self._raise_on_status(self._status_pinned.tolist())
         n = int(self._total_pinned.item())
         k, v = ops.gather_run(plan, blk.kv.dtype, g.num_key_value_heads, g.head_dim, n, max_ctas)
         return k, v, n_sel

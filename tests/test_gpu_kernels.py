@@ -342,6 +342,71 @@ def test_gather_from_pinned_host_bank(ops, dtype):
     assert torch.equal(out_v.cpu(), torch.cat(vs).permute(1, 0, 2))
 
 
+def test_gather_plan_drops_winners_outside_their_shard(ops):
+    """A winner whose local id is one past its shard's last document still indexes the directory (it lands on
+    the next shard's dummy row), so the check can be exercised without touching memory outside a tensor: the
+    plan row must come back empty with status[2] counting it, as must a winner with an owner rank that does not
+    exist; the gather then runs on the sanitised plan only.  Also covers the per-sample destination layout."""
+    g = torch.Generator().manual_seed(5)
+    world, hkv, d, k = 2, 8, 128, 4
+    chunks = [[2, 3, 1], [4, 2]]
+    banks = [torch.randn(sum(c), 2, hkv, d, generator=g).to(torch.bfloat16).pin_memory() for c in chunks]
+    lens = [torch.tensor([0] + c) for c in chunks]
+    offs = [torch.cumsum(torch.cat([torch.zeros(1, dtype=torch.long), ln[:-1]]), 0) for ln in lens]
+    bases = torch.tensor([0, 4])
+    sel_local = torch.tensor([[1, 4, 2, -1],      # local id 4 of shard 0: one past its last document (3)
+                              [2, 1, 3, 1]])      # (rank 7, id 1) and (rank 1, id 3): no such rank / document
+    sel_rank = torch.tensor([[0, 0, 0, 0], [1, 7, 1, 0]], dtype=torch.int32)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    args = (sel_local.to(DEV), sel_rank.to(DEV), world, bases.to(DEV), torch.cat(offs).to(DEV),
+            torch.cat(lens).to(torch.int32).to(DEV), torch.tensor([b.data_ptr() for b in banks], dtype=torch.int64).to(DEV),
+            2 * hkv * d * 2)
+    plan, n_sel, total = ops.gather_plan(*args, status=status)
+    torch.cuda.synchronize()
+    assert status.cpu().tolist()[2] == 3
+    rows = plan.cpu().view(2, k, 4)
+    assert rows[0, :, 1].tolist() == [2, 3, 0, 0] and rows[1, :, 1].tolist() == [2, 2, 0, 0]
+    assert (rows[:, 2:, 0] == 0).all()                       # no source address in the dropped rows
+    assert n_sel.cpu().tolist() == [5, 4] and int(total.item()) == 9
+    out_k, out_v = ops.gather_run(plan, torch.bfloat16, hkv, d, 9)
+    ref_k = torch.cat([banks[0][0:2, 0], banks[0][2:5, 0], banks[0][0:2, 0], banks[1][4:6, 0]]).permute(1, 0, 2)
+    assert torch.equal(out_k.cpu(), ref_k)
+    # per-sample layout: every sample gets `room` entries inside a [B, Hkv, L, D] cache, longer samples are cut
+    room, first = 4, 3
+    plan2, n_sel2, _ = ops.gather_plan(*args, sample_stride=room)
+    kc = torch.zeros(2, hkv, first + room + 2, d, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    ops.gather_run(plan2, torch.bfloat16, hkv, d, room, out=(kc, vc, first))
+    assert n_sel2.cpu().tolist() == [4, 4]
+    assert torch.equal(kc[0, :, first:first + room].cpu(), ref_k[:, 0:4])      # 2 + (3 cut to 2) chunks
+    assert torch.equal(kc[1, :, first:first + room].cpu(), ref_k[:, 5:9])
+    assert (kc[:, :, :first] == 0).all() and (kc[:, :, first + room:] == 0).all()
+    assert torch.equal(vc[1, :, first:first + room].cpu(), torch.cat([banks[0][0:2, 1], banks[1][4:6, 1]]).permute(1, 0, 2))
+
+
+def test_routing_skips_chunk_ids_outside_the_table(ops):
+    """chunk -> document ids outside 1..n_docs never become a table column: skipped and counted in status[2]."""
+    chunks = [8] * 6
+    rk, pool_ids = make_bank(chunks, dtype=torch.bfloat16, seed=3)
+    g = torch.Generator().manual_seed(4)
+    q = torch.nn.functional.normalize(torch.randn(2, 8, 4, 16, 128, generator=g), dim=-1).to(torch.bfloat16)
+    mask = torch.ones(2, 16, dtype=torch.bool)
+    ref = O.route_doc_scores(q.float(), mask, rk.float().transpose(0, 1), pool_ids, len(chunks))
+    bad = pool_ids.clone()
+    bad[40:] = 6 + 5                              # the last document's chunks claim an id beyond n_docs = 6
+    for flags in (0, 1):                          # tensor-core kernel, CUDA-core kernel
+        b, hkv, grp, s, dd = q.shape
+        qf, bias, s_pad = ops.fold_queries(q.reshape(b, hkv * grp, s, dd).to(DEV), mask.to(DEV), grp)
+        keys, status = ops.route_scores(qf, bias, b, s_pad, rk.to(DEV), bad.to(torch.int32).to(DEV), len(chunks),
+                                        alpha=1.0 / 32, flags=flags)
+        torch.cuda.synchronize()
+        st = status.cpu().tolist()
+        assert st[0] == 0 and st[2] > 0
+        table = ops.keys_to_scores(keys).cpu()
+        assert torch.allclose(table[:, 1:6], ref[:, 1:6], atol=1e-3)
+        assert (table[:, 6] == torch.finfo(torch.bfloat16).min).all()
+
+
 # ----------------------------------------------------------------------------- decode attention
 def test_decode_golden_layer(ops, golden):
     g = golden("layer_decode")

@@ -22,7 +22,7 @@ def test_library_loads_and_exports_every_declared_symbol():
     assert declared == set(A.EXPORTS)
     for name in declared:
         assert hasattr(lib, name), name
-    assert lib.msa_abi_version() == 1
+    assert lib.msa_abi_version() == 2
     assert lib.msa_route_s_pad(256, 0) == 256 and lib.msa_route_s_pad(100, 0) == 112
     assert lib.msa_route_s_pad(300, 0) == 320 and lib.msa_route_s_pad(1, 0) == 1 and lib.msa_route_s_pad(77, 1) == 1
     assert lib.msa_decode_workspace_bytes(2, 32, 128, 4) == 2 * 32 * 4 * 130 * 4
@@ -35,6 +35,18 @@ def test_argument_errors_are_reported_before_any_launch():
     assert b"null pointer" in lib.msa_last_error()
     assert lib.msa_topk_select(1, 8, 1, 4, 5000, None, 1, 1, None, None, 0, None) == -1
     assert b"exceeds the supported maximum" in lib.msa_last_error()
+    # msa_gather_plan: directory smaller than the shards' dummy rows, negative per-sample room
+    assert lib.msa_gather_plan(1, None, 1, 4, 2, 1, 1, 1, 1, 1, 4096, 0, 1, 1, 1, None, None, None) == -1
+    assert b"n_dir_rows" in lib.msa_last_error()
+    assert lib.msa_gather_plan(1, None, 1, 4, 1, 1, 8, 1, 1, 1, 4096, -1, 1, 1, 1, None, None, None) == -1
+    assert b"sample_stride" in lib.msa_last_error()
+    assert lib.msa_gather_run(1, 4, 1, 8, 128, 1, 1, 1024, 4, -16, 0, None) == -1
+    # reduce modes
+    assert lib.msa_route_chunk_scores(None, 1, 0, 0, 0, None, 0, 1, 32, 4, 8, 128, 7, 0, None, 1024, 4, 1.0, 0.0, None, 5,
+                                      None) == -1
+    assert b"head_reduce" in lib.msa_last_error()
+    assert lib.msa_route_reduce_chunks(None, 5, 1, 4, None, 2, 3, 0.0, None, 3, None, None) == -1
+    assert b"chunk_reduce" in lib.msa_last_error()
     with pytest.raises(A.MsaError, match="CUDA tensors"):
         from msa_b200 import ops
         ops.pool_chunks(torch.zeros(4, 8, 128), torch.tensor([0, 4], dtype=torch.int32))

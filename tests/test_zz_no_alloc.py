@@ -59,6 +59,14 @@ def test_static_scratch_decode_matches_regular_entry_point(dtype, tol):
         err = float((out_new.double() - out_ref.double()).norm() / out_ref.double().norm())
         assert err < tol, err
         assert torch.equal(kc, kc2) and torch.equal(vc, vc2)      # same in-place append
+        # the point of the entry point: a call leaves the device's free memory and torch's pool untouched
+        # (the first call on a device may load the module that holds the array, so this is a repeat call)
+        torch.cuda.synchronize()
+        free_before, pool_before = torch.cuda.mem_get_info(DEV)[0], torch.cuda.memory_reserved(DEV)
+        A.check(_call(lib.msa_sparse_decode_attn_static, [], q, kc2, vc2, kv_len, nk, nv, out_new, n_splits),
+                "msa_sparse_decode_attn_static")
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info(DEV)[0] == free_before and torch.cuda.memory_reserved(DEV) == pool_before
 
 
 def test_static_scratch_rejects_oversized_problem():
