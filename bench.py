@@ -11,9 +11,21 @@ score/reduce -> per-shard top-k -> (all-gather candidates) -> merge to the globa
 Inputs are seeded synthetic (cosine mode: unit-norm heads; keys = per-document mean N(0,0.5)
 + noise of std 1/8 per chunk, the pooled statistics of benchmark config 3's distribution).
 
-`value` times the step with queries resident in HBM; `e2e` times the same step through
-MSAService.route with the queries in pinned HOST memory (H2D of every layer's queries and
-D2H of every layer's winners inside the timed region).
+`value` times the step with queries resident in HBM; `e2e` times the same work through
+MSAService.doc_query (the call the reference's attention layer makes) with the queries in pinned HOST
+memory: H2D of every layer's queries, routing, merge, fetch of the winners' K/V from the pinned host bank,
+D2H of every layer's winners, all inside the timed region.
+
+The same line also carries, outside the timed region:
+  parity         MSAService.doc_query on a small ragged doc-sharded bank at this N against the oracle's
+                 doc_query_world, plus spot checks of the full-size score table; a mismatch exits non-zero
+  kernels        pooling (config 2), decode attention (config 5 layer), decode-time routing (M = 32, one of 8
+                 shards): time, algorithmic bytes, fraction of the measured HBM rate
+  generate       config-5 tokens/s at this N (64 new tokens)
+  pcie           the host->device copy rate measured in this process (the roof the host fetch is judged by)
+  incumbent_gpu  the reference's own torch-op pipeline (Memory.prefill_stage2 with device="cuda", bf16) on a
+                 bounded sample, and vs_incumbent = value / that
+  cpu_baseline   the reference's own Memory.prefill_stage2 on the host cores (oracle/_ref), or the oracle port
 """
 from __future__ import annotations
 
@@ -32,6 +44,7 @@ sys.path.insert(0, ROOT)
 N_DOCS, CHUNKS_PER_DOC, N_LAYERS = 195_313, 8, 18
 N_QUERIES, Q_TOKENS, HQ, HKV, D, TOP_K = 128, 256, 32, 8, 128, 16
 METRIC = "routing queries/s over 100M-token memory"
+WORKLOAD = "benchmark config 4: 100M-token bank, 18 layers, 128 queries x 256 tokens, top-16"
 
 
 def parse():
@@ -44,8 +57,11 @@ def parse():
     ap.add_argument("--layers", type=int, default=N_LAYERS)
     ap.add_argument("--queries", type=int, default=N_QUERIES)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="routing workload: skip the parity / kernels / generate / incumbent legs (profiling runs)")
     ap.add_argument("--new-tokens", type=int, default=256, help="generate workload: tokens to decode")
-    ap.add_argument("--workload", default="routing", choices=["routing", "pooling", "decode", "fetch", "route-decode", "prefill", "stage1", "generate"],
+    ap.add_argument("--workload", default="routing",
+                    choices=["routing", "pooling", "decode", "fetch", "route-decode", "prefill", "stage1", "generate"],
                     help="routing = the headline (default); the others time one secondary kernel each")
     return ap.parse_args()
 
@@ -54,8 +70,9 @@ def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         p = json.load(open(path))
-        return {"hbm_gbs": p["hbm_gbs"], "tflops": p["bf16_tflops_sustained"], "source": "measured"}
-    return {"hbm_gbs": 6650.0, "tflops": 1400.0, "source": "fallback"}
+        return {"hbm_gbs": p["hbm_gbs"], "tflops": p["bf16_tflops_sustained"], "tflops_burst": p["bf16_tflops"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1400.0, "tflops_burst": 1590.0, "source": "fallback"}
 
 
 class ClockSampler:
@@ -96,34 +113,51 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------
+# CPU legs: the reference's own code (oracle/_ref) when it is there, else the oracle port
+# ------------------------------------------------------------------------------------------
 def cpu_reference_sample(threads: int, target_s: float = 12.0):
-    """The oracle port of Memory.prefill_stage2 (matmul over all 32 heads, masked_fill, head mean,
-    token max, scatter amax, topk) on the host cores, fp32, on a bounded sample; extrapolated
-    linearly in chunks and layers to the full workload."""
+    """Memory.prefill_stage2 of the reference (its own code from oracle/_ref: _generate_slice + the slice loop
+    of matmul over all 32 heads, masked_fill, head mean, token max, two scatter_reduce, topk; or, without
+    oracle/_ref, the oracle port of the same op sequence) on the host cores, fp32, on a bounded sample;
+    scaled linearly in chunks and layers to the full workload.  Returns (queries/s, kind, sample, seconds)."""
     import torch
     from oracle import msa_oracle as O
+    from oracle import ref_runner as R
     torch.set_num_threads(threads)
     g = torch.Generator().manual_seed(4000)
     n_q, docs = 2, 2048
     chunks = docs * CHUNKS_PER_DOC
     rk = torch.nn.functional.normalize(torch.randn(HKV, chunks, D, generator=g), dim=-1)
-    pool_ids = torch.repeat_interleave(torch.arange(1, docs + 1), CHUNKS_PER_DOC)
-    table = torch.arange(docs + 1)
     q = torch.nn.functional.normalize(torch.randn(n_q, HKV, HQ // HKV, Q_TOKENS, D, generator=g), dim=-1)
     mask = torch.ones(n_q, Q_TOKENS, dtype=torch.bool)
+    kind = "port"
+    if R.available():
+        try:
+            mem = R.make_reference_memory(rk.unsqueeze(0), [CHUNKS_PER_DOC] * docs, range(docs), TOP_K)
+            run = lambda: R.reference_prefill_stage2(mem, q, mask)
+            run()
+            kind = "reference"
+        except Exception as e:   # an import the box lacks: say so and time the port
+            sys.stderr.write(f"oracle/_ref could not run ({type(e).__name__}: {e}); timing the oracle port\n")
+    if kind == "port":
+        pool_ids = torch.repeat_interleave(torch.arange(1, docs + 1), CHUNKS_PER_DOC)
+        table = torch.arange(docs + 1)
+        run = lambda: O.prefill_stage2(q, mask, rk, pool_ids, table, TOP_K)
 
     def once():
         t0 = time.perf_counter()
-        O.prefill_stage2(q, mask, rk, pool_ids, table, TOP_K)
+        run()
         return time.perf_counter() - t0
     once()
     t1 = once()
     reps = max(1, min(20, int(target_s / max(t1, 1e-3))))
     t = statistics.median([once() for _ in range(reps)])
     per_query_full = t / n_q * (N_DOCS * CHUNKS_PER_DOC / chunks) * N_LAYERS
-    sample = (f"oracle port of prefill_stage2, fp32, {n_q} queries x {Q_TOKENS} tokens x {chunks} chunks x 1 layer, "
+    what = ("the reference's Memory._generate_slice + Memory.prefill_stage2 (oracle/_ref, unmodified)" if kind == "reference"
+            else "oracle port of Memory.prefill_stage2")
+    sample = (f"{what}, fp32, {n_q} queries x {Q_TOKENS} tokens x {chunks} chunks x 1 layer, "
               f"median of {reps}, scaled x{N_DOCS * CHUNKS_PER_DOC / chunks:.1f} chunks x{N_LAYERS} layers")
-    return 1.0 / per_query_full, sample, t
+    return 1.0 / per_query_full, kind, sample, t
 
 
 def run_reference(args):
@@ -131,9 +165,9 @@ def run_reference(args):
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    vals, sample, t_last = [], "", 0.0
+    vals, kind, sample = [], "port", ""
     for i in range(args.warmup + args.steps):
-        v, sample, t_last = cpu_reference_sample(threads, target_s=2.0)
+        v, kind, sample, _ = cpu_reference_sample(threads, target_s=2.0)
         if i >= args.warmup:
             vals.append(v)
     v = statistics.median(vals)
@@ -141,9 +175,8 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": v, "unit": "queries/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * N_QUERIES / v, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "benchmark config 4: 100M-token bank, 18 layers, 128 queries x 256 tokens, top-16",
-                   "note": "CPU: bounded sample, extrapolated linearly"},
-        "cpu_baseline": {"value": v, "unit": "queries/s", "cores": threads, "kind": "port", "sample": sample},
+        "config": {"workload": WORKLOAD, "note": "host cores: each step is a bounded sample, scaled linearly"},
+        "cpu_baseline": {"value": v, "unit": "queries/s", "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": v, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -167,12 +200,564 @@ def make_bank(torch, dev, docs_local: int, layers: int, seed: int):
     return out
 
 
+def _time_ms(torch, fn, steps, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def measure_pcie(torch, dev):
+    """Host -> device copy rate of this process's GPU: best of 10 cudaMemcpyAsync of 1 GiB from pinned memory
+    (CUDA events).  The roof for the host K/V fetch."""
+    n = 1 << 30
+    host = torch.empty(n, dtype=torch.uint8).pin_memory()
+    dst = torch.empty(n, dtype=torch.uint8, device=dev)
+    best = float("inf")
+    for i in range(12):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        dst.copy_(host, non_blocking=True)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        if i >= 2:
+            best = min(best, e0.elapsed_time(e1))
+    del host, dst
+    return {"h2d_gbs": n / (best / 1e3) / 1e9, "how": "best of 10 copies of 1 GiB, pinned host -> device, CUDA events"}
+
+
+# ------------------------------------------------------------------------------------------
+# parity legs (outside every timed region)
+# ------------------------------------------------------------------------------------------
+def _parity_shard(torch, r):
+    """Seeded small shard r: ragged documents of 1..12 chunks, bf16.  Any rank can rebuild any shard."""
+    g = torch.Generator().manual_seed(8100 + r)
+    n_docs = 1200 + 37 * r
+    chunks = torch.randint(1, 13, (n_docs,), generator=g)
+    c = int(chunks.sum())
+    mu = torch.randn(n_docs, HKV, D, generator=g) * 0.5
+    rk = torch.repeat_interleave(mu, chunks, dim=0) + torch.randn(c, HKV, D, generator=g) / 8.0
+    rk = torch.nn.functional.normalize(rk, dim=-1).to(torch.bfloat16)
+    k = torch.randn(c, HKV, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(c, HKV, D, generator=g).to(torch.bfloat16)
+    gids = [100_000 * (r + 1) + i for i in range(n_docs)]
+    return chunks.tolist(), gids, rk, k, v
+
+
+def _parity_queries(torch, r):
+    g = torch.Generator().manual_seed(8200 + r)
+    b, s = 4, 24 + 8 * (r % 3)                       # ranks pass queries of different lengths
+    q = torch.nn.functional.normalize(torch.randn(b, HQ, s, D, generator=g), dim=-1).to(torch.bfloat16)
+    mask = torch.ones(b, s, dtype=torch.bool)
+    mask[1, s - 7:] = False                          # right padding
+    mask[2, :5] = False                              # left padding
+    return q, mask
+
+
+def parity_check(torch, dist, world, rank, local_rank, dev):
+    """MSAService.doc_query on `world` ranks against oracle.doc_query_world (src/msa_service.py:1133-1314):
+    scores within 1e-3, winners exact outside a 1e-3 gap, fetched K/V rows bit-exact."""
+    from msa_b200.memory import AttentionGeometry, Document, ModelConfig
+    from msa_b200.service import MSAService
+    from oracle import msa_oracle as O
+    shard_k = TOP_K if world == 1 else 2 * TOP_K
+    chunks, gids, rk, k, v = _parity_shard(torch, rank)
+    svc = MSAService(local_rank, None, ModelConfig(doc_top_k=TOP_K, router_layer_idx="0"), None,
+                     AttentionGeometry(num_hidden_layers=1), world_size=world, rank=rank, shard_top_k=shard_k)
+    svc.load_pooled([Document(doc_id=g_, num_chunks=n) for g_, n in zip(gids, chunks)], {0: (k, v, rk.to(dev))})
+    if world > 1:
+        svc.share_host_banks(tag=f"parity{os.environ.get('MASTER_PORT', '0')}")
+    q, mask = _parity_queries(torch, rank)
+    fk, fv, fs, n_sel, wg = svc.doc_query(q.to(dev), mask.to(dev), 0)
+    mine = [t.cpu() for t in (fk, fv, fs, n_sel, wg)]
+    torch.cuda.synchronize(dev)
+    if world > 1:
+        svc.close_host_banks()
+        gathered = [None] * world
+        dist.all_gather_object(gathered, mine)
+    else:
+        gathered = [mine]
+    if rank != 0:
+        return None
+    shards, queries, masks = [], [], []
+    for r in range(world):
+        ch, gi, rk_r, k_r, v_r = _parity_shard(torch, r)
+        shards.append(O.Shard(k_r.float().transpose(0, 1), v_r.float().transpose(0, 1), rk_r.float().transpose(0, 1), ch, gi))
+        q_r, m_r = _parity_queries(torch, r)
+        queries.append(q_r.float())
+        masks.append(m_r)
+    ref = O.doc_query_world(queries, masks, shards, TOP_K, HQ // HKV, shard_top_k=shard_k)
+    max_err, ties, bad = 0.0, 0, []
+    for r in range(world):
+        rk_, rv_, rs_, rn_, rg_ = ref[r]
+        fk, fv, fs, n_sel, wg = gathered[r]
+        max_err = max(max_err, float((fs - rs_).abs().max()))
+        if not torch.allclose(fs, rs_, atol=1e-3, rtol=0):
+            bad.append(f"rank {r}: scores differ by {float((fs - rs_).abs().max()):.2e}")
+        same_all = True
+        for i in range(fs.shape[0]):
+            if set(wg[i].tolist()) != set(rg_[i].tolist()):
+                same_all = False
+                kth = float(rs_[i, -1])
+                diff = set(wg[i].tolist()) ^ set(rg_[i].tolist())
+                sc = {int(g_): float(s_) for g_, s_ in zip(rg_[i].tolist() + wg[i].tolist(), rs_[i].tolist() + fs[i].tolist())}
+                if all(abs(sc[d_] - kth) <= 1e-3 for d_ in diff):
+                    ties += 1
+                else:
+                    bad.append(f"rank {r} sample {i}: winners differ outside the 1e-3 gap")
+        if same_all:    # same winners everywhere: the fetched entries must be the same bytes in the same order
+            if not (torch.equal(n_sel, rn_) and torch.equal(fk.float(), rk_) and torch.equal(fv.float(), rv_)):
+                bad.append(f"rank {r}: fetched K/V rows differ")
+    return {"checked": True, "ok": not bad, "world": world, "what": "MSAService.doc_query vs oracle.doc_query_world on a ragged "
+            f"doc-sharded bank ({sum(len(_parity_shard(torch, r)[0]) for r in range(world))} documents of 1-12 chunks, "
+            f"4 queries per rank of 24-40 tokens, top-{TOP_K}, per-shard top-{shard_k})",
+            "max_score_err": max_err, "tie_swaps_within_1e-3": ties, "fetched_rows": "bit-exact" if not bad else "see errors",
+            "errors": bad[:5]}
+
+
+def fullsize_spot_check(torch, ops, keys, q_local, mask_local, rk, docs_local, row0, shard_k):
+    """Sampled (query, document) pairs of the full-size score table of the last timed layer against the oracle,
+    and the selection against torch.topk of the same table."""
+    from oracle import msa_oracle as O
+    gs = torch.Generator().manual_seed(3)
+    n_s = min(48, docs_local)
+    docs = torch.randint(0, docs_local, (n_s,), generator=gs)
+    rows = torch.cat([torch.arange(d * CHUNKS_PER_DOC, (d + 1) * CHUNKS_PER_DOC) for d in docs.tolist()])
+    sub = [0, q_local.shape[0] // 2, q_local.shape[0] - 1]
+    table = ops.keys_to_scores(keys[[row0 + i for i in sub]])
+    q5 = q_local[sub].view(len(sub), HKV, HQ // HKV, Q_TOKENS, D).float().cpu()
+    pool_ids = torch.arange(1, n_s + 1).repeat_interleave(CHUNKS_PER_DOC)
+    ref = O.route_doc_scores(q5, mask_local[sub].cpu(), rk[rows.to(rk.device)].float().cpu().transpose(0, 1), pool_ids, n_s)
+    got = table[:, (docs + 1).to(table.device)].cpu()
+    err = float((got - ref[:, 1:]).abs().max())
+    sc, li, _ = ops.topk_select(keys[[row0 + i for i in sub]].contiguous(), shard_k)
+    ref_s = torch.topk(table, k=min(shard_k, table.shape[1]), dim=1).values
+    topk_ok = bool(torch.equal(sc, ref_s)) and bool(torch.equal(table.gather(1, li), sc))
+    return {"pairs": len(sub) * n_s, "max_score_err": err, "scores_ok": err <= 1e-3, "topk_exact": topk_ok}
+
+
+# ------------------------------------------------------------------------------------------
+# incumbent: the reference's torch-op pipeline on this GPU
+# ------------------------------------------------------------------------------------------
+def incumbent_gpu(torch, dev, rk_chunk_major, docs_local, value):
+    """Memory.prefill_stage2 as the reference runs it (src/msa_service.py:703-828: per 16,384-chunk slice a 32-head
+    matmul, masked_fill, mean, max, two scatter_reduce, then topk), bf16, device = this GPU, on a bounded sample:
+    16 queries x 256 tokens x this rank's shard x 1 layer; scaled linearly in queries and layers.  With
+    oracle/_ref the reference's own code runs; without it the same op sequence written out here."""
+    from oracle import ref_runner as R
+    n_q = 16
+    c_local = docs_local * CHUNKS_PER_DOC
+    g = torch.Generator(device=dev)
+    g.manual_seed(77)
+    q = torch.nn.functional.normalize(torch.randn((n_q, HKV, HQ // HKV, Q_TOKENS, D), generator=g, device=dev),
+                                      dim=-1).to(torch.bfloat16)
+    mask = torch.ones((n_q, Q_TOKENS), dtype=torch.bool, device=dev)
+    rk_hm = rk_chunk_major.permute(1, 0, 2).contiguous().unsqueeze(0)      # the reference's [1, Hkv, C, D]
+    kind = "ops"
+    if R.available():
+        try:
+            mem = R.make_reference_memory(rk_hm, [CHUNKS_PER_DOC] * docs_local, range(docs_local), TOP_K)
+            run = lambda: R.reference_prefill_stage2(mem, q, mask)
+            run()
+            kind = "reference"
+        except Exception as e:
+            sys.stderr.write(f"oracle/_ref could not run on the GPU ({type(e).__name__}: {e}); timing the op sequence\n")
+    if kind == "ops":
+        pool = torch.arange(docs_local, device=dev).repeat_interleave(CHUNKS_PER_DOC)
+        min_val = torch.finfo(torch.bfloat16).min
+        m5 = ~mask.view(n_q, 1, 1, Q_TOKENS, 1)
+
+        def run():
+            table = torch.full((n_q, docs_local + 1), min_val, dtype=torch.bfloat16, device=dev)
+            for c0 in range(0, c_local, 16384):
+                c1 = min(c_local, c0 + 16384)
+                kt = rk_hm[:, :, c0:c1].transpose(-1, -2).unsqueeze(2)
+                sc = torch.matmul(q, kt)
+                sc.masked_fill_(m5, min_val)
+                sc = sc.flatten(1, 2).mean(dim=1).max(dim=1).values
+                table.scatter_reduce_(1, (pool[c0:c1] + 1).view(1, -1).expand(n_q, -1), sc, reduce="amax", include_self=True)
+            return torch.topk(table, k=TOP_K, dim=1)
+    ms = _time_ms(torch, run, 3, 1)
+    del rk_hm
+    torch.cuda.empty_cache()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    # every rank scores ALL 128 queries against its shard: a step costs (128 / 16) samples x 18 layers per rank
+    step_ms = ms * (N_QUERIES / n_q) * N_LAYERS
+    inc = N_QUERIES / (step_ms / 1e3)
+    return {"value": inc, "unit": "queries/s", "kind": kind, "dtype": "bf16", "sample_ms": ms,
+            "sample": f"{n_q} queries x {Q_TOKENS} tokens x {c_local} chunks (this rank's shard, {world} rank(s)) x 1 layer, "
+                      f"mean of 3; scaled x{N_QUERIES // n_q} queries x{N_LAYERS} layers (collectives of the reference "
+                      "not included)",
+            "what": ("the reference's own Memory._generate_slice + Memory.prefill_stage2 (oracle/_ref) with device=cuda"
+                     if kind == "reference" else "the reference's op sequence (src/msa_service.py:716-828) written out in torch"),
+            "vs_incumbent": value / inc}
+
+
+# ------------------------------------------------------------------------------------------
+# secondary kernels (each returns a dict; `--workload X` prints one as a full line)
+# ------------------------------------------------------------------------------------------
+def leg_pooling(torch, ops, dev, pk, steps=50, warmup=3, n_docs=2048):
+    doc_len, p = 512, 64
+    g = torch.Generator(device=dev)
+    g.manual_seed(2000)
+    t = n_docs * doc_len
+    doc_ids = torch.arange(1, n_docs + 1, device=dev).repeat_interleave(doc_len).view(1, t)
+    tok, off, pooled = ops.chunk_bookkeeping(doc_ids, None, p)
+    ms_bk = _time_ms(torch, lambda: ops.chunk_bookkeeping(doc_ids, None, p, max_chunks=t // p + 1), 3, 1)
+    states = [torch.randn((1, HKV, t, D), generator=g, device=dev).to(torch.bfloat16) for _ in range(3)]
+
+    def step():
+        ops.pool_chunks(states[0], off, tok)
+        ops.pool_chunks(states[1], off, tok)
+        ops.pool_chunks(states[2], off, tok, l2_normalize=True)
+    ms = _time_ms(torch, step, steps, warmup)
+    c = off.numel() - 1
+    alg = 3 * (t * HKV * D * 2 + c * HKV * D * 2)
+    gbs = alg / (ms / 1e3) / 1e9
+    return {"kernel": "pool_kernel", "ms": ms, "tokens_per_s": t / (ms / 1e3), "algorithmic_bytes": alg, "achieved_gbs": gbs,
+            "frac": gbs / pk["hbm_gbs"], "bound": "hbm", "launches": 3 * steps, "bookkeeping_ms": ms_bk,
+            "workload": f"benchmark config 2: {n_docs} docs x {doc_len} tokens, chunk {p}, bf16, K / V / K_r "
+                        f"({t * HKV * D * 2 / 1e9:.2f} GB each, > L2)"}
+
+
+def leg_decode(torch, ops, dev, pk, steps=500, warmup=3):
+    b, L, n_layers = 32, 3 + 128 + 2048, 4
+    g = torch.Generator(device=dev)
+    g.manual_seed(2001)
+    caches = [(torch.randn((b, HKV, L + 8, D), generator=g, device=dev).to(torch.bfloat16),
+               torch.randn((b, HKV, L + 8, D), generator=g, device=dev).to(torch.bfloat16)) for _ in range(n_layers)]
+    q = torch.randn((b, HQ, D), generator=g, device=dev).to(torch.bfloat16)
+    nk = torch.randn((b, HKV, D), generator=g, device=dev).to(torch.bfloat16)
+    nv = torch.randn((b, HKV, D), generator=g, device=dev).to(torch.bfloat16)
+    kv_len = torch.full((b,), L, dtype=torch.int32, device=dev)
+    n_splits = ops.decode_splits(b, HKV, L)
+    ws = torch.empty(max(1, int(b * HQ * n_splits * (D + 2))), dtype=torch.float32, device=dev)
+    out = torch.empty((b, HQ * D), dtype=torch.bfloat16, device=dev)
+
+    def step():
+        for kc, vc in caches:
+            ops.sparse_decode_attn(q, kc, vc, kv_len, nk, nv, n_splits=n_splits, workspace=ws, out=out)
+    _time_ms(torch, step, 2, 2)
+    graph = torch.cuda.CUDAGraph()      # a decode loop replays its token step from a CUDA graph
+    with torch.cuda.graph(graph):
+        step()
+    ms = _time_ms(torch, graph.replay, steps, warmup) / n_layers
+    del graph
+    alg = 2 * b * (L + 1) * HKV * D * 2
+    gbs = alg / (ms / 1e3) / 1e9
+    return {"kernel": "decode_mma_kernel", "ms": ms, "algorithmic_bytes": alg, "achieved_gbs": gbs, "frac": gbs / pk["hbm_gbs"],
+            "bound": "hbm", "launches": (2 + (n_splits > 1)) * n_layers * steps,
+            "workload": f"benchmark config 5 layer: batch {b}, L={L}+1, 32q/8kv heads, d=128, bf16, {n_splits} KV "
+                        f"split(s), {n_layers} distinct caches of 285 MB rotate (> L2), CUDA-graph replay"}
+
+
+def leg_route_decode(torch, ops, dev, pk, steps=500, warmup=3, b=32):
+    docs_local = (N_DOCS + 7) // 8
+    c = docs_local * CHUNKS_PER_DOC
+    n_layers = 4
+    g = torch.Generator(device=dev)
+    g.manual_seed(2002)
+    banks = make_bank(torch, dev, docs_local, n_layers, seed=9000)
+    chunk_doc = torch.arange(1, docs_local + 1, device=dev, dtype=torch.int32).repeat_interleave(CHUNKS_PER_DOC)
+    q = torch.nn.functional.normalize(torch.randn((b, HQ, 1, D), generator=g, device=dev), dim=-1).to(torch.bfloat16)
+    mask = torch.ones((b, 1), dtype=torch.bool, device=dev)
+    keys = torch.empty((b, docs_local + 1), dtype=torch.int32, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    topk_ws = torch.empty((ops.topk_workspace_bytes(b, docs_local + 1, TOP_K) + 7) // 8, dtype=torch.int64, device=dev)
+    ev = []
+
+    def step(timed=False):
+        for rk in banks:
+            qf, bias, s_pad = ops.fold_queries(q, mask, HQ // HKV)
+            ops.route_table_reset(keys, docs_local, torch.finfo(torch.bfloat16).min, status)
+            if timed:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            ops.route_scores(qf, bias, b, s_pad, rk, chunk_doc, docs_local, 1.0 / HQ, keys=keys, status=status, flags=2)
+            if timed:
+                e1.record()
+                ev.append((e0, e1))
+            ops.topk_select(keys, TOP_K, workspace=topk_ws)
+    # the scoring kernel alone, eagerly, with events around each launch
+    _time_ms(torch, lambda: step(True), 5, warmup)
+    route_ms = statistics.mean([a.elapsed_time(b_) for a, b_ in ev[-5 * n_layers:]])
+    # the whole layer-step replayed from a CUDA graph, as a decode loop would issue it
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step(False)
+    ms = _time_ms(torch, graph.replay, steps, warmup) / n_layers
+    del graph
+    alg = c * HKV * D * 2 + b * HKV * D * 2
+    gbs = alg / (ms / 1e3) / 1e9
+    return {"kernel": "route_tc_kernel", "ms": ms, "algorithmic_bytes": alg, "achieved_gbs": gbs, "frac": gbs / pk["hbm_gbs"],
+            "bound": "hbm", "launches": 5 * n_layers * steps, "layer_step": "fold, table reset, scoring, two-level top-k (one CUDA graph)",
+            "route_kernel_ms": route_ms, "route_kernel_frac": alg / (route_ms / 1e3) / 1e9 / pk["hbm_gbs"],
+            "workload": f"benchmark config 5 per-step routing: {b} sequences x 1 token against {c} chunks (400 MB shard, one "
+                        f"of 8), {n_layers} distinct layers rotate"}
+
+
+def _secondary_line(args, metric, unit, value, leg, clocks, extra=None):
+    line = {"metric": metric, "value": value, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": leg["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": {"workload": leg["workload"]}, "gpu_launches": leg.get("launches"), "clocks": clocks,
+            "roofline": {"kernel": leg["kernel"], "bound": leg["bound"], "achieved": leg["achieved_gbs"],
+                         "peak": leg.get("peak", peaks()["hbm_gbs"]), "unit": "GB/s", "frac": leg["frac"], "traffic": None,
+                         "algorithmic_bytes_per_step": leg["algorithmic_bytes"]}}
+    line.update({k: v for k, v in leg.items() if k not in ("kernel", "bound", "achieved_gbs", "frac", "algorithmic_bytes",
+                                                            "workload", "launches", "ms", "peak")})
+    if extra:
+        line.update(extra)
+    print(json.dumps(line))
+
+
+def run_secondary(args):
+    import torch
+    from msa_b200 import ops
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    pk = peaks()
+    g = torch.Generator(device=dev)
+    g.manual_seed(2000)
+    sampler = ClockSampler(0)
+    steps, warmup = max(args.steps, 50), max(args.warmup, 3)   # short kernels: time many launches
+    args.steps, args.warmup = steps, warmup
+
+    if args.workload == "pooling":
+        sampler.start()
+        leg = leg_pooling(torch, ops, dev, pk, steps, warmup, 2048 if args.docs == N_DOCS else args.docs)
+        _secondary_line(args, "chunk-mean pooling tokens/s (K, V, K_r)", "tokens/s", leg["tokens_per_s"], leg, sampler.stop())
+
+    elif args.workload == "decode":
+        sampler.start()
+        leg = leg_decode(torch, ops, dev, pk, 10 * steps, warmup)
+        _secondary_line(args, "sparse decode attention layer-steps/s", "layer-steps/s", 1e3 / leg["ms"], leg, sampler.stop())
+
+    elif args.workload == "route-decode":
+        sampler.start()
+        leg = leg_route_decode(torch, ops, dev, pk, 10 * steps, warmup, b=32 if args.queries == N_QUERIES else args.queries)
+        _secondary_line(args, "decode-time routing layer-steps/s (one of 8 shards)", "layer-steps/s", 1e3 / leg["ms"], leg,
+                        sampler.stop())
+
+    elif args.workload == "fetch":
+        # host bank of 32,768 documents x 8 chunks (1.07 GB pinned); 128 queries x 16 winners per layer
+        pcie = measure_pcie(torch, dev)
+        n_docs, b, k = 32768, N_QUERIES, TOP_K
+        bank = torch.empty((n_docs * CHUNKS_PER_DOC, 2, HKV, D), dtype=torch.bfloat16).pin_memory()
+        bank.copy_(torch.randn(bank.shape, generator=g, device=dev).to(torch.bfloat16))
+        lens = torch.tensor([0] + [CHUNKS_PER_DOC] * n_docs, dtype=torch.int32, device=dev)
+        offs = torch.cumsum(torch.cat([torch.zeros(1, dtype=torch.long, device=dev), lens[:-1].long()]), 0)
+        base = torch.zeros(1, dtype=torch.long, device=dev)
+        kv_base = torch.tensor([bank.data_ptr()], dtype=torch.int64, device=dev)
+        gsel = torch.Generator().manual_seed(7)
+        sels = [torch.stack([torch.randperm(n_docs, generator=gsel)[:k] + 1 for _ in range(b)]).to(dev) for _ in range(4)]
+        n_entries = b * k * CHUNKS_PER_DOC
+        state = {"i": 0}
+
+        def step():
+            sel = sels[state["i"] % len(sels)]
+            state["i"] += 1
+            plan, n_sel, total = ops.gather_plan(sel, None, 1, base, offs, lens, kv_base, 2 * HKV * D * 2)
+            ops.gather_run(plan, torch.bfloat16, HKV, D, n_entries)
+        sampler.start()
+        ms = _time_ms(torch, step, steps, warmup)
+        clocks = sampler.stop()
+        alg = n_entries * 2 * HKV * D * 2
+        gbs = alg / (ms / 1e3) / 1e9
+        leg = {"kernel": "gather_kernel", "ms": ms, "algorithmic_bytes": alg, "achieved_gbs": gbs, "frac": gbs / pcie["h2d_gbs"],
+               "bound": "pcie", "peak": pcie["h2d_gbs"], "launches": 2 * steps, "pcie": pcie,
+               "workload": f"{b} queries x top-{k} documents x {CHUNKS_PER_DOC} chunks = {alg / 1e6:.0f} MB per layer from a "
+                           f"1.07 GB pinned host bank (plan + gather)"}
+        _secondary_line(args, "host K/V fetch documents/s", "documents/s", b * k / (ms / 1e3), leg, clocks)
+
+    elif args.workload == "prefill":
+        # stage 2 of one layer: 32 queries x 128 tokens, each with 3 template entries and 16 documents x 8 chunks
+        # retrieved -> contexts of 259 keys; several layers' tensors rotate so that inputs exceed L2
+        b, s_q, t_len, n_ret, n_layers = 32, 128, 3, TOP_K * CHUNKS_PER_DOC, 6
+        layers = []
+        for _ in range(n_layers):
+            layers.append(dict(
+                q=torch.randn((b, HQ, s_q, D), generator=g, device=dev).to(torch.bfloat16),
+                k=torch.randn((b, HKV, s_q, D), generator=g, device=dev).to(torch.bfloat16),
+                v=torch.randn((b, HKV, s_q, D), generator=g, device=dev).to(torch.bfloat16),
+                tk=torch.randn((1, HKV, t_len, D), generator=g, device=dev).to(torch.bfloat16),
+                tv=torch.randn((1, HKV, t_len, D), generator=g, device=dev).to(torch.bfloat16),
+                sk=torch.randn((HKV, b * n_ret, D), generator=g, device=dev).to(torch.bfloat16),
+                sv=torch.randn((HKV, b * n_ret, D), generator=g, device=dev).to(torch.bfloat16)))
+        valid = torch.ones((b, s_q), dtype=torch.bool, device=dev)
+        n_sel = torch.full((b,), n_ret, dtype=torch.int64, device=dev)
+        max_kv = t_len + n_ret + s_q
+        ev = []
+
+        def step(timed=False):
+            for L in layers:
+                ks, vs, st, ln, qt, nq, _ = ops.assemble_context(L["tk"], L["tv"], L["sk"], L["sv"], n_sel, L["k"], L["v"],
+                                                                 valid, max_kv, 0)
+                if timed:
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                ops.sparse_prefill_attn(L["q"], ks, vs, st, ln, qt, nq)
+                if timed:
+                    e1.record()
+                    ev.append((e0, e1))
+        _time_ms(torch, lambda: step(True), 5, warmup)
+        attn_ms = statistics.mean([a.elapsed_time(b_) for a, b_ in ev[-5 * n_layers:]])
+        lib_ms = None
+        try:    # the library call the reference makes at this point, on the same packed shapes (context only)
+            from flash_attn import flash_attn_varlen_func
+            cu_q = torch.arange(0, (b + 1) * s_q, s_q, dtype=torch.int32, device=dev)
+            cu_k = torch.arange(0, (b + 1) * max_kv, max_kv, dtype=torch.int32, device=dev)
+            qp = torch.randn((b * s_q, HQ, D), generator=g, device=dev).to(torch.bfloat16)
+            kp = torch.randn((b * max_kv, HKV, D), generator=g, device=dev).to(torch.bfloat16)
+            vp = torch.randn((b * max_kv, HKV, D), generator=g, device=dev).to(torch.bfloat16)
+            lib_ms = _time_ms(torch, lambda: flash_attn_varlen_func(qp, kp, vp, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k,
+                                                                    max_seqlen_q=s_q, max_seqlen_k=max_kv, causal=True),
+                              steps, warmup)
+        except Exception:
+            pass
+        sampler.start()
+        ms = _time_ms(torch, step, steps, warmup) / n_layers
+        clocks = sampler.stop()
+        # bytes one layer must move: q read + out written, K/V of template/retrieved/query read and written once by
+        # the assembly and read once more by the attention (they stay in L2 in between)
+        kv_bytes = 2 * b * max_kv * HKV * D * 2
+        alg = 2 * b * HQ * s_q * D * 2 + 2 * kv_bytes
+        flops = 4.0 * b * HQ * D * sum(t_len + n_ret + i + 1 for i in range(s_q))
+        gbs = alg / (ms / 1e3) / 1e9
+        leg = {"kernel": "prefill_attn_kernel", "ms": ms, "algorithmic_bytes": alg, "achieved_gbs": gbs, "frac": gbs / pk["hbm_gbs"],
+               "bound": "hbm", "launches": 2 * n_layers * steps,
+               "workload": f"{b} queries x {s_q} tokens, {t_len} template + {n_ret} retrieved entries, 32q/8kv heads, d=128, "
+                           f"bf16, {n_layers} layers' tensors rotate (> L2)",
+               "attention_kernel_ms": attn_ms, "attention_tflops": flops / (attn_ms / 1e3) / 1e12,
+               "library_varlen_attention_ms": lib_ms,
+               "note": "contexts of a few hundred keys: the kernel is latency / issue bound, far from either roof"}
+        _secondary_line(args, "stage-2 sparse prefill layer-steps/s (assembly + attention)", "layer-steps/s", 1e3 / ms, leg, clocks)
+
+    else:  # stage1
+        # benchmark config 2 shapes: documents of 512 tokens, 32 q / 8 kv heads, d = 128, chunk 64; one block row.
+        # 512 documents (262,144 tokens: q and out 2.1 GB each) keep the run short; time scales linearly in documents.
+        n_docs, doc_len, p = (512 if args.docs == N_DOCS else args.docs), 512, 64
+        t = n_docs * doc_len
+        doc_ids = torch.arange(1, n_docs + 1, device=dev).repeat_interleave(doc_len).view(1, t)
+        tok, off, _ = ops.chunk_bookkeeping(doc_ids, None, p)
+        seg = torch.arange(0, t + 1, doc_len, dtype=torch.int32, device=dev)
+        q = torch.randn((1, HQ, t, D), generator=g, device=dev).to(torch.bfloat16)
+        k = torch.randn((1, HKV, t, D), generator=g, device=dev).to(torch.bfloat16)
+        v = torch.randn((1, HKV, t, D), generator=g, device=dev).to(torch.bfloat16)
+        out = torch.zeros((1, t, HQ * D), dtype=torch.bfloat16, device=dev)
+
+        tc_status = torch.zeros(4, dtype=torch.int32, device=dev)
+
+        def step():      # what the layer mirror runs for unmasked documents: tcgen05 attention, then K and V pooled
+            ops.doc_attention_tc(q, k, v, tok, seg, doc_len, out=out, status=tc_status)
+            ops.pool_chunks(k, off, tok)
+            ops.pool_chunks(v, off, tok)
+        lib_ms = None
+        try:    # what the reference does at this point: the library's varlen attention, then K and V pooled separately
+            from flash_attn import flash_attn_varlen_func
+            qp, kp, vp = q[0].transpose(0, 1).contiguous(), k[0].transpose(0, 1).contiguous(), v[0].transpose(0, 1).contiguous()
+            lib_ms = _time_ms(torch, lambda: flash_attn_varlen_func(qp, kp, vp, cu_seqlens_q=seg, cu_seqlens_k=seg,
+                                                                    max_seqlen_q=doc_len, max_seqlen_k=doc_len, causal=True),
+                              10, 3)
+            del qp, kp, vp
+        except Exception:
+            pass
+        pool_ms = _time_ms(torch, lambda: (ops.pool_chunks(k, off, tok), ops.pool_chunks(v, off, tok)), 10, 3)
+        tc_ms = _time_ms(torch, lambda: ops.doc_attention_tc(q, k, v, tok, seg, doc_len, out=out, status=tc_status), 10, 3)
+        fused_ms = _time_ms(torch, lambda: ops.doc_attention_pool(q, k, v, tok, seg, doc_len, out=out, chunk_offsets=off,
+                                                                  pool_size=p), 10, 3)
+        steps = min(steps, 20)
+        args.steps = steps
+        sampler.start()
+        ms = _time_ms(torch, step, steps, warmup)
+        clocks = sampler.stop()
+        assert tc_status.cpu().tolist()[0] == 0, "a bounded wait ran out inside doc_attn_tc_kernel"
+        flops = 4.0 * n_docs * HQ * D * (doc_len * (doc_len + 1) / 2)          # causal: the part below the diagonal
+        n_tiles = n_docs * HQ * sum(range(1, doc_len // 128 + 1))                # 128 x 128 tiles the kernel executes
+        flops_exec = 4.0 * 128 * 128 * 128 * n_tiles
+        alg = 2 * t * HQ * D * 2 + 2 * t * HKV * D * 2 + 2 * (t // p) * HKV * D * 2
+        peak_tf = pk["tflops_burst"]
+        tf = flops_exec / (tc_ms / 1e3) / 1e12
+        gbs = alg / (ms / 1e3) / 1e9
+        leg = {"kernel": "doc_attn_tc_kernel", "ms": ms, "algorithmic_bytes": alg, "achieved_gbs": gbs, "frac": gbs / pk["hbm_gbs"],
+               "bound": "hbm", "launches": 3 * steps,
+               "workload": f"{n_docs} documents x {doc_len} tokens in one block row, 32q/8kv heads, d=128, chunk {p}, bf16 "
+                           f"(q and out {t * HQ * D * 2 / 1e9:.1f} GB each, > L2)"}
+        _secondary_line(args, "stage-1 document attention + K/V pooling tokens/s", "tokens/s", t / (ms / 1e3), leg, clocks,
+                        {"roofline": {"kernel": "doc_attn_tc_kernel", "bound": "tensor", "achieved": tf, "peak": peak_tf,
+                                      "unit": "TFLOP/s", "frac": tf / peak_tf, "traffic": None,
+                                      "flops_per_launch": flops_exec,
+                                      "note": "executed flops (whole 128 x 128 tiles, diagonal tiles included) over the "
+                                              "kernel's own time; peak = burst bf16 GEMM rate (kernel timed alone)"},
+                         "tcgen05_attention_ms": tc_ms, "tcgen05_attention_causal_tflops": flops / (tc_ms / 1e3) / 1e12,
+                         "separate_kv_pooling_ms": pool_ms,
+                         "mma_sync_attention_with_fused_pooling_ms": fused_ms,
+                         "library_varlen_attention_ms": lib_ms})
+
+
+# ------------------------------------------------------------------------------------------
+# the service over the config-4 bank (shared by the routing and the generate workloads)
+# ------------------------------------------------------------------------------------------
+def build_service(torch, dist, args, world, rank, local_rank, dev, layers, tag):
+    """MSAService over this rank's shard of the config-4 bank: router keys per layer in HBM, one layer's worth of
+    K/V (docs x 8 chunks x 4 KiB) in pinned host memory shared by all router layers, mapped by every rank."""
+    from msa_b200.memory import AttentionGeometry, Document, ModelConfig
+    from msa_b200.service import MSAService
+    n_docs = args.docs
+    per = (n_docs + world - 1) // world
+    d_lo, d_hi = min(n_docs, rank * per), min(n_docs, (rank + 1) * per)
+    docs_local = d_hi - d_lo
+    c_local = docs_local * CHUNKS_PER_DOC
+    shard_k = TOP_K if world == 1 else 2 * TOP_K
+    router_ids = [18 + i for i in range(layers)]
+    svc = MSAService(local_rank, None, ModelConfig(doc_top_k=TOP_K, router_layer_idx=",".join(map(str, router_ids))),
+                     None, AttentionGeometry(), world_size=world, rank=rank, shard_top_k=shard_k)
+    svc.block_desc.init_docs([Document(doc_id=d_lo + i, num_chunks=CHUNKS_PER_DOC) for i in range(docs_local)], dev)
+    svc.block_desc.pool_ids_from_docs(dev)
+    bank = make_bank(torch, dev, docs_local, layers, seed=4000 + 100 * rank)
+    for i, layer in enumerate(router_ids):
+        svc.blocks[layer].rk = bank[i]
+    fetch_note = None
+    try:
+        g_kv = torch.Generator(device=dev)
+        g_kv.manual_seed(77 + rank)
+        kv = torch.empty((c_local, 2, HKV, D), dtype=torch.bfloat16).pin_memory()
+        for c0 in range(0, c_local, 1 << 18):
+            n = min(1 << 18, c_local - c0)
+            kv[c0:c0 + n].copy_(torch.randn((n, 2, HKV, D), generator=g_kv, device=dev).to(torch.bfloat16))
+        first = router_ids[0]
+        for layer in router_ids:
+            svc.blocks[layer].kv, svc.blocks[layer].kv_device_address = kv, kv.data_ptr()
+        if world > 1:
+            shm = "/dev/shm"
+            need = c_local * 2 * HKV * D * 2
+            st = os.statvfs(shm)
+            if st.f_bavail * st.f_frsize < need * 1.1:
+                raise RuntimeError(f"{shm} has {st.f_bavail * st.f_frsize >> 20} MiB free, {need >> 20} MiB needed")
+            svc.router_layer_ids = router_ids[:1]          # one bank file per rank
+            svc.share_host_banks(tag=f"{tag}{os.environ.get('MASTER_PORT', '0')}")
+            svc.router_layer_ids = router_ids
+            base_, offs_, ln_, kvb = svc._directory
+            svc._directory = (base_, offs_, ln_, {layer: kvb[first] for layer in router_ids})
+            for layer in router_ids[1:]:
+                svc.blocks[layer].kv = svc.blocks[first].kv
+        else:
+            svc.publish_directory()
+    except Exception as e:  # the routing numbers stand without the fetch leg
+        fetch_note = f"fetch leg skipped: {e}"
+    return svc, docs_local, shard_k, router_ids, fetch_note
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
     from msa_b200 import ops
-    from msa_b200.memory import AttentionGeometry, Document, ModelConfig
-    from msa_b200.service import MSAService, all_gather_cat
+    from msa_b200.service import all_gather_cat
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -183,24 +768,21 @@ def run_ours(args):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    pk = peaks()
+    extras = not args.no_extras
 
     n_docs, layers, n_q = args.docs, args.layers, args.queries
-    per = (n_docs + world - 1) // world
-    d_lo, d_hi = min(n_docs, rank * per), min(n_docs, (rank + 1) * per)
-    docs_local = d_hi - d_lo
     b = n_q // world
     assert b * world == n_q, "queries must divide over the ranks"
-    shard_k = TOP_K if world == 1 else 2 * TOP_K
 
-    model_cfg = ModelConfig(doc_top_k=TOP_K, router_layer_idx=",".join(str(18 + i) for i in range(layers)))
-    svc = MSAService(local_rank, None, model_cfg, None, AttentionGeometry(), world_size=world, rank=rank,
-                     shard_top_k=shard_k)
-    docs = [Document(doc_id=d_lo + i, num_chunks=CHUNKS_PER_DOC) for i in range(docs_local)]
-    svc.block_desc.init_docs(docs, dev)
-    svc.block_desc.pool_ids_from_docs(dev)
-    bank = make_bank(torch, dev, docs_local, layers, seed=4000 + 100 * rank)
-    for i, layer in enumerate(svc.router_layer_ids):
-        svc.blocks[layer].rk = bank[i]
+    # ---- correctness first: doc_query at this world size against the oracle, on a small ragged bank
+    parity = None
+    if extras:
+        parity = parity_check(torch, dist, world, rank, local_rank, dev)
+    pcie = measure_pcie(torch, dev) if extras else None
+
+    svc, docs_local, shard_k, router_ids, fetch_note = build_service(torch, dist, args, world, rank, local_rank, dev,
+                                                                    layers, "bench")
 
     # queries: pinned host copy (e2e) and device copy (kernel-resident value)
     gq = torch.Generator(device=dev)
@@ -258,63 +840,50 @@ def run_ours(args):
     stage = [torch.empty_like(q_dev[0]) for _ in range(2)]
     res_host = [(torch.empty((b, TOP_K), dtype=torch.float32).pin_memory(),
                  torch.empty((b, TOP_K), dtype=torch.int64).pin_memory()) for _ in range(layers)]
-
-    # host-resident content bank (K then V per chunk), one layer's worth shared by all layers:
-    # docs_local x 8 chunks x 4 KiB per rank (6.4 GB over all ranks), mapped by every rank
-    fetch_note = None
-    try:
-        g_kv = torch.Generator(device=dev)
-        g_kv.manual_seed(77 + rank)
-        for layer in svc.router_layer_ids[:1]:
-            kv = torch.empty((c_local, 2, HKV, D), dtype=torch.bfloat16).pin_memory()
-            step_c = 1 << 18
-            for c0 in range(0, c_local, step_c):
-                n = min(step_c, c_local - c0)
-                kv[c0:c0 + n].copy_(torch.randn((n, 2, HKV, D), generator=g_kv, device=dev).to(torch.bfloat16))
-            svc.blocks[layer].kv = kv
-            svc.blocks[layer].kv_device_address = kv.data_ptr()
-        first = svc.router_layer_ids[0]
-        for layer in svc.router_layer_ids[1:]:
-            svc.blocks[layer].kv = svc.blocks[first].kv
-            svc.blocks[layer].kv_device_address = svc.blocks[first].kv_device_address
-        if world > 1:
-            shm = "/dev/shm"
-            need = c_local * 2 * HKV * D * 2
-            st = os.statvfs(shm)
-            if st.f_bavail * st.f_frsize < need * 1.1:
-                raise RuntimeError(f"{shm} has {st.f_bavail * st.f_frsize >> 20} MiB free, {need >> 20} MiB needed")
-            keep_ids = svc.router_layer_ids
-            svc.router_layer_ids = keep_ids[:1]          # one bank file per rank
-            svc.share_host_banks(tag=f"bench{os.environ.get('MASTER_PORT', '0')}")
-            svc.router_layer_ids = keep_ids
-            base_, offs_, ln_, kvb = svc._directory
-            svc._directory = (base_, offs_, ln_, {layer: kvb[first] for layer in keep_ids})
-            for layer in keep_ids[1:]:
-                svc.blocks[layer].kv = svc.blocks[first].kv
-        else:
-            svc.publish_directory()
-    except Exception as e:  # the routing numbers stand without the fetch leg
-        fetch_note = f"fetch leg skipped: {e}"
     fetch_stream = torch.cuda.Stream(dev)
     max_entries = b * TOP_K * CHUNKS_PER_DOC
     timeline = {}
 
+    def prefetch(i, ready, freed):
+        with torch.cuda.stream(copy_stream):
+            if i >= 2:
+                copy_stream.wait_event(freed[i - 2])
+            stage[i % 2].copy_(q_host[i], non_blocking=True)
+            ready[i].record(copy_stream)
+
     def step_e2e():
-        """Through MSAService.route / .fetch with host-resident queries: the copy stream brings layer
-        l+1's queries over PCIe while layer l is scored; layer l's winners' K/V are fetched from the
-        pinned host bank on a side stream while layer l+1 is scored; winners go back to host memory."""
+        """The reference-facing call: MSAService.doc_query per layer (route, merge, fetch of the winners' K/V from the
+        pinned host bank; one host read-back per layer sizes the result, as the contract of doc_query requires).  The
+        copy stream brings layer l+1's queries over PCIe while layer l runs; winners go back to host memory."""
+        main = torch.cuda.current_stream(dev)
+        ready = [torch.cuda.Event() for _ in range(layers)]
+        freed = [torch.cuda.Event() for _ in range(layers)]
+        prefetch(0, ready, freed)
+        for i, layer in enumerate(svc.router_layer_ids):
+            if i + 1 < layers:
+                prefetch(i + 1, ready, freed)
+            main.wait_event(ready[i])
+            if fetch_note is None:
+                fk, fv, sc, n_sel, gi = svc.doc_query(stage[i % 2], mask_dev, layer)
+            else:
+                sc, _, gi, _ = svc.route(stage[i % 2], mask_dev, layer)
+            freed[i].record(main)
+            res_host[i][0].copy_(sc, non_blocking=True)
+            res_host[i][1].copy_(gi, non_blocking=True)
+
+    def step_overlapped():
+        """The same work without the per-layer read-back (MSAService.route + fetch(max_entries=...)): layer l's
+        fetch runs on a side stream while layer l+1 is scored.  Reported under `fetch`, with its timeline."""
         main = torch.cuda.current_stream(dev)
         ready = [torch.cuda.Event() for _ in range(layers)]
         freed = [torch.cuda.Event() for _ in range(layers)]
         ev = {k_: [torch.cuda.Event(enable_timing=True) for _ in range(layers)] for k_ in ("rs", "re", "fs", "fe")}
         t0 = torch.cuda.Event(enable_timing=True)
         t0.record(main)
+        prefetch(0, ready, freed)
         for i, layer in enumerate(svc.router_layer_ids):
-            with torch.cuda.stream(copy_stream):
-                if i >= 2:
-                    copy_stream.wait_event(freed[i - 2])
-                stage[i % 2].copy_(q_host[i], non_blocking=True)
-                ready[i].record(copy_stream)
+            if i + 1 < layers:
+                prefetch(i + 1, ready, freed)
             main.wait_event(ready[i])
             ev["rs"][i].record(main)
             sc, li, gi, rk_ = svc.route(stage[i % 2], mask_dev, layer)
@@ -322,14 +891,13 @@ def run_ours(args):
             freed[i].record(main)
             res_host[i][0].copy_(sc, non_blocking=True)
             res_host[i][1].copy_(gi, non_blocking=True)
-            if fetch_note is None:
-                fetch_stream.wait_event(ev["re"][i])
-                with torch.cuda.stream(fetch_stream):
-                    ev["fs"][i].record(fetch_stream)
-                    fk, fv, n_sel, total = svc.fetch(li, rk_, layer, max_entries=max_entries)
-                    ev["fe"][i].record(fetch_stream)
-                    for t_ in (li, rk_, fk, fv):
-                        t_.record_stream(fetch_stream)
+            fetch_stream.wait_event(ev["re"][i])
+            with torch.cuda.stream(fetch_stream):
+                ev["fs"][i].record(fetch_stream)
+                fk, fv, n_sel, total = svc.fetch(li, rk_, layer, max_entries=max_entries)
+                ev["fe"][i].record(fetch_stream)
+                for t_ in (li, rk_, fk, fv):
+                    t_.record_stream(fetch_stream)
         main.wait_stream(fetch_stream)
         timeline["ev"], timeline["t0"] = ev, t0
 
@@ -366,6 +934,17 @@ def run_ours(args):
     route_ms = [a.elapsed_time(b_) for a, b_ in route_events]
     route_avg_ms = sum(route_ms) / len(route_ms)
 
+    # the table of the last timed layer is still in `keys`: spot-check it at full size (every rank its own shard)
+    spot = None
+    if extras:
+        spot = fullsize_spot_check(torch, ops, keys, q_dev[layers - 1], mask_dev, svc.blocks[svc.router_layer_ids[-1]].rk,
+                                   docs_local, rank * b, shard_k)
+        if world > 1:
+            flags = [None] * world
+            dist.all_gather_object(flags, spot)
+            spot = dict(flags[0], all_ranks_ok=all(f["scores_ok"] and f["topk_exact"] for f in flags),
+                        max_score_err=max(f["max_score_err"] for f in flags))
+
     for _ in range(max(1, args.warmup // 2)):
         step_e2e()
     ms_e2e = timed_region(step_e2e, args.steps)
@@ -373,6 +952,8 @@ def run_ours(args):
 
     fetch_report = {"note": fetch_note}
     if fetch_note is None:
+        step_overlapped()
+        ms_overlap = timed_region(step_overlapped, max(2, args.steps // 2)) / max(2, args.steps // 2)
         ev, t0 = timeline["ev"], timeline["t0"]
         rs = [t0.elapsed_time(e) for e in ev["rs"]]
         re_ = [t0.elapsed_time(e) for e in ev["re"]]
@@ -381,29 +962,67 @@ def run_ours(args):
         fetch_ms = [b_ - a_ for a_, b_ in zip(fs, fe)]
         hidden = sum(1 for i in range(layers - 1) if fe[i] <= re_[i + 1])
         fetch_bytes = b * TOP_K * CHUNKS_PER_DOC * 2 * HKV * D * 2
+        gbs = fetch_bytes / (sum(fetch_ms) / layers / 1e3) / 1e9
         fetch_report = {
-            "bytes_per_layer_per_gpu": fetch_bytes, "avg_ms": sum(fetch_ms) / layers,
-            "pcie_gbs": fetch_bytes / (sum(fetch_ms) / layers / 1e3) / 1e9,
+            "pipeline": "MSAService.route + fetch(max_entries) without the per-layer read-back: layer l's fetch on a side "
+                        "stream under layer l+1's scoring",
+            "queries_per_s_overlapped": n_q / (ms_overlap / 1e3),
+            "bytes_per_layer_per_gpu": fetch_bytes, "avg_ms": sum(fetch_ms) / layers, "pcie_gbs": gbs,
+            "frac_of_measured_pcie": gbs / pcie["h2d_gbs"] if pcie else None,
             "layers_hidden_behind_next_layer_scoring": f"{hidden}/{layers - 1}",
             "exposed_ms_after_last_layer": max(0.0, fe[-1] - re_[-1]),
             "timeline_ms_first_3_layers": [{"route": [round(rs[i], 3), round(re_[i], 3)],
                                             "fetch": [round(fs[i], 3), round(fe[i], 3)]} for i in range(min(3, layers))],
             "host_bank": "one layer's K/V bank (docs x 8 chunks x 4 KiB), pinned, shared by the 18 layers"}
-        if world > 1:
-            svc.close_host_banks()
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
-    pk = peaks()
+
+    # ---- the other numbers of the path, outside the timed regions
+    kernels = generate = incumbent = None
     ms_step = ms_total / args.steps
     value = n_q / (ms_step / 1e3)
+    if extras:
+        q_dev.clear()
+        stage.clear()
+        keys = None
+        torch.cuda.empty_cache()
+        kernels = {}
+        for name, fn in (("pooling", leg_pooling), ("decode_attention", leg_decode), ("route_decode", leg_route_decode)):
+            try:
+                leg = fn(torch, ops, dev, pk)
+                torch.cuda.empty_cache()
+                kernels[name] = {"kernel": leg["kernel"], "ms": leg["ms"], "algorithmic_bytes": leg["algorithmic_bytes"],
+                                 "achieved_gbs": leg["achieved_gbs"], "frac": leg["frac"], "peak_gbs": pk["hbm_gbs"],
+                                 "workload": leg["workload"],
+                                 **{k_: leg[k_] for k_ in ("route_kernel_ms", "route_kernel_frac", "layer_step", "tokens_per_s") if k_ in leg}}
+            except Exception as e:
+                kernels[name] = {"error": f"{type(e).__name__}: {e}"}
+        if world > 1:
+            dist.barrier()
+        try:
+            incumbent = incumbent_gpu(torch, dev, svc.blocks[svc.router_layer_ids[0]].rk, docs_local, value)
+        except Exception as e:
+            incumbent = {"error": f"{type(e).__name__}: {e}"}
+        if world > 1:
+            dist.barrier()
+        if fetch_note is None and layers == N_LAYERS:
+            try:
+                generate = generate_measure(torch, dist, svc, world, rank, local_rank, dev, n_docs, docs_local, 64)
+            except Exception as e:
+                generate = {"error": f"{type(e).__name__}: {e}"}
+    if world > 1 and fetch_note is None:
+        svc.close_host_banks()
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+            os._exit(0)      # CUDA graphs that captured NCCL kernels were alive: skip the communicator's teardown
+        return
     e2e_value = n_q / (ms_e2e / args.steps / 1e3)
     flops = 2.0 * n_all * s_pad * c_local * (HKV * D)
     achieved_tf = flops / (route_avg_ms / 1e3) / 1e12
     alg_bytes = c_local * HKV * D * 2 + n_all * s_pad * HKV * D * 2
     n_qtiles = (n_all * s_pad + 255) // 256
-    pair = ((c_local + 127) // 128) * n_qtiles >= 2 * 148          # the library's rule for the 2-CTA kernel
+    n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
+    pair = ((c_local + 127) // 128) * n_qtiles >= 2 * n_sm          # the library's rule for the 2-CTA kernel
     kernel_name = "route_tc_pair_kernel" if pair else "route_tc_kernel"
     traffic = ((n_qtiles + 63) // 64) * c_local * HKV * D * 2 + n_all * s_pad * HKV * D * 2
     line = {
@@ -415,12 +1034,15 @@ def run_ours(args):
                    "sharding": f"bank by document over {world} rank(s); every rank scores all queries; "
                                f"per-shard top-{shard_k}, all-gather merge",
                    "l2": "inputs per layer (router keys %.0f MB) exceed L2; 18 distinct layers per step" % (c_local * 2048 / 1e6)},
-        "e2e": {"value": e2e_value, "unit": "queries/s",
+        "e2e": {"value": e2e_value, "unit": "queries/s", "call": "MSAService.doc_query per layer, queries in pinned host memory",
                 "h2d_bytes_per_step": layers * (q_host[0].numel() * 2) * world,
-                "d2h_bytes_per_step": layers * b * TOP_K * 12 * world,
+                "d2h_bytes_per_step": layers * (b * TOP_K * 12 + 8 + 16) * world,
                 "host_to_device_fetch_bytes_per_step": 0 if fetch_note else layers * world * b * TOP_K * CHUNKS_PER_DOC * 2 * HKV * D * 2},
         "gpu_launches": n_launch,
-        "fetch": fetch_report,
+        "parity": None if parity is None else dict(parity, fullsize_spot_check=spot,
+                                                   ok=bool(parity["ok"] and spot["scores_ok"] and spot["topk_exact"]
+                                                           and spot.get("all_ranks_ok", True))),
+        "fetch": fetch_report, "pcie": pcie,
         "clocks": clocks,
         "roofline": {"kernel": kernel_name, "bound": "tensor", "achieved": achieved_tf, "peak": pk["tflops"],
                      "unit": "TFLOP/s", "frac": achieved_tf / pk["tflops"], "traffic": traffic,
@@ -431,359 +1053,35 @@ def run_ours(args):
                      "hbm": {"algorithmic_bytes_per_launch": alg_bytes,
                              "achieved_gbs": alg_bytes / (route_avg_ms / 1e3) / 1e9,
                              "frac_of_hbm": alg_bytes / (route_avg_ms / 1e3) / 1e9 / pk["hbm_gbs"]}},
+        "kernels": kernels, "generate": generate, "incumbent_gpu": incumbent,
+        "vs_incumbent": incumbent.get("vs_incumbent") if isinstance(incumbent, dict) else None,
     }
     if not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
-        v, sample, _ = cpu_reference_sample(threads)
-        line["cpu_baseline"] = {"value": v, "unit": "queries/s", "cores": threads, "kind": "port", "sample": sample}
-    print(json.dumps(line))
+        v, kind, sample, _ = cpu_reference_sample(threads)
+        line["cpu_baseline"] = {"value": v, "unit": "queries/s", "cores": threads, "kind": kind, "sample": sample}
+    print(json.dumps(line), flush=True)
+    ok = parity is None or line["parity"]["ok"]
     if world > 1:
-        dist.destroy_process_group()
-
-
-# ------------------------------------------------------------------------------------------
-# Secondary kernels: one JSON line each (single GPU), HBM or PCIe roofline.
-# ------------------------------------------------------------------------------------------
-def _time_ms(torch, fn, steps, warmup):
-    for _ in range(warmup):
-        fn()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        fn()
-    e1.record()
-    torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / steps
-
-
-def _secondary_line(args, metric, unit, value, ms, workload, kernel, alg_bytes, peak, peak_name, clocks, launches,
-                    extra=None):
-    gbs = alg_bytes / (ms / 1e3) / 1e9
-    line = {"metric": metric, "value": value, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic", "config": {"workload": workload}, "gpu_launches": launches, "clocks": clocks,
-            "roofline": {"kernel": kernel, "bound": "hbm" if peak_name == "hbm" else peak_name, "achieved": gbs,
-                         "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None,
-                         "algorithmic_bytes_per_step": alg_bytes}}
-    if extra:
-        line.update(extra)
-    print(json.dumps(line))
-
-
-def run_secondary(args):
-    import torch
-    from msa_b200 import ops
-    torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
-    pk = peaks()
-    g = torch.Generator(device=dev)
-    g.manual_seed(2000)
-    sampler = ClockSampler(0)
-    steps, warmup = max(args.steps, 50), max(args.warmup, 3)   # short kernels: time many launches
-    args.steps, args.warmup = steps, warmup
-
-    if args.workload == "pooling":
-        # benchmark config 2: 2,048 documents x 512 tokens, K / V / K_r bf16 [1, 8, T, 128], chunk 64
-        n_docs, doc_len, p = (2048 if args.docs == N_DOCS else args.docs), 512, 64
-        t = n_docs * doc_len
-        doc_ids = torch.arange(1, n_docs + 1, device=dev).repeat_interleave(doc_len).view(1, t)
-        tok, off, pooled = ops.chunk_bookkeeping(doc_ids, None, p)
-        ms_bk = _time_ms(torch, lambda: ops.chunk_bookkeeping(doc_ids, None, p, max_chunks=t // p + 1), 3, 1)
-        states = [torch.randn((1, HKV, t, D), generator=g, device=dev).to(torch.bfloat16) for _ in range(3)]
-
-        def step():
-            ops.pool_chunks(states[0], off, tok)
-            ops.pool_chunks(states[1], off, tok)
-            ops.pool_chunks(states[2], off, tok, l2_normalize=True)
-        sampler.start()
-        ms = _time_ms(torch, step, steps, warmup)
-        clocks = sampler.stop()
-        c = off.numel() - 1
-        alg = 3 * (t * HKV * D * 2 + c * HKV * D * 2)
-        _secondary_line(args, "chunk-mean pooling tokens/s (K, V, K_r)", "tokens/s", t / (ms / 1e3), ms,
-                        f"benchmark config 2: {n_docs} docs x {doc_len} tokens, chunk {p}, bf16, 3 tensors "
-                        f"({t * HKV * D * 2 / 1e9:.2f} GB each, > L2)", "pool_kernel", alg, pk["hbm_gbs"], "hbm", clocks, 3 * steps,
-                        {"bookkeeping_ms": ms_bk})
-
-    elif args.workload == "decode":
-        # benchmark config 5: batch 32, 32 q / 8 kv heads, L = 3 template + 128 retrieved + 2048 local
-        b, L, n_layers = 32, 3 + 128 + 2048, 4
-        caches = [(torch.randn((b, HKV, L + 8, D), generator=g, device=dev).to(torch.bfloat16),
-                   torch.randn((b, HKV, L + 8, D), generator=g, device=dev).to(torch.bfloat16)) for _ in range(n_layers)]
-        q = torch.randn((b, HQ, D), generator=g, device=dev).to(torch.bfloat16)
-        nk = torch.randn((b, HKV, D), generator=g, device=dev).to(torch.bfloat16)
-        nv = torch.randn((b, HKV, D), generator=g, device=dev).to(torch.bfloat16)
-        kv_len = torch.full((b,), L, dtype=torch.int32, device=dev)
-        n_splits = ops.decode_splits(b, HKV, L)
-        ws = torch.empty(max(1, int(b * HQ * n_splits * (D + 2))), dtype=torch.float32, device=dev)
-        out = torch.empty((b, HQ * D), dtype=torch.bfloat16, device=dev)
-
-        def step():
-            for kc, vc in caches:
-                ops.sparse_decode_attn(q, kc, vc, kv_len, nk, nv, n_splits=n_splits, workspace=ws, out=out)
-        _time_ms(torch, step, 2, 2)
-        graph = torch.cuda.CUDAGraph()      # a decode loop replays its token step from a CUDA graph
-        with torch.cuda.graph(graph):
-            step()
-        kv_len.fill_(L)
-        sampler.start()
-        ms = _time_ms(torch, graph.replay, 10 * steps, warmup) / n_layers
-        clocks = sampler.stop()
-        alg = 2 * b * (L + 1) * HKV * D * 2
-        _secondary_line(args, "sparse decode attention layer-steps/s", "layer-steps/s", 1e3 / ms, ms,
-                        f"benchmark config 5 layer: batch {b}, L={L}+1, 32q/8kv heads, d=128, bf16, {n_splits} KV "
-                        f"splits, {n_layers} distinct caches of 285 MB rotate (> L2)", "decode_mma_kernel", alg,
-                        pk["hbm_gbs"], "hbm", clocks, 3 * n_layers * steps)
-
-    elif args.workload == "fetch":
-        # host bank of 32,768 documents x 8 chunks (1.07 GB pinned); 128 queries x 16 winners per layer
-        n_docs, b, k = 32768, N_QUERIES, TOP_K
-        bank = torch.empty((n_docs * CHUNKS_PER_DOC, 2, HKV, D), dtype=torch.bfloat16).pin_memory()
-        bank.copy_(torch.randn(bank.shape, generator=g, device=dev).to(torch.bfloat16))
-        lens = torch.tensor([0] + [CHUNKS_PER_DOC] * n_docs, dtype=torch.int32, device=dev)
-        offs = torch.cumsum(torch.cat([torch.zeros(1, dtype=torch.long, device=dev), lens[:-1].long()]), 0)
-        base = torch.zeros(1, dtype=torch.long, device=dev)
-        kv_base = torch.tensor([bank.data_ptr()], dtype=torch.int64, device=dev)
-        gsel = torch.Generator().manual_seed(7)
-        sels = [torch.stack([torch.randperm(n_docs, generator=gsel)[:k] + 1 for _ in range(b)]).to(dev) for _ in range(4)]
-        n_entries = b * k * CHUNKS_PER_DOC
-        state = {"i": 0}
-
-        def step():
-            sel = sels[state["i"] % len(sels)]
-            state["i"] += 1
-            plan, n_sel, total = ops.gather_plan(sel, None, 1, base, offs, lens, kv_base, 2 * HKV * D * 2)
-            ops.gather_run(plan, torch.bfloat16, HKV, D, n_entries)
-        sampler.start()
-        ms = _time_ms(torch, step, steps, warmup)
-        clocks = sampler.stop()
-        alg = n_entries * 2 * HKV * D * 2
-        _secondary_line(args, "host K/V fetch documents/s", "documents/s", b * k / (ms / 1e3), ms,
-                        f"{b} queries x top-{k} documents x {CHUNKS_PER_DOC} chunks = {alg / 1e6:.0f} MB per layer from a "
-                        f"1.07 GB pinned host bank (plan + gather)", "gather_kernel", alg, 55.0, "pcie", clocks,
-                        2 * steps, {"note": "peak = 55 GB/s, a nominal PCIe Gen5 x16 payload rate (not measured)"})
-
-    elif args.workload == "prefill":
-        # stage 2 of one layer: 32 queries x 128 tokens, each with 3 template entries and 16 documents x 8 chunks
-        # retrieved -> contexts of 259 keys; several layers' tensors rotate so that inputs exceed L2
-        b, s_q, t_len, n_ret, n_layers = 32, 128, 3, TOP_K * CHUNKS_PER_DOC, 6
-        layers = []
-        for _ in range(n_layers):
-            layers.append(dict(
-                q=torch.randn((b, HQ, s_q, D), generator=g, device=dev).to(torch.bfloat16),
-                k=torch.randn((b, HKV, s_q, D), generator=g, device=dev).to(torch.bfloat16),
-                v=torch.randn((b, HKV, s_q, D), generator=g, device=dev).to(torch.bfloat16),
-                tk=torch.randn((1, HKV, t_len, D), generator=g, device=dev).to(torch.bfloat16),
-                tv=torch.randn((1, HKV, t_len, D), generator=g, device=dev).to(torch.bfloat16),
-                sk=torch.randn((HKV, b * n_ret, D), generator=g, device=dev).to(torch.bfloat16),
-                sv=torch.randn((HKV, b * n_ret, D), generator=g, device=dev).to(torch.bfloat16)))
-        valid = torch.ones((b, s_q), dtype=torch.bool, device=dev)
-        n_sel = torch.full((b,), n_ret, dtype=torch.int64, device=dev)
-        max_kv = t_len + n_ret + s_q
-        ev = []
-
-        def step(timed=False):
-            for L in layers:
-                ks, vs, st, ln, qt, nq, _ = ops.assemble_context(L["tk"], L["tv"], L["sk"], L["sv"], n_sel, L["k"], L["v"],
-                                                                 valid, max_kv, 0)
-                if timed:
-                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    e0.record()
-                ops.sparse_prefill_attn(L["q"], ks, vs, st, ln, qt, nq)
-                if timed:
-                    e1.record()
-                    ev.append((e0, e1))
-        _time_ms(torch, lambda: step(True), 5, warmup)
-        attn_ms = statistics.mean([a.elapsed_time(b_) for a, b_ in ev[-5 * n_layers:]])
-        lib_ms = None
-        try:    # the library call the reference makes at this point, on the same packed shapes (context only)
-            from flash_attn import flash_attn_varlen_func
-            cu_q = torch.arange(0, (b + 1) * s_q, s_q, dtype=torch.int32, device=dev)
-            cu_k = torch.arange(0, (b + 1) * max_kv, max_kv, dtype=torch.int32, device=dev)
-            qp = torch.randn((b * s_q, HQ, D), generator=g, device=dev).to(torch.bfloat16)
-            kp = torch.randn((b * max_kv, HKV, D), generator=g, device=dev).to(torch.bfloat16)
-            vp = torch.randn((b * max_kv, HKV, D), generator=g, device=dev).to(torch.bfloat16)
-            lib_ms = _time_ms(torch, lambda: flash_attn_varlen_func(qp, kp, vp, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k,
-                                                                    max_seqlen_q=s_q, max_seqlen_k=max_kv, causal=True),
-                              steps, warmup)
-        except Exception:
-            pass
-        sampler.start()
-        ms = _time_ms(torch, step, steps, warmup) / n_layers
-        clocks = sampler.stop()
-        # bytes one layer must move: q read + out written, K/V of template/retrieved/query read and written once by
-        # the assembly and read once more by the attention (they stay in L2 in between)
-        kv_bytes = 2 * b * max_kv * HKV * D * 2
-        alg = 2 * b * HQ * s_q * D * 2 + 2 * kv_bytes
-        flops = 4.0 * b * HQ * D * sum(t_len + n_ret + i + 1 for i in range(s_q))
-        _secondary_line(args, "stage-2 sparse prefill layer-steps/s (assembly + attention)", "layer-steps/s", 1e3 / ms, ms,
-                        f"{b} queries x {s_q} tokens, {t_len} template + {n_ret} retrieved entries, 32q/8kv heads, d=128, "
-                        f"bf16, {n_layers} layers' tensors rotate (> L2)", "prefill_attn_kernel", alg, pk["hbm_gbs"], "hbm",
-                        clocks, 2 * n_layers * steps,
-                        {"attention_kernel_ms": attn_ms, "attention_tflops": flops / (attn_ms / 1e3) / 1e12,
-                         "library_varlen_attention_ms": lib_ms,
-                         "note": "contexts of a few hundred keys: the kernel is latency / issue bound, far from either roof"})
-
-    elif args.workload == "stage1":
-        # benchmark config 2 shapes: documents of 512 tokens, 32 q / 8 kv heads, d = 128, chunk 64; one block row.
-        # 512 documents (262,144 tokens: q and out 2.1 GB each) keep the run short; time scales linearly in documents.
-        n_docs, doc_len, p = (512 if args.docs == N_DOCS else args.docs), 512, 64
-        t = n_docs * doc_len
-        doc_ids = torch.arange(1, n_docs + 1, device=dev).repeat_interleave(doc_len).view(1, t)
-        tok, off, _ = ops.chunk_bookkeeping(doc_ids, None, p)
-        seg = torch.arange(0, t + 1, doc_len, dtype=torch.int32, device=dev)
-        q = torch.randn((1, HQ, t, D), generator=g, device=dev).to(torch.bfloat16)
-        k = torch.randn((1, HKV, t, D), generator=g, device=dev).to(torch.bfloat16)
-        v = torch.randn((1, HKV, t, D), generator=g, device=dev).to(torch.bfloat16)
-        out = torch.zeros((1, t, HQ * D), dtype=torch.bfloat16, device=dev)
-
-        tc_status = torch.zeros(4, dtype=torch.int32, device=dev)
-
-        def step():      # what the layer mirror runs for unmasked documents: tcgen05 attention, then K and V pooled
-            ops.doc_attention_tc(q, k, v, tok, seg, doc_len, out=out, status=tc_status)
-            ops.pool_chunks(k, off, tok)
-            ops.pool_chunks(v, off, tok)
-        lib_ms = None
-        try:    # what the reference does at this point: the library's varlen attention, then K and V pooled separately
-            from flash_attn import flash_attn_varlen_func
-            qp, kp, vp = q[0].transpose(0, 1).contiguous(), k[0].transpose(0, 1).contiguous(), v[0].transpose(0, 1).contiguous()
-            lib_ms = _time_ms(torch, lambda: flash_attn_varlen_func(qp, kp, vp, cu_seqlens_q=seg, cu_seqlens_k=seg,
-                                                                    max_seqlen_q=doc_len, max_seqlen_k=doc_len, causal=True),
-                              10, 3)
-            del qp, kp, vp
-        except Exception:
-            pass
-        pool_ms = _time_ms(torch, lambda: (ops.pool_chunks(k, off, tok), ops.pool_chunks(v, off, tok)), 10, 3)
-        tc_ms = _time_ms(torch, lambda: ops.doc_attention_tc(q, k, v, tok, seg, doc_len, out=out, status=tc_status), 10, 3)
-        fused_ms = _time_ms(torch, lambda: ops.doc_attention_pool(q, k, v, tok, seg, doc_len, out=out, chunk_offsets=off,
-                                                                  pool_size=p), 10, 3)
-        steps = min(steps, 20)
-        args.steps = steps
-        sampler.start()
-        ms = _time_ms(torch, step, steps, warmup)
-        clocks = sampler.stop()
-        assert tc_status.cpu().tolist()[0] == 0, "a bounded wait ran out inside doc_attn_tc_kernel"
-        flops = 4.0 * n_docs * HQ * D * (doc_len * (doc_len + 1) / 2)          # causal: the part below the diagonal
-        n_tiles = n_docs * HQ * sum(range(1, doc_len // 128 + 1))                # 128 x 128 tiles the kernel executes
-        flops_exec = 4.0 * 128 * 128 * 128 * n_tiles
-        alg = 2 * t * HQ * D * 2 + 2 * t * HKV * D * 2 + 2 * (t // p) * HKV * D * 2
-        peak_tf = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"] \
-            if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else 1590.0
-        tf = flops_exec / (tc_ms / 1e3) / 1e12
-        _secondary_line(args, "stage-1 document attention + K/V pooling tokens/s", "tokens/s", t / (ms / 1e3), ms,
-                        f"{n_docs} documents x {doc_len} tokens in one block row, 32q/8kv heads, d=128, chunk {p}, bf16 "
-                        f"(q and out {t * HQ * D * 2 / 1e9:.1f} GB each, > L2)", "doc_attn_tc_kernel", alg, pk["hbm_gbs"],
-                        "hbm", clocks, 3 * steps,
-                        {"roofline": {"kernel": "doc_attn_tc_kernel", "bound": "tensor", "achieved": tf, "peak": peak_tf,
-                                      "unit": "TFLOP/s", "frac": tf / peak_tf, "traffic": None,
-                                      "flops_per_launch": flops_exec,
-                                      "note": "executed flops (whole 128 x 128 tiles, diagonal tiles included) over the "
-                                              "kernel's own time; peak = burst bf16 GEMM rate (kernel timed alone). The kernel "
-                                              "is bound by the exponentials: 16,384 per tile at 16 per clock per SM = 0.54 us "
-                                              "against 0.28 us of MMA per tile"},
-                         "tcgen05_attention_ms": tc_ms, "tcgen05_attention_causal_tflops": flops / (tc_ms / 1e3) / 1e12,
-                         "separate_kv_pooling_ms": pool_ms,
-                         "mma_sync_attention_with_fused_pooling_ms": fused_ms,
-                         "library_varlen_attention_ms": lib_ms})
-
-    else:  # route-decode: benchmark config 5 per-step routing on one of 8 shards
-        b, docs_local = 32, (N_DOCS + 7) // 8
-        c = docs_local * CHUNKS_PER_DOC
-        n_layers = 4
-        banks = make_bank(torch, dev, docs_local, n_layers, seed=9000)
-        chunk_doc = torch.arange(1, docs_local + 1, device=dev, dtype=torch.int32).repeat_interleave(CHUNKS_PER_DOC)
-        q = torch.nn.functional.normalize(torch.randn((b, HQ, 1, D), generator=g, device=dev), dim=-1).to(torch.bfloat16)
-        mask = torch.ones((b, 1), dtype=torch.bool, device=dev)
-        keys = torch.empty((b, docs_local + 1), dtype=torch.int32, device=dev)
-        status = torch.zeros(4, dtype=torch.int32, device=dev)
-        topk_ws = torch.empty((ops.topk_workspace_bytes(b, docs_local + 1, TOP_K) + 7) // 8, dtype=torch.int64, device=dev)
-        ev = []
-
-        def step(timed=False):
-            for rk in banks:
-                qf, bias, s_pad = ops.fold_queries(q, mask, HQ // HKV)
-                ops.route_table_reset(keys, docs_local, torch.finfo(torch.bfloat16).min, status)
-                if timed:
-                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    e0.record()
-                ops.route_scores(qf, bias, b, s_pad, rk, chunk_doc, docs_local, 1.0 / HQ, keys=keys, status=status,
-                                 flags=2)
-                if timed:
-                    e1.record()
-                    ev.append((e0, e1))
-                ops.topk_select(keys, TOP_K, workspace=topk_ws)
-        # the scoring kernel alone, eagerly, with events around each launch
-        _time_ms(torch, lambda: step(True), 5, warmup)
-        route_ms = statistics.mean([a.elapsed_time(b_) for a, b_ in ev[-5 * n_layers:]])
-        # the whole layer-step replayed from a CUDA graph: at ~100 us per layer the Python
-        # launch path would otherwise be the bottleneck, as it would be in a real decode loop
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            step(False)
-        sampler.start()
-        ms = _time_ms(torch, graph.replay, 10 * steps, warmup) / n_layers
-        clocks = sampler.stop()
-        alg = c * HKV * D * 2 + b * HKV * D * 2
-        _secondary_line(args, "decode-time routing layer-steps/s (one of 8 shards)", "layer-steps/s", 1e3 / ms, ms,
-                        f"benchmark config 5 per-step routing: {b} sequences x 1 token against {c} chunks (400 MB shard), "
-                        f"{n_layers} distinct layers rotate", "route_tc_kernel", alg, pk["hbm_gbs"], "hbm", clocks,
-                        5 * n_layers * 10 * steps, {"launch": "one CUDA graph per step (fold, reset, score, top-k)",
-                                                    "route_kernel_ms": route_ms,
-                                               "route_kernel_gbs": alg / (route_ms / 1e3) / 1e9,
-                                               "route_kernel_frac": alg / (route_ms / 1e3) / 1e9 / pk["hbm_gbs"]})
+        dist.barrier()
+        torch.cuda.synchronize(dev)
+        sys.stdout.flush()
+        os._exit(0 if ok else 3)
+    if not ok:
+        raise SystemExit("parity check failed: " + json.dumps(line["parity"]))
 
 
 # ------------------------------------------------------------------------------------------
 # benchmark config 5: end-to-end sparse generation step (Qwen3-4B-shaped decoder, random weights)
 # ------------------------------------------------------------------------------------------
-def run_generate(args):
-    import torch
-    import torch.distributed as dist
+def generate_measure(torch, dist, svc, world, rank, local_rank, dev, n_docs, docs_local, new_tokens, full=False):
+    """tokens/s of the config-5 decode loop over `svc` (router layers 18-35 route every step, the winners' K/V come
+    from the pinned host bank).  Returns a dict; rank 0's is the one that is printed."""
     from msa_b200.decoder import DecoderShape, SparseDecodeModel
-    from msa_b200.memory import AttentionGeometry, Document, ModelConfig
-    from msa_b200.service import MSAService
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    n_docs, batch_total, local_ctx, new_tokens = args.docs, 32, 2048, args.new_tokens
+    batch_total, local_ctx = 32, 2048
     router_ids = list(range(18, 36))
-    per = (n_docs + world - 1) // world
-    d_lo, d_hi = min(n_docs, rank * per), min(n_docs, (rank + 1) * per)
-    docs_local, b = d_hi - d_lo, batch_total // world
-    c_local = docs_local * CHUNKS_PER_DOC
-    shard_k = TOP_K if world == 1 else 2 * TOP_K
-    svc = MSAService(local_rank, None, ModelConfig(doc_top_k=TOP_K, router_layer_idx=",".join(map(str, router_ids))),
-                     None, AttentionGeometry(), world_size=world, rank=rank, shard_top_k=shard_k)
+    b = batch_total // world
     svc.uniform_seqlen = True
-    svc.block_desc.init_docs([Document(doc_id=d_lo + i, num_chunks=CHUNKS_PER_DOC) for i in range(docs_local)], dev)
-    svc.block_desc.pool_ids_from_docs(dev)
-    bank = make_bank(torch, dev, docs_local, len(router_ids), seed=4000 + 100 * rank)
-    g_kv = torch.Generator(device=dev)
-    g_kv.manual_seed(77 + rank)
-    kv = torch.empty((c_local, 2, HKV, D), dtype=torch.bfloat16).pin_memory()
-    for c0 in range(0, c_local, 1 << 18):
-        n = min(1 << 18, c_local - c0)
-        kv[c0:c0 + n].copy_(torch.randn((n, 2, HKV, D), generator=g_kv, device=dev).to(torch.bfloat16))
-    for i, layer in enumerate(router_ids):
-        svc.blocks[layer].rk, svc.blocks[layer].kv, svc.blocks[layer].kv_device_address = bank[i], kv, kv.data_ptr()
-    first = router_ids[0]
-    if world > 1:
-        svc.router_layer_ids = router_ids[:1]
-        svc.share_host_banks(tag=f"gen{os.environ.get('MASTER_PORT', '0')}")
-        svc.router_layer_ids = router_ids
-        base_, offs_, ln_, kvb = svc._directory
-        svc._directory = (base_, offs_, ln_, {layer: kvb[first] for layer in router_ids})
-        for layer in router_ids[1:]:
-            svc.blocks[layer].kv = svc.blocks[first].kv
-    else:
-        svc.publish_directory()
-
     model = SparseDecodeModel(DecoderShape(), svc, router_ids, b, local_ctx, new_tokens + 8,
                               TOP_K * CHUNKS_PER_DOC, dev, seed=10 + rank)
 
@@ -797,8 +1095,6 @@ def run_generate(args):
     for _ in range(2):
         model.step()
     model.probe = {}
-    t0 = torch.cuda.Event(enable_timing=True)
-    t0.record()
     model.step()
     torch.cuda.synchronize(dev)
     pr, model.probe = model.probe, None
@@ -847,40 +1143,66 @@ def run_generate(args):
         sampler.start()
     ms_total, mode = timed_run(True)
     clocks = sampler.stop() if rank == 0 else None
-    ms_plain, _ = timed_run(True, pipelined=False)   # unrotated loop: the fetch has only the rest of its own step
     ms_nofetch, _ = timed_run(False)       # same step without the host fetch: what the fetch may hide behind
+    ms_plain = timed_run(True, pipelined=False)[0] if full else None   # unrotated loop
     svc.check_status()
+    model.check_fetch_counts()
     tokens_host = model.tokens.cpu()
+    value = batch_total * new_tokens / (ms_total / 1e3)
+    per_step_bytes = (sum(p_.numel() for l_ in model.layers for p_ in l_.values()) + model.lm_head.numel()) * 2
+    out = {
+        "value": value, "unit": "tokens/s", "new_tokens": new_tokens, "ms_per_step": ms_total / new_tokens, "launch": mode,
+        "workload": f"benchmark config 5: Qwen3-4B-shaped decoder (36 layers, hidden 2560, 32q/8kv, d 128, FFN 9728, "
+                    f"vocab 151936, random weights), routing in layers 18-35 every step against {n_docs} docs x "
+                    f"{CHUNKS_PER_DOC} chunks, top-{TOP_K}, batch {batch_total}, {local_ctx}-token local context",
+        "parallelism": f"sequences and bank split over {world} rank(s); weights replicated",
+        "per_layer": {"routing_ms_avg": sum(route_ms) / len(route_ms), "attention_ms_avg": sum(attn_ms) / len(attn_ms),
+                      "measured": "eager step, CUDA events"},
+        "fetch": {"ms_per_step_with_fetch": ms_total / new_tokens, "ms_per_step_without_fetch": ms_nofetch / new_tokens,
+                  "ms_per_step_unrotated_loop": None if ms_plain is None else ms_plain / new_tokens,
+                  "loop": "rotated to start at the first router layer: layers 18-35 of step t, sampling, layers 0-17 "
+                          "of step t+1; the fetch issued in step t is needed by layer 18 of step t+1",
+                  "exposed_ms_per_step": max(0.0, (ms_total - ms_nofetch) / new_tokens),
+                  "pcie_bytes_per_step_per_gpu": 18 * b * TOP_K * CHUNKS_PER_DOC * 2 * HKV * D * 2},
+        "dense_weight_bytes_per_step": per_step_bytes, "clocks": clocks,
+        # this package's kernels per step: per layer add+norm x2, q/k norm+rope, decode attention (+ combine),
+        # SiLU*up; per router layer fold, table fill, scoring, top-k x2, merge, gather plan, gather; final norm
+        "gpu_launches": new_tokens * (36 * 5 + 18 * 8 + 1), "last_tokens": tokens_host[:4].tolist()}
+    del model
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_generate(args):
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    svc, docs_local, shard_k, router_ids, fetch_note = build_service(torch, dist, args, world, rank, local_rank, dev,
+                                                                    N_LAYERS, "gen")
+    if fetch_note is not None:
+        raise SystemExit(fetch_note)
+    g = generate_measure(torch, dist, svc, world, rank, local_rank, dev, args.docs, docs_local, args.new_tokens, full=True)
     if world > 1:
         svc.close_host_banks()
     if rank == 0:
-        value = batch_total * new_tokens / (ms_total / 1e3)
-        per_step_bytes = (sum(p_.numel() for l_ in model.layers for p_ in l_.values()) + model.lm_head.numel()) * 2
+        batch_total = 32
         print(json.dumps({
-            "metric": "sparse generation tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world,
-            "steps": new_tokens, "warmup": 3, "ms_per_step": ms_total / new_tokens, "higher_is_better": True,
+            "metric": "sparse generation tokens/s", "value": g["value"], "unit": "tokens/s", "n_gpus": world,
+            "steps": args.new_tokens, "warmup": 3, "ms_per_step": g["ms_per_step"], "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"benchmark config 5: Qwen3-4B-shaped decoder (36 layers, hidden 2560, 32q/8kv, d 128, FFN 9728, "
-                                   f"vocab 151936, random weights), routing in layers 18-35 every step against {n_docs} docs x "
-                                   f"{CHUNKS_PER_DOC} chunks, top-{TOP_K}, batch {batch_total}, {local_ctx}-token local context, "
-                                   f"{new_tokens} new tokens", "launch": mode,
-                       "parallelism": f"sequences and bank split over {world} rank(s); weights replicated"},
-            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+            "config": {"workload": g["workload"] + f", {args.new_tokens} new tokens", "launch": g["launch"],
+                       "parallelism": g["parallelism"]},
+            "e2e": {"value": g["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                     "note": "tokens are produced and consumed on the device; the only host traffic is the K/V fetch",
                     "host_to_device_fetch_bytes_per_step": 18 * batch_total * TOP_K * CHUNKS_PER_DOC * 2 * HKV * D * 2},
-            "per_layer": {"routing_ms_avg": sum(route_ms) / len(route_ms), "attention_ms_avg": sum(attn_ms) / len(attn_ms),
-                          "measured": "eager step, CUDA events"},
-            "fetch": {"ms_per_step_with_fetch": ms_total / new_tokens, "ms_per_step_without_fetch": ms_nofetch / new_tokens,
-                      "ms_per_step_unrotated_loop": ms_plain / new_tokens,
-                      "loop": "rotated to start at the first router layer: layers 18-35 of step t, sampling, layers 0-17 "
-                              "of step t+1; the fetch issued in step t is needed by layer 18 of step t+1",
-                      "exposed_ms_per_step": max(0.0, (ms_total - ms_nofetch) / new_tokens),
-                      "note": "the run without the fetch is a diagnostic; on 8 GPUs it has measured slower than the run with it",
-                      "pcie_bytes_per_step_per_gpu": 18 * b * TOP_K * CHUNKS_PER_DOC * 2 * HKV * D * 2},
-            "dense_weight_bytes_per_step": per_step_bytes, "clocks": clocks,
-            # this package's kernels per step: per layer add+norm x2, q/k norm+rope, decode attention (+ combine),
-            # SiLU*up; per router layer fold, table fill, scoring, top-k x2, merge, gather plan, gather; final norm
-            "gpu_launches": new_tokens * (36 * 5 + 18 * 8 + 1), "last_tokens": tokens_host[:4].tolist()}), flush=True)
+            "per_layer": g["per_layer"], "fetch": g["fetch"], "dense_weight_bytes_per_step": g["dense_weight_bytes_per_step"],
+            "clocks": g["clocks"], "gpu_launches": g["gpu_launches"], "last_tokens": g["last_tokens"]}), flush=True)
     if world > 1:
         # graphs that captured NCCL kernels were alive in this process: leave without tearing the
         # communicator down (its destructor can wait forever on them)

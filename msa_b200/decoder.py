@@ -106,6 +106,12 @@ class SparseDecodeModel:
         self._cos = torch.zeros((batch, 1, s.head_dim), dtype=dtype, device=device)
         self._sin = torch.zeros((batch, 1, s.head_dim), dtype=dtype, device=device)
         self.probe = None  # set to a dict to collect per-layer CUDA events (eager profiling step)
+        # The cache layout [template | retrieved | local] gives every sequence exactly `retrieved_entries`
+        # positions for fetched entries; a step whose winners hold fewer would leave the previous step's entries
+        # in the tail of the segment.  The smallest count seen per router layer is tracked on the device and
+        # checked by check_fetch_counts().
+        self._n_sel_min = {l: torch.full((), retrieved_entries, dtype=torch.int64, device=device)
+                           for l in self.router_layers}
 
     # ------------------------------------------------------------------------------------
     def _rope(self, x, cos, sin):
@@ -160,11 +166,11 @@ class SparseDecodeModel:
                 after_attn.record(main)
                 self.fetch_stream.wait_event(after_attn)
                 with torch.cuda.stream(self.fetch_stream):
-                    fk, fv, n_sel, total = self.svc.fetch(local, rank, l, max_entries=B * self.retrieved, max_ctas=24)
-                    lo_, hi_ = s.template_len, s.template_len + self.retrieved
-                    self.k_cache[l][:, :, lo_:hi_].copy_(fk.view(nkv, B, self.retrieved, d).permute(1, 0, 2, 3))
-                    self.v_cache[l][:, :, lo_:hi_].copy_(fv.view(nkv, B, self.retrieved, d).permute(1, 0, 2, 3))
-                    for t_ in (local, rank, fk, fv):
+                    # the gather writes every sequence's entries into its own retrieved segment of the cache
+                    n_sel = self.svc.fetch_into(local, rank, l, self.k_cache[l], self.v_cache[l], s.template_len,
+                                                self.retrieved, max_ctas=24)
+                    torch.minimum(self._n_sel_min[l], n_sel.min(), out=self._n_sel_min[l])
+                    for t_ in (local, rank, n_sel):
                         t_.record_stream(self.fetch_stream)
                     done = torch.cuda.Event(enable_timing=self.probe is not None)
                     done.record(self.fetch_stream)
@@ -231,6 +237,15 @@ class SparseDecodeModel:
         self._front()
         torch.cuda.current_stream(self.device).wait_stream(self.fetch_stream)
         return nxt
+
+    def check_fetch_counts(self):
+        """Raise if some step fetched fewer entries for a sequence than its retrieved segment holds (documents of
+        varying length, invalid winners): this loop's fixed cache layout needs ``retrieved_entries`` per step."""
+        torch.cuda.synchronize(self.device)
+        low = {l: int(v.item()) for l, v in self._n_sel_min.items() if int(v.item()) < self.retrieved}
+        if low:
+            raise RuntimeError(f"router layers {sorted(low)} fetched as few as {min(low.values())} entries for a sequence; "
+                               f"the decode loop's cache layout holds exactly {self.retrieved} retrieved entries")
 
     def reset(self):
         self.kv_len.fill_(self.ctx0)

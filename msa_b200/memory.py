@@ -147,6 +147,65 @@ class BlockData:
         return self.rk
 
 
+def is_reference_bank(path: str) -> bool:
+    """True when ``path`` holds a bank written by the reference's ``Memory.serialize``
+    (src/msa_service.py:351-420: ``stub.json``, ``meta.pt``, ``layer_<l>_{k,v,rk}.pt``) and not one of this
+    package's (``meta.json``)."""
+    return (not os.path.exists(os.path.join(path, "meta.json"))
+            and (os.path.exists(os.path.join(path, "stub.json")) or os.path.exists(os.path.join(path, "meta.pt"))))
+
+
+def convert_reference_bank(src_dir: str, dst_dir: str) -> dict:
+    """One-time conversion of a bank directory written by the reference (head-major ``[1, Hkv, C, D]`` tensors in
+    ``layer_<l>_k.pt`` / ``_v.pt`` / ``_rk.pt``, documents in ``meta.pt``) into this package's format
+    (``serialize``): chunk-major ``rk_L<l>.bin`` ``[C, Hkv, D]`` and ``kv_L<l>.bin`` ``[C, 2, Hkv, D]``.
+    Runs on the CPU, one layer in memory at a time.  A bank without separate router keys (``decouple_router``
+    off) routes on K, as in the reference (``BlockData.get_router_k``, :241-243).  Returns the written meta."""
+    import sys
+    import types
+    if not is_reference_bank(src_dir):
+        raise A.MsaError(f"{src_dir}: no reference-format bank found (meta.pt)")
+    # meta.pt pickles the reference's src.types.Document; give the unpickler a class of that name and fields
+    injected = []
+    if "src.types" not in sys.modules:
+        pkg = sys.modules.get("src") or types.ModuleType("src")
+        mod = types.ModuleType("src.types")
+        mod.Document = Document
+        for name, m in (("src", pkg), ("src.types", mod)):
+            if name not in sys.modules:
+                sys.modules[name] = m
+                injected.append(name)
+    try:
+        meta = torch.load(os.path.join(src_dir, "meta.pt"), map_location="cpu", weights_only=False)
+    finally:
+        for name in injected:
+            sys.modules.pop(name, None)
+    docs = meta["block_desc"]["docs"]
+    layers = [int(l) for l in meta["router_layer_ids"]]
+    os.makedirs(dst_dir, exist_ok=True)
+    out = None
+    for layer in layers:
+        load = lambda kind: torch.load(os.path.join(src_dir, f"layer_{layer}_{kind}.pt"), map_location="cpu",
+                                       weights_only=False)
+        k, v = load("k"), load("v")
+        rk = load("rk") if os.path.exists(os.path.join(src_dir, f"layer_{layer}_rk.pt")) else k
+        _, h, c, d = k.shape
+        if c != sum(int(x.num_chunks) for x in docs):
+            raise A.MsaError(f"{src_dir}: layer {layer} holds {c} chunks, the documents list {sum(x.num_chunks for x in docs)}")
+        kv = torch.stack([k[0].permute(1, 0, 2), v[0].to(k.dtype).permute(1, 0, 2)], dim=1).contiguous()   # [C, 2, Hkv, D]
+        rk.to(k.dtype)[0].permute(1, 0, 2).contiguous().view(torch.uint8).numpy().tofile(os.path.join(dst_dir, f"rk_L{layer}.bin"))
+        kv.view(torch.uint8).numpy().tofile(os.path.join(dst_dir, f"kv_L{layer}.bin"))
+        out = {"format": "msa_b200-bank-1", "dtype": str(k.dtype).replace("torch.", ""), "n_chunks": int(c),
+               "n_kv_heads": int(h), "head_dim": int(d), "router_layer_ids": layers,
+               "doc_ids": [int(x.doc_id) for x in docs], "doc_chunks": [int(x.num_chunks) for x in docs]}
+    prefix = os.path.join(src_dir, "prefix_cache.pt")
+    pc = torch.load(prefix, map_location="cpu", weights_only=False) if os.path.exists(prefix) else {}
+    torch.save({int(l): (k_, v_) for l, (k_, v_) in pc.items()}, os.path.join(dst_dir, "prefix_cache.pt"))
+    with open(os.path.join(dst_dir, "meta.json"), "w") as f:
+        json.dump(out, f)
+    return out
+
+
 class Memory:
     """One GPU's bank plus local scoring and selection (src/msa_service.py:269-828)."""
 
@@ -241,6 +300,13 @@ class Memory:
                 out = self.deserialize(data_path)
                 assert len(docs) == self.block_desc.nr_docs
                 return out
+            if is_reference_bank(data_path):
+                # the reference would load this directory (it loads whenever the directory exists, :503-505);
+                # rebuilding silently next to its files would hide that the formats differ
+                raise A.MsaError(
+                    f"{data_path} holds a bank in the reference's format (stub.json / meta.pt / layer_*_k.pt), which "
+                    "this package does not read in place: convert it once with "
+                    "msa_b200.memory.convert_reference_bank(src_dir, dst_dir) or point MEMORY_DATA_PATH elsewhere")
         self.begin_blocks(docs)
         for meta in metas or ():
             self.ingest_meta(meta)

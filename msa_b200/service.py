@@ -315,6 +315,25 @@ class MSAService(Memory, MemoryClientBase):
         k, v = ops.gather_run(plan, blk.kv.dtype, g.num_key_value_heads, g.head_dim, n, max_ctas)
         return k, v, n_sel
 
+    def fetch_into(self, winner_local: torch.Tensor, winner_rank: torch.Tensor, layer_idx: int, k_cache: torch.Tensor,
+                   v_cache: torch.Tensor, first_position: int, room: int, max_ctas: int = 0):
+        """``fetch`` for a decode loop: the winners' K/V go straight into positions ``first_position ..
+        first_position + room`` of ``[B, Hkv, L, D]`` caches, sample b's entries into row b (no packed staging
+        buffer, no copies afterwards, no read-back).  A sample whose documents hold more than ``room`` entries
+        is cut; one that holds fewer leaves the tail of its segment as it was.  Returns ``n_sel[B]`` (entries
+        written per sample, on the device)."""
+        if self._directory is None:
+            self.publish_directory()
+        base, offs, ln, kv_base = self._directory
+        g = self.geometry
+        blk = self.blocks[layer_idx]
+        chunk_bytes = 2 * g.num_key_value_heads * g.head_dim * blk.kv.element_size()
+        plan, n_sel, _ = ops.gather_plan(winner_local, winner_rank, self.world_size, base, offs, ln, kv_base[layer_idx],
+                                         chunk_bytes, sample_stride=room, status=self._status)
+        ops.gather_run(plan, blk.kv.dtype, g.num_key_value_heads, g.head_dim, room, max_ctas,
+                       out=(k_cache, v_cache, first_position))
+        return n_sel
+
     def doc_query(self, query_states: torch.Tensor, query_mask: torch.Tensor, layer_idx: int):
         """src/msa_service.py:1133-1314.  query_states ``[B, Hq, S, D]`` (already L2-normalised in
         cosine mode), query_mask ``[B, S]`` bool.  Returns ``(final_k[Hkv, sumN, D], final_v,

@@ -11,6 +11,8 @@ fp32 torch ops on the CPU, the algorithm of the EverMind-AI/MSA reference for:
         src/msa_service.py:1088-1314
   * decode attention over the compact cache
         src/msa/memory_sparse_attention.py:361-405
+  * stage-1 attention inside documents / the template, stage-2 attention over the assembled context
+        src/msa/memory_sparse_attention.py:216-241, 282-357
 
 Only ``tests/``, ``__graft_entry__.smoke()`` and the CPU-baseline / reference legs of
 ``bench.py`` may import it.  The product package never does.
@@ -280,6 +282,104 @@ def decode_attention(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tens
     p = torch.softmax(att, dim=-1)
     o = torch.matmul(p, vv)
     return o.transpose(1, 2).reshape(b, ql, hq * d).to(q.dtype)
+
+
+# --------------------------------------------------------------------------------------
+# Stage-1 and stage-2 attention (the flash_attn_varlen_func calls of the layer)
+# --------------------------------------------------------------------------------------
+
+def _causal_segment(q, k, v, scale, offset):
+    """fp32 attention of one packed sequence: q ``[Hq, nq, D]``, k / v ``[Hkv, nk, D]``; query i sees keys
+    ``0 .. i + offset`` (bottom-right aligned causal mask, ``offset = nk - nq``; what flash-attn >= 2.1 does
+    when the key sequence is longer than the query sequence).  Returns ``[nq, Hq*D]``."""
+    hq, nq, d = q.shape
+    grp = hq // k.shape[0]
+    kk = k.to(torch.float32).repeat_interleave(grp, dim=0)
+    vv = v.to(torch.float32).repeat_interleave(grp, dim=0)
+    att = torch.einsum("hqd,hkd->hqk", q.to(torch.float32), kk) * scale
+    nk = kk.shape[1]
+    limit = torch.arange(nq).view(-1, 1) + offset
+    att = att.masked_fill(torch.arange(nk).view(1, -1) > limit, float("-inf"))
+    return torch.einsum("hqk,hkd->hqd", att.softmax(-1), vv).permute(1, 0, 2).reshape(nq, hq * d)
+
+
+def stage1_doc_attention(q, k, v, doc_ids, attention_mask, scale: Optional[float] = None) -> torch.Tensor:
+    """Stage-1 attention output as it enters ``o_proj`` (src/msa/memory_sparse_attention.py:216-241): every
+    document token attends causally to the unmasked tokens of its own document (runs of equal ``row * (max_id + 1)
+    + doc_id`` among the unmasked document tokens, :226-230), every unmasked template token (doc id -2) to the
+    template tokens of its row (:232-241); all other rows stay zero.  q ``[B, Hq, S, D]``, k / v ``[B, Hkv, S, D]``.
+    Returns ``[B, S, Hq*D]`` fp32."""
+    b, hq, s, d = q.shape
+    scale = d ** -0.5 if scale is None else scale
+    out = torch.zeros(b, s, hq * d, dtype=torch.float32)
+    valid = attention_mask == 1
+    for r in range(b):
+        doc_tok = torch.nonzero((doc_ids[r] > 0) & valid[r]).flatten()
+        if doc_tok.numel():
+            _, counts = torch.unique_consecutive(doc_ids[r][doc_tok], return_counts=True)
+            for seg in torch.split(doc_tok, counts.tolist()):
+                out[r, seg] = _causal_segment(q[r][:, seg], k[r][:, seg], v[r][:, seg], scale, 0)
+        tmpl = torch.nonzero((doc_ids[r] == -2) & valid[r]).flatten()
+        if tmpl.numel():
+            out[r, tmpl] = _causal_segment(q[r][:, tmpl], k[r][:, tmpl], v[r][:, tmpl], scale, 0)
+    return out
+
+
+def stage2_context_attention(q, k, v, template_k, template_v, sel_k, sel_v, valid, n_sel,
+                             scale: Optional[float] = None):
+    """Stage-2 attention and compact cache (src/msa/memory_sparse_attention.py:282-357).  Sequence b's context is
+    ``[template | its n_sel[b] retrieved entries | its valid query tokens]`` (:299-330); its valid query tokens
+    attend to it with the bottom-right aligned causal mask of the varlen call (:334-339).  q ``[B, Hq, S, D]``;
+    k / v ``[B, Hkv, S, D]``; template_* ``[1, Hkv, t, D]``; sel_* ``[Hkv, sum(n_sel), D]`` packed sample after
+    sample (or None); valid ``[B, S]`` bool.  Returns ``(out[B, S, Hq*D] fp32 with zero rows for invalid tokens,
+    compact_k[B, Hkv, maxL, D], compact_v, kv_lengths[B])`` with the caches LEFT padded with zeros (:341-351)."""
+    b, hq, s, d = q.shape
+    scale = d ** -0.5 if scale is None else scale
+    out = torch.zeros(b, s, hq * d, dtype=torch.float32)
+    ctx, off = [], 0
+    for i in range(b):
+        idx = torch.nonzero(valid[i]).flatten()
+        n = int(n_sel[i])
+        parts_k, parts_v = [template_k[0]], [template_v[0]]
+        if n:
+            parts_k.append(sel_k[:, off:off + n])
+            parts_v.append(sel_v[:, off:off + n])
+        off += n
+        kk = torch.cat(parts_k + [k[i][:, idx]], dim=1)
+        vv = torch.cat(parts_v + [v[i][:, idx]], dim=1)
+        ctx.append((kk, vv))
+        if idx.numel():
+            out[i, idx] = _causal_segment(q[i][:, idx], kk, vv, scale, kk.shape[1] - idx.numel())
+    lens = torch.tensor([c[0].shape[1] for c in ctx], dtype=torch.long)
+    max_l = int(lens.max())
+    ck = torch.zeros(b, k.shape[1], max_l, d, dtype=k.dtype)
+    cv = torch.zeros(b, k.shape[1], max_l, d, dtype=v.dtype)
+    for i, (kk, vv) in enumerate(ctx):
+        ck[i, :, max_l - kk.shape[1]:] = kk
+        cv[i, :, max_l - vv.shape[1]:] = vv
+    return out, ck, cv, lens
+
+
+def qwen3_attention_states(hidden, weights: dict, cos, sin, n_q_heads: int, n_kv_heads: int, head_dim: int,
+                           eps: float = 1e-6):
+    """Query / key / value states of the layer before attention, as ``Qwen3Attention`` computes them (third party:
+    transformers ``models/qwen3/modeling_qwen3.py``, pinned to 4.51.3 by the reference's requirements.txt; call
+    site src/msa/memory_sparse_attention.py:124-133): linear projections, per-head RMSNorm of q and k (weights
+    ``q_norm`` / ``k_norm``, fp32 variance), half-split RoPE.  hidden ``[B, S, hidden]``; cos / sin ``[B, S, D]``.
+    Returns q ``[B, Hq, S, D]``, k, v ``[B, Hkv, S, D]`` in fp32."""
+    b, s, _ = hidden.shape
+    x = hidden.to(torch.float32)
+
+    def heads(w, n):
+        return F.linear(x, weights[w].to(torch.float32)).view(b, s, n, head_dim).transpose(1, 2)
+
+    def rms(t, w):
+        return t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps) * weights[w].to(torch.float32)
+    q = rms(heads("q_proj.weight", n_q_heads), "q_norm.weight")
+    k = rms(heads("k_proj.weight", n_kv_heads), "k_norm.weight")
+    v = heads("v_proj.weight", n_kv_heads)
+    c, sn = cos.to(torch.float32).unsqueeze(1), sin.to(torch.float32).unsqueeze(1)
+    return rope_rotate_half(q, c, sn), rope_rotate_half(k, c, sn), v
 
 
 def rope_rotate_half(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:

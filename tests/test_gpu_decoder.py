@@ -130,6 +130,8 @@ def test_pipelined_loop_produces_the_same_tokens_and_caches():
     for x, y in zip(toks_a, toks_c):
         assert torch.equal(x, y)
     a.svc.check_status()
+    for m in (a, b, c):
+        m.check_fetch_counts()     # every step fetched a full retrieved segment for every sequence
 
 
 def test_dense_glue_kernels_match_torch():

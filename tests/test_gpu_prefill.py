@@ -1,6 +1,7 @@
-"""Stage-2 context assembly and sparse prefill attention kernels against a torch fp32 restatement of
-src/msa/memory_sparse_attention.py:282-357 ([template | retrieved | valid query tokens] per sequence,
-bottom-right aligned causal attention, left-padded compact cache)."""
+"""Stage-1 and stage-2 attention kernels against the reference layer's own outputs at head_dim 128
+(tests/golden/layer_attn128.npz) and, on more shapes, against the oracle's fp32 restatements of
+src/msa/memory_sparse_attention.py:216-241 and :282-357 (which tests/test_oracle_golden.py pins to the same fixture).
+Tolerance: 1e-2 norm-wise for bf16 attention outputs and pooled tensors."""
 import math
 
 import pytest
@@ -27,29 +28,15 @@ def _case(seed, b, s, hq, hkv, d, t_len, n_sel, valid_frac, dtype, dev):
 
 
 def _reference(q, k, v, tk, tv, sk, sv, valid, n_sel, scale):
-    """fp32, one sequence at a time.  Returns (out [B,S,Hq*D], list of per-sequence (K, V) contexts)."""
-    b, hq, s, d = q.shape
-    hkv = k.shape[1]
-    grp = hq // hkv
-    out = torch.zeros(b, s, hq * d, dtype=torch.float32, device=q.device)
-    ctx = []
-    off = 0
-    for i in range(b):
-        idx = valid[i].nonzero().flatten()
-        kk = torch.cat([tk[0], sk[:, off:off + n_sel[i]], k[i][:, idx]], dim=1)
-        vv = torch.cat([tv[0], sv[:, off:off + n_sel[i]], v[i][:, idx]], dim=1)
-        off += n_sel[i]
-        ctx.append((kk, vv))
-        nq, nk = idx.numel(), kk.shape[1]
-        qq = q[i][:, idx].float()                                        # [Hq, nq, D]
-        kf = kk.float().repeat_interleave(grp, dim=0)
-        vf = vv.float().repeat_interleave(grp, dim=0)
-        att = torch.einsum("hqd,hkd->hqk", qq, kf) * scale
-        pos_q = torch.arange(nq, device=q.device)[:, None] + (nk - nq)
-        att = att.masked_fill(torch.arange(nk, device=q.device)[None, :] > pos_q, float("-inf"))
-        o = torch.einsum("hqk,hkd->hqd", att.softmax(-1), vf)            # [Hq, nq, D]
-        out[i, idx] = o.permute(1, 0, 2).reshape(nq, hq * d)
-    return out, ctx
+    """The oracle's stage-2 restatement (pinned to the reference layer by tests/test_oracle_golden.py), fp32 on the
+    CPU.  Returns (out [B,S,Hq*D], list of per-sequence (K, V) contexts)."""
+    from oracle import msa_oracle as O
+    c = lambda t: t.cpu()
+    out, ck, cv, lens = O.stage2_context_attention(c(q), c(k), c(v), c(tk), c(tv), c(sk), c(sv), c(valid), n_sel, scale)
+    max_l = ck.shape[2]
+    ctx = [(ck[i, :, max_l - int(lens[i]):].to(q.device), cv[i, :, max_l - int(lens[i]):].to(q.device))
+           for i in range(q.shape[0])]
+    return out.to(q.device), ctx
 
 
 @pytest.mark.parametrize("b,s,hq,hkv,t_len,n_sel,frac", [
@@ -146,15 +133,9 @@ def _stage1_case(seed, doc_lens, n_template, hq, hkv, pad, drop):
 
 
 def _segment_reference(q, k, v, tokens, scale):
-    """fp32 causal attention of one segment; q [Hq,S,D], k/v [Hkv,S,D]; returns [n, Hq*D]."""
-    hq, hkv = q.shape[0], k.shape[0]
-    qq = q[:, tokens].float()
-    kk = k[:, tokens].float().repeat_interleave(hq // hkv, 0)
-    vv = v[:, tokens].float().repeat_interleave(hq // hkv, 0)
-    n = len(tokens)
-    att = torch.einsum("hqd,hkd->hqk", qq, kk) * scale
-    att = att.masked_fill(torch.ones(n, n, dtype=torch.bool).triu(1), float("-inf"))
-    return torch.einsum("hqk,hkd->hqd", att.softmax(-1), vv).permute(1, 0, 2).reshape(n, -1)
+    """fp32 causal attention of one segment (the oracle's routine); q [Hq,S,D], k/v [Hkv,S,D]; returns [n, Hq*D]."""
+    from oracle import msa_oracle as O
+    return O._causal_segment(q[:, tokens], k[:, tokens], v[:, tokens], scale, 0)
 
 
 @pytest.mark.parametrize("doc_lens,drop,p", [
@@ -357,3 +338,133 @@ def test_doc_attention_kernels_with_several_block_rows():
         rows_ = states.cpu()[flat // s, :, flat % s]                       # [Td, Hkv, D]
         exact = O.pool_chunks_exact(rows_.float(), clen).float()
         assert (pooled.float().cpu() - exact).norm() / exact.norm() < 1e-2
+
+
+# ----------------------------------------------------------------------------------------------
+# the kernels against the REFERENCE layer's outputs (fixture made by tests/golden/make_golden.py)
+# ----------------------------------------------------------------------------------------------
+@pytest.fixture(scope="module")
+def attn128(golden):
+    """The layer mirror in bf16 with the fixture's weights; a hook keeps what enters o_proj, and the kernel
+    wrappers are counted so that every test can say which kernel produced its numbers."""
+    from transformers.models.qwen3.modeling_qwen3 import Qwen3RotaryEmbedding
+    from msa_b200 import ops
+    from msa_b200.attention import MemorySparseAttention
+    from msa_b200.configuration import MSAConfig
+    from tests.util import attn128_case
+    g = golden("layer_attn128")
+    weights, geo = attn128_case(g)
+    cfg = MSAConfig(
+        msa_config=dict(router_layer_idx="0", aux_loss=False, aux_loss_method="INFONCE", decouple_router=True,
+                        top_k_docs=geo["top_k"], pooling_kernel_size=geo["pool"], head_reduce_method="mean",
+                        query_reduce_method="max", chunk_reduce_method="max", decouple_pooling_mode="mean"),
+        hidden_size=geo["hidden"], num_attention_heads=geo["hq"], num_key_value_heads=geo["hkv"], head_dim=geo["d"],
+        num_hidden_layers=1, intermediate_size=64, vocab_size=32, max_position_embeddings=1024)
+    cfg._attn_implementation = "eager"
+    layer = MemorySparseAttention(cfg, 0).eval()
+    layer.load_state_dict(weights)
+    layer.to(torch.bfloat16).to("cuda:0")
+    rope = Qwen3RotaryEmbedding(cfg).to("cuda:0")
+    pre, calls = {}, {}
+    layer.o_proj.register_forward_pre_hook(lambda mod, args: pre.__setitem__("x", args[0].detach().float().cpu()))
+    originals = {}
+    for name in ("doc_attention_tc", "doc_attention_pool", "sparse_prefill_attn", "assemble_context", "pool_chunks"):
+        originals[name] = getattr(ops, name)
+
+        def counted(*a, _n=name, **kw):
+            calls[_n] = calls.get(_n, 0) + 1
+            return originals[_n](*a, **kw)
+        setattr(ops, name, counted)
+    yield g, geo, layer, rope, pre, calls
+    for name, fn in originals.items():
+        setattr(ops, name, fn)
+
+
+def _run_stage1(attn128, block):
+    from msa_b200.cache import SparseCacheOnCPU
+    from tests.util import T, from_bf16_bits
+    g, geo, layer, rope, pre, calls = attn128
+    calls.clear()
+    hidden = from_bf16_bits(g[block + "_hidden_bits"]).to(torch.bfloat16).to("cuda:0")
+    cache = SparseCacheOnCPU()
+    cache.record_kwargs(0, {"stage": "prefill_stage1"})
+    with torch.no_grad():
+        layer(hidden, T(g[block + "_doc_ids"]).to("cuda:0"), T(g[block + "_attention_mask"]).to("cuda:0"),
+              rope(hidden, T(g[block + "_position_ids"]).to("cuda:0")), cache)
+    torch.cuda.synchronize()
+    return cache, pre["x"]
+
+
+def _rel(a, b):
+    return float((a.double() - b.double()).norm() / b.double().norm())
+
+
+def test_stage1_unmasked_documents_on_tcgen05_kernel_match_reference_layer(attn128):
+    from tests.util import T
+    g, geo, layer, rope, pre, calls = attn128
+    cache, attn = _run_stage1(attn128, "a")
+    assert calls.get("doc_attention_tc") == 1            # documents: the tcgen05 kernel (the template: mma.sync)
+    ref = T(g["a_attn"])
+    assert _rel(attn, ref) < 1e-2
+    pk, pv = cache.get_kvcache(0)
+    assert _rel(pk.float().cpu(), T(g["a_pooled_k"])) < 1e-2 and _rel(pv.float().cpu(), T(g["a_pooled_v"])) < 1e-2
+    assert _rel(cache.get_router_kcache(0).float().cpu(), T(g["a_pooled_rk"])) < 1e-2
+    assert torch.equal(cache.cache_kwargs[0]["pooled_doc_ids"].cpu(), T(g["a_pooled_doc_ids"]))
+
+
+def test_stage1_masked_documents_on_fused_pooling_kernel_match_reference_layer(attn128):
+    from tests.util import T
+    g, geo, layer, rope, pre, calls = attn128
+    cache, attn = _run_stage1(attn128, "b")
+    assert "doc_attention_tc" not in calls and calls.get("doc_attention_pool") == 2      # documents + template
+    ref = T(g["b_attn"])
+    assert _rel(attn, ref) < 1e-2
+    masked = T(g["b_attention_mask"])[0] == 0
+    assert float(attn[0][masked].abs().sum()) == 0
+    pk, pv = cache.get_kvcache(0)
+    assert _rel(pk.float().cpu(), T(g["b_pooled_k"])) < 1e-2 and _rel(pv.float().cpu(), T(g["b_pooled_v"])) < 1e-2
+    assert _rel(cache.get_router_kcache(0).float().cpu(), T(g["b_pooled_rk"])) < 1e-2
+    assert torch.equal(cache.cache_kwargs[0]["pooled_doc_ids"].cpu(), T(g["b_pooled_doc_ids"]))
+
+
+def test_stage2_on_prefill_kernel_matches_reference_layer(attn128):
+    from msa_b200.cache import SparseCache
+    from msa_b200.memory import AttentionGeometry, Document, ModelConfig
+    from msa_b200.service import MSAService
+    from tests.util import T, from_bf16_bits
+    g, geo, layer, rope, pre, calls = attn128
+    cache1, _ = _run_stage1(attn128, "a")
+    kw = cache1.cache_kwargs[0]
+    chunks = torch.unique_consecutive(kw["pooled_doc_ids"], return_counts=True)[1].tolist()
+    docs = [Document(doc_id=int(i), num_chunks=n) for i, n in zip(g["doc_global_ids"], chunks)]
+    svc = MSAService(0, None, ModelConfig(doc_top_k=geo["top_k"], pooling_kernel_size=geo["pool"], router_layer_idx="0"),
+                     None, AttentionGeometry(num_hidden_layers=1, num_attention_heads=geo["hq"],
+                                             num_key_value_heads=geo["hkv"], head_dim=geo["d"], dtype=torch.bfloat16),
+                     world_size=1, rank=0)
+    svc.generate_blocks(docs, metas=[{"past_key_values": cache1, "nr_docs": len(docs), "chunk_sizes": chunks,
+                                      "doc_ids": [d.doc_id for d in docs], "nr_chunks": chunks}])
+    svc.setup_memory_client(layer)
+    layer.template_prefix_kcache = layer.template_prefix_vcache = None
+    calls.clear()
+    cache2 = SparseCache()
+    cache2.meta["require_recall_topk"] = True
+    cache2.meta["max_generate_tokens"] = 4
+    cache2.record_kwargs(0, {"stage": "prefill_stage2"})
+    hidden2 = from_bf16_bits(g["s2_hidden_bits"]).to(torch.bfloat16).to("cuda:0")
+    with torch.no_grad():
+        layer(hidden2, T(g["s2_doc_ids"]).to("cuda:0"), T(g["s2_attention_mask"]).to("cuda:0"),
+              rope(hidden2, T(g["s2_position_ids"]).to("cuda:0")), cache2)
+    svc.check_status()
+    assert calls.get("sparse_prefill_attn") == 1 and calls.get("assemble_context") == 1
+    kw2 = cache2.cache_kwargs[0]
+    assert [r["topk_doc_ids"] for r in kw2["recall_topk"]] == g["s2_recall_ids"].tolist()
+    got_scores = torch.tensor([r["score"] for r in kw2["recall_topk"]])
+    assert torch.allclose(got_scores, T(g["s2_recall_scores"]).float(), atol=1e-3)
+    assert torch.equal(kw2["kv_lengths"].cpu(), T(g["s2_kv_lengths"]))
+    assert torch.equal(kw2["attention_mask"].cpu(), T(g["s2_mask"]))
+    assert _rel(kw2["compacked_key_cache"].float().cpu(), T(g["s2_cache_k"])) < 1e-2
+    assert _rel(kw2["compacked_value_cache"].float().cpu(), T(g["s2_cache_v"])) < 1e-2
+    valid = T(g["s2_attention_mask"]).bool()
+    ref = T(g["s2_attn"])
+    assert _rel(pre["x"][valid], ref[valid]) < 1e-2
+    layer.set_memory_client(None)

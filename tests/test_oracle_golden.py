@@ -108,6 +108,62 @@ def test_doc_query_two_ranks(golden):
         assert torch.equal(fv, T(g[f"r{r}_final_v"]))
 
 
+def _attn128_states(g, prefix, weights, geo):
+    from tests.util import from_bf16_bits
+    hidden = from_bf16_bits(g[prefix + "_hidden_bits"])
+    cos, sin = O.rope_cos_sin(T(g[prefix + "_position_ids"]), geo["d"], geo["theta"])
+    return hidden, O.qwen3_attention_states(hidden, weights, cos, sin, geo["hq"], geo["hkv"], geo["d"])
+
+
+@pytest.mark.parametrize("block", ["a", "b"])
+def test_stage1_attention_restatement_matches_reference_layer(golden, block):
+    """oracle.stage1_doc_attention against the attention output the reference layer fed to o_proj, at head_dim 128:
+    block a = unmasked documents, block b = masked tokens inside documents; plus the pooled K / V / K_r."""
+    from tests.util import attn128_case
+    g = golden("layer_attn128")
+    weights, geo = attn128_case(g)
+    hidden, (q, k, v) = _attn128_states(g, block, weights, geo)
+    doc_ids, am = T(g[block + "_doc_ids"]), T(g[block + "_attention_mask"])
+    out = O.stage1_doc_attention(q, k, v, doc_ids, am)
+    ref = T(g[block + "_attn"])
+    assert float((out - ref).norm() / ref.norm()) < 1e-5
+    assert float(ref[0][am[0] == 0].abs().sum()) == 0 and float(out[0][am[0] == 0].abs().sum()) == 0
+    doc_indices, gci, pooled_doc_ids, lengths = O.chunk_bookkeeping(doc_ids, am, geo["pool"])
+    assert torch.equal(pooled_doc_ids, T(g[block + "_pooled_doc_ids"]))
+    pk, pv = O.sequence_pooling_kv(k, v, doc_indices, gci)
+    assert float((pk.transpose(0, 1).unsqueeze(0) - T(g[block + "_pooled_k"])).abs().max()) < 1e-5
+    assert float((pv.transpose(0, 1).unsqueeze(0) - T(g[block + "_pooled_v"])).abs().max()) < 1e-5
+
+
+def test_stage2_attention_restatement_matches_reference_layer(golden):
+    """oracle.stage2_context_attention (context assembly, bottom-right causal attention, left-padded compact cache)
+    against the reference layer's stage 2 over block a's bank, the routing included (oracle.doc_query_world)."""
+    from tests.util import attn128_case, from_bf16_bits
+    g = golden("layer_attn128")
+    weights, geo = attn128_case(g)
+    _, (qa, ka, va) = _attn128_states(g, "a", weights, geo)
+    doc_ids_a, am_a = T(g["a_doc_ids"]), T(g["a_attention_mask"])
+    doc_indices, gci, pooled_doc_ids, lengths = O.chunk_bookkeeping(doc_ids_a, am_a, geo["pool"])
+    chunks = torch.unique_consecutive(pooled_doc_ids, return_counts=True)[1].tolist()
+    shard = O.Shard(T(g["a_pooled_k"])[0], T(g["a_pooled_v"])[0], T(g["a_pooled_rk"])[0], chunks, g["doc_global_ids"].tolist())
+    hidden2, (q, k, v) = _attn128_states(g, "s2", weights, geo)
+    d2, a2 = T(g["s2_doc_ids"]), T(g["s2_attention_mask"])
+    b, s = d2.shape
+    rq = torch.nn.functional.linear(hidden2, weights["router_q_proj.0.weight"]).view(b, s, geo["hq"], geo["d"]).transpose(1, 2)
+    rq = O.l2_normalize(rq)
+    (fk, fv, fs, n_sel, wg), = O.doc_query_world([rq], [(d2 == 0) & (a2 == 1)], [shard], geo["top_k"], geo["hq"] // geo["hkv"])
+    assert wg.tolist() == g["s2_recall_ids"].tolist()
+    assert torch.allclose(fs, T(g["s2_recall_scores"]).float(), atol=1e-5)
+    n_t = int((doc_ids_a == -2).sum())
+    out, ck, cv, lens = O.stage2_context_attention(q, k, v, ka[:, :, :n_t], va[:, :, :n_t], fk, fv, a2 == 1, n_sel)
+    assert torch.equal(lens, T(g["s2_kv_lengths"]))
+    assert float((ck - T(g["s2_cache_k"])).abs().max()) < 1e-5 and float((cv - T(g["s2_cache_v"])).abs().max()) < 1e-5
+    ref = T(g["s2_attn"])
+    valid = a2 == 1
+    assert float((out[valid] - ref[valid]).norm() / ref[valid].norm()) < 1e-5
+    assert float(ref[~valid].abs().sum()) == 0
+
+
 def test_decode_matches_reference_layer(golden):
     g = golden("layer_decode")
     ck, cv, lens = T(g["cache_k"]), T(g["cache_v"]), T(g["kv_lengths"])

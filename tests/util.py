@@ -59,3 +59,16 @@ def check_topk(table: torch.Tensor, scores: torch.Tensor, ids: torch.Tensor, k: 
         assert must <= set(d.tolist()), f"row {i}: missing clear winners {must - set(d.tolist())}"
         assert (got >= kth[i] - tol).all() or not finite.all(), f"row {i}: selected a clear loser"
         assert torch.allclose(s[finite], ref_sorted[i, :k_eff][finite], atol=tol, rtol=0)
+
+
+def from_bf16_bits(x) -> torch.Tensor:
+    """fp32 tensor from bf16 bit patterns stored as uint16 (how the fixtures keep bf16-representable values)."""
+    return torch.from_numpy(np.asarray(x).view(np.int16).copy()).view(torch.bfloat16).to(torch.float32)
+
+
+def attn128_case(g):
+    """Weights (fp32, bf16-representable) and geometry of tests/golden/layer_attn128.npz."""
+    weights = {k[len("wbits__"):]: from_bf16_bits(v) for k, v in g.items() if k.startswith("wbits__")}
+    geo = dict(hq=int(g["hq"]), hkv=int(g["hkv"]), d=int(g["d"]), top_k=int(g["top_k"]), pool=int(g["pooling_kernel_size"]),
+               hidden=int(g["hidden_size"]), theta=float(g["rope_theta"]))
+    return weights, geo
