@@ -130,3 +130,73 @@ def test_tensor_layouts_the_tcgen05_attention_accepts():
     assert not ops._tc_view_ok(head_major[:, :, :10])                    # a window of tokens: heads no longer evenly spaced
     assert not ops._tc_view_ok(torch.zeros(b, h, d, s, dtype=torch.bfloat16).transpose(2, 3))   # feature axis not contiguous
     assert not ops._tc_view_ok(head_major.permute(1, 0, 2, 3).contiguous().permute(1, 0, 2, 3))  # batch inside heads
+
+
+def test_reference_format_bank_is_detected_and_converted(tmp_path):
+    """A bank directory in the reference's on-disk format (src/msa_service.py:351-420) is recognised, and the
+    one-time converter writes this package's chunk-major raw files with the same numbers."""
+    import json
+    import sys
+    import types
+    from dataclasses import dataclass
+
+    import numpy as np
+    from msa_b200.memory import convert_reference_bank, is_reference_bank
+
+    @dataclass
+    class RefDocument:           # pickles as src.types.Document, the class the reference's meta.pt refers to
+        doc: str = ""
+        doc_id: int = 0
+        num_chunks: int = 0
+    RefDocument.__module__, RefDocument.__qualname__, RefDocument.__name__ = "src.types", "Document", "Document"
+    had = {n: sys.modules.get(n) for n in ("src", "src.types")}
+    mod = types.ModuleType("src.types")
+    mod.Document = RefDocument
+    sys.modules["src"], sys.modules["src.types"] = types.ModuleType("src"), mod
+    src, dst = tmp_path / "ref", tmp_path / "new"
+    src.mkdir()
+    try:
+        docs = [RefDocument(doc_id=5, num_chunks=2), RefDocument(doc_id=9, num_chunks=3)]
+        json.dump({"world": 1}, open(src / "stub.json", "w"))
+        torch.save({"router_layer_ids": [1], "block_desc": {"docs": docs, "doc_ids": torch.tensor([0, 5, 9]),
+                                                            "pool_ids": torch.tensor([1, 1, 2, 2, 2])}}, src / "meta.pt")
+        g = torch.Generator().manual_seed(0)
+        k, v, rk = (torch.randn(1, 2, 5, 4, generator=g) for _ in range(3))
+        for n, t in (("k", k), ("v", v), ("rk", rk)):
+            torch.save(t, src / f"layer_1_{n}.pt")
+    finally:
+        for n, m in had.items():
+            if m is None:
+                sys.modules.pop(n, None)
+            else:
+                sys.modules[n] = m
+    assert is_reference_bank(str(src))
+    meta = convert_reference_bank(str(src), str(dst))
+    assert meta["doc_ids"] == [5, 9] and meta["doc_chunks"] == [2, 3] and meta["n_chunks"] == 5
+    assert not is_reference_bank(str(dst))
+    kv = torch.from_numpy(np.fromfile(dst / "kv_L1.bin", dtype=np.float32)).view(5, 2, 2, 4)
+    rk2 = torch.from_numpy(np.fromfile(dst / "rk_L1.bin", dtype=np.float32)).view(5, 2, 4)
+    assert torch.equal(kv[:, 0].permute(1, 0, 2), k[0]) and torch.equal(kv[:, 1].permute(1, 0, 2), v[0])
+    assert torch.equal(rk2.permute(1, 0, 2), rk[0])
+
+
+def test_reference_own_code_agrees_with_the_oracle_when_present():
+    """oracle/_ref (the reference's files, copied by oracle/build_ref.py) runs Memory._generate_slice +
+    Memory.prefill_stage2 unmodified; the oracle port must give the same scores and winners."""
+    from oracle import msa_oracle as O
+    from oracle import ref_runner as R
+    if not R.available():
+        pytest.skip("oracle/_ref has not been built on this machine")
+    g = torch.Generator().manual_seed(0)
+    chunks = torch.randint(1, 9, (600,), generator=g).tolist()      # ~2,700 chunks: two slices of >= 1024
+    c = sum(chunks)
+    rk = torch.nn.functional.normalize(torch.randn(1, 8, c, 128, generator=g), dim=-1)
+    q = torch.nn.functional.normalize(torch.randn(2, 8, 4, 16, 128, generator=g), dim=-1)
+    mask = torch.ones(2, 16, dtype=torch.bool)
+    mask[1, 9:] = False
+    mem = R.make_reference_memory(rk, chunks, range(500, 500 + len(chunks)), 16, slice_chunks=1024)
+    s, li, gi = R.reference_prefill_stage2(mem, q, mask)
+    pool = torch.repeat_interleave(torch.arange(1, len(chunks) + 1), torch.tensor(chunks))
+    s2, l2, g2 = O.prefill_stage2(q, mask, rk[0], pool, torch.tensor([0] + list(range(500, 500 + len(chunks)))), 16)
+    assert len(mem.slice_desc) > 1
+    assert torch.allclose(s, s2, atol=1e-6) and torch.equal(li, l2) and torch.equal(gi, g2)
