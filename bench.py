@@ -472,7 +472,12 @@ def leg_route_decode(torch, ops, dev, pk, steps=500, warmup=3, b=32):
     topk_ws = torch.empty((ops.topk_workspace_bytes(b, docs_local + 1, TOP_K) + 7) // 8, dtype=torch.int64, device=dev)
     ev = []
 
-    def step(timed=False):
+    sel_ws = torch.empty((max(int(ops.A.lib().msa_route_score_select_workspace_bytes(b, TOP_K)), 8) + 7) // 8,
+                         dtype=torch.int64, device=dev)
+    outs = (torch.empty((b, TOP_K), dtype=torch.float32, device=dev), torch.empty((b, TOP_K), dtype=torch.int64, device=dev),
+            torch.empty((b, TOP_K), dtype=torch.int64, device=dev))
+
+    def step_table(timed=False):      # fold, table reset, scoring, two-level top-k
         for rk in banks:
             qf, bias, s_pad = ops.fold_queries(q, mask, HQ // HKV)
             ops.route_table_reset(keys, docs_local, torch.finfo(torch.bfloat16).min, status)
@@ -484,20 +489,43 @@ def leg_route_decode(torch, ops, dev, pk, steps=500, warmup=3, b=32):
                 e1.record()
                 ev.append((e0, e1))
             ops.topk_select(keys, TOP_K, workspace=topk_ws)
-    # the scoring kernel alone, eagerly, with events around each launch
-    _time_ms(torch, lambda: step(True), 5, warmup)
-    route_ms = statistics.mean([a.elapsed_time(b_) for a, b_ in ev[-5 * n_layers:]])
-    # the whole layer-step replayed from a CUDA graph, as a decode loop would issue it
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        step(False)
-    ms = _time_ms(torch, graph.replay, steps, warmup) / n_layers
-    del graph
+
+    def step_fused(timed=False):      # fold, fused scoring + per-CTA selection, final selection
+        for rk in banks:
+            qf, bias, s_pad = ops.fold_queries(q, mask, HQ // HKV)
+            if timed:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            ops.route_score_select(qf, bias, b, rk, chunk_doc, docs_local, 1.0 / HQ, TOP_K, status=status, workspace=sel_ws,
+                                   out=outs)
+            if timed:
+                e1.record()
+                ev.append((e0, e1))
+
     alg = c * HKV * D * 2 + b * HKV * D * 2
+    res = {}
+    for name, step in (("table", step_table), ("fused", step_fused)):
+        ev.clear()
+        _time_ms(torch, lambda: step(True), 5, warmup)        # eagerly, with events around the scoring call
+        inner_ms = statistics.mean([a.elapsed_time(b_) for a, b_ in ev[-5 * n_layers:]])
+        graph = torch.cuda.CUDAGraph()                          # the whole layer-step as a decode loop issues it
+        with torch.cuda.graph(graph):
+            step(False)
+        ms = _time_ms(torch, graph.replay, steps, warmup) / n_layers
+        del graph
+        res[name] = (ms, inner_ms)
+    assert status.cpu().tolist()[0] == 0 and status.cpu().tolist()[2] == 0
+    ms, fused_inner = res["fused"]
     gbs = alg / (ms / 1e3) / 1e9
-    return {"kernel": "route_tc_kernel", "ms": ms, "algorithmic_bytes": alg, "achieved_gbs": gbs, "frac": gbs / pk["hbm_gbs"],
-            "bound": "hbm", "launches": 5 * n_layers * steps, "layer_step": "fold, table reset, scoring, two-level top-k (one CUDA graph)",
-            "route_kernel_ms": route_ms, "route_kernel_frac": alg / (route_ms / 1e3) / 1e9 / pk["hbm_gbs"],
+    return {"kernel": "route_dec_kernel", "ms": ms, "algorithmic_bytes": alg, "achieved_gbs": gbs, "frac": gbs / pk["hbm_gbs"],
+            "bound": "hbm", "launches": 3 * n_layers * steps,
+            "layer_step": "fold, fused scoring + per-CTA selection, final selection (one CUDA graph)",
+            "route_kernel_ms": fused_inner, "route_kernel_frac": alg / (fused_inner / 1e3) / 1e9 / pk["hbm_gbs"],
+            "route_kernel_note": "route_dec_kernel + the final selection launch, eager, CUDA events around the call",
+            "table_path": {"layer_step_ms": res["table"][0], "layer_step_frac": alg / (res["table"][0] / 1e3) / 1e9 / pk["hbm_gbs"],
+                           "route_tc_kernel_ms": res["table"][1],
+                           "route_tc_kernel_frac": alg / (res["table"][1] / 1e3) / 1e9 / pk["hbm_gbs"],
+                           "what": "fold, table reset, route_tc_kernel, two-level top-k (5 launches)"},
             "workload": f"benchmark config 5 per-step routing: {b} sequences x 1 token against {c} chunks (400 MB shard, one "
                         f"of 8), {n_layers} distinct layers rotate"}
 
@@ -992,7 +1020,8 @@ def run_ours(args):
                 kernels[name] = {"kernel": leg["kernel"], "ms": leg["ms"], "algorithmic_bytes": leg["algorithmic_bytes"],
                                  "achieved_gbs": leg["achieved_gbs"], "frac": leg["frac"], "peak_gbs": pk["hbm_gbs"],
                                  "workload": leg["workload"],
-                                 **{k_: leg[k_] for k_ in ("route_kernel_ms", "route_kernel_frac", "layer_step", "tokens_per_s") if k_ in leg}}
+                                 **{k_: leg[k_] for k_ in ("route_kernel_ms", "route_kernel_frac", "route_kernel_note", "layer_step",
+                                                           "table_path", "tokens_per_s") if k_ in leg}}
             except Exception as e:
                 kernels[name] = {"error": f"{type(e).__name__}: {e}"}
         if world > 1:

@@ -209,6 +209,31 @@ int msa_topk_select(const uint32_t* score_keys, int64_t table_stride, int32_t n_
                     int64_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Routing, steps 2 + 3 in one call for decode-time routing (one query row per sequence).
+ * Same result as msa_route_scores followed by msa_topk_select (src/msa_service.py:716-828 with one token per
+ * query), without the [n_seq, n_docs + 1] score table: every CTA scores one contiguous range of chunks cut at
+ * document boundaries, keeps the document scores of its range in shared memory, selects its best k per
+ * sequence there, and a second small launch reduces the per-CTA candidates.  The scoring is bound by HBM (the
+ * shard's router keys are read once).
+ *
+ * q_folded / row_bias: output of msa_fold_queries with s_pad == 1 (n_seq rows).  rk, chunk_doc, alpha, n_docs,
+ * min_val, doc_ids_table, out_*: as in msa_route_scores / msa_topk_select; out_* are [n_seq, min(k, n_docs + 1)].
+ * workspace: device, msa_route_score_select_workspace_bytes(n_seq, k) bytes (per-CTA candidates; -1 = no device).
+ * status: device int32[4], written only on error (zero it once): word 0 = a barrier wait ran out, word 2 =
+ * chunk -> document ids outside 1..n_docs (or not non-decreasing) were skipped.
+ * Takes bf16, n_seq <= 128, k <= 32, kdim % 64 == 0; other shapes return MSA_ERR_UNSUPPORTED before any launch
+ * (use the two-call path).
+ */
+int64_t msa_route_score_select_workspace_bytes(int32_t n_seq, int32_t k);
+
+int msa_route_score_select(const void* q_folded, const float* row_bias, int32_t dtype, int32_t n_seq,
+                           const void* rk, int64_t rk_chunk_stride, int32_t n_chunks, int32_t kdim,
+                           const int32_t* chunk_doc, float alpha, int32_t n_docs, float min_val, int32_t k,
+                           const int64_t* doc_ids_table, float* out_scores, int64_t* out_local_ids,
+                           int64_t* out_global_ids, void* workspace, int64_t workspace_bytes,
+                           int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * Cross-rank merge of the per-shard candidates.
  * Replaces steps 4-5 of MSAService.doc_query (src/msa_service.py:1174-1196): top-k over
  * the W*kc candidates of each query, owner rank of each winner, invalidation of winners
@@ -317,10 +342,20 @@ int msa_sparse_decode_attn(const void* q, int32_t dtype, void* k_cache, void* v_
  * then the other tokens in order), error_flag
  * (1 if some len_b exceeds max_kv: that sequence's storage is zero-filled and its kv_start is negative).
  *
- * msa_sparse_prefill_attn (bf16, head_dim 128): out[b, tok, hq*D + d] for every valid query
- * token, attending to the template, all retrieved entries and the query tokens up to itself
- * (bottom-right aligned causal mask); q: [B, Hq, S, D] by strides; out: [B, S, Hq*D]
- * contiguous; the rows of invalid tokens are zero-filled.
+ * msa_sparse_prefill_attn: out[b, tok, hq*D + d] for every valid query token.  causal != 0: the token attends
+ * to the template, all retrieved entries and the query tokens up to itself (bottom-right aligned causal
+ * mask, stage 2).  causal == 0: every valid token attends to all kv_len[b] entries (the multi-token
+ * segments of the reference's qa_mode, src/msa/memory_sparse_attention.py:375-380, after
+ * msa_append_segment has put the segment's own tokens into the store).  q: [B, Hq, S, D] by strides; out:
+ * [B, S, Hq*D] contiguous; the rows of invalid tokens are zero-filled.  bf16 with head_dim 128 runs on the
+ * tensor-core kernel; fp32 and other head sizes (<= 256) on a general CUDA-core kernel.
+ *
+ * msa_append_segment: appends the valid tokens (valid: uint8 [B, S]) of seg_k / seg_v [B, Hkv, S, D] (by
+ * strides) to every sequence's store at positions kv_start[b] + kv_len[b] .., in order, adds their number to
+ * kv_len[b], and writes q_tok[B, S] (valid tokens first) and num_q[B] as msa_assemble_context does.  Tokens
+ * whose mask is 0 are not stored: they are never attended to, so leaving them out keeps a sequence's valid
+ * entries contiguous (the reference stores them and carries a mask instead).  error_flag is set to 1 when a
+ * sequence's store (store_len positions) has no room; that sequence is left unchanged with num_q = 0.
  */
 int msa_assemble_context(const void* template_k, const void* template_v, int32_t template_len,
                          const void* sel_k, const void* sel_v, int64_t sel_head_stride,
@@ -336,12 +371,21 @@ int msa_sparse_prefill_attn(const void* q, int64_t q_stride_b, int64_t q_stride_
                             int64_t store_stride_h, const int32_t* kv_start, const int32_t* kv_len,
                             const int32_t* q_tok, const int32_t* num_q, int32_t n_seq, int32_t seq_len,
                             int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim, int32_t dtype,
-                            float scale, void* out, void* stream);
+                            int32_t causal, float scale, void* out, void* stream);
+
+int msa_append_segment(const void* seg_k, const void* seg_v, int64_t seg_stride_b, int64_t seg_stride_h,
+                       int64_t seg_stride_s, const uint8_t* valid, int32_t n_seq, int32_t seq_len,
+                       int32_t n_kv_heads, int32_t head_dim, int32_t dtype, void* k_store, void* v_store,
+                       int64_t store_stride_b, int64_t store_stride_h, int32_t store_len,
+                       const int32_t* kv_start, int32_t* kv_len, int32_t* q_tok, int32_t* num_q,
+                       int32_t* error_flag, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Stage-1 attention inside every document, with the chunk means of K and V as a by-product.
  * Replaces flash_attn_varlen_func over the document tokens and the K / V pooling of
- * src/msa/memory_sparse_attention.py:216-241 and :166-176 (bf16, head_dim 128).
+ * src/msa/memory_sparse_attention.py:216-241 and :166-176.  bf16 with head_dim 128 runs on tensor cores; fp32
+ * and other head sizes (<= 256) on a general CUDA-core kernel, without the pooling by-product (chunk_offsets
+ * must then be NULL).
  *
  * token_index[Td]: flat positions b*seq_len + s of the tokens that take part, document after
  * document (msa_chunk_bookkeeping's order); seg_offsets[n_segments + 1]: where each document starts

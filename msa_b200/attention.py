@@ -6,18 +6,20 @@ constructor arguments, same module / parameter names (so a reference checkpoint'
 loads), same cache protocol (``cache_kwargs`` / ``meta`` / ``record_kwargs`` / ``update`` /
 ``update_router_kcache``).
 
-What runs where:
+What runs where (every attention of the path is one of this package's kernels; no library attention call):
   * stage 1: projections, norms and RoPE stay PyTorch as in the reference; chunk bookkeeping, the
     intra-document causal attention and all pooling run on this package's kernels.  In bf16 with
     head_dim 128: documents without masked tokens go to the tcgen05 attention kernel (K, V, K_r pooled
     by the pooling kernel), blocks with masked tokens inside documents to the mma.sync kernel that
-    takes the K / V chunk means in the same pass; other dtypes / head sizes: library attention + the
-    pooling kernel;
+    takes the K / V chunk means in the same pass; fp32 and other head sizes: the general CUDA-core
+    attention kernel + the pooling kernel;
   * stage 2: routing, merge and fetch happen inside ``memory_client.doc_query`` (this package's
     ``MSAService``); one kernel assembles [template | retrieved | query] into the left-padded
-    compact cache (allocated with room to append in place) and, for bf16 / head_dim 128, this
-    package's prefill attention kernel reads it there (other shapes: library attention call);
-  * decode: this package's flash-decode kernel, in-place append, no ``torch.cat`` / ``repeat_kv``.
+    compact cache (allocated with room to append in place) and the prefill attention kernel reads it
+    there (tensor cores for bf16 / head_dim 128, the general kernel otherwise);
+  * decode: this package's flash-decode kernel, in-place append, no ``torch.cat`` / ``repeat_kv``;
+    the multi-token, non-causal segments of ``qa_mode`` are appended by one kernel and attended by the
+    prefill kernel without its causal mask.
 The training forward (``_forward``) is out of scope and raises.
 """
 from __future__ import annotations
@@ -29,34 +31,6 @@ from transformers.models.qwen3.modeling_qwen3 import Qwen3Attention, apply_rotar
 
 from . import _cabi as A
 from . import ops
-
-try:  # third-party, exactly as the reference uses it (src/msa/memory_sparse_attention.py:13-17)
-    from flash_attn import flash_attn_varlen_func as _flash_varlen
-except Exception:  # pragma: no cover - depends on the image
-    _flash_varlen = None
-
-
-def varlen_attention(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal=True):
-    """Variable-length causal attention with bottom-right aligned masking: ``flash_attn_varlen_func``
-    when it can run on these tensors, else an SDPA loop over the sequences.  Library call in both
-    cases, as in the reference (this piece is not one of this package's kernels)."""
-    if _flash_varlen is not None and q.is_cuda and q.dtype in (torch.float16, torch.bfloat16):
-        return _flash_varlen(q, k, v, cu_seqlens_q=cu_seqlens_q, cu_seqlens_k=cu_seqlens_k,
-                             max_seqlen_q=max_seqlen_q, max_seqlen_k=max_seqlen_k, dropout_p=0.0, causal=causal)
-    outs = []
-    cq, ck = cu_seqlens_q.tolist(), cu_seqlens_k.tolist()
-    for i in range(len(cq) - 1):
-        qi = q[cq[i]:cq[i + 1]].transpose(0, 1)
-        ki = k[ck[i]:ck[i + 1]].transpose(0, 1)
-        vi = v[ck[i]:ck[i + 1]].transpose(0, 1)
-        if ki.shape[0] != qi.shape[0]:
-            rep = qi.shape[0] // ki.shape[0]
-            ki, vi = ki.repeat_interleave(rep, 0), vi.repeat_interleave(rep, 0)
-        lq, lk = qi.shape[1], ki.shape[1]
-        mask = torch.ones(lq, lk, dtype=torch.bool, device=q.device).tril(diagonal=lk - lq) if causal else None
-        outs.append(F.scaled_dot_product_attention(qi, ki, vi, attn_mask=mask).transpose(0, 1))
-    return torch.cat(outs, 0) if outs else q.new_zeros(q.shape)
-
 
 class MemorySparseAttention(Qwen3Attention):
     #: extra cache positions reserved for tokens appended during decode
@@ -163,49 +137,30 @@ class MemorySparseAttention(Qwen3Attention):
         device, dtype = hidden_states.device, hidden_states.dtype
         hidden_shape = (bsz, q_len, -1, self.head_dim)
         n_heads = self.config.num_attention_heads
-        own_attention = dtype == torch.bfloat16 and self.head_dim == 128
+        tensor_cores = dtype == torch.bfloat16 and self.head_dim == 128
         if self.is_router_layer and bsz != 1:
             raise A.MsaError("stage 1 pools one block per call (the reference's worker uses batch size 1)")
 
         # intra-document and template causal attention (:216-241)
         attn_output = torch.zeros((bsz, q_len, n_heads * self.head_dim), device=device, dtype=dtype)
         pooled_k = pooled_v = pooled_rk = pooled_doc_ids = None
-        if own_attention:
-            (tok_d, off_d, max_d, runs_d), (tok_t, off_t, max_t, _) = self._segments(doc_ids, attention_mask, cache)
-            if runs_d and max_d >= 128 and ops.doc_attention_tc_supported(query_states, key_states, value_states):
-                # unmasked documents: attention on the tcgen05 kernel (K and V are pooled by the pooling kernel below)
-                status = cache.meta.setdefault("_msa_b200_attn_status", torch.zeros(4, dtype=torch.int32, device=device))
-                ops.doc_attention_tc(query_states, key_states, value_states, tok_d, off_d, max_d, out=attn_output,
-                                     scale=self.scaling, status=status)
-            elif self.is_router_layer and self.pooling_kernel_size % 32 == 0:
-                # K and V are pooled from the tiles the attention kernel stages anyway
-                tok, off, pooled_doc_ids = self._bookkeeping(doc_ids, attention_mask, cache)
-                _, pooled_k, pooled_v = ops.doc_attention_pool(
-                    query_states, key_states, value_states, tok, off_d, max_d, out=attn_output, chunk_offsets=off,
-                    pool_size=self.pooling_kernel_size, head_major_out=True, scale=self.scaling)
-            else:
-                ops.doc_attention_pool(query_states, key_states, value_states, tok_d, off_d, max_d, out=attn_output,
-                                       scale=self.scaling)
-            ops.doc_attention_pool(query_states, key_states, value_states, tok_t, off_t, max_t, out=attn_output,
+        (tok_d, off_d, max_d, runs_d), (tok_t, off_t, max_t, _) = self._segments(doc_ids, attention_mask, cache)
+        if tensor_cores and runs_d and max_d >= 128 and ops.doc_attention_tc_supported(query_states, key_states, value_states):
+            # unmasked documents: attention on the tcgen05 kernel (K and V are pooled by the pooling kernel below)
+            status = cache.meta.setdefault("_msa_b200_attn_status", torch.zeros(4, dtype=torch.int32, device=device))
+            ops.doc_attention_tc(query_states, key_states, value_states, tok_d, off_d, max_d, out=attn_output,
+                                 scale=self.scaling, status=status)
+        elif tensor_cores and self.is_router_layer and self.pooling_kernel_size % 32 == 0:
+            # K and V are pooled from the tiles the attention kernel stages anyway
+            tok, off, pooled_doc_ids = self._bookkeeping(doc_ids, attention_mask, cache)
+            _, pooled_k, pooled_v = ops.doc_attention_pool(
+                query_states, key_states, value_states, tok, off_d, max_d, out=attn_output, chunk_offsets=off,
+                pool_size=self.pooling_kernel_size, head_major_out=True, scale=self.scaling)
+        else:   # bf16 / 128 without pooling here, or any other dtype / head size on the general kernel
+            ops.doc_attention_pool(query_states, key_states, value_states, tok_d, off_d, max_d, out=attn_output,
                                    scale=self.scaling)
-        else:   # library calls, as in the reference
-            doc_token_mask = (doc_ids > 0) & (attention_mask == 1)
-            q_t, k_t, v_t = query_states.transpose(1, 2), key_states.transpose(1, 2), value_states.transpose(1, 2)
-            if doc_token_mask.any():
-                idx = torch.nonzero(doc_token_mask, as_tuple=False)
-                gid = idx[:, 0] * (int(doc_ids.max().item()) + 1) + doc_ids[doc_token_mask]
-                _, counts = torch.unique_consecutive(gid, return_counts=True)
-                cu = F.pad(torch.cumsum(counts, 0, dtype=torch.int32), (1, 0))
-                out = varlen_attention(q_t[doc_token_mask], k_t[doc_token_mask], v_t[doc_token_mask], cu, cu,
-                                       int(counts.max()), int(counts.max()))
-                attn_output[doc_token_mask] = out.reshape(-1, n_heads * self.head_dim)
-            template_mask = (doc_ids == -2) & (attention_mask == 1)
-            if template_mask.any():
-                counts = template_mask.sum(dim=1)
-                cu = F.pad(torch.cumsum(counts, 0, dtype=torch.int32), (1, 0))
-                out = varlen_attention(q_t[template_mask], k_t[template_mask], v_t[template_mask], cu, cu,
-                                       int(counts.max()), int(counts.max()))
-                attn_output[template_mask] = out.reshape(-1, n_heads * self.head_dim)
+        ops.doc_attention_pool(query_states, key_states, value_states, tok_t, off_t, max_t, out=attn_output,
+                               scale=self.scaling)
 
         if self.is_router_layer:
             tok, off, pooled_doc_ids = self._bookkeeping(doc_ids, attention_mask, cache)
@@ -273,18 +228,7 @@ class MemorySparseAttention(Qwen3Attention):
             template_k, template_v, final_k, None if final_v is None else final_v.to(device), n_sel, key_states,
             value_states, valid_q, max_kv, reserve)
         left_pad_mask = torch.arange(max_kv, device=device).unsqueeze(0) >= (max_kv - kv_lengths.unsqueeze(1))
-        if dtype == torch.bfloat16 and d == 128:
-            attn_output = ops.sparse_prefill_attn(query_states, k_store, v_store, kv_start, kv_len, q_tok, n_valid,
-                                                  self.scaling)
-        else:
-            cu_q = F.pad(num_q.cumsum(0, dtype=torch.int32), (1, 0))
-            cu_kv = F.pad(kv_lengths.cumsum(0, dtype=torch.int32), (1, 0))
-            k_flat = k_store[:, :, :max_kv].permute(0, 2, 1, 3)[left_pad_mask]
-            v_flat = v_store[:, :, :max_kv].permute(0, 2, 1, 3)[left_pad_mask]
-            out_flat = varlen_attention(query_states.permute(0, 2, 1, 3)[valid_q], k_flat, v_flat, cu_q, cu_kv,
-                                        int(num_q.max()), max_kv).reshape(-1, n_heads * d)
-            attn_output = torch.zeros((bsz, q_len, n_heads * d), device=device, dtype=dtype)
-            attn_output[valid_q] = out_flat
+        attn_output = ops.sparse_prefill_attn(query_states, k_store, v_store, kv_start, kv_len, q_tok, n_valid, self.scaling)
         cache_kwargs.update({
             "compacked_key_cache": k_store[:, :, :max_kv], "compacked_value_cache": v_store[:, :, :max_kv],
             "kv_lengths": kv_lengths, "attention_mask": left_pad_mask,
@@ -312,18 +256,17 @@ class MemorySparseAttention(Qwen3Attention):
             kv_len = kv_len + 1
             cache_kwargs["kv_lengths"] = cache_kwargs["kv_lengths"] + 1
         else:
-            # multi-token segments of qa_mode are non-causal inside the segment (:375-380): library path
-            k_store[:, :, cur_len:cur_len + q_len] = key_states
-            v_store[:, :, cur_len:cur_len + q_len] = value_states
-            mask = cache_kwargs["attention_mask"]
-            mask = torch.cat([mask, attention_mask.to(mask.dtype)], dim=1)
-            cache_kwargs["attention_mask"] = mask
-            g = n_heads // k_store.shape[1]
-            kk = k_store[:, :, :cur_len + q_len].repeat_interleave(g, dim=1)
-            vv = v_store[:, :, :cur_len + q_len].repeat_interleave(g, dim=1)
-            attn_output = F.scaled_dot_product_attention(query_states, kk, vv, attn_mask=mask[:, None, None, :])
-            attn_output = attn_output.transpose(1, 2).reshape(bsz, q_len, -1)
-            kv_len = kv_len + q_len
+            # qa_mode segments (:375-380): every token of the segment attends, without a causal mask, to the cache
+            # and to the segment's own unmasked tokens.  One kernel appends the unmasked tokens in place (kv_len
+            # grows by their number; masked tokens are never attended to, so they are not stored and a sequence's
+            # valid entries stay one contiguous run), the prefill kernel attends without its causal mask.
+            valid = attention_mask.reshape(bsz, q_len) == 1
+            q_tok, num_q, _ = ops.append_segment(key_states, value_states, valid, k_store, v_store, kv_start, kv_len)
+            attn_output = ops.sparse_prefill_attn(query_states, k_store, v_store, kv_start, kv_len, q_tok, num_q,
+                                                  self.scaling, causal=False)
+            pos = torch.arange(cur_len + q_len, device=k_store.device).unsqueeze(0)
+            cache_kwargs["attention_mask"] = (pos >= kv_start.unsqueeze(1)) & (pos < (kv_start + kv_len).unsqueeze(1))
+            cache_kwargs["kv_lengths"] = kv_len.to(cache_kwargs["kv_lengths"].dtype)
         cache_kwargs["compacked_key_cache"] = k_store[:, :, :cur_len + q_len]
         cache_kwargs["compacked_value_cache"] = v_store[:, :, :cur_len + q_len]
         cache_kwargs["_msa_b200_store"] = (k_store, v_store, kv_start, kv_len)
@@ -339,5 +282,8 @@ class MemorySparseAttention(Qwen3Attention):
         k_store = torch.zeros((b, h, cap, d), dtype=ck.dtype, device=ck.device)
         v_store = torch.zeros((b, h, cap, d), dtype=cv.dtype, device=cv.device)
         k_store[:, :, :cur], v_store[:, :, :cur] = ck, cv
+        prev = cache_kwargs.get("_msa_b200_store")
+        if prev is not None:      # our own storage, out of room: positions and lengths stay what they are
+            return k_store, v_store, prev[2], prev[3]
         kv_len = cache_kwargs["kv_lengths"].to(torch.int32)
-        return k_store, v_store, (cur - kv_len).to(torch.int32), kv_len
+        return k_store, v_store, (cur - kv_len).to(torch.int32), kv_len      # a left-padded cache of the reference

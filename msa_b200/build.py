@@ -13,7 +13,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmsa_b200.so")
-SOURCES = ["cabi.cu", "pool.cu", "bookkeeping.cu", "route_simt.cu", "route_tc.cu", "route_modes.cu", "topk.cu", "gather.cu", "decode_attn.cu", "prefill_attn.cu", "doc_attn_tc.cu", "decode_dense.cu"]
+SOURCES = ["cabi.cu", "pool.cu", "bookkeeping.cu", "route_simt.cu", "route_tc.cu", "route_modes.cu", "route_dec.cu", "topk.cu", "gather.cu", "decode_attn.cu", "prefill_attn.cu", "attn_generic.cu", "doc_attn_tc.cu", "decode_dense.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--use_fast_math"]
 

@@ -18,6 +18,17 @@
 
 namespace msa {
 
+// attn_generic.cu: the same attentions for fp32 and for head sizes other than 128
+int launch_attention_rows_by_index(int32_t dtype, const void* q, int64_t q_sb, int64_t q_sh, int64_t q_ss, const void* k,
+                                   const void* v, int64_t k_sb, int64_t k_sh, int64_t k_ss, const int32_t* token_index,
+                                   const int32_t* seg_off, int n_segments, long long n_rows, int S, int n_q_heads,
+                                   int n_kv_heads, int D, float scale, void* out, cudaStream_t stream);
+int launch_attention_rows_in_store(int32_t dtype, const void* q, int64_t q_sb, int64_t q_sh, int64_t q_ss,
+                                   const void* k_store, const void* v_store, int64_t st_b, int64_t st_h,
+                                   const int32_t* kv_start, const int32_t* kv_len, const int32_t* q_tok, const int32_t* num_q,
+                                   int n_seq, int S, int n_q_heads, int n_kv_heads, int D, int causal, float scale, void* out,
+                                   cudaStream_t stream);
+
 constexpr int kAsmThreads = 256;
 constexpr int kAsmSlices = 16;   // CTAs per sequence: the copy loop is dealt over them
 
@@ -249,7 +260,7 @@ prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, long long q_sb, long lo
                     const __nv_bfloat16* __restrict__ k_store, const __nv_bfloat16* __restrict__ v_store, long long st_b,
                     long long st_h, const int32_t* __restrict__ kv_start, const int32_t* __restrict__ kv_len,
                     const int32_t* __restrict__ q_tok, const int32_t* __restrict__ num_q_arr, int S, int n_q_heads,
-                    int n_kv_heads, float scale_log2e, __nv_bfloat16* __restrict__ out) {
+                    int n_kv_heads, int causal, float scale_log2e, __nv_bfloat16* __restrict__ out) {
   extern __shared__ __align__(128) unsigned char smem[];
   const int b = blockIdx.z, hq = blockIdx.y, r0 = blockIdx.x * kPfRows;
   const int num_q = num_q_arr[b];
@@ -262,10 +273,11 @@ prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, long long q_sb, long lo
   }
   if (r0 >= num_q) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2;
-  const int len = kv_len[b], base_keys = len - num_q;   // keys every query token sees
+  // keys every query token sees; without the causal mask (multi-token decode segments) that is the whole context
+  const int len = kv_len[b], base_keys = causal ? len - num_q : len - 1;
   const int hk = hq / (n_q_heads / n_kv_heads);
   const long long kv_base = (long long)b * st_b + (long long)hk * st_h + (long long)kv_start[b] * kMmaD;
-  const int last_row = min(r0 + kPfRows, num_q) - 1;
+  const int last_row = causal ? min(r0 + kPfRows, num_q) - 1 : 0;
   const int n_keys = base_keys + last_row + 1;
   const int n_tiles = (n_keys + kPfKeys - 1) / kPfKeys;
 
@@ -295,9 +307,9 @@ prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, long long q_sb, long lo
 
   AttnState st;
   st.init();
-  const int row_rank[2] = {min(r0 + warp * 16 + g, num_q - 1), min(r0 + warp * 16 + g + 8, num_q - 1)};
+  const int row_rank[2] = {causal ? min(r0 + warp * 16 + g, num_q - 1) : 0, causal ? min(r0 + warp * 16 + g + 8, num_q - 1) : 0};
   const int limit[2] = {base_keys + row_rank[0], base_keys + row_rank[1]};   // last visible key of each row
-  const int warp_limit = base_keys + min(r0 + warp * 16 + 15, num_q - 1);
+  const int warp_limit = base_keys + (causal ? min(r0 + warp * 16 + 15, num_q - 1) : 0);
   const uint32_t q_frag = s_q + (warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * kMmaRow + (lane >> 4) * 16;
 
   for (int t = 0; t < n_tiles; ++t) {
@@ -308,8 +320,8 @@ prefill_attn_kernel(const __nv_bfloat16* __restrict__ q, long long q_sb, long lo
     __syncthreads();
     if (t * kPfKeys <= warp_limit) {   // later tiles are wholly masked for every row of this warp
       const uint32_t kbuf = s_kv + buf * 2 * kPfTile;
-      attn_tile_auto(st, q_frag, kbuf, kbuf + kPfTile, t * kPfKeys, limit, base_keys + min(r0 + warp * 16, num_q - 1),
-                     scale_log2e, lane);
+      attn_tile_auto(st, q_frag, kbuf, kbuf + kPfTile, t * kPfKeys, limit,
+                     base_keys + (causal ? min(r0 + warp * 16, num_q - 1) : 0), scale_log2e, lane);
     }
     __syncthreads();   // the tile's buffers may be refilled
   }
@@ -500,12 +512,17 @@ extern "C" int msa_sparse_prefill_attn(const void* q, int64_t q_stride_b, int64_
                                        int64_t store_stride_h, const int32_t* kv_start, const int32_t* kv_len,
                                        const int32_t* q_tok, const int32_t* num_q, int32_t n_seq, int32_t seq_len,
                                        int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim, int32_t dtype,
-                                       float scale, void* out, void* stream) {
+                                       int32_t causal, float scale, void* out, void* stream) {
   MSA_REQUIRE(q && k_store && v_store && kv_start && kv_len && q_tok && num_q && out, "prefill: null pointer");
-  MSA_REQUIRE(dtype == MSA_BF16 && head_dim == kMmaD,
-              "prefill: this kernel takes bf16 with head_dim 128 (other shapes use the library attention path)");
+  MSA_REQUIRE(dtype_ok(dtype) && head_dim > 0, "prefill: unknown dtype %d or bad head_dim", dtype);
   MSA_REQUIRE(n_seq >= 0 && seq_len >= 0 && n_q_heads > 0 && n_kv_heads > 0 && n_q_heads % n_kv_heads == 0 &&
                   n_q_heads <= 65535 && n_seq <= 65535, "prefill: bad sizes");
+  if (dtype != MSA_BF16 || head_dim != kMmaD) {   // fp32 / other head sizes: the general kernel
+    if (n_seq == 0 || seq_len == 0) return MSA_OK;
+    return launch_attention_rows_in_store(dtype, q, q_stride_b, q_stride_h, q_stride_s, k_store, v_store, store_stride_b,
+                                          store_stride_h, kv_start, kv_len, q_tok, num_q, n_seq, seq_len, n_q_heads,
+                                          n_kv_heads, head_dim, causal != 0, scale, out, (cudaStream_t)stream);
+  }
   MSA_REQUIRE(q_stride_b % 8 == 0 && q_stride_h % 8 == 0 && q_stride_s % 8 == 0 && store_stride_b % 8 == 0 &&
                   store_stride_h % 8 == 0 && aligned16(q) && aligned16(k_store) && aligned16(v_store) && aligned16(out),
               "prefill: rows must be 16-byte aligned");
@@ -516,7 +533,7 @@ extern "C" int msa_sparse_prefill_attn(const void* q, int64_t q_stride_b, int64_
   prefill_attn_kernel<<<grid, 128, kPfSmem, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)q, q_stride_b, q_stride_h, q_stride_s, (const __nv_bfloat16*)k_store,
       (const __nv_bfloat16*)v_store, store_stride_b, store_stride_h, kv_start, kv_len, q_tok, num_q, seq_len, n_q_heads,
-      n_kv_heads, scale * 1.4426950408889634f, (__nv_bfloat16*)out);
+      n_kv_heads, causal != 0, scale * 1.4426950408889634f, (__nv_bfloat16*)out);
   MSA_LAUNCH_OK("prefill_attn_kernel");
   return MSA_OK;
 }
@@ -529,8 +546,18 @@ extern "C" int msa_doc_attention_pool(const void* q, int64_t q_stride_b, int64_t
                                       const int32_t* chunk_offsets, int32_t n_chunks, int32_t pool_size, void* pooled_k,
                                       void* pooled_v, int64_t pool_chunk_stride, int64_t pool_head_stride, void* stream) {
   MSA_REQUIRE(q && k && v && token_index && seg_offsets && out, "doc_attention: null pointer");
-  MSA_REQUIRE(dtype == MSA_BF16 && head_dim == kMmaD,
-              "doc_attention: this kernel takes bf16 with head_dim 128 (other shapes use the library attention path)");
+  MSA_REQUIRE(dtype_ok(dtype) && head_dim > 0, "doc_attention: unknown dtype %d or bad head_dim", dtype);
+  if (dtype != MSA_BF16 || head_dim != kMmaD) {   // fp32 / other head sizes: the general kernel, pooling separately
+    MSA_REQUIRE(chunk_offsets == nullptr, "doc_attention: the K / V pooling by-product needs bf16 with head_dim 128 "
+                                          "(pool with msa_pool_chunks instead)");
+    MSA_REQUIRE(n_segments >= 0 && max_segment_len >= 0 && seq_len > 0 && n_q_heads > 0 && n_kv_heads > 0 &&
+                    n_q_heads % n_kv_heads == 0, "doc_attention: bad sizes");
+    if (n_segments == 0 || max_segment_len == 0) return MSA_OK;
+    return launch_attention_rows_by_index(dtype, q, q_stride_b, q_stride_h, q_stride_s, k, v, k_stride_b, k_stride_h,
+                                          k_stride_s, token_index, seg_offsets, n_segments,
+                                          (long long)n_segments * max_segment_len, seq_len, n_q_heads, n_kv_heads, head_dim,
+                                          scale, out, (cudaStream_t)stream);
+  }
   MSA_REQUIRE(n_segments >= 0 && max_segment_len >= 0 && seq_len > 0 && n_q_heads > 0 && n_kv_heads > 0 &&
                   n_q_heads % n_kv_heads == 0 && n_q_heads <= 65535 && n_segments <= 65535,
               "doc_attention: bad sizes (at most 65535 segments per call)");

@@ -7,6 +7,7 @@
 // row and writes the result.  Rows are cut into slices so that even a handful of queries
 // (decode-time routing) spreads over the whole GPU.  One read of the table, k results written.
 #include "common.cuh"
+#include "topk_warp.cuh"
 
 namespace msa {
 
@@ -69,88 +70,6 @@ sort_topk_kernel(const uint32_t* __restrict__ keys, long long table_stride, int 
   }
 }
 
-// Small k (<= kSelectMaxK): no sort.  Each warp extracts the k largest items of its eighth of the
-// slice by k rounds of a warp arg-max (shuffles only, no CTA barrier); warp 0 then extracts the
-// final k from the 8*k survivors.  Output order is descending by construction.
-constexpr int kSelectMaxK = 64;
-
-// k rounds over items[0..n) (shared memory, owned by this warp): writes the k largest, in order.
-// Every lane keeps the best of its own (strided) items in registers; a round is one redux on the
-// 32-bit score keys, a ballot (plus a second redux only when scores tie), and a rescan by the one
-// lane that lost its item.
-__device__ __forceinline__ void warp_extract_topk(unsigned long long* items, int n, int k, unsigned long long* out) {
-  const int lane = threadIdx.x & 31;
-  unsigned long long best = 0ull;
-  int best_i = -1;
-  auto rescan = [&]() {
-    best = 0ull;
-    best_i = -1;
-    for (int i = lane; i < n; i += 32) {
-      const unsigned long long v = items[i];
-      if (v > best) { best = v; best_i = i; }
-    }
-  };
-  rescan();
-  for (int r = 0; r < k; ++r) {
-    const uint32_t hi = (uint32_t)(best >> 32), lo = (uint32_t)best;
-    const uint32_t kmax = __reduce_max_sync(0xffffffffu, hi);
-    uint32_t tie = __ballot_sync(0xffffffffu, best != 0ull && hi == kmax);
-    if (__popc(tie) > 1) {  // equal scores: the smaller column (larger inverted column) goes first
-      const bool in_tie = (tie >> lane) & 1u;
-      const uint32_t lmax = __reduce_max_sync(0xffffffffu, in_tie ? lo : 0u);
-      tie = __ballot_sync(0xffffffffu, in_tie && lo == lmax);
-    }
-    unsigned long long top = 0ull;
-    if (tie != 0u) {
-      const int winner = __ffs(tie) - 1;
-      top = __shfl_sync(0xffffffffu, best, winner);
-      if (lane == winner) {
-        items[best_i] = 0ull;
-        rescan();
-      }
-    }
-    if (lane == 0) out[r] = top;
-    __syncwarp();
-  }
-}
-
-// k <= 32 without serial rounds.  The k-th largest of the 32 per-lane maxima is a lower bound T of the
-// k-th largest item (k items are >= T), so only items >= T can win: they are compacted in place
-// (typically a few more than k survive) and ordered by counting.  `scratch` holds 32 items.
-__device__ __forceinline__ void warp_filter_topk(unsigned long long* items, int n, int k, unsigned long long* out,
-                                                 unsigned long long* scratch) {
-  const int lane = threadIdx.x & 31;
-  const uint32_t lt_mask = (1u << lane) - 1u;
-  unsigned long long best = 0ull;
-  for (int i = lane; i < n; i += 32) best = items[i] > best ? items[i] : best;
-  scratch[lane] = best;
-  __syncwarp();
-  int rank = 0;
-#pragma unroll 8
-  for (int j = 0; j < 32; ++j) rank += (scratch[j] > best || (scratch[j] == best && j < lane)) ? 1 : 0;
-  const uint32_t kth = __ballot_sync(0xffffffffu, rank == k - 1);
-  const unsigned long long threshold = __shfl_sync(0xffffffffu, best, __ffs(kth) - 1);   // may be 0: keep everything
-  int n_c = 0;
-  for (int i0 = 0; i0 < n; i0 += 32) {
-    const int i = i0 + lane;
-    const unsigned long long v = i < n ? items[i] : 0ull;
-    const bool keep = v != 0ull && v >= threshold;
-    const uint32_t bal = __ballot_sync(0xffffffffu, keep);
-    __syncwarp();                                   // this row is in registers: its slots may be overwritten
-    if (keep) items[n_c + __popc(bal & lt_mask)] = v;
-    n_c += __popc(bal);
-  }
-  __syncwarp();
-  for (int c = lane; c < n_c; c += 32) {
-    const unsigned long long mine = items[c];
-    int r = 0;
-    for (int j = 0; j < n_c; ++j) r += items[j] > mine ? 1 : 0;   // composite items are unique
-    if (r < k) out[r] = mine;
-  }
-  for (int r = n_c + lane; r < k; r += 32) out[r] = 0ull;
-  __syncwarp();
-}
-
 template <bool FROM_KEYS>
 __global__ void __launch_bounds__(kSortThreads)
 select_topk_kernel(const uint32_t* __restrict__ keys, long long table_stride, int n_cols, int slice,
@@ -194,8 +113,14 @@ select_topk_kernel(const uint32_t* __restrict__ keys, long long table_stride, in
   }
   for (int i = threadIdx.x; i < keep; i += kSortThreads) {
     const unsigned long long w = s_final[i];
-    const long long col = 0xffffffffu - (uint32_t)(w & 0xffffffffull);
     const long long o = (long long)row * keep + i;
+    if (w == 0ull) {   // fewer than `keep` real items (producers that dropped entries): an empty slot, not a column
+      out_scores[o] = -INFINITY;
+      out_local[o] = 0;
+      if (out_global) out_global[o] = doc_ids_table ? doc_ids_table[0] : 0;
+      continue;
+    }
+    const long long col = 0xffffffffu - (uint32_t)(w & 0xffffffffull);
     out_scores[o] = key_to_float((uint32_t)(w >> 32));
     out_local[o] = col;
     if (out_global) out_global[o] = doc_ids_table ? doc_ids_table[col] : col;
@@ -246,6 +171,22 @@ topk_merge_kernel(const float* __restrict__ cand_scores, const int64_t* __restri
       out_rank[o] = w;
     }
   }
+}
+
+// Final level on its own: every row of `cand` holds n_in composite items (score key high, inverted column low,
+// 0 = empty) gathered from several producers; writes the best k_eff per row.  Used by the fused decode-time
+// routing kernel, whose CTAs are the producers.
+int launch_topk_from_candidates(const unsigned long long* cand, int n_in, int n_seq, int k_eff, const int64_t* doc_ids_table,
+                                float* out_scores, int64_t* out_local, int64_t* out_global, cudaStream_t stream) {
+  MSA_REQUIRE(n_in >= 1 && n_in <= kMaxSlice && k_eff >= 1 && k_eff <= kSelectMaxK && n_seq >= 1 && n_seq <= 65535,
+              "topk (candidates): bad sizes");
+  const int n2 = pow2_ceil(n_in);
+  static DeviceSmem configured{};
+  MSA_OK_OR_RETURN(ensure_dynamic_smem(select_topk_kernel<false>, kMaxSlice * 8, configured));
+  select_topk_kernel<false><<<dim3(1, n_seq), kSortThreads, (size_t)n2 * 8, stream>>>(
+      nullptr, 0, 0, 0, cand, n_in, n2, k_eff, nullptr, doc_ids_table, out_scores, out_local, out_global);
+  MSA_LAUNCH_OK("select_topk_kernel (candidates)");
+  return MSA_OK;
 }
 
 }  // namespace msa

@@ -40,6 +40,7 @@ class ModelConfig:
     router_layer_idx: str = "all"
     template_token_id: int = -2
     template_id_num: int = 3
+    envs: Optional[dict] = None     # environment of the stage-1 worker process (get_model_envs in the reference)
 
 
 @dataclass
@@ -242,6 +243,8 @@ class Memory:
         self.template_prefix_kvcache: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
         self._kv_offset = 0
         self._status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        #: decode-time routing (one query row per sequence) on the fused score + select kernel
+        self.fused_decode_routing = os.environ.get("MSA_B200_NO_FUSED_DECODE_ROUTING") is None
 
     # ------------------------------------------------------------------ bank build
     def _init_block_data(self, dtype: torch.dtype):
@@ -273,25 +276,71 @@ class Memory:
                         kw[layer]["template_prefix_vcache"].to(self.device))
                 for layer in kw if "template_prefix_kcache" in kw[layer]}
         n = None
+        chunk_major = hasattr(cache, "kv_chunk_major")     # a SharedPooledCache: already in the bank's layouts
         for layer in self.router_layer_ids:
-            k, v = cache.get_kvcache(layer)
-            rk = cache.get_router_kcache(layer)
-            if rk is None:
-                rk = k
-            n = k.shape[2] if n is None else n
-            assert n == k.shape[2] and self._kv_offset + n <= self.block_desc.chunks()
             blk = self.blocks[layer]
-            sl = slice(self._kv_offset, self._kv_offset + n)
-            blk.rk[sl].copy_(rk[0].permute(1, 0, 2), non_blocking=True)
-            blk.kv[sl, 0].copy_(k[0].permute(1, 0, 2))
-            blk.kv[sl, 1].copy_(v[0].permute(1, 0, 2))
+            if chunk_major:
+                kv, rk = cache.kv_chunk_major(layer), cache.rk_chunk_major(layer)
+                n = kv.shape[0] if n is None else n
+                assert n == kv.shape[0] and self._kv_offset + n <= self.block_desc.chunks()
+                sl = slice(self._kv_offset, self._kv_offset + n)
+                blk.kv[sl].copy_(kv)
+                blk.rk[sl].copy_(rk if rk is not None else kv[:, 0])
+            else:
+                k, v = cache.get_kvcache(layer)
+                rk = cache.get_router_kcache(layer)
+                if rk is None:
+                    rk = k
+                n = k.shape[2] if n is None else n
+                assert n == k.shape[2] and self._kv_offset + n <= self.block_desc.chunks()
+                sl = slice(self._kv_offset, self._kv_offset + n)
+                blk.rk[sl].copy_(rk[0].permute(1, 0, 2), non_blocking=True)
+                blk.kv[sl, 0].copy_(k[0].permute(1, 0, 2))
+                blk.kv[sl, 1].copy_(v[0].permute(1, 0, 2))
             if layer == self.router_layer_ids[0]:
                 self.block_desc.tmp_doc_ids.append(cache.cache_kwargs[layer]["pooled_doc_ids"])
         self._kv_offset += n or 0
+        if hasattr(cache, "clear_kvcache"):
+            cache.clear_kvcache()        # the receive loop's last step per block (:569); unlinks a shared block file
+
+    def _start_worker(self):
+        """Start this GPU's stage-1 worker process and wait until it has loaded its model (src/msa_service.py:323-337)."""
+        import multiprocessing as mp
+        from .prefill import PrefillStage1Worker
+        ctx = mp.get_context("spawn")
+        self._worker_req_q, self._worker_rsp_q = ctx.Queue(), ctx.Queue()
+        template = getattr(self.generate_config, "template", None) or {"prompt": "<|im_start|>user\n{prompt}<|im_end|>\n"}
+        envs = dict(getattr(self.model_config, "envs", None) or {})
+        self._worker_process = ctx.Process(
+            target=PrefillStage1Worker.prefill_worker_main,
+            args=(self.gpu_id, self._worker_req_q, self._worker_rsp_q, self.model_config.model_path, template,
+                  self.memory_config.pooling_kernel_size, self.memory_config.block_size, envs),
+            name=f"PrefillStage1Worker-{self.gpu_id}")
+        self._worker_process.start()
+        PrefillStage1Worker.wait_for_ready(self._worker_rsp_q)
+
+    def _stop_worker(self):
+        from .prefill import PrefillStage1Worker
+        PrefillStage1Worker.close_worker(self._worker_req_q)
+        self._worker_process.join()
+        self._worker_process = None
+        self._worker_req_q = self._worker_rsp_q = None
+
+    def _worker_metas(self, docs: List[Document]):
+        """The receive loop of the reference's ``generate_blocks`` (:511-523): send the documents, yield META
+        payloads until every document has come back."""
+        from .prefill import PrefillStage1Worker
+        PrefillStage1Worker.send_documents(self._worker_req_q, docs)
+        recv = 0
+        while recv < len(docs):
+            meta = PrefillStage1Worker.recv_meta(self._worker_rsp_q)
+            recv += meta["nr_docs"]
+            yield meta
 
     def generate_blocks(self, docs: List[Document], metas: Optional[Iterable[dict]] = None):
-        """``Memory.generate_blocks`` (src/msa_service.py:497-582) with the stage-1 results handed in
-        as an iterable of META payloads instead of being pulled from a worker process."""
+        """``Memory.generate_blocks`` (src/msa_service.py:497-582).  Without ``metas`` the stage-1 results are pulled
+        from this GPU's ``PrefillStage1Worker`` process, as in the reference; ``metas`` (an iterable of META payloads)
+        feeds a bank from a worker the caller drives itself."""
         data_path = os.environ.get("MEMORY_DATA_PATH", "")
         if data_path:   # same convention as the reference: $MEMORY_DATA_PATH/gpu<world>/<gpu_id> (:498-505)
             world = getattr(self, "world_size", None) or getattr(self.generate_config, "world", 1) or 1
@@ -307,9 +356,17 @@ class Memory:
                     f"{data_path} holds a bank in the reference's format (stub.json / meta.pt / layer_*_k.pt), which "
                     "this package does not read in place: convert it once with "
                     "msa_b200.memory.convert_reference_bank(src_dir, dst_dir) or point MEMORY_DATA_PATH elsewhere")
+        own_worker = metas is None and bool(self.model_config.model_path)
+        if own_worker:
+            self._start_worker()
+            metas = self._worker_metas(docs)
         self.begin_blocks(docs)
-        for meta in metas or ():
-            self.ingest_meta(meta)
+        try:
+            for meta in metas or ():
+                self.ingest_meta(meta)
+        finally:
+            if own_worker:
+                self._stop_worker()
         self.block_desc.merge_poolig_doc_id(self.device)
         if data_path:
             self.serialize(data_path)
@@ -428,6 +485,16 @@ class Memory:
         desc = self.block_desc
         blk = self.blocks[layer_idx]
         min_val = torch.finfo(blk.rk.dtype).min
+        if self.chunk_reduce_method == "max" and self.fused_decode_routing and \
+                ops.route_score_select_supported(blk.rk, n_seq, s_pad, top_k):
+            # one token per sequence: scoring and per-CTA selection in one launch, no score table
+            need = (n_seq, top_k)
+            ws = self.__dict__.get("_select_ws")
+            if ws is None or ws[0] != need:
+                n_bytes = int(A.lib().msa_route_score_select_workspace_bytes(n_seq, top_k))
+                ws = self._select_ws = (need, torch.empty((max(n_bytes, 8) + 7) // 8, dtype=torch.int64, device=self.device))
+            return ops.route_score_select(q_folded, row_bias, n_seq, blk.rk, desc.chunk_doc, desc.nr_docs, scale / n_heads,
+                                          top_k, desc.doc_ids, min_val, self._status, ws[1], out)
         if self.chunk_reduce_method == "max":
             keys, _ = ops.route_scores(q_folded, row_bias, n_seq, s_pad, blk.rk, desc.chunk_doc, desc.nr_docs,
                                        alpha=scale / n_heads, min_val=min_val, status=self._status)

@@ -192,6 +192,53 @@ def route_reduce_chunks(chunk_keys: torch.Tensor, chunk_doc: torch.Tensor, n_doc
     return keys
 
 
+ROUTE_SELECT_MAX_SEQ, ROUTE_SELECT_MAX_K = 128, 32
+
+
+def route_score_select_supported(rk: torch.Tensor, n_seq: int, s_pad: int, top_k: int) -> bool:
+    """Whether ``route_score_select`` takes this shape (bf16 keys, one row per sequence, small batch and k)."""
+    kdim = rk[0].numel() if rk.shape[0] else 0
+    return (rk.dtype == torch.bfloat16 and s_pad == 1 and 1 <= n_seq <= ROUTE_SELECT_MAX_SEQ and top_k <= ROUTE_SELECT_MAX_K
+            and rk.shape[0] > 0 and kdim % 64 == 0)
+
+
+def route_score_select(q_folded: torch.Tensor, row_bias: torch.Tensor, n_seq: int, rk: torch.Tensor,
+                       chunk_doc: torch.Tensor, n_docs: int, alpha: float, top_k: int,
+                       doc_ids_table: Optional[torch.Tensor] = None, min_val: Optional[float] = None,
+                       status: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None, out=None):
+    """Decode-time routing in one call: scores ``n_seq`` single-row queries against the shard and selects the best
+    ``top_k`` documents of each, without a score table (see ``msa_route_score_select``).  Same results, ties included,
+    as ``route_scores`` + ``topk_select``.  Returns ``(scores f32, local_ids i64, global_ids i64)``, ``[n_seq, k_eff]``."""
+    A.need_cuda(q_folded, row_bias, rk, chunk_doc, doc_ids_table, status, workspace)
+    dev = rk.device
+    c = rk.shape[0]
+    rk2 = rk.reshape(c, -1) if rk.is_contiguous() else rk.flatten(1)
+    if chunk_doc.dtype != torch.int32:
+        raise A.MsaError("route_score_select: chunk_doc must be int32")
+    k_eff = min(top_k, n_docs + 1)
+    if out is not None:
+        scores, local, glob = out
+    else:
+        scores = torch.empty((n_seq, k_eff), dtype=torch.float32, device=dev)
+        local = torch.empty((n_seq, k_eff), dtype=torch.int64, device=dev)
+        glob = torch.empty((n_seq, k_eff), dtype=torch.int64, device=dev)
+    if min_val is None:
+        min_val = torch.finfo(rk.dtype).min
+    if status is None:
+        status = torch.zeros(4, dtype=torch.int32, device=dev)
+    need = int(A.lib().msa_route_score_select_workspace_bytes(n_seq, top_k))
+    if need < 0:
+        raise A.MsaError("route_score_select: no CUDA device is current")
+    if workspace is None or workspace.numel() * workspace.element_size() < need:
+        workspace = torch.empty((need + 7) // 8, dtype=torch.int64, device=dev)
+    A.check(A.lib().msa_route_score_select(A.ptr(q_folded), A.ptr(row_bias), A.dtype_code(rk.dtype), n_seq, A.ptr(rk2),
+                                           rk2.stride(0), c, rk2.shape[1], A.ptr(chunk_doc), float(alpha), n_docs,
+                                           float(min_val), top_k, A.ptr(doc_ids_table), A.ptr(scores), A.ptr(local),
+                                           A.ptr(glob), A.ptr(workspace), workspace.numel() * workspace.element_size(),
+                                           A.ptr(status), A.stream_ptr(dev)), "msa_route_score_select")
+    return scores, local, glob
+
+
 def route_table_reset(keys: torch.Tensor, n_docs: int, min_val: float, status: Optional[torch.Tensor] = None):
     A.need_cuda(keys, status)
     A.check(A.lib().msa_route_table_reset(A.ptr(keys), keys.stride(0), n_docs, keys.shape[0], float(min_val),
@@ -419,10 +466,38 @@ def assemble_context(template_k, template_v, sel_k, sel_v, n_sel, key_states, va
     return k_store, v_store, kv_start, kv_len, q_tok, num_q, err
 
 
+def append_segment(key_states: torch.Tensor, value_states: torch.Tensor, valid: torch.Tensor, k_store: torch.Tensor,
+                   v_store: torch.Tensor, kv_start: Optional[torch.Tensor], kv_len: torch.Tensor):
+    """Append the valid tokens of a segment ``[B, Hkv, S, D]`` to every sequence's store ``[B, Hkv, L, D]`` in place;
+    ``kv_len`` (int32) grows by the number of valid tokens.  Returns ``(q_tok[B, S], num_q[B], error_flag[1])``;
+    ``error_flag`` is 1 when some sequence's store had no room (that sequence is unchanged, ``num_q`` 0)."""
+    A.need_cuda(key_states, value_states, valid, k_store, v_store, kv_start, kv_len)
+    b, hkv, s, d = key_states.shape
+    if key_states.stride(3) != 1 or value_states.stride() != key_states.stride():
+        key_states, value_states = key_states.contiguous(), value_states.contiguous()
+    if k_store.stride(3) != 1 or k_store.stride(2) != d or v_store.stride() != k_store.stride():
+        raise A.MsaError("append_segment: stores must be [B, Hkv, L, D] with contiguous (L, D)")
+    if kv_len.dtype != torch.int32 or (kv_start is not None and kv_start.dtype != torch.int32):
+        raise A.MsaError("append_segment: kv_start / kv_len must be int32")
+    vmask = valid.reshape(b, s)
+    vmask = vmask.contiguous().view(torch.uint8) if vmask.dtype == torch.bool else vmask.to(torch.uint8).contiguous()
+    dev = key_states.device
+    q_tok = torch.empty((b, s), dtype=torch.int32, device=dev)
+    meta = torch.zeros(b + 1, dtype=torch.int32, device=dev)
+    A.check(A.lib().msa_append_segment(
+        A.ptr(key_states), A.ptr(value_states), key_states.stride(0), key_states.stride(1), key_states.stride(2),
+        A.ptr(vmask), b, s, hkv, d, A.dtype_code(key_states.dtype), A.ptr(k_store), A.ptr(v_store), k_store.stride(0),
+        k_store.stride(1), k_store.shape[2], A.ptr(kv_start), A.ptr(kv_len), A.ptr(q_tok), A.ptr(meta), A.ptr(meta[b:]),
+        A.stream_ptr(dev)), "msa_append_segment")
+    return q_tok, meta[:b], meta[b:]
+
+
 def sparse_prefill_attn(q: torch.Tensor, k_store, v_store, kv_start, kv_len, q_tok, num_q, scale: Optional[float] = None,
-                        out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """q ``[B, Hq, S, D]`` (bf16, D = 128).  Returns ``[B, S, Hq*D]``; rows of invalid tokens are zero
-    (written by the kernel: ``out`` may be uninitialised)."""
+                        out: Optional[torch.Tensor] = None, causal: bool = True) -> torch.Tensor:
+    """q ``[B, Hq, S, D]``.  Returns ``[B, S, Hq*D]``; rows of invalid tokens are zero (written by the kernel:
+    ``out`` may be uninitialised).  ``causal``: bottom-right aligned causal mask (stage 2); False = every valid
+    token sees the whole context (multi-token decode segments).  bf16 / D = 128 on tensor cores, anything else on
+    the general kernel."""
     A.need_cuda(q, k_store, v_store)
     b, hq, s, d = q.shape
     if q.stride(3) != 1:
@@ -433,7 +508,7 @@ def sparse_prefill_attn(q: torch.Tensor, k_store, v_store, kv_start, kv_len, q_t
     A.check(A.lib().msa_sparse_prefill_attn(
         A.ptr(q), q.stride(0), q.stride(1), q.stride(2), A.ptr(k_store), A.ptr(v_store), k_store.stride(0),
         k_store.stride(1), A.ptr(kv_start), A.ptr(kv_len), A.ptr(q_tok), A.ptr(num_q), b, s, hq, k_store.shape[1], d,
-        A.dtype_code(q.dtype), float(scale), A.ptr(out), A.stream_ptr(q.device)), "msa_sparse_prefill_attn")
+        A.dtype_code(q.dtype), int(causal), float(scale), A.ptr(out), A.stream_ptr(q.device)), "msa_sparse_prefill_attn")
     return out
 
 
@@ -441,8 +516,8 @@ def doc_attention_pool(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, token_
                        seg_offsets: torch.Tensor, max_segment_len: int, out: Optional[torch.Tensor] = None,
                        chunk_offsets: Optional[torch.Tensor] = None, pool_size: int = 64, head_major_out: bool = False,
                        scale: Optional[float] = None):
-    """Causal attention inside every segment of ``token_index`` (bf16, D = 128) and, when ``chunk_offsets`` is
-    given, the chunk means of K and V from the same pass.  q ``[B, Hq, S, D]``; k, v ``[B, Hkv, S, D]``;
+    """Causal attention inside every segment of ``token_index`` and, when ``chunk_offsets`` is given (bf16, D = 128
+    only), the chunk means of K and V from the same pass.  q ``[B, Hq, S, D]``; k, v ``[B, Hkv, S, D]``;
     token_index ``[Td]`` int32 flat positions; seg_offsets ``[n+1]`` int32.  ``out`` ``[B, S, Hq*D]`` keeps its
     content on rows that no segment lists (zeros when allocated here).
     Returns ``(out, pooled_k, pooled_v)``; pooled ``[C, Hkv, D]`` or, head major, ``[1, Hkv, C, D]`` (None without pooling)."""

@@ -382,6 +382,26 @@ def qwen3_attention_states(hidden, weights: dict, cos, sin, n_q_heads: int, n_kv
     return rope_rotate_half(q, c, sn), rope_rotate_half(k, c, sn), v
 
 
+def decode_segment_attention(q, cache_k, cache_v, key_mask, new_k, new_v, new_mask, scale: Optional[float] = None):
+    """The decode branch in ``qa_mode`` (src/msa/memory_sparse_attention.py:371-399, mask handling :375-380): a
+    segment of q_len tokens, EVERY one of which attends to the cache positions whose ``key_mask`` is set and to the
+    segment's own tokens whose ``new_mask`` is set -- no causal mask inside the segment.  q ``[B, Hq, q_len, D]``;
+    cache ``[B, Hkv, L, D]``; key_mask ``[B, L]`` bool; new_k / new_v ``[B, Hkv, q_len, D]``; new_mask ``[B, q_len]``.
+    Returns ``(out[B, q_len, Hq*D], grown cache_k, cache_v, key_mask)`` as the reference leaves them (masked tokens
+    are stored too; the mask says so).  Rows of sequences with no visible key at all are NaN in the reference and
+    left as zeros here."""
+    b, hq, ql, d = q.shape
+    g = hq // cache_k.shape[1]
+    full_k, full_v = torch.cat([cache_k, new_k], dim=2), torch.cat([cache_v, new_v], dim=2)
+    mask = torch.cat([key_mask.bool(), new_mask.bool()], dim=1)
+    s = scale if scale is not None else 1.0 / math.sqrt(d)
+    att = torch.matmul(q.to(torch.float32), full_k.repeat_interleave(g, dim=1).to(torch.float32).transpose(-1, -2)) * s
+    att = att.masked_fill(~mask[:, None, None, :], float("-inf"))
+    p = torch.softmax(att, dim=-1).nan_to_num(0.0)
+    o = torch.matmul(p, full_v.repeat_interleave(g, dim=1).to(torch.float32))
+    return o.transpose(1, 2).reshape(b, ql, hq * d), full_k, full_v, mask
+
+
 def rope_rotate_half(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
     """Half-split RoPE of transformers' Qwen3 (``apply_rotary_pos_emb``; third-party, pinned
     by requirements.txt to transformers 4.51.3; call site

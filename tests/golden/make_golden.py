@@ -199,6 +199,52 @@ def gen_layer(svc, msa_layer, MSAConfig):
     save("layer_decode", cache_k=ck, cache_v=cv, kv_lengths=kv_lengths, **steps)
 
 
+def gen_layer_decode_qa(svc, msa_layer, MSAConfig):
+    """The decode branch of the reference layer in qa_mode (memory_sparse_attention.py:375-380): a multi-token segment
+    with masked tokens (left padding and a finished sequence), then a one-token step in which one sequence is masked,
+    then another segment.  Every token of a step attends, without a causal mask, to the cache and to the step's own
+    unmasked tokens."""
+    from transformers.models.qwen3.modeling_qwen3 import Qwen3RotaryEmbedding
+    torch.manual_seed(707)
+    hq, hkv, d = 4, 2, 16
+    cfg = MSAConfig(
+        msa_config=dict(router_layer_idx="0", aux_loss=False, aux_loss_method="INFONCE", decouple_router=True,
+                        top_k_docs=2, pooling_kernel_size=8, head_reduce_method="mean",
+                        query_reduce_method="max", chunk_reduce_method="max", decouple_pooling_mode="mean"),
+        hidden_size=hq * d, num_attention_heads=hq, num_key_value_heads=hkv, head_dim=d,
+        num_hidden_layers=1, intermediate_size=64, vocab_size=32, max_position_embeddings=512)
+    cfg._attn_implementation = "eager"
+    layer = msa_layer.MemorySparseAttention(cfg, 0).eval()
+    rope = Qwen3RotaryEmbedding(cfg)
+    b, max_l = 3, 9
+    kv_lengths = torch.tensor([9, 6, 3])
+    ck, cv = torch.randn(b, hkv, max_l, d), torch.randn(b, hkv, max_l, d)
+    cache = StubCache()
+    cache.meta["qa_mode"] = True
+    cache.record_kwargs(0, {"stage": "generate", "compacked_key_cache": ck.clone(), "compacked_value_cache": cv.clone(),
+                            "kv_lengths": kv_lengths.clone(),
+                            "attention_mask": torch.arange(max_l).unsqueeze(0) >= (max_l - kv_lengths.unsqueeze(1))})
+    arrays = {"w__" + k: v for k, v in layer.state_dict().items()}
+    arrays.update(hq=hq, hkv=hkv, d=d, cache_k=ck, cache_v=cv, kv_lengths=kv_lengths,
+                  rope_theta=float(getattr(cfg, "rope_theta", 0.0) or cfg.rope_parameters["rope_theta"]))
+    masks = [torch.tensor([[0, 0, 1, 1, 1], [1, 1, 1, 1, 1], [0, 0, 0, 0, 0]]),      # left padding; a finished sequence
+             torch.tensor([[1], [0], [1]]),
+             torch.tensor([[1, 1, 1], [0, 1, 1], [0, 0, 1]])]
+    pos = kv_lengths.clone()
+    for step, am in enumerate(masks):
+        q_len = am.shape[1]
+        hidden = torch.randn(b, q_len, hq * d)
+        position_ids = pos.view(b, 1) + (am.cumsum(1) - 1).clamp(min=0)
+        with torch.no_grad():
+            out, _ = layer(hidden, torch.full((b, q_len), -1), am, rope(hidden, position_ids), cache)
+        pos = pos + am.sum(1)
+        arrays.update({f"s{step}_hidden": hidden, f"s{step}_attention_mask": am, f"s{step}_position_ids": position_ids,
+                       f"s{step}_out": out})
+    arrays.update(final_mask=cache.cache_kwargs[0]["attention_mask"], final_cache_k=cache.cache_kwargs[0]["compacked_key_cache"],
+                  n_steps=len(masks))
+    save("layer_decode_qa", **arrays)
+
+
 def gen_layer_e2e(svc, msa_layer, MSAConfig):
     """One reference layer through the whole path: stage 1 (encode a block, pool), a reference
     MSAService built from that stage-1 cache (one gloo rank), stage 2 (route, fetch, assemble,
@@ -509,4 +555,5 @@ if __name__ == "__main__":
     gen_routing(svc)
     gen_layer_e2e(svc, msa_layer, MSAConfig)
     gen_layer_attn128(svc, msa_layer, MSAConfig)
+    gen_layer_decode_qa(svc, msa_layer, MSAConfig)
     gen_doc_query(a.reference)

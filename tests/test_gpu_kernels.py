@@ -205,6 +205,80 @@ def test_routing_vs_oracle(ops, shape, dtype):
         assert torch.allclose(table, table_simt, atol=2e-5, rtol=0)
 
 
+FUSED_CASES = [
+    # (sequences, documents, chunks per document (lo, hi), k, masked sequences)
+    (32, 3000, (8, 8), 16, []),         # uniform documents, several tiles per CTA
+    (1, 500, (1, 12), 16, []),          # a single sequence
+    (100, 2500, (1, 20), 32, [3]),      # ragged, k = 32, one sequence without any routing token
+    (128, 900, (1, 9), 8, [0, 127]),    # the widest query tile
+    (16, 40, (1, 3), 16, []),           # fewer chunk tiles than SMs
+    (7, 9, (1, 2), 16, []),             # fewer documents than k: k' = n_docs + 1, the dummy document is selected
+    (32, 60000, (1, 1), 16, []),        # single-chunk documents: more documents per CTA than table rows -> flushes
+    (24, 30000, (1, 4), 16, []),        # flushes with documents that are still open at the flush
+    (8, 6, (200, 400), 4, []),          # documents longer than a CTA's range
+]
+
+
+@pytest.mark.parametrize("case", FUSED_CASES)
+def test_route_score_select_equals_table_path(ops, case):
+    """The fused decode-time routing call against msa_route_scores + msa_topk_select on the same inputs: scores,
+    local ids and global ids must be identical, ties and the dummy document included."""
+    b, n_docs, (lo, hi), k, masked = case
+    chunks = ragged_docs(n_docs, lo, hi, seed=n_docs + b)
+    rk, pool_ids = make_bank(chunks, dtype=torch.bfloat16, seed=b)
+    g = torch.Generator().manual_seed(17 + b)
+    q = torch.nn.functional.normalize(torch.randn(b, 32, 1, 128, generator=g), dim=-1).to(torch.bfloat16)
+    mask = torch.ones(b, 1, dtype=torch.bool)
+    for i in masked:
+        mask[i] = False
+    table_ids = torch.arange(1000, 1000 + n_docs + 1)
+    table_ids[0] = 0
+    rk_d, cd, tid = rk.to(DEV), pool_ids.to(torch.int32).to(DEV), table_ids.to(DEV)
+    qf, bias, s_pad = ops.fold_queries(q.to(DEV), mask.to(DEV), 4)
+    assert s_pad == 1 and ops.route_score_select_supported(rk_d, b, s_pad, k)
+    keys, status = ops.route_scores(qf, bias, b, s_pad, rk_d, cd, n_docs, alpha=1.0 / 32)
+    ref_s, ref_l, ref_g = ops.topk_select(keys, k, tid)
+    status2 = torch.zeros(4, dtype=torch.int32, device=DEV)
+    s, l, g_ = ops.route_score_select(qf, bias, b, rk_d, cd, n_docs, 1.0 / 32, k, tid, status=status2)
+    torch.cuda.synchronize()
+    assert status.cpu().tolist() == [0, 0, 0, 0] and status2.cpu().tolist() == [0, 0, 0, 0]
+    assert s.shape == ref_s.shape == (b, min(k, n_docs + 1))
+    assert torch.equal(s, ref_s) and torch.equal(l, ref_l) and torch.equal(g_, ref_g)
+    # and against the oracle, tie aware
+    table_ref = O.route_doc_scores(q.float().view(b, 8, 4, 1, 128), mask, rk.float().transpose(0, 1), pool_ids, n_docs)
+    live = [i for i in range(b) if i not in masked]
+    check_topk(table_ref.clamp_min(torch.finfo(torch.bfloat16).min)[live], s[live], l[live], k, tol=1e-3)
+
+
+def test_route_score_select_through_memory_and_bounds(ops):
+    """Memory.score_folded takes the fused path for one-token queries (same winners as with the path switched
+    off), and chunk ids outside 1..n_docs are skipped and counted instead of being used as table rows."""
+    from msa_b200.memory import AttentionGeometry, Document, Memory, ModelConfig
+    chunks = ragged_docs(700, 1, 9, seed=5)
+    rk, pool_ids = make_bank(chunks, dtype=torch.bfloat16, seed=6)
+    mem = Memory(0, None, ModelConfig(doc_top_k=16, router_layer_idx="0"), None, AttentionGeometry(num_hidden_layers=1))
+    z = torch.zeros_like(rk)
+    mem.load_pooled([Document(doc_id=50 + i, num_chunks=n) for i, n in enumerate(chunks)], {0: (z, z, rk.to(DEV))})
+    g = torch.Generator().manual_seed(7)
+    q = torch.nn.functional.normalize(torch.randn(20, 8, 4, 1, 128, generator=g), dim=-1).to(torch.bfloat16).to(DEV)
+    mask = torch.ones(20, 1, 1, 1, 1, dtype=torch.bool, device=DEV)
+    assert mem.fused_decode_routing
+    a = mem.prefill_stage2(0, q, mask)
+    mem.fused_decode_routing = False
+    b_ = mem.prefill_stage2(0, q, mask)
+    mem.check_status()
+    assert all(torch.equal(x, y) for x, y in zip(a, b_))
+    bad = pool_ids.clone().to(torch.int32)
+    bad[-4:] = len(chunks) + 3
+    qf, bias, _ = ops.fold_queries(q.view(20, 32, 1, 128), mask.view(20, 1), 4)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    s, l, _ = ops.route_score_select(qf, bias, 20, rk.to(DEV), bad.to(DEV), len(chunks), 1.0 / 32, 16, status=status)
+    torch.cuda.synchronize()
+    st = status.cpu().tolist()
+    assert st[0] == 0 and st[2] > 0
+    assert int(l.max()) <= len(chunks)
+
+
 def test_routing_scaled_dot_mode(ops):
     """Un-normalised scores times head_dim^-0.5 (the mode the reference falls into when
     aux_loss_method is not exactly "INFONCE", src/msa_service.py:318-321, 1095-1096)."""

@@ -112,3 +112,54 @@ def test_training_forward_is_rejected(e2e):
             layer(torch.zeros(1, 2, 64, device=DEV), torch.zeros(1, 2, dtype=torch.long, device=DEV))
     finally:
         layer.eval()
+
+
+def test_qa_mode_decode_segments_match_reference_layer(golden):
+    """The layer mirror's decode branch in qa_mode (multi-token, non-causal segments with masked tokens; reference:
+    src/msa/memory_sparse_attention.py:375-380) against the reference layer's own outputs.  fp32, head_dim 16: the
+    segment append kernel and the general attention kernel.  Rows of masked tokens are unspecified in the reference
+    (it computes them and nobody reads them) and zero here."""
+    from transformers.models.qwen3.modeling_qwen3 import Qwen3RotaryEmbedding
+    from msa_b200.attention import MemorySparseAttention
+    from msa_b200.cache import SparseCache
+    from msa_b200.configuration import MSAConfig
+    g = golden("layer_decode_qa")
+    hq, hkv, d = int(g["hq"]), int(g["hkv"]), int(g["d"])
+    cfg = MSAConfig(
+        msa_config=dict(router_layer_idx="0", aux_loss=False, aux_loss_method="INFONCE", decouple_router=True,
+                        top_k_docs=2, pooling_kernel_size=8, head_reduce_method="mean", query_reduce_method="max",
+                        chunk_reduce_method="max", decouple_pooling_mode="mean"),
+        hidden_size=hq * d, num_attention_heads=hq, num_key_value_heads=hkv, head_dim=d, num_hidden_layers=1,
+        intermediate_size=64, vocab_size=32, max_position_embeddings=512)
+    cfg._attn_implementation = "eager"
+    layer = MemorySparseAttention(cfg, 0).eval()
+    layer.load_state_dict({k[3:]: T(v) for k, v in g.items() if k.startswith("w__")})
+    layer.to(DEV)
+    rope = Qwen3RotaryEmbedding(cfg).to(DEV)
+    ck, cv, lens = T(g["cache_k"]).to(DEV), T(g["cache_v"]).to(DEV), T(g["kv_lengths"]).to(DEV)
+    max_l = ck.shape[2]
+    cache = SparseCache()
+    cache.meta["qa_mode"] = True
+    cache.record_kwargs(0, {"stage": "generate", "compacked_key_cache": ck.clone(), "compacked_value_cache": cv.clone(),
+                            "kv_lengths": lens.clone(),
+                            "attention_mask": torch.arange(max_l, device=DEV).unsqueeze(0) >= (max_l - lens.unsqueeze(1))})
+    valid_total = lens.clone()
+    for step in range(int(g["n_steps"])):
+        hidden, am = T(g[f"s{step}_hidden"]).to(DEV), T(g[f"s{step}_attention_mask"]).to(DEV)
+        b, q_len = am.shape
+        with torch.no_grad():
+            out, _ = layer(hidden, torch.full((b, q_len), -1, device=DEV), am,
+                           rope(hidden, T(g[f"s{step}_position_ids"]).to(DEV)), cache)
+        valid = (am == 1).cpu()
+        assert rel_err(out.cpu()[valid], T(g[f"s{step}_out"])[valid]) < 1e-5
+        valid_total = valid_total + am.sum(1)
+        kw = cache.cache_kwargs[0]
+        # the store keeps only unmasked entries, one contiguous run per sequence
+        assert torch.equal(kw["attention_mask"].sum(1), valid_total)
+        assert torch.equal(kw["kv_lengths"], valid_total)
+    # same entries as the reference's cache, in the same order, once its masked slots are dropped
+    kw = cache.cache_kwargs[0]
+    ref_k, ref_m = T(g["final_cache_k"]), T(g["final_mask"]).bool()
+    got_k, got_m = kw["compacked_key_cache"].cpu(), kw["attention_mask"].cpu()
+    for i in range(ref_k.shape[0]):
+        assert rel_err(got_k[i][:, got_m[i]], ref_k[i][:, ref_m[i]]) < 1e-6

@@ -96,16 +96,105 @@ def test_assemble_fp32_and_overflow_flag():
         assert start2[long_one].item() < 0 and ks2[long_one].abs().sum().item() == 0
 
 
-def test_prefill_rejects_other_shapes():
+@pytest.mark.parametrize("dtype,d,tol", [(torch.float32, 16, 1e-5), (torch.float32, 128, 1e-5), (torch.bfloat16, 64, 1e-2),
+                                         (torch.float32, 200, 1e-5)])
+@pytest.mark.parametrize("causal", [True, False])
+def test_general_attention_kernel_in_store(dtype, d, tol, causal):
+    """fp32 and head sizes other than 128 (the reference's CPU-runnable configuration among them): stage-2 attention
+    on the general kernel, with and without the causal mask, against the oracle."""
     from msa_b200 import ops
-    from msa_b200._cabi import MsaError
+    from oracle import msa_oracle as O
     dev = torch.device("cuda:0")
-    q = torch.zeros(1, 4, 8, 64, dtype=torch.bfloat16, device=dev)
-    ks = torch.zeros(1, 2, 16, 64, dtype=torch.bfloat16, device=dev)
-    z = torch.zeros(1, dtype=torch.int32, device=dev)
-    qt = torch.zeros(1, 8, dtype=torch.int32, device=dev)
-    with pytest.raises(MsaError):
-        ops.sparse_prefill_attn(q, ks, ks, z, z, qt, z)
+    b, s, hq, hkv, t_len, n_sel = 3, 37, 8, 2, 3, [11, 0, 40]
+    q, k, v, tk, tv, sk, sv, valid = _case(23, b, s, hq, hkv, d, t_len, n_sel, 0.8, dtype, dev)
+    nsel = torch.tensor(n_sel, dtype=torch.int64, device=dev)
+    lens = [t_len + n_sel[i] + int(valid[i].sum()) for i in range(b)]
+    ks, vs, kv_start, kv_len, q_tok, num_q, err = ops.assemble_context(tk, tv, sk, sv, nsel, k, v, valid, max(lens), 2)
+    out = ops.sparse_prefill_attn(q, ks, vs, kv_start, kv_len, q_tok, num_q, causal=causal)
+    torch.cuda.synchronize()
+    if causal:
+        ref, _ = _reference(q, k, v, tk, tv, sk, sv, valid, n_sel, d ** -0.5)
+    else:   # every valid token sees its whole context
+        ref = torch.zeros(b, s, hq * d)
+        for i in range(b):
+            idx = valid[i].nonzero().flatten().cpu()
+            kk, vv = ks[i, :, max(lens) - lens[i]:max(lens)].cpu(), vs[i, :, max(lens) - lens[i]:max(lens)].cpu()
+            full = O._causal_segment(q[i][:, idx].cpu(), kk, vv, d ** -0.5, lens[i])       # offset >= nk: no masking
+            ref[i, idx] = full
+        ref = ref.to(dev)
+    errn = (out.float() - ref.float()).norm() / ref.float().norm()
+    assert errn.item() < tol, errn.item()
+    assert out[~valid].abs().sum().item() == 0
+
+
+@pytest.mark.parametrize("dtype,d,tol", [(torch.float32, 16, 1e-5), (torch.bfloat16, 64, 1e-2), (torch.float32, 128, 1e-5)])
+def test_general_attention_kernel_by_index(dtype, d, tol):
+    """Stage-1 attention inside documents on the general kernel (masked tokens inside documents, two block rows)."""
+    from msa_b200 import ops
+    from oracle import msa_oracle as O
+    dev = torch.device("cuda:0")
+    hq, hkv, s = 4, 2, 90
+    g = torch.Generator().manual_seed(31)
+    doc_ids = torch.zeros(2, s, dtype=torch.long)
+    doc_ids[0, :3] = -2
+    doc_ids[0, 3:40], doc_ids[0, 40:41], doc_ids[0, 41:90] = 1, 2, 3
+    doc_ids[1, 5:70], doc_ids[1, 70:88] = 1, 2
+    mask = torch.ones(2, s, dtype=torch.long)
+    mask[0, 10:13] = 0
+    mask[1, 69] = 0
+    q, k, v = [torch.randn(2, h, s, d, generator=g).to(dtype) for h in (hq, hkv, hkv)]
+    ref = O.stage1_doc_attention(q, k, v, doc_ids, mask)
+    tok, off, _ = ops.chunk_bookkeeping(doc_ids.to(dev), mask.to(dev), 8)
+    flat = (doc_ids > 0) & (mask == 1)
+    counts = torch.unique_consecutive((torch.arange(2).view(2, 1) * 10 + doc_ids)[flat], return_counts=True)[1]
+    seg = torch.cat([torch.zeros(1, dtype=torch.long), counts.cumsum(0)]).to(torch.int32).to(dev)
+    out, _, _ = ops.doc_attention_pool(q.to(dev), k.to(dev), v.to(dev), tok, seg, int(counts.max()))
+    t_tok = torch.arange(3, dtype=torch.int32, device=dev)
+    ops.doc_attention_pool(q.to(dev), k.to(dev), v.to(dev), t_tok, torch.tensor([0, 3], dtype=torch.int32, device=dev), 3, out=out)
+    torch.cuda.synchronize()
+    assert ((out.float().cpu() - ref).norm() / ref.norm()).item() < tol
+    untouched = ~(flat | ((doc_ids == -2) & (mask == 1)))
+    assert out.cpu()[untouched].abs().sum().item() == 0
+
+
+def test_append_segment_and_noncausal_attention_bf16():
+    """Multi-token decode segment on the tensor-core kernel: the segment's unmasked tokens are appended in place and
+    every valid token attends to the whole grown context (oracle.decode_segment_attention)."""
+    from msa_b200 import ops
+    from oracle import msa_oracle as O
+    dev = torch.device("cuda:0")
+    b, hq, hkv, d, l0, q_len, cap = 3, 8, 2, 128, 150, 40, 230
+    g = torch.Generator().manual_seed(41)
+    lens = torch.tensor([150, 97, 3])
+    ck, cv = [torch.randn(b, hkv, l0, d, generator=g).to(torch.bfloat16) for _ in range(2)]
+    key_mask = torch.arange(l0).unsqueeze(0) >= (l0 - lens.unsqueeze(1))
+    q = torch.randn(b, hq, q_len, d, generator=g).to(torch.bfloat16)
+    nk, nv = [torch.randn(b, hkv, q_len, d, generator=g).to(torch.bfloat16) for _ in range(2)]
+    new_mask = torch.rand(b, q_len, generator=g) < 0.7
+    new_mask[2] = False
+    new_mask[2, -1] = True
+    ref, _, _, _ = O.decode_segment_attention(q.float(), ck.float(), cv.float(), key_mask, nk.float(), nv.float(), new_mask)
+    k_store = torch.zeros(b, hkv, cap, d, dtype=torch.bfloat16, device=dev)
+    v_store = torch.zeros_like(k_store)
+    k_store[:, :, :l0], v_store[:, :, :l0] = ck.to(dev), cv.to(dev)
+    kv_start, kv_len = (l0 - lens).to(torch.int32).to(dev), lens.to(torch.int32).to(dev)
+    q_tok, num_q, err = ops.append_segment(nk.to(dev), nv.to(dev), new_mask.to(dev), k_store, v_store, kv_start, kv_len)
+    out = ops.sparse_prefill_attn(q.to(dev), k_store, v_store, kv_start, kv_len, q_tok, num_q, causal=False)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0 and num_q.cpu().tolist() == new_mask.sum(1).tolist()
+    assert kv_len.cpu().tolist() == (lens + new_mask.sum(1)).tolist()
+    for i in range(b):      # appended in order, right behind the old entries
+        idx = new_mask[i].nonzero().flatten()
+        assert torch.equal(k_store[i, :, l0:l0 + len(idx)].cpu(), nk[i][:, idx])
+        assert q_tok[i, :len(idx)].cpu().tolist() == idx.tolist()
+    got = out.float().cpu()
+    assert ((got[new_mask] - ref[new_mask]).norm() / ref[new_mask].norm()).item() < 1e-2
+    assert got[~new_mask].abs().sum().item() == 0
+    # no room: flagged, sequence untouched
+    small = torch.zeros(b, hkv, l0 + 5, d, dtype=torch.bfloat16, device=dev)
+    kv_len2 = lens.to(torch.int32).to(dev)
+    _, num_q2, err2 = ops.append_segment(nk.to(dev), nv.to(dev), new_mask.to(dev), small, small.clone(), kv_start, kv_len2)
+    assert int(err2.item()) == 1 and kv_len2.cpu().tolist()[0] == 150 and num_q2.cpu().tolist()[0] == 0
 
 
 # ----------------------------------------------------------------------------------------------

@@ -43,14 +43,14 @@ def test_prefill_stage2_golden(golden):
     assert svc.get_max_local_pool_doc_id() == len(chunks)
 
 
-def test_unsupported_reduce_modes_are_rejected():
+def test_unknown_reduce_modes_are_rejected():
+    """Every reduce mode of the reference is implemented (tests/test_gpu_reduce_modes.py); a name that is none of
+    them is refused when the bank is created, not when the first query arrives."""
     from msa_b200 import _cabi as A
-    with pytest.raises(A.MsaError, match="not supported"):
-        _service([1], [5], torch.zeros(1, 8, 128), torch.zeros(1, 8, 128), torch.zeros(1, 8, 128), 1, torch.float32,
-                 head_reduce_method="max")
-    with pytest.raises(A.MsaError, match="not supported"):
-        _service([1], [5], torch.zeros(1, 8, 128), torch.zeros(1, 8, 128), torch.zeros(1, 8, 128), 1, torch.float32,
-                 chunk_reduce_method="mean")
+    z = torch.zeros(1, 8, 128)
+    for kw in ({"head_reduce_method": "median"}, {"chunk_reduce_method": "sum"}, {"query_reduce_method": "first"}):
+        with pytest.raises(A.MsaError, match="unknown"):
+            _service([1], [5], z, z, z, 1, torch.float32, **kw)
 
 
 def test_doc_query_golden_two_shards_one_gpu(golden):

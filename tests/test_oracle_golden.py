@@ -172,3 +172,24 @@ def test_decode_matches_reference_layer(golden):
         out = O.decode_attention(q, ck, cv, lens, k, v)
         assert torch.allclose(out, T(g[f"out{step}"]), atol=2e-6, rtol=1e-5)
         ck, cv, lens = torch.cat([ck, k], 2), torch.cat([cv, v], 2), lens + 1
+
+
+def test_qa_mode_decode_segments_match_reference_layer(golden):
+    """oracle.decode_segment_attention against the reference layer's decode branch in qa_mode: two multi-token
+    segments and a one-token step, with left padding, a masked step and a finished sequence."""
+    g = golden("layer_decode_qa")
+    hq, hkv, d = int(g["hq"]), int(g["hkv"]), int(g["d"])
+    weights = {k[3:]: T(v) for k, v in g.items() if k.startswith("w__")}
+    ck, cv, lens = T(g["cache_k"]), T(g["cache_v"]), T(g["kv_lengths"])
+    mask = torch.arange(ck.shape[2]).unsqueeze(0) >= (ck.shape[2] - lens.unsqueeze(1))
+    for step in range(int(g["n_steps"])):
+        hidden, am = T(g[f"s{step}_hidden"]), T(g[f"s{step}_attention_mask"])
+        cos, sin = O.rope_cos_sin(T(g[f"s{step}_position_ids"]), d, float(g["rope_theta"]))
+        q, k, v = O.qwen3_attention_states(hidden, weights, cos, sin, hq, hkv, d)
+        out, ck, cv, mask = O.decode_segment_attention(q, ck, cv, mask, k, v, am == 1)
+        out = torch.nn.functional.linear(out, weights["o_proj.weight"])
+        ref = T(g[f"s{step}_out"])
+        valid = am == 1
+        assert torch.allclose(out[valid], ref[valid], atol=2e-6, rtol=1e-5)
+    assert torch.equal(mask, T(g["final_mask"]))
+    assert torch.allclose(ck, T(g["final_cache_k"]), atol=1e-6)
