@@ -60,6 +60,8 @@ def parse():
     ap.add_argument("--no-extras", action="store_true",
                     help="routing workload: skip the parity / kernels / generate / incumbent legs (profiling runs)")
     ap.add_argument("--new-tokens", type=int, default=256, help="generate workload: tokens to decode")
+    ap.add_argument("--short", action="store_true", help="secondary workloads: take --steps / --warmup as given (profiling runs)")
+    ap.add_argument("--decode-batch", type=int, default=32, help="route-decode workload: sequences per step (<= 128)")
     ap.add_argument("--workload", default="routing",
                     choices=["routing", "pooling", "decode", "fetch", "route-decode", "prefill", "stage1", "generate"],
                     help="routing = the headline (default); the others time one secondary kernel each")
@@ -490,21 +492,50 @@ def leg_route_decode(torch, ops, dev, pk, steps=500, warmup=3, b=32):
                 ev.append((e0, e1))
             ops.topk_select(keys, TOP_K, workspace=topk_ws)
 
-    def step_fused(timed=False):      # fold, fused scoring + per-CTA selection, final selection
-        for rk in banks:
+    blocked = [ops.block_router_keys(rk) for rk in banks]
+
+    side = torch.cuda.Stream(dev)
+
+    def step_blocked(timed=False):    # the table path over tile-blocked keys (16 contiguous KiB per TMA box)
+        main = torch.cuda.current_stream(dev)
+        for rk in blocked:
+            fork, join = torch.cuda.Event(), torch.cuda.Event()      # the table reset runs beside the fold kernel
+            fork.record(main)
+            side.wait_event(fork)
+            with torch.cuda.stream(side):
+                ops.route_table_reset(keys, docs_local, torch.finfo(torch.bfloat16).min)
+                join.record(side)
+            qf, bias, s_pad = ops.fold_queries(q, mask, HQ // HKV)
+            main.wait_event(join)
+            if timed:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            ops.route_scores(qf, bias, b, s_pad, rk, chunk_doc, docs_local, 1.0 / HQ, keys=keys, status=status, flags=2,
+                             blocked=True)
+            if timed:
+                e1.record()
+                ev.append((e0, e1))
+            ops.topk_select(keys, TOP_K, workspace=topk_ws)
+
+    def step_fused(timed=False, key_sets=None):      # fold, fused scoring + per-CTA selection, final selection
+        for rk in (banks if key_sets is None else key_sets):
             qf, bias, s_pad = ops.fold_queries(q, mask, HQ // HKV)
             if timed:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
             ops.route_score_select(qf, bias, b, rk, chunk_doc, docs_local, 1.0 / HQ, TOP_K, status=status, workspace=sel_ws,
-                                   out=outs)
+                                   out=outs, blocked=key_sets is not None)
             if timed:
                 e1.record()
                 ev.append((e0, e1))
 
     alg = c * HKV * D * 2 + b * HKV * D * 2
     res = {}
-    for name, step in (("table", step_table), ("fused", step_fused)):
+    fused_ok = ops.route_score_select_supported(banks[0], b, 1, TOP_K)
+    variants = [("table", step_table), ("blocked", step_blocked)]
+    if fused_ok:
+        variants += [("fused", step_fused), ("fused_blocked", lambda timed=False: step_fused(timed, blocked))]
+    for name, step in variants:
         ev.clear()
         _time_ms(torch, lambda: step(True), 5, warmup)        # eagerly, with events around the scoring call
         inner_ms = statistics.mean([a.elapsed_time(b_) for a, b_ in ev[-5 * n_layers:]])
@@ -515,17 +546,31 @@ def leg_route_decode(torch, ops, dev, pk, steps=500, warmup=3, b=32):
         del graph
         res[name] = (ms, inner_ms)
     assert status.cpu().tolist()[0] == 0 and status.cpu().tolist()[2] == 0
-    ms, fused_inner = res["fused"]
+    frac = lambda t_ms: alg / (t_ms / 1e3) / 1e9 / pk["hbm_gbs"]
+    table_leg = lambda name, what: {"layer_step_ms": res[name][0], "layer_step_frac": frac(res[name][0]),
+                                    "route_tc_kernel_ms": res[name][1], "route_tc_kernel_frac": frac(res[name][1]), "what": what}
+    fused_leg = lambda name, what: {"layer_step_ms": res[name][0], "layer_step_frac": frac(res[name][0]),
+                                    "call_ms": res[name][1], "call_frac": frac(res[name][1]), "what": what}
+    legs = {"table_blocked_keys": table_leg("blocked", "fold (table reset beside it on a second stream), route_tc_kernel over "
+                                            "tile-blocked keys, two-level top-k: five launches"),
+            "table_row_major_keys": table_leg("table", "fold, table reset, route_tc_kernel over row-major keys (128 pieces "
+                                              "2 KiB apart per TMA box), two-level top-k: five launches")}
+    if fused_ok:
+        legs["fused_blocked_keys"] = fused_leg("fused_blocked", "fold, route_dec_kernel over tile-blocked keys (scoring + per-CTA "
+                                               "selection in registers), final selection: three launches, no score table")
+        legs["fused_row_major_keys"] = fused_leg("fused", "the same three launches over row-major keys")
+    primary = "fused_blocked" if fused_ok and res["fused_blocked"][0] <= res["blocked"][0] else "blocked"
+    ms, inner = res[primary]
     gbs = alg / (ms / 1e3) / 1e9
-    return {"kernel": "route_dec_kernel", "ms": ms, "algorithmic_bytes": alg, "achieved_gbs": gbs, "frac": gbs / pk["hbm_gbs"],
-            "bound": "hbm", "launches": 3 * n_layers * steps,
-            "layer_step": "fold, fused scoring + per-CTA selection, final selection (one CUDA graph)",
-            "route_kernel_ms": fused_inner, "route_kernel_frac": alg / (fused_inner / 1e3) / 1e9 / pk["hbm_gbs"],
-            "route_kernel_note": "route_dec_kernel + the final selection launch, eager, CUDA events around the call",
-            "table_path": {"layer_step_ms": res["table"][0], "layer_step_frac": alg / (res["table"][0] / 1e3) / 1e9 / pk["hbm_gbs"],
-                           "route_tc_kernel_ms": res["table"][1],
-                           "route_tc_kernel_frac": alg / (res["table"][1] / 1e3) / 1e9 / pk["hbm_gbs"],
-                           "what": "fold, table reset, route_tc_kernel, two-level top-k (5 launches)"},
+    return {"kernel": "route_dec_kernel" if primary == "fused_blocked" else "route_tc_kernel", "ms": ms, "algorithmic_bytes": alg,
+            "achieved_gbs": gbs, "frac": gbs / pk["hbm_gbs"], "bound": "hbm",
+            "launches": (3 if primary == "fused_blocked" else 5) * n_layers * steps,
+            "layer_step": legs["fused_blocked_keys" if primary == "fused_blocked" else "table_blocked_keys"]["what"] +
+                          " (one CUDA graph; this is the path the service takes at this shape)",
+            "route_kernel_ms": inner, "route_kernel_frac": frac(inner),
+            "route_kernel_note": "the scoring call alone, eager, CUDA events around it (for the fused path it includes the "
+                                 "final selection launch)",
+            "variants": legs,
             "workload": f"benchmark config 5 per-step routing: {b} sequences x 1 token against {c} chunks (400 MB shard, one "
                         f"of 8), {n_layers} distinct layers rotate"}
 
@@ -553,8 +598,8 @@ def run_secondary(args):
     g = torch.Generator(device=dev)
     g.manual_seed(2000)
     sampler = ClockSampler(0)
-    steps, warmup = max(args.steps, 50), max(args.warmup, 3)   # short kernels: time many launches
-    args.steps, args.warmup = steps, warmup
+    steps, warmup = (args.steps, args.warmup) if args.short else (max(args.steps, 50), max(args.warmup, 3))
+    args.steps, args.warmup = steps, warmup                      # short kernels: time many launches
 
     if args.workload == "pooling":
         sampler.start()
@@ -568,7 +613,7 @@ def run_secondary(args):
 
     elif args.workload == "route-decode":
         sampler.start()
-        leg = leg_route_decode(torch, ops, dev, pk, 10 * steps, warmup, b=32 if args.queries == N_QUERIES else args.queries)
+        leg = leg_route_decode(torch, ops, dev, pk, steps if args.short else 10 * steps, warmup, b=args.decode_batch)
         _secondary_line(args, "decode-time routing layer-steps/s (one of 8 shards)", "layer-steps/s", 1e3 / leg["ms"], leg,
                         sampler.stop())
 
@@ -1021,7 +1066,7 @@ def run_ours(args):
                                  "achieved_gbs": leg["achieved_gbs"], "frac": leg["frac"], "peak_gbs": pk["hbm_gbs"],
                                  "workload": leg["workload"],
                                  **{k_: leg[k_] for k_ in ("route_kernel_ms", "route_kernel_frac", "route_kernel_note", "layer_step",
-                                                           "table_path", "tokens_per_s") if k_ in leg}}
+                                                           "row_major_keys", "fused_score_select", "tokens_per_s") if k_ in leg}}
             except Exception as e:
                 kernels[name] = {"error": f"{type(e).__name__}: {e}"}
         if world > 1:
@@ -1034,6 +1079,7 @@ def run_ours(args):
             dist.barrier()
         if fetch_note is None and layers == N_LAYERS:
             try:
+                svc.block_router_keys(free_rows=True)     # decode steps route one token per sequence: bandwidth bound
                 generate = generate_measure(torch, dist, svc, world, rank, local_rank, dev, n_docs, docs_local, 64)
             except Exception as e:
                 generate = {"error": f"{type(e).__name__}: {e}"}
@@ -1216,6 +1262,7 @@ def run_generate(args):
                                                                     N_LAYERS, "gen")
     if fetch_note is not None:
         raise SystemExit(fetch_note)
+    svc.block_router_keys(free_rows=True)
     g = generate_measure(torch, dist, svc, world, rank, local_rank, dev, args.docs, docs_local, args.new_tokens, full=True)
     if world > 1:
         svc.close_host_banks()

@@ -6,16 +6,20 @@
 // kernel fills is pure overhead: a reset launch, 4-byte scattered stores, and a selection kernel that reads it
 // back.  Here the table never leaves the SM:
 //
-//   * every CTA owns ONE contiguous range of chunks whose ends are moved to document boundaries, so a document is
-//     scored by exactly one CTA; ranges are equal (no partial last wave), tiles step through a range 128 chunks at
-//     a time from wherever the range starts (TMA has no alignment rule for the row coordinate), and the last tile
-//     of a range is fetched in 32-row boxes so that rows of the neighbour's range are not read twice;
-//   * the epilogue reduces chunk scores to document scores into a SHARED-MEMORY table [document][sequence] of
-//     order-preserving keys (atomicMax on shared memory; documents are addressed relative to the first document of
-//     the current segment);
-//   * when the table is full, and at the end of the range, the epilogue warps select every sequence's best k among
-//     (table column + the sequence's running list) with the warp routines of topk_warp.cuh; a document that is
-//     still open at a flush (its chunks continue in the next tile) is carried over, not selected;
+//   * the keys are cut into fixed tiles of 128 chunks (the rows of one UMMA); every CTA takes an equal share of
+//     whole tiles and owns the documents that START in its share: both ends of the share are moved forward to the
+//     next document start, so a document is scored by exactly one CTA.  The first tile's rows before that start
+//     are masked; the tile after the share is read, in 32-row boxes, only as far as the CTA's last document
+//     reaches.  Tiles being whole and aligned, the same loop reads row-major keys (2-D tensor map) or the
+//     tile-blocked copy (4-D map; every box is one contiguous 16 KiB run, which HBM serves measurably faster);
+//   * the epilogue reduces a tile's chunk scores to document scores into a SHARED-MEMORY table [document][sequence]
+//     of order-preserving keys (atomicMax on shared memory; rows are documents relative to the first document of
+//     the tile);
+//   * after every tile, epilogue thread s (one per sequence) walks the tile's finished documents in its own table
+//     column and feeds them to a sorted list of its best k that lives in REGISTERS (a branch-free chain of k
+//     compare-and-swaps per document, skipped when no lane of the warp has a candidate above its k-th best); a
+//     document whose chunks continue in the next tile is carried over in row 0, not consumed.  This runs while
+//     the next tile streams in, so nothing but the last tile's walk is left after the stream ends;
 //   * the CTA writes k candidates per sequence; one small launch (the second level of the stand-alone selection)
 //     reduces the n_ctas * k candidates of a sequence to the result.
 //
@@ -24,31 +28,35 @@
 // equals the selection over the full table, ties included (column 0, the reference's dummy document with
 // finfo.min, is seeded by CTA 0).
 //
-// Roles as in route_tc.cu: warps 0-3 epilogue (TMEM lane quarter = warp), warp 4 TMA producer, warp 5 MMA issuer
-// and TMEM owner.  Every mbarrier wait is bounded; a wait that runs out raises status[0] and the CTA drains and
+// Roles: warps 0-7 epilogue (TMEM lane quarter = warp % 4; the two warps of a quarter split a tile's columns),
+// warp 8 TMA producer, warp 9 MMA issuer and TMEM owner.  Every mbarrier wait is bounded; a wait that runs out raises status[0] and the CTA drains and
 // returns (its candidates are then incomplete, which status reports).
 #include <cuda.h>
+
+#include <cstdlib>
 
 #include "common.cuh"
 #include "route.cuh"
 #include "tc_common.cuh"
-#include "topk_warp.cuh"
 
 namespace msa {
 
 constexpr int kDecBM = 128;         // chunks per tile (UMMA M)
 constexpr int kDecBK = 64;          // bf16 elements per K block (one 128-byte swizzle row)
 constexpr int kDecUmmaK = 16;
-constexpr int kDecThreads = 192;
-constexpr int kDecEpiThreads = 128;
+constexpr int kDecEpiWarps = 8;     // two per TMEM lane quarter: they split a tile's columns
+constexpr int kDecEpiThreads = kDecEpiWarps * 32;
+constexpr int kDecThreads = kDecEpiThreads + 64;
+constexpr int kDecProducerWarp = kDecEpiWarps, kDecMmaWarp = kDecEpiWarps + 1;
 constexpr int kDecMaxBN = 128;      // sequences (query rows) per launch
 constexpr int kDecMaxKeep = 32;     // candidates per CTA and sequence
 constexpr int kDecTmemCols = 256;   // two accumulators of up to 128 columns
-constexpr int kDecTailBox = 32;     // rows per TMA box of a range's last tile
-constexpr int kDecMaxStages = 8;
+constexpr int kDecTailBox = 32;     // rows per TMA box of a partly needed tile
+constexpr int kDecMaxStages = 12;
+constexpr int kDecRows = kDecBM + 2;  // table rows: a tile's documents (at most one per chunk) and a carried one
 
 struct RouteDecParams {
-  int n_seq, bn, bn_pad, n_chunks, n_docs, k_blocks, stages, cap, keep, per_cta;
+  int n_seq, bn, bn_pad, n_chunks, n_docs, k_blocks, stages, cap, keep, tiles_q, tiles_rem, blocked;
   uint32_t min_key;
   float alpha;
   const float* row_bias;
@@ -63,17 +71,42 @@ struct DecEpiScratch {
   DecSeg seg[32];
 };
 
-__device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(kDecEpiThreads) : "memory"); }
 
-// First chunk at or after p that starts a document (p itself when it does; n_chunks at the end).
-__device__ __forceinline__ int snap_to_document(const int32_t* chunk_doc, int p, int n_chunks) {
+// First chunk at or after p that starts a document (p itself when it does; n_chunks at the end).  One warp: the
+// lanes look at 32 chunks at a time, so a boundary costs one round of global loads, not one per chunk.
+__device__ __forceinline__ int snap_to_document(const int32_t* chunk_doc, int p, int n_chunks, int lane) {
   if (p <= 0) return 0;
   if (p >= n_chunks) return n_chunks;
   const int d = chunk_doc[p - 1];
-  while (p < n_chunks && chunk_doc[p] == d) ++p;
-  return p;
+  for (;;) {
+    const int c = p + lane;
+    const bool other = c >= n_chunks || chunk_doc[c] != d;      // the end of the shard ends the document too
+    const uint32_t bal = __ballot_sync(0xffffffffu, other);
+    if (bal) return min(p + __ffs(bal) - 1, n_chunks);
+    p += 32;
+  }
 }
 
+// One step of a sorted insertion without branches: (key, doc) falls through the descending list, swapping
+// with every entry it beats.  Strict comparison: of two equal scores the earlier document (documents arrive in
+// ascending order) stays ahead, which is the tie order of the table path.
+template <int KMAX>
+__device__ __forceinline__ void list_insert(uint32_t (&lk)[KMAX], int (&ld)[KMAX], uint32_t key, int doc) {
+#pragma unroll
+  for (int i = 0; i < KMAX; ++i) {
+    const bool up = key > lk[i];
+    const uint32_t tk = lk[i];
+    const int td = ld[i];
+    lk[i] = up ? key : tk;
+    ld[i] = up ? doc : td;
+    key = up ? tk : key;
+    doc = up ? td : doc;
+  }
+}
+
+// tmap_k / tmap_k_tail: 128-row and 32-row boxes over the keys, 2-D (row-major keys) or 4-D (tile-blocked keys).
+template <int KMAX>
 __global__ void __launch_bounds__(kDecThreads, 1)
 route_dec_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_k_tail,
                  const __grid_constant__ CUtensorMap tmap_q, const RouteDecParams p) {
@@ -82,29 +115,31 @@ route_dec_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort, s_lo, s_hi;
   __shared__ float s_bias[kDecMaxBN];
-  __shared__ DecEpiScratch s_epi[kDecEpiThreads / 32];
-  __shared__ unsigned long long s_scr32[kDecEpiThreads / 32][32];
+  __shared__ DecEpiScratch s_epi[kDecEpiWarps];
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
   const uint32_t a_bytes = kDecBM * kDecBK * 2, b_bytes = (uint32_t)p.bn * kDecBK * 2, stage_bytes = a_bytes + b_bytes;
   uint32_t* tbl = reinterpret_cast<uint32_t*>(tiles + (size_t)p.stages * stage_bytes);            // [cap][bn_pad]
-  unsigned long long* run = reinterpret_cast<unsigned long long*>(tbl + (size_t)p.cap * p.bn_pad + (((size_t)p.cap * p.bn_pad) & 1));
-  unsigned long long* scratch = run + (size_t)p.bn * p.keep;                                       // [4][cap + keep]
   volatile int* abort_flag = &s_abort;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&s_acc_full[b], 1); mbar_init(&s_acc_empty[b], kDecEpiThreads / 32); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&s_acc_full[b], 1); mbar_init(&s_acc_empty[b], kDecEpiWarps); }
     mbar_init(&s_drain, 1);
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    // this CTA's range: equal shares of the chunk axis, both ends moved forward to the next document start
-    const long long a = (long long)blockIdx.x * p.per_cta, b = a + p.per_cta;
-    s_lo = snap_to_document(p.chunk_doc, (int)(a < p.n_chunks ? a : p.n_chunks), p.n_chunks);
-    s_hi = snap_to_document(p.chunk_doc, (int)(b < p.n_chunks ? b : p.n_chunks), p.n_chunks);
   }
-  if (warp == 5) {
+  if (warp == 0 || warp == kDecProducerWarp) {
+    // This CTA owns the documents that START in its share of the (whole) tiles: both ends of the share are moved
+    // forward to the next document start, so its last document may reach into the next CTA's first tile, whose
+    // leading rows that CTA skips.  (The producer warp finds the start, warp 0 the end, at the same time.)
+    const int c = (int)blockIdx.x + (warp == 0 ? 1 : 0);     // CTA c's share starts at tile c*q + min(c, rem)
+    const long long a = ((long long)c * p.tiles_q + min(c, p.tiles_rem)) * kDecBM;
+    const int v = snap_to_document(p.chunk_doc, (int)(a < p.n_chunks ? a : p.n_chunks), p.n_chunks, lane);
+    if (lane == 0) *(warp == 0 ? &s_hi : &s_lo) = v;
+  }
+  if (warp == kDecMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
                  "r"(kDecTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -114,28 +149,33 @@ route_dec_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = s_tmem_base;
   const int lo = s_lo, hi = s_hi;
-  const int n_tiles = (hi - lo + kDecBM - 1) / kDecBM;
+  const int first_tile = lo / kDecBM;                                     // tiles are the fixed 128-chunk blocks
+  const int n_tiles = lo < hi ? (hi + kDecBM - 1) / kDecBM - first_tile : 0;
 
-  if (warp == 4) {
+  if (warp == kDecProducerWarp) {
     // ------------------------------- TMA producer -------------------------------------
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0, armed = 0, armed_parity = 0;
       bool ok = true;
       for (int t = 0; t < n_tiles && ok; ++t) {
-        const int row0 = lo + t * kDecBM, rows = min(kDecBM, hi - row0);
-        const int tail_boxes = rows < kDecBM ? (rows + kDecTailBox - 1) / kDecTailBox : 0;
+        const int tile = first_tile + t, row0 = tile * kDecBM, rows = min(kDecBM, hi - row0);
+        // a tile of which only the first rows are wanted (the end of the CTA's last document) comes in 32-row boxes
+        const int tail_boxes = rows <= kDecBM - kDecTailBox ? (rows + kDecTailBox - 1) / kDecTailBox : 0;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!(ok = mbar_wait(&s_empty[stage], phase ^ 1u, abort_flag, p.status, 1))) break;
           unsigned char* sa = tiles + (size_t)stage * stage_bytes;
           if (tail_boxes == 0) {
             mbar_expect_tx(&s_full[stage], stage_bytes);
-            tma_load_2d(sa, &tmap_k, kb * kDecBK, row0, &s_full[stage]);
+            if (p.blocked) tma_load_4d(sa, &tmap_k, 0, 0, kb, tile, &s_full[stage]);
+            else tma_load_2d(sa, &tmap_k, kb * kDecBK, row0, &s_full[stage]);
           } else {   // 32-row boxes land where the rows of a 128-row box would (8-row swizzle groups of 1 KiB)
             mbar_expect_tx(&s_full[stage], (uint32_t)tail_boxes * kDecTailBox * kDecBK * 2 + b_bytes);
-            for (int j = 0; j < tail_boxes; ++j)
-              tma_load_2d(sa + (size_t)j * kDecTailBox * kDecBK * 2, &tmap_k_tail, kb * kDecBK, row0 + j * kDecTailBox,
-                          &s_full[stage]);
+            for (int j = 0; j < tail_boxes; ++j) {
+              unsigned char* dst = sa + (size_t)j * kDecTailBox * kDecBK * 2;
+              if (p.blocked) tma_load_4d(dst, &tmap_k_tail, 0, j * kDecTailBox, kb, tile, &s_full[stage]);
+              else tma_load_2d(dst, &tmap_k_tail, kb * kDecBK, row0 + j * kDecTailBox, &s_full[stage]);
+            }
           }
           tma_load_2d(sa + a_bytes, &tmap_q, kb * kDecBK, 0, &s_full[stage]);
           armed |= 1u << stage;
@@ -151,7 +191,7 @@ route_dec_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
           }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kDecMmaWarp) {
     // ------------------------------- MMA issuer ----------------------------------------
     if (lane == 0) {
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.bn >> 3) << 17) |
@@ -183,59 +223,35 @@ route_dec_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
       while (!mbar_try_wait(&s_drain, 0) && global_ns() - t0 < kWaitLimitNs) {}
     }
   } else {
-    // ------------------------------- epilogue + selection (warps 0-3) ------------------
-    const int tid = threadIdx.x;   // 0..127
+    // ------------------------------- epilogue + selection (warps 0-7) ------------------
+    const int tid = threadIdx.x;                       // 0..255; thread tid < bn also owns sequence / table column tid
+    const int quarter = warp & 3, part = warp >> 2;    // TMEM lane quarter; share of the tile's columns
     DecEpiScratch& scr = s_epi[warp];
-    unsigned long long* my_scratch = scratch + (size_t)warp * (p.cap + p.keep);
     for (int i = tid; i < p.cap * p.bn_pad; i += kDecEpiThreads) tbl[i] = p.min_key;
-    for (int i = tid; i < p.bn * p.keep; i += kDecEpiThreads) run[i] = 0ull;
     if (tid < p.bn) s_bias[tid] = tid < p.n_seq ? p.row_bias[tid] : -INFINITY;
+    // this thread's sequence: its best `keep` documents so far, sorted, in registers (key 0 = empty slot)
+    uint32_t lk[KMAX];
+    int ld[KMAX];
+#pragma unroll
+    for (int i = 0; i < KMAX; ++i) { lk[i] = 0u; ld[i] = 0; }
+    const bool owns_seq = tid < p.n_seq;
+    if (blockIdx.x == 0 && owns_seq) lk[0] = p.min_key;   // column 0: the dummy document, scored finfo.min like every untouched column
     epi_barrier();
-    if (blockIdx.x == 0 && tid < p.n_seq)   // column 0: the dummy document, scored finfo.min like every untouched column
-      run[(size_t)tid * p.keep] = ((unsigned long long)p.min_key << 32) | 0xffffffffull;
-    int seg_base = lo < hi ? p.chunk_doc[lo] : 0;   // document id of table row 0
-    int rows_used = 0;
-
-    // Select every sequence's best `keep` among the table rows in use (except an open document) and its running
-    // list; then clear the table, keeping the open document's partial maxima as row 0.
-    auto flush = [&](int open_doc) {
-      epi_barrier();                                   // every warp's table updates are in
-      const int open_row = open_doc >= 0 ? open_doc - seg_base : -1;
-      for (int seq = warp; seq < p.n_seq; seq += kDecEpiThreads / 32) {
-        for (int r = lane; r < rows_used; r += 32)
-          my_scratch[r] = r == open_row ? 0ull
-                                        : (((unsigned long long)tbl[(size_t)r * p.bn_pad + seq] << 32) |
-                                           (unsigned long long)(0xffffffffu - (uint32_t)(seg_base + r)));
-        for (int j = lane; j < p.keep; j += 32) my_scratch[rows_used + j] = run[(size_t)seq * p.keep + j];
-        __syncwarp();
-        warp_filter_topk(my_scratch, rows_used + p.keep, p.keep, run + (size_t)seq * p.keep, s_scr32[warp]);
-        __syncwarp();
-      }
-      epi_barrier();                                   // selections have read the table
-      if (tid < p.bn) {
-        const uint32_t keep_val = open_row >= 0 && open_row < rows_used ? tbl[(size_t)open_row * p.bn_pad + tid] : p.min_key;
-        for (int r = 0; r < rows_used; ++r) tbl[(size_t)r * p.bn_pad + tid] = p.min_key;
-        if (open_row >= 0) tbl[tid] = keep_val;
-      }
-      epi_barrier();
-    };
+    int seg_base = lo < hi ? p.chunk_doc[lo] : 0;          // document id of table row 0
+    bool carried = false;                                  // row 0 holds the partial maxima of a document that continues
 
     bool ok = true;
     for (int t = 0; t < n_tiles && ok; ++t) {
-      const int row0 = lo + t * kDecBM;
-      const int chunk = row0 + tid;
+      const int row0 = (first_tile + t) * kDecBM;
+      const int chunk = row0 + quarter * 32 + lane;
+      const bool mine = chunk >= lo && chunk < hi;        // rows before lo belong to the previous CTA's last document
       const int last_chunk = min(row0 + kDecBM, hi) - 1;
-      const int first_doc = p.chunk_doc[row0], last_doc = p.chunk_doc[last_chunk];
-      if (last_doc - seg_base >= p.cap && rows_used > 0) {      // the tile's documents do not fit: flush first
-        const int open_doc = (row0 > lo && p.chunk_doc[row0 - 1] == first_doc) ? first_doc : -1;
-        flush(open_doc);
-        seg_base = first_doc;
-        rows_used = open_doc >= 0 ? 1 : 0;
-      }
+      const int last_doc = p.chunk_doc[last_chunk];
+      const int next_doc = last_chunk + 1 < hi ? p.chunk_doc[last_chunk + 1] : -1;   // first document of the next tile
       // runs of lanes that hold chunks of one document
-      int doc = chunk < hi ? p.chunk_doc[chunk] : -1 - lane;
-      if (chunk < hi && (doc < 1 || doc > p.n_docs || (unsigned)(doc - seg_base) >= (unsigned)p.cap)) {
-        atomicAdd(p.status + 2, 1);                     // an id outside the table: counted, never used as a row
+      int doc = mine ? p.chunk_doc[chunk] : -1 - lane;
+      if (mine && (doc < 1 || doc > p.n_docs || (unsigned)(doc - seg_base) >= (unsigned)p.cap)) {
+        if (part == 0) atomicAdd(p.status + 2, 1);      // an id outside the table: counted, never used as a row
         doc = -1 - lane;
       }
       const int doc_up = __shfl_up_sync(0xffffffffu, doc, 1);
@@ -253,9 +269,9 @@ route_dec_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)buf * kDecMaxBN;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * kDecMaxBN;
       const int n_items = n_seg * 16;
-      for (int c0 = 0; c0 < p.bn; c0 += 16) {
+      for (int c0 = part * 16; c0 < p.bn; c0 += 16 * (kDecEpiWarps / 4)) {
         uint32_t r[16];
         tmem_ld16(taddr + c0, r);
         tmem_ld_wait();
@@ -277,38 +293,62 @@ route_dec_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_acc_empty[buf]);
-      rows_used = max(rows_used, min(min(last_doc, p.n_docs) - seg_base + 1, p.cap));   // rows never stand for ids > n_docs
+
+      // ---- walk the tile's finished documents: thread = sequence, rows = documents
+      epi_barrier();                                     // every warp's table updates of this tile are in
+      const int n_rows = max(carried ? 1 : 0, min(min(last_doc, p.n_docs) - seg_base + 1, p.cap));
+      const bool open = n_rows >= 1 && next_doc == last_doc && last_doc - seg_base == n_rows - 1;   // the last row's document continues
+      const int n_done = open ? n_rows - 1 : n_rows;
+      const uint32_t walkers = __ballot_sync(0xffffffffu, tid < p.bn);   // lanes of this warp that own a table column
+      if (tid < p.bn) {
+        for (int r = 0; r < n_done; ++r) {
+          const uint32_t key = tbl[(size_t)r * p.bn_pad + tid];
+          tbl[(size_t)r * p.bn_pad + tid] = p.min_key;
+          // the whole warp takes the insertion chain or skips it together
+          if (__any_sync(walkers, owns_seq && key > lk[KMAX - 1])) {
+            if (owns_seq) list_insert<KMAX>(lk, ld, key, seg_base + r);
+          }
+        }
+        uint32_t keep_val = p.min_key;
+        if (open) {                                      // carry the open document's partial maxima to row 0
+          keep_val = tbl[(size_t)n_done * p.bn_pad + tid];
+          tbl[(size_t)n_done * p.bn_pad + tid] = p.min_key;
+        }
+        tbl[tid] = keep_val;
+      }
+      seg_base = open ? last_doc : (next_doc > 0 ? next_doc : seg_base);
+      carried = open;
+      epi_barrier();                                     // the table is clean before the next tile is reduced into it
     }
-    if (ok) {
-      flush(-1);
+    if (ok && owns_seq) {
       const long long n_in = (long long)gridDim.x * p.keep;
-      for (int i = tid; i < p.n_seq * p.keep; i += kDecEpiThreads)
-        p.cand[(long long)(i / p.keep) * n_in + (long long)blockIdx.x * p.keep + (i % p.keep)] = run[i];
+      unsigned long long* dst = p.cand + (long long)tid * n_in + (long long)blockIdx.x * p.keep;
+#pragma unroll
+      for (int i = 0; i < KMAX; ++i)
+        if (i < p.keep)
+          dst[i] = lk[i] ? (((unsigned long long)lk[i] << 32) | (unsigned long long)(0xffffffffu - (uint32_t)ld[i])) : 0ull;
     }
   }
 
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == 5)
+  if (warp == kDecMmaWarp)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kDecTmemCols) : "memory");
 }
 
-// Shared-memory plan for bn query rows and `keep` candidates; returns false when it does not fit.
+// Shared-memory plan for bn query rows: as many operand stages as fit beside the document table.
 static bool route_dec_plan(int bn, int keep, RouteDecParams* p, size_t* smem) {
   const size_t stage_bytes = (size_t)kDecBM * kDecBK * 2 + (size_t)bn * kDecBK * 2;
   const int bn_pad = bn + 1;
-  const size_t budget = 212 * 1024;   // dynamic part; the kernel's static arrays take another 12 KB of the 227 KB
-  // table rows: at least one tile's worth of single-chunk documents plus a carried one; more when there is room
-  for (int stages = kDecMaxStages; stages >= 4; --stages) {
-    for (int cap = 256; cap >= kDecBM + 2; cap -= 2) {
-      const size_t tbl = ((size_t)cap * bn_pad * 4 + 7) & ~(size_t)7;
-      const size_t total = 1024 + stages * stage_bytes + tbl + (size_t)bn * keep * 8 + 4ull * (cap + keep) * 8;
-      if (total <= budget) {
-        p->stages = stages; p->cap = cap; p->bn = bn; p->bn_pad = bn_pad; p->keep = keep;
-        *smem = total;
-        return true;
-      }
+  const size_t budget = 202 * 1024;   // dynamic part; the kernel's static arrays (epilogue scratch) take 23 KB more of the 227 KB
+  const size_t tbl = ((size_t)kDecRows * bn_pad * 4 + 15) & ~(size_t)15;
+  for (int stages = kDecMaxStages; stages >= 3; --stages) {
+    const size_t total = 1024 + stages * stage_bytes + tbl;
+    if (total <= budget) {
+      p->stages = stages; p->cap = kDecRows; p->bn = bn; p->bn_pad = bn_pad; p->keep = keep;
+      *smem = total;
+      return true;
     }
   }
   return false;
@@ -335,7 +375,7 @@ extern "C" int msa_route_score_select(const void* q_folded, const float* row_bia
                                       const int32_t* chunk_doc, float alpha, int32_t n_docs, float min_val, int32_t k,
                                       const int64_t* doc_ids_table, float* out_scores, int64_t* out_local_ids,
                                       int64_t* out_global_ids, void* workspace, int64_t workspace_bytes,
-                                      int32_t* status, void* stream) {
+                                      uint32_t flags, int32_t* status, void* stream) {
   MSA_REQUIRE(q_folded && row_bias && rk && chunk_doc && out_scores && out_local_ids && status && workspace,
               "route_score_select: null pointer");
   MSA_REQUIRE(n_seq >= 1 && n_chunks >= 1 && kdim > 0 && n_docs >= 1 && k >= 1, "route_score_select: bad sizes");
@@ -345,7 +385,8 @@ extern "C" int msa_route_score_select(const void* q_folded, const float* row_bia
               "use msa_route_scores + msa_topk_select for other shapes", kDecMaxBN, kDecMaxKeep, kDecBK);
     return MSA_ERR_UNSUPPORTED;
   }
-  MSA_REQUIRE(aligned16(q_folded) && aligned16(rk) && rk_chunk_stride % 8 == 0 && rk_chunk_stride >= kdim,
+  const bool blocked = (flags & MSA_ROUTE_KEYS_BLOCKED) != 0;
+  MSA_REQUIRE(aligned16(q_folded) && aligned16(rk) && (blocked || (rk_chunk_stride % 8 == 0 && rk_chunk_stride >= kdim)),
               "route_score_select: rows must be 16-byte aligned");
   const int k_eff = k < n_docs + 1 ? k : n_docs + 1;
   RouteDecParams p{};
@@ -363,18 +404,32 @@ extern "C" int msa_route_score_select(const void* q_folded, const float* row_bia
               (long long)n_seq * grid * k_eff * 8);
   MSA_REQUIRE((long long)grid * k_eff <= 8192, "route_score_select: too many candidates per sequence");
   p.n_seq = n_seq; p.n_chunks = n_chunks; p.n_docs = n_docs; p.k_blocks = kdim / kDecBK;
-  p.per_cta = (n_chunks + grid - 1) / grid;
+  p.tiles_q = n_tiles / grid; p.tiles_rem = n_tiles % grid; p.blocked = blocked ? 1 : 0;
   p.min_key = float_to_key(min_val); p.alpha = alpha; p.row_bias = row_bias; p.chunk_doc = chunk_doc;
   p.cand = (unsigned long long*)workspace; p.status = status;
 
+  if (const char* e = getenv("MSA_B200_ROUTE_STAGES")) {   // tuning knob: fewer operand stages than fit
+    const int v = atoi(e);
+    if (v >= 2 && v < p.stages) { smem -= (size_t)(p.stages - v) * ((size_t)kDecBM * kDecBK * 2 + (size_t)bn * kDecBK * 2); p.stages = v; }
+  }
   CUtensorMap map_k, map_k_tail, map_q;
-  MSA_OK_OR_RETURN(make_map(&map_k, rk, (uint64_t)n_chunks, (uint64_t)kdim, (uint64_t)rk_chunk_stride, kDecBK, kDecBM));
-  MSA_OK_OR_RETURN(make_map(&map_k_tail, rk, (uint64_t)n_chunks, (uint64_t)kdim, (uint64_t)rk_chunk_stride, kDecBK, kDecTailBox));
+  if (blocked) {
+    MSA_OK_OR_RETURN(make_map_blocked(&map_k, rk, (uint64_t)n_tiles, (uint64_t)p.k_blocks));
+    MSA_OK_OR_RETURN(make_map_blocked(&map_k_tail, rk, (uint64_t)n_tiles, (uint64_t)p.k_blocks, kDecTailBox));
+  } else {
+    MSA_OK_OR_RETURN(make_map(&map_k, rk, (uint64_t)n_chunks, (uint64_t)kdim, (uint64_t)rk_chunk_stride, kDecBK, kDecBM));
+    MSA_OK_OR_RETURN(make_map(&map_k_tail, rk, (uint64_t)n_chunks, (uint64_t)kdim, (uint64_t)rk_chunk_stride, kDecBK, kDecTailBox));
+  }
   MSA_OK_OR_RETURN(make_map(&map_q, q_folded, (uint64_t)n_seq, (uint64_t)kdim, (uint64_t)kdim, kDecBK, (uint32_t)bn));
-  static DeviceSmem configured{};
-  MSA_OK_OR_RETURN(ensure_dynamic_smem(route_dec_kernel, smem, configured));
+  static DeviceSmem configured[2] = {};
   cudaStream_t st = (cudaStream_t)stream;
-  route_dec_kernel<<<grid, kDecThreads, smem, st>>>(map_k, map_k_tail, map_q, p);
+  if (k_eff <= 16) {
+    MSA_OK_OR_RETURN(ensure_dynamic_smem(route_dec_kernel<16>, smem, configured[0]));
+    route_dec_kernel<16><<<grid, kDecThreads, smem, st>>>(map_k, map_k_tail, map_q, p);
+  } else {
+    MSA_OK_OR_RETURN(ensure_dynamic_smem(route_dec_kernel<32>, smem, configured[1]));
+    route_dec_kernel<32><<<grid, kDecThreads, smem, st>>>(map_k, map_k_tail, map_q, p);
+  }
   MSA_LAUNCH_OK("route_dec_kernel");
   return launch_topk_from_candidates(p.cand, grid * k_eff, n_seq, k_eff, doc_ids_table, out_scores, out_local_ids,
                                      out_global_ids, st);

@@ -203,6 +203,36 @@ int launch_route_simt(int32_t dtype, const void* qf, const float* row_bias, int 
 
 using namespace msa;
 
+// Row-major router keys -> the tile-blocked layout (see tc_common.cuh): one 16-byte vector per thread.
+__global__ void block_keys_kernel(const uint4* __restrict__ rows, long long row_stride_vec, long long first_chunk,
+                                  long long n_rows, int kdim, uint4* __restrict__ blocked) {
+  const int vec_row = kdim / 8, k_blocks = kdim / 64;
+  const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (i >= n_rows * vec_row) return;
+  const long long r = i / vec_row, c = first_chunk + r;
+  const int v = (int)(i % vec_row), kb = v / 8, in_kb = v % 8;
+  const long long dst = (((c / 128) * k_blocks + kb) * 128 + (c % 128)) * 8 + in_kb;
+  blocked[dst] = rows[r * row_stride_vec + v];
+}
+
+extern "C" int64_t msa_router_keys_blocked_bytes(int32_t n_chunks, int32_t kdim) {
+  if (n_chunks < 0 || kdim <= 0 || kdim % 64 != 0) return -1;
+  return (int64_t)((n_chunks + 127) / 128) * 128 * kdim * 2;
+}
+
+extern "C" int msa_router_keys_block(const void* rk_rows, int64_t rk_chunk_stride, int32_t first_chunk, int32_t n_rows,
+                                     int32_t kdim, void* rk_blocked, void* stream) {
+  MSA_REQUIRE(first_chunk >= 0 && n_rows >= 0 && kdim > 0 && kdim % 64 == 0, "router_keys_block: bad sizes (kdim %% 64 == 0)");
+  if (n_rows == 0) return MSA_OK;
+  MSA_REQUIRE(rk_rows && rk_blocked && aligned16(rk_rows) && aligned16(rk_blocked) && rk_chunk_stride % 8 == 0 &&
+                  rk_chunk_stride >= kdim, "router_keys_block: rows must be 16-byte aligned");
+  const long long total = (long long)n_rows * (kdim / 8);
+  block_keys_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (const uint4*)rk_rows, rk_chunk_stride / 8, first_chunk, n_rows, kdim, (uint4*)rk_blocked);
+  MSA_LAUNCH_OK("block_keys_kernel");
+  return MSA_OK;
+}
+
 extern "C" int32_t msa_route_s_pad(int32_t seq_len, int32_t query_reduce) {
   if (query_reduce != MSA_QREDUCE_MAX || seq_len <= 1) return 1;
   const int s16 = (seq_len + 15) / 16 * 16;
@@ -276,9 +306,12 @@ extern "C" int msa_route_scores(const void* q_folded, const float* row_bias, int
     MSA_CUDA_OK(cudaMemsetAsync(status, 0, 4 * sizeof(int32_t), st));
   }
   if (n_seq == 0 || n_chunks == 0) return MSA_OK;
+  const bool blocked = (flags & MSA_ROUTE_KEYS_BLOCKED) != 0;
+  MSA_REQUIRE(!blocked || (dtype == MSA_BF16 && !(flags & MSA_ROUTE_FORCE_SIMT) && kdim % 64 == 0),
+              "route: tile-blocked router keys are read by the tensor-core kernel only (bf16, kdim %% 64 == 0)");
   if (dtype == MSA_BF16 && !(flags & MSA_ROUTE_FORCE_SIMT))
     return launch_route_tc(q_folded, row_bias, n_seq, s_pad, rk, rk_chunk_stride, n_chunks, kdim, chunk_doc, n_docs,
-                           alpha, min_val, score_keys, table_stride, status, st);
+                           alpha, min_val, score_keys, table_stride, status, blocked, st);
   return launch_route_simt(dtype, q_folded, row_bias, n_seq, s_pad, rk, rk_chunk_stride, n_chunks, kdim, chunk_doc,
                            n_docs, alpha, score_keys, table_stride, status, st);
 }

@@ -39,11 +39,11 @@ constexpr int kBK = 64;         // bf16 elements per K block = one 128-byte swiz
 constexpr int kUmmaK = 16;      // K of one tcgen05.mma (bf16)
 constexpr int kTcThreads = 192;
 constexpr int kEpiThreads = 128;
-constexpr int kMaxStages = 8;
+constexpr int kMaxStages = 12;
 constexpr int kTmemCols = 512;
 
 struct RouteTcParams {
-  int n_rows, n_seq, s_pad, bn, n_chunks, n_docs, n_ctiles, n_qtiles, qgroup, k_blocks, stages;
+  int n_rows, n_seq, s_pad, bn, n_chunks, n_docs, n_ctiles, n_qtiles, qgroup, k_blocks, stages, blocked;
   uint32_t min_key;
   float alpha;
   const float* row_bias;
@@ -108,8 +108,10 @@ __device__ __forceinline__ SegInfo seg_info(const RouteTcParams& p, int chunk, i
 
 // Reads this warp's 32 accumulator rows (one chunk per lane, p.bn columns) and publishes the
 // per-(sequence, document) maxima.
+// `part` of `n_parts`: the warps that share a TMEM lane quarter split the tile's columns among themselves.
 __device__ __forceinline__ void epilogue_compute(const RouteTcParams& p, const SegInfo& si, const float* bias,
-                                                 uint32_t taddr, int q0, EpiScratch& scr, int lane) {
+                                                 uint32_t taddr, int q0, EpiScratch& scr, int lane, int part = 0,
+                                                 int n_parts = 1) {
   const int seg = min(p.s_pad, p.bn);  // columns of one sequence inside a tile
   auto publish_score = [&](float v, int seq) {
     if (seq < p.n_seq) {
@@ -133,7 +135,7 @@ __device__ __forceinline__ void epilogue_compute(const RouteTcParams& p, const S
     // (document, column) pairs are dealt out over the lanes, so every lane reduces and publishes
     // distinct pairs instead of all lanes shuffling every column.
     const int n_items = si.n_seg * 16;
-    for (int c0 = 0; c0 < p.bn; c0 += 16) {
+    for (int c0 = part * 16; c0 < p.bn; c0 += 16 * n_parts) {
       float v[16];
       load16(c0, v);
 #pragma unroll
@@ -157,7 +159,7 @@ __device__ __forceinline__ void epilogue_compute(const RouteTcParams& p, const S
       __syncwarp();
     }
   } else {             // `seg` consecutive columns belong to one sequence: in-thread max first
-    for (int s0 = 0; s0 < p.bn; s0 += seg) {
+    for (int s0 = part * seg; s0 < p.bn; s0 += seg * n_parts) {
       float run = -INFINITY;
       for (int c0 = s0; c0 < s0 + seg; c0 += 16) {
         float v[16];
@@ -174,15 +176,22 @@ __device__ __forceinline__ void epilogue_compute(const RouteTcParams& p, const S
   }
 }
 
-__global__ void __launch_bounds__(kTcThreads, 1)
+// kEpiWarps = 4: one epilogue warp per TMEM lane quarter.  kEpiWarps = 8 (bandwidth-bound shapes, one row per
+// sequence): two warps per quarter split the tile's columns; there the epilogue, not the stream, was what set the
+// pace (a tile's 16 K blocks arrive in ~5 us, its reduction took longer), and the CTA's other warps are idle anyway.
+template <int kEpiWarps>
+__global__ void __launch_bounds__((kEpiWarps + 2) * 32, 1)
 route_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_q,
                 const RouteTcParams p) {
   extern __shared__ unsigned char smem_dyn[];
   __shared__ uint64_t s_full[kMaxStages], s_empty[kMaxStages], s_acc_full[2], s_acc_empty[2], s_drain;
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
-  __shared__ float s_bias[kEpiThreads / 32][kRouteMaxN];  // one private copy per epilogue warp
-  __shared__ EpiScratch s_epi[kEpiThreads / 32];
+  // kEpiWarps == 4: one private bias copy per epilogue warp, refilled per tile (query tiles change).  More warps
+  // only run with a single query tile: one copy, which every warp fills with the same values before it reads it.
+  __shared__ float s_bias[kEpiWarps == 4 ? 4 : 1][kRouteMaxN];
+  __shared__ EpiScratch s_epi[kEpiWarps];
+  constexpr int kProducerWarp = kEpiWarps, kMmaWarp = kEpiWarps + 1;
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
@@ -192,12 +201,12 @@ route_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constan
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&s_acc_full[b], 1); mbar_init(&s_acc_empty[b], kEpiThreads / 32); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&s_acc_full[b], 1); mbar_init(&s_acc_empty[b], kEpiWarps); }
     mbar_init(&s_drain, 1);
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
                  "r"(kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -207,7 +216,7 @@ route_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = s_tmem_base;
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     // ------------------------------- TMA producer -------------------------------------
     if (lane == 0) {
       int stage = 0;
@@ -219,7 +228,8 @@ route_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constan
           if (!(ok = mbar_wait(&s_empty[stage], phase ^ 1u, abort_flag, p.status, 1))) break;
           unsigned char* sa = tiles + (size_t)stage * stage_bytes;
           mbar_expect_tx(&s_full[stage], stage_bytes);
-          tma_load_2d(sa, &tmap_k, kb * kBK, tc.ct * kBM, &s_full[stage]);
+          if (p.blocked) tma_load_4d(sa, &tmap_k, 0, 0, kb, tc.ct, &s_full[stage]);   // one contiguous 16 KiB
+          else tma_load_2d(sa, &tmap_k, kb * kBK, tc.ct * kBM, &s_full[stage]);
           tma_load_2d(sa + a_bytes, &tmap_q, kb * kBK, tc.qt * p.bn, &s_full[stage]);
           armed |= 1u << stage;
           armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
@@ -234,7 +244,7 @@ route_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constan
           }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------- MMA issuer ----------------------------------------
     if (lane == 0) {
       // instruction descriptor: D=f32, A=B=bf16, both K-major, N=bn, M=128
@@ -270,7 +280,8 @@ route_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constan
       while (!mbar_try_wait(&s_drain, 0) && global_ns() - t0 < kWaitLimitNs) {}
     }
   } else {
-    // ------------------------------- epilogue (warps 0-3) ------------------------------
+    // ------------------------------- epilogue (warps 0 .. kEpiWarps-1) -----------------
+    const int quarter = warp & 3, part = warp >> 2;   // TMEM lane quarter; share of the columns
     long long it = 0;
     bool ok = true;
     for (long long t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++it) {
@@ -278,19 +289,20 @@ route_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constan
       const int buf = (int)(it & 1);
       const uint32_t acc_phase = (uint32_t)((it >> 1) & 1);
       const int q0 = tc.qt * p.bn;
-      float* bias = s_bias[warp];
+      float* bias = s_bias[kEpiWarps == 4 ? warp : 0];
       __syncwarp();  // the previous tile's reads of this warp's bias copy are done
-      for (int j = lane; j < p.bn; j += 32) bias[j] = (q0 + j < p.n_rows) ? p.row_bias[q0 + j] : -INFINITY;
-      const SegInfo si = seg_info(p, tc.ct * kBM + (int)threadIdx.x, lane, s_epi[warp]);
+      if (kEpiWarps == 4 || it == 0)
+        for (int j = lane; j < p.bn; j += 32) bias[j] = (q0 + j < p.n_rows) ? p.row_bias[q0 + j] : -INFINITY;
+      const SegInfo si = seg_info(p, tc.ct * kBM + quarter * 32 + lane, lane, s_epi[warp]);
       __syncwarp();
       // every lane waits; the warp then agrees on the outcome so that it never diverges
       ok = mbar_wait(&s_acc_full[buf], acc_phase, abort_flag, p.status, 4);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)buf * kRouteMaxN;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * kRouteMaxN;
 
-      epilogue_compute(p, si, bias, taddr, q0, s_epi[warp], lane);
+      epilogue_compute(p, si, bias, taddr, q0, s_epi[warp], lane, part, kEpiWarps / 4);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_acc_empty[buf]);
@@ -301,7 +313,7 @@ route_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constan
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == 5)
+  if (warp == kMmaWarp)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
 }
 
@@ -506,7 +518,7 @@ __global__ void wait_selftest_kernel(unsigned long long limit_ns, int32_t* statu
 // ---- host side ------------------------------------------------------------------------
 int launch_route_tc(const void* qf, const float* row_bias, int n_seq, int s_pad, const void* rk, int64_t rk_stride,
                     int n_chunks, int kdim, const int32_t* chunk_doc, int n_docs, float alpha, float min_val,
-                    uint32_t* keys, int64_t table_stride, int32_t* status, cudaStream_t stream) {
+                    uint32_t* keys, int64_t table_stride, int32_t* status, bool blocked, cudaStream_t stream) {
   MSA_REQUIRE(kdim % kBK == 0, "route (tensor-core path): kdim=%d must be a multiple of %d", kdim, kBK);
   MSA_REQUIRE(aligned16(qf) && aligned16(rk) && rk_stride % 8 == 0 && rk_stride >= kdim,
               "route (tensor-core path): rows must be 16-byte aligned");
@@ -531,8 +543,14 @@ int launch_route_tc(const void* qf, const float* row_bias, int n_seq, int s_pad,
   p.n_qtiles = (p.n_rows + p.bn - 1) / p.bn;
   p.k_blocks = kdim / kBK;
   const size_t stage_bytes = (size_t)kBM * kBK * 2 + (size_t)p.bn * kBK * 2;
-  p.stages = (int)((204 * 1024) / stage_bytes);
+  // bandwidth-bound shapes (one row per sequence, a single query tile): 8 or 16 epilogue warps and their scratch
+  const int epi_warps = (s_pad == 1 && n_seq <= kRouteMaxN) ? (p.bn > 64 ? 16 : 8) : 4;
+  p.stages = (int)(((epi_warps == 16 ? 180 : epi_warps == 8 ? 196 : 204) * 1024) / stage_bytes);
   if (p.stages > kMaxStages) p.stages = kMaxStages;
+  if (const char* e = getenv("MSA_B200_ROUTE_STAGES")) {   // tuning knob: fewer operand stages than fit
+    const int v = atoi(e);
+    if (v >= 2 && v < p.stages) p.stages = v;
+  }
   MSA_REQUIRE(p.stages >= 2, "route: tile does not fit shared memory");
   const size_t qtile_bytes = (size_t)p.bn * kdim * 2;
   p.qgroup = (int)((32u << 20) / qtile_bytes);
@@ -542,21 +560,25 @@ int launch_route_tc(const void* qf, const float* row_bias, int n_seq, int s_pad,
   p.status = status;
   p.min_key = float_to_key(min_val);
 
+  p.blocked = blocked ? 1 : 0;
   CUtensorMap map_k, map_q;
-  int rc = make_map(&map_k, rk, (uint64_t)n_chunks, (uint64_t)kdim, (uint64_t)rk_stride, kBK, kBM);
+  int rc = blocked ? make_map_blocked(&map_k, rk, (uint64_t)p.n_ctiles, (uint64_t)p.k_blocks)
+                   : make_map(&map_k, rk, (uint64_t)n_chunks, (uint64_t)kdim, (uint64_t)rk_stride, kBK, kBM);
   if (rc != MSA_OK) return rc;
   rc = make_map(&map_q, qf, (uint64_t)p.n_rows, (uint64_t)kdim, (uint64_t)kdim, kBK, (uint32_t)p.bn);
   if (rc != MSA_OK) return rc;
 
   int n_sm = 0;
   MSA_OK_OR_RETURN(device_sm_count(&n_sm));
-  static DeviceSmem smem_set{}, pair_set{};
+  static DeviceSmem smem_set{}, smem_set_8{}, smem_set_16{}, pair_set{};
   const size_t smem = (size_t)p.stages * stage_bytes + 1024;
-  MSA_OK_OR_RETURN(ensure_dynamic_smem(route_tc_kernel, smem, smem_set));
+  if (epi_warps == 16) MSA_OK_OR_RETURN(ensure_dynamic_smem(route_tc_kernel<16>, smem, smem_set_16));
+  else if (epi_warps == 8) MSA_OK_OR_RETURN(ensure_dynamic_smem(route_tc_kernel<8>, smem, smem_set_8));
+  else MSA_OK_OR_RETURN(ensure_dynamic_smem(route_tc_kernel<4>, smem, smem_set));
   const long long n_tiles = (long long)p.n_ctiles * p.n_qtiles;
   // Tensor-bound shapes (full 256-row query tiles, enough chunk tiles to fill the GPU) run on CTA pairs.
   static const bool pair_off = getenv("MSA_B200_ROUTE_NO_PAIR") != nullptr;
-  if (!pair_off && p.bn == kPairBN && p.n_rows % kPairBN == 0 && n_tiles >= 2ll * n_sm) {
+  if (!pair_off && !blocked && p.bn == kPairBN && p.n_rows % kPairBN == 0 && n_tiles >= 2ll * n_sm) {
     RouteTcParams p2 = p;
     p2.n_ctiles = (n_chunks + kPairBM - 1) / kPairBM;
     p2.stages = 6;  // 6 x 32 KB
@@ -573,7 +595,9 @@ int launch_route_tc(const void* qf, const float* row_bias, int n_seq, int s_pad,
     return MSA_OK;
   }
   const int grid = (int)(n_tiles < n_sm ? n_tiles : n_sm);
-  route_tc_kernel<<<grid, kTcThreads, smem, stream>>>(map_k, map_q, p);
+  if (epi_warps == 16) route_tc_kernel<16><<<grid, 18 * 32, smem, stream>>>(map_k, map_q, p);
+  else if (epi_warps == 8) route_tc_kernel<8><<<grid, 10 * 32, smem, stream>>>(map_k, map_q, p);
+  else route_tc_kernel<4><<<grid, kTcThreads, smem, stream>>>(map_k, map_q, p);
   MSA_LAUNCH_OK("route_tc_kernel");
   return MSA_OK;
 }

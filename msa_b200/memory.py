@@ -128,7 +128,9 @@ class BlockDesc:
 
 @dataclass
 class BlockData:
-    rk: Optional[torch.Tensor] = None   # [C, Hkv, D] device
+    rk: Optional[torch.Tensor] = None   # [C, Hkv, D] device (None once only the blocked copy is kept)
+    rk_blocked: Optional[torch.Tensor] = None   # [tiles, Hkv*D/64, 128, 64] device: tile-blocked copy of rk
+    n_chunks: int = 0                   # chunks held (rk_blocked is padded to whole tiles)
     kv: Optional[torch.Tensor] = None   # [C, 2, Hkv, D] pinned host
     kv_device_address: int = 0          # address the GPU uses for ``kv``
 
@@ -142,10 +144,14 @@ class BlockData:
 
     @property
     def rk_head_major(self):
-        return self.rk.permute(1, 0, 2).unsqueeze(0)
+        return self.get_router_k().permute(1, 0, 2).unsqueeze(0)
 
     def get_router_k(self):
-        return self.rk
+        """Row-major router keys ``[C, Hkv, D]`` (materialised from the blocked copy when only that is kept)."""
+        if self.rk is not None:
+            return self.rk
+        h, d = self.kv.shape[2], self.kv.shape[3]
+        return ops.unblock_router_keys(self.rk_blocked, self.n_chunks).view(self.n_chunks, h, d)
 
 
 def is_reference_bank(path: str) -> bool:
@@ -394,15 +400,16 @@ class Memory:
         os.makedirs(path, exist_ok=True)
         g = self.geometry
         first = self.blocks[self.router_layer_ids[0]]
-        meta = {"format": "msa_b200-bank-1", "dtype": str(first.rk.dtype).replace("torch.", ""),
-                "n_chunks": int(first.rk.shape[0]), "n_kv_heads": g.num_key_value_heads, "head_dim": g.head_dim,
+        first_rk = first.get_router_k()
+        meta = {"format": "msa_b200-bank-1", "dtype": str(first_rk.dtype).replace("torch.", ""),
+                "n_chunks": int(first_rk.shape[0]), "n_kv_heads": g.num_key_value_heads, "head_dim": g.head_dim,
                 "router_layer_ids": list(self.router_layer_ids),
                 "doc_ids": [d.doc_id for d in self.block_desc.docs],
                 "doc_chunks": [d.num_chunks for d in self.block_desc.docs]}
         torch.cuda.synchronize(self.device)
         for layer in self.router_layer_ids:
             blk = self.blocks[layer]
-            blk.rk.cpu().contiguous().view(torch.uint8).numpy().tofile(os.path.join(path, f"rk_L{layer}.bin"))
+            blk.get_router_k().cpu().contiguous().view(torch.uint8).numpy().tofile(os.path.join(path, f"rk_L{layer}.bin"))
             blk.kv.contiguous().view(torch.uint8).numpy().tofile(os.path.join(path, f"kv_L{layer}.bin"))
         torch.save({l: (k.cpu(), v.cpu()) for l, (k, v) in self.template_prefix_kvcache.items()},
                    os.path.join(path, "prefix_cache.pt"))
@@ -467,8 +474,24 @@ class Memory:
 
     def _post_process(self):
         first = self.blocks[self.router_layer_ids[0]]
-        kv_bytes = first.rk.nbytes * len(self.router_layer_ids)
-        return kv_bytes, tuple(first.rk_head_major.shape)
+        rk = first.rk if first.rk is not None else first.rk_blocked
+        kv_bytes = rk.nbytes * len(self.router_layer_ids)
+        return kv_bytes, (1, self.geometry.num_key_value_heads, self.block_desc.chunks(), self.geometry.head_dim)
+
+    def block_router_keys(self, free_rows: bool = False):
+        """Re-lay every router layer's keys in 128-chunk tiles (``ops.block_router_keys``): the bandwidth-bound
+        routing of decode steps then streams them ~19 % faster from HBM, with identical results.  Call once after
+        the bank is built.  ``free_rows`` drops the row-major copy layer by layer (a bank that fills most of HBM);
+        every routing call then reads the blocked copy (prefill-shaped calls on the one-CTA tensor-core kernel)."""
+        for layer in self.router_layer_ids:
+            blk = self.blocks[layer]
+            if blk.rk is None or blk.rk.dtype != torch.bfloat16 or blk.rk[0].numel() % 64 != 0:
+                continue
+            blk.n_chunks = blk.rk.shape[0]
+            blk.rk_blocked = ops.block_router_keys(blk.rk)
+            if free_rows:
+                torch.cuda.current_stream(self.device).synchronize()
+                blk.rk = None
 
     def get_max_local_pool_doc_id(self) -> int:
         return int(self.block_desc.pool_ids_cpu[-1])
@@ -477,6 +500,36 @@ class Memory:
         return self.template_prefix_kvcache[layer_idx]
 
     # ------------------------------------------------------------------ scoring + selection
+    def prepare_table(self, n_seq: int):
+        """Reset the score table for ``n_seq`` sequences on a side stream, NOW, so that the reset overlaps whatever the
+        caller issues next on the current stream (the fold kernel, the query all-gather); the next ``score_folded``
+        call for ``n_seq`` sequences joins it.  A dependent launch costs a few microseconds even when the kernel is
+        tiny, which matters for decode-time routing (a layer-step of ~90 us).  Fork and join both happen inside the
+        routing call, so the pattern can be captured in a CUDA graph."""
+        desc = self.block_desc
+        tbl = self.__dict__.get("_table")
+        if tbl is None or tbl.shape[0] != n_seq or tbl.shape[1] != desc.nr_docs + 1:
+            tbl = self._table = torch.empty((n_seq, desc.nr_docs + 1), dtype=torch.int32, device=self.device)
+        if "_side" not in self.__dict__:
+            self._side = torch.cuda.Stream(self.device)
+        main = torch.cuda.current_stream(self.device)
+        fork = torch.cuda.Event()
+        fork.record(main)
+        self._side.wait_event(fork)
+        dtype = next(b.rk if b.rk is not None else b.rk_blocked for b in self.blocks.values()).dtype
+        with torch.cuda.stream(self._side):
+            ops.route_table_reset(tbl, desc.nr_docs, torch.finfo(dtype).min)      # status is not touched from here
+            done = torch.cuda.Event()
+            done.record(self._side)
+        self._table_ready = (n_seq, done)
+
+    def _take_prepared_table(self, n_seq: int):
+        ready = self.__dict__.pop("_table_ready", None)
+        if ready is None:
+            return None
+        torch.cuda.current_stream(self.device).wait_event(ready[1])      # join, whatever happens next
+        return self._table if ready[0] == n_seq else None
+
     def score_folded(self, layer_idx: int, q_folded, row_bias, n_seq: int, s_pad: int, n_heads: int, top_k: int,
                      scale: float = 1.0, out=None):
         """Score ``n_seq`` folded sequences (head_reduce "mean") against this shard and select ``top_k``
@@ -484,27 +537,32 @@ class Memory:
         fills a per-chunk table with the same kernel (every chunk its own document) and reduces it."""
         desc = self.block_desc
         blk = self.blocks[layer_idx]
-        min_val = torch.finfo(blk.rk.dtype).min
+        use_blocked = blk.rk_blocked is not None and (blk.rk is None or s_pad == 1)   # bandwidth-bound shapes, or no rows left
+        keys_src = blk.rk_blocked if use_blocked else blk.rk
+        min_val = torch.finfo(keys_src.dtype).min
         if self.chunk_reduce_method == "max" and self.fused_decode_routing and \
-                ops.route_score_select_supported(blk.rk, n_seq, s_pad, top_k):
+                ops.route_score_select_supported(keys_src, n_seq, s_pad, top_k, use_blocked):
             # one token per sequence: scoring and per-CTA selection in one launch, no score table
             need = (n_seq, top_k)
             ws = self.__dict__.get("_select_ws")
             if ws is None or ws[0] != need:
                 n_bytes = int(A.lib().msa_route_score_select_workspace_bytes(n_seq, top_k))
                 ws = self._select_ws = (need, torch.empty((max(n_bytes, 8) + 7) // 8, dtype=torch.int64, device=self.device))
-            return ops.route_score_select(q_folded, row_bias, n_seq, blk.rk, desc.chunk_doc, desc.nr_docs, scale / n_heads,
-                                          top_k, desc.doc_ids, min_val, self._status, ws[1], out)
+            self._take_prepared_table(n_seq)      # joins a table reset that a caller may have started
+            return ops.route_score_select(q_folded, row_bias, n_seq, keys_src, desc.chunk_doc, desc.nr_docs, scale / n_heads,
+                                          top_k, desc.doc_ids, min_val, self._status, ws[1], out, blocked=use_blocked)
+        prepared = self._take_prepared_table(n_seq)
         if self.chunk_reduce_method == "max":
-            keys, _ = ops.route_scores(q_folded, row_bias, n_seq, s_pad, blk.rk, desc.chunk_doc, desc.nr_docs,
-                                       alpha=scale / n_heads, min_val=min_val, status=self._status)
+            keys, _ = ops.route_scores(q_folded, row_bias, n_seq, s_pad, keys_src, desc.chunk_doc, desc.nr_docs,
+                                       alpha=scale / n_heads, min_val=min_val, status=self._status, blocked=use_blocked,
+                                       keys=prepared, flags=A.ROUTE_NO_INIT if prepared is not None else 0)
         else:
-            c = blk.rk.shape[0]
+            c = desc.chunk_doc.numel()
             ident = self.__dict__.get("_identity_ids")
             if ident is None or ident.numel() != c:
                 ident = self._identity_ids = torch.arange(1, c + 1, dtype=torch.int32, device=self.device)
-            chunk_keys, _ = ops.route_scores(q_folded, row_bias, n_seq, s_pad, blk.rk, ident, c, alpha=scale / n_heads,
-                                             min_val=min_val, status=self._status)
+            chunk_keys, _ = ops.route_scores(q_folded, row_bias, n_seq, s_pad, keys_src, ident, c, alpha=scale / n_heads,
+                                             min_val=min_val, status=self._status, blocked=use_blocked)
             keys = ops.route_reduce_chunks(chunk_keys, desc.chunk_doc, desc.nr_docs, "mean", min_val, status=self._status)
         return self._select(keys, n_seq, top_k, out)
 
@@ -513,9 +571,10 @@ class Memory:
         head (``ops.route_chunk_scores``) and the chunk table is reduced to documents."""
         desc = self.block_desc
         blk = self.blocks[layer_idx]
-        min_val = torch.finfo(blk.rk.dtype).min
+        rk = blk.get_router_k()
+        min_val = torch.finfo(rk.dtype).min
         self._status.zero_()
-        chunk_keys = ops.route_chunk_scores(query_states, query_mask, self.num_key_value_groups, blk.rk,
+        chunk_keys = ops.route_chunk_scores(query_states, query_mask, self.num_key_value_groups, rk,
                                             self.head_reduce_method, self.query_reduce_method, scale, min_val)
         keys = ops.route_reduce_chunks(chunk_keys, desc.chunk_doc, desc.nr_docs, self.chunk_reduce_method, min_val,
                                        status=self._status)

@@ -242,6 +242,8 @@ class MSAService(Memory, MemoryClientBase):
         n_all = self.world_size * b
         if self.head_reduce_method == "max":
             return self._route_unfolded(query_states, query_mask, layer_idx, l2_normalize, scale)
+        if s == 1 and self.chunk_reduce_method == "max" and self.blocks[layer_idx].rk_blocked is not None:
+            self.prepare_table(n_all)      # decode step over blocked keys (table path): the reset overlaps fold + all-gather
         qf, bias, s_pad, _ = self._gather_querys(query_states, query_mask, l2_normalize, all_valid)
         if self.world_size > 1:
             # the selection writes straight into one buffer (scores, local ids, global ids as planes), ONE

@@ -213,9 +213,10 @@ FUSED_CASES = [
     (128, 900, (1, 9), 8, [0, 127]),    # the widest query tile
     (16, 40, (1, 3), 16, []),           # fewer chunk tiles than SMs
     (7, 9, (1, 2), 16, []),             # fewer documents than k: k' = n_docs + 1, the dummy document is selected
-    (32, 60000, (1, 1), 16, []),        # single-chunk documents: more documents per CTA than table rows -> flushes
-    (24, 30000, (1, 4), 16, []),        # flushes with documents that are still open at the flush
-    (8, 6, (200, 400), 4, []),          # documents longer than a CTA's range
+    (32, 60000, (1, 1), 16, []),        # single-chunk documents: every table row of every tile in use
+    (24, 30000, (1, 4), 16, []),        # documents that continue across tile and share borders
+    (8, 6, (200, 400), 4, []),          # documents longer than a CTA's share of the tiles
+    (48, 20000, (3, 3), 16, []),        # document starts never on a tile border after the first
 ]
 
 
@@ -244,6 +245,13 @@ def test_route_score_select_equals_table_path(ops, case):
     assert status.cpu().tolist() == [0, 0, 0, 0] and status2.cpu().tolist() == [0, 0, 0, 0]
     assert s.shape == ref_s.shape == (b, min(k, n_docs + 1))
     assert torch.equal(s, ref_s) and torch.equal(l, ref_l) and torch.equal(g_, ref_g)
+    # the same call over the tile-blocked copy of the keys
+    blocked = ops.block_router_keys(rk_d)
+    assert ops.route_score_select_supported(blocked, b, s_pad, k, blocked=True)
+    s3, l3, g3 = ops.route_score_select(qf, bias, b, blocked, cd, n_docs, 1.0 / 32, k, tid, status=status2, blocked=True)
+    torch.cuda.synchronize()
+    assert status2.cpu().tolist() == [0, 0, 0, 0]
+    assert torch.equal(s3, ref_s) and torch.equal(l3, ref_l) and torch.equal(g3, ref_g)
     # and against the oracle, tie aware
     table_ref = O.route_doc_scores(q.float().view(b, 8, 4, 1, 128), mask, rk.float().transpose(0, 1), pool_ids, n_docs)
     live = [i for i in range(b) if i not in masked]
@@ -277,6 +285,65 @@ def test_route_score_select_through_memory_and_bounds(ops):
     st = status.cpu().tolist()
     assert st[0] == 0 and st[2] > 0
     assert int(l.max()) <= len(chunks)
+
+
+@pytest.mark.parametrize("shape", [(32, 1, 4, 3000, (8, 8), 16), (4, 128, 4, 150, (1, 12), 16), (2, 300, 1, 64, (1, 20), 16),
+                                   (128, 1, 4, 333, (1, 9), 16), (3, 256, 4, 2600, (1, 16), 32)])
+def test_routing_over_tile_blocked_keys_is_bit_identical(ops, shape):
+    """The tile-blocked key layout ([tiles][K blocks][128 chunks][64]) only changes where the bytes of a TMA box lie
+    in memory: the score table must come out bit for bit as from the row-major layout (chunk counts that are not a
+    multiple of 128 included), and the packing must round-trip."""
+    b, s, grp, n_docs, (lo, hi), k = shape
+    chunks = ragged_docs(n_docs, lo, hi, seed=b + s)
+    rk, pool_ids = make_bank(chunks, dtype=torch.bfloat16, seed=s + 1)
+    g = torch.Generator().manual_seed(3 + b)
+    q = torch.nn.functional.normalize(torch.randn(b, 8 * grp, s, 128, generator=g), dim=-1).to(torch.bfloat16)
+    mask = torch.ones(b, s, dtype=torch.bool)
+    if s > 4:
+        mask[0, s // 2:] = False
+    rk_d, cd = rk.to(DEV), pool_ids.to(torch.int32).to(DEV)
+    blocked = ops.block_router_keys(rk_d)
+    c = rk.shape[0]
+    assert blocked.shape == ((c + 127) // 128, 16, 128, 64)
+    assert torch.equal(ops.unblock_router_keys(blocked, c), rk_d.view(c, -1))
+    # the same storage filled in two pieces, as bank ingestion does block by block
+    half = c // 3
+    pieces = ops.block_router_keys(rk_d[:half], n_chunks_total=c)
+    ops.block_router_keys(rk_d[half:], blocked=pieces, first_chunk=half)
+    assert torch.equal(pieces, blocked)
+    qf, bias, s_pad = ops.fold_queries(q.to(DEV), mask.to(DEV), grp)
+    keys_rows, st1 = ops.route_scores(qf, bias, b, s_pad, rk_d, cd, n_docs, alpha=1.0 / (8 * grp))
+    keys_blk, st2 = ops.route_scores(qf, bias, b, s_pad, blocked, cd, n_docs, alpha=1.0 / (8 * grp), blocked=True)
+    torch.cuda.synchronize()
+    assert st1.cpu().tolist() == [0, 0, 0, 0] and st2.cpu().tolist() == [0, 0, 0, 0]
+    assert torch.equal(keys_rows, keys_blk)
+
+
+def test_memory_with_blocked_keys_gives_the_same_winners(ops):
+    from msa_b200.memory import AttentionGeometry, Document, Memory, ModelConfig
+    chunks = ragged_docs(900, 1, 9, seed=8)
+    rk, _ = make_bank(chunks, dtype=torch.bfloat16, seed=9)
+    mem = Memory(0, None, ModelConfig(doc_top_k=16, router_layer_idx="0"), None, AttentionGeometry(num_hidden_layers=1))
+    z = torch.zeros_like(rk)
+    mem.load_pooled([Document(doc_id=70 + i, num_chunks=n) for i, n in enumerate(chunks)], {0: (z, z, rk.to(DEV))})
+    g = torch.Generator().manual_seed(10)
+    q1 = torch.nn.functional.normalize(torch.randn(20, 8, 4, 1, 128, generator=g), dim=-1).to(torch.bfloat16).to(DEV)
+    q2 = torch.nn.functional.normalize(torch.randn(3, 8, 4, 40, 128, generator=g), dim=-1).to(torch.bfloat16).to(DEV)
+    m1 = torch.ones(20, 1, 1, 1, 1, dtype=torch.bool, device=DEV)
+    m2 = torch.ones(3, 1, 1, 40, 1, dtype=torch.bool, device=DEV)
+    before = [mem.prefill_stage2(0, q1, m1), mem.prefill_stage2(0, q2, m2)]
+    mem.block_router_keys()
+    assert mem.blocks[0].rk_blocked is not None and mem.blocks[0].rk is not None
+    kept = [mem.prefill_stage2(0, q1, m1), mem.prefill_stage2(0, q2, m2)]
+    mem.block_router_keys(free_rows=True)
+    assert mem.blocks[0].rk is None
+    freed = [mem.prefill_stage2(0, q1, m1), mem.prefill_stage2(0, q2, m2)]
+    mem.check_status()
+    for other in (kept, freed):
+        for a, b_ in zip(before, other):
+            assert all(torch.equal(x, y) for x, y in zip(a, b_))
+    assert torch.equal(mem.blocks[0].get_router_k(), rk.to(DEV))        # the rows can still be read back
+    assert mem.blocks[0].rk_head_major.shape == (1, 8, rk.shape[0], 128)
 
 
 def test_routing_scaled_dot_mode(ops):
