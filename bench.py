@@ -1223,6 +1223,7 @@ def generate_measure(torch, dist, svc, world, rank, local_rank, dev, n_docs, doc
     svc.check_status()
     model.check_fetch_counts()
     tokens_host = model.tokens.cpu()
+    timeline = generate_timeline(torch, model, router_ids, dev)
     value = batch_total * new_tokens / (ms_total / 1e3)
     per_step_bytes = (sum(p_.numel() for l_ in model.layers for p_ in l_.values()) + model.lm_head.numel()) * 2
     out = {
@@ -1239,13 +1240,68 @@ def generate_measure(torch, dist, svc, world, rank, local_rank, dev, n_docs, doc
                           "of step t+1; the fetch issued in step t is needed by layer 18 of step t+1",
                   "exposed_ms_per_step": max(0.0, (ms_total - ms_nofetch) / new_tokens),
                   "pcie_bytes_per_step_per_gpu": 18 * b * TOP_K * CHUNKS_PER_DOC * 2 * HKV * D * 2},
-        "dense_weight_bytes_per_step": per_step_bytes, "clocks": clocks,
+        "timeline": timeline, "dense_weight_bytes_per_step": per_step_bytes, "clocks": clocks,
         # this package's kernels per step: per layer add+norm x2, q/k norm+rope, decode attention (+ combine),
         # SiLU*up; per router layer fold, table fill, scoring, top-k x2, merge, gather plan, gather; final norm
         "gpu_launches": new_tokens * (36 * 5 + 18 * 8 + 1), "last_tokens": tokens_host[:4].tolist()}
     del model
     torch.cuda.empty_cache()
     return out
+
+
+def generate_timeline(torch, model, router_ids, dev):
+    """Where one config-5 decode step spends its time: the rotated step captured in a CUDA graph WITH event-record
+    nodes (external events) on the main and the fetch stream and around every all-gather, replayed, and read back.
+    The main stream is serial, so its spans add up; the fetch stream runs beside it."""
+    import msa_b200.service as S
+    try:
+        model.fetch_enabled = True
+        model.reset()
+        model.prime()
+        model.probe, model.probe_external = {}, True
+        S.COLLECTIVE_PROBE, S.COLLECTIVE_PROBE_EXTERNAL = [], True
+        graph = torch.cuda.CUDAGraph()
+        try:
+            with torch.cuda.graph(graph):
+                model.step_pipelined()
+        finally:
+            pr, coll = model.probe, S.COLLECTIVE_PROBE
+            model.probe, model.probe_external = None, False
+            S.COLLECTIVE_PROBE, S.COLLECTIVE_PROBE_EXTERNAL = None, False
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize(dev)
+        t0 = pr["back_start"][0]
+        at = lambda e: t0.elapsed_time(e)
+        span = lambda a, b: a.elapsed_time(b)
+        step_ms = at(pr["step_end"][0])
+        main_ms = at(pr["front_end"][0])
+        routing = sum(span(pr["route_start"][l], pr["route_end"][l]) for l in router_ids)
+        collectives = sum(span(a, b) for a, b in coll)
+        attention = sum(span(pr["attn_start"][l], pr["attn_end"][l]) for l in pr["attn_start"])
+        fetch_busy = sum(span(pr["fetch_start"][l], pr["fetch_end"][l]) for l in pr.get("fetch_start", {}))
+        # the entries fetched after layer l's attention are read by layer l's attention of the NEXT step
+        slack = [step_ms + at(pr["attn_start"][l]) - at(pr["fetch_end"][l]) for l in pr.get("fetch_end", {})]
+        split = {"routing_scoring_and_selection": routing - collectives, "collectives": collectives, "attention": attention,
+                 "dense_gemms_and_elementwise": main_ms - routing - attention, "waiting_for_fetch_at_step_end": step_ms - main_ms}
+        layers = []
+        for l in router_ids[:3]:
+            layers.append({"layer": l, "route": [at(pr["route_start"][l]), at(pr["route_end"][l])],
+                           "attention": [at(pr["attn_start"][l]), at(pr["attn_end"][l])],
+                           "fetch": [at(pr["fetch_start"][l]), at(pr["fetch_end"][l])] if l in pr.get("fetch_start", {}) else None})
+        del graph
+        return {"how": "rotated step in a CUDA graph with event-record nodes, third replay; ms from the first router layer's start",
+                "step_ms": step_ms, "split_ms": {k: round(v, 4) for k, v in split.items()},
+                "limiter": max(split, key=split.get),
+                "fetch_stream": {"busy_ms": fetch_busy, "last_end_ms": max((at(e) for e in pr.get("fetch_end", {}).values()),
+                                                                            default=None),
+                                 "min_slack_before_next_use_ms": min(slack) if slack else None},
+                "collective_calls": len(coll), "first_router_layers_ms": layers}
+    except Exception as e:      # a timeline is an explanation, not a result: never fail the bench for it
+        model.probe = None
+        S.COLLECTIVE_PROBE = None
+        torch.cuda.synchronize(dev)
+        return {"error": f"{type(e).__name__}: {e}"}
 
 
 def run_generate(args):

@@ -56,7 +56,7 @@ constexpr int kDecMaxStages = 12;
 constexpr int kDecRows = kDecBM + 2;  // table rows: a tile's documents (at most one per chunk) and a carried one
 
 struct RouteDecParams {
-  int n_seq, bn, bn_pad, n_chunks, n_docs, k_blocks, stages, cap, keep, tiles_q, tiles_rem, blocked;
+  int n_seq, bn, bn_pad, n_chunks, n_docs, k_blocks, stages, cap, keep, lists, tiles_q, tiles_rem, blocked;
   uint32_t min_key;
   float alpha;
   const float* row_bias;
@@ -65,8 +65,16 @@ struct RouteDecParams {
   int32_t* status;
 };
 
+#ifdef MSA_ROUTE_DEC_TRACE
+__device__ unsigned long long g_dec_trace[160][12];
+#define TRACE(i) g_dec_trace[blockIdx.x][i] = global_ns()
+#define TRACE_ADD(i, v) g_dec_trace[blockIdx.x][i] += (v)
+#else
+#define TRACE(i)
+#define TRACE_ADD(i, v)
+#endif
 struct DecSeg { int start, len, doc; };
-struct DecEpiScratch {
+struct alignas(16) DecEpiScratch {
   float xpose[16][33];
   DecSeg seg[32];
 };
@@ -105,6 +113,26 @@ __device__ __forceinline__ void list_insert(uint32_t (&lk)[KMAX], int (&ld)[KMAX
   }
 }
 
+// (key, doc) a is better than b: the higher score, and of equal scores the earlier document (empty slots, key 0, last).
+__device__ __forceinline__ bool list_better(uint32_t ka, int da, uint32_t kb, int db) {
+  return ka > kb || (ka == kb && da < db);
+}
+__device__ __forceinline__ void list_take_better(uint32_t& k, int& d, uint32_t ko, int d_o) {
+  const bool other = list_better(ko, d_o, k, d);
+  k = other ? ko : k;
+  d = other ? d_o : d;
+}
+// compare-exchange: the better entry ends up in (k0, d0)
+__device__ __forceinline__ void list_order_pair(uint32_t& k0, int& d0, uint32_t& k1, int& d1) {
+  const bool swap = list_better(k1, d1, k0, d0);
+  const uint32_t tk = k0;
+  const int td = d0;
+  k0 = swap ? k1 : k0;
+  d0 = swap ? d1 : d0;
+  k1 = swap ? tk : k1;
+  d1 = swap ? td : d1;
+}
+
 // tmap_k / tmap_k_tail: 128-row and 32-row boxes over the keys, 2-D (row-major keys) or 4-D (tile-blocked keys).
 template <int KMAX>
 __global__ void __launch_bounds__(kDecThreads, 1)
@@ -124,20 +152,37 @@ route_dec_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
   volatile int* abort_flag = &s_abort;
 
   if (threadIdx.x == 0) {
+    TRACE(0);
+#ifdef MSA_ROUTE_DEC_TRACE
+    g_dec_trace[blockIdx.x][9] = 0; g_dec_trace[blockIdx.x][10] = 0;
+#endif
     for (int s = 0; s < p.stages; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(&s_acc_full[b], 1); mbar_init(&s_acc_empty[b], kDecEpiWarps); }
     mbar_init(&s_drain, 1);
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 0 || warp == kDecProducerWarp) {
-    // This CTA owns the documents that START in its share of the (whole) tiles: both ends of the share are moved
-    // forward to the next document start, so its last document may reach into the next CTA's first tile, whose
-    // leading rows that CTA skips.  (The producer warp finds the start, warp 0 the end, at the same time.)
-    const int c = (int)blockIdx.x + (warp == 0 ? 1 : 0);     // CTA c's share starts at tile c*q + min(c, rem)
+  __syncthreads();                                   // the barriers exist
+  // This CTA's share of the (whole, aligned) tiles; it owns the documents that START there: both ends of the share
+  // are moved forward to the next document start, so its last document may reach into the next CTA's first tile,
+  // whose leading rows that CTA masks.
+  const int first_tile = (int)blockIdx.x * p.tiles_q + min((int)blockIdx.x, p.tiles_rem);
+  const int prologue = min(p.stages, p.k_blocks);    // K blocks of the first tile that are requested before the ends are known
+  if (warp == kDecProducerWarp && lane == 0) {
+    for (int kb = 0; kb < prologue; ++kb) {          // the ring is empty: no waits; the first tile is read whole
+      unsigned char* sa = tiles + (size_t)kb * stage_bytes;
+      mbar_expect_tx(&s_full[kb], stage_bytes);
+      if (p.blocked) tma_load_4d(sa, &tmap_k, 0, 0, kb, first_tile, &s_full[kb]);
+      else tma_load_2d(sa, &tmap_k, kb * kDecBK, first_tile * kDecBM, &s_full[kb]);
+      tma_load_2d(sa + a_bytes, &tmap_q, kb * kDecBK, 0, &s_full[kb]);
+    }
+    TRACE(2);
+  }
+  if (warp < 2) {                                    // two dependent rounds of global loads, beside the first requests
+    const int c = (int)blockIdx.x + warp;            // warp 0: start of this share, warp 1: start of the next
     const long long a = ((long long)c * p.tiles_q + min(c, p.tiles_rem)) * kDecBM;
     const int v = snap_to_document(p.chunk_doc, (int)(a < p.n_chunks ? a : p.n_chunks), p.n_chunks, lane);
-    if (lane == 0) *(warp == 0 ? &s_hi : &s_lo) = v;
+    if (lane == 0) *(warp == 0 ? &s_lo : &s_hi) = v;
   }
   if (warp == kDecMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
@@ -149,8 +194,9 @@ route_dec_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = s_tmem_base;
   const int lo = s_lo, hi = s_hi;
-  const int first_tile = lo / kDecBM;                                     // tiles are the fixed 128-chunk blocks
-  const int n_tiles = lo < hi ? (hi + kDecBM - 1) / kDecBM - first_tile : 0;
+  if (threadIdx.x == 0) TRACE(1);
+  const bool owns = lo < hi;                         // false: one document covers the whole share (the first tile is still drained)
+  const int n_tiles = owns ? (hi + kDecBM - 1) / kDecBM - first_tile : 1;
 
   if (warp == kDecProducerWarp) {
     // ------------------------------- TMA producer -------------------------------------
@@ -158,11 +204,14 @@ route_dec_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
       int stage = 0;
       uint32_t phase = 0, armed = 0, armed_parity = 0;
       bool ok = true;
+      for (int s = 0; s < prologue; ++s) { armed |= 1u << s; }
+      stage = prologue == p.stages ? 0 : prologue;
+      phase = prologue == p.stages ? 1u : 0u;
       for (int t = 0; t < n_tiles && ok; ++t) {
         const int tile = first_tile + t, row0 = tile * kDecBM, rows = min(kDecBM, hi - row0);
         // a tile of which only the first rows are wanted (the end of the CTA's last document) comes in 32-row boxes
-        const int tail_boxes = rows <= kDecBM - kDecTailBox ? (rows + kDecTailBox - 1) / kDecTailBox : 0;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        const int tail_boxes = (t > 0 && rows <= kDecBM - kDecTailBox) ? (rows + kDecTailBox - 1) / kDecTailBox : 0;
+        for (int kb = (t == 0 ? prologue : 0); kb < p.k_blocks; ++kb) {
           if (!(ok = mbar_wait(&s_empty[stage], phase ^ 1u, abort_flag, p.status, 1))) break;
           unsigned char* sa = tiles + (size_t)stage * stage_bytes;
           if (tail_boxes == 0) {
@@ -178,6 +227,7 @@ route_dec_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
             }
           }
           tma_load_2d(sa + a_bytes, &tmap_q, kb * kDecBK, 0, &s_full[stage]);
+          TRACE(3);
           armed |= 1u << stage;
           armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
           if (++stage == p.stages) { stage = 0; phase ^= 1u; }
@@ -217,6 +267,7 @@ route_dec_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
           if (++stage == p.stages) { stage = 0; phase ^= 1u; }
         }
         if (ok) tc_commit(&s_acc_full[buf]);
+        TRACE(4);
       }
       tc_commit(&s_drain);
       const unsigned long long t0 = global_ns();
@@ -224,33 +275,53 @@ route_dec_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
     }
   } else {
     // ------------------------------- epilogue + selection (warps 0-7) ------------------
-    const int tid = threadIdx.x;                       // 0..255; thread tid < bn also owns sequence / table column tid
+    const int tid = threadIdx.x;                       // 0..255
     const int quarter = warp & 3, part = warp >> 2;    // TMEM lane quarter; share of the tile's columns
     DecEpiScratch& scr = s_epi[warp];
     for (int i = tid; i < p.cap * p.bn_pad; i += kDecEpiThreads) tbl[i] = p.min_key;
     if (tid < p.bn) s_bias[tid] = tid < p.n_seq ? p.row_bias[tid] : -INFINITY;
-    // this thread's sequence: its best `keep` documents so far, sorted, in registers (key 0 = empty slot)
+    // Selection: every table column (sequence) is walked by p.lists threads, thread (seq, phase) taking the rows
+    // phase, phase + lists, ...; each keeps the best `keep` documents it has seen, sorted, in registers
+    // (key 0 = empty slot).  With few sequences this spreads the insertion chains over all epilogue warps.
+    const int seq = tid % p.bn, phase = tid / p.bn;
+    const bool walker = phase < p.lists;
+    const bool owns_seq = walker && seq < p.n_seq;
     uint32_t lk[KMAX];
     int ld[KMAX];
 #pragma unroll
     for (int i = 0; i < KMAX; ++i) { lk[i] = 0u; ld[i] = 0; }
-    const bool owns_seq = tid < p.n_seq;
-    if (blockIdx.x == 0 && owns_seq) lk[0] = p.min_key;   // column 0: the dummy document, scored finfo.min like every untouched column
+    if (blockIdx.x == 0 && owns_seq && phase == 0) lk[0] = p.min_key;   // column 0: the dummy document, scored finfo.min like every untouched column
     epi_barrier();
-    int seg_base = lo < hi ? p.chunk_doc[lo] : 0;          // document id of table row 0
+    const int doc_lo = owns ? p.chunk_doc[lo] : 0;         // the first document of this CTA
+    int seg_base = doc_lo;                                 // document id of table row 0
     bool carried = false;                                  // row 0 holds the partial maxima of a document that continues
 
-    bool ok = true;
-    for (int t = 0; t < n_tiles && ok; ++t) {
+    // chunk -> document ids of a tile, requested one tile ahead (the loads have a tile's time to arrive)
+    struct TileIds { int doc, last_doc, next_doc; bool mine, any_mine; };
+    auto load_ids = [&](int t) {
+      TileIds r;
       const int row0 = (first_tile + t) * kDecBM;
       const int chunk = row0 + quarter * 32 + lane;
-      const bool mine = chunk >= lo && chunk < hi;        // rows before lo belong to the previous CTA's last document
+      r.mine = owns && t < n_tiles && chunk >= lo && chunk < hi;   // rows before lo belong to the previous CTA's last document
       const int last_chunk = min(row0 + kDecBM, hi) - 1;
-      const int last_doc = p.chunk_doc[last_chunk];
-      const int next_doc = last_chunk + 1 < hi ? p.chunk_doc[last_chunk + 1] : -1;   // first document of the next tile
+      r.any_mine = owns && t < n_tiles && last_chunk >= lo;        // false: the whole tile belongs to the previous CTA
+      r.last_doc = r.any_mine ? p.chunk_doc[last_chunk] : 0;
+      r.next_doc = r.any_mine && last_chunk + 1 < hi ? p.chunk_doc[last_chunk + 1] : -1;   // first document of the next tile
+      r.doc = r.mine ? p.chunk_doc[chunk] : -1 - lane;
+      return r;
+    };
+    TileIds nxt = load_ids(0);
+    const uint32_t walkers = __ballot_sync(0xffffffffu, walker);   // lanes of this warp that walk a column
+
+    bool alive = true;       // false once a wait ran out: the remaining tiles only keep the barriers in step
+    for (int t = 0; t < n_tiles; ++t) {
+      const TileIds cur = nxt;
+      nxt = load_ids(t + 1);
+      const int last_doc = cur.last_doc, next_doc = cur.next_doc;
+      const bool any_mine = cur.any_mine;
       // runs of lanes that hold chunks of one document
-      int doc = mine ? p.chunk_doc[chunk] : -1 - lane;
-      if (mine && (doc < 1 || doc > p.n_docs || (unsigned)(doc - seg_base) >= (unsigned)p.cap)) {
+      int doc = cur.doc;
+      if (cur.mine && (doc < 1 || doc > p.n_docs || (unsigned)(doc - seg_base) >= (unsigned)p.cap)) {
         if (part == 0) atomicAdd(p.status + 2, 1);      // an id outside the table: counted, never used as a row
         doc = -1 - lane;
       }
@@ -265,64 +336,104 @@ route_dec_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
       __syncwarp();
       const int buf = t & 1;
       const uint32_t acc_phase = (uint32_t)((t >> 1) & 1);
-      ok = mbar_wait(&s_acc_full[buf], acc_phase, abort_flag, p.status, 4);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * kDecMaxBN;
-      const int n_items = n_seg * 16;
-      for (int c0 = part * 16; c0 < p.bn; c0 += 16 * (kDecEpiWarps / 4)) {
-        uint32_t r[16];
-        tmem_ld16(taddr + c0, r);
-        tmem_ld_wait();
+#ifdef MSA_ROUTE_DEC_TRACE
+      const unsigned long long tw0 = global_ns();
+#endif
+      if (alive) alive = mbar_wait(&s_acc_full[buf], acc_phase, abort_flag, p.status, 4);
+#ifdef MSA_ROUTE_DEC_TRACE
+      if (tid == 0) { TRACE_ADD(9, global_ns() - tw0); if (t == 0) TRACE(5); TRACE(6); }
+#endif
+      alive = __all_sync(0xffffffffu, alive);
+      if (alive) {
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * kDecMaxBN;
+        const int n_items = n_seg * 16;
+        for (int c0 = part * 16; c0 < p.bn; c0 += 16 * (kDecEpiWarps / 4)) {
+          uint32_t r[16];
+          tmem_ld16(taddr + c0, r);
+          tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 16; ++j) scr.xpose[j][lane] = __uint_as_float(r[j]) + s_bias[c0 + j];
-        __syncwarp();
-        // (document, column) pairs dealt over the lanes: max over the document's chunks, one shared-memory atomic
-        for (int item = lane; item < n_items; item += 32) {
-          const DecSeg e = scr.seg[item >> 4];
-          const int j = item & 15, seq = c0 + j;
-          if (e.doc > 0 && seq < p.n_seq) {
-            float m = scr.xpose[j][e.start];
-            for (int u = 1; u < e.len; ++u) m = fmaxf(m, scr.xpose[j][e.start + u]);
-            atomicMax(tbl + (size_t)(e.doc - seg_base) * p.bn_pad + seq, float_to_key(m * p.alpha));
+          for (int j = 0; j < 16; ++j) scr.xpose[j][lane] = __uint_as_float(r[j]) + s_bias[c0 + j];
+          __syncwarp();
+          // (document, column) pairs dealt over the lanes: max over the document's chunks, one shared-memory atomic
+          for (int item = lane; item < n_items; item += 32) {
+            const DecSeg e = scr.seg[item >> 4];
+            const int j = item & 15, col = c0 + j;
+            if (e.doc > 0 && col < p.n_seq) {
+              float m = scr.xpose[j][e.start];
+#pragma unroll 8
+              for (int u = 1; u < e.len; ++u) m = fmaxf(m, scr.xpose[j][e.start + u]);   // independent loads
+              atomicMax(tbl + (size_t)(e.doc - seg_base) * p.bn_pad + col, float_to_key(m * p.alpha));
+            }
           }
+          __syncwarp();
         }
+        tc_fence_before();
         __syncwarp();
+        if (lane == 0) mbar_arrive(&s_acc_empty[buf]);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_acc_empty[buf]);
 
-      // ---- walk the tile's finished documents: thread = sequence, rows = documents
+      // ---- walk the tile's finished documents
       epi_barrier();                                     // every warp's table updates of this tile are in
-      const int n_rows = max(carried ? 1 : 0, min(min(last_doc, p.n_docs) - seg_base + 1, p.cap));
+      const int n_rows = any_mine ? max(carried ? 1 : 0, min(min(last_doc, p.n_docs) - seg_base + 1, p.cap)) : 0;
       const bool open = n_rows >= 1 && next_doc == last_doc && last_doc - seg_base == n_rows - 1;   // the last row's document continues
       const int n_done = open ? n_rows - 1 : n_rows;
-      const uint32_t walkers = __ballot_sync(0xffffffffu, tid < p.bn);   // lanes of this warp that own a table column
-      if (tid < p.bn) {
-        for (int r = 0; r < n_done; ++r) {
-          const uint32_t key = tbl[(size_t)r * p.bn_pad + tid];
-          tbl[(size_t)r * p.bn_pad + tid] = p.min_key;
-          // the whole warp takes the insertion chain or skips it together
-          if (__any_sync(walkers, owns_seq && key > lk[KMAX - 1])) {
-            if (owns_seq) list_insert<KMAX>(lk, ld, key, seg_base + r);
+      if (walker) {
+        for (int r0 = 0; r0 < n_done; r0 += p.lists) {   // the same trip count for every walker of the warp
+          const int r = r0 + phase;
+          uint32_t key = 0u;                             // 0 never enters a list
+          if (r < n_done) {
+            key = tbl[(size_t)r * p.bn_pad + seq];
+            tbl[(size_t)r * p.bn_pad + seq] = p.min_key;
           }
+          // the whole warp takes the insertion chain or skips it together
+          if (__any_sync(walkers, owns_seq && key > lk[KMAX - 1])) list_insert<KMAX>(lk, ld, key, seg_base + r);
         }
-        uint32_t keep_val = p.min_key;
-        if (open) {                                      // carry the open document's partial maxima to row 0
-          keep_val = tbl[(size_t)n_done * p.bn_pad + tid];
-          tbl[(size_t)n_done * p.bn_pad + tid] = p.min_key;
+        if (phase == 0) {
+          uint32_t keep_val = p.min_key;
+          if (open) {                                    // carry the open document's partial maxima to row 0
+            keep_val = tbl[(size_t)n_done * p.bn_pad + seq];
+            tbl[(size_t)n_done * p.bn_pad + seq] = p.min_key;
+          }
+          tbl[seq] = keep_val;
         }
-        tbl[tid] = keep_val;
       }
-      seg_base = open ? last_doc : (next_doc > 0 ? next_doc : seg_base);
+      seg_base = max(doc_lo, open ? last_doc : (next_doc > 0 ? next_doc : seg_base));
       carried = open;
       epi_barrier();                                     // the table is clean before the next tile is reduced into it
+      if (tid == 0) TRACE(7);
     }
-    if (ok && owns_seq) {
-      const long long n_in = (long long)gridDim.x * p.keep;
-      unsigned long long* dst = p.cand + (long long)tid * n_in + (long long)blockIdx.x * p.keep;
+
+    // ---- merge the lists of a sequence, pairwise: in round r the thread of phase p (p % 2^(r+1) == 0) takes the sorted
+    // list of phase p + 2^r from shared memory; the element-wise better of (mine[i], theirs[KMAX-1-i]) are the best
+    // KMAX of both as a bitonic sequence, which a merge network sorts in registers.  The operand ring is free now (the
+    // last accumulator was complete, so every copy has landed and every MMA has read its operands) and holds the lists,
+    // element i of thread t at [i][t].
+    unsigned long long* xchg = reinterpret_cast<unsigned long long*>(tiles);
+    for (int stride = 1; stride < p.lists; stride *= 2) {
+      const bool sender = walker && (phase & (2 * stride - 1)) == stride;
+      const bool receiver = walker && (phase & (2 * stride - 1)) == 0;
+      if (sender) {
+#pragma unroll
+        for (int i = 0; i < KMAX; ++i) xchg[i * kDecEpiThreads + tid] = ((unsigned long long)lk[i] << 32) | (uint32_t)ld[i];
+      }
+      epi_barrier();
+      if (receiver) {
+        const int partner = tid + stride * p.bn;
+#pragma unroll
+        for (int i = 0; i < KMAX; ++i) {
+          const unsigned long long o = xchg[(KMAX - 1 - i) * kDecEpiThreads + partner];
+          list_take_better(lk[i], ld[i], (uint32_t)(o >> 32), (int)(uint32_t)o);
+        }
+#pragma unroll
+        for (int span = KMAX / 2; span >= 1; span /= 2)
+#pragma unroll
+          for (int i = 0; i < KMAX; ++i)
+            if ((i & span) == 0) list_order_pair(lk[i], ld[i], lk[i + span], ld[i + span]);
+      }
+    }
+    if (alive && owns_seq && phase == 0) {
+      unsigned long long* dst = p.cand + ((long long)seq * gridDim.x + blockIdx.x) * p.keep;
 #pragma unroll
       for (int i = 0; i < KMAX; ++i)
         if (i < p.keep)
@@ -332,6 +443,7 @@ route_dec_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
 
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) TRACE(8);
   tc_fence_after();
   if (warp == kDecMmaWarp)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kDecTmemCols) : "memory");
@@ -343,10 +455,15 @@ static bool route_dec_plan(int bn, int keep, RouteDecParams* p, size_t* smem) {
   const int bn_pad = bn + 1;
   const size_t budget = 202 * 1024;   // dynamic part; the kernel's static arrays (epilogue scratch) take 23 KB more of the 227 KB
   const size_t tbl = ((size_t)kDecRows * bn_pad * 4 + 15) & ~(size_t)15;
+  int lists = 1;                                                           // walker threads per sequence: a power of two
+  int max_lists = 2;                                                       // every doubling costs a merge round at the end
+  if (const char* e = getenv("MSA_B200_DEC_LISTS")) max_lists = atoi(e);    // tuning knob
+  while (lists * 2 <= kDecEpiThreads / bn && lists * 2 <= max_lists) lists *= 2;
+  const size_t merge_bytes = (size_t)kDecEpiThreads * (keep <= 16 ? 16 : 32) * 8;   // the exchanged lists, in the freed ring
   for (int stages = kDecMaxStages; stages >= 3; --stages) {
     const size_t total = 1024 + stages * stage_bytes + tbl;
-    if (total <= budget) {
-      p->stages = stages; p->cap = kDecRows; p->bn = bn; p->bn_pad = bn_pad; p->keep = keep;
+    if (total <= budget && stages * stage_bytes >= merge_bytes) {
+      p->stages = stages; p->cap = kDecRows; p->bn = bn; p->bn_pad = bn_pad; p->keep = keep; p->lists = lists;
       *smem = total;
       return true;
     }
@@ -363,6 +480,11 @@ int launch_topk_from_candidates(const unsigned long long* cand, int n_in, int n_
                                 float* out_scores, int64_t* out_local, int64_t* out_global, cudaStream_t stream);
 }
 
+#ifdef MSA_ROUTE_DEC_TRACE
+extern "C" int msa_route_dec_trace(unsigned long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, g_dec_trace, sizeof(g_dec_trace)) == cudaSuccess ? 0 : 1;
+}
+#endif
 extern "C" int64_t msa_route_score_select_workspace_bytes(int32_t n_seq, int32_t k) {
   if (n_seq <= 0 || k <= 0) return 0;
   int n_sm = 0;
@@ -408,10 +530,6 @@ extern "C" int msa_route_score_select(const void* q_folded, const float* row_bia
   p.min_key = float_to_key(min_val); p.alpha = alpha; p.row_bias = row_bias; p.chunk_doc = chunk_doc;
   p.cand = (unsigned long long*)workspace; p.status = status;
 
-  if (const char* e = getenv("MSA_B200_ROUTE_STAGES")) {   // tuning knob: fewer operand stages than fit
-    const int v = atoi(e);
-    if (v >= 2 && v < p.stages) { smem -= (size_t)(p.stages - v) * ((size_t)kDecBM * kDecBK * 2 + (size_t)bn * kDecBK * 2); p.stages = v; }
-  }
   CUtensorMap map_k, map_k_tail, map_q;
   if (blocked) {
     MSA_OK_OR_RETURN(make_map_blocked(&map_k, rk, (uint64_t)n_tiles, (uint64_t)p.k_blocks));

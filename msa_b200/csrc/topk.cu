@@ -15,6 +15,7 @@ constexpr int kSortThreads = 256;
 constexpr int kMaxK = 1024;
 constexpr int kMinSlice = 2048;   // items per CTA at level 1 (power of two)
 constexpr int kMaxSlice = 8192;   // 64 KiB of shared memory
+constexpr int kSurvivorCap = 1024;   // items that may pass the threshold of the final level's selection
 
 __device__ __forceinline__ void bitonic_sort_desc(unsigned long long* s, int n2) {
   for (int size = 2; size <= n2; size <<= 1)
@@ -80,17 +81,25 @@ select_topk_kernel(const uint32_t* __restrict__ keys, long long table_stride, in
   __shared__ unsigned long long s_win[(kSortThreads / 32) * kSelectMaxK];
   __shared__ unsigned long long s_final[kSelectMaxK];
   __shared__ unsigned long long s_scratch[kSortThreads / 32][32];
-  const int row = blockIdx.y, sl = blockIdx.x, warp = threadIdx.x >> 5, n_warps = kSortThreads / 32;
+  __shared__ unsigned long long s_best[kSortThreads];
+  __shared__ unsigned long long s_surv[kSurvivorCap];
+  __shared__ unsigned long long s_threshold;
+  __shared__ int s_count;
+  const int row = blockIdx.y, sl = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = kSortThreads / 32;
   if (FROM_KEYS) {
     const int c0 = sl * slice;
     const uint32_t* src = keys + (long long)row * table_stride;
     for (int i = threadIdx.x; i < n2; i += kSortThreads) {
       const int c = c0 + i;
-      s_items[i] = (i < slice && c < n_cols) ? (((unsigned long long)src[c] << 32) | (0xffffffffu - (uint32_t)c)) : 0ull;
+      const unsigned long long v = (i < slice && c < n_cols) ? (((unsigned long long)src[c] << 32) | (0xffffffffu - (uint32_t)c)) : 0ull;
+      s_items[i] = v;
     }
   } else {
     const unsigned long long* src = cand + (long long)row * n_in;
-    for (int i = threadIdx.x; i < n2; i += kSortThreads) s_items[i] = i < n_in ? src[i] : 0ull;
+    for (int i = threadIdx.x; i < n2; i += kSortThreads) {
+      const unsigned long long v = i < n_in ? src[i] : 0ull;
+      s_items[i] = v;
+    }
   }
   __syncthreads();
   auto cta_select = [&](int n_items) {   // best `keep` of s_items[0..n_items) -> s_final, in order
@@ -105,7 +114,52 @@ select_topk_kernel(const uint32_t* __restrict__ keys, long long table_stride, in
     }
     __syncthreads();
   };
-  cta_select(n2);
+  // Final level (one CTA per row, so latency counts, not instructions): the keep-th largest of the 256 per-thread
+  // maxima is a lower bound T of the keep-th largest item (keep items are >= T), so only items >= T can win.
+  // Typically a few dozen survive; they are ranked by counting.  (Level 1 runs hundreds of CTAs and keeps the
+  // warp-level selection, which executes far fewer instructions.)
+  bool done = false;
+  if (!FROM_KEYS && keep <= kSortThreads / 2) {
+    unsigned long long best = 0ull;
+    for (int i = threadIdx.x; i < n2; i += kSortThreads) best = s_items[i] > best ? s_items[i] : best;
+    s_best[threadIdx.x] = best;
+    if (threadIdx.x == 0) s_count = 0;
+    __syncthreads();
+    int rank = 0;
+#pragma unroll 8
+    for (int j = 0; j < kSortThreads; ++j) {
+      const unsigned long long o = s_best[j];
+      rank += (o > best || (o == best && j < (int)threadIdx.x)) ? 1 : 0;
+    }
+    if (rank == keep - 1) s_threshold = best;      // exactly one thread; 0 when fewer than keep threads hold an item
+    __syncthreads();
+    const unsigned long long threshold = s_threshold;
+    for (int i0 = 0; i0 < n2; i0 += kSortThreads) {
+      const int i = i0 + threadIdx.x;
+      const unsigned long long v = i < n2 ? s_items[i] : 0ull;
+      const bool take = v != 0ull && v >= threshold;
+      const uint32_t bal = __ballot_sync(0xffffffffu, take);
+      int base = 0;
+      if (lane == 0 && bal) base = atomicAdd(&s_count, __popc(bal));
+      base = __shfl_sync(0xffffffffu, base, 0);
+      const int pos = base + __popc(bal & ((1u << lane) - 1u));
+      if (take && pos < kSurvivorCap) s_surv[pos] = v;
+    }
+    __syncthreads();
+    const int n_c = s_count;
+    if (n_c <= kSurvivorCap) {      // (more survivors than the buffer holds: the general path below)
+      for (int c = threadIdx.x; c < n_c; c += kSortThreads) {
+        const unsigned long long mine = s_surv[c];
+        int r = 0;
+        for (int j = 0; j < n_c; ++j) r += s_surv[j] > mine ? 1 : 0;   // composite items are unique
+        if (r < keep) s_final[r] = mine;
+      }
+      for (int r = n_c + threadIdx.x; r < keep; r += kSortThreads) s_final[r] = 0ull;
+      __syncthreads();
+      done = true;
+    }
+  }
+  if (!done) cta_select(n2);
   if (cand_out) {
     unsigned long long* dst = cand_out + ((long long)row * gridDim.x + sl) * keep;
     for (int i = threadIdx.x; i < keep; i += kSortThreads) dst[i] = s_final[i];

@@ -105,7 +105,8 @@ class SparseDecodeModel:
         self.fused = dtype == torch.bfloat16 and s.head_dim == 128 and s.hidden % 2 == 0 and s.ffn % 2 == 0
         self._cos = torch.zeros((batch, 1, s.head_dim), dtype=dtype, device=device)
         self._sin = torch.zeros((batch, 1, s.head_dim), dtype=dtype, device=device)
-        self.probe = None  # set to a dict to collect per-layer CUDA events (eager profiling step)
+        self.probe = None  # set to a dict to collect per-layer CUDA events (a profiled step)
+        self.probe_external = False  # True: event-record nodes, readable after the replay of a graph that captured them
         # The cache layout [template | retrieved | local] gives every sequence exactly `retrieved_entries`
         # positions for fetched entries; a step whose winners hold fewer would leave the previous step's entries
         # in the tail of the segment.  The smallest count seen per router layer is tracked on the device and
@@ -119,10 +120,10 @@ class SparseDecodeModel:
         rot = torch.cat([-x[..., d // 2:], x[..., : d // 2]], dim=-1)
         return x * cos + rot * sin
 
-    def _mark(self, name, layer):
+    def _mark(self, name, layer, stream=None):
         if self.probe is not None:
-            e = torch.cuda.Event(enable_timing=True)
-            e.record()
+            e = torch.cuda.Event(enable_timing=True, external=self.probe_external)
+            e.record(stream if stream is not None else torch.cuda.current_stream(self.device))
             self.probe.setdefault(name, {})[layer] = e
 
     def _layers(self, x, pending, lo, hi, fetch_done):
@@ -134,6 +135,7 @@ class SparseDecodeModel:
         nq, nkv, d = s.n_q_heads, s.n_kv_heads, s.head_dim
         for l in range(lo, hi):
             p = self.layers[l]
+            self._mark("layer_start", l)
             if self.fused:
                 x, h = ops.add_rmsnorm(x, pending, p["w_in"], s.rms_eps)
             else:
@@ -166,15 +168,19 @@ class SparseDecodeModel:
                 after_attn.record(main)
                 self.fetch_stream.wait_event(after_attn)
                 with torch.cuda.stream(self.fetch_stream):
+                    self._mark("fetch_start", l, self.fetch_stream)
                     # the gather writes every sequence's entries into its own retrieved segment of the cache
                     n_sel = self.svc.fetch_into(local, rank, l, self.k_cache[l], self.v_cache[l], s.template_len,
                                                 self.retrieved, max_ctas=24)
                     torch.minimum(self._n_sel_min[l], n_sel.min(), out=self._n_sel_min[l])
                     for t_ in (local, rank, n_sel):
                         t_.record_stream(self.fetch_stream)
-                    done = torch.cuda.Event(enable_timing=self.probe is not None)
+                    done = torch.cuda.Event(enable_timing=self.probe is not None,
+                                            external=self.probe is not None and self.probe_external)
                     done.record(self.fetch_stream)
                     fetch_done.append(done)
+                    if self.probe is not None:
+                        self.probe.setdefault("fetch_end", {})[l] = done
             attn = self.attn_out @ p["w_o"]
             if self.fused:
                 x, h = ops.add_rmsnorm(x, attn, p["w_post"], s.rms_eps)
@@ -188,6 +194,7 @@ class SparseDecodeModel:
 
     def _front(self):
         """Embedding, rotary tables and the layers below the first router layer -> ``self._x_mid``."""
+        self._mark("front_start", 0)
         ang = self.positions.to(torch.float32).unsqueeze(-1) * self.inv_freq
         emb = torch.cat([ang, ang], dim=-1)
         self._cos.copy_(emb.cos().unsqueeze(1))
@@ -201,6 +208,7 @@ class SparseDecodeModel:
         """Router layers and everything above them, lm_head, greedy token, cache-length update."""
         s = self.s
         fetch_done = []
+        self._mark("back_start", 0)
         x, pending = self._layers(self._x_mid, self._pending_mid if self.split_layer > 0 else None, self.split_layer,
                                   s.num_layers, fetch_done)
         if self.fused:
@@ -235,7 +243,9 @@ class SparseDecodeModel:
         refreshes.  Call ``prime`` once before the first call.  One call = one token per sequence."""
         nxt = self._back()
         self._front()
+        self._mark("front_end", 0)
         torch.cuda.current_stream(self.device).wait_stream(self.fetch_stream)
+        self._mark("step_end", 0)
         return nxt
 
     def check_fetch_counts(self):

@@ -54,13 +54,27 @@ def balanced_bucket_partition(docs: Sequence[Document], n_buckets: int) -> List[
     return buckets
 
 
+# Set to a list to collect a (start, end) pair of timing events around every all-gather (a profiled step);
+# ``COLLECTIVE_PROBE_EXTERNAL`` makes them event-record nodes, so that they can be read after a CUDA-graph replay.
+COLLECTIVE_PROBE: Optional[list] = None
+COLLECTIVE_PROBE_EXTERNAL = False
+
+
 def all_gather_cat(t: torch.Tensor, world: int, group=None) -> torch.Tensor:
     """All-gather equal-shaped tensors along a new leading rank axis ``[W, ...]``."""
     out = torch.empty((world,) + tuple(t.shape), dtype=t.dtype, device=t.device)
     if world == 1:
         out[0].copy_(t)
-    else:
-        dist.all_gather_into_tensor(out.view(-1), t.contiguous().view(-1), group=group)
+        return out
+    probe = COLLECTIVE_PROBE
+    if probe is not None:
+        e0 = torch.cuda.Event(enable_timing=True, external=COLLECTIVE_PROBE_EXTERNAL)
+        e0.record()
+    dist.all_gather_into_tensor(out.view(-1), t.contiguous().view(-1), group=group)
+    if probe is not None:
+        e1 = torch.cuda.Event(enable_timing=True, external=COLLECTIVE_PROBE_EXTERNAL)
+        e1.record()
+        probe.append((e0, e1))
     return out
 
 
