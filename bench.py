@@ -1333,7 +1333,8 @@ def run_generate(args):
             "e2e": {"value": g["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                     "note": "tokens are produced and consumed on the device; the only host traffic is the K/V fetch",
                     "host_to_device_fetch_bytes_per_step": 18 * batch_total * TOP_K * CHUNKS_PER_DOC * 2 * HKV * D * 2},
-            "per_layer": g["per_layer"], "fetch": g["fetch"], "dense_weight_bytes_per_step": g["dense_weight_bytes_per_step"],
+            "per_layer": g["per_layer"], "fetch": g["fetch"], "timeline": g["timeline"],
+            "dense_weight_bytes_per_step": g["dense_weight_bytes_per_step"],
             "clocks": g["clocks"], "gpu_launches": g["gpu_launches"], "last_tokens": g["last_tokens"]}), flush=True)
     if world > 1:
         # graphs that captured NCCL kernels were alive in this process: leave without tearing the

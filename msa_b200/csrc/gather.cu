@@ -5,6 +5,8 @@
 // the device-visible mapping with 16-byte loads (PCIe reads, no staging copy, no host
 // thread involved) and scatters it into the head-major [Hkv, entries, D] layout the
 // attention path consumes.  Bound by PCIe bandwidth: 2*chunks*Hkv*D*e bytes per document.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace msa {
@@ -137,6 +139,27 @@ gather_kernel(const int64_t* __restrict__ plan, int n_items, int n_kv_heads, int
 
 using namespace msa;
 
+// The plan and gather kernels run on a side stream beside kernels that need almost all of an SM's shared memory
+// (the persistent routing kernels).  A kernel with little shared memory of its own leaves the SM configured for a
+// large L1, and a CTA that needs 200 KB cannot join it there until the SM has drained: measured on B200, a 3.2 GB
+// routing launch took 758 us instead of 461 us next to a 24-CTA gather, because the routing CTAs of the occupied
+// SMs started only when the first wave had ended.  Asking for the largest shared-memory carve-out keeps those SMs
+// open (507 us).
+static int prefer_shared_carveout() {
+  static bool done[kMaxDevices] = {};
+  int device = 0;
+  MSA_OK_OR_RETURN(current_device(&device));
+  if (done[device] || getenv("MSA_B200_GATHER_DEFAULT_CARVEOUT")) return MSA_OK;
+  MSA_CUDA_OK(cudaFuncSetAttribute(gather_kernel<__nv_bfloat16>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                   cudaSharedmemCarveoutMaxShared));
+  MSA_CUDA_OK(cudaFuncSetAttribute(gather_kernel<float>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                   cudaSharedmemCarveoutMaxShared));
+  MSA_CUDA_OK(cudaFuncSetAttribute(gather_plan_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                   cudaSharedmemCarveoutMaxShared));
+  done[device] = true;
+  return MSA_OK;
+}
+
 extern "C" int msa_gather_plan(const int64_t* sel_local, const int32_t* sel_rank, int32_t n_seq, int32_t k,
                                int32_t world, const int64_t* shard_doc_base, int64_t n_dir_rows,
                                const int64_t* doc_chunk_offset, const int32_t* doc_chunk_len,
@@ -151,6 +174,7 @@ extern "C" int msa_gather_plan(const int64_t* sel_local, const int32_t* sel_rank
               (long long)n_dir_rows, world);
   MSA_REQUIRE(chunk_bytes > 0 && chunk_bytes % 16 == 0, "gather_plan: chunk_bytes must be a multiple of 16");
   MSA_REQUIRE(sample_stride >= 0, "gather_plan: sample_stride must not be negative");
+  MSA_OK_OR_RETURN(prefer_shared_carveout());
   gather_plan_kernel<<<1, kPlanThreads, 0, (cudaStream_t)stream>>>(
       sel_local, sel_rank, n_seq, k, world, shard_doc_base, n_dir_rows, doc_chunk_offset, doc_chunk_len, shard_kv_base,
       chunk_bytes, sample_stride, plan, n_sel, total, total_host_mapped, status);
@@ -174,6 +198,7 @@ extern "C" int msa_gather_run(const int64_t* plan, int32_t n_items, int32_t dtyp
               "gather_run: rows must be 16-byte multiples");
   if (n_items == 0 || out_entries == 0) return MSA_OK;
   MSA_REQUIRE(out_k && out_v && aligned16(out_k) && aligned16(out_v), "gather_run: bad output pointers");
+  MSA_OK_OR_RETURN(prefer_shared_carveout());
   if (dtype == MSA_BF16)
     gather_kernel<__nv_bfloat16><<<grid, kGatherThreads, 0, (cudaStream_t)stream>>>(
         plan, n_items, n_kv_heads, head_dim, (__nv_bfloat16*)out_k, (__nv_bfloat16*)out_v, out_head_stride, out_entries,
