@@ -508,6 +508,126 @@ def _rank_main(rank, world, ref_path, payload, ret):
     dist.destroy_process_group()
 
 
+def gen_front_end(ref_path):
+    """Engine request preparation (``MSAEngine._prepare_template`` / ``_apply_template`` / ``_apply_template_regenerate``
+    / ``generate``, src/msa_service.py:1703-1906) and the Memory-Interleave loop (``MSAGenerationMixin._sample``,
+    src/msa/generate.py:23-354), both run from the reference's own code with a character tokenizer and a scripted
+    model (tests/fake_text.py).  Stored as JSON: what each GPU would be sent, and every forward call the loop made."""
+    import json
+    import queue
+    import threading
+    sys.path.insert(0, os.path.join(HERE, "..", ".."))
+    from tests import fake_text as F
+    import src.msa_service as svc
+    from src.msa.generate import MSAGenerationMixin
+    from src.utils.tools import RequestLimiter
+
+    tok = F.CharTokenizer()
+    out = {"requests": [], "interleave": []}
+
+    # ---- engine: template + request preparation (no processes: the worker queues are plain queues)
+    def make_engine(world, top_k):
+        e = object.__new__(svc.MSAEngine)
+        e.generate_config = SimpleNamespace(world=world, devices=list(range(world)), template=F.TEMPLATE, max_batch_size=0,
+                                            max_seq_len=0, max_query_seq_len=0)
+        e.model_config = SimpleNamespace(doc_top_k=top_k)
+        e.tokenizer = tok
+        e.worker_qs = {g: queue.Queue() for g in range(world)}
+        e.limiter = RequestLimiter(4)
+        e.requests, e.msg_id = {}, 0
+        e.lock = threading.Lock()
+        e._prepare_template()
+        return e
+
+    regen = ("<regenerate>" + F.QUESTION_HEAD + "what is it" + "\nPlease return all documents related to the question\n"
+             "<|im_start|>[3]<|object_ref_end|>[3]. gamma doc\n<|object_ref_end|>[1]<|object_ref_end|>[1]. alpha doc\n<|object_ref_end|>")
+    for world, top_k, prompts in [(2, 16, ["short", "a longer prompt here", "mid one"]),
+                                  (1, 4, ["only one"]),
+                                  (4, 16, ["p%d " % i * (i + 1) for i in range(6)]),
+                                  (2, 16, ["plain question", regen])]:
+        e = make_engine(world, top_k)
+        e.generate(list(prompts), userdata="u", require_recall_topk=True, callback=lambda *a: None)
+        reqs = [e.worker_qs[g].get_nowait() for g in range(world)]
+        stub = e.requests[e.msg_id]
+        out["requests"].append({
+            "world": world, "top_k": top_k, "prompts": prompts, "nr_dummy": stub.nr_dummy,
+            "tail_input_ids": e.prompt_tail_input_ids, "tail_doc_ids": e.tail_doc_ids,
+            "per_gpu": [{"msg_id": r.msg_id, "seq_id": r.seq_id, "prompts": r.prompts, "input_ids": r.input_ids,
+                         "attention_mask": r.attention_mask, "doc_ids": r.doc_ids, "positions": r.positions,
+                         "require_recall_topk": r.require_recall_topk} for r in reqs]})
+
+    # ---- GenerateStub.respond: merge of the per-GPU responses
+    got = {}
+    stub = svc.GenerateStub(msg_id=7, userdata="ud", nr_dummy=1, responses=[], callback=lambda t, r, u: got.update(t=t, r=r, u=u))
+    stub.responses.append(svc.GenerateResponse(msg_id=7, seq_id=1, gpu_id=1, generated_texts=["c", "d"], recall_topk={18: [{"x": 3}]}))
+    stub.responses.append(svc.GenerateResponse(msg_id=7, seq_id=0, gpu_id=0, generated_texts=["a", "b"], recall_topk={18: [{"x": 1}], 19: [{"x": 2}]}))
+    stub.respond()
+    out["respond"] = {"texts": got["t"], "recall": {str(k): v for k, v in got["r"].items()}, "userdata": got["u"]}
+
+    # ---- the interleave loop, driven directly (``_sample`` with the helpers of GenerationMixin it calls replaced by
+    # the few lines they amount to for a decoder-only model with a custom cache)
+    class Scripted(MSAGenerationMixin):
+        def __init__(self, lm):
+            self.lm, self.config = lm, lm.config
+
+        def _has_unfinished_sequences(self, this_peer_finished, synced_gpus, device=None):
+            return not bool(this_peer_finished)
+
+        def _get_initial_cache_position(self, input_ids, model_kwargs):
+            model_kwargs["cache_position"] = torch.arange(input_ids.shape[1])
+            return model_kwargs
+
+        def _update_model_kwargs_for_generation(self, outputs, model_kwargs, is_encoder_decoder=False):
+            model_kwargs["past_key_values"] = outputs.past_key_values
+            am = model_kwargs["attention_mask"]
+            model_kwargs["attention_mask"] = torch.cat([am, am.new_ones((am.shape[0], 1))], dim=-1)
+            model_kwargs["cache_position"] = model_kwargs["cache_position"][-1:] + 1
+            return model_kwargs
+
+        def __call__(self, **kw):
+            kw.pop("return_dict", None)
+            return self.lm.forward(**kw)
+
+    for name, prompts, scripts in F.INTERLEAVE_CASES:
+        e = make_engine(1, 16)
+        e.generate(list(prompts), callback=lambda *a: None)
+        req = e.worker_qs[0].get_nowait()
+        lm = F.ScriptedLM(scripts, tok)
+        cache = F.StubCache()
+        cache.meta.update({"require_recall_topk": False, "qa_mode": True, "max_generate_tokens": 64, "tokenizer": tok,
+                           "idx_to_doc": F.IDX_TO_DOC, "pattern": r"\[(\d+)\]", "response_string": ["" for _ in prompts]})
+        for layer in range(lm.config.num_hidden_layers):
+            cache.record_kwargs(layer, {"stage": "prefill_stage2"})
+        gen_cfg = SimpleNamespace(_pad_token_tensor=torch.tensor(tok.pad_token_id), output_attentions=False,
+                                  output_hidden_states=False, output_scores=False, output_logits=False,
+                                  return_dict_in_generate=False, do_sample=False, prefill_chunk_size=None)
+        eos = torch.tensor([tok.eos_token_id])
+
+        class Eos:
+            eos_token_id = eos
+
+            def __call__(self, ids, scores):
+                return torch.isin(ids[:, -1], eos)
+
+        class Criteria(list):
+            def __call__(self, ids, scores):
+                return self[0](ids, scores)
+
+        seqs = Scripted(lm)._sample(
+            torch.LongTensor(req.input_ids), logits_processor=lambda ids, logits: logits, stopping_criteria=Criteria([Eos()]),
+            generation_config=gen_cfg, synced_gpus=False, streamer=None,
+            attention_mask=torch.LongTensor(req.attention_mask), doc_ids=torch.LongTensor(req.doc_ids), use_cache=True,
+            position_ids=torch.LongTensor(req.positions), past_key_values=cache)
+        out["interleave"].append({
+            "name": name, "prompts": prompts, "scripts": scripts, "sequences": seqs.tolist(),
+            "response_string": cache.meta["response_string"],
+            "calls": [{k: (v.tolist() if torch.is_tensor(v) else v) for k, v in c.items()} for c in lm.calls]})
+        print("interleave", name, "calls", len(lm.calls), "sequence length", seqs.shape[1], cache.meta["response_string"])
+    with open(os.path.join(HERE, "front_end.json"), "w") as f:
+        json.dump(out, f)
+    print("wrote front_end.json")
+
+
 def gen_doc_query(ref_path):
     import torch.multiprocessing as mp
     g = torch.Generator().manual_seed(404)
@@ -548,12 +668,17 @@ def gen_doc_query(ref_path):
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True)
+    ap.add_argument("--only", default="", help="run one generator only, e.g. front_end")
     a = ap.parse_args()
     svc, msa_layer, MSAConfig = import_reference(a.reference)
+    if a.only == "front_end":
+        gen_front_end(a.reference)
+        sys.exit(0)
     gen_pooling(svc, msa_layer)
     gen_layer(svc, msa_layer, MSAConfig)
     gen_routing(svc)
     gen_layer_e2e(svc, msa_layer, MSAConfig)
     gen_layer_attn128(svc, msa_layer, MSAConfig)
     gen_layer_decode_qa(svc, msa_layer, MSAConfig)
+    gen_front_end(a.reference)
     gen_doc_query(a.reference)
