@@ -1190,7 +1190,7 @@ def generate_measure(torch, dist, svc, world, rank, local_rank, dev, n_docs, doc
                 one_step()
             run = graph.replay
         except Exception as e:  # e.g. a collective that cannot be captured
-            mode, run, graph = f"eager ({type(e).__name__})", one_step, None
+            mode, run, graph = f"eager ({type(e).__name__}: {str(e)[:160]})", one_step, None
             torch.cuda.synchronize(dev)
         model.reset()
         model.prime()
@@ -1218,12 +1218,13 @@ def generate_measure(torch, dist, svc, world, rank, local_rank, dev, n_docs, doc
         sampler.start()
     ms_total, mode = timed_run(True)
     clocks = sampler.stop() if rank == 0 else None
-    ms_nofetch, _ = timed_run(False)       # same step without the host fetch: what the fetch may hide behind
+    ms_nofetch, mode_nofetch = timed_run(False)       # same step without the host fetch: what the fetch may hide behind
     ms_plain = timed_run(True, pipelined=False)[0] if full else None   # unrotated loop
     svc.check_status()
     model.check_fetch_counts()
     tokens_host = model.tokens.cpu()
     timeline = generate_timeline(torch, model, router_ids, dev)
+    timeline_nofetch = generate_timeline(torch, model, router_ids, dev, with_fetch=False) if full or world > 1 else None
     value = batch_total * new_tokens / (ms_total / 1e3)
     per_step_bytes = (sum(p_.numel() for l_ in model.layers for p_ in l_.values()) + model.lm_head.numel()) * 2
     out = {
@@ -1238,9 +1239,11 @@ def generate_measure(torch, dist, svc, world, rank, local_rank, dev, n_docs, doc
                   "ms_per_step_unrotated_loop": None if ms_plain is None else ms_plain / new_tokens,
                   "loop": "rotated to start at the first router layer: layers 18-35 of step t, sampling, layers 0-17 "
                           "of step t+1; the fetch issued in step t is needed by layer 18 of step t+1",
+                  "launch_without_fetch": mode_nofetch,
                   "exposed_ms_per_step": max(0.0, (ms_total - ms_nofetch) / new_tokens),
                   "pcie_bytes_per_step_per_gpu": 18 * b * TOP_K * CHUNKS_PER_DOC * 2 * HKV * D * 2},
-        "timeline": timeline, "dense_weight_bytes_per_step": per_step_bytes, "clocks": clocks,
+        "timeline": timeline, "timeline_without_fetch": timeline_nofetch,
+        "dense_weight_bytes_per_step": per_step_bytes, "clocks": clocks,
         # this package's kernels per step: per layer add+norm x2, q/k norm+rope, decode attention (+ combine),
         # SiLU*up; per router layer fold, table fill, scoring, top-k x2, merge, gather plan, gather; final norm
         "gpu_launches": new_tokens * (36 * 5 + 18 * 8 + 1), "last_tokens": tokens_host[:4].tolist()}
@@ -1249,13 +1252,13 @@ def generate_measure(torch, dist, svc, world, rank, local_rank, dev, n_docs, doc
     return out
 
 
-def generate_timeline(torch, model, router_ids, dev):
+def generate_timeline(torch, model, router_ids, dev, with_fetch=True):
     """Where one config-5 decode step spends its time: the rotated step captured in a CUDA graph WITH event-record
     nodes (external events) on the main and the fetch stream and around every all-gather, replayed, and read back.
     The main stream is serial, so its spans add up; the fetch stream runs beside it."""
     import msa_b200.service as S
     try:
-        model.fetch_enabled = True
+        model.fetch_enabled = with_fetch
         model.reset()
         model.prime()
         model.probe, model.probe_external = {}, True
@@ -1334,6 +1337,7 @@ def run_generate(args):
                     "note": "tokens are produced and consumed on the device; the only host traffic is the K/V fetch",
                     "host_to_device_fetch_bytes_per_step": 18 * batch_total * TOP_K * CHUNKS_PER_DOC * 2 * HKV * D * 2},
             "per_layer": g["per_layer"], "fetch": g["fetch"], "timeline": g["timeline"],
+            "timeline_without_fetch": g["timeline_without_fetch"],
             "dense_weight_bytes_per_step": g["dense_weight_bytes_per_step"],
             "clocks": g["clocks"], "gpu_launches": g["gpu_launches"], "last_tokens": g["last_tokens"]}), flush=True)
     if world > 1:
