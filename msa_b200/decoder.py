@@ -97,6 +97,7 @@ class SparseDecodeModel:
         self.attn_out = torch.empty((batch, s.n_q_heads * s.head_dim), dtype=dtype, device=device)
         self.fetch_stream = torch.cuda.Stream(device, priority=-1)   # its small copies go ahead of queued compute
         self.fetch_enabled = True
+        self._fetch_issued = False
         # the decode loop is cut at the first router layer (see step_pipelined)
         self.split_layer = min(self.router_layers) if (self.router_layers and service is not None) else s.num_layers
         self._x_mid = torch.zeros((batch, s.hidden), dtype=dtype, device=device)
@@ -179,6 +180,7 @@ class SparseDecodeModel:
                                             external=self.probe is not None and self.probe_external)
                     done.record(self.fetch_stream)
                     fetch_done.append(done)
+                    self._fetch_issued = True
                     if self.probe is not None:
                         self.probe.setdefault("fetch_end", {})[l] = done
             attn = self.attn_out @ p["w_o"]
@@ -229,7 +231,7 @@ class SparseDecodeModel:
         the refreshed retrieved segments are in place."""
         self._front()
         nxt = self._back()
-        torch.cuda.current_stream(self.device).wait_stream(self.fetch_stream)
+        self._join_fetch()
         return nxt
 
     def prime(self):
@@ -244,9 +246,17 @@ class SparseDecodeModel:
         nxt = self._back()
         self._front()
         self._mark("front_end", 0)
-        torch.cuda.current_stream(self.device).wait_stream(self.fetch_stream)
+        self._join_fetch()
         self._mark("step_end", 0)
         return nxt
+
+    def _join_fetch(self):
+        """The step ends when the refreshed segments are in place.  Only a step that issued a fetch waits: inside a
+        stream capture, waiting on the fetch stream when nothing was forked into it would tie the captured graph to
+        work outside the capture, which invalidates the capture."""
+        if self._fetch_issued:
+            torch.cuda.current_stream(self.device).wait_stream(self.fetch_stream)
+            self._fetch_issued = False
 
     def check_fetch_counts(self):
         """Raise if some step fetched fewer entries for a sequence than its retrieved segment holds (documents of
