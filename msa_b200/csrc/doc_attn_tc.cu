@@ -22,8 +22,14 @@
 // are loaded once the current item's last S has been issued.  Every mbarrier wait is bounded; on expiry the CTA
 // raises status[0], drains and frees TMEM.
 //
-// Bounds: 4*128*64*128 flops per tile on the tensor pipe (0.14 us per SM at the measured peak) and 8,192
-// exponentials (16 per clock per SM: 0.27 us), so the kernel is bound by the exponentials.
+// Bounds per 64-key tile and CTA: 524 tensor-pipe cycles by flops (S: 8 MMAs of 128x64x16, PV: 4 of 128x128x16), but
+// an S MMA reads 6 KB of operands from shared memory for 33 cycles of math, so at 128 B per clock it is bound by
+// the operand reads (48 cycles): about 640 cycles of the pipe per tile, and the pipe is shared, in order, by the two
+// CTAs of the SM.  The exponentials take 512 cycles of the SFU per warp and tile (1,024 with two CTAs).  Per-tile
+// timestamps show the MMA-issuing thread blocked on the pipe for about 1,200 of the 1,750 cycles a tile takes, while
+// the pipe counter reads 30 % (math cycles only): the kernel is bound by the pipe as this tiling uses it.  Wider S
+// tiles (128 keys per MMA, two query tiles per CTA in ping-pong) would halve the operand reads per flop; they need
+// all 512 TMEM columns, i.e. one CTA per SM.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -96,6 +102,36 @@ __device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t smem_addr, uint32
   return d;
 }
 
+// Packed and three-input arithmetic of sm_100: the softmax threads are bound by the number of instructions they issue
+// (one thread per row, one or two warps per scheduler), so two elements per FFMA / FADD and two per maximum count.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+__device__ __forceinline__ unsigned long long f32x2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f32x2_split(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma_f32x2(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ unsigned long long add_f32x2(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("add.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
 __device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -284,21 +320,35 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         tmem_ld32(s_addr, va);
         tmem_ld32(s_addr + 32, vb);
         tmem_ld_wait();
-        float mx = -INFINITY;
+        // row maximum: two elements per instruction, two independent chains per chunk
+        float mx = -INFINITY, mx2 = -INFINITY;
         if (d0 >= 32) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(va[i]));
+          for (int i = 0; i < 32; i += 4) {
+            mx = max3(mx, __uint_as_float(va[i]), __uint_as_float(va[i + 1]));
+            mx2 = max3(mx2, __uint_as_float(va[i + 2]), __uint_as_float(va[i + 3]));
+          }
         } else if (d0 == 0) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, i <= lane ? __uint_as_float(va[i]) : -INFINITY);
+          for (int i = 0; i < 32; i += 2) {
+            mx = fmaxf(mx, i <= lane ? __uint_as_float(va[i]) : -INFINITY);
+            mx2 = fmaxf(mx2, i + 1 <= lane ? __uint_as_float(va[i + 1]) : -INFINITY);
+          }
         }
         if (d1 >= 32) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(vb[i]));
+          for (int i = 0; i < 32; i += 4) {
+            mx = max3(mx, __uint_as_float(vb[i]), __uint_as_float(vb[i + 1]));
+            mx2 = max3(mx2, __uint_as_float(vb[i + 2]), __uint_as_float(vb[i + 3]));
+          }
         } else if (d1 == 0) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, i <= lane ? __uint_as_float(vb[i]) : -INFINITY);
+          for (int i = 0; i < 32; i += 2) {
+            mx = fmaxf(mx, i <= lane ? __uint_as_float(vb[i]) : -INFINITY);
+            mx2 = fmaxf(mx2, i + 1 <= lane ? __uint_as_float(vb[i + 1]) : -INFINITY);
+          }
         }
+        mx = fmaxf(mx, mx2);
         // advance the reference only when the maximum ran ahead by more than the step (always on the first tile;
         // never on a tile this warp does not see at all, where mx is -inf)
         const bool move = (mx - m_ref) * p.scale_log2e > kRescaleStep;
@@ -324,43 +374,43 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         }
         const float neg_m = -m_ref * p.scale_log2e;
         // exponentials, row sum, P as packed bf16 over the consumed columns of this buffer
-        float sum = 0.f;
+        unsigned long long sum_a = 0ull, sum_b = 0ull;       // two packed accumulators = four partial row sums
+        const unsigned long long scale2 = f32x2(p.scale_log2e, p.scale_log2e), neg_m2 = f32x2(neg_m, neg_m);
         uint32_t pk[16];
-        if (d0 >= 0) {
+        auto exps = [&](const uint32_t (&v)[32], int d) {
+          if (d < 0) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float e0 = exp2f(fmaf(__uint_as_float(va[i]), p.scale_log2e, neg_m));
-            float e1 = exp2f(fmaf(__uint_as_float(va[i + 1]), p.scale_log2e, neg_m));
-            if (d0 == 0) {
+            for (int i = 0; i < 16; ++i) pk[i] = 0u;
+            return;
+          }
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            float x0, x1, x2, x3;
+            f32x2_split(fma_f32x2(f32x2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), scale2, neg_m2), x0, x1);
+            f32x2_split(fma_f32x2(f32x2(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])), scale2, neg_m2), x2, x3);
+            float e0 = ex2_approx(x0), e1 = ex2_approx(x1), e2 = ex2_approx(x2), e3 = ex2_approx(x3);
+            if (d == 0) {                                      // the diagonal chunk: key i is visible to lanes >= i
               if (i > lane) e0 = 0.f;
               if (i + 1 > lane) e1 = 0.f;
+              if (i + 2 > lane) e2 = 0.f;
+              if (i + 3 > lane) e3 = 0.f;
             }
-            sum += e0 + e1;
+            sum_a = add_f32x2(sum_a, f32x2(e0, e1));
+            sum_b = add_f32x2(sum_b, f32x2(e2, e3));
             pk[i >> 1] = pack2_bf16(e0, e1);
+            pk[(i >> 1) + 1] = pack2_bf16(e2, e3);
           }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) pk[i] = 0u;
-        }
+        };
+        exps(va, d0);
         tmem_st16(s_addr, pk);
-        if (d1 >= 0) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float e0 = exp2f(fmaf(__uint_as_float(vb[i]), p.scale_log2e, neg_m));
-            float e1 = exp2f(fmaf(__uint_as_float(vb[i + 1]), p.scale_log2e, neg_m));
-            if (d1 == 0) {
-              if (i > lane) e0 = 0.f;
-              if (i + 1 > lane) e1 = 0.f;
-            }
-            sum += e0 + e1;
-            pk[i >> 1] = pack2_bf16(e0, e1);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) pk[i] = 0u;
-        }
+        exps(vb, d1);
         tmem_st16(s_addr + 16, pk);
-        l_run += sum;
+        {
+          float s0, s1, s2, s3;
+          f32x2_split(sum_a, s0, s1);
+          f32x2_split(sum_b, s2, s3);
+          l_run += (s0 + s1) + (s2 + s3);
+        }
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
