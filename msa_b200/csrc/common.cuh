@@ -124,4 +124,28 @@ template <> struct Elem<__nv_bfloat16> {
   __device__ static inline float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 };
 
+
+// Programmatic dependent launch (sm_90+): a kernel launched with `pdl` may start while the kernel before it in the
+// stream is still running; it must execute grid_dependency_wait() before it touches anything that kernel writes.
+// The earlier kernel lets dependents start early with grid_launch_dependents(); without that call they start when
+// it completes.  Both are no-ops in a kernel that was launched normally.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     bool pdl, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 }  // namespace msa

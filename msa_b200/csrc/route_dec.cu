@@ -174,9 +174,13 @@ route_dec_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
       mbar_expect_tx(&s_full[kb], stage_bytes);
       if (p.blocked) tma_load_4d(sa, &tmap_k, 0, 0, kb, first_tile, &s_full[kb]);
       else tma_load_2d(sa, &tmap_k, kb * kDecBK, first_tile * kDecBM, &s_full[kb]);
-      tma_load_2d(sa + a_bytes, &tmap_q, kb * kDecBK, 0, &s_full[kb]);
     }
     TRACE(2);
+    // Everything up to here reads only the bank.  The folded queries and their bias come from the kernel before this
+    // one in the stream; as a programmatic dependent this kernel may have started beside it.
+    grid_dependency_wait();
+    for (int kb = 0; kb < prologue; ++kb)
+      tma_load_2d(tiles + (size_t)kb * stage_bytes + a_bytes, &tmap_q, kb * kDecBK, 0, &s_full[kb]);
   }
   if (warp < 2) {                                    // two dependent rounds of global loads, beside the first requests
     const int c = (int)blockIdx.x + warp;            // warp 0: start of this share, warp 1: start of the next
@@ -184,6 +188,7 @@ route_dec_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
     const int v = snap_to_document(p.chunk_doc, (int)(a < p.n_chunks ? a : p.n_chunks), p.n_chunks, lane);
     if (lane == 0) *(warp == 0 ? &s_lo : &s_hi) = v;
   }
+  if (!(warp == kDecProducerWarp && lane == 0)) grid_dependency_wait();   // (the producer thread has waited above)
   if (warp == kDecMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
                  "r"(kDecTmemCols) : "memory");
@@ -404,6 +409,7 @@ route_dec_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_consta
       if (tid == 0) TRACE(7);
     }
 
+    if (tid == 0) grid_launch_dependents();      // the final selection may start launching; it waits for this grid to end
     // ---- merge the lists of a sequence, pairwise: in round r the thread of phase p (p % 2^(r+1) == 0) takes the sorted
     // list of phase p + 2^r from shared memory; the element-wise better of (mine[i], theirs[KMAX-1-i]) are the best
     // KMAX of both as a bitonic sequence, which a merge network sorts in registers.  The operand ring is free now (the
@@ -477,7 +483,8 @@ using namespace msa;
 
 namespace msa {
 int launch_topk_from_candidates(const unsigned long long* cand, int n_in, int n_seq, int k_eff, const int64_t* doc_ids_table,
-                                float* out_scores, int64_t* out_local, int64_t* out_global, cudaStream_t stream);
+                                float* out_scores, int64_t* out_local, int64_t* out_global, cudaStream_t stream,
+                                bool pdl = false);
 }
 
 #ifdef MSA_ROUTE_DEC_TRACE
@@ -541,14 +548,17 @@ extern "C" int msa_route_score_select(const void* q_folded, const float* row_bia
   MSA_OK_OR_RETURN(make_map(&map_q, q_folded, (uint64_t)n_seq, (uint64_t)kdim, (uint64_t)kdim, kDecBK, (uint32_t)bn));
   static DeviceSmem configured[2] = {};
   cudaStream_t st = (cudaStream_t)stream;
+  // programmatic dependent launches: this kernel sets itself up and requests its first key tile while the fold
+  // kernel before it still runs, and the final selection is resident when this kernel ends
+  static const bool pdl = getenv("MSA_B200_PDL") != nullptr;   // opt-in until measured
   if (k_eff <= 16) {
     MSA_OK_OR_RETURN(ensure_dynamic_smem(route_dec_kernel<16>, smem, configured[0]));
-    route_dec_kernel<16><<<grid, kDecThreads, smem, st>>>(map_k, map_k_tail, map_q, p);
+    MSA_CUDA_OK(launch_kernel_pdl(route_dec_kernel<16>, dim3(grid), dim3(kDecThreads), smem, st, pdl, map_k, map_k_tail, map_q, p));
   } else {
     MSA_OK_OR_RETURN(ensure_dynamic_smem(route_dec_kernel<32>, smem, configured[1]));
-    route_dec_kernel<32><<<grid, kDecThreads, smem, st>>>(map_k, map_k_tail, map_q, p);
+    MSA_CUDA_OK(launch_kernel_pdl(route_dec_kernel<32>, dim3(grid), dim3(kDecThreads), smem, st, pdl, map_k, map_k_tail, map_q, p));
   }
   MSA_LAUNCH_OK("route_dec_kernel");
   return launch_topk_from_candidates(p.cand, grid * k_eff, n_seq, k_eff, doc_ids_table, out_scores, out_local_ids,
-                                     out_global_ids, st);
+                                     out_global_ids, st, pdl);
 }

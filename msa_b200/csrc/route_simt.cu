@@ -18,6 +18,7 @@ __global__ void fold_kernel(const T* __restrict__ q, long long stride_b, long lo
                             int head_dim, int n_kv, int normalize, int query_reduce, int s_pad, T* __restrict__ folded,
                             float* __restrict__ row_bias) {
   constexpr int V = Elem<T>::kVec;
+  grid_launch_dependents();      // a routing kernel launched as a programmatic dependent may set itself up beside this one
   const int lph = head_dim / V;  // lanes per head (power of two <= 32)
   // the CTA is padded to whole warps; surplus threads shadow head 0 and store nothing
   const bool live = (int)threadIdx.x < n_kv * lph;

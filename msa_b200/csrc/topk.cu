@@ -1,11 +1,15 @@
 // Exact top-k over the document score table, and the cross-rank merge.
 //
-// Scores live in the table as order-preserving uint32 keys.  Selection is two levels of the
-// same kernel: every CTA sorts one slice of a row (composite 64-bit items: key high, inverted
-// column low, so equal scores order by ascending column) with a bitonic network in shared
-// memory and keeps the slice's best k; a second launch sorts the survivors of all slices of a
-// row and writes the result.  Rows are cut into slices so that even a handful of queries
-// (decode-time routing) spreads over the whole GPU.  One read of the table, k results written.
+// Scores live in the table as order-preserving uint32 keys; items are 64-bit composites (key high, inverted
+// column low), so equal scores order by ascending column and items are unique.  Selection has two levels: every
+// CTA of level 1 takes one slice of a row and keeps its best k, a second launch reduces the survivors of all
+// slices of a row and writes the result; rows are cut into slices so that even a handful of queries (decode-time
+// routing) spreads over the whole GPU.  One read of the table, k results written.
+//   k <= 64 (select_topk_kernel): no sort.  Level 1: per warp, threshold = k-th largest lane maximum, compaction of
+//   the survivors, ranks by counting (k <= 32) or k rounds of a warp arg-max; final level (one CTA per row, where
+//   latency counts): threshold = k-th largest of the CTA's 256 per-thread maxima, compaction, ranks by counting.
+//   larger k (sort_topk_kernel): a bitonic network over the slice in shared memory.
+// The final level also serves the fused decode-time routing kernel, whose CTAs write k candidates per sequence.
 #include "common.cuh"
 #include "topk_warp.cuh"
 
@@ -86,6 +90,7 @@ select_topk_kernel(const uint32_t* __restrict__ keys, long long table_stride, in
   __shared__ unsigned long long s_threshold;
   __shared__ int s_count;
   const int row = blockIdx.y, sl = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = kSortThreads / 32;
+  grid_dependency_wait();      // launched as a programmatic dependent, this kernel may be resident before its input is complete
   if (FROM_KEYS) {
     const int c0 = sl * slice;
     const uint32_t* src = keys + (long long)row * table_stride;
@@ -231,15 +236,15 @@ topk_merge_kernel(const float* __restrict__ cand_scores, const int64_t* __restri
 // 0 = empty) gathered from several producers; writes the best k_eff per row.  Used by the fused decode-time
 // routing kernel, whose CTAs are the producers.
 int launch_topk_from_candidates(const unsigned long long* cand, int n_in, int n_seq, int k_eff, const int64_t* doc_ids_table,
-                                float* out_scores, int64_t* out_local, int64_t* out_global, cudaStream_t stream) {
+                                float* out_scores, int64_t* out_local, int64_t* out_global, cudaStream_t stream, bool pdl) {
   MSA_REQUIRE(n_in >= 1 && n_in <= kMaxSlice && k_eff >= 1 && k_eff <= kSelectMaxK && n_seq >= 1 && n_seq <= 65535,
               "topk (candidates): bad sizes");
   const int n2 = pow2_ceil(n_in);
   static DeviceSmem configured{};
   MSA_OK_OR_RETURN(ensure_dynamic_smem(select_topk_kernel<false>, kMaxSlice * 8, configured));
-  select_topk_kernel<false><<<dim3(1, n_seq), kSortThreads, (size_t)n2 * 8, stream>>>(
-      nullptr, 0, 0, 0, cand, n_in, n2, k_eff, nullptr, doc_ids_table, out_scores, out_local, out_global);
-  MSA_LAUNCH_OK("select_topk_kernel (candidates)");
+  MSA_CUDA_OK(launch_kernel_pdl(select_topk_kernel<false>, dim3(1, n_seq), dim3(kSortThreads), (size_t)n2 * 8, stream, pdl,
+                                (const uint32_t*)nullptr, 0ll, 0, 0, cand, n_in, n2, k_eff, (unsigned long long*)nullptr,
+                                doc_ids_table, out_scores, out_local, out_global));
   return MSA_OK;
 }
 

@@ -258,6 +258,36 @@ def test_route_score_select_equals_table_path(ops, case):
     check_topk(table_ref.clamp_min(torch.finfo(torch.bfloat16).min)[live], s[live], l[live], k, tol=1e-3)
 
 
+def test_route_score_select_right_behind_the_fold(ops):
+    """The fused routing kernel is launched as a programmatic dependent of the kernel before it and starts while
+    that kernel (normally the fold) still runs; it must not read the folded queries before they are written.  New
+    queries every iteration, fold and routing back to back with no synchronisation in between, buffers recycled by
+    the allocator: every result must match the table path on the same queries."""
+    b, n_docs, k = 32, 4000, 16
+    chunks = ragged_docs(n_docs, 4, 8, seed=3)
+    rk, pool_ids = make_bank(chunks, dtype=torch.bfloat16, seed=4)
+    rk_d, cd = rk.to(DEV), pool_ids.to(torch.int32).to(DEV)
+    blocked = ops.block_router_keys(rk_d)
+    mask = torch.ones(b, 1, dtype=torch.bool, device=DEV)
+    g = torch.Generator(device=DEV)
+    g.manual_seed(11)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    qs, outs = [], []
+    for _ in range(24):
+        q = torch.nn.functional.normalize(torch.randn(b, 32, 1, 128, generator=g, device=DEV), dim=-1).to(torch.bfloat16)
+        qf, bias, _ = ops.fold_queries(q, mask, 4)
+        outs.append(ops.route_score_select(qf, bias, b, blocked, cd, n_docs, 1.0 / 32, k, status=status, blocked=True))
+        qs.append(q)
+        del qf, bias
+    torch.cuda.synchronize()
+    assert status.cpu().tolist() == [0, 0, 0, 0]
+    for q, (s, l, _) in zip(qs, outs):
+        qf, bias, s_pad = ops.fold_queries(q, mask, 4)
+        keys, _ = ops.route_scores(qf, bias, b, s_pad, rk_d, cd, n_docs, alpha=1.0 / 32)
+        ref_s, ref_l, _ = ops.topk_select(keys, k)
+        assert torch.equal(s, ref_s) and torch.equal(l, ref_l)
+
+
 def test_route_score_select_through_memory_and_bounds(ops):
     """Memory.score_folded takes the fused path for one-token queries (same winners as with the path switched
     off), and chunk ids outside 1..n_docs are skipped and counted instead of being used as table rows."""
