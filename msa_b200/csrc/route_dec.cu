@@ -550,7 +550,7 @@ extern "C" int msa_route_score_select(const void* q_folded, const float* row_bia
   cudaStream_t st = (cudaStream_t)stream;
   // programmatic dependent launches: this kernel sets itself up and requests its first key tile while the fold
   // kernel before it still runs, and the final selection is resident when this kernel ends
-  static const bool pdl = getenv("MSA_B200_PDL") != nullptr;   // opt-in until measured
+  static const bool pdl = getenv("MSA_B200_NO_PDL") == nullptr;   // measured: 84.6 -> 81.5 us per layer-step at 32 sequences
   if (k_eff <= 16) {
     MSA_OK_OR_RETURN(ensure_dynamic_smem(route_dec_kernel<16>, smem, configured[0]));
     MSA_CUDA_OK(launch_kernel_pdl(route_dec_kernel<16>, dim3(grid), dim3(kDecThreads), smem, st, pdl, map_k, map_k_tail, map_q, p));

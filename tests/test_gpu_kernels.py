@@ -177,6 +177,7 @@ ROUTE_SHAPES = [
     (5, 7, 4, 40, (1, 3), 8),          # short query padded to 16 rows
     (2, 64, 1, 2000, (8, 8), 16),      # benchmark config 1 shape (G = 1), 16,000 chunks
     (6, 128, 4, 2600, (1, 16), 32),    # many tiles per CTA: exercises the ring and both accumulators
+    (112, 1, 4, 8000, (1, 9), 16),     # decode-time routing, more than 64 sequences, more than 2 tiles per SM
 ]
 
 
@@ -318,7 +319,8 @@ def test_route_score_select_through_memory_and_bounds(ops):
 
 
 @pytest.mark.parametrize("shape", [(32, 1, 4, 3000, (8, 8), 16), (4, 128, 4, 150, (1, 12), 16), (2, 300, 1, 64, (1, 20), 16),
-                                   (128, 1, 4, 333, (1, 9), 16), (3, 256, 4, 2600, (1, 16), 32)])
+                                   (128, 1, 4, 333, (1, 9), 16), (3, 256, 4, 2600, (1, 16), 32),
+                                   (128, 1, 4, 9001, (1, 9), 16)])
 def test_routing_over_tile_blocked_keys_is_bit_identical(ops, shape):
     """The tile-blocked key layout ([tiles][K blocks][128 chunks][64]) only changes where the bytes of a TMA box lie
     in memory: the score table must come out bit for bit as from the row-major layout (chunk counts that are not a

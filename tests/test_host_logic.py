@@ -47,6 +47,17 @@ def test_argument_errors_are_reported_before_any_launch():
     assert b"head_reduce" in lib.msa_last_error()
     assert lib.msa_route_reduce_chunks(None, 5, 1, 4, None, 2, 3, 0.0, None, 3, None, None) == -1
     assert b"chunk_reduce" in lib.msa_last_error()
+    # fused decode-time routing: shapes it does not take are refused with MSA_ERR_UNSUPPORTED before any launch
+    one = 1       # any non-null pointer value: nothing is dereferenced on these paths
+    unsupported = A.lib().msa_route_score_select(one, one, A.dtype_code(torch.float32), 4, one, 1024, 4096, 1024, one, 1.0, 8, -1e38,
+                                                 16, None, one, one, None, one, 1 << 20, 0, one, None)
+    assert unsupported not in (0, -1) and b"at most 128 sequences" in lib.msa_last_error()
+    assert lib.msa_route_score_select(one, one, A.dtype_code(torch.bfloat16), 200, one, 1024, 4096, 1024, one, 1.0, 8, -1e38,
+                                      16, None, one, one, None, one, 1 << 20, 0, one, None) == unsupported
+    assert lib.msa_route_score_select(one, one, A.dtype_code(torch.bfloat16), 4, one, 1024, 4096, 1024, one, 0.0, 8, -1e38,
+                                      16, None, one, one, None, one, 1 << 20, 0, one, None) == -1
+    assert b"alpha must be positive" in lib.msa_last_error()
+    assert lib.msa_router_keys_blocked_bytes(129, 1024) == 2 * 16 * 128 * 64 * 2
     with pytest.raises(A.MsaError, match="CUDA tensors"):
         from msa_b200 import ops
         ops.pool_chunks(torch.zeros(4, 8, 128), torch.tensor([0, 4], dtype=torch.int32))
