@@ -249,7 +249,10 @@ class MemorySparseAttention(Qwen3Attention):
         if store is None or cur_len + q_len > store[0].shape[2]:
             store = self._adopt_cache(cache_kwargs, q_len)
         k_store, v_store, kv_start, kv_len = store
-        if q_len == 1 and not cache.meta.get("qa_mode", False):
+        # one token per sequence, all of them real: the flash-decode kernel.  A caller that feeds masked single tokens
+        # (samples that wait in the interleave loop) says so in meta["step_all_valid"]; those steps, like qa_mode
+        # segments, go through the segment path, which stores only the unmasked tokens.
+        if q_len == 1 and not cache.meta.get("qa_mode", False) and cache.meta.get("step_all_valid", True):
             out = ops.sparse_decode_attn(query_states[:, :, 0], k_store, v_store, kv_len, key_states[:, :, 0],
                                          value_states[:, :, 0], kv_start=kv_start)
             attn_output = out.view(bsz, 1, n_heads * d)

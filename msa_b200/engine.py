@@ -215,14 +215,25 @@ class MSAEngine:
         self.stop_workers()
         return False
 
+    def _next_response(self):
+        """The next message of a service process; raises instead of waiting forever when one of them has died."""
+        while True:
+            try:
+                return self.response_queue.get(timeout=1.0)
+            except queue.Empty:
+                dead = [p.name for p in self.worker_processes if not p.is_alive()]
+                if dead:
+                    raise RuntimeError(f"service process(es) {dead} exited during start-up")
+
     def _wait_ready_signal(self):
         for _ in range(len(self.worker_qs)):
-            ProtocolConstants.expect(self.response_queue, MEMORY_WORKER_READY)
+            tag, _ = self._next_response()
+            assert tag == MEMORY_WORKER_READY, f"expect {MEMORY_WORKER_READY} but got {tag}"
 
     def _worker_all_gather(self, cmdname: str):
         responses = []
         while len(responses) < len(self.worker_qs):
-            rsp = self.response_queue.get()
+            rsp = self._next_response()
             assert rsp.name == cmdname, f"worker all gather got response {rsp.name} expect {cmdname}"
             responses.append(rsp)
         responses.sort(key=lambda r: r.gpu_id)
@@ -488,7 +499,9 @@ def service_generate(service, model, tokenizer, idx_to_doc, generate_config: Gen
         eos_token_ids=[eos] if isinstance(eos, int) else list(eos or []),
         pad_token_id=tokenizer.pad_token_id if tokenizer.pad_token_id is not None else 0, **create_generate_args(generate_config))
     texts = tokenizer.batch_decode(sequences, skip_special_token=True)
-    recall = ({layer: args["recall_topk"] for layer, args in cache.cache_kwargs.items() if "recall_topk" in args}
-              if req.require_recall_topk else None)
+    # the entries travel to the parent through a process queue: host tensors, not handles to this process's memory
+    to_host = lambda v: v.detach().cpu() if torch.is_tensor(v) else v
+    recall = ({layer: [{k: to_host(v) for k, v in entry.items()} for entry in args["recall_topk"]]
+               for layer, args in cache.cache_kwargs.items() if "recall_topk" in args} if req.require_recall_topk else None)
     return GenerateResponse(msg_id=req.msg_id, seq_id=req.seq_id, gpu_id=service.gpu_id, generated_texts=texts,
                             recall_topk=recall)

@@ -64,17 +64,21 @@ def interleave_generate(model, input_ids: torch.Tensor, attention_mask: torch.Te
     eos = torch.as_tensor(list(eos_token_ids), dtype=torch.long, device=dev)
     n_layers = model.config.num_hidden_layers
 
-    unfinished = torch.ones(bsz, dtype=torch.long, device=dev)
-    retrieval_end = torch.zeros(bsz, dtype=torch.bool, device=dev)     # the sample said <End-of-Retrieve>
-    round_end = torch.zeros(bsz, dtype=torch.bool, device=dev)         # the sample closed its list of this round
+    # per-sample state lives on the host: every step needs the new tokens there anyway (to decode them into text),
+    # so the flags cost no extra synchronisation and no swarm of one-element device kernels
+    unfinished = torch.ones(bsz, dtype=torch.long)
+    retrieval_end = torch.zeros(bsz, dtype=torch.bool)                  # the sample said <End-of-Retrieve>
+    round_end = torch.zeros(bsz, dtype=torch.bool)                      # the sample closed its list of this round
     inner = [""] * bsz                                                  # text since the last appended context
     all_input_str = [""] * bsz
     last_valid = input_ids[:, -1:].clone()
+    eos_host = eos.cpu()
     kw = {"attention_mask": attention_mask, "doc_ids": doc_ids, "position_ids": position_ids}
     hist = {}
     pos = None
     source_copied = has_stage3 = round_over = finished = False
     is_first = is_prefill = True
+    step_all_valid = False          # the first call is the prefill
     stage, cnt = 1, 0
 
     while not finished:
@@ -98,6 +102,8 @@ def interleave_generate(model, input_ids: torch.Tensor, attention_mask: torch.Te
         if round_over:
             break
 
+        # lets a decode branch pick its single-token kernel without looking at the mask on the device
+        meta["step_all_valid"] = step_all_valid
         out = model(input_ids=step_ids, attention_mask=am, position_ids=pos, doc_ids=kw["doc_ids"],
                     past_key_values=past_key_values, use_cache=True)
         is_prefill = is_first = False
@@ -108,6 +114,7 @@ def interleave_generate(model, input_ids: torch.Tensor, attention_mask: torch.Te
             next_tokens = torch.multinomial(probs, num_samples=1, generator=generator).squeeze(1)
         else:
             next_tokens = torch.argmax(scores, dim=-1)
+        next_tokens = next_tokens.cpu()
         if eos.numel():
             next_tokens = next_tokens * unfinished + pad_token_id * (1 - unfinished)
         new_text = tokenizer.batch_decode(next_tokens)
@@ -137,27 +144,28 @@ def interleave_generate(model, input_ids: torch.Tensor, attention_mask: torch.Te
             input_ids = src_ids
             kw["attention_mask"], kw["doc_ids"], kw["position_ids"] = src_mask, torch.zeros_like(src_ids), src_pos
             source_copied, finished, is_first = True, False, True
+            step_all_valid = False                                  # a multi-token, left-padded segment
             inner = [""] * bsz
             if stage == 2:
                 round_over, stage = True, 1
             else:
                 stage = 4
-            round_end = torch.zeros(bsz, dtype=torch.bool, device=dev)
+            round_end = torch.zeros(bsz, dtype=torch.bool)
         else:
             if eos.numel():
-                unfinished = unfinished & ~torch.isin(next_tokens, eos)
+                unfinished = unfinished & ~torch.isin(next_tokens, eos_host)
             finished = bool(unfinished.max() == 0)
-            input_ids = next_tokens[:, None]
+            input_ids = next_tokens[:, None].to(dev)
             kw["doc_ids"] = F.pad(kw["doc_ids"], (0, 1), value=-1)
-            kw["attention_mask"] = torch.ones(bsz, 1, dtype=torch.long, device=dev)
+            step_mask = torch.ones(bsz, 1, dtype=torch.long)
             if stage == 1:
-                for i in range(bsz):
-                    if retrieval_end[i] or round_end[i]:
-                        kw["attention_mask"][i, 0] = 0        # waits for the others: fed nothing, keeps its position
-                    else:
-                        last_valid[i, -1] = input_ids[i, -1]
+                waiting = retrieval_end | round_end               # waits for the others: fed nothing, keeps its position
+                step_mask[waiting, 0] = 0
+                last_valid = torch.where(waiting.to(dev).unsqueeze(1), last_valid, input_ids)
             else:
-                last_valid[:, -1] = input_ids[:, -1]
+                last_valid = input_ids.clone()
+            step_all_valid = bool(step_mask.min() == 1)
+            kw["attention_mask"] = step_mask.to(dev)
             for i in range(bsz):
                 response_string[i] += new_text[i]
                 inner[i] += new_text[i]

@@ -110,3 +110,20 @@ INTERLEAVE_CASES = [
     ("malformed_list", ["x", "y"],
      ["[3]oops<|object_ref_end|>   ", "[1]<|object_ref_end|>        "]),
 ]
+
+
+def factory(model_path, device):
+    """``MSA_B200_MODEL_FACTORY`` target for the engine's end-to-end test: a tiny seeded decoder stack of this package
+    (2 layers, router layer 1, head_dim 128, chunk 64) with the character tokenizer above."""
+    from msa_b200.configuration import MSAConfig
+    from msa_b200.model import MSAForCausalLM
+    cfg = MSAConfig(
+        msa_config=dict(router_layer_idx="1", aux_loss=False, aux_loss_method="INFONCE", decouple_router=True,
+                        top_k_docs=2, pooling_kernel_size=64, head_reduce_method="mean", query_reduce_method="max",
+                        chunk_reduce_method="max", decouple_pooling_mode="mean"),
+        hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=128, num_hidden_layers=2,
+        intermediate_size=128, vocab_size=VOCAB, max_position_embeddings=8192)
+    cfg._attn_implementation = "eager"
+    torch.manual_seed(4321)
+    model = MSAForCausalLM(cfg).to(torch.bfloat16).to(device).eval()
+    return model, CharTokenizer()
