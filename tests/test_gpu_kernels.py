@@ -218,6 +218,9 @@ FUSED_CASES = [
     (24, 30000, (1, 4), 16, []),        # documents that continue across tile and share borders
     (8, 6, (200, 400), 4, []),          # documents longer than a CTA's share of the tiles
     (48, 20000, (3, 3), 16, []),        # document starts never on a tile border after the first
+    (80, 20000, (3, 3), 16, [5]),       # more than 64 sequences
+    (128, 60000, (1, 1), 16, []),       # ... with a document per chunk, several tiles per CTA
+    (65, 7, (300, 900), 4, []),         # ... with documents longer than a CTA's share
 ]
 
 
