@@ -22,6 +22,7 @@ config 5 asks to time.)  KV layout per layer: ``[template t | retrieved k*c | lo
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from typing import List, Optional
 
@@ -98,6 +99,7 @@ class SparseDecodeModel:
         self.fetch_stream = torch.cuda.Stream(device, priority=-1)   # its small copies go ahead of queued compute
         self.fetch_enabled = True
         self._fetch_issued = False
+        self.gather_ctas = int(os.environ.get("MSA_B200_DECODE_GATHER_CTAS", "24"))   # CTAs of the host gather beside the step's kernels
         # the decode loop is cut at the first router layer (see step_pipelined)
         self.split_layer = min(self.router_layers) if (self.router_layers and service is not None) else s.num_layers
         self._x_mid = torch.zeros((batch, s.hidden), dtype=dtype, device=device)
@@ -172,7 +174,7 @@ class SparseDecodeModel:
                     self._mark("fetch_start", l, self.fetch_stream)
                     # the gather writes every sequence's entries into its own retrieved segment of the cache
                     n_sel = self.svc.fetch_into(local, rank, l, self.k_cache[l], self.v_cache[l], s.template_len,
-                                                self.retrieved, max_ctas=24)
+                                                self.retrieved, max_ctas=self.gather_ctas)
                     torch.minimum(self._n_sel_min[l], n_sel.min(), out=self._n_sel_min[l])
                     for t_ in (local, rank, n_sel):
                         t_.record_stream(self.fetch_stream)
