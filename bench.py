@@ -806,7 +806,7 @@ def build_service(torch, dist, args, world, rank, local_rank, dev, layers, tag):
         first = router_ids[0]
         for layer in router_ids:
             svc.blocks[layer].kv, svc.blocks[layer].kv_device_address = kv, kv.data_ptr()
-        if world > 1:
+        if world > 1 or os.environ.get("MSA_B200_BENCH_SHARED_BANK"):   # the env: the multi-rank bank format on one rank
             shm = "/dev/shm"
             need = c_local * 2 * HKV * D * 2
             st = os.statvfs(shm)

@@ -10,7 +10,7 @@ fused kernels; attention runs on this package's flash-decode kernel with
 in-place append, and the router layers route every step through ``MSAService``:
 
     route(step t, layer l)  ->  fetch of the winners' pooled K/V from the pinned host bank on a
-    side stream  ->  written into the "retrieved" segment of layer l's cache, where the attention
+    side stream, started with the scoring of the next router layer  ->  written into the "retrieved" segment of layer l's cache, where the attention
     of step t+1 reads it.
 
 So the host fetch never sits on the critical path: it overlaps the rest of the step, and with
@@ -99,6 +99,11 @@ class SparseDecodeModel:
         self.fetch_stream = torch.cuda.Stream(device, priority=-1)   # its small copies go ahead of queued compute
         self.fetch_enabled = True
         self._fetch_issued = False
+        # Where a router layer's host gather starts.  "routing": with the NEXT router layer's scoring kernel, which its
+        # zero-copy reads slow by a tenth; "dense": right after the layer's attention, beside the output / MLP GEMMs,
+        # which ran 2.1x slower while 24 CTAs of PCIe reads were in flight (1.3x beside 8 CTAs; 1.2x beside the same
+        # gather reading device memory).
+        self.fetch_beside = os.environ.get("MSA_B200_DECODE_FETCH_BESIDE", "routing")
         self.gather_ctas = int(os.environ.get("MSA_B200_DECODE_GATHER_CTAS", "24"))   # CTAs of the host gather beside the step's kernels
         # the decode loop is cut at the first router layer (see step_pipelined)
         self.split_layer = min(self.router_layers) if (self.router_layers and service is not None) else s.num_layers
@@ -136,6 +141,7 @@ class SparseDecodeModel:
         main = torch.cuda.current_stream(self.device)
         cos, sin = self._cos, self._sin
         nq, nkv, d = s.n_q_heads, s.n_kv_heads, s.head_dim
+        deferred = None
         for l in range(lo, hi):
             p = self.layers[l]
             self._mark("layer_start", l)
@@ -156,6 +162,9 @@ class SparseDecodeModel:
             routed = None
             if l in self.router_layers and self.svc is not None:
                 self._mark("route_start", l)
+                if deferred is not None:        # the previous router layer's fetch starts with this layer's routing
+                    self._issue_fetch(*deferred, fetch_done)
+                    deferred = None
                 rq = qkv[:, (nq + 2 * nkv) * d:].view(B, nq, 1, d)      # L2-normalised inside the fold kernel
                 routed = self.svc.route(rq, self.query_mask, l, l2_normalize=True, all_valid=True)
                 self._mark("route_end", l)
@@ -164,27 +173,14 @@ class SparseDecodeModel:
                                    workspace=self.workspace, out=self.attn_out)
             self._mark("attn_end", l)
             if routed is not None and self.fetch_enabled:
-                # fetch the winners' K/V on the side stream and refresh the retrieved segment; it may
-                # only be overwritten once this step's attention has read it
-                _, local, _, rank = routed
-                after_attn = torch.cuda.Event()
-                after_attn.record(main)
-                self.fetch_stream.wait_event(after_attn)
-                with torch.cuda.stream(self.fetch_stream):
-                    self._mark("fetch_start", l, self.fetch_stream)
-                    # the gather writes every sequence's entries into its own retrieved segment of the cache
-                    n_sel = self.svc.fetch_into(local, rank, l, self.k_cache[l], self.v_cache[l], s.template_len,
-                                                self.retrieved, max_ctas=self.gather_ctas)
-                    torch.minimum(self._n_sel_min[l], n_sel.min(), out=self._n_sel_min[l])
-                    for t_ in (local, rank, n_sel):
-                        t_.record_stream(self.fetch_stream)
-                    done = torch.cuda.Event(enable_timing=self.probe is not None,
-                                            external=self.probe is not None and self.probe_external)
-                    done.record(self.fetch_stream)
-                    fetch_done.append(done)
-                    self._fetch_issued = True
-                    if self.probe is not None:
-                        self.probe.setdefault("fetch_end", {})[l] = done
+                # the retrieved segment may only be overwritten once this step's attention has read it
+                if deferred is not None:
+                    self._issue_fetch(*deferred, fetch_done)
+                    deferred = None
+                if self.fetch_beside == "routing" and l + 1 < hi:
+                    deferred = (routed, l)
+                else:
+                    self._issue_fetch(routed, l, fetch_done)
             attn = self.attn_out @ p["w_o"]
             if self.fused:
                 x, h = ops.add_rmsnorm(x, attn, p["w_post"], s.rms_eps)
@@ -194,7 +190,33 @@ class SparseDecodeModel:
                 h = F.rms_norm(x, (s.hidden,), p["w_post"], s.rms_eps)
                 gu = h @ p["w_gate_up"]
                 pending = (F.silu(gu[:, : s.ffn]) * gu[:, s.ffn:]) @ p["w_down"]
+        if deferred is not None:
+            self._issue_fetch(*deferred, fetch_done)
         return x, pending
+
+    def _issue_fetch(self, routed, l, fetch_done):
+        """Fetch the winners' K/V of router layer ``l`` on the side stream, from this point of the main stream on,
+        and refresh the layer's retrieved segment."""
+        s = self.s
+        _, local, _, rank = routed
+        gate = torch.cuda.Event()
+        gate.record(torch.cuda.current_stream(self.device))
+        self.fetch_stream.wait_event(gate)
+        with torch.cuda.stream(self.fetch_stream):
+            self._mark("fetch_start", l, self.fetch_stream)
+            # the gather writes every sequence's entries into its own retrieved segment of the cache
+            n_sel = self.svc.fetch_into(local, rank, l, self.k_cache[l], self.v_cache[l], s.template_len,
+                                        self.retrieved, max_ctas=self.gather_ctas)
+            torch.minimum(self._n_sel_min[l], n_sel.min(), out=self._n_sel_min[l])
+            for t_ in (local, rank, n_sel):
+                t_.record_stream(self.fetch_stream)
+            done = torch.cuda.Event(enable_timing=self.probe is not None,
+                                    external=self.probe is not None and self.probe_external)
+            done.record(self.fetch_stream)
+            fetch_done.append(done)
+            self._fetch_issued = True
+            if self.probe is not None:
+                self.probe.setdefault("fetch_end", {})[l] = done
 
     def _front(self):
         """Embedding, rotary tables and the layers below the first router layer -> ``self._x_mid``."""
