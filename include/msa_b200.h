@@ -443,6 +443,24 @@ int msa_doc_attention_tc(const void* q, int64_t q_stride_b, int64_t q_stride_h, 
                          int32_t n_kv_heads, int32_t head_dim, int32_t dtype, float scale, void* out,
                          int32_t* status, void* stream);
 
+/* msa_sparse_prefill_attn_tc: msa_sparse_prefill_attn (same arguments, same result, rows of tokens that are not
+ * queries zero-filled) on the tcgen05 kernel of msa_doc_attention_tc, for the case that the valid tokens of every
+ * sequence are ONE run of consecutive tokens (q_tok[b, r] = q_tok[b, 0] + r for r < num_q[b]; the caller checks
+ * this: left- or right-padded segments are, tokens masked in the middle are not).  bf16, head_dim 128; q
+ * token-major or contiguous head-major; the stores contiguous [B, Hkv, store_len, D] whose positions outside a
+ * sequence's entries hold finite numbers (msa_assemble_context zero-fills them).  Replaces the attention call of
+ * src/msa/memory_sparse_attention.py:334-339 (stage 2, causal != 0) and :375-380 (causal == 0).
+ * status: int32[4], zeroed by the caller; status[0] != 0 after completion means a bounded barrier wait ran
+ * out inside the kernel (output invalid).
+ */
+int msa_sparse_prefill_attn_tc(const void* q, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                               const void* k_store, const void* v_store, int64_t store_stride_b,
+                               int64_t store_stride_h, int32_t store_len, const int32_t* kv_start,
+                               const int32_t* kv_len, const int32_t* q_tok, const int32_t* num_q, int32_t n_seq,
+                               int32_t seq_len, int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim,
+                               int32_t dtype, int32_t causal, float scale, void* out, int32_t* status,
+                               void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * Dense glue of a decode step (bf16).  No single reference function: they replace the chains of
  * elementwise torch kernels that transformers' Qwen3 modules issue between the GEMMs of a layer as

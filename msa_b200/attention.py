@@ -16,10 +16,12 @@ What runs where (every attention of the path is one of this package's kernels; n
   * stage 2: routing, merge and fetch happen inside ``memory_client.doc_query`` (this package's
     ``MSAService``); one kernel assembles [template | retrieved | query] into the left-padded
     compact cache (allocated with room to append in place) and the prefill attention kernel reads it
-    there (tensor cores for bf16 / head_dim 128, the general kernel otherwise);
+    there (bf16 / head_dim 128: the tcgen05 kernel when every sequence's question tokens are one run of
+    consecutive tokens, as left- or right-padded questions are, the mma.sync kernel otherwise; other
+    dtypes and head sizes: the general kernel);
   * decode: this package's flash-decode kernel, in-place append, no ``torch.cat`` / ``repeat_kv``;
     the multi-token, non-causal segments of ``qa_mode`` are appended by one kernel and attended by the
-    prefill kernel without its causal mask.
+    prefill kernels without their causal mask.
 The training forward (``_forward``) is out of scope and raises.
 """
 from __future__ import annotations
@@ -131,6 +133,23 @@ class MemorySparseAttention(Qwen3Attention):
             cache.meta["_msa_b200_segments"] = hit
         return hit[1], hit[2]
 
+    def _valid_runs(self, valid, cache):
+        """Device flags ``[2]`` int32: whether the valid tokens of every row are one run of consecutive tokens (what the
+        tcgen05 context kernel takes), and the status word of the earlier tensor-core attention launches.  The caller
+        reads them back together with whatever else it needs on the host."""
+        s = valid.shape[1]
+        idx = torch.arange(s, device=valid.device).unsqueeze(0)
+        first = torch.where(valid, idx, s).amin(dim=1)
+        last = torch.where(valid, idx, -1).amax(dim=1)
+        runs = (((last - first + 1) == valid.sum(dim=1)) | (last < 0)).all().to(torch.int32)
+        status = cache.meta.setdefault("_msa_b200_attn_status", torch.zeros(4, dtype=torch.int32, device=valid.device))
+        return torch.stack([runs, status[0]])
+
+    @staticmethod
+    def _check_attn_status(word):
+        if word != 0:
+            raise A.MsaError("a bounded barrier wait ran out inside doc_attn_tc_kernel (attention output invalid)")
+
     def _stage1(self, hidden_states, doc_ids, attention_mask, cache, query_states, key_states, value_states):
         """src/msa/memory_sparse_attention.py:137-243."""
         bsz, q_len, _ = hidden_states.shape
@@ -222,13 +241,22 @@ class MemorySparseAttention(Qwen3Attention):
         num_q = valid_q.sum(dim=1)
         t_len = template_k.shape[2]
         kv_lengths = t_len + n_sel + num_q
-        max_kv = int(kv_lengths.max())
+        tc = dtype == torch.bfloat16 and d == 128
+        if tc:   # one read-back for the cache size, the run check and the status of earlier launches
+            max_kv, runs, word = torch.cat([kv_lengths.max().reshape(1).to(torch.int32), self._valid_runs(valid_q, cache)]).tolist()
+            self._check_attn_status(word)
+            tc = bool(runs)
+        else:
+            max_kv = int(kv_lengths.max())
         reserve = int(cache.meta.get("max_generate_tokens", self.decode_reserve))
         k_store, v_store, kv_start, kv_len, q_tok, n_valid, _ = ops.assemble_context(
             template_k, template_v, final_k, None if final_v is None else final_v.to(device), n_sel, key_states,
             value_states, valid_q, max_kv, reserve)
         left_pad_mask = torch.arange(max_kv, device=device).unsqueeze(0) >= (max_kv - kv_lengths.unsqueeze(1))
-        attn_output = ops.sparse_prefill_attn(query_states, k_store, v_store, kv_start, kv_len, q_tok, n_valid, self.scaling)
+        # question tokens that form one run per sequence (left / right padding): tcgen05 kernel; else mma.sync
+        status = cache.meta["_msa_b200_attn_status"] if tc else None
+        attn_output = ops.sparse_prefill_attn(query_states, k_store, v_store, kv_start, kv_len, q_tok, n_valid, self.scaling,
+                                              q_runs=tc, status=status)
         cache_kwargs.update({
             "compacked_key_cache": k_store[:, :, :max_kv], "compacked_value_cache": v_store[:, :, :max_kv],
             "kv_lengths": kv_lengths, "attention_mask": left_pad_mask,
@@ -265,8 +293,15 @@ class MemorySparseAttention(Qwen3Attention):
             # valid entries stay one contiguous run), the prefill kernel attends without its causal mask.
             valid = attention_mask.reshape(bsz, q_len) == 1
             q_tok, num_q, _ = ops.append_segment(key_states, value_states, valid, k_store, v_store, kv_start, kv_len)
+            # segments of 16 tokens and more whose unmasked tokens form one run per sequence: tcgen05 kernel
+            tc = q_len >= 16 and query_states.dtype == torch.bfloat16 and d == 128
+            if tc:
+                runs, word = self._valid_runs(valid, cache).tolist()
+                self._check_attn_status(word)
+                tc = bool(runs)
+            status = cache.meta["_msa_b200_attn_status"] if tc else None
             attn_output = ops.sparse_prefill_attn(query_states, k_store, v_store, kv_start, kv_len, q_tok, num_q,
-                                                  self.scaling, causal=False)
+                                                  self.scaling, causal=False, q_runs=tc, status=status)
             pos = torch.arange(cur_len + q_len, device=k_store.device).unsqueeze(0)
             cache_kwargs["attention_mask"] = (pos >= kv_start.unsqueeze(1)) & (pos < (kv_start + kv_len).unsqueeze(1))
             cache_kwargs["kv_lengths"] = kv_len.to(cache_kwargs["kv_lengths"].dtype)

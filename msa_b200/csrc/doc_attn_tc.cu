@@ -51,6 +51,13 @@ constexpr float kRescaleStep = 8.f;                      // log2 units the row m
 struct DocAttnTcParams {
   const int32_t* token_index;   // flat position of every listed token; a segment's tokens are consecutive
   const int32_t* seg_off;
+  // context mode (q_tok != nullptr): segment = sequence b; its queries are the run of num_q[b] tokens that starts at
+  // token q_tok[b * S], its keys the kv_len[b] positions from kv_start[b] on of (b, head) in the K / V stores
+  const int32_t* q_tok;
+  const int32_t* num_q;
+  const int32_t* kv_start;
+  const int32_t* kv_len;
+  int causal;                   // context mode: bottom-right aligned causal mask, or every key visible
   int S, n_q_heads, n_kv_heads;
   int q_yb, q_yh, q_xh;         // q tile coordinates: y = b*q_yb + h*q_yh + s, x = h*q_xh + 64*block
   int k_yb, k_yh, k_xh;
@@ -142,27 +149,61 @@ __device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
 // n_q_heads + hq with x counting a document's row blocks from its last (longest) one: the fixed-stride walk
 // of the persistent CTAs then hands every CTA the same mix of long and short items, and the heads of a kv
 // group run side by side and share K / V through L2.  Item w of a document with fewer row blocks is skipped.
-struct AtItem { int len, r0, n_kt, hq, hk, tok0, b, s0; bool valid; };
+// A query row i of the segment sees key j iff j <= i + shift and j < n_keys.  Documents: shift 0, and keys past the
+// document's end sit above the diagonal of every valid row, so n_keys is left unbounded there.
+struct AtItem { int len, r0, n_kt, hq, hk, tok0, b, s0, k_s0, shift, n_keys, x; bool valid; };
+constexpr int kAtUnbounded = 1 << 29;
+template <bool CTX>
 __device__ __forceinline__ AtItem at_item(const DocAttnTcParams& p, long long w) {
   AtItem it;
-  const int x = (int)(w / p.n_sh);
+  it.x = (int)(w / p.n_sh);
   const long long sh = w % p.n_sh;
   it.hq = (int)(sh % p.n_q_heads);
   const int seg = (int)(sh / p.n_q_heads);
+  it.hk = it.hq / (p.n_q_heads / p.n_kv_heads);
+  if constexpr (CTX) {
+    it.len = p.num_q[seg];
+    const int n_mb = (it.len + kAtRows - 1) / kAtRows;
+    it.valid = it.x < n_mb;
+    const int mb = n_mb - 1 - it.x;
+    it.r0 = mb * kAtRows;
+    it.b = seg;
+    it.s0 = it.len > 0 ? p.q_tok[(long long)seg * p.S] : 0;
+    it.tok0 = seg * p.S + it.s0;
+    it.k_s0 = p.kv_start[seg];
+    it.n_keys = p.kv_len[seg];
+    it.shift = p.causal ? it.n_keys - it.len : kAtUnbounded;
+    const long long reach = (long long)it.r0 + kAtRows + it.shift;
+    it.n_kt = (int)(((reach < it.n_keys ? reach : (long long)it.n_keys) + kAtKeys - 1) / kAtKeys);
+    it.valid = it.valid && it.n_keys > 0 && it.k_s0 >= 0 && it.shift >= 0;
+    return it;
+  }
   const int t0 = p.seg_off[seg];
   it.len = p.seg_off[seg + 1] - t0;
   const int n_mb = (it.len + kAtRows - 1) / kAtRows;
-  it.valid = x < n_mb;
-  const int mb = n_mb - 1 - x;
+  it.valid = it.x < n_mb;
+  const int mb = n_mb - 1 - it.x;
   it.r0 = mb * kAtRows;
   it.n_kt = 2 * (mb + 1);              // 64-key tiles up to the end of the row block
-  it.hk = it.hq / (p.n_q_heads / p.n_kv_heads);
   it.tok0 = it.valid ? p.token_index[t0] : 0;
   it.b = (int)((__umulhi((uint32_t)it.tok0, p.div_mul) + (uint32_t)it.tok0) >> p.div_shift);
   it.s0 = it.tok0 - it.b * p.S;
+  it.k_s0 = it.s0;
+  it.shift = 0;
+  it.n_keys = kAtUnbounded;
   return it;
 }
 
+// Context mode: the rows [lo, hi) of sequence b get zeros in head hq's columns (tokens that are not queries).
+__device__ __forceinline__ void at_zero_rows(const DocAttnTcParams& p, int b, int hq, int lo, int hi, int tid) {
+  const long long row_stride = (long long)p.n_q_heads * kAtD;
+  __nv_bfloat16* base = p.out + (long long)b * p.S * row_stride + (long long)hq * kAtD;
+  for (int idx = tid; idx < (hi - lo) * 16; idx += 128)
+    *reinterpret_cast<uint4*>(base + (long long)(lo + (idx >> 4)) * row_stride + 8 * (idx & 15)) = make_uint4(0u, 0u, 0u, 0u);
+}
+
+// CTX = false: documents (segments listed by token_index / seg_off); true: context mode.
+template <bool CTX>
 __global__ void __launch_bounds__(kAtThreads, 2)
 doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                    const __grid_constant__ CUtensorMap tmap_v, const DocAttnTcParams p) {
@@ -212,10 +253,10 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       uint32_t n_it = 0, n_t = 0;
       bool ok = true;
       for (long long w = blockIdx.x; w < p.n_items && ok; w += gridDim.x) {
-        const AtItem it = at_item(p, w);
+        const AtItem it = at_item<CTX>(p, w);
         if (!it.valid) continue;
         const int qy = it.b * p.q_yb + it.hq * p.q_yh + it.s0 + it.r0, qx = it.hq * p.q_xh;
-        const int ky = it.b * p.k_yb + it.hk * p.k_yh + it.s0, kx = it.hk * p.k_xh;
+        const int ky = it.b * p.k_yb + it.hk * p.k_yh + it.k_s0, kx = it.hk * p.k_xh;
         // the query buffer is free once the previous item's last S has completed
         if (!(ok = mbar_wait(&s_q_empty, (n_it & 1u) ^ 1u, abort_flag, p.status, 1))) break;
         mbar_expect_tx(&s_q_full, kAtTile);
@@ -271,7 +312,7 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         return true;
       };
       for (long long w = blockIdx.x; w < p.n_items && ok; w += gridDim.x) {
-        const AtItem it = at_item(p, w);
+        const AtItem it = at_item<CTX>(p, w);
         if (!it.valid) continue;
         if (!(ok = mbar_wait(&s_q_full, n_it & 1u, abort_flag, p.status, 2))) break;
         // two S tiles run ahead of the softmax (n_kt is even: a row block spans whole pairs of key tiles)
@@ -304,8 +345,11 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     uint32_t n_t = 0;
     bool ok = true;
     for (long long w = blockIdx.x; w < p.n_items && ok; w += gridDim.x) {
-      const AtItem it = at_item(p, w);
-      if (!it.valid) continue;
+      const AtItem it = at_item<CTX>(p, w);
+      if (!it.valid) {
+        if (CTX && it.x == 0) at_zero_rows(p, it.b, it.hq, 0, p.S, threadIdx.x);   // no query at all
+        continue;
+      }
       float m_ref = -INFINITY, l_run = 0.f;                // m_ref: the maximum the exponentials refer to
       for (int t = 0; t < it.n_kt; ++t, ++n_t) {
         const uint32_t st = n_t & 1u;
@@ -314,39 +358,55 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         if (!ok) break;
         tc_fence_after();
         const uint32_t s_addr = lane_base + kColS + st * kAtKeys;
-        // Visibility of the two 32-key chunks for this warp's 32 rows: d = (first row of the warp) - (first key
-        // of the chunk); d >= 32: every key visible, d == 0: key i visible to lanes >= i, d < 0: hidden.
-        const int d0 = it.r0 + warp * 32 - t * kAtKeys, d1 = d0 - 32;
+        // Visibility of the two 32-key chunks for this warp's 32 rows.  Key i of a chunk is visible to a lane iff
+        // i <= lim = min(lane + d, ke), d = (first row of the warp) + shift - (first key of the chunk), ke = (last
+        // key of the segment) - (first key of the chunk).  A chunk is fully visible (class 2: d >= 31 and ke >= 31),
+        // hidden from the whole warp (class 0: d <= -32 or ke < 0) or cut (class 1).  For documents d is a multiple of
+        // 32 and ke unbounded: the classes are d >= 32, d == 0 (lim = lane) and d < 0.
+        int cls0, cls1, lim0, lim1;
+        if constexpr (CTX) {
+          const int d0 = it.r0 + warp * 32 + it.shift - t * kAtKeys, d1 = d0 - 32;
+          const int ke0 = it.n_keys - 1 - t * kAtKeys, ke1 = ke0 - 32;
+          cls0 = (d0 >= 31 && ke0 >= 31) ? 2 : ((d0 <= -32 || ke0 < 0) ? 0 : 1);
+          cls1 = (d1 >= 31 && ke1 >= 31) ? 2 : ((d1 <= -32 || ke1 < 0) ? 0 : 1);
+          lim0 = min(lane + d0, ke0);
+          lim1 = min(lane + d1, ke1);
+        } else {
+          const int d0 = it.r0 + warp * 32 - t * kAtKeys, d1 = d0 - 32;
+          cls0 = d0 >= 32 ? 2 : (d0 == 0 ? 1 : 0);
+          cls1 = d1 >= 32 ? 2 : (d1 == 0 ? 1 : 0);
+          lim0 = lim1 = lane;
+        }
         uint32_t va[32], vb[32];
         tmem_ld32(s_addr, va);
         tmem_ld32(s_addr + 32, vb);
         tmem_ld_wait();
         // row maximum: two elements per instruction, two independent chains per chunk
         float mx = -INFINITY, mx2 = -INFINITY;
-        if (d0 >= 32) {
+        if (cls0 == 2) {
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
             mx = max3(mx, __uint_as_float(va[i]), __uint_as_float(va[i + 1]));
             mx2 = max3(mx2, __uint_as_float(va[i + 2]), __uint_as_float(va[i + 3]));
           }
-        } else if (d0 == 0) {
+        } else if (cls0 == 1) {
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            mx = fmaxf(mx, i <= lane ? __uint_as_float(va[i]) : -INFINITY);
-            mx2 = fmaxf(mx2, i + 1 <= lane ? __uint_as_float(va[i + 1]) : -INFINITY);
+            mx = fmaxf(mx, i <= lim0 ? __uint_as_float(va[i]) : -INFINITY);
+            mx2 = fmaxf(mx2, i + 1 <= lim0 ? __uint_as_float(va[i + 1]) : -INFINITY);
           }
         }
-        if (d1 >= 32) {
+        if (cls1 == 2) {
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
             mx = max3(mx, __uint_as_float(vb[i]), __uint_as_float(vb[i + 1]));
             mx2 = max3(mx2, __uint_as_float(vb[i + 2]), __uint_as_float(vb[i + 3]));
           }
-        } else if (d1 == 0) {
+        } else if (cls1 == 1) {
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            mx = fmaxf(mx, i <= lane ? __uint_as_float(vb[i]) : -INFINITY);
-            mx2 = fmaxf(mx2, i + 1 <= lane ? __uint_as_float(vb[i + 1]) : -INFINITY);
+            mx = fmaxf(mx, i <= lim1 ? __uint_as_float(vb[i]) : -INFINITY);
+            mx2 = fmaxf(mx2, i + 1 <= lim1 ? __uint_as_float(vb[i + 1]) : -INFINITY);
           }
         }
         mx = fmaxf(mx, mx2);
@@ -378,8 +438,8 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         unsigned long long sum_a = 0ull, sum_b = 0ull;       // two packed accumulators = four partial row sums
         const unsigned long long scale2 = f32x2(p.scale_log2e, p.scale_log2e), neg_m2 = f32x2(neg_m, neg_m);
         uint32_t pk[16];
-        auto exps = [&](const uint32_t (&v)[32], int d) {
-          if (d < 0) {
+        auto exps = [&](const uint32_t (&v)[32], int cls, int lim) {
+          if (cls == 0) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) pk[i] = 0u;
             return;
@@ -390,11 +450,11 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             f32x2_split(fma_f32x2(f32x2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), scale2, neg_m2), x0, x1);
             f32x2_split(fma_f32x2(f32x2(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])), scale2, neg_m2), x2, x3);
             float e0 = ex2_approx(x0), e1 = ex2_approx(x1), e2 = ex2_approx(x2), e3 = ex2_approx(x3);
-            if (d == 0) {                                      // the diagonal chunk: key i is visible to lanes >= i
-              if (i > lane) e0 = 0.f;
-              if (i + 1 > lane) e1 = 0.f;
-              if (i + 2 > lane) e2 = 0.f;
-              if (i + 3 > lane) e3 = 0.f;
+            if (cls == 1) {                                    // a cut chunk: key i is visible iff i <= lim
+              if (i > lim) e0 = 0.f;
+              if (i + 1 > lim) e1 = 0.f;
+              if (i + 2 > lim) e2 = 0.f;
+              if (i + 3 > lim) e3 = 0.f;
             }
             sum_a = add_f32x2(sum_a, f32x2(e0, e1));
             sum_b = add_f32x2(sum_b, f32x2(e2, e3));
@@ -402,9 +462,9 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             pk[(i >> 1) + 1] = pack2_bf16(e2, e3);
           }
         };
-        exps(va, d0);
+        exps(va, cls0, lim0);
         tmem_st16(s_addr, pk);
-        exps(vb, d1);
+        exps(vb, cls1, lim1);
         tmem_st16(s_addr + 16, pk);
         {
           float s0, s1, s2, s3;
@@ -455,6 +515,10 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         }
         __syncwarp();   // the staging block is rewritten by the next column group
       }
+      if (CTX && it.x == 0) {   // the item of the last row block also clears the rows around the run
+        at_zero_rows(p, it.b, it.hq, 0, it.s0, threadIdx.x);
+        at_zero_rows(p, it.b, it.hq, it.s0 + it.len, p.S, threadIdx.x);
+      }
       tc_fence_before();   // the next item's first PV (gated by this warp's next arrival) overwrites O
     }
   }
@@ -487,6 +551,30 @@ View2D view_2d(int64_t sb, int64_t sh, int64_t ss, int B, int H, int S, int D) {
 }
 }  // namespace
 
+namespace {
+template <bool CTX>
+int launch_doc_attn_tc(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, DocAttnTcParams& p,
+                       int n_segments, int max_rows, cudaStream_t stream) {
+  static DeviceSmem configured{};
+  MSA_OK_OR_RETURN(ensure_dynamic_smem(doc_attn_tc_kernel<CTX>, kAtSmem, configured));
+  p.max_mb = (max_rows + kAtRows - 1) / kAtRows;
+  p.n_sh = (long long)n_segments * p.n_q_heads;
+  p.n_items = p.n_sh * p.max_mb;
+  int n_sm = 0;
+  MSA_OK_OR_RETURN(device_sm_count(&n_sm));
+  const long long grid = p.n_items < 2ll * n_sm ? p.n_items : 2ll * n_sm;   // persistent: two CTAs per SM
+  doc_attn_tc_kernel<CTX><<<(unsigned)grid, kAtThreads, kAtSmem, stream>>>(map_q, map_k, map_v, p);
+  MSA_LAUNCH_OK("doc_attn_tc_kernel");
+  return MSA_OK;
+}
+void set_token_division(DocAttnTcParams& p, int seq_len) {
+  uint32_t shift = 0;
+  while ((1ull << shift) < (uint64_t)seq_len) ++shift;
+  p.div_shift = shift;
+  p.div_mul = (uint32_t)((((1ull << shift) - (uint64_t)seq_len) << 32) / (uint64_t)seq_len + 1);
+}
+}  // namespace
+
 extern "C" int msa_doc_attention_tc(const void* q, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
                                     const void* k, const void* v, int64_t k_stride_b, int64_t k_stride_h,
                                     int64_t k_stride_s, const int32_t* token_index, const int32_t* seg_offsets,
@@ -516,23 +604,50 @@ extern "C" int msa_doc_attention_tc(const void* q, int64_t q_stride_b, int64_t q
   DocAttnTcParams p{};
   p.token_index = token_index; p.seg_off = seg_offsets; p.S = seq_len; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
   p.q_yb = vq.yb; p.q_yh = vq.yh; p.q_xh = vq.xh; p.k_yb = vk.yb; p.k_yh = vk.yh; p.k_xh = vk.xh;
-  uint32_t shift = 0;
-  while ((1ull << shift) < (uint64_t)seq_len) ++shift;
-  p.div_shift = shift;
-  p.div_mul = (uint32_t)((((1ull << shift) - (uint64_t)seq_len) << 32) / (uint64_t)seq_len + 1);
+  set_token_division(p, seq_len);
   p.scale_log2e = scale * 1.4426950408889634f;
   p.out = (__nv_bfloat16*)out;
   p.status = status;
 
-  static DeviceSmem configured{};
-  MSA_OK_OR_RETURN(ensure_dynamic_smem(doc_attn_tc_kernel, kAtSmem, configured));
-  p.max_mb = (max_segment_len + kAtRows - 1) / kAtRows;
-  p.n_sh = (long long)n_segments * n_q_heads;
-  p.n_items = p.n_sh * p.max_mb;
-  int n_sm = 0;
-  MSA_OK_OR_RETURN(device_sm_count(&n_sm));
-  const long long grid = p.n_items < 2ll * n_sm ? p.n_items : 2ll * n_sm;   // persistent: two CTAs per SM
-  doc_attn_tc_kernel<<<(unsigned)grid, kAtThreads, kAtSmem, (cudaStream_t)stream>>>(map_q, map_k, map_v, p);
-  MSA_LAUNCH_OK("doc_attn_tc_kernel");
-  return MSA_OK;
+  return launch_doc_attn_tc<false>(map_q, map_k, map_v, p, n_segments, max_segment_len, (cudaStream_t)stream);
+}
+
+extern "C" int msa_sparse_prefill_attn_tc(const void* q, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                                          const void* k_store, const void* v_store, int64_t store_stride_b,
+                                          int64_t store_stride_h, int32_t store_len, const int32_t* kv_start,
+                                          const int32_t* kv_len, const int32_t* q_tok, const int32_t* num_q, int32_t n_seq,
+                                          int32_t seq_len, int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim,
+                                          int32_t dtype, int32_t causal, float scale, void* out, int32_t* status,
+                                          void* stream) {
+  MSA_REQUIRE(q && k_store && v_store && kv_start && kv_len && q_tok && num_q && out && status,
+              "sparse_prefill_attn_tc: null pointer");
+  MSA_REQUIRE(dtype == MSA_BF16 && head_dim == kAtD, "sparse_prefill_attn_tc: bf16 with head_dim 128 only");
+  MSA_REQUIRE(n_seq > 0 && seq_len > 0 && store_len > 0 && n_q_heads > 0 && n_kv_heads > 0 && n_q_heads % n_kv_heads == 0,
+              "sparse_prefill_attn_tc: bad sizes");
+  MSA_REQUIRE((long long)n_seq * seq_len * n_q_heads < (1ll << 31) && (long long)n_seq * store_len * n_kv_heads < (1ll << 31),
+              "sparse_prefill_attn_tc: more than 2^31 token rows");
+  MSA_REQUIRE(aligned16(q) && aligned16(k_store) && aligned16(v_store) && aligned16(out) && q_stride_s % 8 == 0,
+              "sparse_prefill_attn_tc: rows must be 16-byte aligned");
+  const View2D vq = view_2d(q_stride_b, q_stride_h, q_stride_s, n_seq, n_q_heads, seq_len, head_dim);
+  const View2D vk = view_2d(store_stride_b, store_stride_h, head_dim, n_seq, n_kv_heads, store_len, head_dim);
+  MSA_REQUIRE(vq.ok, "sparse_prefill_attn_tc: q must be a token-major or contiguous head-major tensor");
+  MSA_REQUIRE(vk.ok, "sparse_prefill_attn_tc: the stores must be contiguous [B, Hkv, store_len, D] tensors");
+
+  CUtensorMap map_q, map_k, map_v;
+  int rc = make_map(&map_q, q, vq.rows, vq.cols, vq.row_stride, 64, kAtRows);
+  if (rc != MSA_OK) return rc;
+  rc = make_map(&map_k, k_store, vk.rows, vk.cols, vk.row_stride, 64, kAtKeys);
+  if (rc != MSA_OK) return rc;
+  rc = make_map(&map_v, v_store, vk.rows, vk.cols, vk.row_stride, 64, kAtKeys);
+  if (rc != MSA_OK) return rc;
+
+  DocAttnTcParams p{};
+  p.q_tok = q_tok; p.num_q = num_q; p.kv_start = kv_start; p.kv_len = kv_len; p.causal = causal != 0;
+  p.S = seq_len; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
+  p.q_yb = vq.yb; p.q_yh = vq.yh; p.q_xh = vq.xh; p.k_yb = vk.yb; p.k_yh = vk.yh; p.k_xh = vk.xh;
+  set_token_division(p, seq_len);
+  p.scale_log2e = scale * 1.4426950408889634f;
+  p.out = (__nv_bfloat16*)out;
+  p.status = status;
+  return launch_doc_attn_tc<true>(map_q, map_k, map_v, p, n_seq, seq_len, (cudaStream_t)stream);
 }

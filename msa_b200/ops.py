@@ -550,11 +550,13 @@ def append_segment(key_states: torch.Tensor, value_states: torch.Tensor, valid: 
 
 
 def sparse_prefill_attn(q: torch.Tensor, k_store, v_store, kv_start, kv_len, q_tok, num_q, scale: Optional[float] = None,
-                        out: Optional[torch.Tensor] = None, causal: bool = True) -> torch.Tensor:
+                        out: Optional[torch.Tensor] = None, causal: bool = True, q_runs: bool = False,
+                        status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """q ``[B, Hq, S, D]``.  Returns ``[B, S, Hq*D]``; rows of invalid tokens are zero (written by the kernel:
     ``out`` may be uninitialised).  ``causal``: bottom-right aligned causal mask (stage 2); False = every valid
     token sees the whole context (multi-token decode segments).  bf16 / D = 128 on tensor cores, anything else on
-    the general kernel."""
+    the general kernel.  ``q_runs``: the caller has checked that every sequence's valid tokens are one run of
+    consecutive tokens; bf16 / D = 128 then runs on the tcgen05 kernel (``status[0] != 0`` after a sync = it gave up)."""
     A.need_cuda(q, k_store, v_store)
     b, hq, s, d = q.shape
     if q.stride(3) != 1:
@@ -562,6 +564,19 @@ def sparse_prefill_attn(q: torch.Tensor, k_store, v_store, kv_start, kv_len, q_t
     if out is None:
         out = torch.empty((b, s, hq * d), dtype=q.dtype, device=q.device)
     scale = (1.0 / math.sqrt(d)) if scale is None else scale
+    if (q_runs and q.dtype == torch.bfloat16 and d == 128 and _tc_view_ok(q)
+            and k_store.stride(3) == 1 and k_store.stride(2) == d and v_store.stride() == k_store.stride()
+            and k_store.stride(1) == k_store.shape[2] * d and (b == 1 or k_store.stride(0) == k_store.shape[1] * k_store.stride(1))
+            and k_store.data_ptr() % 16 == 0 and v_store.data_ptr() % 16 == 0
+            and b * s * hq < 2 ** 31 and b * k_store.shape[1] * k_store.shape[2] < 2 ** 31):
+        if status is None:
+            status = torch.zeros(4, dtype=torch.int32, device=q.device)
+        A.check(A.lib().msa_sparse_prefill_attn_tc(
+            A.ptr(q), q.stride(0), q.stride(1), q.stride(2), A.ptr(k_store), A.ptr(v_store), k_store.stride(0),
+            k_store.stride(1), k_store.shape[2], A.ptr(kv_start), A.ptr(kv_len), A.ptr(q_tok), A.ptr(num_q), b, s, hq,
+            k_store.shape[1], d, A.dtype_code(q.dtype), int(causal), float(scale), A.ptr(out), A.ptr(status),
+            A.stream_ptr(q.device)), "msa_sparse_prefill_attn_tc")
+        return out
     A.check(A.lib().msa_sparse_prefill_attn(
         A.ptr(q), q.stride(0), q.stride(1), q.stride(2), A.ptr(k_store), A.ptr(v_store), k_store.stride(0),
         k_store.stride(1), A.ptr(kv_start), A.ptr(kv_len), A.ptr(q_tok), A.ptr(num_q), b, s, hq, k_store.shape[1], d,

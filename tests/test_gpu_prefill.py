@@ -75,6 +75,82 @@ def test_assemble_and_prefill_match_restatement(b, s, hq, hkv, t_len, n_sel, fra
     assert out[~valid].abs().sum().item() == 0
 
 
+@pytest.mark.parametrize("b,s,hq,hkv,t_len,n_sel,pad", [
+    (3, 70, 8, 2, 3, [130, 0, 61], "left"),            # one row block, ragged contexts, a sequence without retrieved entries
+    (2, 300, 32, 8, 3, [1024, 517], "left"),           # three row blocks of queries
+    (4, 128, 16, 8, 3, [64, 0, 200, 1], "right"),      # right padding, queries ending inside a row block
+    (3, 33, 8, 8, 0, [0, 5, 0], "none"),               # no template, contexts shorter than one key tile
+])
+def test_context_attention_on_tcgen05_kernel_matches_restatement(b, s, hq, hkv, t_len, n_sel, pad):
+    """Stage-2 attention through the tcgen05 kernel's context mode (every sequence's valid tokens are one run) against
+    the oracle's restatement and against the mma.sync kernel on the same store, token-major queries as the layer
+    passes them; one sequence has no valid token at all."""
+    from msa_b200 import ops
+    dev = torch.device("cuda:0")
+    d = 128
+    q, k, v, tk, tv, sk, sv, _ = _case(300 + b, b, s, hq, hkv, d, t_len, n_sel, 1.0, torch.bfloat16, dev)
+    q = q.transpose(1, 2).contiguous().transpose(1, 2)        # [B, Hq, S, D] view of token-major storage
+    g = torch.Generator().manual_seed(5 + s)
+    valid = torch.ones(b, s, dtype=torch.bool)
+    for i in range(b):
+        n = int(torch.randint(1, s + 1, (1,), generator=g)) if (pad != "none" and i > 0) else s
+        if pad == "left":
+            valid[i, : s - n] = False
+        elif pad == "right":
+            valid[i, n:] = False
+    if b > 2:
+        valid[2] = False                                       # nothing to attend for: its rows must come back zero
+    valid = valid.to(dev)
+    nsel = torch.tensor(n_sel, dtype=torch.int64, device=dev)
+    lens = [t_len + n_sel[i] + int(valid[i].sum()) for i in range(b)]
+    max_kv, reserve = max(lens), 9
+    ks, vs, kv_start, kv_len, q_tok, num_q, err = ops.assemble_context(tk, tv, sk, sv, nsel, k, v, valid, max_kv, reserve)
+    scale = 1.0 / math.sqrt(d)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    out = torch.full((b, s, hq * d), float("nan"), dtype=torch.bfloat16, device=dev)     # the kernel writes every row
+    ops.sparse_prefill_attn(q, ks, vs, kv_start, kv_len, q_tok, num_q, scale, out=out, q_runs=True, status=status)
+    legacy = ops.sparse_prefill_attn(q, ks, vs, kv_start, kv_len, q_tok, num_q, scale)
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0] and int(err.item()) == 0
+    ref, _ = _reference(q, k, v, tk, tv, sk, sv, valid, n_sel, scale)
+    assert out[~valid].abs().sum().item() == 0
+    errn = (out.float()[valid] - ref[valid]).norm() / ref[valid].norm().clamp_min(1e-6)
+    assert errn.item() < 1e-2, errn.item()
+    assert ((out.float() - legacy.float()).norm() / legacy.float().norm().clamp_min(1e-6)).item() < 1e-2
+
+
+def test_context_attention_on_tcgen05_kernel_without_causal_mask():
+    """A multi-token decode segment (every valid token sees the whole grown context) through the context mode: contexts
+    that end inside a key tile, a segment longer than one row block."""
+    from msa_b200 import ops
+    from oracle import msa_oracle as O
+    dev = torch.device("cuda:0")
+    b, hq, hkv, d, l0, q_len, cap = 3, 8, 2, 128, 150, 200, 400
+    g = torch.Generator().manual_seed(43)
+    lens = torch.tensor([150, 97, 3])
+    ck, cv = [torch.randn(b, hkv, l0, d, generator=g).to(torch.bfloat16) for _ in range(2)]
+    key_mask = torch.arange(l0).unsqueeze(0) >= (l0 - lens.unsqueeze(1))
+    q = torch.randn(b, hq, q_len, d, generator=g).to(torch.bfloat16)
+    nk, nv = [torch.randn(b, hkv, q_len, d, generator=g).to(torch.bfloat16) for _ in range(2)]
+    new_mask = torch.ones(b, q_len, dtype=torch.bool)
+    new_mask[1, :77] = False                 # left padded
+    new_mask[2, 5:] = False                  # right padded
+    ref, _, _, _ = O.decode_segment_attention(q.float(), ck.float(), cv.float(), key_mask, nk.float(), nv.float(), new_mask)
+    k_store = torch.zeros(b, hkv, cap, d, dtype=torch.bfloat16, device=dev)
+    v_store = torch.zeros_like(k_store)
+    k_store[:, :, :l0], v_store[:, :, :l0] = ck.to(dev), cv.to(dev)
+    kv_start, kv_len = (l0 - lens).to(torch.int32).to(dev), lens.to(torch.int32).to(dev)
+    q_tok, num_q, err = ops.append_segment(nk.to(dev), nv.to(dev), new_mask.to(dev), k_store, v_store, kv_start, kv_len)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    out = ops.sparse_prefill_attn(q.to(dev), k_store, v_store, kv_start, kv_len, q_tok, num_q, causal=False, q_runs=True,
+                                  status=status)
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0] and int(err.item()) == 0
+    got = out.float().cpu()
+    assert ((got[new_mask] - ref[new_mask]).norm() / ref[new_mask].norm()).item() < 1e-2
+    assert got[~new_mask].abs().sum().item() == 0
+
+
 def test_assemble_fp32_and_overflow_flag():
     from msa_b200 import ops
     dev = torch.device("cuda:0")
@@ -462,6 +538,7 @@ def attn128(golden):
 
         def counted(*a, _n=name, **kw):
             calls[_n] = calls.get(_n, 0) + 1
+            calls[_n + ":kwargs"] = kw
             return originals[_n](*a, **kw)
         setattr(ops, name, counted)
     yield g, geo, layer, rope, pre, calls
@@ -545,6 +622,7 @@ def test_stage2_on_prefill_kernel_matches_reference_layer(attn128):
               rope(hidden2, T(g["s2_position_ids"]).to("cuda:0")), cache2)
     svc.check_status()
     assert calls.get("sparse_prefill_attn") == 1 and calls.get("assemble_context") == 1
+    assert calls["sparse_prefill_attn:kwargs"].get("q_runs") is True       # left-padded questions: the tcgen05 kernel
     kw2 = cache2.cache_kwargs[0]
     assert [r["topk_doc_ids"] for r in kw2["recall_topk"]] == g["s2_recall_ids"].tolist()
     got_scores = torch.tensor([r["score"] for r in kw2["recall_topk"]])
