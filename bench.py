@@ -750,6 +750,14 @@ def run_secondary(args):
         tc_ms = _time_ms(torch, lambda: ops.doc_attention_tc(q, k, v, tok, seg, doc_len, out=out, status=tc_status), 10, 3)
         fused_ms = _time_ms(torch, lambda: ops.doc_attention_pool(q, k, v, tok, seg, doc_len, out=out, chunk_offsets=off,
                                                                   pool_size=p), 10, 3)
+        # the same documents with 5 % of the tokens inside them masked: spans + bitmap on the tcgen05 kernel
+        keep = torch.rand(t, generator=g, device=dev) >= 0.05
+        keep[seg[:-1].long()] = True
+        keep[(seg[1:] - 1).long()] = True
+        bits = ops.token_bitmap(keep)
+        span_tok = torch.arange(t, dtype=torch.int32, device=dev)
+        masked_ms = _time_ms(torch, lambda: ops.doc_attention_tc_masked(q, k, v, span_tok, seg, doc_len, bits, out=out,
+                                                                        status=tc_status), 10, 3)
         steps = min(steps, 20)
         args.steps = steps
         sampler.start()
@@ -773,7 +781,8 @@ def run_secondary(args):
                                       "flops_per_launch": flops_exec,
                                       "note": "executed flops (whole 128 x 128 tiles, diagonal tiles included) over the "
                                               "kernel's own time; peak = burst bf16 GEMM rate (kernel timed alone)"},
-                         "tcgen05_attention_ms": tc_ms, "tcgen05_attention_causal_tflops": flops / (tc_ms / 1e3) / 1e12,
+                         "tcgen05_attention_ms": tc_ms, "tcgen05_attention_with_5pct_masked_tokens_ms": masked_ms,
+                         "tcgen05_attention_causal_tflops": flops / (tc_ms / 1e3) / 1e12,
                          "separate_kv_pooling_ms": pool_ms,
                          "mma_sync_attention_with_fused_pooling_ms": fused_ms,
                          "library_varlen_attention_ms": lib_ms})

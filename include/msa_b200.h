@@ -443,6 +443,23 @@ int msa_doc_attention_tc(const void* q, int64_t q_stride_b, int64_t q_stride_h, 
                          int32_t n_kv_heads, int32_t head_dim, int32_t dtype, float scale, void* out,
                          int32_t* status, void* stream);
 
+/* msa_doc_attention_tc_masked: msa_doc_attention_tc for documents with tokens inside them that do not take part
+ * (attention mask 0: src/msa/memory_sparse_attention.py:216-241 indexes them away before the attention call).  A
+ * segment is the SPAN of memory from a document's first to its last participating token: span_index lists every
+ * position of the span (ascending by one), span_offsets the spans, and valid_bits (bit p of the bitmap = flat token
+ * position p takes part; n_bit_words 32-bit words, covering every token plus 256 positions, plus one more word)
+ * says which of them are tokens of the document.  The others are never attended to and their rows of out are left
+ * as they are; causality follows the position in the span, which orders the participating tokens as the
+ * reference's compacted list does.  Spans of different documents must not overlap (documents that are packed one
+ * after the other, as the reference's blocks are, never do).
+ */
+int msa_doc_attention_tc_masked(const void* q, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s, const void* k,
+                                const void* v, int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s,
+                                const int32_t* span_index, const int32_t* span_offsets, int32_t n_segments,
+                                int32_t max_span_len, int32_t n_seq, int32_t seq_len, int32_t n_q_heads,
+                                int32_t n_kv_heads, int32_t head_dim, int32_t dtype, float scale, void* out,
+                                const uint32_t* valid_bits, int64_t n_bit_words, int32_t* status, void* stream);
+
 /* msa_sparse_prefill_attn_tc: msa_sparse_prefill_attn (same arguments, same result, rows of tokens that are not
  * queries zero-filled) on the tcgen05 kernel of msa_doc_attention_tc, for the case that the valid tokens of every
  * sequence are ONE run of consecutive tokens (q_tok[b, r] = q_tok[b, 0] + r for r < num_q[b]; the caller checks

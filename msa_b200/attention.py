@@ -9,9 +9,10 @@ loads), same cache protocol (``cache_kwargs`` / ``meta`` / ``record_kwargs`` / `
 What runs where (every attention of the path is one of this package's kernels; no library attention call):
   * stage 1: projections, norms and RoPE stay PyTorch as in the reference; chunk bookkeeping, the
     intra-document causal attention and all pooling run on this package's kernels.  In bf16 with
-    head_dim 128: documents without masked tokens go to the tcgen05 attention kernel (K, V, K_r pooled
-    by the pooling kernel), blocks with masked tokens inside documents to the mma.sync kernel that
-    takes the K / V chunk means in the same pass; fp32 and other head sizes: the general CUDA-core
+    head_dim 128: documents of 128 tokens and more go to the tcgen05 attention kernel (blocks with masked
+    tokens inside documents: over each document's span of memory with a bitmap of the tokens that take
+    part; K, V, K_r pooled by the pooling kernel), blocks of shorter documents to the mma.sync kernel
+    that takes the K / V chunk means in the same pass; fp32 and other head sizes: the general CUDA-core
     attention kernel + the pooling kernel;
   * stage 2: routing, merge and fetch happen inside ``memory_client.doc_query`` (this package's
     ``MSAService``); one kernel assembles [template | retrieved | query] into the left-padded
@@ -129,9 +130,14 @@ class MemorySparseAttention(Qwen3Attention):
                 first, last = tok[off[:-1]], tok[off[1:] - 1]
                 runs = bool(((last - first == counts - 1) & (first // s == last // s)).all().item())
                 return tok.to(torch.int32), off.to(torch.int32), int(counts.max().item()), runs
-            hit = (key, table((doc_ids > 0) & valid, doc_ids), table((doc_ids == -2) & valid, torch.zeros_like(doc_ids)))
+            listed = (doc_ids > 0) & valid
+            docs = table(listed, doc_ids)
+            spans = None
+            if not docs[3] and docs[0].numel() > 0:      # masked tokens inside documents: spans + bitmap for the tcgen05 kernel
+                spans = ops.document_spans(docs[0], docs[1]) + (ops.token_bitmap(listed),)
+            hit = (key, docs, table((doc_ids == -2) & valid, torch.zeros_like(doc_ids)), spans)
             cache.meta["_msa_b200_segments"] = hit
-        return hit[1], hit[2]
+        return hit[1], hit[2], hit[3]
 
     def _valid_runs(self, valid, cache):
         """Device flags ``[2]`` int32: whether the valid tokens of every row are one run of consecutive tokens (what the
@@ -163,12 +169,19 @@ class MemorySparseAttention(Qwen3Attention):
         # intra-document and template causal attention (:216-241)
         attn_output = torch.zeros((bsz, q_len, n_heads * self.head_dim), device=device, dtype=dtype)
         pooled_k = pooled_v = pooled_rk = pooled_doc_ids = None
-        (tok_d, off_d, max_d, runs_d), (tok_t, off_t, max_t, _) = self._segments(doc_ids, attention_mask, cache)
-        if tensor_cores and runs_d and max_d >= 128 and ops.doc_attention_tc_supported(query_states, key_states, value_states):
+        (tok_d, off_d, max_d, runs_d), (tok_t, off_t, max_t, _), spans = self._segments(doc_ids, attention_mask, cache)
+        tc_ok = tensor_cores and max_d >= 128 and ops.doc_attention_tc_supported(query_states, key_states, value_states)
+        if tc_ok and runs_d:
             # unmasked documents: attention on the tcgen05 kernel (K and V are pooled by the pooling kernel below)
             status = cache.meta.setdefault("_msa_b200_attn_status", torch.zeros(4, dtype=torch.int32, device=device))
             ops.doc_attention_tc(query_states, key_states, value_states, tok_d, off_d, max_d, out=attn_output,
                                  scale=self.scaling, status=status)
+        elif tc_ok and spans is not None:
+            # masked tokens inside documents: the same kernel over each document's span of memory with a bitmap of
+            # the tokens that take part (masked rows of attn_output stay zero)
+            status = cache.meta.setdefault("_msa_b200_attn_status", torch.zeros(4, dtype=torch.int32, device=device))
+            ops.doc_attention_tc_masked(query_states, key_states, value_states, spans[0], spans[1], spans[2], spans[3],
+                                        out=attn_output, scale=self.scaling, status=status)
         elif tensor_cores and self.is_router_layer and self.pooling_kernel_size % 32 == 0:
             # K and V are pooled from the tiles the attention kernel stages anyway
             tok, off, pooled_doc_ids = self._bookkeeping(doc_ids, attention_mask, cache)

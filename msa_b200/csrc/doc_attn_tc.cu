@@ -58,6 +58,9 @@ struct DocAttnTcParams {
   const int32_t* kv_start;
   const int32_t* kv_len;
   int causal;                   // context mode: bottom-right aligned causal mask, or every key visible
+  // masked documents: bit (flat token position) = the token belongs to its document; a segment then lists EVERY
+  // position from its first to its last such token, and the others are neither attended to nor written
+  const uint32_t* valid_bits;
   int S, n_q_heads, n_kv_heads;
   int q_yb, q_yh, q_xh;         // q tile coordinates: y = b*q_yb + h*q_yh + s, x = h*q_xh + 64*block
   int k_yb, k_yh, k_xh;
@@ -202,8 +205,19 @@ __device__ __forceinline__ void at_zero_rows(const DocAttnTcParams& p, int b, in
     *reinterpret_cast<uint4*>(base + (long long)(lo + (idx >> 4)) * row_stride + 8 * (idx & 15)) = make_uint4(0u, 0u, 0u, 0u);
 }
 
-// CTX = false: documents (segments listed by token_index / seg_off); true: context mode.
-template <bool CTX>
+// 32 bits of a bitmap from bit position pos on (the bitmap is padded so that the word after the last one exists).
+__device__ __forceinline__ uint32_t at_bits(const uint32_t* __restrict__ words, long long pos) {
+  const long long w = pos >> 5;
+  return __funnelshift_r(__ldg(words + w), __ldg(words + w + 1), (uint32_t)(pos & 31));
+}
+// The keys 0..lim of a 32-key chunk as a bit mask.
+__device__ __forceinline__ uint32_t at_upto(int lim) {
+  return lim >= 31 ? 0xffffffffu : (lim < 0 ? 0u : ((2u << lim) - 1u));
+}
+
+// CTX = false: documents (segments listed by token_index / seg_off); true: context mode.  MASKED (documents only):
+// segments are spans of memory with tokens that do not take part (valid_bits).
+template <bool CTX, bool MASKED>
 __global__ void __launch_bounds__(kAtThreads, 2)
 doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                    const __grid_constant__ CUtensorMap tmap_v, const DocAttnTcParams p) {
@@ -353,6 +367,12 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       float m_ref = -INFINITY, l_run = 0.f;                // m_ref: the maximum the exponentials refer to
       for (int t = 0; t < it.n_kt; ++t, ++n_t) {
         const uint32_t st = n_t & 1u;
+        uint32_t km0 = 0xffffffffu, km1 = 0xffffffffu;       // MASKED: which keys of the tile's two chunks take part
+        if constexpr (MASKED) {                               // fetched while the tile's S is still on its way
+          const long long kpos = (long long)it.tok0 + (long long)t * kAtKeys;
+          km0 = at_bits(p.valid_bits, kpos);
+          km1 = at_bits(p.valid_bits, kpos + 32);
+        }
         ok = mbar_wait(&s_s_full[st], (n_t >> 1) & 1u, abort_flag, p.status, 5);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -377,10 +397,34 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           cls1 = d1 >= 32 ? 2 : (d1 == 0 ? 1 : 0);
           lim0 = lim1 = lane;
         }
+        uint32_t vis0 = 0xffffffffu, vis1 = 0xffffffffu;      // MASKED: the keys this lane's row sees, chunk by chunk
+        if constexpr (MASKED) {
+          vis0 = km0 & (cls0 == 2 ? 0xffffffffu : (cls0 == 1 ? at_upto(lim0) : 0u));
+          vis1 = km1 & (cls1 == 2 ? 0xffffffffu : (cls1 == 1 ? at_upto(lim1) : 0u));
+          // a chunk with a hole is handled like a cut one; a chunk without a visible key for the whole warp is hidden
+          if (cls0 == 2 && km0 != 0xffffffffu) cls0 = 1;
+          if (cls1 == 2 && km1 != 0xffffffffu) cls1 = 1;
+          if (km0 == 0u) cls0 = 0;
+          if (km1 == 0u) cls1 = 0;
+        }
         uint32_t va[32], vb[32];
         tmem_ld32(s_addr, va);
         tmem_ld32(s_addr + 32, vb);
         tmem_ld_wait();
+        if constexpr (MASKED) {
+          // a chunk with hidden keys: their scores become -inf once (their exponentials are then zero by themselves)
+          // and the chunk goes through the code of a fully visible one
+          if (cls0 == 1) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) if (!((vis0 >> i) & 1u)) va[i] = 0xff800000u;
+            cls0 = 2;
+          }
+          if (cls1 == 1) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) if (!((vis1 >> i) & 1u)) vb[i] = 0xff800000u;
+            cls1 = 2;
+          }
+        }
         // row maximum: two elements per instruction, two independent chains per chunk
         float mx = -INFINITY, mx2 = -INFINITY;
         if (cls0 == 2) {
@@ -392,8 +436,8 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         } else if (cls0 == 1) {
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            mx = fmaxf(mx, i <= lim0 ? __uint_as_float(va[i]) : -INFINITY);
-            mx2 = fmaxf(mx2, i + 1 <= lim0 ? __uint_as_float(va[i + 1]) : -INFINITY);
+            mx = fmaxf(mx, (MASKED ? (vis0 >> i) & 1u : (uint32_t)(i <= lim0)) ? __uint_as_float(va[i]) : -INFINITY);
+            mx2 = fmaxf(mx2, (MASKED ? (vis0 >> (i + 1)) & 1u : (uint32_t)(i + 1 <= lim0)) ? __uint_as_float(va[i + 1]) : -INFINITY);
           }
         }
         if (cls1 == 2) {
@@ -405,8 +449,8 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         } else if (cls1 == 1) {
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            mx = fmaxf(mx, i <= lim1 ? __uint_as_float(vb[i]) : -INFINITY);
-            mx2 = fmaxf(mx2, i + 1 <= lim1 ? __uint_as_float(vb[i + 1]) : -INFINITY);
+            mx = fmaxf(mx, (MASKED ? (vis1 >> i) & 1u : (uint32_t)(i <= lim1)) ? __uint_as_float(vb[i]) : -INFINITY);
+            mx2 = fmaxf(mx2, (MASKED ? (vis1 >> (i + 1)) & 1u : (uint32_t)(i + 1 <= lim1)) ? __uint_as_float(vb[i + 1]) : -INFINITY);
           }
         }
         mx = fmaxf(mx, mx2);
@@ -438,7 +482,7 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         unsigned long long sum_a = 0ull, sum_b = 0ull;       // two packed accumulators = four partial row sums
         const unsigned long long scale2 = f32x2(p.scale_log2e, p.scale_log2e), neg_m2 = f32x2(neg_m, neg_m);
         uint32_t pk[16];
-        auto exps = [&](const uint32_t (&v)[32], int cls, int lim) {
+        auto exps = [&](const uint32_t (&v)[32], int cls, int lim, uint32_t vis) {
           if (cls == 0) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) pk[i] = 0u;
@@ -451,10 +495,17 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             f32x2_split(fma_f32x2(f32x2(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])), scale2, neg_m2), x2, x3);
             float e0 = ex2_approx(x0), e1 = ex2_approx(x1), e2 = ex2_approx(x2), e3 = ex2_approx(x3);
             if (cls == 1) {                                    // a cut chunk: key i is visible iff i <= lim
-              if (i > lim) e0 = 0.f;
-              if (i + 1 > lim) e1 = 0.f;
-              if (i + 2 > lim) e2 = 0.f;
-              if (i + 3 > lim) e3 = 0.f;
+              if constexpr (MASKED) {                          // ... and the token takes part
+                if (!((vis >> i) & 1u)) e0 = 0.f;
+                if (!((vis >> (i + 1)) & 1u)) e1 = 0.f;
+                if (!((vis >> (i + 2)) & 1u)) e2 = 0.f;
+                if (!((vis >> (i + 3)) & 1u)) e3 = 0.f;
+              } else {
+                if (i > lim) e0 = 0.f;
+                if (i + 1 > lim) e1 = 0.f;
+                if (i + 2 > lim) e2 = 0.f;
+                if (i + 3 > lim) e3 = 0.f;
+              }
             }
             sum_a = add_f32x2(sum_a, f32x2(e0, e1));
             sum_b = add_f32x2(sum_b, f32x2(e2, e3));
@@ -462,9 +513,9 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             pk[(i >> 1) + 1] = pack2_bf16(e2, e3);
           }
         };
-        exps(va, cls0, lim0);
+        exps(va, cls0, lim0, vis0);
         tmem_st16(s_addr, pk);
-        exps(vb, cls1, lim1);
+        exps(vb, cls1, lim1, vis1);
         tmem_st16(s_addr + 16, pk);
         {
           float s0, s1, s2, s3;
@@ -491,6 +542,8 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       unsigned char* stg = out_stage + warp * kAtOutStage;
       const long long row_stride = (long long)p.n_q_heads * kAtD;
       __nv_bfloat16* dst0 = p.out + ((long long)it.tok0 + it.r0 + warp * 32) * row_stride + (long long)it.hq * kAtD;
+      uint32_t row_bits = 0xffffffffu;    // MASKED: which of the warp's 32 rows are tokens of the document
+      if constexpr (MASKED) row_bits = at_bits(p.valid_bits, (long long)it.tok0 + it.r0 + warp * 32);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
@@ -510,7 +563,7 @@ doc_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         for (int i = 0; i < 4; ++i) {
           const int r = (lane >> 2) + 8 * i, piece = lane & 3;
           const uint4 o = *reinterpret_cast<const uint4*>(stg + r * 64 + ((piece ^ ((r >> 1) & 3)) << 4));
-          if (it.r0 + warp * 32 + r < it.len)
+          if (it.r0 + warp * 32 + r < it.len && ((row_bits >> r) & 1u))
             *reinterpret_cast<uint4*>(dst0 + (long long)r * row_stride + 32 * c + 8 * piece) = o;
         }
         __syncwarp();   // the staging block is rewritten by the next column group
@@ -552,18 +605,18 @@ View2D view_2d(int64_t sb, int64_t sh, int64_t ss, int B, int H, int S, int D) {
 }  // namespace
 
 namespace {
-template <bool CTX>
+template <bool CTX, bool MASKED>
 int launch_doc_attn_tc(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, DocAttnTcParams& p,
                        int n_segments, int max_rows, cudaStream_t stream) {
   static DeviceSmem configured{};
-  MSA_OK_OR_RETURN(ensure_dynamic_smem(doc_attn_tc_kernel<CTX>, kAtSmem, configured));
+  MSA_OK_OR_RETURN(ensure_dynamic_smem(doc_attn_tc_kernel<CTX, MASKED>, kAtSmem, configured));
   p.max_mb = (max_rows + kAtRows - 1) / kAtRows;
   p.n_sh = (long long)n_segments * p.n_q_heads;
   p.n_items = p.n_sh * p.max_mb;
   int n_sm = 0;
   MSA_OK_OR_RETURN(device_sm_count(&n_sm));
   const long long grid = p.n_items < 2ll * n_sm ? p.n_items : 2ll * n_sm;   // persistent: two CTAs per SM
-  doc_attn_tc_kernel<CTX><<<(unsigned)grid, kAtThreads, kAtSmem, stream>>>(map_q, map_k, map_v, p);
+  doc_attn_tc_kernel<CTX, MASKED><<<(unsigned)grid, kAtThreads, kAtSmem, stream>>>(map_q, map_k, map_v, p);
   MSA_LAUNCH_OK("doc_attn_tc_kernel");
   return MSA_OK;
 }
@@ -575,12 +628,13 @@ void set_token_division(DocAttnTcParams& p, int seq_len) {
 }
 }  // namespace
 
-extern "C" int msa_doc_attention_tc(const void* q, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
-                                    const void* k, const void* v, int64_t k_stride_b, int64_t k_stride_h,
-                                    int64_t k_stride_s, const int32_t* token_index, const int32_t* seg_offsets,
-                                    int32_t n_segments, int32_t max_segment_len, int32_t n_seq, int32_t seq_len,
-                                    int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim, int32_t dtype, float scale,
-                                    void* out, int32_t* status, void* stream) {
+namespace {
+int doc_attention_tc_impl(const void* q, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s, const void* k,
+                          const void* v, int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s,
+                          const int32_t* token_index, const int32_t* seg_offsets, int32_t n_segments,
+                          int32_t max_segment_len, int32_t n_seq, int32_t seq_len, int32_t n_q_heads, int32_t n_kv_heads,
+                          int32_t head_dim, int32_t dtype, float scale, void* out, const uint32_t* valid_bits,
+                          int32_t* status, void* stream) {
   MSA_REQUIRE(q && k && v && token_index && seg_offsets && out && status, "doc_attention_tc: null pointer");
   MSA_REQUIRE(dtype == MSA_BF16 && head_dim == kAtD, "doc_attention_tc: bf16 with head_dim 128 only");
   MSA_REQUIRE(n_segments >= 0 && max_segment_len >= 0 && n_seq > 0 && seq_len > 0 && n_q_heads > 0 &&
@@ -608,8 +662,38 @@ extern "C" int msa_doc_attention_tc(const void* q, int64_t q_stride_b, int64_t q
   p.scale_log2e = scale * 1.4426950408889634f;
   p.out = (__nv_bfloat16*)out;
   p.status = status;
+  p.valid_bits = valid_bits;
+  if (valid_bits != nullptr)
+    return launch_doc_attn_tc<false, true>(map_q, map_k, map_v, p, n_segments, max_segment_len, (cudaStream_t)stream);
+  return launch_doc_attn_tc<false, false>(map_q, map_k, map_v, p, n_segments, max_segment_len, (cudaStream_t)stream);
+}
+}  // namespace
 
-  return launch_doc_attn_tc<false>(map_q, map_k, map_v, p, n_segments, max_segment_len, (cudaStream_t)stream);
+extern "C" int msa_doc_attention_tc(const void* q, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                                    const void* k, const void* v, int64_t k_stride_b, int64_t k_stride_h,
+                                    int64_t k_stride_s, const int32_t* token_index, const int32_t* seg_offsets,
+                                    int32_t n_segments, int32_t max_segment_len, int32_t n_seq, int32_t seq_len,
+                                    int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim, int32_t dtype, float scale,
+                                    void* out, int32_t* status, void* stream) {
+  return doc_attention_tc_impl(q, q_stride_b, q_stride_h, q_stride_s, k, v, k_stride_b, k_stride_h, k_stride_s, token_index,
+                               seg_offsets, n_segments, max_segment_len, n_seq, seq_len, n_q_heads, n_kv_heads, head_dim,
+                               dtype, scale, out, nullptr, status, stream);
+}
+
+extern "C" int msa_doc_attention_tc_masked(const void* q, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                                           const void* k, const void* v, int64_t k_stride_b, int64_t k_stride_h,
+                                           int64_t k_stride_s, const int32_t* span_index, const int32_t* span_offsets,
+                                           int32_t n_segments, int32_t max_span_len, int32_t n_seq, int32_t seq_len,
+                                           int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim, int32_t dtype,
+                                           float scale, void* out, const uint32_t* valid_bits, int64_t n_bit_words,
+                                           int32_t* status, void* stream) {
+  MSA_REQUIRE(valid_bits != nullptr, "doc_attention_tc_masked: null pointer");
+  // the kernel reads bits up to 256 positions past the last token and the word after the one that holds a position
+  MSA_REQUIRE(n_seq > 0 && seq_len > 0 && n_bit_words >= ((int64_t)n_seq * seq_len + 256 + 31) / 32 + 1,
+              "doc_attention_tc_masked: the bitmap must cover every token plus 256 positions and one more word");
+  return doc_attention_tc_impl(q, q_stride_b, q_stride_h, q_stride_s, k, v, k_stride_b, k_stride_h, k_stride_s, span_index,
+                               span_offsets, n_segments, max_span_len, n_seq, seq_len, n_q_heads, n_kv_heads, head_dim,
+                               dtype, scale, out, valid_bits, status, stream);
 }
 
 extern "C" int msa_sparse_prefill_attn_tc(const void* q, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
@@ -649,5 +733,5 @@ extern "C" int msa_sparse_prefill_attn_tc(const void* q, int64_t q_stride_b, int
   p.scale_log2e = scale * 1.4426950408889634f;
   p.out = (__nv_bfloat16*)out;
   p.status = status;
-  return launch_doc_attn_tc<true>(map_q, map_k, map_v, p, n_seq, seq_len, (cudaStream_t)stream);
+  return launch_doc_attn_tc<true, false>(map_q, map_k, map_v, p, n_seq, seq_len, (cudaStream_t)stream);
 }

@@ -670,6 +670,54 @@ def doc_attention_tc(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, token_in
     return out, status
 
 
+def token_bitmap(mask: torch.Tensor) -> torch.Tensor:
+    """``mask`` (bool, any shape) as a bitmap of 32-bit words over its flattened positions, padded by the 256
+    positions and the extra word that ``doc_attention_tc_masked`` reads past the end."""
+    flat = mask.reshape(-1)
+    n = flat.numel()
+    words = (n + 256 + 31) // 32 + 1
+    padded = torch.zeros(words * 32, dtype=torch.int64, device=flat.device)
+    padded[:n] = flat
+    weights = torch.ones(32, dtype=torch.int64, device=flat.device) << torch.arange(32, device=flat.device)
+    return (padded.view(words, 32) * weights).sum(dim=1).to(torch.int32)
+
+
+def document_spans(token_index: torch.Tensor, seg_offsets: torch.Tensor):
+    """From segments given as token lists (``token_index`` int32 ascending, ``seg_offsets``) the spans that
+    ``doc_attention_tc_masked`` takes: every position from a segment's first to its last token.
+    Returns ``(span_index int32, span_offsets int32, max_span_len)`` (one read-back for the sizes)."""
+    first = token_index[seg_offsets[:-1].long()].long()
+    last = token_index[(seg_offsets[1:] - 1).long()].long()
+    length = last - first + 1
+    off = torch.nn.functional.pad(length.cumsum(0), (1, 0))
+    total, longest = torch.stack([off[-1], length.max()]).tolist()
+    index = torch.repeat_interleave(first - off[:-1], length, output_size=total) + torch.arange(total, device=first.device)
+    return index.to(torch.int32), off.to(torch.int32), int(longest)
+
+
+def doc_attention_tc_masked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, span_index: torch.Tensor,
+                            span_offsets: torch.Tensor, max_span_len: int, valid_bits: torch.Tensor, out: torch.Tensor,
+                            scale: Optional[float] = None, status: Optional[torch.Tensor] = None):
+    """``doc_attention_tc`` for documents with masked tokens inside: segments are spans of memory
+    (``document_spans``), ``valid_bits`` (``token_bitmap``) says which positions are tokens of their document; the
+    rows of the others keep what ``out`` holds.  Returns ``(out, status)``."""
+    A.need_cuda(q, k, v, span_index, span_offsets, valid_bits, out)
+    b, hq, s, d = q.shape
+    if v.stride() != k.stride() or q.stride(3) != 1 or k.stride(3) != 1:
+        raise A.MsaError("doc_attention_tc_masked: k and v must share strides and the feature axis must be contiguous")
+    if span_index.dtype != torch.int32 or span_offsets.dtype != torch.int32 or valid_bits.dtype != torch.int32:
+        raise A.MsaError("doc_attention_tc_masked: span_index, span_offsets and valid_bits must be int32")
+    if status is None:
+        status = torch.zeros(4, dtype=torch.int32, device=q.device)
+    scale = (1.0 / math.sqrt(d)) if scale is None else scale
+    A.check(A.lib().msa_doc_attention_tc_masked(
+        A.ptr(q), q.stride(0), q.stride(1), q.stride(2), A.ptr(k), A.ptr(v), k.stride(0), k.stride(1), k.stride(2),
+        A.ptr(span_index), A.ptr(span_offsets), span_offsets.numel() - 1, int(max_span_len), b, s, hq, k.shape[1], d,
+        A.dtype_code(q.dtype), float(scale), A.ptr(out), A.ptr(valid_bits.contiguous()), valid_bits.numel(), A.ptr(status),
+        A.stream_ptr(q.device)), "msa_doc_attention_tc_masked")
+    return out, status
+
+
 def qk_norm_rope(qkv: torch.Tensor, n_q_heads: int, n_kv_heads: int, q_weight: torch.Tensor, k_weight: torch.Tensor,
                  eps: float, cos: torch.Tensor, sin: torch.Tensor, q_out: Optional[torch.Tensor] = None,
                  k_out: Optional[torch.Tensor] = None):

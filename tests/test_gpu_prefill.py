@@ -303,6 +303,55 @@ def _segment_reference(q, k, v, tokens, scale):
     return O._causal_segment(q[:, tokens], k[:, tokens], v[:, tokens], scale, 0)
 
 
+@pytest.mark.parametrize("doc_lens,drop_frac,layout", [
+    ([300, 129, 700], 0.1, "token_major"),
+    ([128, 513, 40, 260], 0.3, "head_major"),       # a short document between long ones, many holes
+    ([1000], 0.02, "token_major"),
+])
+def test_doc_attention_tc_masked_matches_restatement(doc_lens, drop_frac, layout):
+    """Documents with masked tokens inside on the tcgen05 kernel: spans of memory + bitmap of the tokens that take
+    part, against the oracle's causal attention over each document's compacted token list and against the mma.sync
+    kernel; rows of masked tokens keep what the output held."""
+    from msa_b200 import ops
+    dev = torch.device("cuda:0")
+    hq, hkv, n_t = 8, 2, 3
+    g = torch.Generator().manual_seed(len(doc_lens) * 7 + 1)
+    total = sum(doc_lens)
+    drop = [n_t + int(t) for t in torch.nonzero(torch.rand(total, generator=g) < drop_frac).flatten()]
+    # the first and the last token of every document stay (a span is delimited by participating tokens)
+    edges, pos = set(), n_t
+    for n in doc_lens:
+        edges.update((pos, pos + n - 1))
+        pos += n
+    drop = [t for t in drop if t not in edges]
+    doc_ids, mask, q, k, v = _stage1_case(5, doc_lens, n_t, hq, hkv, pad=9, drop=drop)
+    s = doc_ids.shape[1]
+    if layout == "token_major":
+        q, k, v = [x.transpose(1, 2).contiguous().transpose(1, 2) for x in (q, k, v)]
+    valid = (doc_ids[0] > 0) & (mask[0] == 1)
+    segs = [[t for t in range(s) if valid[t] and doc_ids[0, t] == i + 1] for i in range(len(doc_lens))]
+    tok = torch.tensor([t for x in segs for t in x], dtype=torch.int32, device=dev)
+    seg_off = torch.tensor([0] + [len(x) for x in segs]).cumsum(0).to(torch.int32).to(dev)
+    span_tok, span_off, max_span = ops.document_spans(tok, seg_off)
+    assert span_off.tolist() == [0] + torch.tensor(doc_lens).cumsum(0).tolist() and max_span == max(doc_lens)
+    bits = ops.token_bitmap(valid.view(1, s).to(dev))
+    scale = 128 ** -0.5
+    qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    out = torch.full((1, s, hq * 128), 7.0, dtype=torch.bfloat16, device=dev)
+    _, status = ops.doc_attention_tc_masked(qd, kd, vd, span_tok, span_off, max_span, bits, out=out, scale=scale)
+    legacy, _, _ = ops.doc_attention_pool(qd, kd, vd, tok, seg_off, max(len(x) for x in segs), scale=scale)
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0]
+    ref = torch.zeros(s, hq * 128)
+    for x in segs:
+        ref[x] = _segment_reference(q[0], k[0], v[0], x, scale)
+    got = out[0].float().cpu()
+    listed = valid.clone()
+    assert (got[listed] - ref[listed]).norm() / ref[listed].norm() < 1e-2
+    assert (got[listed] - legacy[0].float().cpu()[listed]).norm() / ref[listed].norm() < 1e-2
+    assert bool((got[~listed] == 7.0).all())             # masked, template and padding rows: untouched
+
+
 @pytest.mark.parametrize("doc_lens,drop,p", [
     ([512, 64, 1, 65, 130], [], 64),
     ([100, 300, 31], [5, 6, 150, 151, 152], 64),      # masked tokens inside documents
@@ -533,7 +582,8 @@ def attn128(golden):
     pre, calls = {}, {}
     layer.o_proj.register_forward_pre_hook(lambda mod, args: pre.__setitem__("x", args[0].detach().float().cpu()))
     originals = {}
-    for name in ("doc_attention_tc", "doc_attention_pool", "sparse_prefill_attn", "assemble_context", "pool_chunks"):
+    for name in ("doc_attention_tc", "doc_attention_tc_masked", "doc_attention_pool", "sparse_prefill_attn", "assemble_context",
+                 "pool_chunks"):
         originals[name] = getattr(ops, name)
 
         def counted(*a, _n=name, **kw):
@@ -578,11 +628,12 @@ def test_stage1_unmasked_documents_on_tcgen05_kernel_match_reference_layer(attn1
     assert torch.equal(cache.cache_kwargs[0]["pooled_doc_ids"].cpu(), T(g["a_pooled_doc_ids"]))
 
 
-def test_stage1_masked_documents_on_fused_pooling_kernel_match_reference_layer(attn128):
+def test_stage1_masked_documents_on_tcgen05_kernel_match_reference_layer(attn128):
     from tests.util import T
     g, geo, layer, rope, pre, calls = attn128
     cache, attn = _run_stage1(attn128, "b")
-    assert "doc_attention_tc" not in calls and calls.get("doc_attention_pool") == 2      # documents + template
+    # documents: the tcgen05 kernel over spans + bitmap; the template: mma.sync
+    assert "doc_attention_tc" not in calls and calls.get("doc_attention_tc_masked") == 1 and calls.get("doc_attention_pool") == 1
     ref = T(g["b_attn"])
     assert _rel(attn, ref) < 1e-2
     masked = T(g["b_attention_mask"])[0] == 0
