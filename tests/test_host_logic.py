@@ -58,6 +58,18 @@ def test_argument_errors_are_reported_before_any_launch():
                                       16, None, one, one, None, one, 1 << 20, 0, one, None) == -1
     assert b"alpha must be positive" in lib.msa_last_error()
     assert lib.msa_router_keys_blocked_bytes(129, 1024) == 2 * 16 * 128 * 64 * 2
+    # tcgen05 attention entry points: dtype / head size, store layout and bitmap size are checked before any tensor map
+    bf16, f32 = A.dtype_code(torch.bfloat16), A.dtype_code(torch.float32)
+    ctx = lambda dtype, d, stride_h: lib.msa_sparse_prefill_attn_tc(
+        256, 64 * 8 * d, d, 8 * d, 256, 256, 2 * 100 * d, stride_h, 100, one, one, one, one, 2, 64, 8, 2, d, dtype, 1, 0.1,
+        256, one, None)
+    assert ctx(f32, 128, 100 * 128) == -1 and b"bf16 with head_dim 128 only" in lib.msa_last_error()
+    assert ctx(bf16, 64, 100 * 64) == -1 and b"bf16 with head_dim 128 only" in lib.msa_last_error()
+    assert ctx(bf16, 128, 101 * 128) == -1 and b"contiguous [B, Hkv, store_len, D]" in lib.msa_last_error()
+    masked = lambda words: lib.msa_doc_attention_tc_masked(
+        256, 0, 128, 8 * 128, 256, 256, 0, 128, 2 * 128, one, one, 1, 300, 1, 1000, 8, 2, 128, bf16, 0.1, 256, one, words,
+        one, None)
+    assert masked(1000 // 32) == -1 and b"bitmap must cover" in lib.msa_last_error()
     with pytest.raises(A.MsaError, match="CUDA tensors"):
         from msa_b200 import ops
         ops.pool_chunks(torch.zeros(4, 8, 128), torch.tensor([0, 4], dtype=torch.int32))
@@ -141,6 +153,26 @@ def test_tensor_layouts_the_tcgen05_attention_accepts():
     assert not ops._tc_view_ok(head_major[:, :, :10])                    # a window of tokens: heads no longer evenly spaced
     assert not ops._tc_view_ok(torch.zeros(b, h, d, s, dtype=torch.bfloat16).transpose(2, 3))   # feature axis not contiguous
     assert not ops._tc_view_ok(head_major.permute(1, 0, 2, 3).contiguous().permute(1, 0, 2, 3))  # batch inside heads
+
+
+def test_span_tables_of_documents_with_masked_tokens():
+    """ops.document_spans / ops.token_bitmap: what the tcgen05 kernel takes for documents with masked tokens inside."""
+    import torch
+    from msa_b200 import ops
+    g = torch.Generator().manual_seed(3)
+    mask = torch.rand(2, 75, generator=g) < 0.6
+    bits = ops.token_bitmap(mask)
+    flat = mask.reshape(-1)
+    assert bits.dtype == torch.int32 and bits.numel() == (150 + 256 + 31) // 32 + 1
+    for pos in range(150 + 64):
+        want = bool(flat[pos]) if pos < 150 else False
+        assert bool((int(bits[pos >> 5]) >> (pos & 31)) & 1) == want
+    # three documents as token lists with holes: spans run from the first to the last listed token
+    tok = torch.tensor([4, 5, 7, 20, 21, 22, 40, 44], dtype=torch.int32)
+    off = torch.tensor([0, 3, 6, 8], dtype=torch.int32)
+    index, span_off, longest = ops.document_spans(tok, off)
+    assert index.tolist() == [4, 5, 6, 7, 20, 21, 22, 40, 41, 42, 43, 44]
+    assert span_off.tolist() == [0, 4, 7, 12] and longest == 5 and index.dtype == span_off.dtype == torch.int32
 
 
 def test_reference_format_bank_is_detected_and_converted(tmp_path):
