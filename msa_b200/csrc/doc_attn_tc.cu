@@ -22,14 +22,26 @@
 // are loaded once the current item's last S has been issued.  Every mbarrier wait is bounded; on expiry the CTA
 // raises status[0], drains and frees TMEM.
 //
-// Bounds per 64-key tile and CTA: 524 tensor-pipe cycles by flops (S: 8 MMAs of 128x64x16, PV: 4 of 128x128x16), but
-// an S MMA reads 6 KB of operands from shared memory for 33 cycles of math, so at 128 B per clock it is bound by
-// the operand reads (48 cycles): about 640 cycles of the pipe per tile, and the pipe is shared, in order, by the two
-// CTAs of the SM.  The exponentials take 512 cycles of the SFU per warp and tile (1,024 with two CTAs).  Per-tile
-// timestamps show the MMA-issuing thread blocked on the pipe for about 1,200 of the 1,750 cycles a tile takes, while
-// the pipe counter reads 30 % (math cycles only): the kernel is bound by the pipe as this tiling uses it.  Wider S
-// tiles (128 keys per MMA, two query tiles per CTA in ping-pong) would halve the operand reads per flop; they need
-// all 512 TMEM columns, i.e. one CTA per SM.
+// Three uses of one kernel (template flags): documents (segments listed by token index, consecutive tokens);
+// documents with tokens inside them that do not take part (MASKED: a segment is the span of memory from the first to
+// the last participating token, a bitmap says which positions count; a 32-key chunk with a hole gets -inf scores
+// there and then runs the code of a full chunk; rows of the other tokens are not written); and context mode (CTX:
+// segment = sequence, queries = its run of valid tokens, keys = its entries in the compact K / V store, key j visible
+// to query row i iff j <= i + kv_len - n_q and j < kv_len, or every key when not causal; the item of the last row
+// block zero-fills the rows of the tokens that are not queries).
+//
+// Bounds per 64-key tile and CTA, measured with a kernel that only issues the instructions: an S MMA (128x64x16, both
+// operands in shared memory) takes 48 cycles, not the 32 of its math, because it reads 6 KB of operands at 128 B per
+// clock; the same with N = 128 takes 64 and with N = 256 128 cycles (the only shape at the nominal rate); a PV MMA
+// (128x128x16, P from TMEM, V MN-major) takes 64; one tile as issued here (8 S + 4 PV) takes 619 cycles, whatever the
+// number of issuing warps.  The pipe is shared, in order, by the two CTAs of the SM.  The exponentials take 512
+// cycles of the SFU per warp and tile (1,024 with two CTAs).  Per-tile timestamps show 2,040 cycles per tile and CTA
+// inside long items: the MMA-issuing thread is blocked in its 12 instructions behind the other CTA's for 1,440 of
+// them and waits for P for 600; an item boundary costs about 5,000 cycles from the last P to the next item's first
+// S.  Over a whole launch on 512-token documents the pipe is busy 38 % of the time.  Measured and dropped: S for pairs
+// of key tiles with N = 128 (fewer pipe cycles, but both S buffers must be free at once and the softmax then waits
+// after every second tile), reading an item's output out under the next item's first softmax, an L2 prefetch of the
+// next item's queries.  Wider tiles with two query tiles per CTA in ping-pong need all 512 TMEM columns (one CTA per SM).
 #include <cuda.h>
 
 #include "common.cuh"
