@@ -66,8 +66,13 @@ def pool_chunks(states: torch.Tensor, chunk_offsets: torch.Tensor, token_index: 
         if states.shape[0] != 1:
             raise A.MsaError("pool_chunks: a [B, H, T, D] input needs B == 1 (call it per row)")
         _, h, t, d = states.shape
-        states = states.contiguous()
-        tok_stride, head_stride = d, t * d
+        vec = 16 // states.element_size()
+        # any [1, H, T, D] view with a contiguous feature axis and 16-byte aligned rows is read in place (the layer's
+        # projections are token major: heads side by side in a token's row); only other layouts are copied
+        if not (states.stride(3) == 1 and states.stride(1) % vec == 0 and states.stride(2) % vec == 0
+                and states.data_ptr() % 16 == 0):
+            states = states.contiguous()
+        tok_stride, head_stride = states.stride(2), states.stride(1)
     elif states.dim() == 3:
         t, h, d = states.shape
         states = states.contiguous()

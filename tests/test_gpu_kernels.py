@@ -110,6 +110,9 @@ def test_pooling_real_shape(ops, dtype, tol, head_major):
     out = ops.pool_chunks(src, off, tok)
     assert out.shape == (ref_len.numel(), 8, 128)
     assert rel_err(out, exact) < tol
+    if head_major:   # a [1, H, T, D] view of token-major storage (what the layer's projections give) is read in place
+        view = k[0].transpose(0, 1).contiguous().to(DEV).transpose(0, 1).unsqueeze(0)
+        assert not view.is_contiguous() and torch.equal(ops.pool_chunks(view, off, tok), out)
     # the reference's own cumsum-difference formula is no closer to the exact mean
     assert rel_err(O.pool_chunks_cumsum(k_docs.float(), ref_len), exact) < 1e-5
     # reference layout + fused L2 normalisation of the router keys
