@@ -102,8 +102,11 @@ class SparseDecodeModel:
         # Where a router layer's host gather starts.  "routing": with the NEXT router layer's scoring kernel, which its
         # zero-copy reads slow by a tenth; "dense": right after the layer's attention, beside the output / MLP GEMMs,
         # which ran 2.1x slower while 24 CTAs of PCIe reads were in flight (1.3x beside 8 CTAs; 1.2x beside the same
-        # gather reading device memory).
-        self.fetch_beside = os.environ.get("MSA_B200_DECODE_FETCH_BESIDE", "routing")
+        # gather reading device memory).  Beside the scoring pays while the scoring of this rank's shard lasts at
+        # least as long as the gather (measured, 1.56M chunks, batch 32: 1 GPU 13.64 -> 13.57 ms per step, 2 GPUs
+        # 11.13 -> 10.60 ms); with a shorter scoring kernel the gather runs into the routing's collectives and the
+        # selection (4 GPUs: 7.5-7.6 ms beside the GEMMs, 8.2 ms beside the scoring).
+        self.fetch_beside = os.environ.get("MSA_B200_DECODE_FETCH_BESIDE") or self._fetch_placement()
         self.gather_ctas = int(os.environ.get("MSA_B200_DECODE_GATHER_CTAS", "24"))   # CTAs of the host gather beside the step's kernels
         # the decode loop is cut at the first router layer (see step_pipelined)
         self.split_layer = min(self.router_layers) if (self.router_layers and service is not None) else s.num_layers
@@ -193,6 +196,20 @@ class SparseDecodeModel:
         if deferred is not None:
             self._issue_fetch(*deferred, fetch_done)
         return x, pending
+
+    def _fetch_placement(self):
+        """"routing" when streaming this rank's router keys of one layer (at 6.5 TB/s) takes at least as long as reading
+        this rank's share of a layer's winners from host memory, else "dense".  Host reads: 48 GB/s for one GPU, and
+        about 80 GB/s for all GPUs of the node together (measured per GPU: 35 GB/s at 2, 28 at 4, 10 at 8)."""
+        if self.svc is None or not self.router_layers:
+            return "dense"
+        rk = self.svc.blocks[min(self.router_layers)].rk
+        s = self.s
+        world = max(1, self.svc.world_size)
+        scoring_s = rk.numel() * rk.element_size() / 6.5e12
+        fetch_bytes = self.batch * self.retrieved * 2 * s.n_kv_heads * s.head_dim * self.dtype.itemsize / world
+        gather_s = fetch_bytes / min(48e9, 80e9 / world)
+        return "routing" if scoring_s >= gather_s else "dense"
 
     def _issue_fetch(self, routed, l, fetch_done):
         """Fetch the winners' K/V of router layer ``l`` on the side stream, from this point of the main stream on,
