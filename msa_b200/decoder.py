@@ -203,7 +203,10 @@ class SparseDecodeModel:
         about 80 GB/s for all GPUs of the node together (measured per GPU: 35 GB/s at 2, 28 at 4, 10 at 8)."""
         if self.svc is None or not self.router_layers:
             return "dense"
-        rk = self.svc.blocks[min(self.router_layers)].rk
+        blk = self.svc.blocks[min(self.router_layers)]
+        rk = blk.rk if blk.rk is not None else blk.rk_blocked
+        if rk is None:
+            return "dense"
         s = self.s
         world = max(1, self.svc.world_size)
         scoring_s = rk.numel() * rk.element_size() / 6.5e12

@@ -89,10 +89,15 @@ def _routed_model(seed):
                              device=DEV, seed=seed)
 
 
-def test_pipelined_loop_produces_the_same_tokens_and_caches():
+@pytest.mark.parametrize("beside", ["dense", "routing"])
+def test_pipelined_loop_produces_the_same_tokens_and_caches(beside, monkeypatch):
     """step_pipelined is step rotated to start at the first router layer: same tokens, same caches (the
-    retrieved segments included), eagerly and replayed from a CUDA graph."""
+    retrieved segments included), eagerly and replayed from a CUDA graph; with a layer's host gather started right
+    after its attention ("dense") or with the next router layer's scoring ("routing")."""
+    assert _routed_model(9).fetch_beside == "dense"        # what the rule picks for a bank this small
+    monkeypatch.setenv("MSA_B200_DECODE_FETCH_BESIDE", beside)
     a, b, c = _routed_model(9), _routed_model(9), _routed_model(9)
+    assert a.fetch_beside == beside
     n = 5
     toks_a = [a.step().cpu() for _ in range(n)]
     b.prime()
