@@ -589,6 +589,57 @@ def _secondary_line(args, metric, unit, value, leg, clocks, extra=None):
     print(json.dumps(line))
 
 
+def leg_stage1_attention(torch, ops, dev, pk, n_docs=256, doc_len=512):
+    """Stage-1 attention inside documents on the tcgen05 kernel (benchmark config 2 shapes; 256 documents keep it short,
+    time is linear in documents); executed flops (whole 128 x 128 tiles) over the kernel's own time against the burst
+    bf16 rate."""
+    g = torch.Generator(device=dev)
+    g.manual_seed(2100)
+    t = n_docs * doc_len
+    seg = torch.arange(0, t + 1, doc_len, dtype=torch.int32, device=dev)
+    tok = torch.arange(t, dtype=torch.int32, device=dev)
+    q = torch.randn((1, HQ, t, D), generator=g, device=dev).to(torch.bfloat16)
+    k = torch.randn((1, HKV, t, D), generator=g, device=dev).to(torch.bfloat16)
+    v = torch.randn((1, HKV, t, D), generator=g, device=dev).to(torch.bfloat16)
+    out = torch.zeros((1, t, HQ * D), dtype=torch.bfloat16, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    ms = _time_ms(torch, lambda: ops.doc_attention_tc(q, k, v, tok, seg, doc_len, out=out, status=status), 10, 3)
+    if status.tolist()[0] != 0:
+        raise RuntimeError("a bounded wait ran out inside doc_attn_tc_kernel")
+    n_tiles = n_docs * HQ * sum(range(1, doc_len // 128 + 1))
+    tf = 4.0 * 128 * 128 * 128 * n_tiles / (ms / 1e3) / 1e12
+    return {"kernel": "doc_attn_tc_kernel", "ms": ms, "bound": "tensor", "tflops_executed": tf, "peak_tflops": pk["tflops_burst"],
+            "frac": tf / pk["tflops_burst"], "tokens_per_s": t / (ms / 1e3),
+            "workload": f"{n_docs} documents x {doc_len} tokens, 32q/8kv heads, d=128, bf16 (q and out {t * HQ * D * 2 / 1e9:.1f} GB each, > L2)"}
+
+
+def leg_stage2_attention(torch, ops, dev, pk, b=32, s_q=128, t_len=3, n_layers=6):
+    """Stage 2 of one layer: context assembly + attention of 32 queries x 128 tokens over 3 template + 128 retrieved
+    entries, on the tcgen05 kernel's context mode; several layers' tensors rotate so that the inputs exceed L2."""
+    g = torch.Generator(device=dev)
+    g.manual_seed(2200)
+    n_ret = TOP_K * CHUNKS_PER_DOC
+    mk = lambda *shape: torch.randn(shape, generator=g, device=dev).to(torch.bfloat16)
+    layers = [dict(q=mk(b, HQ, s_q, D), k=mk(b, HKV, s_q, D), v=mk(b, HKV, s_q, D), tk=mk(1, HKV, t_len, D), tv=mk(1, HKV, t_len, D),
+                   sk=mk(HKV, b * n_ret, D), sv=mk(HKV, b * n_ret, D)) for _ in range(n_layers)]
+    valid = torch.ones((b, s_q), dtype=torch.bool, device=dev)
+    n_sel = torch.full((b,), n_ret, dtype=torch.int64, device=dev)
+    max_kv = t_len + n_ret + s_q
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+
+    def step():
+        for L in layers:
+            ks, vs, st, ln, qt, nq, _ = ops.assemble_context(L["tk"], L["tv"], L["sk"], L["sv"], n_sel, L["k"], L["v"], valid, max_kv, 0)
+            ops.sparse_prefill_attn(L["q"], ks, vs, st, ln, qt, nq, q_runs=True, status=status)
+    ms = _time_ms(torch, step, 50, 3) / n_layers
+    if status.tolist()[0] != 0:
+        raise RuntimeError("a bounded wait ran out inside the stage-2 attention kernel")
+    alg = 2 * b * HQ * s_q * D * 2 + 4 * b * max_kv * HKV * D * 2
+    return {"kernel": "assemble_kernel + doc_attn_tc_kernel (context mode)", "ms": ms, "bound": "latency", "algorithmic_bytes": alg,
+            "achieved_gbs": alg / (ms / 1e3) / 1e9, "frac": alg / (ms / 1e3) / 1e9 / pk["hbm_gbs"], "peak_gbs": pk["hbm_gbs"],
+            "workload": f"{b} queries x {s_q} tokens, {t_len} template + {n_ret} retrieved entries, 32q/8kv heads, d=128, bf16"}
+
+
 def run_secondary(args):
     import torch
     from msa_b200 import ops
@@ -1082,6 +1133,12 @@ def run_ours(args):
                                  "workload": leg["workload"],
                                  **{k_: leg[k_] for k_ in ("route_kernel_ms", "route_kernel_frac", "route_kernel_note", "layer_step",
                                                            "row_major_keys", "fused_score_select", "tokens_per_s") if k_ in leg}}
+            except Exception as e:
+                kernels[name] = {"error": f"{type(e).__name__}: {e}"}
+        for name, fn in (("stage1_attention", leg_stage1_attention), ("stage2_attention", leg_stage2_attention)):
+            try:
+                kernels[name] = fn(torch, ops, dev, pk)
+                torch.cuda.empty_cache()
             except Exception as e:
                 kernels[name] = {"error": f"{type(e).__name__}: {e}"}
         if world > 1:
