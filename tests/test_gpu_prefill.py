@@ -151,6 +151,27 @@ def test_context_attention_on_tcgen05_kernel_without_causal_mask():
     assert got[~new_mask].abs().sum().item() == 0
 
 
+def test_run_check_that_picks_the_stage2_kernel():
+    """MemorySparseAttention._valid_runs: 1 when every row's valid tokens are one run (left / right padding, empty rows),
+    0 when a row has a hole; the second word is the status of the earlier tensor-core attention launches."""
+    from types import SimpleNamespace
+    from msa_b200.attention import MemorySparseAttention
+    dev = torch.device("cuda:0")
+    cache = SimpleNamespace(meta={})
+    runs = torch.zeros(4, 12, dtype=torch.bool, device=dev)
+    runs[0] = True
+    runs[1, 5:] = True
+    runs[2, :3] = True                      # row 3 stays empty
+    assert MemorySparseAttention._valid_runs(None, runs, cache).tolist() == [1, 0]
+    hole = runs.clone()
+    hole[1, 8] = False
+    assert MemorySparseAttention._valid_runs(None, hole, cache).tolist() == [0, 0]
+    cache.meta["_msa_b200_attn_status"][0] = 6          # what a kernel that gave up leaves behind
+    assert MemorySparseAttention._valid_runs(None, runs, cache).tolist() == [1, 6]
+    with pytest.raises(Exception, match="bounded barrier wait"):
+        MemorySparseAttention._check_attn_status(6)
+
+
 def test_assemble_fp32_and_overflow_flag():
     from msa_b200 import ops
     dev = torch.device("cuda:0")
