@@ -155,6 +155,28 @@ def test_tensor_layouts_the_tcgen05_attention_accepts():
     assert not ops._tc_view_ok(head_major.permute(1, 0, 2, 3).contiguous().permute(1, 0, 2, 3))  # batch inside heads
 
 
+def test_decode_loop_places_the_host_gather_by_shard_and_fetch_size():
+    """SparseDecodeModel._fetch_placement on the benchmark's sizes: beside the scoring kernel on 1-2 GPUs, beside the
+    dense GEMMs from 4 GPUs on, and beside the GEMMs whenever there is no bank to score."""
+    from types import SimpleNamespace
+    import torch
+    from msa_b200.decoder import DecoderShape, SparseDecodeModel
+    shape = DecoderShape()
+    chunks = 1_562_560
+    picks = {}
+    for world in (1, 2, 4, 8):
+        rk = torch.empty((chunks // world, shape.n_kv_heads, shape.head_dim), dtype=torch.bfloat16, device="meta")
+        for stored in ("rows", "blocked"):
+            blk = SimpleNamespace(rk=rk if stored == "rows" else None, rk_blocked=None if stored == "rows" else rk)
+            me = SimpleNamespace(svc=SimpleNamespace(blocks={18: blk, 19: blk}, world_size=world), router_layers={18, 19}, s=shape,
+                                 batch=32, retrieved=128, dtype=torch.bfloat16)
+            picks[world, stored] = SparseDecodeModel._fetch_placement(me)
+    assert [picks[w, "rows"] for w in (1, 2, 4, 8)] == ["routing", "routing", "dense", "dense"]
+    assert all(picks[w, "blocked"] == picks[w, "rows"] for w in (1, 2, 4, 8))
+    empty = SimpleNamespace(svc=None, router_layers=set(), s=shape, batch=32, retrieved=128, dtype=torch.bfloat16)
+    assert SparseDecodeModel._fetch_placement(empty) == "dense"
+
+
 def test_span_tables_of_documents_with_masked_tokens():
     """ops.document_spans / ops.token_bitmap: what the tcgen05 kernel takes for documents with masked tokens inside."""
     import torch
