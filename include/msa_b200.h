@@ -316,6 +316,22 @@ int msa_gather_plan(const int64_t* sel_local, const int32_t* sel_rank, int32_t n
                     int64_t* plan, int64_t* n_sel, int64_t* total, int64_t* total_host_mapped,
                     int32_t* status, void* stream);
 
+/* msa_gather_plan_resident: msa_gather_plan for a decode loop that refreshes the same per-sample segment every step
+ * (what a per-step doc_query, src/msa_service.py:1193-1283, would fetch again and again).  A sample's room is k
+ * slots of slot_len entries; resident [n_seq, k] int64 (filled with -1 by the caller before the first call, then
+ * owned by this function) records which document (owner rank << 40 | local id) each slot holds.  For a sample whose
+ * k winners are all valid and hold exactly slot_len entries each, the winners that already sit in a slot are left
+ * there and only the others are planned, into the slots of the documents that dropped out (attention is indifferent
+ * to the order of the entries); n_sel[b] is then k * slot_len.  Any other sample is planned in full, as by
+ * msa_gather_plan with sample_stride = k * slot_len, and its row of the table is cleared.
+ */
+int msa_gather_plan_resident(const int64_t* sel_local, const int32_t* sel_rank, int32_t n_seq, int32_t k,
+                             int32_t world, const int64_t* shard_doc_base, int64_t n_dir_rows,
+                             const int64_t* doc_chunk_offset, const int32_t* doc_chunk_len,
+                             const uint64_t* shard_kv_base, int64_t chunk_bytes, int32_t slot_len,
+                             int64_t* resident, int64_t* plan, int64_t* n_sel, int64_t* total, int32_t* status,
+                             void* stream);
+
 int msa_gather_run(const int64_t* plan, int32_t n_items, int32_t dtype, int32_t n_kv_heads,
                    int32_t head_dim, void* out_k, void* out_v, int64_t out_head_stride,
                    int64_t out_entries, int64_t out_sample_stride, int32_t max_ctas, void* stream);

@@ -22,7 +22,7 @@ ROUTE_FORCE_SIMT, ROUTE_NO_INIT, ROUTE_KEYS_BLOCKED = 1, 2, 4
 
 EXPORTS = [
     "msa_abi_version", "msa_last_error", "msa_bookkeeping_workspace_bytes", "msa_chunk_bookkeeping", "msa_pool_chunks", "msa_fold_queries",
-    "msa_route_s_pad", "msa_router_keys_blocked_bytes", "msa_router_keys_block", "msa_selftest_bounded_wait", "msa_route_table_reset", "msa_route_scores", "msa_route_chunk_scores", "msa_route_reduce_chunks", "msa_route_score_select_workspace_bytes", "msa_route_score_select", "msa_topk_workspace_bytes", "msa_topk_select", "msa_topk_merge", "msa_gather_plan",
+    "msa_route_s_pad", "msa_router_keys_blocked_bytes", "msa_router_keys_block", "msa_selftest_bounded_wait", "msa_route_table_reset", "msa_route_scores", "msa_route_chunk_scores", "msa_route_reduce_chunks", "msa_route_score_select_workspace_bytes", "msa_route_score_select", "msa_topk_workspace_bytes", "msa_topk_select", "msa_topk_merge", "msa_gather_plan", "msa_gather_plan_resident",
     "msa_gather_run", "msa_bank_register_host", "msa_bank_unregister_host", "msa_assemble_context", "msa_sparse_prefill_attn", "msa_append_segment", "msa_doc_attention_pool", "msa_doc_attention_tc", "msa_doc_attention_tc_masked", "msa_sparse_prefill_attn_tc", "msa_qk_norm_rope", "msa_add_rmsnorm", "msa_silu_mul", "msa_decode_workspace_bytes", "msa_sparse_decode_attn",
     "msa_decode_static_scratch_bytes", "msa_sparse_decode_attn_static",
 ]
@@ -71,6 +71,7 @@ def lib() -> C.CDLL:
         l.msa_topk_select.argtypes = [vp, i64, i32, i32, i32, vp, vp, vp, vp, vp, i64, vp]
         l.msa_topk_merge.argtypes = [vp, vp, vp, i64, i64, i32, i32, i32, i32, f32, vp, vp, vp, vp, vp]
         l.msa_gather_plan.argtypes = [vp, vp, i32, i32, i32, vp, i64, vp, vp, vp, i64, i64, vp, vp, vp, vp, vp, vp]
+        l.msa_gather_plan_resident.argtypes = [vp, vp, i32, i32, i32, vp, i64, vp, vp, vp, i64, i32, vp, vp, vp, vp, vp, vp]
         l.msa_gather_run.argtypes = [vp, i32, i32, i32, i32, vp, vp, i64, i64, i64, i32, vp]
         l.msa_bank_register_host.argtypes = [vp, i64, vp]
         l.msa_bank_unregister_host.argtypes = [vp]

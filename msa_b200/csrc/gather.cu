@@ -22,7 +22,7 @@ gather_plan_kernel(const int64_t* __restrict__ sel_local, const int32_t* __restr
                    const int64_t* __restrict__ doc_chunk_offset, const int32_t* __restrict__ doc_chunk_len,
                    const uint64_t* __restrict__ shard_kv_base, long long chunk_bytes, long long sample_stride,
                    int64_t* __restrict__ plan, int64_t* __restrict__ n_sel, int64_t* __restrict__ total,
-                   int64_t* total_host, int32_t* __restrict__ status) {
+                   int64_t* total_host, int32_t* __restrict__ status, int64_t* __restrict__ resident, int slot_len) {
   __shared__ long long s_scan[kPlanThreads];
   __shared__ long long s_carry;
   if (threadIdx.x == 0) s_carry = 0;
@@ -48,6 +48,44 @@ gather_plan_kernel(const int64_t* __restrict__ sel_local, const int32_t* __restr
         key[p] = kk;
       }
       if (dropped && status) atomicAdd(status + 2, dropped);
+      // Resident set (a decode loop that refreshes the same segment every step): the sample's room is k slots of
+      // slot_len entries, resident[b][s] is the document whose entries slot s holds.  When the k winners are all
+      // valid and every one holds exactly slot_len entries, the winners that are already in a slot stay where they
+      // are and only the others are planned, into the slots of the documents that dropped out.  Any other sample
+      // is planned in full (below) and its table is cleared.
+      bool keep_slots = resident != nullptr && n == k && sample_stride == (long long)k * slot_len;
+      if (keep_slots)
+        for (int j = 0; j < k && keep_slots; ++j) {
+          const long long d = shard_doc_base[(int)(key[j] >> 40)] + (key[j] & ((1ll << 40) - 1));
+          keep_slots = doc_chunk_len[d] == slot_len;
+        }
+      if (keep_slots) {
+        int64_t* res = resident + (long long)b * k;
+        unsigned long long kept = 0ull, hit = 0ull;       // slots that keep their document; winners that have a slot
+        for (int s = 0; s < k; ++s) {
+          const long long have = res[s];
+          for (int j = 0; j < k; ++j)
+            if (have == key[j]) { kept |= 1ull << s; hit |= 1ull << j; break; }
+        }
+        int s = 0;
+        for (int j = 0; j < k; ++j) {
+          int64_t* row = plan + ((long long)b * k + j) * 4;
+          row[3] = b;
+          if ((hit >> j) & 1ull) { row[0] = 0; row[1] = 0; row[2] = 0; continue; }
+          while ((kept >> s) & 1ull) ++s;
+          kept |= 1ull << s;
+          res[s] = key[j];
+          const int r = (int)(key[j] >> 40);
+          const long long d = shard_doc_base[r] + (key[j] & ((1ll << 40) - 1));
+          row[0] = (int64_t)(shard_kv_base[r] + (unsigned long long)(doc_chunk_offset[d] * chunk_bytes));
+          row[1] = slot_len;
+          row[2] = (long long)s * slot_len;
+        }
+        mine = (long long)k * slot_len;
+        n_sel[b] = mine;
+      } else {
+      if (resident != nullptr)
+        for (int s = 0; s < k; ++s) resident[(long long)b * k + s] = -1;
       for (int j = 0; j < k; ++j) {
         int64_t* row = plan + ((long long)b * k + j) * 4;
         long long len = 0;
@@ -67,6 +105,7 @@ gather_plan_kernel(const int64_t* __restrict__ sel_local, const int32_t* __restr
         if (len > 0) mine += len;
       }
       n_sel[b] = mine;
+      }
     }
     // exclusive scan of the per-sample totals across the CTA, carried between rounds
     s_scan[threadIdx.x] = mine;
@@ -160,12 +199,12 @@ static int prefer_shared_carveout() {
   return MSA_OK;
 }
 
-extern "C" int msa_gather_plan(const int64_t* sel_local, const int32_t* sel_rank, int32_t n_seq, int32_t k,
-                               int32_t world, const int64_t* shard_doc_base, int64_t n_dir_rows,
-                               const int64_t* doc_chunk_offset, const int32_t* doc_chunk_len,
-                               const uint64_t* shard_kv_base, int64_t chunk_bytes, int64_t sample_stride,
-                               int64_t* plan, int64_t* n_sel, int64_t* total, int64_t* total_host_mapped,
-                               int32_t* status, void* stream) {
+namespace {
+int gather_plan_launch(const int64_t* sel_local, const int32_t* sel_rank, int32_t n_seq, int32_t k, int32_t world,
+                       const int64_t* shard_doc_base, int64_t n_dir_rows, const int64_t* doc_chunk_offset,
+                       const int32_t* doc_chunk_len, const uint64_t* shard_kv_base, int64_t chunk_bytes,
+                       int64_t sample_stride, int64_t* plan, int64_t* n_sel, int64_t* total, int64_t* total_host_mapped,
+                       int32_t* status, int64_t* resident, int32_t slot_len, void* stream) {
   MSA_REQUIRE(sel_local && shard_doc_base && doc_chunk_offset && doc_chunk_len && shard_kv_base && plan && n_sel &&
                   total, "gather_plan: null pointer");
   MSA_REQUIRE(n_seq >= 0 && k >= 1 && k <= kPlanMaxK && world >= 1, "gather_plan: bad sizes (k must be <= %d)",
@@ -174,12 +213,38 @@ extern "C" int msa_gather_plan(const int64_t* sel_local, const int32_t* sel_rank
               (long long)n_dir_rows, world);
   MSA_REQUIRE(chunk_bytes > 0 && chunk_bytes % 16 == 0, "gather_plan: chunk_bytes must be a multiple of 16");
   MSA_REQUIRE(sample_stride >= 0, "gather_plan: sample_stride must not be negative");
+  MSA_REQUIRE(resident == nullptr || (slot_len > 0 && sample_stride == (int64_t)k * slot_len),
+              "gather_plan: a resident table needs sample_stride == k * slot_len");
   MSA_OK_OR_RETURN(prefer_shared_carveout());
   gather_plan_kernel<<<1, kPlanThreads, 0, (cudaStream_t)stream>>>(
       sel_local, sel_rank, n_seq, k, world, shard_doc_base, n_dir_rows, doc_chunk_offset, doc_chunk_len, shard_kv_base,
-      chunk_bytes, sample_stride, plan, n_sel, total, total_host_mapped, status);
+      chunk_bytes, sample_stride, plan, n_sel, total, total_host_mapped, status, resident, slot_len);
   MSA_LAUNCH_OK("gather_plan_kernel");
   return MSA_OK;
+}
+}  // namespace
+
+extern "C" int msa_gather_plan(const int64_t* sel_local, const int32_t* sel_rank, int32_t n_seq, int32_t k,
+                               int32_t world, const int64_t* shard_doc_base, int64_t n_dir_rows,
+                               const int64_t* doc_chunk_offset, const int32_t* doc_chunk_len,
+                               const uint64_t* shard_kv_base, int64_t chunk_bytes, int64_t sample_stride,
+                               int64_t* plan, int64_t* n_sel, int64_t* total, int64_t* total_host_mapped,
+                               int32_t* status, void* stream) {
+  return gather_plan_launch(sel_local, sel_rank, n_seq, k, world, shard_doc_base, n_dir_rows, doc_chunk_offset, doc_chunk_len,
+                            shard_kv_base, chunk_bytes, sample_stride, plan, n_sel, total, total_host_mapped, status, nullptr,
+                            0, stream);
+}
+
+extern "C" int msa_gather_plan_resident(const int64_t* sel_local, const int32_t* sel_rank, int32_t n_seq, int32_t k,
+                                        int32_t world, const int64_t* shard_doc_base, int64_t n_dir_rows,
+                                        const int64_t* doc_chunk_offset, const int32_t* doc_chunk_len,
+                                        const uint64_t* shard_kv_base, int64_t chunk_bytes, int32_t slot_len,
+                                        int64_t* resident, int64_t* plan, int64_t* n_sel, int64_t* total,
+                                        int32_t* status, void* stream) {
+  MSA_REQUIRE(resident != nullptr, "gather_plan_resident: null pointer");
+  return gather_plan_launch(sel_local, sel_rank, n_seq, k, world, shard_doc_base, n_dir_rows, doc_chunk_offset, doc_chunk_len,
+                            shard_kv_base, chunk_bytes, (int64_t)k * slot_len, plan, n_sel, total, nullptr, status, resident,
+                            slot_len, stream);
 }
 
 extern "C" int msa_gather_run(const int64_t* plan, int32_t n_items, int32_t dtype, int32_t n_kv_heads,

@@ -124,6 +124,12 @@ class SparseDecodeModel:
         # checked by check_fetch_counts().
         self._n_sel_min = {l: torch.full((), retrieved_entries, dtype=torch.int64, device=device)
                            for l in self.router_layers}
+        # Which document every slot of a sequence's retrieved segment holds, per router layer: a document that is
+        # selected again in the next step keeps its entries and is not read from the host again.
+        self._resident = {}
+        top_k = service.model_config.doc_top_k if service is not None else 0
+        if top_k and retrieved_entries % top_k == 0 and os.environ.get("MSA_B200_DECODE_RESIDENT", "1") != "0":
+            self._resident = {l: torch.full((batch, top_k), -1, dtype=torch.int64, device=device) for l in self.router_layers}
 
     # ------------------------------------------------------------------------------------
     def _rope(self, x, cos, sin):
@@ -226,7 +232,7 @@ class SparseDecodeModel:
             self._mark("fetch_start", l, self.fetch_stream)
             # the gather writes every sequence's entries into its own retrieved segment of the cache
             n_sel = self.svc.fetch_into(local, rank, l, self.k_cache[l], self.v_cache[l], s.template_len,
-                                        self.retrieved, max_ctas=self.gather_ctas)
+                                        self.retrieved, max_ctas=self.gather_ctas, resident=self._resident.get(l))
             torch.minimum(self._n_sel_min[l], n_sel.min(), out=self._n_sel_min[l])
             for t_ in (local, rank, n_sel):
                 t_.record_stream(self.fetch_stream)
@@ -312,5 +318,7 @@ class SparseDecodeModel:
                                f"the decode loop's cache layout holds exactly {self.retrieved} retrieved entries")
 
     def reset(self):
+        for table in self._resident.values():      # the caller may refill the caches: no segment's content is known any more
+            table.fill_(-1)
         self.kv_len.fill_(self.ctx0)
         self.positions.fill_(self.s.template_len + 16 + (self.ctx0 - self.s.template_len - self.retrieved))

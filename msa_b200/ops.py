@@ -392,10 +392,12 @@ def topk_merge(cand_scores: torch.Tensor, cand_local: torch.Tensor, cand_global:
 def gather_plan(sel_local: torch.Tensor, sel_rank: Optional[torch.Tensor], world: int, shard_doc_base: torch.Tensor,
                 doc_chunk_offset: torch.Tensor, doc_chunk_len: torch.Tensor, shard_kv_base: torch.Tensor,
                 chunk_bytes: int, total_host: Optional[torch.Tensor] = None, sample_stride: int = 0,
-                status: Optional[torch.Tensor] = None):
+                status: Optional[torch.Tensor] = None, resident: Optional[torch.Tensor] = None):
     """Plan the fetch of the winners ``sel_local[B, k]`` (owner ranks ``sel_rank``).  ``sample_stride`` 0 packs
     the samples one after another; > 0 gives every sample that many entries of room (see ``gather_run``).
-    Winners outside the directory are dropped and counted in ``status[2]``.
+    Winners outside the directory are dropped and counted in ``status[2]``.  ``resident`` ``[B, k]`` int64 (-1 =
+    empty, updated in place; needs ``sample_stride`` = k slots of equal length): winners whose entries the sample's
+    segment already holds are not planned again, the others go into the slots that became free.
     Returns ``(plan[B*k, 4], n_sel[B], total[1])``."""
     A.need_cuda(sel_local, sel_rank, shard_doc_base, doc_chunk_offset, doc_chunk_len, shard_kv_base, status)
     n_seq, k = sel_local.shape
@@ -407,6 +409,18 @@ def gather_plan(sel_local: torch.Tensor, sel_rank: Optional[torch.Tensor], world
     plan = torch.empty((n_seq * k, 4), dtype=torch.int64, device=dev)
     n_sel = torch.empty((n_seq,), dtype=torch.int64, device=dev)
     total = torch.empty((1,), dtype=torch.int64, device=dev)
+    if resident is not None:
+        A.need_cuda(resident)
+        if resident.dtype != torch.int64 or tuple(resident.shape) != (n_seq, k) or not resident.is_contiguous():
+            raise A.MsaError("gather_plan: resident must be a contiguous int64 [B, k] tensor")
+        if sample_stride <= 0 or sample_stride % k != 0:
+            raise A.MsaError("gather_plan: a resident table needs sample_stride = k slots of equal length")
+        A.check(A.lib().msa_gather_plan_resident(
+            A.ptr(sel_local.contiguous()), A.ptr(sel_rank.contiguous() if sel_rank is not None else None), n_seq, k, world,
+            A.ptr(shard_doc_base), doc_chunk_len.numel(), A.ptr(doc_chunk_offset), A.ptr(doc_chunk_len), A.ptr(shard_kv_base),
+            chunk_bytes, int(sample_stride) // k, A.ptr(resident), A.ptr(plan), A.ptr(n_sel), A.ptr(total), A.ptr(status),
+            A.stream_ptr(dev)), "msa_gather_plan_resident")
+        return plan, n_sel, total
     A.check(A.lib().msa_gather_plan(A.ptr(sel_local.contiguous()), A.ptr(sel_rank.contiguous() if sel_rank is not None else None),
                                     n_seq, k, world, A.ptr(shard_doc_base), doc_chunk_len.numel(), A.ptr(doc_chunk_offset),
                                     A.ptr(doc_chunk_len), A.ptr(shard_kv_base), chunk_bytes, int(sample_stride),

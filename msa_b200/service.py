@@ -332,12 +332,15 @@ class MSAService(Memory, MemoryClientBase):
         return k, v, n_sel
 
     def fetch_into(self, winner_local: torch.Tensor, winner_rank: torch.Tensor, layer_idx: int, k_cache: torch.Tensor,
-                   v_cache: torch.Tensor, first_position: int, room: int, max_ctas: int = 0):
+                   v_cache: torch.Tensor, first_position: int, room: int, max_ctas: int = 0,
+                   resident: Optional[torch.Tensor] = None):
         """``fetch`` for a decode loop: the winners' K/V go straight into positions ``first_position ..
         first_position + room`` of ``[B, Hkv, L, D]`` caches, sample b's entries into row b (no packed staging
         buffer, no copies afterwards, no read-back).  A sample whose documents hold more than ``room`` entries
-        is cut; one that holds fewer leaves the tail of its segment as it was.  Returns ``n_sel[B]`` (entries
-        written per sample, on the device)."""
+        is cut; one that holds fewer leaves the tail of its segment as it was.  ``resident`` (int64 ``[B, k]``, -1
+        before the first step, the caller's for this layer's segment): documents a sample selected again keep their
+        entries and only the new ones are read from the host (``ops.gather_plan``).  Returns ``n_sel[B]`` (entries
+        valid per sample, on the device)."""
         if self._directory is None:
             self.publish_directory()
         base, offs, ln, kv_base = self._directory
@@ -345,7 +348,7 @@ class MSAService(Memory, MemoryClientBase):
         blk = self.blocks[layer_idx]
         chunk_bytes = 2 * g.num_key_value_heads * g.head_dim * blk.kv.element_size()
         plan, n_sel, _ = ops.gather_plan(winner_local, winner_rank, self.world_size, base, offs, ln, kv_base[layer_idx],
-                                         chunk_bytes, sample_stride=room, status=self._status)
+                                         chunk_bytes, sample_stride=room, status=self._status, resident=resident)
         ops.gather_run(plan, blk.kv.dtype, g.num_key_value_heads, g.head_dim, room, max_ctas,
                        out=(k_cache, v_cache, first_position))
         return n_sel

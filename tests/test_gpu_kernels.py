@@ -563,6 +563,60 @@ def test_gather_plan_drops_winners_outside_their_shard(ops):
     assert torch.equal(vc[1, :, first:first + room].cpu(), torch.cat([banks[0][0:2, 1], banks[1][4:6, 1]]).permute(1, 0, 2))
 
 
+def test_gather_plan_keeps_documents_that_are_selected_again(ops):
+    """Resident set of a decode loop: over three steps a sample's winners partly repeat; only the new documents are
+    planned (into the slots of those that dropped out), the segment always holds exactly the step's winners, and a
+    sample with an invalid winner or a document of another length is planned in full with its table cleared."""
+    g = torch.Generator().manual_seed(8)
+    world, hkv, d, k, slot = 2, 8, 128, 4, 2
+    chunks = [[2] * 10, [2] * 7 + [3]]                 # every document 2 chunks, except the last of shard 1
+    banks = [torch.randn(sum(c), 2, hkv, d, generator=g).to(torch.bfloat16).pin_memory() for c in chunks]
+    lens = [torch.tensor([0] + c) for c in chunks]
+    offs = [torch.cumsum(torch.cat([torch.zeros(1, dtype=torch.long), ln[:-1]]), 0) for ln in lens]
+    bases = torch.tensor([0, 11])
+    common = (world, bases.to(DEV), torch.cat(offs).to(DEV), torch.cat(lens).to(torch.int32).to(DEV),
+              torch.tensor([b.data_ptr() for b in banks], dtype=torch.int64).to(DEV), 2 * hkv * d * 2)
+    first, room = 3, k * slot
+    kc = torch.zeros(3, hkv, first + room + 1, d, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    resident = torch.full((3, k), -1, dtype=torch.int64, device=DEV)
+    steps = [
+        # (rank, local id) per sample; sample 2 has an invalid winner in step 2 and the 3-chunk document in step 3
+        [[(0, 1), (0, 2), (1, 3), (1, 4)], [(0, 5), (0, 6), (0, 7), (1, 1)], [(0, 1), (0, 2), (0, 3), (0, 4)]],
+        [[(0, 2), (1, 4), (0, 9), (1, 5)], [(0, 5), (0, 6), (0, 7), (1, 1)], [(0, 1), (0, 2), (0, 3), (0, -1)]],
+        [[(1, 5), (0, 9), (0, 10), (0, 2)], [(1, 2), (0, 6), (1, 6), (0, 8)], [(0, 1), (0, 2), (0, 3), (1, 8)]],
+    ]
+    planned = []
+    for winners in steps:
+        sel_rank = torch.tensor([[r for r, _ in row] for row in winners], dtype=torch.int32, device=DEV)
+        sel_local = torch.tensor([[i for _, i in row] for row in winners], dtype=torch.int64, device=DEV)
+        before = kc.clone()
+        plan, n_sel, _ = ops.gather_plan(sel_local, sel_rank, *common, sample_stride=room, resident=resident)
+        ops.gather_run(plan, torch.bfloat16, hkv, d, room, out=(kc, vc, first))
+        torch.cuda.synchronize()
+        rows = plan.cpu().view(3, k, 4)
+        planned.append([int((rows[b, :, 1] > 0).sum()) for b in range(3)])
+        table = resident.cpu()
+        for b, row in enumerate(winners):
+            full = all(i > 0 and chunks[r][i - 1] == slot for r, i in row)
+            if not full:
+                assert table[b].tolist() == [-1] * k
+                continue
+            assert int(n_sel[b]) == room
+            assert sorted(table[b].tolist()) == sorted((r << 40) | i for r, i in row)
+            for s_ in range(k):      # every slot holds the document the table names
+                r, i = int(table[b, s_]) >> 40, int(table[b, s_]) & ((1 << 40) - 1)
+                o = int(offs[r][i])
+                lo = first + s_ * slot
+                assert torch.equal(kc[b, :, lo:lo + slot].cpu(), banks[r][o:o + slot, 0].permute(1, 0, 2))
+                assert torch.equal(vc[b, :, lo:lo + slot].cpu(), banks[r][o:o + slot, 1].permute(1, 0, 2))
+        assert torch.equal(kc[:, :, :first], before[:, :, :first]) and torch.equal(kc[:, :, first + room:], before[:, :, first + room:])
+    # sample 0: 4 new, then 2 of 4 repeat, then 3 of 4 repeat; sample 1: 4, all repeat, 1 repeats; sample 2 falls back
+    # to a full plan in step 2 (3 valid winners) and step 3 (a longer document, cut to the room)
+    assert [p[0] for p in planned] == [4, 2, 1] and [p[1] for p in planned] == [4, 0, 3]
+    assert [p[2] for p in planned] == [4, 3, 4]
+
+
 def test_routing_skips_chunk_ids_outside_the_table(ops):
     """chunk -> document ids outside 1..n_docs never become a table column: skipped and counted in status[2]."""
     chunks = [8] * 6

@@ -41,6 +41,11 @@ def test_argument_errors_are_reported_before_any_launch():
     assert lib.msa_gather_plan(1, None, 1, 4, 1, 1, 8, 1, 1, 1, 4096, -1, 1, 1, 1, None, None, None) == -1
     assert b"sample_stride" in lib.msa_last_error()
     assert lib.msa_gather_run(1, 4, 1, 8, 128, 1, 1, 1024, 4, -16, 0, None) == -1
+    # the resident-set plan needs a table and slots of at least one entry
+    assert lib.msa_gather_plan_resident(1, None, 1, 4, 1, 1, 8, 1, 1, 1, 4096, 2, None, 1, 1, 1, None, None) == -1
+    assert b"null pointer" in lib.msa_last_error()
+    assert lib.msa_gather_plan_resident(1, None, 1, 4, 1, 1, 8, 1, 1, 1, 4096, 0, 1, 1, 1, 1, None, None) == -1
+    assert b"resident table needs" in lib.msa_last_error()
     # reduce modes
     assert lib.msa_route_chunk_scores(None, 1, 0, 0, 0, None, 0, 1, 32, 4, 8, 128, 7, 0, None, 1024, 4, 1.0, 0.0, None, 5,
                                       None) == -1
