@@ -216,7 +216,7 @@ class SparseDecodeModel:
         s = self.s
         world = max(1, self.svc.world_size)
         scoring_s = rk.numel() * rk.element_size() / 6.5e12
-        fetch_bytes = self.batch * self.retrieved * 2 * s.n_kv_heads * s.head_dim * self.dtype.itemsize / world
+        fetch_bytes = self.batch * self.retrieved * 2 * s.n_kv_heads * s.head_dim * self.dtype.itemsize   # this rank's sequences
         gather_s = fetch_bytes / min(48e9, 80e9 / world)
         return "routing" if scoring_s >= gather_s else "dense"
 

@@ -174,7 +174,7 @@ def test_decode_loop_places_the_host_gather_by_shard_and_fetch_size():
         for stored in ("rows", "blocked"):
             blk = SimpleNamespace(rk=rk if stored == "rows" else None, rk_blocked=None if stored == "rows" else rk)
             me = SimpleNamespace(svc=SimpleNamespace(blocks={18: blk, 19: blk}, world_size=world), router_layers={18, 19}, s=shape,
-                                 batch=32, retrieved=128, dtype=torch.bfloat16)
+                                 batch=32 // world, retrieved=128, dtype=torch.bfloat16)      # a rank decodes its share of the batch
             picks[world, stored] = SparseDecodeModel._fetch_placement(me)
     assert [picks[w, "rows"] for w in (1, 2, 4, 8)] == ["routing", "routing", "dense", "dense"]
     assert all(picks[w, "blocked"] == picks[w, "rows"] for w in (1, 2, 4, 8))
